@@ -1,0 +1,353 @@
+"""TEST INFRASTRUCTURE -- not product code.
+
+Python face of the CPU checker: ctypes bindings over ``_build/liboracle.so`` (the plain-C
+restatement in ``flint_oracle.c``) and, when it was built, over ``_ref/libflint_cpu.so`` -- the
+reference's own CPU backend, whose float32 ``fl_matmul`` (flint/cpu/matmul.cc:306-322) then does
+the heavy product. Only tests, the smoke check and the bench's CPU-baseline leg import this.
+
+16-bit floats travel as ``numpy.uint16`` bit patterns; codes as ``numpy.uint8``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from ctypes import POINTER, c_float, c_int, c_int32, c_int64, c_uint8, c_uint16, c_void_p
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(HERE, "_build", "liboracle.so")
+REF_SO = os.path.join(HERE, "_ref", "libflint_cpu.so")
+
+ACT_NONE = 0
+ACT_GELU_TANH = 1
+
+
+def build(ref: bool = True) -> None:
+    """Compile the C restatement, and the reference's CPU library where its checkout exists."""
+    subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
+    if ref and os.path.isdir(os.environ.get("FLINT_REFERENCE_DIR", "/root/reference")):
+        subprocess.run(["make", "-s", "-C", HERE, "ref", "-j8"], check=True)
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(ORACLE_SO):
+            build(ref=False)
+        L = ctypes.CDLL(ORACLE_SO)
+        u8p, u16p, f32p, f64p = POINTER(c_uint8), POINTER(c_uint16), POINTER(c_float), POINTER(ctypes.c_double)
+        L.fo_e4m3_decode.argtypes = [c_uint8]; L.fo_e4m3_decode.restype = c_float
+        L.fo_e4m3_encode.argtypes = [c_float]; L.fo_e4m3_encode.restype = c_uint8
+        L.fo_e2m1_decode.argtypes = [c_uint8]; L.fo_e2m1_decode.restype = c_float
+        L.fo_e2m1_encode.argtypes = [c_float]; L.fo_e2m1_encode.restype = c_uint8
+        L.fo_bf16_from_f32.argtypes = [c_float]; L.fo_bf16_from_f32.restype = c_uint16
+        L.fo_bf16_to_f32.argtypes = [c_uint16]; L.fo_bf16_to_f32.restype = c_float
+        L.fo_f16_from_f32.argtypes = [c_float]; L.fo_f16_from_f32.restype = c_uint16
+        L.fo_f16_to_f32.argtypes = [c_uint16]; L.fo_f16_to_f32.restype = c_float
+        L.fo_quantize_fp8_tensor.argtypes = [f32p, c_int64, u8p, f32p]
+        L.fo_quantize_fp8_rows.argtypes = [f32p, c_int, c_int, u8p, f32p]
+        L.fo_quantize_fp8_act.argtypes = [u16p, c_int, c_int, c_int, u8p, f32p]
+        L.fo_quantize_nvfp4_weight.argtypes = [f32p, c_int, c_int, u8p, u8p, f32p]
+        L.fo_quantize_nvfp4_act.argtypes = [u16p, c_int, c_int, c_int, u8p, u8p]
+        L.fo_decode_e4m3.argtypes = [u8p, c_int64, f32p]
+        L.fo_decode_nvfp4.argtypes = [u8p, u8p, c_int, c_int, f32p]
+        L.fo_widen_16.argtypes = [u16p, c_int, c_int64, f32p]
+        L.fo_gemm_f32_nt.argtypes = [f32p, f32p, f32p, c_int, c_int, c_int]
+        L.fo_gemm_f64_nt.argtypes = [f32p, f32p, f64p, c_int, c_int, c_int]
+        L.fo_epilogue.argtypes = [f32p, c_int, c_int, f32p, f32p, c_int, c_float, u16p, u16p,
+                                  c_int, c_int, u16p]
+        _lib = L
+    return _lib
+
+
+def _p(a: np.ndarray | None, ctype):
+    if a is None:
+        return None
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(POINTER(ctype))
+
+
+# ---- codecs -------------------------------------------------------------------------------
+
+def e4m3_decode_table() -> np.ndarray:
+    return np.array([lib().fo_e4m3_decode(c) for c in range(256)], dtype=np.float32)
+
+
+def e4m3_encode(x: np.ndarray) -> np.ndarray:
+    L = lib()
+    flat = np.ascontiguousarray(x, dtype=np.float32).ravel()
+    return np.array([L.fo_e4m3_encode(float(v)) for v in flat], dtype=np.uint8).reshape(np.shape(x))
+
+
+def e2m1_encode(x: np.ndarray) -> np.ndarray:
+    L = lib()
+    flat = np.ascontiguousarray(x, dtype=np.float32).ravel()
+    return np.array([L.fo_e2m1_encode(float(v)) for v in flat], dtype=np.uint8).reshape(np.shape(x))
+
+
+def widen(x16: np.ndarray, is_bf16: bool) -> np.ndarray:
+    x16 = np.ascontiguousarray(x16, dtype=np.uint16)
+    out = np.empty(x16.shape, dtype=np.float32)
+    lib().fo_widen_16(_p(x16, c_uint16), int(is_bf16), x16.size, _p(out, c_float))
+    return out
+
+
+def narrow(x: np.ndarray, is_bf16: bool) -> np.ndarray:
+    """float32 -> bf16/fp16 bit patterns, RNE (vectorised restatement for bf16; scalar for fp16)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    if is_bf16:
+        bits = x.view(np.uint32).astype(np.uint64)
+        nan = (bits & 0x7FFFFFFF) > 0x7F800000
+        rounded = (bits + 0x7FFF + ((bits >> 16) & 1)) >> 16
+        rounded = np.where(nan, (bits >> 16) | 0x40, rounded)
+        return rounded.astype(np.uint16)
+    return x.astype(np.float16).view(np.uint16)  # numpy's cast is RNE; checked against fo_f16_from_f32
+
+
+# ---- quantizers ---------------------------------------------------------------------------
+
+def quantize_fp8_tensor(w: np.ndarray):
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    codes = np.empty(w.shape, dtype=np.uint8)
+    scale = np.zeros(1, dtype=np.float32)
+    lib().fo_quantize_fp8_tensor(_p(w, c_float), w.size, _p(codes, c_uint8), _p(scale, c_float))
+    return codes, scale
+
+
+def quantize_fp8_rows(w: np.ndarray):
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    rows, k = w.shape
+    codes = np.empty((rows, k), dtype=np.uint8)
+    scales = np.zeros(rows, dtype=np.float32)
+    lib().fo_quantize_fp8_rows(_p(w, c_float), rows, k, _p(codes, c_uint8), _p(scales, c_float))
+    return codes, scales
+
+
+def quantize_fp8_act(x16: np.ndarray, is_bf16: bool):
+    x16 = np.ascontiguousarray(x16, dtype=np.uint16)
+    rows, k = x16.shape
+    codes = np.empty((rows, k), dtype=np.uint8)
+    scales = np.zeros(rows, dtype=np.float32)
+    lib().fo_quantize_fp8_act(_p(x16, c_uint16), int(is_bf16), rows, k, _p(codes, c_uint8), _p(scales, c_float))
+    return codes, scales
+
+
+def quantize_nvfp4_weight(w: np.ndarray):
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    rows, k = w.shape
+    assert k % 16 == 0
+    codes = np.empty((rows, k // 2), dtype=np.uint8)
+    sf = np.empty((rows, k // 16), dtype=np.uint8)
+    g = np.zeros(1, dtype=np.float32)
+    lib().fo_quantize_nvfp4_weight(_p(w, c_float), rows, k, _p(codes, c_uint8), _p(sf, c_uint8), _p(g, c_float))
+    return codes, sf, g
+
+
+def quantize_nvfp4_act(x16: np.ndarray, is_bf16: bool):
+    x16 = np.ascontiguousarray(x16, dtype=np.uint16)
+    rows, k = x16.shape
+    assert k % 16 == 0
+    codes = np.empty((rows, k // 2), dtype=np.uint8)
+    sf = np.empty((rows, k // 16), dtype=np.uint8)
+    lib().fo_quantize_nvfp4_act(_p(x16, c_uint16), int(is_bf16), rows, k, _p(codes, c_uint8), _p(sf, c_uint8))
+    return codes, sf
+
+
+def decode_e4m3(codes: np.ndarray) -> np.ndarray:
+    codes = np.ascontiguousarray(codes, dtype=np.uint8)
+    out = np.empty(codes.shape, dtype=np.float32)
+    lib().fo_decode_e4m3(_p(codes, c_uint8), codes.size, _p(out, c_float))
+    return out
+
+
+def decode_nvfp4(codes: np.ndarray, sf: np.ndarray) -> np.ndarray:
+    codes = np.ascontiguousarray(codes, dtype=np.uint8)
+    sf = np.ascontiguousarray(sf, dtype=np.uint8)
+    rows, k = codes.shape[0], codes.shape[1] * 2
+    out = np.empty((rows, k), dtype=np.float32)
+    lib().fo_decode_nvfp4(_p(codes, c_uint8), _p(sf, c_uint8), rows, k, _p(out, c_float))
+    return out
+
+
+# ---- float32 product: the reference's own fl_matmul when built, else the C port ------------
+
+class _Ref:
+    """Minimal ctypes use of the reference's C ABI (flint/capi.h:151-234,440-446)."""
+
+    def __init__(self):
+        L = ctypes.CDLL(REF_SO)
+        self.L = L
+        L.fl_init.restype = None
+        L.fl_get_last_error_message.restype = ctypes.c_char_p
+        L.fl_operators_create.argtypes = [c_int, POINTER(c_void_p)]
+        L.fl_tensor_data_borrow.argtypes = [c_void_p, c_int, c_int64, POINTER(c_void_p)]
+        L.fl_tensor_data_destroy.argtypes = [c_void_p]; L.fl_tensor_data_destroy.restype = None
+        L.fl_tensor_view_create.argtypes = [c_void_p, POINTER(c_int32), POINTER(c_int32), c_int32, c_int64, POINTER(c_void_p)]
+        L.fl_tensor_view_destroy.argtypes = [c_void_p]; L.fl_tensor_view_destroy.restype = None
+        L.fl_matmul.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p]
+        L.fl_init()
+        self.ops = c_void_p()
+        self._check(L.fl_operators_create(0, ctypes.byref(self.ops)))
+
+    def _check(self, code):
+        if code != 0:
+            raise RuntimeError("reference flint: " + self.L.fl_get_last_error_message().decode())
+
+    def _view(self, arr: np.ndarray, shape, stride):
+        data = c_void_p()
+        self._check(self.L.fl_tensor_data_borrow(arr.ctypes.data_as(c_void_p), 1, arr.size, ctypes.byref(data)))
+        view = c_void_p()
+        sh = (c_int32 * len(shape))(*shape)
+        st = (c_int32 * len(stride))(*stride)
+        self._check(self.L.fl_tensor_view_create(data, sh, st, len(shape), 0, ctypes.byref(view)))
+        return data, view
+
+    def matmul_nt(self, a: np.ndarray, b: np.ndarray) -> np.ndarray:
+        """a (m,k) times the transpose of b (n,k), both float32, through fl_matmul."""
+        m, k = a.shape
+        n = b.shape[0]
+        out = np.empty((m, n), dtype=np.float32)
+        da, va = self._view(a, (m, k), (k, 1))
+        db, vb = self._view(b, (k, n), (1, k))  # the transpose as a view: no copy
+        do, vo = self._view(out, (m, n), (n, 1))
+        try:
+            self._check(self.L.fl_matmul(self.ops, va, vb, vo))
+        finally:
+            for v in (va, vb, vo):
+                self.L.fl_tensor_view_destroy(v)
+            for d in (da, db, do):
+                self.L.fl_tensor_data_destroy(d)
+        return out
+
+
+_ref = None
+
+
+def have_ref() -> bool:
+    return os.path.exists(REF_SO)
+
+
+def ref() -> _Ref:
+    global _ref
+    if _ref is None:
+        _ref = _Ref()
+    return _ref
+
+
+def gemm_f32_nt(a: np.ndarray, b: np.ndarray, engine: str = "auto") -> np.ndarray:
+    """C = A Bt in float32. engine: "auto" (reference build if present), "reference", "port"."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    if engine == "reference" or (engine == "auto" and have_ref()):
+        return ref().matmul_nt(a, b)
+    m, k = a.shape
+    n = b.shape[0]
+    out = np.empty((m, n), dtype=np.float32)
+    lib().fo_gemm_f32_nt(_p(a, c_float), _p(b, c_float), _p(out, c_float), m, n, k)
+    return out
+
+
+def gemm_f64_nt(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    m, k = a.shape
+    n = b.shape[0]
+    out = np.empty((m, n), dtype=np.float64)
+    lib().fo_gemm_f64_nt(_p(a, c_float), _p(b, c_float), _p(out, ctypes.c_double), m, n, k)
+    return out
+
+
+def epilogue(acc, row_scale=None, col_scale=None, global_scale=1.0, bias=None, residual=None,
+             act=ACT_NONE, out_is_bf16=True) -> np.ndarray:
+    acc = np.ascontiguousarray(acc, dtype=np.float32)
+    m, n = acc.shape
+    out = np.empty((m, n), dtype=np.uint16)
+    cs = None if col_scale is None else np.ascontiguousarray(col_scale, dtype=np.float32).ravel()
+    rs = None if row_scale is None else np.ascontiguousarray(row_scale, dtype=np.float32).ravel()
+    if rs is not None:
+        assert rs.size == m
+    if cs is not None:
+        assert cs.size in (1, n)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.uint16).ravel()
+    r = None if residual is None else np.ascontiguousarray(residual, dtype=np.uint16).reshape(m, n)
+    lib().fo_epilogue(_p(acc, c_float), m, n, _p(rs, c_float), _p(cs, c_float),
+                      0 if cs is None else cs.size, float(global_scale), _p(b, c_uint16),
+                      _p(r, c_uint16), int(act), int(out_is_bf16), _p(out, c_uint16))
+    return out
+
+
+# ---- the three linears, end to end ---------------------------------------------------------
+
+def fp8_matmul(a16, codes, scale, addend=None, is_bf16=False, engine="auto"):
+    """The reference's fl_fp8_matmul[_add] (flint/capi.cc:1047-1097): 16-bit activation, NOT
+    narrowed, times the e4m3 weight's values, times one scale, plus addend, one rounding."""
+    a16 = np.ascontiguousarray(a16, dtype=np.uint16)
+    lead = a16.shape[:-1]
+    k = a16.shape[-1]
+    a = widen(a16.reshape(-1, k), is_bf16)
+    w = decode_e4m3(codes)
+    acc = gemm_f32_nt(a, w, engine)
+    m, n = acc.shape
+    bias = residual = None
+    if addend is not None:
+        addend = np.asarray(addend, dtype=np.uint16)
+        if addend.size == n and addend.ndim == 1:
+            bias = addend
+        else:
+            residual = np.broadcast_to(addend, lead + (n,)).reshape(m, n)
+    out = epilogue(acc, None, np.asarray(scale, dtype=np.float32), 1.0, bias, residual, ACT_NONE, is_bf16)
+    return out.reshape(lead + (n,))
+
+
+def fp8_linear(x16, codes, scales, bias=None, residual=None, act=ACT_NONE, is_bf16=True, engine="auto"):
+    """Dynamic per-token e4m3 activation x e4m3 weight (per-channel or per-tensor scale)."""
+    x16 = np.ascontiguousarray(x16, dtype=np.uint16)
+    lead = x16.shape[:-1]
+    k = x16.shape[-1]
+    xc, xs = quantize_fp8_act(x16.reshape(-1, k), is_bf16)
+    acc = gemm_f32_nt(decode_e4m3(xc), decode_e4m3(codes), engine)
+    m, n = acc.shape
+    res = None if residual is None else np.asarray(residual, dtype=np.uint16).reshape(m, n)
+    out = epilogue(acc, xs, scales, 1.0, bias, res, act, is_bf16)
+    return out.reshape(lead + (n,))
+
+
+def nvfp4_linear(x16, codes, block_scales, global_scale, bias=None, residual=None, act=ACT_NONE,
+                 is_bf16=True, engine="auto"):
+    """Dynamic per-16-block e2m1 activation x NVFP4 weight, fp32 accumulate."""
+    x16 = np.ascontiguousarray(x16, dtype=np.uint16)
+    lead = x16.shape[:-1]
+    k = x16.shape[-1]
+    xc, xsf = quantize_nvfp4_act(x16.reshape(-1, k), is_bf16)
+    acc = gemm_f32_nt(decode_nvfp4(xc, xsf), decode_nvfp4(codes, block_scales), engine)
+    m, n = acc.shape
+    res = None if residual is None else np.asarray(residual, dtype=np.uint16).reshape(m, n)
+    g = float(np.asarray(global_scale, dtype=np.float32).ravel()[0])
+    out = epilogue(acc, None, None, g, bias, res, act, is_bf16)
+    return out.reshape(lead + (n,))
+
+
+# ---- error measures the parity tests use ---------------------------------------------------
+
+def rel_l2(y: np.ndarray, ref_: np.ndarray) -> float:
+    """flint/cuda/gemm_fp8_cutlass_test.cc:77-92 (relativeRmse)."""
+    y = np.asarray(y, dtype=np.float64)
+    ref_ = np.asarray(ref_, dtype=np.float64)
+    den = float(np.sum(ref_ * ref_))
+    num = float(np.sum((y - ref_) ** 2))
+    if den == 0.0:
+        return 0.0 if num == 0.0 else float("inf")
+    return float(np.sqrt(num / den))
+
+
+def ulp16_at(scale_value: float, is_bf16: bool) -> float:
+    """One ulp of the 16-bit output type at the magnitude `scale_value`."""
+    if scale_value <= 0 or not np.isfinite(scale_value):
+        return 0.0
+    e = int(np.floor(np.log2(scale_value)))
+    return float(2.0 ** (e - (7 if is_bf16 else 10)))
