@@ -1,0 +1,184 @@
+/* flint_sm100.h -- C ABI of libflint_sm100.so: a B200 (sm_100a) implementation of the quantized
+ * matmul/linear path of flint, the tensor library of ling0322/libwaifu.
+ *
+ * Part 1 repeats, signature for signature and value for value, the subset of the reference's
+ * flint/capi.h that a caller needs to reach the FP8 product: error reporting, storage, views,
+ * transfers and fl_fp8_available / fl_fp8_matmul / fl_fp8_matmul_add. A program (or the Rust FFI
+ * in waifu/src/flint/ffi.rs) written against those declarations links against this library
+ * unchanged. Each declaration cites the reference interface it replaces as file:line.
+ *
+ * Part 2 is additive: new enum values appended after the reference's, and new entry points with
+ * new names (bf16, per-output-channel scales, dynamic activation quantisation, fused
+ * bias/GELU/residual, NVFP4). Nothing in part 1 changes meaning because of it.
+ *
+ * Conventions (flint/capi.h:20-54): every call returns FL_OK or an error code and leaves a
+ * message readable through fl_get_last_error_message() on the calling thread; no exception
+ * crosses the boundary. Work on the GPU is enqueued on the legacy default stream and calls
+ * return without synchronising (flint/cuda/common.h:51-55); a transfer to the host synchronises.
+ */
+#ifndef FLINT_SM100_H_
+#define FLINT_SM100_H_
+
+#include <stdint.h>
+
+#if defined(_WIN32)
+#define FLAPI
+#else
+#define FLAPI __attribute__((visibility("default")))
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ======================= Part 1: the reference's declarations ============================= */
+
+/* flint/capi.h:48-54 */
+#define FL_OK 0
+#define FL_ERROR_INVALID_ARG 0x0100
+#define FL_ERROR_ABORTED 0x0102
+#define FL_ERROR_OUT_OF_MEMORY 0x0103
+
+/* flint/capi.h:57-82 */
+typedef struct fl_tensor_data_impl_t *fl_tensor_data_t;
+typedef struct fl_tensor_view_impl_t *fl_tensor_view_t;
+typedef struct fl_operators_impl_t *fl_operators_t;
+
+/* flint/capi.h:84-94. 5 and 7 are holes in the reference and stay holes. 11 and 12 are additive. */
+typedef enum fl_dtype_t {
+  FL_DTYPE_UNKNOWN = 0,
+  FL_DTYPE_FLOAT = 1,
+  FL_DTYPE_LONG = 2,
+  FL_DTYPE_UINT8 = 3,
+  FL_DTYPE_FLOAT16 = 4,
+  FL_DTYPE_INT8 = 6,
+  FL_DTYPE_BOOL = 8,
+  FL_DTYPE_INT32 = 9,
+  FL_DTYPE_FP8E4M3 = 10,
+  /* additive (part 2) */
+  FL_DTYPE_BFLOAT16 = 11,
+  /* Two e2m1 values per element (one byte): low nibble is the even k. A view's last dimension
+   * counts bytes, i.e. k / 2. */
+  FL_DTYPE_FP4E2M1X2 = 12,
+} fl_dtype_t;
+
+/* flint/capi.h:96-106 */
+typedef enum fl_device_type_t {
+  FL_DEVICE_CPU = 0,
+  FL_DEVICE_CUDA = 1,
+  FL_DEVICE_CUDA_HOST = 2,
+  FL_DEVICE_METAL = 3,
+  FL_DEVICE_VULKAN = 4,
+  FL_DEVICE_UNKNOWN = 5,
+} fl_device_type_t;
+
+/* flint/capi.h:137-147 */
+typedef enum fl_alloc_hint_t {
+  FL_ALLOC_ACTIVATION = 0,
+  FL_ALLOC_WEIGHT = 1,
+  FL_ALLOC_OTHER = 2,
+  FL_ALLOC_TEMPORARY_WEIGHT = 3,
+} fl_alloc_hint_t;
+
+/* flint/capi.h:151. Picks up the CUDA device; later calls do nothing. */
+FLAPI void fl_init(void);
+/* flint/capi.h:155. CPU (storage only), CUDA and CUDA_HOST report 1 when a B200-class card exists. */
+FLAPI int32_t fl_is_device_available(fl_device_type_t device, int32_t *out);
+/* flint/capi.h:158,162 */
+FLAPI int32_t fl_get_last_error_code(void);
+FLAPI const char *fl_get_last_error_message(void);
+/* flint/capi.h:169-175. Only FL_DEVICE_CUDA has operators in this library. */
+FLAPI int32_t fl_operators_create(fl_device_type_t device, fl_operators_t *out);
+FLAPI void fl_operators_destroy(fl_operators_t operators);
+FLAPI int32_t fl_operators_get_device(fl_operators_t operators, fl_device_type_t *out);
+
+/* flint/capi.h:185-213 (storage) */
+FLAPI int32_t fl_tensor_data_create(fl_device_type_t device, fl_dtype_t dtype, int64_t numel, fl_alloc_hint_t hint,
+                                    fl_tensor_data_t *out);
+FLAPI int32_t fl_tensor_data_borrow(const void *data, fl_dtype_t dtype, int64_t numel, fl_tensor_data_t *out);
+FLAPI void fl_tensor_data_destroy(fl_tensor_data_t data);
+FLAPI int32_t fl_tensor_data_get_host_ptr(fl_tensor_data_t data, void **out);
+
+/* flint/capi.h:217-234 (views: shape/stride/offset count elements; stride 0 repeats) */
+FLAPI int32_t fl_tensor_view_create(fl_tensor_data_t data, const int32_t *shape, const int32_t *stride, int32_t ndim,
+                                    int64_t offset, fl_tensor_view_t *out);
+FLAPI void fl_tensor_view_destroy(fl_tensor_view_t view);
+
+/* flint/capi.h:254. Contiguous src -> contiguous dest on another device, same shape and dtype. */
+FLAPI int32_t fl_transfer(fl_operators_t operators, fl_tensor_view_t src, fl_tensor_view_t dest);
+
+/* flint/capi.h:458-460, flint/capi.cc:1039-1045. 1 for FL_DEVICE_CUDA on compute capability 10.x,
+ * 0 for every other device or card, never an error for a missing device. */
+FLAPI int32_t fl_fp8_available(fl_device_type_t device, int32_t *out);
+
+/* flint/capi.h:462-468, flint/capi.cc:1047-1053.
+ * a <float16>(..., k) times the transpose of data <fp8e4m3>(rows, k) times its one <float> scale,
+ * into out <float16>(..., rows). rows a multiple of 8, k of 16. The activation is NOT narrowed:
+ * the weight is widened to half and multiplied in half with fp32 accumulation, as the reference
+ * does (flint/cuda/gemm_fp8_cutlass.cu:20-29). <bfloat16> a/out is accepted too (additive). */
+FLAPI int32_t fl_fp8_matmul(fl_tensor_view_t a, fl_tensor_view_t data, fl_tensor_view_t scale, fl_tensor_view_t out);
+
+/* flint/capi.h:470-478, flint/capi.cc:1055-1097. addend <float16> broadcast over out's leading
+ * dimensions: a bias (rows), or a residual; added to the fp32 sum after the scale, one rounding
+ * (flint/cuda/gemm_fp8_cutlass.cu:409-426). */
+FLAPI int32_t fl_fp8_matmul_add(fl_tensor_view_t a, fl_tensor_view_t data, fl_tensor_view_t scale,
+                                fl_tensor_view_t addend, fl_tensor_view_t out);
+
+/* ======================= Part 2: additive entry points ==================================== */
+
+/* Activation applied by the fused epilogue. */
+typedef enum fl_activation_t {
+  FL_ACT_NONE = 0,
+  FL_ACT_GELU_TANH = 1, /* 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), waifu/src/krea2/dit.rs:170-188 */
+} fl_activation_t;
+
+/* FP8 linear with both operands narrow:
+ *   a <float16|bfloat16>(..., k) is quantised on the fly, per row (token): s_m = amax_m / 448,
+ *   code = e4m3(a / s_m); data <fp8e4m3>(rows, k); scales <float>(rows) per output channel or
+ *   <float>(1) per tensor (the reference's format, docs/fp8.md:16-18).
+ *   out = round16( act( acc * (s_m * scale_n) + bias_n ) + residual_mn ),   fp32 until the end.
+ * bias (rows), residual of out's shape; either may be NULL. rows a multiple of 8, k of 16.
+ * No counterpart in the reference, whose activations stay in half. */
+FLAPI int32_t fl_fp8_linear(fl_tensor_view_t a, fl_tensor_view_t data, fl_tensor_view_t scales, fl_tensor_view_t bias,
+                            fl_tensor_view_t residual, int32_t act, fl_tensor_view_t out);
+
+/* 1 where fl_nvfp4_linear can run (the same cards as fl_fp8_available). */
+FLAPI int32_t fl_nvfp4_available(fl_device_type_t device, int32_t *out);
+
+/* NVFP4 linear:
+ *   codes <fp4e2m1x2>(rows, k/2); block_scales <fp8e4m3>(rows, k/16), unsigned, one per 16
+ *   consecutive k; global_scale <float>(1). a is quantised on the fly per 16-element block:
+ *   s = e4m3(amax_block / 6), code = e2m1(a / s), global 1.
+ *   out = round16( act( acc * global_scale + bias_n ) + residual_mn ).
+ * rows a multiple of 8, k of 32. No counterpart in the reference (it has no FP4 of any kind). */
+FLAPI int32_t fl_nvfp4_linear(fl_tensor_view_t a, fl_tensor_view_t codes, fl_tensor_view_t block_scales,
+                              fl_tensor_view_t global_scale, fl_tensor_view_t bias, fl_tensor_view_t residual,
+                              int32_t act, fl_tensor_view_t out);
+
+/* Device-side weight preparation, the rule of tools/model_writer.py:143-174 applied per row:
+ * w <float>(rows, k) -> codes <fp8e4m3>(rows, k), scales <float>(rows). */
+FLAPI int32_t fl_quantize_fp8_rows(fl_tensor_view_t w, fl_tensor_view_t codes, fl_tensor_view_t scales);
+/* w <float>(rows, k) -> NVFP4 codes, block scales and the global scale (amax / (448 * 6)). */
+FLAPI int32_t fl_quantize_nvfp4(fl_tensor_view_t w, fl_tensor_view_t codes, fl_tensor_view_t block_scales,
+                                fl_tensor_view_t global_scale);
+/* The dynamic activation quantiser on its own (what fl_fp8_linear applies to `a`), for tests:
+ * a <float16|bfloat16>(m, k) -> codes <fp8e4m3>(m, k), scales <float>(m). */
+FLAPI int32_t fl_quantize_fp8_activation(fl_tensor_view_t a, fl_tensor_view_t codes, fl_tensor_view_t scales);
+
+/* Storage over device memory the caller already owns (for instance a torch tensor's): nothing
+ * is copied and nothing is freed on destroy. The device counterpart of fl_tensor_data_borrow(). */
+FLAPI int32_t fl_tensor_data_borrow_device(void *device_ptr, fl_dtype_t dtype, int64_t numel, fl_tensor_data_t *out);
+
+/* Selects the CUDA device this thread's later calls use (one process per GPU sets its own). */
+FLAPI int32_t fl_sm100_set_device(int32_t ordinal);
+/* Waits for the default stream, then reports the kernels' status word: 0, or the code of the
+ * bounded wait that gave up inside a kernel (the call then also returns FL_ERROR_ABORTED). */
+FLAPI int32_t fl_sm100_synchronize(int32_t *kernel_status);
+/* How many kernels of this library the calling process has launched so far. */
+FLAPI int64_t fl_sm100_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FLINT_SM100_H_ */

@@ -1,0 +1,1035 @@
+// The C ABI of libflint_sm100.so (declared in include/flint_sm100.h): handles, the thread-local
+// error, the argument checks of flint's FP8 entry points (flint/capi.cc:955-1097) restated, and
+// the dispatch into the sm_100a kernels. There is no CPU path: a call that cannot run on the GPU
+// fails with an error code.
+#include "../../include/flint_sm100.h"
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "gemm_sm100.cuh"
+#include "quant_sm100.cuh"
+
+using namespace flsm100;
+
+struct fl_tensor_data_impl_t {
+  void *ptr = nullptr;
+  int64_t numel = 0;
+  fl_dtype_t dtype = FL_DTYPE_UNKNOWN;
+  fl_device_type_t device = FL_DEVICE_UNKNOWN;
+  bool owned = false;
+};
+
+struct fl_tensor_view_impl_t {
+  fl_tensor_data_impl_t *data = nullptr;
+  std::vector<int32_t> shape;
+  std::vector<int32_t> stride;
+  int64_t offset = 0;
+};
+
+struct fl_operators_impl_t {
+  fl_device_type_t device;
+};
+
+namespace {
+
+// ---- errors ------------------------------------------------------------------------------
+
+struct FlError {
+  int32_t code;
+  std::string message;
+};
+
+[[noreturn]] void invalid(const std::string &m) { throw FlError{FL_ERROR_INVALID_ARG, m}; }
+[[noreturn]] void aborted(const std::string &m) { throw FlError{FL_ERROR_ABORTED, m}; }
+
+thread_local int32_t t_code = FL_OK;
+thread_local std::string t_message;
+
+int32_t set_error(int32_t code, const std::string &message) {
+  t_code = code;
+  t_message = message;
+  return code;
+}
+
+int32_t clear_error() {
+  t_code = FL_OK;
+  t_message.clear();
+  return FL_OK;
+}
+
+// Runs `body`; whatever it throws becomes an error code (flint/capi.cc:191-206).
+template <typename Body>
+int32_t guard(Body &&body) {
+  try {
+    return body();
+  } catch (const FlError &e) {
+    return set_error(e.code, e.message);
+  } catch (const std::bad_alloc &) {
+    return set_error(FL_ERROR_ABORTED, "out of memory");
+  } catch (const std::exception &e) {
+    return set_error(FL_ERROR_ABORTED, e.what());
+  } catch (...) {
+    return set_error(FL_ERROR_ABORTED, "unknown exception");
+  }
+}
+
+void cuda_check(cudaError_t e, const char *what) {
+  if (e == cudaSuccess) return;
+  std::string m = std::string(what) + ": " + cudaGetErrorString(e);
+  if (e == cudaErrorMemoryAllocation) throw FlError{FL_ERROR_OUT_OF_MEMORY, m};
+  aborted(m);
+}
+
+// ---- dtypes ------------------------------------------------------------------------------
+
+int64_t dtype_size(fl_dtype_t t) {
+  switch (t) {
+    case FL_DTYPE_FLOAT: return 4;
+    case FL_DTYPE_LONG: return 8;
+    case FL_DTYPE_UINT8: return 1;
+    case FL_DTYPE_FLOAT16: return 2;
+    case FL_DTYPE_INT8: return 1;
+    case FL_DTYPE_BOOL: return 1;
+    case FL_DTYPE_INT32: return 4;
+    case FL_DTYPE_FP8E4M3: return 1;
+    case FL_DTYPE_BFLOAT16: return 2;
+    case FL_DTYPE_FP4E2M1X2: return 1;
+    default: invalid("unknown dtype");
+  }
+}
+
+const char *device_name(fl_device_type_t d) {
+  switch (d) {
+    case FL_DEVICE_CPU: return "cpu";
+    case FL_DEVICE_CUDA: return "cuda";
+    case FL_DEVICE_CUDA_HOST: return "cuda_host";
+    case FL_DEVICE_METAL: return "metal";
+    case FL_DEVICE_VULKAN: return "vulkan";
+    default: return "unknown";
+  }
+}
+
+// ---- the device --------------------------------------------------------------------------
+
+struct DeviceState {
+  bool probed = false;
+  bool present = false;  // a CUDA device exists
+  bool sm100 = false;    // and it is compute capability 10.x
+  // Kernel status word in mapped host memory: kernels write it, the host reads it without a copy.
+  uint32_t *status_host = nullptr;
+  uint32_t *status_dev = nullptr;
+  // Grow-only scratch for quantised activations, re-tiled scale factors and widened weights.
+  // All work is ordered on the legacy default stream, so one arena can be reused call after call.
+  uint8_t *scratch = nullptr;
+  size_t scratch_cap = 0;
+};
+
+std::mutex g_mutex;
+DeviceState g_dev;
+std::atomic<int64_t> g_gemm_launches{0};
+
+void probe_locked() {
+  if (g_dev.probed) return;
+  g_dev.probed = true;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count < 1) {
+    cudaGetLastError();
+    return;
+  }
+  g_dev.present = true;
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess &&
+      cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) == cudaSuccess) {
+    g_dev.sm100 = (major == 10);
+  }
+}
+
+DeviceState &device_state() {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  probe_locked();
+  return g_dev;
+}
+
+void require_kernels() {
+  DeviceState &d = device_state();
+  if (!d.present) aborted("no CUDA device is present");
+  if (!d.sm100) aborted("the CUDA device is not compute capability 10.x; these kernels are sm_100a only");
+}
+
+uint32_t *status_word() {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_dev.status_host) {
+    void *h = nullptr;
+    cuda_check(cudaHostAlloc(&h, 64, cudaHostAllocMapped), "cudaHostAlloc(status)");
+    std::memset(h, 0, 64);
+    void *d = nullptr;
+    cuda_check(cudaHostGetDevicePointer(&d, h, 0), "cudaHostGetDevicePointer(status)");
+    g_dev.status_host = static_cast<uint32_t *>(h);
+    g_dev.status_dev = static_cast<uint32_t *>(d);
+  }
+  return g_dev.status_dev;
+}
+
+// A kernel that gave up on a wait in an earlier call is reported by the next call.
+void check_earlier_kernel_status() {
+  uint32_t *h;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    h = g_dev.status_host;
+  }
+  if (h && *reinterpret_cast<volatile uint32_t *>(h) != 0) {
+    uint32_t code = *reinterpret_cast<volatile uint32_t *>(h);
+    *reinterpret_cast<volatile uint32_t *>(h) = 0;
+    aborted("an earlier kernel gave up on a bounded wait (status " + std::to_string(code) + ")");
+  }
+}
+
+// Bump allocation out of the scratch arena; `reset` at the start of every entry point.
+struct Scratch {
+  size_t used = 0;
+  std::vector<std::pair<size_t, size_t>> wants;  // (offset, bytes)
+
+  size_t reserve(size_t bytes) {
+    size_t off = (used + 255) & ~size_t(255);
+    used = off + bytes;
+    return off;
+  }
+  // Grows the arena if needed (a rare, synchronising event) and returns its base.
+  uint8_t *commit() {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (used > g_dev.scratch_cap) {
+      size_t cap = used + used / 4 + (1 << 20);
+      if (g_dev.scratch) {
+        cuda_check(cudaStreamSynchronize(0), "cudaStreamSynchronize before regrowing scratch");
+        cuda_check(cudaFree(g_dev.scratch), "cudaFree(scratch)");
+        g_dev.scratch = nullptr;
+        g_dev.scratch_cap = 0;
+      }
+      void *p = nullptr;
+      cuda_check(cudaMalloc(&p, cap), "cudaMalloc(scratch)");
+      g_dev.scratch = static_cast<uint8_t *>(p);
+      g_dev.scratch_cap = cap;
+    }
+    return g_dev.scratch;
+  }
+};
+
+// ---- views -------------------------------------------------------------------------------
+
+fl_tensor_data_impl_t &deref(fl_tensor_data_t d) {
+  if (!d) invalid("tensor data is null");
+  return *d;
+}
+
+fl_tensor_view_impl_t &deref(fl_tensor_view_t v) {
+  if (!v) invalid("tensor view is null");
+  return *v;
+}
+
+int64_t numel_of(const fl_tensor_view_impl_t &v) {
+  int64_t n = 1;
+  for (int32_t s : v.shape) n *= s;
+  return n;
+}
+
+// flint/tensor_view.cc:163-170
+bool is_contiguous(const fl_tensor_view_impl_t &v) {
+  int64_t numel = 1;
+  for (int i = static_cast<int>(v.shape.size()) - 1; i >= 0; --i) {
+    if (numel != v.stride[i] && v.shape[i] != 1) return false;
+    numel *= v.shape[i];
+  }
+  return true;
+}
+
+std::string shape_string(const std::vector<int32_t> &shape) {
+  std::string s = "(";
+  for (size_t i = 0; i < shape.size(); ++i) {
+    if (i) s += ", ";
+    s += std::to_string(shape[i]);
+  }
+  return s + ")";
+}
+
+uint8_t *raw_ptr(const fl_tensor_view_impl_t &v) {
+  return static_cast<uint8_t *>(v.data->ptr) + v.offset * dtype_size(v.data->dtype);
+}
+
+fl_dtype_t dtype_of(const fl_tensor_view_impl_t &v) { return v.data->dtype; }
+fl_device_type_t device_of(const fl_tensor_view_impl_t &v) { return v.data->device; }
+
+bool is_half_type(fl_dtype_t t) { return t == FL_DTYPE_FLOAT16 || t == FL_DTYPE_BFLOAT16; }
+
+void check_shape(const fl_tensor_view_impl_t &v, const std::vector<int32_t> &shape, const char *what) {
+  if (v.shape != shape) {
+    invalid(std::string(what) + " is " + shape_string(v.shape) + " where " + shape_string(shape) + " was expected");
+  }
+}
+
+// ---- the checks of flint/capi.cc:979-1035, restated --------------------------------------
+
+void check_fp8_weight(const fl_tensor_view_impl_t &data, const fl_tensor_view_impl_t &scale, bool per_channel_ok) {
+  if (dtype_of(data) != FL_DTYPE_FP8E4M3 || data.shape.size() != 2) {
+    invalid("fp8 operand: data is not <fp8e4m3>(rows, k)");
+  }
+  const int64_t sn = numel_of(scale);
+  if (dtype_of(scale) != FL_DTYPE_FLOAT || !(sn == 1 || (per_channel_ok && sn == data.shape[0]))) {
+    invalid(per_channel_ok ? "fp8 operand: the scale is not <float>(1) or <float>(rows)"
+                           : "fp8 operand: the scale is not a single <float>");
+  }
+  if (device_of(data) != device_of(scale)) invalid("fp8 operand: the data and the scale are on different devices");
+  if (!is_contiguous(data) || !is_contiguous(scale)) invalid("fp8 operand: not contiguous");
+  if (numel_of(data) >= INT32_MAX) invalid("fp8 operand: more elements than the kernels can index");
+}
+
+void check_activation(const fl_tensor_view_impl_t &x, fl_device_type_t device, const char *what) {
+  if (device_of(x) != device) invalid(std::string(what) + " is not on the same device as the weight");
+  if (!is_contiguous(x)) invalid(std::string(what) + " is not contiguous");
+  if (x.shape.size() < 2) invalid(std::string(what) + " has fewer than two dimensions");
+  if (!is_half_type(dtype_of(x))) {
+    invalid(std::string(what) + " is not <float16> (or <bfloat16>), which is what this device multiplies in");
+  }
+}
+
+void check_result(const fl_tensor_view_impl_t &out, const fl_tensor_view_impl_t &a, int rows,
+                  fl_device_type_t device) {
+  if (device_of(out) != device || dtype_of(out) != dtype_of(a)) {
+    invalid("out is not <float16> on the weight's device (or <bfloat16> where the left operand is)");
+  }
+  if (!is_contiguous(out)) invalid("out is not contiguous");
+  std::vector<int32_t> shape = a.shape;
+  shape.back() = rows;
+  check_shape(out, shape, "out");
+}
+
+void check_tiles(int rows, int k, int k_multiple) {
+  if (rows % 8 != 0) invalid("the fp8 operand's row count is not a multiple of 8");
+  if (k % k_multiple != 0) {
+    invalid("the " + std::string(k_multiple == 16 ? "fp8" : "nvfp4") + " operand's k is not a multiple of " +
+            std::to_string(k_multiple));
+  }
+}
+
+int64_t leading_rows(const fl_tensor_view_impl_t &a) {
+  int64_t m = 1;
+  for (size_t i = 0; i + 1 < a.shape.size(); ++i) m *= a.shape[i];
+  return m;
+}
+
+// How the epilogue reads an addend: as a bias, as rows that repeat with a period over m, or (when
+// neither fits) from an expanded copy in scratch.
+struct AddendPlan {
+  const void *bias = nullptr;
+  const void *residual = nullptr;
+  int residual_rows = 0;
+  int64_t residual_ld = 0;
+  bool needs_expand = false;
+};
+
+// `addend` broadcast over out's leading dimensions (right-aligned, each dimension 1 or equal).
+AddendPlan plan_addend(const fl_tensor_view_impl_t &addend, const fl_tensor_view_impl_t &out,
+                       std::vector<int32_t> *bshape, std::vector<int64_t> *bstride) {
+  const int od = static_cast<int>(out.shape.size());
+  const int ad = static_cast<int>(addend.shape.size());
+  const int n = out.shape.back();
+  if (ad < 1 || addend.shape.back() != n) invalid("the addend's last dimension is not out's");
+  bshape->assign(out.shape.begin(), out.shape.end());
+  bstride->assign(od, 0);
+  for (int i = 0; i < ad; ++i) {
+    const int o = od - ad + i;
+    if (addend.shape[i] == out.shape[o]) {
+      (*bstride)[o] = (addend.shape[i] == 1) ? 0 : addend.stride[i];
+    } else if (addend.shape[i] == 1) {
+      (*bstride)[o] = 0;
+    } else {
+      invalid("the addend does not broadcast over out's leading dimensions");
+    }
+  }
+  AddendPlan plan;
+  const void *base = raw_ptr(addend);
+  const bool unit_last = (n == 1) || (*bstride)[od - 1] == 1;
+  // Leading dimensions of extent 1 index nothing.
+  bool all_leading_zero = true;
+  for (int i = 0; i < od - 1; ++i) {
+    if (out.shape[i] != 1 && (*bstride)[i] != 0) all_leading_zero = false;
+  }
+  if (unit_last && all_leading_zero) {
+    plan.bias = base;  // (n), or a zero-stride expansion of it: read in the epilogue as a bias
+    return plan;
+  }
+  if (unit_last) {
+    // Rows with pitch L whose pattern repeats with period P over m: a suffix of the leading
+    // dimensions dense with pitch L, everything before it broadcast.
+    int i = od - 2;
+    while (i >= 0 && out.shape[i] == 1) --i;
+    if (i >= 0 && (*bstride)[i] >= n) {
+      const int64_t ld = (*bstride)[i];
+      int64_t period = 1;
+      int64_t expect = ld;
+      bool ok = true;
+      int j = i;
+      for (; j >= 0; --j) {
+        if (out.shape[j] == 1) continue;
+        if ((*bstride)[j] == expect) {
+          period *= out.shape[j];
+          expect *= out.shape[j];
+        } else {
+          break;
+        }
+      }
+      for (; j >= 0; --j) {
+        if (out.shape[j] != 1 && (*bstride)[j] != 0) ok = false;
+      }
+      if (ok && period <= INT32_MAX) {
+        plan.residual = base;
+        plan.residual_rows = static_cast<int>(period);
+        plan.residual_ld = ld;
+        return plan;
+      }
+    }
+  }
+  plan.needs_expand = true;
+  return plan;
+}
+
+struct Epilogue {
+  const float *row_scale = nullptr;
+  const float *col_scale = nullptr;
+  int col_scale_scalar = 0;
+  const float *global_scale = nullptr;
+  const void *bias = nullptr;
+  const void *residual = nullptr;
+  int residual_rows = 0;
+  int64_t residual_ld = 0;
+  int act = 0;
+};
+
+void run_gemm(GemmKind kind, int m, int n, int k, const void *a, const void *b, const uint8_t *sfa,
+              const uint8_t *sfb, const Epilogue &ep, int out_bf16, void *out) {
+  GemmArgs g{};
+  g.kind = kind;
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  g.a = a;
+  g.b = b;
+  g.sfa = sfa;
+  g.sfb = sfb;
+  g.sf_k_tiles = (kind == kGemmNvf4) ? sf_k_tiles_for(k) : 0;
+  g.row_scale = ep.row_scale;
+  g.col_scale = ep.col_scale;
+  g.col_scale_scalar = ep.col_scale_scalar;
+  g.global_scale = ep.global_scale;
+  g.bias = ep.bias;
+  g.residual = ep.residual;
+  g.residual_rows = ep.residual_rows;
+  g.residual_ld = ep.residual_ld;
+  g.act = ep.act;
+  g.out_bf16 = out_bf16;
+  g.out = out;
+  g.status = status_word();
+  g.stream = 0;
+  const char *why = "";
+  cudaError_t e = launch_gemm(g, &why);
+  if (e != cudaSuccess) aborted(std::string("GEMM launch: ") + why + " (" + cudaGetErrorString(e) + ")");
+  ++g_gemm_launches;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Resolves the optional addend/bias/residual views of an entry point into epilogue pointers,
+// expanding into scratch what the epilogue cannot index. Scratch offsets are reserved in
+// `scratch` first and resolved after commit(), hence the two phases.
+struct AddendResolver {
+  AddendPlan plan;
+  std::vector<int32_t> bshape;
+  std::vector<int64_t> bstride;
+  size_t expand_off = 0;
+  const fl_tensor_view_impl_t *view = nullptr;
+
+  void prepare(const fl_tensor_view_impl_t *addend, const fl_tensor_view_impl_t &out, Scratch *scratch) {
+    view = addend;
+    if (!addend) return;
+    plan = plan_addend(*addend, out, &bshape, &bstride);
+    if (plan.needs_expand) expand_off = scratch->reserve(static_cast<size_t>(numel_of(out)) * 2);
+  }
+  void resolve(uint8_t *scratch_base, int m, int n, Epilogue *ep) {
+    if (!view) return;
+    if (plan.needs_expand) {
+      void *dst = scratch_base + expand_off;
+      cuda_check(expand_16(raw_ptr(*view), bshape.data(), bstride.data(), static_cast<int>(bshape.size()), dst, 0),
+                 "expanding the addend");
+      ep->residual = dst;
+      ep->residual_rows = m;
+      ep->residual_ld = n;
+    } else if (plan.bias) {
+      ep->bias = plan.bias;
+    } else {
+      ep->residual = plan.residual;
+      ep->residual_rows = plan.residual_rows;
+      ep->residual_ld = plan.residual_ld;
+    }
+  }
+};
+
+}  // namespace
+
+// ============================ Part 1 ==========================================================
+
+extern "C" {
+
+void fl_init(void) {
+  guard([&]() {
+    device_state();
+    return clear_error();
+  });
+}
+
+int32_t fl_is_device_available(fl_device_type_t device, int32_t *out) {
+  return guard([&]() {
+    if (!out) invalid("out is null");
+    DeviceState &d = device_state();
+    switch (device) {
+      case FL_DEVICE_CPU: *out = 1; break;  // storage only
+      case FL_DEVICE_CUDA:
+      case FL_DEVICE_CUDA_HOST: *out = (d.present && d.sm100) ? 1 : 0; break;
+      case FL_DEVICE_METAL:
+      case FL_DEVICE_VULKAN: *out = 0; break;
+      default: invalid("unknown device");
+    }
+    return clear_error();
+  });
+}
+
+int32_t fl_get_last_error_code(void) { return t_code; }
+
+const char *fl_get_last_error_message(void) { return t_message.c_str(); }
+
+int32_t fl_operators_create(fl_device_type_t device, fl_operators_t *out) {
+  return guard([&]() {
+    if (!out) invalid("out is null");
+    if (device != FL_DEVICE_CUDA) {
+      invalid(std::string("this library has operators for cuda only, not ") + device_name(device));
+    }
+    require_kernels();
+    *out = new fl_operators_impl_t{device};
+    return clear_error();
+  });
+}
+
+void fl_operators_destroy(fl_operators_t operators) { delete operators; }
+
+int32_t fl_operators_get_device(fl_operators_t operators, fl_device_type_t *out) {
+  return guard([&]() {
+    if (!operators) invalid("operators is null");
+    if (!out) invalid("out is null");
+    *out = operators->device;
+    return clear_error();
+  });
+}
+
+int32_t fl_tensor_data_create(fl_device_type_t device, fl_dtype_t dtype, int64_t numel, fl_alloc_hint_t hint,
+                              fl_tensor_data_t *out) {
+  (void)hint;
+  return guard([&]() {
+    if (!out) invalid("out is null");
+    if (numel < 1) invalid("storage holds at least one element");
+    if (numel > (int64_t(1) << 30) * 4) invalid("too many elements");
+    const size_t bytes = static_cast<size_t>(numel * dtype_size(dtype));
+    void *p = nullptr;
+    switch (device) {
+      case FL_DEVICE_CPU:
+        if (posix_memalign(&p, 64, bytes < 64 ? 64 : bytes) != 0) throw FlError{FL_ERROR_OUT_OF_MEMORY, "host allocation failed"};
+        break;
+      case FL_DEVICE_CUDA:
+        require_kernels();
+        cuda_check(cudaMalloc(&p, bytes), "cudaMalloc");
+        break;
+      case FL_DEVICE_CUDA_HOST:
+        require_kernels();
+        cuda_check(cudaMallocHost(&p, bytes), "cudaMallocHost");
+        break;
+      default: invalid(std::string("no storage on ") + device_name(device));
+    }
+    auto *d = new fl_tensor_data_impl_t();
+    d->ptr = p;
+    d->numel = numel;
+    d->dtype = dtype;
+    d->device = device;
+    d->owned = true;
+    *out = d;
+    return clear_error();
+  });
+}
+
+int32_t fl_tensor_data_borrow(const void *data, fl_dtype_t dtype, int64_t numel, fl_tensor_data_t *out) {
+  return guard([&]() {
+    if (!out) invalid("out is null");
+    if (!data) invalid("data is null");
+    if (numel < 1) invalid("storage holds at least one element");
+    const int64_t alignment = dtype_size(dtype);
+    if (reinterpret_cast<uintptr_t>(data) % alignment != 0) {
+      invalid("data is not aligned to its " + std::to_string(alignment) + "-byte elements");
+    }
+    auto *d = new fl_tensor_data_impl_t();
+    d->ptr = const_cast<void *>(data);
+    d->numel = numel;
+    d->dtype = dtype;
+    d->device = FL_DEVICE_CPU;
+    d->owned = false;
+    *out = d;
+    return clear_error();
+  });
+}
+
+void fl_tensor_data_destroy(fl_tensor_data_t data) {
+  if (!data) return;
+  if (data->owned && data->ptr) {
+    switch (data->device) {
+      case FL_DEVICE_CPU: free(data->ptr); break;
+      case FL_DEVICE_CUDA: cudaFree(data->ptr); break;  // synchronises with outstanding work
+      case FL_DEVICE_CUDA_HOST: cudaFreeHost(data->ptr); break;
+      default: break;
+    }
+  }
+  delete data;
+}
+
+int32_t fl_tensor_data_get_host_ptr(fl_tensor_data_t data, void **out) {
+  return guard([&]() {
+    if (!out) invalid("out is null");
+    fl_tensor_data_impl_t &d = deref(data);
+    if (d.device != FL_DEVICE_CPU && d.device != FL_DEVICE_CUDA_HOST) {
+      invalid(std::string("storage on ") + device_name(d.device) + " has no address the caller may touch");
+    }
+    *out = d.ptr;
+    return clear_error();
+  });
+}
+
+int32_t fl_tensor_view_create(fl_tensor_data_t data, const int32_t *shape, const int32_t *stride, int32_t ndim,
+                              int64_t offset, fl_tensor_view_t *out) {
+  return guard([&]() {
+    if (!out) invalid("out is null");
+    fl_tensor_data_impl_t &storage = deref(data);
+    if (ndim < 0) invalid("ndim must not be negative");
+    if (ndim > 0 && (!shape || !stride)) invalid("shape or stride is null");
+    if (offset < 0) invalid("offset must not be negative");
+    int64_t last = offset;
+    bool empty = false;
+    for (int32_t d = 0; d < ndim; ++d) {
+      if (shape[d] < 0) invalid("shape must not be negative");
+      if (stride[d] < 0) invalid("stride must not be negative");
+      if (shape[d] == 0) empty = true;
+      last += static_cast<int64_t>(shape[d] > 0 ? shape[d] - 1 : 0) * stride[d];
+    }
+    if (!empty && last >= storage.numel) {
+      invalid("the view reaches element " + std::to_string(last) + " of storage holding " +
+              std::to_string(storage.numel));
+    }
+    auto *v = new fl_tensor_view_impl_t();
+    v->data = &storage;
+    v->shape.assign(shape, shape + ndim);
+    v->stride.assign(stride, stride + ndim);
+    v->offset = offset;
+    *out = v;
+    return clear_error();
+  });
+}
+
+void fl_tensor_view_destroy(fl_tensor_view_t view) { delete view; }
+
+int32_t fl_transfer(fl_operators_t operators, fl_tensor_view_t src_h, fl_tensor_view_t dest_h) {
+  return guard([&]() {
+    if (!operators) invalid("operators is null");
+    fl_tensor_view_impl_t &src = deref(src_h);
+    fl_tensor_view_impl_t &dest = deref(dest_h);
+    if (!is_contiguous(src) || !is_contiguous(dest)) invalid("transfer: both views have to be contiguous");
+    if (src.shape != dest.shape) invalid("transfer: the shapes differ");
+    if (dtype_of(src) != dtype_of(dest)) invalid("transfer: the dtypes differ");
+    const bool src_host = device_of(src) != FL_DEVICE_CUDA;
+    const bool dest_host = device_of(dest) != FL_DEVICE_CUDA;
+    if (src_host == dest_host) invalid("transfer: one side has to be on the device and the other on the host");
+    check_earlier_kernel_status();
+    const size_t bytes = static_cast<size_t>(numel_of(src) * dtype_size(dtype_of(src)));
+    if (bytes == 0) return clear_error();
+    cuda_check(cudaMemcpyAsync(raw_ptr(dest), raw_ptr(src), bytes,
+                               src_host ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, 0),
+               "cudaMemcpyAsync");
+    if (dest_host) {
+      cuda_check(cudaStreamSynchronize(0), "cudaStreamSynchronize");
+      check_earlier_kernel_status();
+    }
+    return clear_error();
+  });
+}
+
+int32_t fl_fp8_available(fl_device_type_t device, int32_t *out) {
+  return guard([&]() {
+    if (!out) invalid("out is null");
+    if (device < FL_DEVICE_CPU || device > FL_DEVICE_UNKNOWN) invalid("unknown device");
+    DeviceState &d = device_state();
+    *out = (device == FL_DEVICE_CUDA && d.present && d.sm100) ? 1 : 0;
+    return clear_error();
+  });
+}
+
+int32_t fl_fp8_matmul(fl_tensor_view_t a, fl_tensor_view_t data, fl_tensor_view_t scale, fl_tensor_view_t out) {
+  return fl_fp8_matmul_add(a, data, scale, nullptr, out);
+}
+
+int32_t fl_fp8_matmul_add(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_view_t scale_h,
+                          fl_tensor_view_t addend_h, fl_tensor_view_t out_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &weight = deref(data_h);
+    const fl_tensor_view_impl_t &scale = deref(scale_h);
+    check_fp8_weight(weight, scale, /*per_channel_ok=*/false);
+    const fl_device_type_t device = device_of(weight);
+    const int rows = weight.shape[0];
+    const int k = weight.shape[1];
+    const fl_tensor_view_impl_t &a = deref(a_h);
+    check_activation(a, device, "the left operand");
+    if (a.shape.back() != k) invalid("the two operands disagree about k");
+    const fl_tensor_view_impl_t &out = deref(out_h);
+    check_result(out, a, rows, device);
+    const fl_tensor_view_impl_t *addend = addend_h ? &deref(addend_h) : nullptr;
+    if (addend) {
+      if (device_of(*addend) != device || dtype_of(*addend) != dtype_of(out) ||
+          addend->shape.size() > out.shape.size()) {
+        invalid("the addend is not <float16> on the weight's device, of out's shape");
+      }
+    }
+    if (device != FL_DEVICE_CUDA) invalid("the fp8 operand is on a device with no FP8 kernels");
+    check_tiles(rows, k, 16);
+    require_kernels();
+    check_earlier_kernel_status();
+
+    const int64_t m64 = leading_rows(a);
+    if (m64 == 0) return clear_error();
+    if (m64 > INT32_MAX) invalid("the left operand has more rows than the kernels can index");
+    const int m = static_cast<int>(m64);
+    const int is_bf16 = dtype_of(a) == FL_DTYPE_BFLOAT16;
+
+    // The weight is widened to the activation's 16-bit type (exactly) into scratch, then
+    // multiplied by the 16-bit tcgen05 kernel; the scale and the addend go into the epilogue.
+    Scratch scratch;
+    const size_t w_off = scratch.reserve(static_cast<size_t>(rows) * k * 2);
+    size_t a_off = 0;
+    const bool a_misaligned = !aligned16(raw_ptr(a));
+    if (a_misaligned) a_off = scratch.reserve(static_cast<size_t>(m) * k * 2);
+    AddendResolver res;
+    res.prepare(addend, out, &scratch);
+    uint8_t *base = scratch.commit();
+
+    cuda_check(widen_e4m3(raw_ptr(weight), static_cast<int64_t>(rows) * k, base + w_off, is_bf16, 0), "widening");
+    const void *a_ptr = raw_ptr(a);
+    if (a_misaligned) {
+      cuda_check(cudaMemcpyAsync(base + a_off, a_ptr, static_cast<size_t>(m) * k * 2, cudaMemcpyDeviceToDevice, 0),
+                 "staging the left operand");
+      a_ptr = base + a_off;
+    }
+    Epilogue ep;
+    ep.col_scale = reinterpret_cast<const float *>(raw_ptr(scale));
+    ep.col_scale_scalar = 1;
+    res.resolve(base, m, rows, &ep);
+    run_gemm(is_bf16 ? kGemmBF16 : kGemmF16, m, rows, k, a_ptr, base + w_off, nullptr, nullptr, ep, is_bf16,
+             raw_ptr(out));
+    return clear_error();
+  });
+}
+
+// ============================ Part 2 ==========================================================
+
+int32_t fl_fp8_linear(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_view_t scales_h,
+                      fl_tensor_view_t bias_h, fl_tensor_view_t residual_h, int32_t act, fl_tensor_view_t out_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &weight = deref(data_h);
+    const fl_tensor_view_impl_t &scales = deref(scales_h);
+    check_fp8_weight(weight, scales, /*per_channel_ok=*/true);
+    const fl_device_type_t device = device_of(weight);
+    const int rows = weight.shape[0];
+    const int k = weight.shape[1];
+    const fl_tensor_view_impl_t &a = deref(a_h);
+    check_activation(a, device, "the left operand");
+    if (a.shape.back() != k) invalid("the two operands disagree about k");
+    const fl_tensor_view_impl_t &out = deref(out_h);
+    check_result(out, a, rows, device);
+    if (act != FL_ACT_NONE && act != FL_ACT_GELU_TANH) invalid("unknown activation");
+    const fl_tensor_view_impl_t *bias = bias_h ? &deref(bias_h) : nullptr;
+    const fl_tensor_view_impl_t *residual = residual_h ? &deref(residual_h) : nullptr;
+    if (bias) {
+      if (device_of(*bias) != device || dtype_of(*bias) != dtype_of(out) || numel_of(*bias) != rows ||
+          !is_contiguous(*bias)) {
+        invalid("the bias is not a contiguous (rows) vector of out's type on the weight's device");
+      }
+    }
+    if (residual) {
+      if (device_of(*residual) != device || dtype_of(*residual) != dtype_of(out) || !is_contiguous(*residual)) {
+        invalid("the residual is not contiguous, of out's type, on the weight's device");
+      }
+      check_shape(*residual, out.shape, "the residual");
+    }
+    if (device != FL_DEVICE_CUDA) invalid("the fp8 operand is on a device with no FP8 kernels");
+    check_tiles(rows, k, 16);
+    require_kernels();
+    check_earlier_kernel_status();
+
+    const int64_t m64 = leading_rows(a);
+    if (m64 == 0) return clear_error();
+    if (m64 > INT32_MAX) invalid("the left operand has more rows than the kernels can index");
+    const int m = static_cast<int>(m64);
+    const int is_bf16 = dtype_of(a) == FL_DTYPE_BFLOAT16;
+
+    Scratch scratch;
+    const size_t codes_off = scratch.reserve(static_cast<size_t>(m) * k);
+    const size_t scales_off = scratch.reserve(static_cast<size_t>(m) * 4);
+    size_t w_off = 0;
+    const bool w_misaligned = !aligned16(raw_ptr(weight));
+    if (w_misaligned) w_off = scratch.reserve(static_cast<size_t>(rows) * k);
+    uint8_t *base = scratch.commit();
+
+    uint8_t *codes = base + codes_off;
+    float *row_scales = reinterpret_cast<float *>(base + scales_off);
+    cuda_check(quantize_fp8_act(raw_ptr(a), is_bf16, m, k, codes, row_scales, 0), "quantising the activation");
+    const void *w_ptr = raw_ptr(weight);
+    if (w_misaligned) {
+      cuda_check(cudaMemcpyAsync(base + w_off, w_ptr, static_cast<size_t>(rows) * k, cudaMemcpyDeviceToDevice, 0),
+                 "staging the weight");
+      w_ptr = base + w_off;
+    }
+    Epilogue ep;
+    ep.row_scale = row_scales;
+    ep.col_scale = reinterpret_cast<const float *>(raw_ptr(scales));
+    ep.col_scale_scalar = numel_of(scales) == 1 ? 1 : 0;
+    ep.bias = bias ? raw_ptr(*bias) : nullptr;
+    if (residual) {
+      ep.residual = raw_ptr(*residual);
+      ep.residual_rows = m;
+      ep.residual_ld = rows;
+    }
+    ep.act = act;
+    run_gemm(kGemmE4M3, m, rows, k, codes, w_ptr, nullptr, nullptr, ep, is_bf16, raw_ptr(out));
+    return clear_error();
+  });
+}
+
+int32_t fl_nvfp4_available(fl_device_type_t device, int32_t *out) { return fl_fp8_available(device, out); }
+
+int32_t fl_nvfp4_linear(fl_tensor_view_t a_h, fl_tensor_view_t codes_h, fl_tensor_view_t block_scales_h,
+                        fl_tensor_view_t global_scale_h, fl_tensor_view_t bias_h, fl_tensor_view_t residual_h,
+                        int32_t act, fl_tensor_view_t out_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &wcodes = deref(codes_h);
+    const fl_tensor_view_impl_t &wsf = deref(block_scales_h);
+    const fl_tensor_view_impl_t &gs = deref(global_scale_h);
+    if (dtype_of(wcodes) != FL_DTYPE_FP4E2M1X2 || wcodes.shape.size() != 2) {
+      invalid("nvfp4 operand: codes is not <fp4e2m1x2>(rows, k/2)");
+    }
+    const fl_device_type_t device = device_of(wcodes);
+    const int rows = wcodes.shape[0];
+    const int64_t k64 = static_cast<int64_t>(wcodes.shape[1]) * 2;
+    if (k64 > INT32_MAX) invalid("nvfp4 operand: k is too large");
+    const int k = static_cast<int>(k64);
+    if (dtype_of(wsf) != FL_DTYPE_FP8E4M3 || wsf.shape.size() != 2 || wsf.shape[0] != rows ||
+        static_cast<int64_t>(wsf.shape[1]) * 16 != k) {
+      invalid("nvfp4 operand: block_scales is not <fp8e4m3>(rows, k/16)");
+    }
+    if (dtype_of(gs) != FL_DTYPE_FLOAT || numel_of(gs) != 1) invalid("nvfp4 operand: the global scale is not a single <float>");
+    if (device_of(wsf) != device || device_of(gs) != device) invalid("nvfp4 operand: its parts are on different devices");
+    if (!is_contiguous(wcodes) || !is_contiguous(wsf) || !is_contiguous(gs)) invalid("nvfp4 operand: not contiguous");
+    if (numel_of(wcodes) >= INT32_MAX) invalid("nvfp4 operand: more elements than the kernels can index");
+    const fl_tensor_view_impl_t &a = deref(a_h);
+    check_activation(a, device, "the left operand");
+    if (a.shape.back() != k) invalid("the two operands disagree about k");
+    const fl_tensor_view_impl_t &out = deref(out_h);
+    check_result(out, a, rows, device);
+    if (act != FL_ACT_NONE && act != FL_ACT_GELU_TANH) invalid("unknown activation");
+    const fl_tensor_view_impl_t *bias = bias_h ? &deref(bias_h) : nullptr;
+    const fl_tensor_view_impl_t *residual = residual_h ? &deref(residual_h) : nullptr;
+    if (bias) {
+      if (device_of(*bias) != device || dtype_of(*bias) != dtype_of(out) || numel_of(*bias) != rows ||
+          !is_contiguous(*bias)) {
+        invalid("the bias is not a contiguous (rows) vector of out's type on the weight's device");
+      }
+    }
+    if (residual) {
+      if (device_of(*residual) != device || dtype_of(*residual) != dtype_of(out) || !is_contiguous(*residual)) {
+        invalid("the residual is not contiguous, of out's type, on the weight's device");
+      }
+      check_shape(*residual, out.shape, "the residual");
+    }
+    if (device != FL_DEVICE_CUDA) invalid("the nvfp4 operand is on a device with no NVFP4 kernels");
+    check_tiles(rows, k, 32);
+    require_kernels();
+    check_earlier_kernel_status();
+
+    const int64_t m64 = leading_rows(a);
+    if (m64 == 0) return clear_error();
+    if (m64 > INT32_MAX) invalid("the left operand has more rows than the kernels can index");
+    const int m = static_cast<int>(m64);
+    const int is_bf16 = dtype_of(a) == FL_DTYPE_BFLOAT16;
+
+    Scratch scratch;
+    const size_t xcodes_off = scratch.reserve(static_cast<size_t>(m) * k / 2);
+    const size_t sfa_bytes = static_cast<size_t>(sf_tiled_bytes(m, k, 0));
+    const size_t sfb_bytes = static_cast<size_t>(sf_tiled_bytes(rows, k, 1));  // one spare row group: a
+    const size_t sfa_off = scratch.reserve(sfa_bytes);                          // tile may read past the last
+    const size_t sfb_off = scratch.reserve(sfb_bytes);
+    size_t w_off = 0;
+    const bool w_misaligned = !aligned16(raw_ptr(wcodes));
+    if (w_misaligned) w_off = scratch.reserve(static_cast<size_t>(rows) * k / 2);
+    uint8_t *base = scratch.commit();
+
+    cuda_check(cudaMemsetAsync(base + sfa_off, 0, sfa_bytes, 0), "clearing scale factors");
+    cuda_check(cudaMemsetAsync(base + sfb_off, 0, sfb_bytes, 0), "clearing scale factors");
+    cuda_check(quantize_nvfp4_act(raw_ptr(a), is_bf16, m, k, base + xcodes_off, base + sfa_off, 0),
+               "quantising the activation");
+    cuda_check(pack_scale_factors(raw_ptr(wsf), rows, k, base + sfb_off, 0), "re-tiling the block scales");
+    const void *w_ptr = raw_ptr(wcodes);
+    if (w_misaligned) {
+      cuda_check(cudaMemcpyAsync(base + w_off, w_ptr, static_cast<size_t>(rows) * k / 2, cudaMemcpyDeviceToDevice, 0),
+                 "staging the weight");
+      w_ptr = base + w_off;
+    }
+    Epilogue ep;
+    ep.global_scale = reinterpret_cast<const float *>(raw_ptr(gs));
+    ep.bias = bias ? raw_ptr(*bias) : nullptr;
+    if (residual) {
+      ep.residual = raw_ptr(*residual);
+      ep.residual_rows = m;
+      ep.residual_ld = rows;
+    }
+    ep.act = act;
+    run_gemm(kGemmNvf4, m, rows, k, base + xcodes_off, w_ptr, base + sfa_off, base + sfb_off, ep, is_bf16,
+             raw_ptr(out));
+    return clear_error();
+  });
+}
+
+int32_t fl_quantize_fp8_rows(fl_tensor_view_t w_h, fl_tensor_view_t codes_h, fl_tensor_view_t scales_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &w = deref(w_h);
+    const fl_tensor_view_impl_t &codes = deref(codes_h);
+    const fl_tensor_view_impl_t &scales = deref(scales_h);
+    if (dtype_of(w) != FL_DTYPE_FLOAT || w.shape.size() != 2 || !is_contiguous(w)) invalid("w is not a contiguous <float>(rows, k)");
+    if (dtype_of(codes) != FL_DTYPE_FP8E4M3 || codes.shape != w.shape || !is_contiguous(codes)) invalid("codes is not a contiguous <fp8e4m3>(rows, k)");
+    if (dtype_of(scales) != FL_DTYPE_FLOAT || numel_of(scales) != w.shape[0] || !is_contiguous(scales)) invalid("scales is not a contiguous <float>(rows)");
+    if (device_of(w) != FL_DEVICE_CUDA || device_of(codes) != FL_DEVICE_CUDA || device_of(scales) != FL_DEVICE_CUDA) invalid("the operands are not all on cuda");
+    require_kernels();
+    if (numel_of(w) == 0) return clear_error();
+    cuda_check(quantize_fp8_rows_f32(reinterpret_cast<const float *>(raw_ptr(w)), w.shape[0], w.shape[1], raw_ptr(codes),
+                                     reinterpret_cast<float *>(raw_ptr(scales)), 0),
+               "quantising");
+    return clear_error();
+  });
+}
+
+int32_t fl_quantize_fp8_activation(fl_tensor_view_t a_h, fl_tensor_view_t codes_h, fl_tensor_view_t scales_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &a = deref(a_h);
+    const fl_tensor_view_impl_t &codes = deref(codes_h);
+    const fl_tensor_view_impl_t &scales = deref(scales_h);
+    if (!is_half_type(dtype_of(a)) || a.shape.size() != 2 || !is_contiguous(a)) invalid("a is not a contiguous 16-bit (m, k)");
+    if (dtype_of(codes) != FL_DTYPE_FP8E4M3 || codes.shape != a.shape || !is_contiguous(codes)) invalid("codes is not a contiguous <fp8e4m3>(m, k)");
+    if (dtype_of(scales) != FL_DTYPE_FLOAT || numel_of(scales) != a.shape[0] || !is_contiguous(scales)) invalid("scales is not a contiguous <float>(m)");
+    if (device_of(a) != FL_DEVICE_CUDA || device_of(codes) != FL_DEVICE_CUDA || device_of(scales) != FL_DEVICE_CUDA) invalid("the operands are not all on cuda");
+    require_kernels();
+    if (numel_of(a) == 0) return clear_error();
+    cuda_check(quantize_fp8_act(raw_ptr(a), dtype_of(a) == FL_DTYPE_BFLOAT16, a.shape[0], a.shape[1], raw_ptr(codes),
+                                reinterpret_cast<float *>(raw_ptr(scales)), 0),
+               "quantising");
+    return clear_error();
+  });
+}
+
+int32_t fl_quantize_nvfp4(fl_tensor_view_t w_h, fl_tensor_view_t codes_h, fl_tensor_view_t block_scales_h,
+                          fl_tensor_view_t global_scale_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &w = deref(w_h);
+    const fl_tensor_view_impl_t &codes = deref(codes_h);
+    const fl_tensor_view_impl_t &sf = deref(block_scales_h);
+    const fl_tensor_view_impl_t &gs = deref(global_scale_h);
+    if (dtype_of(w) != FL_DTYPE_FLOAT || w.shape.size() != 2 || !is_contiguous(w)) invalid("w is not a contiguous <float>(rows, k)");
+    const int rows = w.shape[0], k = w.shape[1];
+    if (k % 16 != 0) invalid("k is not a multiple of 16");
+    if (dtype_of(codes) != FL_DTYPE_FP4E2M1X2 || codes.shape != std::vector<int32_t>{rows, k / 2} || !is_contiguous(codes)) invalid("codes is not a contiguous <fp4e2m1x2>(rows, k/2)");
+    if (dtype_of(sf) != FL_DTYPE_FP8E4M3 || sf.shape != std::vector<int32_t>{rows, k / 16} || !is_contiguous(sf)) invalid("block_scales is not a contiguous <fp8e4m3>(rows, k/16)");
+    if (dtype_of(gs) != FL_DTYPE_FLOAT || numel_of(gs) != 1) invalid("global_scale is not a single <float>");
+    if (device_of(w) != FL_DEVICE_CUDA || device_of(codes) != FL_DEVICE_CUDA || device_of(sf) != FL_DEVICE_CUDA || device_of(gs) != FL_DEVICE_CUDA) invalid("the operands are not all on cuda");
+    require_kernels();
+    if (numel_of(w) == 0) return clear_error();
+    Scratch scratch;
+    const size_t word_off = scratch.reserve(256);
+    uint8_t *base = scratch.commit();
+    cuda_check(quantize_nvfp4_weight_f32(reinterpret_cast<const float *>(raw_ptr(w)), rows, k, raw_ptr(codes), raw_ptr(sf),
+                                         reinterpret_cast<float *>(raw_ptr(gs)),
+                                         reinterpret_cast<uint32_t *>(base + word_off), 0),
+               "quantising");
+    return clear_error();
+  });
+}
+
+int32_t fl_tensor_data_borrow_device(void *device_ptr, fl_dtype_t dtype, int64_t numel, fl_tensor_data_t *out) {
+  return guard([&]() {
+    if (!out) invalid("out is null");
+    if (!device_ptr) invalid("device_ptr is null");
+    if (numel < 1) invalid("storage holds at least one element");
+    const int64_t alignment = dtype_size(dtype);
+    if (reinterpret_cast<uintptr_t>(device_ptr) % alignment != 0) {
+      invalid("device_ptr is not aligned to its " + std::to_string(alignment) + "-byte elements");
+    }
+    auto *d = new fl_tensor_data_impl_t();
+    d->ptr = device_ptr;
+    d->numel = numel;
+    d->dtype = dtype;
+    d->device = FL_DEVICE_CUDA;
+    d->owned = false;
+    *out = d;
+    return clear_error();
+  });
+}
+
+int32_t fl_sm100_set_device(int32_t ordinal) {
+  return guard([&]() {
+    {
+      std::lock_guard<std::mutex> lock(g_mutex);
+      if (g_dev.scratch || g_dev.status_host) invalid("the device has to be chosen before the first operation");
+    }
+    cuda_check(cudaSetDevice(ordinal), "cudaSetDevice");
+    {
+      std::lock_guard<std::mutex> lock(g_mutex);
+      g_dev.probed = false;
+      probe_locked();
+    }
+    return clear_error();
+  });
+}
+
+int32_t fl_sm100_synchronize(int32_t *kernel_status) {
+  return guard([&]() -> int32_t {
+    cuda_check(cudaStreamSynchronize(0), "cudaStreamSynchronize");
+    uint32_t code = 0;
+    {
+      std::lock_guard<std::mutex> lock(g_mutex);
+      if (g_dev.status_host) {
+        code = *reinterpret_cast<volatile uint32_t *>(g_dev.status_host);
+        *reinterpret_cast<volatile uint32_t *>(g_dev.status_host) = 0;
+      }
+    }
+    if (kernel_status) *kernel_status = static_cast<int32_t>(code);
+    if (code != 0) aborted("a kernel gave up on a bounded wait (status " + std::to_string(code) + ")");
+    return clear_error();
+  });
+}
+
+int64_t fl_sm100_launch_count(void) { return g_gemm_launches.load() + helper_launch_count(); }
+
+}  // extern "C"

@@ -1,0 +1,515 @@
+// The sm_100a GEMM kernels behind flint's quantized matmul (replaces the CUTLASS 2.x Sm80
+// mma.sync kernel of flint/cuda/gemm_fp8_cutlass.cu:94-197,267-305).
+//
+// One persistent CTA per SM, six warps:
+//   warps 0-3  epilogue: tensor memory -> registers -> scale/bias/GELU/residual -> 16-bit stores
+//   warp  4    producer: TMA tile loads of A and B (and the NVFP4 scale-factor tiles) into a
+//              ring of shared-memory stages, signalled through mbarriers
+//   warp  5    MMA: one thread issues tcgen05.mma on the staged tiles, accumulating in tensor
+//              memory; tcgen05.commit hands stages back to the producer and finished
+//              accumulators to the epilogue
+// The accumulator is double-buffered in tensor memory so the epilogue of tile i overlaps the
+// main loop of tile i+1.
+//
+// Every operand row in a stage is 128 bytes (64 half / 128 e4m3 / 256 e2m1 elements) in the
+// 128-byte swizzle, and one tcgen05.mma consumes 32 bytes of K from every row, so the three
+// element kinds share all of the addressing and differ only in the instruction issued.
+#include "gemm_sm100.cuh"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <mutex>
+
+#include "ptx_sm100.cuh"
+
+namespace flsm100 {
+
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kRowBytes = 128;          // bytes of K per operand row per stage
+constexpr int kMmaKBytes = 32;          // bytes of K one tcgen05.mma consumes per row
+constexpr int kMmasPerStage = kRowBytes / kMmaKBytes;
+constexpr int kSfTileBytes = 512;       // 128 rows x 4 scale factors
+constexpr int kNumThreads = 192;
+constexpr int kEpilogueWarps = 4;
+constexpr int kProducerWarp = 4;
+constexpr int kMmaWarp = 5;
+
+struct KernelParams {
+  int m, n;
+  int num_kb;  // stages of K per tile
+  int tiles_m, tiles_n;
+  const uint8_t *sfa;
+  const uint8_t *sfb;
+  int sf_k_tiles;
+  const float *row_scale;
+  const float *col_scale;
+  int col_scale_scalar;
+  const float *global_scale;
+  const void *bias;
+  const void *residual;
+  int residual_rows;
+  long long residual_ld;
+  int act;
+  int out_bf16;
+  void *out;
+  uint32_t *status;
+};
+
+template <int BLOCK_N, bool NVF4>
+struct Config {
+  static constexpr int kABytes = kBlockM * kRowBytes;
+  static constexpr int kBBytes = BLOCK_N * kRowBytes;
+  // Scale factors: A has one 128-row group; B is loaded as whole 128-row groups that cover the
+  // tile (a 192-wide tile starts mid-group on odd tiles, so it needs two).
+  static constexpr int kSfbGroups = NVF4 ? (BLOCK_N + 127) / 128 : 0;
+  static constexpr int kSfaBytes = NVF4 ? kMmasPerStage * kSfTileBytes : 0;
+  static constexpr int kSfbBytes = NVF4 ? kSfbGroups * kMmasPerStage * kSfTileBytes : 0;
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kSmemBudget = 227 * 1024 - 2048;
+  static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + slack to align to 1024
+  // Tensor memory columns: two accumulators, then the scale factors of one stage.
+  static constexpr int kAccCols = 2 * BLOCK_N;
+  static constexpr int kSfaCols = NVF4 ? kMmasPerStage * 4 : 0;
+  static constexpr int kSfbColsPerMma = NVF4 ? kSfbGroups * 4 : 0;
+  static constexpr int kSfbCols = kMmasPerStage * kSfbColsPerMma;
+  static constexpr int kUsedCols = kAccCols + kSfaCols + kSfbCols;
+  static constexpr int kTmemCols = kUsedCols <= 32 ? 32 : kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128
+                                   : kUsedCols <= 256 ? 256 : 512;
+  static_assert(kUsedCols <= 512, "tensor memory holds 512 columns");
+  static_assert(kStages >= 2, "need at least two stages");
+};
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  // 0.5 x (1 + tanh(u)) == x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715 x^3)
+  // (waifu/src/krea2/dit.rs:170-188 spells the same function as seven graph nodes).
+  const float kAlpha = 0.7978845608028654f;
+  float u = kAlpha * (x + 0.044715f * x * x * x);
+  float e = __expf(-2.0f * u);
+  return __fdividef(x, 1.0f + e);
+}
+
+__device__ __forceinline__ float load16(const void *p, long long idx, int is_bf16) {
+  if (is_bf16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[idx]);
+  return __half2float(reinterpret_cast<const __half *>(p)[idx]);
+}
+
+__device__ __forceinline__ uint32_t pack16(float lo, float hi, int is_bf16) {
+  if (is_bf16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+  }
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+
+template <int KIND, int BLOCK_N>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const KernelParams p) {
+  constexpr bool NVF4 = (KIND == kKindNvf4);
+  using Cfg = Config<BLOCK_N, NVF4>;
+  constexpr int STAGES = Cfg::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t acc_full_bar[2];
+  __shared__ __align__(8) uint64_t acc_empty_bar[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ volatile uint32_t abort_flag;
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full_bar[s], 1);
+      mbar_init(&acc_empty_bar[s], kEpilogueWarps);
+    }
+    fence_barrier_init();
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(&tmem_base_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  auto stage_a = [&](int s) { return smem + s * Cfg::kStageBytes; };
+  auto stage_b = [&](int s) { return smem + s * Cfg::kStageBytes + Cfg::kABytes; };
+  auto stage_sfa = [&](int s) { return smem + s * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBBytes; };
+  auto stage_sfb = [&](int s) { return smem + s * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBBytes + Cfg::kSfaBytes; };
+
+  if (warp == kProducerWarp) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int tm = tile % p.tiles_m;
+        const int tn = tile / p.tiles_m;
+        const int m0 = tm * kBlockM;
+        const int n0 = tn * BLOCK_N;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, &abort_flag)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          tma_load_2d(stage_a(stage), &tmap_a, &full_bar[stage], kb * kRowBytes, m0);
+          tma_load_2d(stage_b(stage), &tmap_b, &full_bar[stage], kb * kRowBytes, n0);
+          if constexpr (NVF4) {
+            // Scale-factor tiles of this k block: kMmasPerStage consecutive 512-byte tiles per
+            // 128-row group.
+            const long long ktile = static_cast<long long>(kb) * kMmasPerStage;
+            const uint8_t *src_a = p.sfa + (static_cast<long long>(tm) * p.sf_k_tiles + ktile) * kSfTileBytes;
+            bulk_load_1d(stage_sfa(stage), src_a, Cfg::kSfaBytes, &full_bar[stage]);
+            const int group0 = n0 / 128;
+            for (int g = 0; g < Cfg::kSfbGroups; ++g) {
+              const uint8_t *src_b =
+                  p.sfb + (static_cast<long long>(group0 + g) * p.sf_k_tiles + ktile) * kSfTileBytes;
+              bulk_load_1d(stage_sfb(stage) + g * kMmasPerStage * kSfTileBytes, src_b,
+                           kMmasPerStage * kSfTileBytes, &full_bar[stage]);
+            }
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(p.status, 0u, static_cast<uint32_t>(kStatusProducerTimeout));
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      // e4m3 is format 0 of kind::f8f6f4; fp16 / bf16 are formats 0 / 1 of kind::f16.
+      constexpr uint32_t kFmt = (KIND == kKindBF16) ? 1u : 0u;
+      constexpr uint32_t idesc = NVF4 ? umma_idesc_nvf4(kBlockM, BLOCK_N) : umma_idesc(kBlockM, BLOCK_N, kFmt, kFmt);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, &abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint64_t adesc = umma_desc_sw128(smem_u32(stage_a(stage)));
+          const uint64_t bdesc = umma_desc_sw128(smem_u32(stage_b(stage)));
+          if constexpr (NVF4) {
+            const uint32_t sfa_tmem = tmem_base + Cfg::kAccCols;
+            const uint32_t sfb_tmem = sfa_tmem + Cfg::kSfaCols;
+            const uint32_t sfa_smem = smem_u32(stage_sfa(stage));
+            const uint32_t sfb_smem = smem_u32(stage_sfb(stage));
+#pragma unroll
+            for (int j = 0; j < kMmasPerStage; ++j) {
+              tmem_cp_sf(sfa_tmem + j * 4, umma_desc_sf(sfa_smem + j * kSfTileBytes));
+#pragma unroll
+              for (int g = 0; g < Cfg::kSfbGroups; ++g) {
+                tmem_cp_sf(sfb_tmem + j * Cfg::kSfbColsPerMma + g * 4,
+                           umma_desc_sf(sfb_smem + (g * kMmasPerStage + j) * kSfTileBytes));
+              }
+            }
+            // A tile that starts 64 rows into a 128-row group reads its scale factors two
+            // columns further on (32 rows per column).
+            const int tn = tile / p.tiles_m;
+            const uint32_t sfb_skip = ((tn * BLOCK_N) % 128) / 32;
+#pragma unroll
+            for (int j = 0; j < kMmasPerStage; ++j) {
+              umma_nvf4_ss(d_tmem, adesc + j * (kMmaKBytes >> 4), bdesc + j * (kMmaKBytes >> 4), idesc,
+                           (kb | j) != 0 ? 1u : 0u, sfa_tmem + j * 4,
+                           sfb_tmem + j * Cfg::kSfbColsPerMma + sfb_skip);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < kMmasPerStage; ++j) {
+              umma_ss<KIND>(d_tmem, adesc + j * (kMmaKBytes >> 4), bdesc + j * (kMmaKBytes >> 4),
+                            idesc, (kb | j) != 0 ? 1u : 0u);
+            }
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full_bar[acc]);
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(p.status, 0u, static_cast<uint32_t>(kStatusMmaTimeout));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    bool ok = true;
+    int local = 0;
+    const int is_bf16 = p.out_bf16;
+    const float gscale = p.global_scale ? __ldg(p.global_scale) : 1.0f;
+    const float cs_scalar = (p.col_scale && p.col_scale_scalar) ? __ldg(p.col_scale) : 1.0f;
+    const bool out_vec_ok = (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      const int tm = tile % p.tiles_m;
+      const int tn = tile / p.tiles_m;
+      const int row = tm * kBlockM + warp * 32 + lane;
+      const int n0 = tn * BLOCK_N;
+      if (!mbar_wait(&acc_full_bar[acc], acc_phase, &abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const bool row_ok = row < p.m;
+      const float rs = (p.row_scale && row_ok) ? __ldg(p.row_scale + row) : 1.0f;
+      const long long res_row =
+          (p.residual && row_ok) ? static_cast<long long>(row % p.residual_rows) * p.residual_ld : 0;
+      uint16_t *out_row = reinterpret_cast<uint16_t *>(p.out) + static_cast<long long>(row) * p.n;
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        const int nc = n0 + c * 32;
+        if (nc >= p.n) break;  // warp-uniform
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + ((warp * 32) << 16) + acc * BLOCK_N + c * 32, v);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float x[2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int n = nc + j + h;
+            float val = __uint_as_float(v[j + h]);
+            if (n < p.n) {
+              float cs = p.col_scale ? (p.col_scale_scalar ? cs_scalar : __ldg(p.col_scale + n)) : 1.0f;
+              val = val * (rs * cs);
+              if (p.global_scale) val *= gscale;
+              if (p.bias) val += load16(p.bias, n, is_bf16);
+              if (p.act == kActGeluTanh) val = gelu_tanh(val);
+              if (p.residual && row_ok) val += load16(p.residual, res_row + n, is_bf16);
+            }
+            x[h] = val;
+          }
+          packed[j >> 1] = pack16(x[0], x[1], is_bf16);
+        }
+        if (row_ok) {
+          if (out_vec_ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (nc + g * 8 < p.n) {  // n is a multiple of 8, so a group is whole or absent
+                uint4 q = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+                *reinterpret_cast<uint4 *>(out_row + nc + g * 8) = q;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (nc + j < p.n) {
+                out_row[nc + j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffff));
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+    }
+    if (!ok && lane == 0) {
+      abort_flag = 1;
+      atomicCAS(p.status, 0u, static_cast<uint32_t>(kStatusEpilogueTimeout));
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (abort_flag != 0) {
+    // A wait gave up. Give loads that may still be in flight time to land before the shared
+    // memory and tensor memory they target are released.
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    __syncthreads();
+  }
+  if (warp == kMmaWarp) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+// A (rows, row_bytes) byte matrix cut into boxes of (box_rows, 128 bytes) in the 128-byte swizzle.
+bool make_tmap(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kRowBytes), box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int KIND, int BLOCK_N>
+cudaError_t launch_one(const GemmArgs &a, const KernelParams &kp, uint64_t row_bytes, const char **why) {
+  using Cfg = Config<BLOCK_N, KIND == kKindNvf4>;
+  CUtensorMap ta, tb;
+  if (!make_tmap(&ta, a.a, a.m, row_bytes, kBlockM) || !make_tmap(&tb, a.b, a.n, row_bytes, BLOCK_N)) {
+    *why = "cuTensorMapEncodeTiled refused the operand";
+    return cudaErrorInvalidValue;
+  }
+  auto kernel = gemm_tn_kernel<KIND, BLOCK_N>;
+  static bool attr_set = false;  // per instantiation
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) {
+      *why = "cudaFuncSetAttribute(max dynamic shared memory) failed";
+      return e;
+    }
+    attr_set = true;
+  }
+  int grid = kp.tiles_m * kp.tiles_n;
+  int sms = sm_count();
+  if (grid > sms) grid = sms;
+  kernel<<<grid, kNumThreads, Cfg::kSmemBytes, a.stream>>>(ta, tb, kp);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) *why = "kernel launch failed";
+  return e;
+}
+
+}  // namespace
+
+int sm_count() {
+  static int cached = 0;
+  if (cached == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) {
+      cached = n;
+    } else {
+      cached = 148;
+    }
+  }
+  return cached;
+}
+
+cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
+  *why = "";
+  uint64_t row_bytes;
+  switch (a.kind) {
+    case kGemmF16:
+    case kGemmBF16: row_bytes = static_cast<uint64_t>(a.k) * 2; break;
+    case kGemmE4M3: row_bytes = static_cast<uint64_t>(a.k); break;
+    default: row_bytes = static_cast<uint64_t>(a.k) / 2; break;
+  }
+  if (a.m <= 0 || a.n <= 0 || a.k <= 0 || row_bytes % 16 != 0 || a.n % 8 != 0) {
+    *why = "shape the kernels cannot read (rows of 16 bytes, n a multiple of 8)";
+    return cudaErrorInvalidValue;
+  }
+  if ((reinterpret_cast<uintptr_t>(a.a) & 15) || (reinterpret_cast<uintptr_t>(a.b) & 15)) {
+    *why = "operand base is not 16-byte aligned";
+    return cudaErrorInvalidValue;
+  }
+  KernelParams kp;
+  kp.m = a.m;
+  kp.n = a.n;
+  kp.num_kb = static_cast<int>((row_bytes + kRowBytes - 1) / kRowBytes);
+  kp.tiles_m = (a.m + kBlockM - 1) / kBlockM;
+  kp.sfa = a.sfa;
+  kp.sfb = a.sfb;
+  kp.sf_k_tiles = a.sf_k_tiles;
+  kp.row_scale = a.row_scale;
+  kp.col_scale = a.col_scale;
+  kp.col_scale_scalar = a.col_scale_scalar;
+  kp.global_scale = a.global_scale;
+  kp.bias = a.bias;
+  kp.residual = a.residual;
+  kp.residual_rows = a.residual_rows > 0 ? a.residual_rows : a.m;
+  kp.residual_ld = a.residual_ld;
+  kp.act = a.act;
+  kp.out_bf16 = a.out_bf16;
+  kp.out = a.out;
+  kp.status = a.status;
+
+  if (a.kind == kGemmNvf4) {
+    constexpr int BN = 192;
+    kp.tiles_n = (a.n + BN - 1) / BN;
+    return launch_one<kKindNvf4, BN>(a, kp, row_bytes, why);
+  }
+  // Narrow outputs use the narrower tile so that fewer columns of the MMA are padding.
+  const bool narrow = a.n <= 128;
+  if (a.kind == kGemmE4M3) {
+    if (narrow) {
+      kp.tiles_n = (a.n + 127) / 128;
+      return launch_one<kKindF8, 128>(a, kp, row_bytes, why);
+    }
+    kp.tiles_n = (a.n + 255) / 256;
+    return launch_one<kKindF8, 256>(a, kp, row_bytes, why);
+  }
+  if (narrow) {
+    kp.tiles_n = (a.n + 127) / 128;
+    return a.kind == kGemmBF16 ? launch_one<kKindBF16, 128>(a, kp, row_bytes, why)
+                               : launch_one<kKindF16, 128>(a, kp, row_bytes, why);
+  }
+  kp.tiles_n = (a.n + 255) / 256;
+  return a.kind == kGemmBF16 ? launch_one<kKindBF16, 256>(a, kp, row_bytes, why)
+                             : launch_one<kKindF16, 256>(a, kp, row_bytes, why);
+}
+
+}  // namespace flsm100

@@ -1,0 +1,65 @@
+// Host-side interface of the sm_100a GEMM module: one persistent, warp-specialised tcgen05
+// kernel family computing  out[m,n] = epilogue( sum_k A[m,k] * B[n,k] )  with both operands
+// K-major ("TN": the activation (m,k) row-major and the weight (n,k) row-major, which is how the
+// reference stores a linear layer's weight, flint/cuda/gemm_fp8_cutlass.cu:359-367).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace flsm100 {
+
+enum GemmKind : int {
+  kGemmF16 = 0,   // fp16 x fp16 (kind::f16), K a multiple of 8
+  kGemmBF16 = 1,  // bf16 x bf16 (kind::f16), K a multiple of 8
+  kGemmE4M3 = 2,  // e4m3 x e4m3 (kind::f8f6f4), K a multiple of 16
+  kGemmNvf4 = 3,  // e2m1 x e2m1 with unsigned-e4m3 scales per 16 (kind::mxf4nvf4), K a multiple of 32
+};
+
+enum Activation : int { kActNone = 0, kActGeluTanh = 1 };
+
+// Status words the kernels write when a bounded wait runs out.
+enum : uint32_t {
+  kStatusOk = 0,
+  kStatusProducerTimeout = 1,
+  kStatusMmaTimeout = 2,
+  kStatusEpilogueTimeout = 3,
+};
+
+struct GemmArgs {
+  GemmKind kind;
+  int m, n, k;  // k counts elements
+  // Operands in device memory, rows 16-byte aligned (pitch = k * element size, a multiple of 16).
+  const void *a;  // (m, k)
+  const void *b;  // (n, k)
+  // NVFP4 only: scale factors in the 128-row x 4-factor tile layout the tensor cores read
+  // (see pack_scale_factors()), and how many 4-factor tiles one row group holds along k.
+  const uint8_t *sfa;
+  const uint8_t *sfb;
+  int sf_k_tiles;
+  // Epilogue, applied in fp32 in this order, then one rounding to the output type:
+  //   v = acc * (row_scale[m] * col_scale[n]);  v *= *global_scale;  v += bias[n];
+  //   v = act(v);  v += residual[(m % residual_rows) * residual_ld + n]
+  const float *row_scale;      // (m) or NULL
+  const float *col_scale;      // (n), or (1) when col_scale_scalar, or NULL
+  int col_scale_scalar;
+  const float *global_scale;   // (1) or NULL
+  const void *bias;            // (n) in the output type, or NULL
+  const void *residual;        // rows of n in the output type, or NULL
+  int residual_rows;           // period of the residual's rows over m (m itself for a full one)
+  int64_t residual_ld;
+  int act;
+  int out_bf16;                // 1 bf16, 0 fp16
+  void *out;                   // (m, n), pitch n
+  uint32_t *status;            // device word, zeroed by the caller; non-zero after a failed wait
+  cudaStream_t stream;
+};
+
+// Launches the GEMM. Returns cudaSuccess or the launch/encode error; `why` then points at a
+// static description. Never allocates.
+cudaError_t launch_gemm(const GemmArgs &args, const char **why);
+
+// Number of SMs the persistent grid is sized for on the current device.
+int sm_count();
+
+}  // namespace flsm100

@@ -1,0 +1,368 @@
+// Helper kernels of the quantized-linear path. All of them are HBM-bound streaming kernels:
+// 16-byte vector accesses, one pass where the row fits in registers' reach of L1, grids sized by
+// rows. Divisions are IEEE (this file is compiled without fast-math) because the codes must be
+// bit-identical to the CPU oracle's.
+#include "quant_sm100.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+
+#include <atomic>
+
+namespace flsm100 {
+
+namespace {
+
+std::atomic<int64_t> g_helper_launches{0};
+
+__device__ __forceinline__ float widen(uint16_t v, int is_bf16) {
+  if (is_bf16) return __uint_as_float(static_cast<uint32_t>(v) << 16);
+  return __half2float(__ushort_as_half(v));
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ float block_max(float v, float *red) {
+  v = warp_max(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = (lane < nwarps) ? red[lane] : 0.0f;
+  r = warp_max(r);
+  __syncthreads();
+  return r;
+}
+
+__device__ __forceinline__ uint8_t e4m3_of(float v) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+
+__device__ __forceinline__ float e4m3_value(uint8_t code) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(code), __NV_E4M3);
+  return __half2float(__half(h));
+}
+
+// ---- per-row e4m3 ----------------------------------------------------------------------------
+
+// One CTA per row. Pass 1 finds amax, pass 2 re-reads the row (an L1/L2 hit: a row is a few KB)
+// and writes the codes. VEC: 16-byte accesses, possible when the bases are 16-byte aligned.
+template <bool VEC>
+__global__ void __launch_bounds__(128) quantize_fp8_act_kernel(const uint16_t *__restrict__ x, int is_bf16, int k,
+                                                             uint8_t *__restrict__ codes,
+                                                             float *__restrict__ scales) {
+  __shared__ float red[4];
+  const int64_t row = blockIdx.x;
+  const uint16_t *xr = x + row * k;
+  uint8_t *cr = codes + row * k;
+  float amax = 0.0f;
+  if (VEC) {
+    const uint4 *xv = reinterpret_cast<const uint4 *>(xr);
+    for (int i = threadIdx.x; i < k / 8; i += blockDim.x) {
+      uint4 q = xv[i];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        amax = fmaxf(amax, fabsf(widen(static_cast<uint16_t>(w[j] & 0xffff), is_bf16)));
+        amax = fmaxf(amax, fabsf(widen(static_cast<uint16_t>(w[j] >> 16), is_bf16)));
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < k; i += blockDim.x) amax = fmaxf(amax, fabsf(widen(xr[i], is_bf16)));
+  }
+  amax = block_max(amax, red);
+  const float scale = __fdiv_rn(amax, 448.0f);
+  const float divisor = scale > 0.0f ? scale : 1.0f;
+  if (threadIdx.x == 0) scales[row] = scale;
+  if (VEC) {
+    const uint4 *xv = reinterpret_cast<const uint4 *>(xr);
+    uint2 *cv = reinterpret_cast<uint2 *>(cr);
+    for (int i = threadIdx.x; i < k / 8; i += blockDim.x) {
+      uint4 q = xv[i];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      uint32_t out[2] = {0, 0};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t lo = e4m3_of(__fdiv_rn(widen(static_cast<uint16_t>(w[j] & 0xffff), is_bf16), divisor));
+        uint32_t hi = e4m3_of(__fdiv_rn(widen(static_cast<uint16_t>(w[j] >> 16), is_bf16), divisor));
+        out[j >> 1] |= (lo | (hi << 8)) << ((j & 1) * 16);
+      }
+      cv[i] = make_uint2(out[0], out[1]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < k; i += blockDim.x) cr[i] = e4m3_of(__fdiv_rn(widen(xr[i], is_bf16), divisor));
+  }
+}
+
+__global__ void __launch_bounds__(128) quantize_fp8_rows_f32_kernel(const float *__restrict__ w, int k,
+                                                                  uint8_t *__restrict__ codes,
+                                                                  float *__restrict__ scales) {
+  __shared__ float red[4];
+  const int64_t row = blockIdx.x;
+  const float *wr = w + row * k;
+  float amax = 0.0f;
+  for (int i = threadIdx.x; i < k; i += blockDim.x) amax = fmaxf(amax, fabsf(wr[i]));
+  amax = block_max(amax, red);
+  const float scale = __fdiv_rn(amax, 448.0f);
+  const float divisor = scale > 0.0f ? scale : 1.0f;
+  if (threadIdx.x == 0) scales[row] = scale;
+  for (int i = threadIdx.x; i < k; i += blockDim.x) codes[row * k + i] = e4m3_of(__fdiv_rn(wr[i], divisor));
+}
+
+// ---- NVFP4 -----------------------------------------------------------------------------------
+
+__device__ __forceinline__ int64_t sf_tiled_offset(int r, int b, int sf_k_tiles) {
+  return (static_cast<int64_t>(r / 128) * sf_k_tiles + b / 4) * 512 + (r % 32) * 16 + ((r % 128) / 32) * 4 + (b % 4);
+}
+
+// 16 values -> 8 code bytes and the block's scale code, exactly as the oracle's nvfp4_block().
+__device__ __forceinline__ uint8_t nvfp4_block(const float (&v)[16], float global, uint32_t (&packed)[2]) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  uint8_t sc = global > 0.0f ? e4m3_of(__fdiv_rn(amax, __fmul_rn(6.0f, global))) : 0;
+  const float denom = __fmul_rn(e4m3_value(sc), global);
+  packed[0] = packed[1] = 0;
+  if (!(denom > 0.0f)) return 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float2 pair = make_float2(__fdiv_rn(v[2 * j], denom), __fdiv_rn(v[2 * j + 1], denom));
+    uint32_t byte = static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(pair, __NV_E2M1, cudaRoundNearest));
+    packed[j >> 2] |= (byte & 0xff) << ((j & 3) * 8);
+  }
+  return sc;
+}
+
+// One thread per 16-element block of a 16-bit activation.
+__global__ void __launch_bounds__(256) quantize_nvfp4_act_kernel(const uint16_t *__restrict__ x, int is_bf16, int m,
+                                                               int k, uint8_t *__restrict__ codes,
+                                                               uint8_t *__restrict__ sf_tiled, int sf_k_tiles,
+                                                               int vec_ok) {
+  const int blocks_per_row = k / 16;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(m) * blocks_per_row) return;
+  const int r = static_cast<int>(idx / blocks_per_row);
+  const int b = static_cast<int>(idx % blocks_per_row);
+  const uint16_t *src = x + static_cast<int64_t>(r) * k + 16 * b;
+  float v[16];
+  if (vec_ok) {
+    const uint4 *sv = reinterpret_cast<const uint4 *>(src);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint4 q = sv[h];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[h * 8 + 2 * j] = widen(static_cast<uint16_t>(w[j] & 0xffff), is_bf16);
+        v[h * 8 + 2 * j + 1] = widen(static_cast<uint16_t>(w[j] >> 16), is_bf16);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = widen(src[j], is_bf16);
+  }
+  uint32_t packed[2];
+  uint8_t sc = nvfp4_block(v, 1.0f, packed);
+  uint8_t *dst = codes + (static_cast<int64_t>(r) * k) / 2 + 8 * b;
+  if (vec_ok) {
+    *reinterpret_cast<uint2 *>(dst) = make_uint2(packed[0], packed[1]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[j] = static_cast<uint8_t>(packed[j >> 2] >> ((j & 3) * 8));
+  }
+  sf_tiled[sf_tiled_offset(r, b, sf_k_tiles)] = sc;
+}
+
+__global__ void __launch_bounds__(256) amax_f32_kernel(const float *__restrict__ w, int64_t numel, uint32_t *amax_word) {
+  __shared__ float red[8];
+  float amax = 0.0f;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < numel;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    amax = fmaxf(amax, fabsf(w[i]));
+  }
+  amax = block_max(amax, red);
+  // Non-negative floats order like their bit patterns.
+  if (threadIdx.x == 0) atomicMax(amax_word, __float_as_uint(amax));
+}
+
+__global__ void nvfp4_global_scale_kernel(const uint32_t *amax_word, float *global_scale) {
+  *global_scale = __fdiv_rn(__uint_as_float(*amax_word), 448.0f * 6.0f);
+}
+
+__global__ void __launch_bounds__(256) quantize_nvfp4_weight_kernel(const float *__restrict__ w, int rows, int k,
+                                                                  const float *__restrict__ global_scale,
+                                                                  uint8_t *__restrict__ codes,
+                                                                  uint8_t *__restrict__ sf_plain) {
+  const int blocks_per_row = k / 16;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(rows) * blocks_per_row) return;
+  const float *src = w + idx * 16;
+  float v[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = src[j];
+  uint32_t packed[2];
+  uint8_t sc = nvfp4_block(v, *global_scale, packed);
+  uint8_t *dst = codes + idx * 8;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) dst[j] = static_cast<uint8_t>(packed[j >> 2] >> ((j & 3) * 8));
+  sf_plain[idx] = sc;
+}
+
+__global__ void __launch_bounds__(256) pack_sf_kernel(const uint8_t *__restrict__ sf_plain, int rows, int kblocks,
+                                                    uint8_t *__restrict__ sf_tiled, int sf_k_tiles) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(rows) * kblocks) return;
+  const int r = static_cast<int>(idx / kblocks);
+  const int b = static_cast<int>(idx % kblocks);
+  sf_tiled[sf_tiled_offset(r, b, sf_k_tiles)] = sf_plain[idx];
+}
+
+// ---- widening and gathers --------------------------------------------------------------------
+
+__global__ void __launch_bounds__(256) widen_e4m3_kernel(const uint8_t *__restrict__ codes, int64_t numel,
+                                                       uint16_t *__restrict__ out, int out_bf16, int vec_ok) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  auto one = [&](uint8_t c) -> uint16_t {
+    __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(c), __NV_E4M3);
+    if (!out_bf16) return h.x;
+    return __bfloat16_as_ushort(__float2bfloat16_rn(__half2float(__half(h))));
+  };
+  if (vec_ok) {
+    const int64_t nvec = numel / 16;
+    const uint4 *cv = reinterpret_cast<const uint4 *>(codes);
+    uint4 *ov = reinterpret_cast<uint4 *>(out);
+    for (int64_t i = tid; i < nvec; i += stride) {
+      uint4 q = cv[i];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      uint32_t o[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        o[2 * j] = one(w[j] & 0xff) | (static_cast<uint32_t>(one((w[j] >> 8) & 0xff)) << 16);
+        o[2 * j + 1] = one((w[j] >> 16) & 0xff) | (static_cast<uint32_t>(one(w[j] >> 24)) << 16);
+      }
+      ov[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
+      ov[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+    for (int64_t i = nvec * 16 + tid; i < numel; i += stride) out[i] = one(codes[i]);
+  } else {
+    for (int64_t i = tid; i < numel; i += stride) out[i] = one(codes[i]);
+  }
+}
+
+struct ExpandDims {
+  int ndim;
+  int32_t shape[8];
+  int64_t stride[8];
+};
+
+__global__ void __launch_bounds__(256) expand_16_kernel(const uint16_t *__restrict__ src, ExpandDims d, int64_t numel,
+                                                      uint16_t *__restrict__ dst) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < numel;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int64_t rem = i, off = 0;
+    for (int a = d.ndim - 1; a >= 0; --a) {
+      off += (rem % d.shape[a]) * d.stride[a];
+      rem /= d.shape[a];
+    }
+    dst[i] = src[off];
+  }
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+inline int capped_grid(int64_t work_items, int per_block) {
+  int64_t g = (work_items + per_block - 1) / per_block;
+  const int64_t cap = 148 * 16;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return static_cast<int>(g);
+}
+
+}  // namespace
+
+int64_t helper_launch_count() { return g_helper_launches.load(); }
+
+cudaError_t quantize_fp8_act(const void *x, int is_bf16, int m, int k, uint8_t *codes, float *scales,
+                             cudaStream_t stream) {
+  const bool vec = aligned16(x) && aligned16(codes) && (k % 16 == 0);
+  const uint16_t *xs = static_cast<const uint16_t *>(x);
+  if (vec) quantize_fp8_act_kernel<true><<<m, 128, 0, stream>>>(xs, is_bf16, k, codes, scales);
+  else quantize_fp8_act_kernel<false><<<m, 128, 0, stream>>>(xs, is_bf16, k, codes, scales);
+  ++g_helper_launches;
+  return cudaGetLastError();
+}
+
+cudaError_t quantize_fp8_rows_f32(const float *w, int rows, int k, uint8_t *codes, float *scales,
+                                  cudaStream_t stream) {
+  quantize_fp8_rows_f32_kernel<<<rows, 128, 0, stream>>>(w, k, codes, scales);
+  ++g_helper_launches;
+  return cudaGetLastError();
+}
+
+cudaError_t quantize_nvfp4_act(const void *x, int is_bf16, int m, int k, uint8_t *codes, uint8_t *sf_tiled,
+                               cudaStream_t stream) {
+  const int64_t blocks = static_cast<int64_t>(m) * (k / 16);
+  const int grid = static_cast<int>((blocks + 255) / 256);
+  const int vec = aligned16(x) && (reinterpret_cast<uintptr_t>(codes) & 7) == 0;
+  quantize_nvfp4_act_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t *>(x), is_bf16, m, k, codes,
+                                                     sf_tiled, sf_k_tiles_for(k), vec);
+  ++g_helper_launches;
+  return cudaGetLastError();
+}
+
+cudaError_t quantize_nvfp4_weight_f32(const float *w, int rows, int k, uint8_t *codes, uint8_t *sf_plain,
+                                      float *global_scale, uint32_t *amax_word, cudaStream_t stream) {
+  const int64_t numel = static_cast<int64_t>(rows) * k;
+  cudaError_t e = cudaMemsetAsync(amax_word, 0, sizeof(uint32_t), stream);
+  if (e != cudaSuccess) return e;
+  amax_f32_kernel<<<capped_grid(numel, 256 * 8), 256, 0, stream>>>(w, numel, amax_word);
+  nvfp4_global_scale_kernel<<<1, 1, 0, stream>>>(amax_word, global_scale);
+  const int64_t blocks = numel / 16;
+  quantize_nvfp4_weight_kernel<<<static_cast<int>((blocks + 255) / 256), 256, 0, stream>>>(w, rows, k, global_scale,
+                                                                                          codes, sf_plain);
+  g_helper_launches += 3;
+  return cudaGetLastError();
+}
+
+cudaError_t pack_scale_factors(const uint8_t *sf_plain, int rows, int k, uint8_t *sf_tiled, cudaStream_t stream) {
+  const int kblocks = k / 16;
+  const int64_t n = static_cast<int64_t>(rows) * kblocks;
+  pack_sf_kernel<<<static_cast<int>((n + 255) / 256), 256, 0, stream>>>(sf_plain, rows, kblocks, sf_tiled,
+                                                                       sf_k_tiles_for(k));
+  ++g_helper_launches;
+  return cudaGetLastError();
+}
+
+cudaError_t widen_e4m3(const uint8_t *codes, int64_t numel, void *out16, int out_bf16, cudaStream_t stream) {
+  const int vec = aligned16(codes) && aligned16(out16);
+  widen_e4m3_kernel<<<capped_grid(numel, 256 * 16), 256, 0, stream>>>(codes, numel, static_cast<uint16_t *>(out16),
+                                                                     out_bf16, vec);
+  ++g_helper_launches;
+  return cudaGetLastError();
+}
+
+cudaError_t expand_16(const void *src, const int32_t *shape, const int64_t *stride, int ndim, void *dst,
+                      cudaStream_t stream) {
+  if (ndim > 8) return cudaErrorInvalidValue;
+  ExpandDims d;
+  d.ndim = ndim;
+  int64_t numel = 1;
+  for (int i = 0; i < ndim; ++i) {
+    d.shape[i] = shape[i];
+    d.stride[i] = stride[i];
+    numel *= shape[i];
+  }
+  if (numel == 0) return cudaSuccess;
+  expand_16_kernel<<<capped_grid(numel, 256), 256, 0, stream>>>(static_cast<const uint16_t *>(src), d, numel,
+                                                               static_cast<uint16_t *>(dst));
+  ++g_helper_launches;
+  return cudaGetLastError();
+}
+
+}  // namespace flsm100

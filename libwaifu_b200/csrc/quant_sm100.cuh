@@ -1,0 +1,47 @@
+// Bandwidth-shaped helper kernels around the GEMM: the dynamic activation quantisers, the
+// device-side weight quantisers, the scale-factor re-tiling NVFP4 needs, and the e4m3 -> half
+// widening of the reference-compatible path. None of them allocates.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace flsm100 {
+
+// Per-row (token) e4m3: scales[r] = amax_r / 448, codes = e4m3_rn_sat(x / scales[r]); a zero
+// row gives scale 0 and codes 0 (the zero rule of tools/model_writer.py:162-170).
+cudaError_t quantize_fp8_act(const void *x, int is_bf16, int m, int k, uint8_t *codes, float *scales,
+                             cudaStream_t stream);
+cudaError_t quantize_fp8_rows_f32(const float *w, int rows, int k, uint8_t *codes, float *scales,
+                                  cudaStream_t stream);
+
+// Scale factors of a (rows, k/16) operand in the tile layout the block-scaled MMA reads: tiles
+// of 128 rows x 4 factors (512 bytes), byte (r % 32) * 16 + ((r % 128) / 32) * 4 + (b % 4) of
+// tile (r / 128, b / 4); tiles of one row group are consecutive, `sf_k_tiles` per group.
+inline int sf_k_tiles_for(int k) { return ((k / 16 + 3) / 4 + 3) / 4 * 4; }
+inline int64_t sf_tiled_bytes(int rows, int k, int extra_groups) {
+  return static_cast<int64_t>((rows + 127) / 128 + extra_groups) * sf_k_tiles_for(k) * 512;
+}
+
+// Per-16-block e2m1 with unsigned-e4m3 block scales, global scale 1; codes (m, k/2) row-major,
+// scale factors written straight into the tile layout (`sf_tiled` zeroed by the caller).
+cudaError_t quantize_nvfp4_act(const void *x, int is_bf16, int m, int k, uint8_t *codes, uint8_t *sf_tiled,
+                               cudaStream_t stream);
+// NVFP4 weight from fp32: global = amax / (448 * 6); plain (rows, k/16) block scales.
+// `amax_word` is a device word used for the reduction.
+cudaError_t quantize_nvfp4_weight_f32(const float *w, int rows, int k, uint8_t *codes, uint8_t *sf_plain,
+                                      float *global_scale, uint32_t *amax_word, cudaStream_t stream);
+// Plain (rows, k/16) scale factors -> tile layout (`sf_tiled` zeroed by the caller).
+cudaError_t pack_scale_factors(const uint8_t *sf_plain, int rows, int k, uint8_t *sf_tiled, cudaStream_t stream);
+
+// codes -> fp16 / bf16 values (exact), the widening flint's kernel does in registers
+// (flint/cuda/gemm_fp8_cutlass.cu:20-29).
+cudaError_t widen_e4m3(const uint8_t *codes, int64_t numel, void *out16, int out_bf16, cudaStream_t stream);
+
+// Strided gather of a 16-bit view into a contiguous buffer (for addends no epilogue can index).
+cudaError_t expand_16(const void *src, const int32_t *shape, const int64_t *stride, int ndim, void *dst,
+                      cudaStream_t stream);
+
+int64_t helper_launch_count();
+
+}  // namespace flsm100

@@ -1,0 +1,390 @@
+"""Host-side mirror of the reference's safe wrapper over the flint C ABI, for the quantized-linear
+path only: ``Tensor`` (waifu/src/flint/tensor.rs), ``fp8_available`` (waifu/src/flint/fp8.rs:41-49)
+and ``functional.fp8_matmul`` / ``fp8_matmul_add`` (waifu/src/flint/functional.rs:653-703), plus the
+additive ``fp8_linear`` / ``nvfp4_linear``. Everything goes through ``libflint_sm100.so`` by ctypes,
+exactly the calls a cgo/Rust/ctypes binding of the reference would make.
+
+There is no fallback: if the CUDA library is missing, importing this module's ``lib()`` raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, byref, c_char_p, c_int32, c_int64, c_void_p
+from typing import Optional, Sequence
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "lib", "libflint_sm100.so")
+
+# flint/capi.h:48-54
+FL_OK = 0
+FL_ERROR_INVALID_ARG = 0x0100
+FL_ERROR_ABORTED = 0x0102
+FL_ERROR_OUT_OF_MEMORY = 0x0103
+
+
+class DType:
+    """flint/capi.h:84-94, plus the two appended values."""
+    FLOAT = 1
+    LONG = 2
+    UINT8 = 3
+    FLOAT16 = 4
+    INT8 = 6
+    BOOL = 8
+    INT32 = 9
+    FP8E4M3 = 10
+    BFLOAT16 = 11
+    FP4E2M1X2 = 12
+
+
+DTYPE_SIZE = {DType.FLOAT: 4, DType.LONG: 8, DType.UINT8: 1, DType.FLOAT16: 2, DType.INT8: 1, DType.BOOL: 1,
+              DType.INT32: 4, DType.FP8E4M3: 1, DType.BFLOAT16: 2, DType.FP4E2M1X2: 1}
+
+
+class Device:
+    """flint/capi.h:96-106"""
+    CPU = 0
+    CUDA = 1
+    CUDA_HOST = 2
+    METAL = 3
+    VULKAN = 4
+    UNKNOWN = 5
+
+
+ACT_NONE = 0
+ACT_GELU_TANH = 1
+
+
+class FlintError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"flint error 0x{code:04x}: {message}")
+        self.code = code
+        self.message = message
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded C-ABI library. Raises if it has not been built -- there is no other path."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m libwaifu_b200.build` (needs nvcc). "
+            "The quantized-linear path has no CPU or library fallback.")
+    L = ctypes.CDLL(LIB_PATH)
+    V = c_void_p
+    L.fl_init.restype = None
+    L.fl_get_last_error_code.restype = c_int32
+    L.fl_get_last_error_message.restype = c_char_p
+    L.fl_is_device_available.argtypes = [c_int32, POINTER(c_int32)]
+    L.fl_operators_create.argtypes = [c_int32, POINTER(V)]
+    L.fl_operators_destroy.argtypes = [V]; L.fl_operators_destroy.restype = None
+    L.fl_operators_get_device.argtypes = [V, POINTER(c_int32)]
+    L.fl_tensor_data_create.argtypes = [c_int32, c_int32, c_int64, c_int32, POINTER(V)]
+    L.fl_tensor_data_borrow.argtypes = [V, c_int32, c_int64, POINTER(V)]
+    L.fl_tensor_data_borrow_device.argtypes = [V, c_int32, c_int64, POINTER(V)]
+    L.fl_tensor_data_destroy.argtypes = [V]; L.fl_tensor_data_destroy.restype = None
+    L.fl_tensor_data_get_host_ptr.argtypes = [V, POINTER(V)]
+    L.fl_tensor_view_create.argtypes = [V, POINTER(c_int32), POINTER(c_int32), c_int32, c_int64, POINTER(V)]
+    L.fl_tensor_view_destroy.argtypes = [V]; L.fl_tensor_view_destroy.restype = None
+    L.fl_transfer.argtypes = [V, V, V]
+    L.fl_fp8_available.argtypes = [c_int32, POINTER(c_int32)]
+    L.fl_nvfp4_available.argtypes = [c_int32, POINTER(c_int32)]
+    L.fl_fp8_matmul.argtypes = [V, V, V, V]
+    L.fl_fp8_matmul_add.argtypes = [V, V, V, V, V]
+    L.fl_fp8_linear.argtypes = [V, V, V, V, V, c_int32, V]
+    L.fl_nvfp4_linear.argtypes = [V, V, V, V, V, V, c_int32, V]
+    L.fl_quantize_fp8_rows.argtypes = [V, V, V]
+    L.fl_quantize_fp8_activation.argtypes = [V, V, V]
+    L.fl_quantize_nvfp4.argtypes = [V, V, V, V]
+    L.fl_sm100_set_device.argtypes = [c_int32]
+    L.fl_sm100_synchronize.argtypes = [POINTER(c_int32)]
+    L.fl_sm100_launch_count.restype = c_int64
+    for name in ("fl_is_device_available", "fl_operators_create", "fl_operators_get_device", "fl_tensor_data_create",
+                 "fl_tensor_data_borrow", "fl_tensor_data_borrow_device", "fl_tensor_data_get_host_ptr",
+                 "fl_tensor_view_create", "fl_transfer", "fl_fp8_available", "fl_nvfp4_available", "fl_fp8_matmul",
+                 "fl_fp8_matmul_add", "fl_fp8_linear", "fl_nvfp4_linear", "fl_quantize_fp8_rows",
+                 "fl_quantize_fp8_activation", "fl_quantize_nvfp4", "fl_sm100_set_device", "fl_sm100_synchronize"):
+        getattr(L, name).restype = c_int32
+    L.fl_init()
+    _lib = L
+    return L
+
+
+def check(code: int) -> None:
+    """waifu/src/flint/mod.rs `check`: a non-zero code becomes an error carrying the message."""
+    if code != FL_OK:
+        raise FlintError(code, lib().fl_get_last_error_message().decode("utf-8", "replace"))
+
+
+def init() -> None:
+    lib()
+
+
+def set_device(ordinal: int) -> None:
+    check(lib().fl_sm100_set_device(int(ordinal)))
+
+
+def synchronize() -> None:
+    status = c_int32(0)
+    check(lib().fl_sm100_synchronize(byref(status)))
+
+
+def launch_count() -> int:
+    return int(lib().fl_sm100_launch_count())
+
+
+def fp8_available(device: int = Device.CUDA) -> bool:
+    """waifu/src/flint/fp8.rs:41-49: a device without the kernels answers no, never an error."""
+    out = c_int32(0)
+    try:
+        check(lib().fl_fp8_available(int(device), byref(out)))
+    except FlintError:
+        return False
+    return out.value != 0
+
+
+def nvfp4_available(device: int = Device.CUDA) -> bool:
+    out = c_int32(0)
+    try:
+        check(lib().fl_nvfp4_available(int(device), byref(out)))
+    except FlintError:
+        return False
+    return out.value != 0
+
+
+_operators = None
+
+
+def operators():
+    """The CUDA operators handle (process-wide, as flint's are: flint/operators.cc:696-793)."""
+    global _operators
+    if _operators is None:
+        h = c_void_p()
+        check(lib().fl_operators_create(Device.CUDA, byref(h)))
+        _operators = h
+    return _operators
+
+
+def _contiguous_strides(shape: Sequence[int]):
+    strides = []
+    acc = 1
+    for s in reversed(shape):
+        strides.append(acc)
+        acc *= max(int(s), 1)
+    return list(reversed(strides))
+
+
+class Tensor:
+    """Storage plus one view of it (waifu/src/flint/tensor.rs). Owns its storage unless borrowed."""
+
+    def __init__(self, data: c_void_p, view: c_void_p, shape, dtype: int, device: int, owns_data: bool = True,
+                 keepalive=None):
+        self._data = data
+        self._view = view
+        self._shape = tuple(int(s) for s in shape)
+        self._dtype = dtype
+        self._device = device
+        self._owns = owns_data
+        self._keepalive = keepalive
+
+    # -- construction ---------------------------------------------------------------------
+    @staticmethod
+    def empty(shape: Sequence[int], dtype: int, device: int = Device.CUDA) -> "Tensor":
+        numel = int(np.prod(shape)) if len(shape) else 1
+        data = c_void_p()
+        check(lib().fl_tensor_data_create(device, dtype, max(numel, 1), 0, byref(data)))
+        return Tensor._over(data, shape, _contiguous_strides(shape), 0, dtype, device, True)
+
+    @staticmethod
+    def _over(data, shape, stride, offset, dtype, device, owns, keepalive=None) -> "Tensor":
+        nd = len(shape)
+        sh = (c_int32 * max(nd, 1))(*[int(s) for s in shape])
+        st = (c_int32 * max(nd, 1))(*[int(s) for s in stride])
+        view = c_void_p()
+        code = lib().fl_tensor_view_create(data, sh, st, nd, int(offset), byref(view))
+        if code != FL_OK:
+            if owns:
+                lib().fl_tensor_data_destroy(data)
+            check(code)
+        return Tensor(data, view, shape, dtype, device, owns, keepalive)
+
+    @staticmethod
+    def from_numpy(arr: np.ndarray, dtype: int, device: int = Device.CUDA) -> "Tensor":
+        """Copies a host array (whose bytes already are `dtype`'s encoding) to `device`."""
+        arr = np.ascontiguousarray(arr)
+        assert arr.dtype.itemsize == DTYPE_SIZE[dtype], (arr.dtype, dtype)
+        host_data = c_void_p()
+        check(lib().fl_tensor_data_borrow(arr.ctypes.data_as(c_void_p), dtype, max(arr.size, 1), byref(host_data)))
+        host = Tensor._over(host_data, arr.shape, _contiguous_strides(arr.shape), 0, dtype, Device.CPU, True, arr)
+        if device == Device.CPU:
+            return host
+        out = Tensor.empty(arr.shape, dtype, device)
+        if arr.size:
+            check(lib().fl_transfer(operators(), host.raw(), out.raw()))
+        return out
+
+    @staticmethod
+    def from_device_ptr(ptr: int, shape: Sequence[int], dtype: int, keepalive=None, stride=None,
+                        numel: Optional[int] = None) -> "Tensor":
+        """A view over device memory someone else owns (a torch tensor's data_ptr())."""
+        n = int(np.prod(shape)) if numel is None else int(numel)
+        data = c_void_p()
+        check(lib().fl_tensor_data_borrow_device(c_void_p(ptr), dtype, max(n, 1), byref(data)))
+        st = _contiguous_strides(shape) if stride is None else stride
+        return Tensor._over(data, shape, st, 0, dtype, Device.CUDA, True, keepalive)
+
+    # -- access ---------------------------------------------------------------------------
+    def raw(self) -> c_void_p:
+        return self._view
+
+    @property
+    def shape(self):
+        return self._shape
+
+    @property
+    def dtype(self) -> int:
+        return self._dtype
+
+    @property
+    def device(self) -> int:
+        return self._device
+
+    def view_as(self, shape, stride, offset=0) -> "Tensor":
+        """Another view of the same storage (shares it; this tensor must outlive the result)."""
+        return Tensor._over(self._data, shape, stride, offset, self._dtype, self._device, False, self)
+
+    def numpy(self) -> np.ndarray:
+        """Copies to the host; 16-bit floats and codes come back as raw uint16 / uint8."""
+        np_dtype = {1: np.uint8, 2: np.uint16, 4: np.float32 if self._dtype == DType.FLOAT else np.int32,
+                    8: np.int64}[DTYPE_SIZE[self._dtype]]
+        out = np.empty(self._shape, dtype=np_dtype)
+        if out.size == 0:
+            return out
+        if self._device == Device.CPU:
+            p = c_void_p()
+            check(lib().fl_tensor_data_get_host_ptr(self._data, byref(p)))
+            ctypes.memmove(out.ctypes.data, p.value, out.nbytes)
+            return out
+        host_data = c_void_p()
+        check(lib().fl_tensor_data_borrow(out.ctypes.data_as(c_void_p), self._dtype, out.size, byref(host_data)))
+        host = Tensor._over(host_data, out.shape, _contiguous_strides(out.shape), 0, self._dtype, Device.CPU, True, out)
+        check(lib().fl_transfer(operators(), self.raw(), host.raw()))
+        return out
+
+    def __del__(self):
+        try:
+            L = _lib
+            if L is None:
+                return
+            if self._view:
+                L.fl_tensor_view_destroy(self._view)
+                self._view = None
+            if self._owns and self._data:
+                L.fl_tensor_data_destroy(self._data)
+                self._data = None
+        except Exception:
+            pass
+
+
+def _fp8_result(a: Tensor, rows: int) -> Tensor:
+    """waifu/src/flint/functional.rs:655-662: (..., rows) in the activation's type on the device."""
+    if len(a.shape) < 1:
+        raise FlintError(FL_ERROR_INVALID_ARG, "fp8 matmul: an operand has no dimensions")
+    return Tensor.empty(tuple(a.shape[:-1]) + (rows,), a.dtype, Device.CUDA)
+
+
+def _broadcast_to(addend: Tensor, out: Tensor) -> Tensor:
+    """waifu/src/flint/functional.rs:80-108: the addend expanded to out's shape as a zero-stride view."""
+    ashape = addend.shape
+    oshape = out.shape
+    if len(ashape) > len(oshape):
+        raise FlintError(FL_ERROR_INVALID_ARG, "fp8_matmul_add: the addend has more dimensions than the product")
+    base = _contiguous_strides(ashape)
+    shape, stride = [], []
+    pad = len(oshape) - len(ashape)
+    for i, o in enumerate(oshape):
+        if i < pad:
+            shape.append(o); stride.append(0)
+            continue
+        a = ashape[i - pad]
+        if a == o:
+            shape.append(o); stride.append(base[i - pad])
+        elif a == 1:
+            shape.append(o); stride.append(0)
+        else:
+            raise FlintError(FL_ERROR_INVALID_ARG, f"fp8_matmul_add: {ashape} does not broadcast to {oshape}")
+    return addend.view_as(shape, stride, 0)
+
+
+def fp8_matmul(a: Tensor, weight: Tensor, scale: Tensor) -> Tensor:
+    """`a` (..., k) times the transpose of an FP8 weight (rows, k) with one <float> scale, as
+    (..., rows); the activation is not narrowed (functional.rs:664-680)."""
+    out = _fp8_result(a, weight.shape[0])
+    check(lib().fl_fp8_matmul(a.raw(), weight.raw(), scale.raw(), out.raw()))
+    return out
+
+
+def fp8_matmul_add(a: Tensor, weight: Tensor, scale: Tensor, addend: Tensor, expand: bool = True) -> Tensor:
+    """fp8_matmul plus a bias or residual added in the epilogue, one rounding (functional.rs:682-703).
+    `expand` pre-broadcasts the addend to the product's shape as a view, as the Rust wrapper does;
+    pass False to hand the addend over as it is, as the reference's C++ tests do."""
+    out = _fp8_result(a, weight.shape[0])
+    if addend.dtype != out.dtype:
+        raise FlintError(FL_ERROR_INVALID_ARG, "fp8_matmul_add: the addend is not of the product's type")
+    ad = _broadcast_to(addend, out) if expand else addend
+    check(lib().fl_fp8_matmul_add(a.raw(), weight.raw(), scale.raw(), ad.raw(), out.raw()))
+    return out
+
+
+def fp8_linear(a: Tensor, weight: Tensor, scales: Tensor, bias: Optional[Tensor] = None,
+               residual: Optional[Tensor] = None, act: int = ACT_NONE, out: Optional[Tensor] = None) -> Tensor:
+    """Dynamic per-token e4m3 activation x e4m3 weight with per-channel (or per-tensor) scales and
+    the fused bias / GELU-tanh / residual epilogue."""
+    if out is None:
+        out = _fp8_result(a, weight.shape[0])
+    check(lib().fl_fp8_linear(a.raw(), weight.raw(), scales.raw(), bias.raw() if bias else None,
+                              residual.raw() if residual else None, int(act), out.raw()))
+    return out
+
+
+def nvfp4_linear(a: Tensor, codes: Tensor, block_scales: Tensor, global_scale: Tensor,
+                 bias: Optional[Tensor] = None, residual: Optional[Tensor] = None, act: int = ACT_NONE,
+                 out: Optional[Tensor] = None) -> Tensor:
+    """Dynamic per-16-block e2m1 activation x NVFP4 weight with the same fused epilogue."""
+    if out is None:
+        out = _fp8_result(a, codes.shape[0])
+    check(lib().fl_nvfp4_linear(a.raw(), codes.raw(), block_scales.raw(), global_scale.raw(),
+                                bias.raw() if bias else None, residual.raw() if residual else None, int(act),
+                                out.raw()))
+    return out
+
+
+def quantize_fp8_rows(w: Tensor):
+    rows, k = w.shape
+    codes = Tensor.empty((rows, k), DType.FP8E4M3)
+    scales = Tensor.empty((rows,), DType.FLOAT)
+    check(lib().fl_quantize_fp8_rows(w.raw(), codes.raw(), scales.raw()))
+    return codes, scales
+
+
+def quantize_fp8_activation(a: Tensor):
+    m, k = a.shape
+    codes = Tensor.empty((m, k), DType.FP8E4M3)
+    scales = Tensor.empty((m,), DType.FLOAT)
+    check(lib().fl_quantize_fp8_activation(a.raw(), codes.raw(), scales.raw()))
+    return codes, scales
+
+
+def quantize_nvfp4(w: Tensor):
+    rows, k = w.shape
+    codes = Tensor.empty((rows, k // 2), DType.FP4E2M1X2)
+    sf = Tensor.empty((rows, k // 16), DType.FP8E4M3)
+    g = Tensor.empty((1,), DType.FLOAT)
+    check(lib().fl_quantize_nvfp4(w.raw(), codes.raw(), sf.raw(), g.raw()))
+    return codes, sf, g

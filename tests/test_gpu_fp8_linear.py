@@ -1,0 +1,185 @@
+"""GPU parity of fl_fp8_linear (dynamic per-token e4m3 activation x e4m3 weight, per-channel
+scales, fused bias / GELU-tanh / residual) against the CPU oracle, through the C ABI.
+Tolerance: relative L2 <= 5e-3 and max abs error <= 2 bf16 ulp at the output's scale."""
+import os
+
+import numpy as np
+import pytest
+
+from helpers import check_parity, randn
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(F, arr, dtype):
+    return F.Tensor.from_numpy(arr, dtype, F.Device.CUDA)
+
+
+def make_case(O, rng, m, n, k, is_bf16=True, bias=False, residual=False, per_tensor=False):
+    x = O.narrow(randn(rng, (m, k)), is_bf16)
+    w = randn(rng, (n, k), 0.02)
+    if per_tensor:
+        codes, scales = O.quantize_fp8_tensor(w)
+    else:
+        codes, scales = O.quantize_fp8_rows(w)
+    b = O.narrow(randn(rng, (n,), 0.01), is_bf16) if bias else None
+    r = O.narrow(randn(rng, (m, n)), is_bf16) if residual else None
+    return x, codes, scales, b, r
+
+
+def run(F, x, codes, scales, bias, res, act, is_bf16=True):
+    dt = F.DType.BFLOAT16 if is_bf16 else F.DType.FLOAT16
+    out = F.fp8_linear(dev(F, x, dt), dev(F, codes, F.DType.FP8E4M3), dev(F, scales, F.DType.FLOAT),
+                       dev(F, bias, dt) if bias is not None else None, dev(F, res, dt) if res is not None else None, act)
+    y = out.numpy()
+    F.synchronize()
+    return y
+
+
+def test_activation_quantiser_is_bit_exact(flint, oracle):
+    rng = np.random.default_rng(21)
+    F = flint
+    for is_bf16 in (True, False):
+        for (m, k) in [(5, 16), (130, 208), (257, 3072)]:
+            x = oracle.narrow(randn(rng, (m, k)), is_bf16)
+            x[min(3, m - 1)] = 0  # a zero row: scale 0, codes 0
+            x[0, 0] = oracle.narrow(np.array([1e4], np.float32), is_bf16)[0]  # an outlier row
+            codes, scales = F.quantize_fp8_activation(dev(F, x, F.DType.BFLOAT16 if is_bf16 else F.DType.FLOAT16))
+            want_c, want_s = oracle.quantize_fp8_act(x, is_bf16)
+            assert np.array_equal(scales.numpy().view(np.uint32), want_s.view(np.uint32))
+            assert np.array_equal(codes.numpy(), want_c)
+
+
+def test_weight_quantiser_is_bit_exact(flint, oracle):
+    rng = np.random.default_rng(22)
+    F = flint
+    w = randn(rng, (72, 208), 0.02)
+    w[7] = 0
+    codes, scales = F.quantize_fp8_rows(dev(F, w, F.DType.FLOAT))
+    want_c, want_s = oracle.quantize_fp8_rows(w)
+    assert np.array_equal(scales.numpy().view(np.uint32), want_s.view(np.uint32))
+    assert np.array_equal(codes.numpy(), want_c)
+
+
+EDGE = [(1, 8, 16), (2, 16, 16), (17, 128, 64), (129, 264, 96), (64, 64, 80), (300, 200, 256), (513, 64, 64),
+        (128, 256, 128), (1, 3072, 3072), (16, 12288, 3072), (256, 1032, 144)]
+
+
+@pytest.mark.parametrize("m,n,k", EDGE)
+def test_edge_shapes(flint, oracle, m, n, k):
+    rng = np.random.default_rng(100 + m + n + k)
+    x, codes, scales, b, r = make_case(oracle, rng, m, n, k, bias=True, residual=True)
+    got = run(flint, x, codes, scales, b, r, 0)
+    want = oracle.fp8_linear(x, codes, scales, b, r, 0)
+    check_parity(oracle, got, want, True, what=f"{m}x{n}x{k}")
+
+
+@pytest.mark.parametrize("act", [0, 1])
+@pytest.mark.parametrize("is_bf16", [True, False])
+def test_epilogue_variants(flint, oracle, act, is_bf16):
+    rng = np.random.default_rng(31 + act)
+    for bias, residual, per_tensor in [(False, False, False), (True, False, True), (False, True, False), (True, True, False)]:
+        x, codes, scales, b, r = make_case(oracle, rng, 200, 320, 192, is_bf16, bias, residual, per_tensor)
+        got = run(flint, x, codes, scales, b, r, act, is_bf16)
+        want = oracle.fp8_linear(x, codes, scales, b, r, act, is_bf16)
+        check_parity(oracle, got, want, is_bf16, what=f"act={act} bias={bias} res={residual} pt={per_tensor}")
+
+
+def test_zero_rows_and_outliers(flint, oracle):
+    rng = np.random.default_rng(41)
+    x, codes, scales, b, r = make_case(oracle, rng, 96, 136, 128, bias=True)
+    x[5] = 0
+    x[9, 17] = oracle.narrow(np.array([1e4], np.float32), True)[0]
+    codes[3] = 0
+    scales[3] = 0.0
+    got = run(flint, x, codes, scales, b, None, 0)
+    want = oracle.fp8_linear(x, codes, scales, b, None, 0)
+    assert np.array_equal(got[5], want[5])  # zero activation row -> bias only
+    check_parity(oracle, got, want, True, what="zeros/outliers")
+
+
+def test_all_codes_sweep(flint, oracle):
+    """Every finite e4m3 code on both sides with unit scales: products are exact in fp32."""
+    F = flint
+    finite = np.array([c for c in range(256) if (c & 0x7F) != 0x7F], np.uint8)
+    rng = np.random.default_rng(42)
+    codes = rng.choice(finite, size=(256, 256))
+    # An activation whose every row's amax is 448 quantises to its own codes with scale 1.
+    table = oracle.e4m3_decode_table()
+    xa = rng.choice(finite, size=(128, 256))
+    xa[:, 0] = 0x7E
+    vals = table[xa] / 64.0  # keep sums small enough for bf16-exact inputs; scale = 1/64
+    x = oracle.narrow(vals.astype(np.float32), True)
+    got = run(F, x, codes, np.ones(256, np.float32), None, None, 0)
+    want = oracle.fp8_linear(x, codes, np.ones(256, np.float32))
+    check_parity(oracle, got, want, True, what="all codes")
+
+
+@pytest.mark.parametrize("name", ["linear_a", "linear_b"])
+def test_golden_vectors(flint, oracle, name):
+    fx = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "quantized_linear.npz"))
+    bias = fx[name + "_bias"] if name + "_bias" in fx else None
+    res = fx[name + "_res"] if name + "_res" in fx else None
+    got = run(flint, fx[name + "_x"], fx[name + "_codes"], fx[name + "_scales"], bias, res, int(fx[name + "_act"][0]))
+    check_parity(oracle, got, fx[name + "_y"], True, what=name)
+
+
+def test_config1_single_fp8_linear(flint, oracle):
+    """X bf16 [4096,3072] ~N(0,1), W ~N(0,0.02) e4m3 per-row scales, bias ~N(0,0.01), seed 0."""
+    import torch
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x = torch.randn(4096, 3072, generator=g).bfloat16().view(torch.uint16).numpy()
+    w = (0.02 * torch.randn(3072, 3072, generator=g)).numpy()
+    b = (0.01 * torch.randn(3072, generator=g)).bfloat16().view(torch.uint16).numpy()
+    codes, scales = oracle.quantize_fp8_rows(w)
+    got = run(flint, x, codes, scales, b, None, 0)
+    want = oracle.fp8_linear(x, codes, scales, b, None, 0)
+    r, u = check_parity(oracle, got, want, True, what="config 1")
+    print(f"config 1: rel L2 {r:.3e}, max {u:.2f} ulp")
+
+
+def test_config2_mlp_each_linear_and_chained(flint, oracle):
+    """Qwen-Image-shaped FP8 MLP: up 3072->12288 + GELU-tanh, down 12288->3072 + residual X.
+    Each linear is checked on identical inputs; the chain (the second GEMM fed the GPU's own H
+    against the oracle fed its own H) is checked to the same bound."""
+    import torch
+    F = flint
+    g = torch.Generator(device="cpu").manual_seed(0)
+    m = 4352
+    x = torch.randn(m, 3072, generator=g).bfloat16().view(torch.uint16).numpy()
+    w_up = (0.02 * torch.randn(12288, 3072, generator=g)).numpy()
+    w_down = (0.02 * torch.randn(3072, 12288, generator=g)).numpy()
+    up_c, up_s = oracle.quantize_fp8_rows(w_up)
+    dn_c, dn_s = oracle.quantize_fp8_rows(w_down)
+    bf = F.DType.BFLOAT16
+    xd = dev(F, x, bf)
+    h = F.fp8_linear(xd, dev(F, up_c, F.DType.FP8E4M3), dev(F, up_s, F.DType.FLOAT), None, None, F.ACT_GELU_TANH)
+    y = F.fp8_linear(h, dev(F, dn_c, F.DType.FP8E4M3), dev(F, dn_s, F.DType.FLOAT), None, xd, F.ACT_NONE)
+    h_gpu, y_gpu = h.numpy(), y.numpy()
+    F.synchronize()
+    h_ref = oracle.fp8_linear(x, up_c, up_s, None, None, oracle.ACT_GELU_TANH)
+    check_parity(oracle, h_gpu, h_ref, True, what="up + GELU")
+    y_same_in = oracle.fp8_linear(h_gpu, dn_c, dn_s, None, x, oracle.ACT_NONE)
+    check_parity(oracle, y_gpu, y_same_in, True, what="down + residual (same H)")
+    y_chain = oracle.fp8_linear(h_ref, dn_c, dn_s, None, x, oracle.ACT_NONE)
+    check_parity(oracle, y_gpu, y_chain, True, what="chained MLP")
+
+
+def test_linearity_in_the_weight_scale_at_full_size(flint, oracle):
+    """A size-independent property at the benchmark's size: doubling every channel scale doubles
+    the product exactly (power-of-two scaling commutes with every rounding involved)."""
+    rng = np.random.default_rng(51)
+    F = flint
+    m, n, k = 4352, 3072, 3072
+    x = oracle.narrow(randn(rng, (m, k)), True)
+    codes = rng.integers(0, 256, size=(n, k), dtype=np.uint8)
+    codes[(codes & 0x7F) == 0x7F] = 0x3C
+    scales = (rng.random(n).astype(np.float32) + 0.5) * np.float32(1e-3)
+    xd, cd = dev(F, x, F.DType.BFLOAT16), dev(F, codes, F.DType.FP8E4M3)
+    y1 = F.fp8_linear(xd, cd, dev(F, scales, F.DType.FLOAT)).numpy()
+    y2 = F.fp8_linear(xd, cd, dev(F, scales * 2, F.DType.FLOAT)).numpy()
+    assert np.array_equal(oracle.widen(y1, True) * 2, oracle.widen(y2, True))
+    # and a row subsample against the oracle
+    rows = rng.choice(m, size=64, replace=False)
+    want = oracle.fp8_linear(x[rows], codes, scales)
+    check_parity(oracle, y1[rows], want, True, what="row subsample")
