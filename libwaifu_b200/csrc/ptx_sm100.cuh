@@ -61,7 +61,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // Upper bound on try_wait polls before a wait gives up. One poll blocks for a hardware-chosen
 // slice (well under a millisecond), so the bound is reached only when the awaited event never
 // comes; legitimate waits in these kernels last microseconds.
-constexpr uint32_t kWaitPollLimit = 1u << 22;
+constexpr uint32_t kWaitPollLimit = 1u << 20;
 
 // Waits for the phase with the given parity to complete. Returns false when it gave up, either
 // because the poll budget ran out or because another role raised the CTA's abort flag.
