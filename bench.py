@@ -1,0 +1,406 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A step is one pass of the workload over one batch of seeded synthetic input:
+
+  c2_mlp (default)  the Qwen-Image-shaped FP8 MLP: X bf16 [4352,3072]; up W e4m3 [12288,3072] with
+                    per-row scales and GELU-tanh in the epilogue; down W e4m3 [3072,12288] with the
+                    residual X added in the epilogue. Two fl_fp8_linear calls per step.
+  c1_linear         one FP8 linear, X [4096,3072] x W [3072,3072] + bias.
+  c3_nvfp4_qkv      the NVFP4 fused-QKV GEMM, X [4352,3072] x W [9216,3072].
+
+`value` is whole-job TFLOP/s (2*M*N*K per GEMM, nothing else counted) with operands resident in
+HBM; `e2e` is the same metric through the C ABI with the step's activation copied from pinned host
+memory and the result copied back inside the timed region. With N > 1 every rank runs its own
+batch (weights replicated, no collective in the data path): weak scaling.
+
+Prints one JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "quantized GEMM TFLOP/s"
+UNIT = "TFLOP/s"
+
+WORKLOADS = {
+    # name: (m, list of (n, k)), description
+    "c2_mlp": dict(m=4352, gemms=[(12288, 3072), (3072, 12288)], kind="fp8",
+                   desc="FP8 MLP 4352x3072 -> 12288 (GELU-tanh) -> 3072 (+residual)"),
+    "c1_linear": dict(m=4096, gemms=[(3072, 3072)], kind="fp8", desc="FP8 linear 4096x3072x3072 + bias"),
+    "c3_nvfp4_qkv": dict(m=4352, gemms=[(9216, 3072)], kind="nvfp4", desc="NVFP4 fused-QKV 4352x9216x3072"),
+}
+
+NOMINAL_PEAK = {"fp8": 4500.0, "nvfp4": 9000.0}   # dense TFLOP/s, NVIDIA's B200 figures
+PEAK_MULT = {"fp8": 2.0, "nvfp4": 4.0}            # relative to the measured bf16 cuBLAS throughput
+FALLBACK_BF16_TFLOPS = 1590.0
+
+# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch from the committed ncu captures
+# (profiles/), keyed by workload; None until a capture of that workload exists.
+NCU_TRAFFIC_BYTES = {"c2_mlp": None, "c1_linear": None, "c3_nvfp4_qkv": None}
+
+
+def flops_per_step(wl, m=None):
+    m = wl["m"] if m is None else m
+    return sum(2.0 * m * n * k for (n, k) in wl["gemms"])
+
+
+def algorithmic_bytes_per_step(wl):
+    """Each operand once: X (bf16), W (1 B or 0.5+1/16 B), scales, Y (bf16), residual/bias."""
+    m = wl["m"]
+    total = 0.0
+    for (n, k) in wl["gemms"]:
+        wbytes = n * k * (1.0 if wl["kind"] == "fp8" else 0.5 + 1.0 / 16.0)
+        total += m * k * 2 + wbytes + n * 4 + m * n * 2
+    if len(wl["gemms"]) == 2:
+        total += m * wl["gemms"][1][0] * 2  # the residual read
+    return total
+
+
+class ClockSampler(threading.Thread):
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.stop_flag = threading.Event()
+
+    def run(self):
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 7:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self.stop_flag.wait(0.1)
+
+    def summary(self):
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[3 + i].lower().startswith("active") for s in self.samples)]
+        # under load = the upper half of the samples by power draw
+        pw = [float(s[2]) for s in self.samples if s[2].replace(".", "").isdigit()]
+        loaded = sm
+        if pw and len(pw) == len(sm) and len(sm) >= 4:
+            cut = statistics.median(pw)
+            loaded = [c for c, p in zip(sm, pw) if p >= cut] or sm
+        return {"sm_mhz": statistics.median(loaded) if loaded else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d.get("bf16_tflops", FALLBACK_BF16_TFLOPS)), float(d.get("hbm_gbs", 6650.0)), "measured"
+    return FALLBACK_BF16_TFLOPS, 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------
+# the reference arm: the reference's own CPU float32 GEMM over dequantised operands
+# ------------------------------------------------------------------------------------------------
+
+def cpu_reference_step_factory(wl, rows):
+    """Builds a closure that runs one bounded-sample step on the host cores and returns nothing.
+    The product is fl_matmul of the reference's CPU build when it was compiled (kind "reference"),
+    else the C port of the oracle (kind "port")."""
+    import numpy as np
+    from oracle import oracle as O
+    O.lib()
+    kind = "reference" if O.have_ref() else "port"
+    rng = np.random.default_rng(0)
+    x = O.narrow(rng.standard_normal((rows, wl["gemms"][0][1])).astype(np.float32), True)
+    weights = []
+    for (n, k) in wl["gemms"]:
+        w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+        if wl["kind"] == "fp8":
+            codes, scales = O.quantize_fp8_rows(w)
+            weights.append((O.decode_e4m3(codes), scales))
+        else:
+            codes, sf, g = O.quantize_nvfp4_weight(w)
+            weights.append((O.decode_nvfp4(codes, sf), g))
+
+    def step():
+        if wl["kind"] == "fp8":
+            cur = x
+            for i, (wdec, scales) in enumerate(weights):
+                xc, xs = O.quantize_fp8_act(cur, True)
+                acc = O.gemm_f32_nt(O.decode_e4m3(xc), wdec, kind)
+                last = i == len(weights) - 1
+                act = O.ACT_GELU_TANH if (len(weights) == 2 and i == 0) else O.ACT_NONE
+                res = x if (len(weights) == 2 and last) else None
+                cur = O.epilogue(acc, xs, scales, 1.0, None, res, act, True)
+        else:
+            (wdec, g), = weights
+            xc, xsf = O.quantize_nvfp4_act(x, True)
+            acc = O.gemm_f32_nt(O.decode_nvfp4(xc, xsf), wdec, kind)
+            O.epilogue(acc, None, None, float(g[0]), None, None, O.ACT_NONE, True)
+
+    cores = os.cpu_count() or 1
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except Exception:
+        pass
+    return step, kind, cores
+
+
+def run_reference(args, wl):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = min(wl["m"], args.reference_rows)
+    step, kind, cores = cpu_reference_step_factory(wl, rows)
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    ms = dt * 1e3 / args.steps
+    value = flops_per_step(wl, rows) / (ms * 1e-3) / 1e12
+    sample = f"{rows} of {wl['m']} rows per step, whole step on the host (quantise, fp32 GEMM, epilogue)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "what": wl["desc"], "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+
+def run_ours(args, wl):
+    import torch
+    from libwaifu_b200 import flint as F
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    F.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if not F.fp8_available():
+        raise RuntimeError("the CUDA path is unavailable on this device; there is no fallback")
+
+    bf = F.DType.BFLOAT16
+    m = wl["m"]
+    sets = args.rotate
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+
+    def wrap(t, dt, shape=None):
+        return F.Tensor.from_device_ptr(t.data_ptr(), tuple(shape or t.shape), dt, keepalive=t)
+
+    # operand sets that rotate so that no operand survives in L2 from one step to the next
+    operand_sets = []
+    for _ in range(sets):
+        x = torch.randn(m, wl["gemms"][0][1], device="cuda", dtype=torch.bfloat16, generator=gen)
+        layers = []
+        for (n, k) in wl["gemms"]:
+            w = torch.randn(n, k, device="cuda", dtype=torch.float32, generator=gen) * 0.02
+            if wl["kind"] == "fp8":
+                codes, scales = F.quantize_fp8_rows(wrap(w, F.DType.FLOAT))
+                layers.append((codes, scales))
+            else:
+                codes, sf, g = F.quantize_nvfp4(wrap(w, F.DType.FLOAT))
+                layers.append((codes, sf, g))
+            F.synchronize()
+            del w
+        bias = None
+        if args.workload == "c1_linear":
+            b = torch.randn(wl["gemms"][0][0], device="cuda", dtype=torch.bfloat16, generator=gen) * 0.01
+            bias = wrap(b, bf)
+        operand_sets.append((wrap(x, bf), layers, bias))
+    outs = [F.Tensor.empty((m, n), bf) for (n, _) in wl["gemms"]]
+
+    def step(i, x_override=None):
+        x, layers, bias = operand_sets[i % sets]
+        if x_override is not None:
+            x = x_override
+        if wl["kind"] == "nvfp4":
+            codes, sf, g = layers[0]
+            F.nvfp4_linear(x, codes, sf, g, None, None, F.ACT_NONE, outs[0])
+        elif len(layers) == 2:
+            F.fp8_linear(x, layers[0][0], layers[0][1], None, None, F.ACT_GELU_TANH, outs[0])
+            F.fp8_linear(outs[0], layers[1][0], layers[1][1], None, x, F.ACT_NONE, outs[1])
+        else:
+            F.fp8_linear(x, layers[0][0], layers[0][1], bias, None, F.ACT_NONE, outs[0])
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing ----------------------------------------------------------------
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = F.launch_count()
+    F.gemm_timing(True)
+    F.gemm_timing_read()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    gemm_ms, gemm_launches = F.gemm_timing_read()
+    F.gemm_timing(False)
+    launches = F.launch_count() - launches0
+    sampler.stop_flag.set()
+    sampler.join(timeout=5)
+    F.synchronize()
+    ms_step = max_over_ranks(ms_total / args.steps)
+    value = world * flops_per_step(wl) / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end through the C ABI with host buffers ----------------------------------------
+    k0 = wl["gemms"][0][1]
+    n_last = wl["gemms"][-1][0]
+    host_x = F.Tensor.empty((m, k0), bf, F.Device.CUDA_HOST)
+    host_y = F.Tensor.empty((m, n_last), bf, F.Device.CUDA_HOST)
+    dev_x = F.Tensor.empty((m, k0), bf)
+    import ctypes
+    import numpy as np
+    p = ctypes.c_void_p()
+    F.check(F.lib().fl_tensor_data_get_host_ptr(host_x._data, ctypes.byref(p)))
+    hx = np.ctypeslib.as_array(ctypes.cast(p.value, ctypes.POINTER(ctypes.c_uint16)), shape=(m * k0,))
+    hx[:] = (np.random.default_rng(7 + rank).standard_normal(m * k0).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    ops = F.operators()
+
+    def e2e_step(i):
+        F.check(F.lib().fl_transfer(ops, host_x.raw(), dev_x.raw()))
+        step(i, x_override=dev_x)
+        F.check(F.lib().fl_transfer(ops, outs[-1].raw(), host_y.raw()))  # synchronises
+
+    e2e_steps = max(3, min(args.steps, 20))
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    e0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
+    e2e_value = world * flops_per_step(wl) / (e2e_ms * 1e-3) / 1e12
+
+    # ---- roofline of the dominant kernel (the tcgen05 GEMM), from its own events ---------------
+    bf16_peak, hbm_peak, peak_kind = measured_peaks()
+    peak = PEAK_MULT[wl["kind"]] * bf16_peak
+    gemm_tflops = flops_per_step(wl) * args.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+    traffic = NCU_TRAFFIC_BYTES.get(args.workload)
+    roofline = {
+        "bound": "tensor", "kernel": "gemm_tn_kernel", "achieved": gemm_tflops, "peak": peak, "unit": UNIT,
+        "frac": (gemm_tflops / peak) if gemm_tflops else None,
+        "peak_source": f"{PEAK_MULT[wl['kind']]:.0f} x bf16 cuBLAS burst, of {peak_kind}",
+        "frac_of_nominal": (gemm_tflops / NOMINAL_PEAK[wl["kind"]]) if gemm_tflops else None,
+        "nominal_peak": NOMINAL_PEAK[wl["kind"]],
+        "launches": gemm_launches, "avg_launch_ms": gemm_ms / gemm_launches if gemm_launches else None,
+        "traffic": traffic, "algorithmic_bytes_per_step": algorithmic_bytes_per_step(wl),
+    }
+
+    # ---- CPU baseline on a bounded sample (rank 0, N = 1 only) ---------------------------------
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        rows = min(m, args.reference_rows)
+        cstep, kind, cores = cpu_reference_step_factory(wl, rows)
+        cstep()
+        best = None
+        for _ in range(3):
+            t0 = time.perf_counter()
+            cstep()
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        cpu_baseline = {"value": flops_per_step(wl, rows) / best / 1e12, "unit": UNIT, "cores": cores, "kind": kind,
+                        "sample": f"{rows} of {m} rows, whole step on the host, best of 3"}
+
+    if rank == 0:
+        touched = sets * (m * k0 * 2 + sum(n * k * (1 if wl["kind"] == "fp8" else 0.5625) for (n, k) in wl["gemms"]))
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "e4m3" if wl["kind"] == "fp8" else "e2m1", "data": "synthetic",
+            "config": {"workload": args.workload, "what": wl["desc"], "m_per_gpu": m,
+                       "parallelism": f"batch-sharded x{world}, weights replicated, no collective",
+                       "l2": f"{sets} rotating operand sets ({touched / 1e6:.0f} MB of inputs) > 126 MB L2",
+                       "accumulate": "fp32", "out": "bf16"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": m * k0 * 2,
+                    "d2h_bytes_per_step": m * n_last * 2, "steps": e2e_steps},
+            "gpu_launches": launches,
+            "clocks": sampler.summary(),
+            "roofline": roofline,
+            "cpu_baseline": cpu_baseline,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2_mlp", choices=sorted(WORKLOADS))
+    ap.add_argument("--rotate", type=int, default=3, help="operand sets rotated through to defeat L2 reuse")
+    ap.add_argument("--rows", type=int, default=None, help="override the workload's row count (for small profile captures)")
+    ap.add_argument("--reference-rows", type=int, default=1088, help="rows of the bounded CPU sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl = dict(WORKLOADS[args.workload])
+    if args.rows:
+        wl["m"] = args.rows
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args, wl)
+    else:
+        run_ours(args, wl)
+
+
+if __name__ == "__main__":
+    main()

@@ -174,6 +174,11 @@ FLAPI int32_t fl_sm100_set_device(int32_t ordinal);
 /* Waits for the default stream, then reports the kernels' status word: 0, or the code of the
  * bounded wait that gave up inside a kernel (the call then also returns FL_ERROR_ABORTED). */
 FLAPI int32_t fl_sm100_synchronize(int32_t *kernel_status);
+/* Per-launch timing of the GEMM kernel alone: while enabled, every GEMM launch is bracketed by
+ * CUDA events on its stream; fl_sm100_gemm_timing_read() waits for the stream, returns the summed
+ * kernel time and the number of launches since the last read, and clears them. For benchmarks. */
+FLAPI int32_t fl_sm100_gemm_timing(int32_t enable);
+FLAPI int32_t fl_sm100_gemm_timing_read(double *total_ms, int64_t *launches);
 /* How many kernels of this library the calling process has launched so far. */
 FLAPI int64_t fl_sm100_launch_count(void);
 

@@ -17,7 +17,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
-    "-cudart", "static",
+    "-cudart", "static", "-Wno-deprecated-gpu-targets",
 ]
 
 
@@ -51,7 +51,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             cmd.insert(2, "-v")
         subprocess.run(cmd, check=True)
         objs.append(obj)
-    subprocess.run([nvcc, "-shared", "-cudart", "static", "-o", LIB_PATH, *objs, "-lpthread", "-ldl", "-lrt"], check=True)
+    subprocess.run([nvcc, "-shared", "-cudart", "static", "-Wno-deprecated-gpu-targets", "-o", LIB_PATH, *objs, "-lpthread", "-ldl", "-lrt"], check=True)
     return LIB_PATH
 
 

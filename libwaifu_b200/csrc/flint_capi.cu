@@ -136,6 +136,15 @@ std::mutex g_mutex;
 DeviceState g_dev;
 std::atomic<int64_t> g_gemm_launches{0};
 
+// Optional per-launch timing of the GEMM kernel alone (events on the launching stream), so a
+// benchmark can separate it from the quantisation kernels launched by the same entry point.
+struct GemmTiming {
+  bool enabled = false;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> used;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> spare;
+};
+GemmTiming g_timing;
+
 void probe_locked() {
   if (g_dev.probed) return;
   g_dev.probed = true;
@@ -438,7 +447,22 @@ void run_gemm(GemmKind kind, int m, int n, int k, const void *a, const void *b, 
   g.status = status_word();
   g.stream = 0;
   const char *why = "";
+  std::pair<cudaEvent_t, cudaEvent_t> ev{nullptr, nullptr};
+  if (g_timing.enabled) {
+    if (!g_timing.spare.empty()) {
+      ev = g_timing.spare.back();
+      g_timing.spare.pop_back();
+    } else {
+      cuda_check(cudaEventCreate(&ev.first), "cudaEventCreate");
+      cuda_check(cudaEventCreate(&ev.second), "cudaEventCreate");
+    }
+    cuda_check(cudaEventRecord(ev.first, g.stream), "cudaEventRecord");
+  }
   cudaError_t e = launch_gemm(g, &why);
+  if (ev.first) {
+    cudaEventRecord(ev.second, g.stream);
+    g_timing.used.push_back(ev);
+  }
   if (e != cudaSuccess) aborted(std::string("GEMM launch: ") + why + " (" + cudaGetErrorString(e) + ")");
   ++g_gemm_launches;
 }
@@ -1026,6 +1050,31 @@ int32_t fl_sm100_synchronize(int32_t *kernel_status) {
     }
     if (kernel_status) *kernel_status = static_cast<int32_t>(code);
     if (code != 0) aborted("a kernel gave up on a bounded wait (status " + std::to_string(code) + ")");
+    return clear_error();
+  });
+}
+
+int32_t fl_sm100_gemm_timing(int32_t enable) {
+  return guard([&]() {
+    g_timing.enabled = enable != 0;
+    return clear_error();
+  });
+}
+
+int32_t fl_sm100_gemm_timing_read(double *total_ms, int64_t *launches) {
+  return guard([&]() {
+    if (!total_ms || !launches) invalid("out is null");
+    cuda_check(cudaStreamSynchronize(0), "cudaStreamSynchronize");
+    double sum = 0.0;
+    for (auto &ev : g_timing.used) {
+      float ms = 0.0f;
+      cuda_check(cudaEventElapsedTime(&ms, ev.first, ev.second), "cudaEventElapsedTime");
+      sum += ms;
+      g_timing.spare.push_back(ev);
+    }
+    *launches = static_cast<int64_t>(g_timing.used.size());
+    *total_ms = sum;
+    g_timing.used.clear();
     return clear_error();
   });
 }

@@ -105,6 +105,9 @@ def lib() -> ctypes.CDLL:
     L.fl_sm100_set_device.argtypes = [c_int32]
     L.fl_sm100_synchronize.argtypes = [POINTER(c_int32)]
     L.fl_sm100_launch_count.restype = c_int64
+    L.fl_sm100_gemm_timing.argtypes = [c_int32]; L.fl_sm100_gemm_timing.restype = c_int32
+    L.fl_sm100_gemm_timing_read.argtypes = [POINTER(ctypes.c_double), POINTER(c_int64)]
+    L.fl_sm100_gemm_timing_read.restype = c_int32
     for name in ("fl_is_device_available", "fl_operators_create", "fl_operators_get_device", "fl_tensor_data_create",
                  "fl_tensor_data_borrow", "fl_tensor_data_borrow_device", "fl_tensor_data_get_host_ptr",
                  "fl_tensor_view_create", "fl_transfer", "fl_fp8_available", "fl_nvfp4_available", "fl_fp8_matmul",
@@ -133,6 +136,18 @@ def set_device(ordinal: int) -> None:
 def synchronize() -> None:
     status = c_int32(0)
     check(lib().fl_sm100_synchronize(byref(status)))
+
+
+def gemm_timing(enable: bool) -> None:
+    check(lib().fl_sm100_gemm_timing(1 if enable else 0))
+
+
+def gemm_timing_read():
+    """(summed GEMM-kernel milliseconds, launches) since the last read; waits for the stream."""
+    ms = ctypes.c_double(0.0)
+    n = c_int64(0)
+    check(lib().fl_sm100_gemm_timing_read(byref(ms), byref(n)))
+    return ms.value, n.value
 
 
 def launch_count() -> int:

@@ -190,6 +190,12 @@ class _Ref:
         L.fl_tensor_view_create.argtypes = [c_void_p, POINTER(c_int32), POINTER(c_int32), c_int32, c_int64, POINTER(c_void_p)]
         L.fl_tensor_view_destroy.argtypes = [c_void_p]; L.fl_tensor_view_destroy.restype = None
         L.fl_matmul.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p]
+        try:
+            L.fl_set_log_level.argtypes = [c_int32]
+            L.fl_set_log_level.restype = None
+            L.fl_set_log_level(3)  # errors only (flint/capi.h:672-690)
+        except AttributeError:
+            pass
         L.fl_init()
         self.ops = c_void_p()
         self._check(L.fl_operators_create(0, ctypes.byref(self.ops)))

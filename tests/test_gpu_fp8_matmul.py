@@ -145,8 +145,8 @@ def test_in_place_residual(flint):
     a = np.zeros((m, k), np.float32)
     a[:, 0] = a[:, 1] = 1.0
     res = dev(F, f16(np.ones((m, n))), F.DType.FLOAT16)
-    F.check(F.lib().fl_fp8_matmul_add(dev(F, f16(a), F.DType.FLOAT16).raw(), dev(F, codes, F.DType.FP8E4M3).raw(),
-                                      dev(F, np.array([8.0], np.float32), F.DType.FLOAT).raw(), res.raw(), res.raw()))
+    ad, wd, sd = dev(F, f16(a), F.DType.FLOAT16), dev(F, codes, F.DType.FP8E4M3), dev(F, np.array([8.0], np.float32), F.DType.FLOAT)
+    F.check(F.lib().fl_fp8_matmul_add(ad.raw(), wd.raw(), sd.raw(), res.raw(), res.raw()))
     assert np.all(from_f16(res.numpy()) == 2050.0)
 
 
@@ -195,8 +195,8 @@ def test_misaligned_view_offset(flint, oracle):
     out_buf = F.Tensor.empty((m * n + pad,), F.DType.FLOAT16)
     a_view = a_buf.view_as((m, k), (k, 1), pad)
     out_view = out_buf.view_as((m, n), (n, 1), pad)
-    F.check(F.lib().fl_fp8_matmul(a_view.raw(), dev(F, codes, F.DType.FP8E4M3).raw(),
-                                  dev(F, np.array([K_SCALE], np.float32), F.DType.FLOAT).raw(), out_view.raw()))
+    wd, sd = dev(F, codes, F.DType.FP8E4M3), dev(F, np.array([K_SCALE], np.float32), F.DType.FLOAT)
+    F.check(F.lib().fl_fp8_matmul(a_view.raw(), wd.raw(), sd.raw(), out_view.raw()))
     got = out_buf.numpy()[pad:].reshape(m, n)
     check_parity(oracle, got, oracle.fp8_matmul(a, codes, [K_SCALE]), False, what="offset view")
 
