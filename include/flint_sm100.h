@@ -142,6 +142,39 @@ typedef enum fl_activation_t {
 FLAPI int32_t fl_fp8_linear(fl_tensor_view_t a, fl_tensor_view_t data, fl_tensor_view_t scales, fl_tensor_view_t bias,
                             fl_tensor_view_t residual, int32_t act, fl_tensor_view_t out);
 
+/* fl_fp8_linear() for callers that must not allocate. It has no counterpart in the reference.
+ *
+ * Who needs it: a host that runs with every byte of the card already budgeted -- flint's own
+ * callers keep weights resident up to a memory limit and evict one when an allocation fails
+ * (waifu/src/flint/ir.rs:489-503), so a library that quietly grows a scratch arena behind them can
+ * fail or push a weight out -- and a host that cannot afford the device-wide stall a cudaMalloc or
+ * cudaFree brings in the middle of a pass. fl_fp8_linear() may grow its arena on any call whose
+ * m * k is larger than every earlier one; this entry point never does.
+ *
+ * How: the quantised activation (m * k bytes), its m row scales and the kernels' status word live
+ * in one fixed device array compiled into the library, about 16.3 MiB, which every GPU that loads
+ * the library holds until the process ends. The call makes no cudaMalloc, cudaFree, cudaHostAlloc
+ * or other allocating call. Arguments, checks, arithmetic and results are fl_fp8_linear()'s.
+ *
+ * Limits, refused with FL_ERROR_INVALID_ARG before anything is launched: at most 65536 activation
+ * rows (the product of a's leading dimensions), at most 16 Mi elements in m * k (4352 x 3072 fits),
+ * and a weight whose first element is 16-byte aligned (the ordinary entry point would stage it).
+ *
+ * Sharing: every call on a device uses the same array and finds the last call's bytes in it. The
+ * call clears the status word itself and overwrites all codes and scales it reads, so nothing has
+ * to be cleared by the caller; but two calls that overlap on the GPU (from two threads, or if this
+ * library is ever driven on more than its one stream) race on it and must be serialised by the
+ * caller. To report a kernel that gave up on a wait, each call first reads the previous call's
+ * status word back, which waits for that call's kernels: consecutive calls do not overlap their
+ * launches the way fl_fp8_linear() calls do.
+ *
+ * First call: on each device, the first call looks the array's device address up (once, with that
+ * device current) and, like any first launch, loads the kernels. Make that first call before
+ * beginning any stream capture on that device. */
+FLAPI int32_t fl_fp8_linear_static(fl_tensor_view_t a, fl_tensor_view_t data, fl_tensor_view_t scales,
+                                   fl_tensor_view_t bias, fl_tensor_view_t residual, int32_t act,
+                                   fl_tensor_view_t out);
+
 /* 1 where fl_nvfp4_linear can run (the same cards as fl_fp8_available). */
 FLAPI int32_t fl_nvfp4_available(fl_device_type_t device, int32_t *out);
 

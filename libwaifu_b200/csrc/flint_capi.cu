@@ -1081,4 +1081,154 @@ int32_t fl_sm100_gemm_timing_read(double *total_ms, int64_t *launches) {
 
 int64_t fl_sm100_launch_count(void) { return g_gemm_launches.load() + helper_launch_count(); }
 
+
+}  // extern "C"
+
+// ============================ fl_fp8_linear_static ============================================
+//
+// fl_fp8_linear for callers that must not allocate. Its activation scratch (the e4m3 codes, the
+// per-row scales and the kernels' status word) is the file-scope device array below instead of the
+// library's growable arena, so the call makes no cudaMalloc / cudaFree / cudaHostAlloc and none of
+// the device-wide synchronisation those imply. Every GPU whose context loads this library holds
+// the array (about 16.3 MiB) until the process exits.
+
+namespace {
+
+constexpr size_t kStaticStatusBytes = 256;                 // status word, padded
+constexpr size_t kStaticMaxRows = 65536;                   // rows of the activation (m)
+constexpr size_t kStaticMaxCodes = size_t(16) << 20;       // m * k, one byte per element
+constexpr size_t kStaticScalesOffset = kStaticStatusBytes;
+constexpr size_t kStaticCodesOffset = kStaticScalesOffset + kStaticMaxRows * sizeof(float);
+constexpr size_t kStaticBytes = kStaticCodesOffset + kStaticMaxCodes;
+
+// In host code this name is only a handle for cudaGetSymbolAddress(); it is not a device address
+// and must never be handed to a kernel as one.
+static __device__ __align__(256) uint8_t g_static_scratch[kStaticBytes];
+
+constexpr int kStaticMaxDevices = 64;
+uint8_t *g_static_base[kStaticMaxDevices] = {};
+std::mutex g_static_mutex;
+
+// The array's device address on the current device, looked up once per device with that device
+// current. No allocation: the array was placed when the module was loaded.
+uint8_t *static_scratch_base() {
+  int dev = 0;
+  cuda_check(cudaGetDevice(&dev), "cudaGetDevice");
+  if (dev < 0 || dev >= kStaticMaxDevices) aborted("device ordinal beyond the static scratch table");
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_base[dev]) {
+    void *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || !ptr) {
+      aborted(std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e));
+    }
+    g_static_base[dev] = static_cast<uint8_t *>(ptr);
+  }
+  return g_static_base[dev];
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t fl_fp8_linear_static(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_view_t scales_h,
+                             fl_tensor_view_t bias_h, fl_tensor_view_t residual_h, int32_t act,
+                             fl_tensor_view_t out_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &weight = deref(data_h);
+    const fl_tensor_view_impl_t &scales = deref(scales_h);
+    check_fp8_weight(weight, scales, /*per_channel_ok=*/true);
+    const fl_device_type_t device = device_of(weight);
+    const int rows = weight.shape[0];
+    const int k = weight.shape[1];
+    const fl_tensor_view_impl_t &a = deref(a_h);
+    check_activation(a, device, "the left operand");
+    if (a.shape.back() != k) invalid("the two operands disagree about k");
+    const fl_tensor_view_impl_t &out = deref(out_h);
+    check_result(out, a, rows, device);
+    if (act != FL_ACT_NONE && act != FL_ACT_GELU_TANH) invalid("unknown activation");
+    const fl_tensor_view_impl_t *bias = bias_h ? &deref(bias_h) : nullptr;
+    const fl_tensor_view_impl_t *residual = residual_h ? &deref(residual_h) : nullptr;
+    if (bias) {
+      if (device_of(*bias) != device || dtype_of(*bias) != dtype_of(out) || numel_of(*bias) != rows ||
+          !is_contiguous(*bias)) {
+        invalid("the bias is not a contiguous (rows) vector of out's type on the weight's device");
+      }
+    }
+    if (residual) {
+      if (device_of(*residual) != device || dtype_of(*residual) != dtype_of(out) || !is_contiguous(*residual)) {
+        invalid("the residual is not contiguous, of out's type, on the weight's device");
+      }
+      check_shape(*residual, out.shape, "the residual");
+    }
+    if (device != FL_DEVICE_CUDA) invalid("the fp8 operand is on a device with no FP8 kernels");
+    check_tiles(rows, k, 16);
+    require_kernels();
+
+    const int64_t m64 = leading_rows(a);
+    if (m64 == 0) return clear_error();
+    // The limits of the fixed scratch, refused before anything is launched.
+    if (m64 > static_cast<int64_t>(kStaticMaxRows)) {
+      invalid("fl_fp8_linear_static: " + std::to_string(m64) + " activation rows exceed the static scratch's " +
+              std::to_string(kStaticMaxRows) + "; use fl_fp8_linear");
+    }
+    if (m64 * k > static_cast<int64_t>(kStaticMaxCodes)) {
+      invalid("fl_fp8_linear_static: m * k = " + std::to_string(m64 * k) + " exceeds the static scratch's " +
+              std::to_string(kStaticMaxCodes) + " elements; use fl_fp8_linear");
+    }
+    // The ordinary entry point stages a misaligned weight through its arena; there is no room
+    // set aside for that here.
+    if (!aligned16(raw_ptr(weight))) {
+      invalid("fl_fp8_linear_static: the weight's first element is not 16-byte aligned; use fl_fp8_linear");
+    }
+    const int m = static_cast<int>(m64);
+    const int is_bf16 = dtype_of(a) == FL_DTYPE_BFLOAT16;
+
+    uint8_t *base = static_scratch_base();
+    uint32_t *status = reinterpret_cast<uint32_t *>(base);
+    float *row_scales = reinterpret_cast<float *>(base + kStaticScalesOffset);
+    uint8_t *codes = base + kStaticCodesOffset;
+
+    // The array keeps whatever the last call left in it. The previous call's status word is read
+    // back first (a 4-byte copy that waits for the stream), then cleared for this call; codes and
+    // scales are fully overwritten by the quantiser for the m x k in use, so need no clearing.
+    uint32_t previous = 0;
+    cuda_check(cudaMemcpy(&previous, status, sizeof(previous), cudaMemcpyDeviceToHost), "reading the static status word");
+    cuda_check(cudaMemsetAsync(status, 0, sizeof(uint32_t), 0), "clearing the static status word");
+    if (previous != 0) {
+      aborted("the previous fl_fp8_linear_static call's kernel gave up on a bounded wait (status " +
+              std::to_string(previous) + ")");
+    }
+
+    cuda_check(quantize_fp8_act(raw_ptr(a), is_bf16, m, k, codes, row_scales, 0), "quantising the activation");
+
+    GemmArgs g{};
+    g.kind = kGemmE4M3;
+    g.m = m;
+    g.n = rows;
+    g.k = k;
+    g.a = codes;
+    g.b = raw_ptr(weight);
+    g.row_scale = row_scales;
+    g.col_scale = reinterpret_cast<const float *>(raw_ptr(scales));
+    g.col_scale_scalar = numel_of(scales) == 1 ? 1 : 0;
+    g.bias = bias ? raw_ptr(*bias) : nullptr;
+    if (residual) {
+      g.residual = raw_ptr(*residual);
+      g.residual_rows = m;
+      g.residual_ld = rows;
+    }
+    g.act = act;
+    g.out_bf16 = is_bf16;
+    g.out = raw_ptr(out);
+    g.status = status;
+    g.stream = 0;
+    const char *why = "";
+    cudaError_t e = launch_gemm(g, &why);
+    if (e != cudaSuccess) aborted(std::string("GEMM launch: ") + why + " (" + cudaGetErrorString(e) + ")");
+    ++g_gemm_launches;
+    return clear_error();
+  });
+}
+
 }  // extern "C"

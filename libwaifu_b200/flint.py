@@ -99,6 +99,8 @@ def lib() -> ctypes.CDLL:
     L.fl_fp8_matmul_add.argtypes = [V, V, V, V, V]
     L.fl_fp8_linear.argtypes = [V, V, V, V, V, c_int32, V]
     L.fl_nvfp4_linear.argtypes = [V, V, V, V, V, V, c_int32, V]
+    L.fl_fp8_linear_static.argtypes = [V, V, V, V, V, c_int32, V]
+    L.fl_fp8_linear_static.restype = c_int32
     L.fl_quantize_fp8_rows.argtypes = [V, V, V]
     L.fl_quantize_fp8_activation.argtypes = [V, V, V]
     L.fl_quantize_nvfp4.argtypes = [V, V, V, V]
@@ -365,6 +367,20 @@ def fp8_linear(a: Tensor, weight: Tensor, scales: Tensor, bias: Optional[Tensor]
         out = _fp8_result(a, weight.shape[0])
     check(lib().fl_fp8_linear(a.raw(), weight.raw(), scales.raw(), bias.raw() if bias else None,
                               residual.raw() if residual else None, int(act), out.raw()))
+    return out
+
+
+def fp8_linear_static(a: Tensor, weight: Tensor, scales: Tensor, bias: Optional[Tensor] = None,
+                      residual: Optional[Tensor] = None, act: int = ACT_NONE, out: Optional[Tensor] = None) -> Tensor:
+    """fp8_linear through the entry point that allocates nothing: its activation scratch is a fixed
+    16.3 MiB device array inside the library (at most 65536 rows and 16 Mi elements of m * k).
+    For hosts that run with the whole card budgeted or cannot take an allocation's device-wide
+    stall mid-pass. `out` should be passed by such a host; when it is None it is allocated here,
+    by this wrapper, which is a convenience of the wrapper and not of the entry point."""
+    if out is None:
+        out = _fp8_result(a, weight.shape[0])
+    check(lib().fl_fp8_linear_static(a.raw(), weight.raw(), scales.raw(), bias.raw() if bias else None,
+                                     residual.raw() if residual else None, int(act), out.raw()))
     return out
 
 
