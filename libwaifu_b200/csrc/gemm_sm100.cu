@@ -56,6 +56,7 @@ struct KernelParams {
   int act;
   int out_bf16;
   void *out;
+  int tma_store;  // the output's base is 16-byte aligned, so tiles leave through TMA stores
   uint32_t *status;
 };
 
@@ -69,10 +70,18 @@ struct Config {
   static constexpr int kSfaBytes = NVF4 ? kMmasPerStage * kSfTileBytes : 0;
   static constexpr int kSfbBytes = NVF4 ? kSfbGroups * kMmasPerStage * kSfTileBytes : 0;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kSmemBudget = 227 * 1024 - 2048;
+  // Epilogue staging: per epilogue warp two 32-row x 64-byte output slabs (64-byte swizzle) for
+  // the TMA stores, then each warp's own copy of the tile's per-column scale and bias as fp32
+  // (a private copy needs no barrier between warps, so no wait in the epilogue is unbounded).
+  static constexpr int kOutSlabBytes = 32 * 64;
+  static constexpr int kOutStageBytes = kEpilogueWarps * 2 * kOutSlabBytes;
+  static constexpr int kColParamBytes = kEpilogueWarps * 2 * BLOCK_N * 4;
+  static constexpr int kSmemBudget = 227 * 1024 - 2048 - kOutStageBytes - kColParamBytes;
   static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + slack to align to 1024
+  static constexpr int kOutStageOffset = kStages * kStageBytes;
+  static constexpr int kColParamOffset = kOutStageOffset + kOutStageBytes;
+  static constexpr int kSmemBytes = kColParamOffset + kColParamBytes + 1024;  // + slack to align to 1024
   // Tensor memory columns: two accumulators, then the scale factors of one stage.
   static constexpr int kAccCols = 2 * BLOCK_N;
   static constexpr int kSfaCols = NVF4 ? kMmasPerStage * 4 : 0;
@@ -111,7 +120,7 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi, int is_bf16) {
 template <int KIND, int BLOCK_N>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const KernelParams p) {
+               const __grid_constant__ CUtensorMap tmap_out, const KernelParams p) {
   constexpr bool NVF4 = (KIND == kKindNvf4);
   using Cfg = Config<BLOCK_N, NVF4>;
   constexpr int STAGES = Cfg::kStages;
@@ -280,17 +289,43 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // ------------------------------------------------------------------ epilogue
     bool ok = true;
     int local = 0;
+    uint32_t stores = 0;  // TMA stores this warp has issued, for the two-slab rotation
     const int is_bf16 = p.out_bf16;
-    const float gscale = p.global_scale ? __ldg(p.global_scale) : 1.0f;
+    const bool has_cs_vec = p.col_scale != nullptr && !p.col_scale_scalar;
+    const bool has_bias = p.bias != nullptr;
+    const bool has_res = p.residual != nullptr;
+    const bool has_gs = p.global_scale != nullptr;
+    const float gscale = has_gs ? __ldg(p.global_scale) : 1.0f;
     const float cs_scalar = (p.col_scale && p.col_scale_scalar) ? __ldg(p.col_scale) : 1.0f;
-    const bool out_vec_ok = (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+    const bool use_tma_store = p.tma_store != 0;
+    const bool res_vec_ok = has_res && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0 && (p.residual_ld % 8) == 0;
+    float *col_params = reinterpret_cast<float *>(smem + Cfg::kColParamOffset);
+    const uint32_t out_stage = smem_u32(smem + Cfg::kOutStageOffset + warp * 2 * Cfg::kOutSlabBytes);
+    if (warp == 0 && lane == 0 && use_tma_store) tma_prefetch_desc(&tmap_out);
+
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       const int tm = tile % p.tiles_m;
       const int tn = tile / p.tiles_m;
-      const int row = tm * kBlockM + warp * 32 + lane;
+      const int row0 = tm * kBlockM + warp * 32;
+      const int row = row0 + lane;
       const int n0 = tn * BLOCK_N;
+
+      // This tile's per-column scale and bias, widened to fp32 once, in this warp's own slice of
+      // shared memory.
+      float *cs_t = col_params + warp * 2 * BLOCK_N;
+      float *bias_t = cs_t + BLOCK_N;
+      if (has_cs_vec || has_bias) {
+        __syncwarp();  // the previous tile's reads are done
+        for (int i = lane; i < BLOCK_N; i += 32) {
+          const int n = n0 + i;
+          cs_t[i] = (has_cs_vec && n < p.n) ? __ldg(p.col_scale + n) : 1.0f;
+          bias_t[i] = (has_bias && n < p.n) ? load16(p.bias, n, is_bf16) : 0.0f;
+        }
+        __syncwarp();
+      }
+
       if (!mbar_wait(&acc_full_bar[acc], acc_phase, &abort_flag)) {
         ok = false;
         break;
@@ -298,59 +333,130 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       tc_fence_after_sync();
       const bool row_ok = row < p.m;
       const float rs = (p.row_scale && row_ok) ? __ldg(p.row_scale + row) : 1.0f;
+      const float rs_cs = rs * cs_scalar;
       const long long res_row =
-          (p.residual && row_ok) ? static_cast<long long>(row % p.residual_rows) * p.residual_ld : 0;
+          (has_res && row_ok) ? static_cast<long long>(row % p.residual_rows) * p.residual_ld : 0;
       uint16_t *out_row = reinterpret_cast<uint16_t *>(p.out) + static_cast<long long>(row) * p.n;
-#pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
+      const int chunks = min(BLOCK_N / 32, (p.n - n0 + 31) / 32);  // chunks holding a valid column
+      const uint32_t tacc = tmem_base + ((warp * 32) << 16) + acc * BLOCK_N;
+
+      // One 32-column chunk: scale, bias, activation, residual in fp32; one rounding; store.
+      auto finish_chunk = [&](int c, uint32_t (&v)[32]) {
         const int nc = n0 + c * 32;
-        if (nc >= p.n) break;  // warp-uniform
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + ((warp * 32) << 16) + acc * BLOCK_N + c * 32, v);
-        tmem_ld_wait();
-        uint32_t packed[16];
+        float x[32];
+        if (has_cs_vec) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float x[2];
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int n = nc + j + h;
-            float val = __uint_as_float(v[j + h]);
-            if (n < p.n) {
-              float cs = p.col_scale ? (p.col_scale_scalar ? cs_scalar : __ldg(p.col_scale + n)) : 1.0f;
-              val = val * (rs * cs);
-              if (p.global_scale) val *= gscale;
-              if (p.bias) val += load16(p.bias, n, is_bf16);
-              if (p.act == kActGeluTanh) val = gelu_tanh(val);
-              if (p.residual && row_ok) val += load16(p.residual, res_row + n, is_bf16);
-            }
-            x[h] = val;
+          for (int j = 0; j < 32; j += 4) {
+            const float4 s4 = *reinterpret_cast<const float4 *>(cs_t + c * 32 + j);
+            x[j] = __uint_as_float(v[j]) * (rs * s4.x);
+            x[j + 1] = __uint_as_float(v[j + 1]) * (rs * s4.y);
+            x[j + 2] = __uint_as_float(v[j + 2]) * (rs * s4.z);
+            x[j + 3] = __uint_as_float(v[j + 3]) * (rs * s4.w);
           }
-          packed[j >> 1] = pack16(x[0], x[1], is_bf16);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]) * rs_cs;
         }
-        if (row_ok) {
-          if (out_vec_ok) {
+        if (has_gs) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] *= gscale;
+        }
+        if (has_bias) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const float4 b4 = *reinterpret_cast<const float4 *>(bias_t + c * 32 + j);
+            x[j] += b4.x;
+            x[j + 1] += b4.y;
+            x[j + 2] += b4.z;
+            x[j + 3] += b4.w;
+          }
+        }
+        if (p.act == kActGeluTanh) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) x[j] = gelu_tanh(x[j]);
+        }
+        if (has_res && row_ok) {
+          if (res_vec_ok) {
+            const uint4 *rp = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.residual) + res_row + nc);
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
-              if (nc + g * 8 < p.n) {  // n is a multiple of 8, so a group is whole or absent
-                uint4 q = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
-                *reinterpret_cast<uint4 *>(out_row + nc + g * 8) = q;
+              if (nc + g * 8 < p.n) {  // n is a multiple of 8: a group of 8 is whole or absent
+                const uint4 q = rp[g];
+                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                  if (is_bf16) {
+                    x[g * 8 + 2 * h] += __uint_as_float(w[h] << 16);
+                    x[g * 8 + 2 * h + 1] += __uint_as_float(w[h] & 0xffff0000u);
+                  } else {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[h]));
+                    x[g * 8 + 2 * h] += f.x;
+                    x[g * 8 + 2 * h + 1] += f.y;
+                  }
+                }
               }
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              if (nc + j < p.n) {
-                out_row[nc + j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffff));
-              }
+              if (nc + j < p.n) x[j] += load16(p.residual, res_row + nc + j, is_bf16);
             }
           }
+        }
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) packed[j] = pack16(x[2 * j], x[2 * j + 1], is_bf16);
+
+        if (use_tma_store) {
+          if (row0 < p.m) {  // warp-uniform: a slab wholly below the matrix is not stored
+            const uint32_t slab = out_stage + (stores & 1) * Cfg::kOutSlabBytes;
+            ++stores;
+            // The slab is free once the store issued from it two chunks ago has read it.
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+            const uint32_t sw = (lane >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index ^ row bits [1,2]
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              st_shared_v4(slab + lane * 64 + ((g ^ sw) << 4), packed[4 * g], packed[4 * g + 1], packed[4 * g + 2],
+                           packed[4 * g + 3]);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_out, reinterpret_cast<const void *>(__cvta_shared_to_generic(slab)), nc * 2, row0);
+              tma_store_commit();
+            }
+          }
+        } else if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (nc + j < p.n) {
+              out_row[nc + j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffff));
+            }
+          }
+        }
+      };
+
+      // Tensor-memory loads run one chunk ahead of the arithmetic.
+      uint32_t va[32], vb[32];
+      if (chunks > 0) tmem_ld_32x32(tacc, va);
+#pragma unroll 1
+      for (int c = 0; c < chunks; c += 2) {
+        tmem_ld_wait(va);
+        if (c + 1 < chunks) tmem_ld_32x32(tacc + (c + 1) * 32, vb);
+        finish_chunk(c, va);
+        if (c + 1 < chunks) {
+          tmem_ld_wait(vb);
+          if (c + 2 < chunks) tmem_ld_32x32(tacc + (c + 2) * 32, va);
+          finish_chunk(c + 1, vb);
         }
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
     }
+    // Stores in flight still read this CTA's shared memory.
+    if (lane == 0) tma_store_wait_all();
     if (!ok && lane == 0) {
       abort_flag = 1;
       atomicCAS(p.status, 0u, static_cast<uint32_t>(kStatusEpilogueTimeout));
@@ -392,27 +498,38 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// A (rows, row_bytes) byte matrix cut into boxes of (box_rows, 128 bytes) in the 128-byte swizzle.
-bool make_tmap(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+// A (rows, row_bytes) byte matrix cut into boxes of (box_rows, box_bytes): operands use 128-byte
+// boxes in the 128-byte swizzle, the output 64-byte boxes in the 64-byte swizzle.
+bool make_tmap(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+               uint32_t box_bytes = kRowBytes) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {row_bytes, rows};
   cuuint64_t strides[1] = {row_bytes};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(kRowBytes), box_rows};
+  cuuint32_t box[2] = {box_bytes, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
 template <int KIND, int BLOCK_N>
 cudaError_t launch_one(const GemmArgs &a, const KernelParams &kp, uint64_t row_bytes, const char **why) {
   using Cfg = Config<BLOCK_N, KIND == kKindNvf4>;
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tout;
   if (!make_tmap(&ta, a.a, a.m, row_bytes, kBlockM) || !make_tmap(&tb, a.b, a.n, row_bytes, BLOCK_N)) {
     *why = "cuTensorMapEncodeTiled refused the operand";
     return cudaErrorInvalidValue;
+  }
+  if (kp.tma_store) {
+    if (!make_tmap(&tout, a.out, a.m, static_cast<uint64_t>(a.n) * 2, 32, 64)) {
+      *why = "cuTensorMapEncodeTiled refused the output";
+      return cudaErrorInvalidValue;
+    }
+  } else {
+    tout = ta;  // never dereferenced
   }
   auto kernel = gemm_tn_kernel<KIND, BLOCK_N>;
   static bool attr_set = false;  // per instantiation
@@ -427,7 +544,7 @@ cudaError_t launch_one(const GemmArgs &a, const KernelParams &kp, uint64_t row_b
   int grid = kp.tiles_m * kp.tiles_n;
   int sms = sm_count();
   if (grid > sms) grid = sms;
-  kernel<<<grid, kNumThreads, Cfg::kSmemBytes, a.stream>>>(ta, tb, kp);
+  kernel<<<grid, kNumThreads, Cfg::kSmemBytes, a.stream>>>(ta, tb, tout, kp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) *why = "kernel launch failed";
   return e;
@@ -485,6 +602,7 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
   kp.act = a.act;
   kp.out_bf16 = a.out_bf16;
   kp.out = a.out;
+  kp.tma_store = (reinterpret_cast<uintptr_t>(a.out) & 15) == 0 ? 1 : 0;
   kp.status = a.status;
 
   if (a.kind == kGemmNvf4) {
