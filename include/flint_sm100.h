@@ -134,7 +134,7 @@ typedef enum fl_activation_t {
 
 /* FP8 linear with both operands narrow:
  *   a <float16|bfloat16>(..., k) is quantised on the fly, per row (token): s_m = amax_m / 448,
- *   code = e4m3(a / s_m); data <fp8e4m3>(rows, k); scales <float>(rows) per output channel or
+ *   code = e4m3(a * (1 / s_m)), the reciprocal taken once per row; data <fp8e4m3>(rows, k); scales <float>(rows) per output channel or
  *   <float>(1) per tensor (the reference's format, docs/fp8.md:16-18).
  *   out = round16( act( acc * (s_m * scale_n) + bias_n ) + residual_mn ),   fp32 until the end.
  * bias (rows), residual of out's shape; either may be NULL. rows a multiple of 8, k of 16.
@@ -181,7 +181,7 @@ FLAPI int32_t fl_nvfp4_available(fl_device_type_t device, int32_t *out);
 /* NVFP4 linear:
  *   codes <fp4e2m1x2>(rows, k/2); block_scales <fp8e4m3>(rows, k/16), unsigned, one per 16
  *   consecutive k; global_scale <float>(1). a is quantised on the fly per 16-element block:
- *   s = e4m3(amax_block / 6), code = e2m1(a / s), global 1.
+ *   s = e4m3(amax_block / 6), code = e2m1(a * (1 / s)), global 1.
  *   out = round16( act( acc * global_scale + bias_n ) + residual_mn ).
  * rows a multiple of 8, k of 32. No counterpart in the reference (it has no FP4 of any kind). */
 FLAPI int32_t fl_nvfp4_linear(fl_tensor_view_t a, fl_tensor_view_t codes, fl_tensor_view_t block_scales,

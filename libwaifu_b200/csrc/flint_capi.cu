@@ -446,6 +446,12 @@ void run_gemm(GemmKind kind, int m, int n, int k, const void *a, const void *b, 
   g.out = out;
   g.status = status_word();
   g.stream = 0;
+  // FLINT_SM100_SINGLE_CTA=1 keeps every GEMM on the single-CTA kernel (for A/B measurements).
+  static const bool single_cta = []() {
+    const char *v = std::getenv("FLINT_SM100_SINGLE_CTA");
+    return v && v[0] == '1';
+  }();
+  g.force_single_cta = single_cta ? 1 : 0;
   const char *why = "";
   std::pair<cudaEvent_t, cudaEvent_t> ev{nullptr, nullptr};
   if (g_timing.enabled) {

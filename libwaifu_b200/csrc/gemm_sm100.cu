@@ -1,11 +1,13 @@
 // The sm_100a GEMM kernels behind flint's quantized matmul (replaces the CUTLASS 2.x Sm80
 // mma.sync kernel of flint/cuda/gemm_fp8_cutlass.cu:94-197,267-305).
 //
-// One persistent CTA per SM, six warps:
-//   warps 0-3  epilogue: tensor memory -> registers -> scale/bias/GELU/residual -> 16-bit stores
-//   warp  4    producer: TMA tile loads of A and B (and the NVFP4 scale-factor tiles) into a
+// One persistent CTA per SM (or one pair of CTAs per two SMs), ten warps:
+//   warps 0-7  epilogue: tensor memory -> registers -> scale/bias/GELU/residual -> 16-bit stores.
+//              Warp w reads the 32 accumulator rows of lane quarter (w & 3) and the column half
+//              (w >> 2) of the tile.
+//   warp  8    producer: TMA tile loads of A and B (and the NVFP4 scale-factor tiles) into a
 //              ring of shared-memory stages, signalled through mbarriers
-//   warp  5    MMA: one thread issues tcgen05.mma on the staged tiles, accumulating in tensor
+//   warp  9    MMA: one thread issues tcgen05.mma on the staged tiles, accumulating in tensor
 //              memory; tcgen05.commit hands stages back to the producer and finished
 //              accumulators to the epilogue
 // The accumulator is double-buffered in tensor memory so the epilogue of tile i overlaps the
@@ -20,6 +22,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "ptx_sm100.cuh"
@@ -33,10 +37,13 @@ constexpr int kRowBytes = 128;          // bytes of K per operand row per stage
 constexpr int kMmaKBytes = 32;          // bytes of K one tcgen05.mma consumes per row
 constexpr int kMmasPerStage = kRowBytes / kMmaKBytes;
 constexpr int kSfTileBytes = 512;       // 128 rows x 4 scale factors
-constexpr int kNumThreads = 192;
-constexpr int kEpilogueWarps = 4;
-constexpr int kProducerWarp = 4;
-constexpr int kMmaWarp = 5;
+constexpr int kEpilogueWarps = 8;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kNumThreads = 320;
+// Tiles are walked in bands of this many tile columns, rows fastest inside a band, so that the
+// tiles in flight at one time share a compact set of A and B rows in L2.
+constexpr int kBandTiles = 8;
 
 struct KernelParams {
   int m, n;
@@ -56,31 +63,34 @@ struct KernelParams {
   int act;
   int out_bf16;
   void *out;
-  int tma_store;  // the output's base is 16-byte aligned, so tiles leave through TMA stores
+  int out_vector;  // the output's base is 16-byte aligned: 16-byte stores; else 2-byte stores
   uint32_t *status;
+  int probe;  // development builds (-DFLSM100_PROBE) only: bit 0 skips the loads, bit 1 the epilogue
 };
 
-template <int BLOCK_N, bool NVF4>
+// CTAS == 2: a pair of CTAs (one cluster) shares a 256 x BLOCK_N tile through cta_group::2 UMMAs;
+// each CTA stages its own 128 rows of A and its own half of the BLOCK_N rows of B.
+template <int BLOCK_N, bool NVF4, int CTAS = 1>
 struct Config {
+  static_assert(CTAS == 1 || !NVF4, "the pair form is not built for the block-scaled kind");
+  static_assert(BLOCK_N % 64 == 0, "each epilogue warp takes whole 32-column chunks of half a tile");
   static constexpr int kABytes = kBlockM * kRowBytes;
-  static constexpr int kBBytes = BLOCK_N * kRowBytes;
+  static constexpr int kBRows = BLOCK_N / CTAS;
+  static constexpr int kBBytes = kBRows * kRowBytes;
   // Scale factors: A has one 128-row group; B is loaded as whole 128-row groups that cover the
   // tile (a 192-wide tile starts mid-group on odd tiles, so it needs two).
   static constexpr int kSfbGroups = NVF4 ? (BLOCK_N + 127) / 128 : 0;
   static constexpr int kSfaBytes = NVF4 ? kMmasPerStage * kSfTileBytes : 0;
   static constexpr int kSfbBytes = NVF4 ? kSfbGroups * kMmasPerStage * kSfTileBytes : 0;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  // Epilogue staging: per epilogue warp two 32-row x 64-byte output slabs (64-byte swizzle) for
-  // the TMA stores, then each warp's own copy of the tile's per-column scale and bias as fp32
-  // (a private copy needs no barrier between warps, so no wait in the epilogue is unbounded).
-  static constexpr int kOutSlabBytes = 32 * 64;
-  static constexpr int kOutStageBytes = kEpilogueWarps * 2 * kOutSlabBytes;
-  static constexpr int kColParamBytes = kEpilogueWarps * 2 * BLOCK_N * 4;
-  static constexpr int kSmemBudget = 227 * 1024 - 2048 - kOutStageBytes - kColParamBytes;
+  // Each epilogue warp keeps its own copy of its columns' scale and bias as fp32 (a private copy
+  // needs no barrier between warps, so no wait in the epilogue is unbounded).
+  static constexpr int kHalfN = BLOCK_N / 2;
+  static constexpr int kColParamBytes = kEpilogueWarps * 2 * kHalfN * 4;
+  static constexpr int kSmemBudget = 227 * 1024 - 2048 - kColParamBytes;
   static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kOutStageOffset = kStages * kStageBytes;
-  static constexpr int kColParamOffset = kOutStageOffset + kOutStageBytes;
+  static constexpr int kColParamOffset = kStages * kStageBytes;
   static constexpr int kSmemBytes = kColParamOffset + kColParamBytes + 1024;  // + slack to align to 1024
   // Tensor memory columns: two accumulators, then the scale factors of one stage.
   static constexpr int kAccCols = 2 * BLOCK_N;
@@ -95,12 +105,18 @@ struct Config {
 };
 
 __device__ __forceinline__ float gelu_tanh(float x) {
-  // 0.5 x (1 + tanh(u)) == x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715 x^3)
+  // 0.5 x (1 + tanh(u)) == x * sigmoid(2u) == x / (1 + 2^z), u = sqrt(2/pi) (x + 0.044715 x^3),
+  // z = -2 u log2(e) = x (c0 + c1 x^2)
   // (waifu/src/krea2/dit.rs:170-188 spells the same function as seven graph nodes).
-  const float kAlpha = 0.7978845608028654f;
-  float u = kAlpha * (x + 0.044715f * x * x * x);
-  float e = __expf(-2.0f * u);
-  return __fdividef(x, 1.0f + e);
+  // Five FP32 operations and two special-function operations; both approximations are good to
+  // about 2^-22, far inside the 16-bit output step. x -> -inf gives 2^z = inf, 1/inf = 0, -0.
+  constexpr float kC0 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;
+  constexpr float kC1 = kC0 * 0.044715f;
+  const float z = x * fmaf(x * x, kC1, kC0);
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+  return x * r;
 }
 
 __device__ __forceinline__ float load16(const void *p, long long idx, int is_bf16) {
@@ -117,13 +133,29 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi, int is_bf16) {
   return *reinterpret_cast<uint32_t *>(&v);
 }
 
-template <int KIND, int BLOCK_N>
+// Tile index -> (row tile, column tile): bands of kBandTiles tile columns, rows fastest.
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int *tm, int *tn) {
+  const int per_band = kBandTiles * tiles_m;
+  const int band = tile / per_band;
+  const int r = tile - band * per_band;
+  const int width = min(kBandTiles, tiles_n - band * kBandTiles);
+  *tm = r / width;
+  *tn = band * kBandTiles + (r - (*tm) * width);
+}
+
+template <int KIND, int BLOCK_N, int CTAS>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const __grid_constant__ CUtensorMap tmap_out, const KernelParams p) {
+               const KernelParams p) {
   constexpr bool NVF4 = (KIND == kKindNvf4);
-  using Cfg = Config<BLOCK_N, NVF4>;
+  using Cfg = Config<BLOCK_N, NVF4, CTAS>;
   constexpr int STAGES = Cfg::kStages;
+  // A work unit is one CTA, or one pair of CTAs; rank 0 of a pair is its leader: it owns the
+  // barriers both producers signal and it alone issues the UMMAs.
+  const uint32_t cta_rank = (CTAS == 2) ? cluster_cta_rank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int unit = blockIdx.x / CTAS;
+  const int num_units = gridDim.x / CTAS;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -138,6 +170,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
+#ifdef FLSM100_PROBE
+  long long probe_c0 = 0;
+  unsigned long long probe_t0 = 0;
+  if ((p.probe & 16) && blockIdx.x == 0 && threadIdx.x == 0) {
+    probe_c0 = clock64();
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(probe_t0));
+  }
+#endif
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -147,7 +187,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&acc_full_bar[s], 1);
-      mbar_init(&acc_empty_bar[s], kEpilogueWarps);
+      mbar_init(&acc_empty_bar[s], kEpilogueWarps * CTAS);  // in a pair both CTAs' epilogues report to the leader
     }
     fence_barrier_init();
   }
@@ -156,13 +196,18 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     tma_prefetch_desc(&tmap_b);
   }
   if (warp == kMmaWarp) {
-    tmem_alloc(&tmem_base_slot, Cfg::kTmemCols);
-    tmem_relinquish();
+    tmem_alloc<CTAS>(&tmem_base_slot, Cfg::kTmemCols);
+    tmem_relinquish<CTAS>();
   }
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (CTAS == 2) cluster_sync_all();  // the other CTA's barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
+  // Everything above touched no global memory, so it may overlap the tail of the kernel before
+  // this one in the stream (the activation quantiser); from here on its results are needed.
+  griddep_wait();
+  griddep_launch_dependents();
 
   auto stage_a = [&](int s) { return smem + s * Cfg::kStageBytes; };
   auto stage_b = [&](int s) { return smem + s * Cfg::kStageBytes + Cfg::kABytes; };
@@ -175,19 +220,38 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int tm = tile % p.tiles_m;
-        const int tn = tile / p.tiles_m;
-        const int m0 = tm * kBlockM;
+      for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
+        const int m0 = tm * (kBlockM * CTAS) + static_cast<int>(cta_rank) * kBlockM;
         const int n0 = tn * BLOCK_N;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, &abort_flag)) {
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-          tma_load_2d(stage_a(stage), &tmap_a, &full_bar[stage], kb * kRowBytes, m0);
-          tma_load_2d(stage_b(stage), &tmap_b, &full_bar[stage], kb * kRowBytes, n0);
+#ifdef FLSM100_PROBE
+          if (p.probe & 1) {  // timing probe: hand over the stage without loading it
+            if (leader) mbar_arrive(&full_bar[stage]);
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+            continue;
+          }
+#endif
+          if constexpr (CTAS == 2) {
+            // Both CTAs' bytes are counted on the leader's barrier, which the leader arms.
+            if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
+            const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+            tma_load_2d_pair(stage_a(stage), &tmap_a, bar, kb * kRowBytes, m0);
+            tma_load_2d_pair(stage_b(stage), &tmap_b, bar, kb * kRowBytes,
+                             n0 + static_cast<int>(cta_rank) * Cfg::kBRows);
+          } else {
+            mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+            tma_load_2d(stage_a(stage), &tmap_a, &full_bar[stage], kb * kRowBytes, m0);
+            tma_load_2d(stage_b(stage), &tmap_b, &full_bar[stage], kb * kRowBytes, n0);
+          }
           if constexpr (NVF4) {
             // Scale-factor tiles of this k block: kMmasPerStage consecutive 512-byte tiles per
             // 128-row group.
@@ -215,15 +279,24 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issue
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       // e4m3 is format 0 of kind::f8f6f4; fp16 / bf16 are formats 0 / 1 of kind::f16.
       constexpr uint32_t kFmt = (KIND == kKindBF16) ? 1u : 0u;
-      constexpr uint32_t idesc = NVF4 ? umma_idesc_nvf4(kBlockM, BLOCK_N) : umma_idesc(kBlockM, BLOCK_N, kFmt, kFmt);
+      constexpr uint32_t idesc =
+          NVF4 ? umma_idesc_nvf4(kBlockM, BLOCK_N) : umma_idesc(kBlockM * CTAS, BLOCK_N, kFmt, kFmt);
+      // Hands a barrier (same offset in every CTA of the pair) the completion of the UMMAs so far.
+      auto commit_to = [&](uint64_t *bar) {
+        if constexpr (CTAS == 2) {
+          umma_commit_pair_both(bar);
+        } else {
+          umma_commit(bar);
+        }
+      };
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int local = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, &abort_flag)) {
@@ -256,7 +329,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
             // A tile that starts 64 rows into a 128-row group reads its scale factors two
             // columns further on (32 rows per column).
-            const int tn = tile / p.tiles_m;
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
             const uint32_t sfb_skip = ((tn * BLOCK_N) % 128) / 32;
 #pragma unroll
             for (int j = 0; j < kMmasPerStage; ++j) {
@@ -267,18 +341,23 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           } else {
 #pragma unroll
             for (int j = 0; j < kMmasPerStage; ++j) {
-              umma_ss<KIND>(d_tmem, adesc + j * (kMmaKBytes >> 4), bdesc + j * (kMmaKBytes >> 4),
-                            idesc, (kb | j) != 0 ? 1u : 0u);
+              if constexpr (CTAS == 2) {
+                umma_ss_pair<KIND>(d_tmem, adesc + j * (kMmaKBytes >> 4), bdesc + j * (kMmaKBytes >> 4), idesc,
+                                   (kb | j) != 0 ? 1u : 0u);
+              } else {
+                umma_ss<KIND>(d_tmem, adesc + j * (kMmaKBytes >> 4), bdesc + j * (kMmaKBytes >> 4), idesc,
+                              (kb | j) != 0 ? 1u : 0u);
+              }
             }
           }
-          umma_commit(&empty_bar[stage]);
+          commit_to(&empty_bar[stage]);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        umma_commit(&acc_full_bar[acc]);
+        commit_to(&acc_full_bar[acc]);
       }
       if (!ok) {
         abort_flag = 1;
@@ -287,9 +366,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------------ epilogue
+    constexpr int HALF_N = Cfg::kHalfN;
+    constexpr int HALF_CHUNKS = HALF_N / 32;
+    const uint32_t quarter = warp & 3;  // which 32 lanes of tensor memory, i.e. which 32 rows of the tile
+    const uint32_t half = warp >> 2;    // which half of the tile's columns
     bool ok = true;
     int local = 0;
-    uint32_t stores = 0;  // TMA stores this warp has issued, for the two-slab rotation
     const int is_bf16 = p.out_bf16;
     const bool has_cs_vec = p.col_scale != nullptr && !p.col_scale_scalar;
     const bool has_bias = p.bias != nullptr;
@@ -297,28 +379,24 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const bool has_gs = p.global_scale != nullptr;
     const float gscale = has_gs ? __ldg(p.global_scale) : 1.0f;
     const float cs_scalar = (p.col_scale && p.col_scale_scalar) ? __ldg(p.col_scale) : 1.0f;
-    const bool use_tma_store = p.tma_store != 0;
+    const bool out_vector = p.out_vector != 0;
     const bool res_vec_ok = has_res && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0 && (p.residual_ld % 8) == 0;
-    float *col_params = reinterpret_cast<float *>(smem + Cfg::kColParamOffset);
-    const uint32_t out_stage = smem_u32(smem + Cfg::kOutStageOffset + warp * 2 * Cfg::kOutSlabBytes);
-    if (warp == 0 && lane == 0 && use_tma_store) tma_prefetch_desc(&tmap_out);
+    float *cs_t = reinterpret_cast<float *>(smem + Cfg::kColParamOffset) + warp * 2 * HALF_N;
+    float *bias_t = cs_t + HALF_N;
 
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+    for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++local) {
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
-      const int tm = tile % p.tiles_m;
-      const int tn = tile / p.tiles_m;
-      const int row0 = tm * kBlockM + warp * 32;
-      const int row = row0 + lane;
-      const int n0 = tn * BLOCK_N;
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
+      const int row = tm * (kBlockM * CTAS) + static_cast<int>(cta_rank) * kBlockM + quarter * 32 + lane;
+      const int n0 = tn * BLOCK_N + half * HALF_N;  // first column this warp owns
 
-      // This tile's per-column scale and bias, widened to fp32 once, in this warp's own slice of
-      // shared memory.
-      float *cs_t = col_params + warp * 2 * BLOCK_N;
-      float *bias_t = cs_t + BLOCK_N;
+      // This warp's per-column scale and bias, widened to fp32 once, in its own slice of shared
+      // memory.
       if (has_cs_vec || has_bias) {
         __syncwarp();  // the previous tile's reads are done
-        for (int i = lane; i < BLOCK_N; i += 32) {
+        for (int i = lane; i < HALF_N; i += 32) {
           const int n = n0 + i;
           cs_t[i] = (has_cs_vec && n < p.n) ? __ldg(p.col_scale + n) : 1.0f;
           bias_t[i] = (has_bias && n < p.n) ? load16(p.bias, n, is_bf16) : 0.0f;
@@ -337,8 +415,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const long long res_row =
           (has_res && row_ok) ? static_cast<long long>(row % p.residual_rows) * p.residual_ld : 0;
       uint16_t *out_row = reinterpret_cast<uint16_t *>(p.out) + static_cast<long long>(row) * p.n;
-      const int chunks = min(BLOCK_N / 32, (p.n - n0 + 31) / 32);  // chunks holding a valid column
-      const uint32_t tacc = tmem_base + ((warp * 32) << 16) + acc * BLOCK_N;
+      int chunks = (p.n - n0 + 31) / 32;  // chunks of this warp's half that hold a valid column
+      chunks = chunks < 0 ? 0 : (chunks > HALF_CHUNKS ? HALF_CHUNKS : chunks);
+      const uint32_t tacc = tmem_base + ((quarter * 32) << 16) + acc * BLOCK_N + half * HALF_N;
 
       // One 32-column chunk: scale, bias, activation, residual in fp32; one rounding; store.
       auto finish_chunk = [&](int c, uint32_t (&v)[32]) {
@@ -406,28 +485,20 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         uint32_t packed[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) packed[j] = pack16(x[2 * j], x[2 * j + 1], is_bf16);
-
-        if (use_tma_store) {
-          if (row0 < p.m) {  // warp-uniform: a slab wholly below the matrix is not stored
-            const uint32_t slab = out_stage + (stores & 1) * Cfg::kOutSlabBytes;
-            ++stores;
-            // The slab is free once the store issued from it two chunks ago has read it.
-            if (lane == 0) tma_store_wait_read<1>();
-            __syncwarp();
-            const uint32_t sw = (lane >> 1) & 3;  // 64-byte swizzle: 16-byte chunk index ^ row bits [1,2]
+#ifdef FLSM100_PROBE
+        if (p.probe & 4) return;  // timing probe: no stores
+#endif
+        if (!row_ok) return;
+        if (out_vector) {
+          // 64 contiguous bytes of this thread's row, as four 16-byte stores.
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              st_shared_v4(slab + lane * 64 + ((g ^ sw) << 4), packed[4 * g], packed[4 * g + 1], packed[4 * g + 2],
-                           packed[4 * g + 3]);
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(&tmap_out, reinterpret_cast<const void *>(__cvta_shared_to_generic(slab)), nc * 2, row0);
-              tma_store_commit();
+          for (int g = 0; g < 4; ++g) {
+            if (nc + g * 8 < p.n) {  // n is a multiple of 8: a group of 8 is whole or absent
+              *reinterpret_cast<uint4 *>(out_row + nc + g * 8) =
+                  make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
             }
           }
-        } else if (row_ok) {
+        } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (nc + j < p.n) {
@@ -439,24 +510,33 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
       // Tensor-memory loads run one chunk ahead of the arithmetic.
       uint32_t va[32], vb[32];
-      if (chunks > 0) tmem_ld_32x32(tacc, va);
+#ifdef FLSM100_PROBE
+      const int chunks_run = (p.probe & 2) ? 0 : chunks;  // timing probe: release the accumulator unread
+#else
+      const int chunks_run = chunks;
+#endif
+      if (chunks_run > 0) tmem_ld_32x32(tacc, va);
 #pragma unroll 1
-      for (int c = 0; c < chunks; c += 2) {
+      for (int c = 0; c < chunks_run; c += 2) {
         tmem_ld_wait(va);
-        if (c + 1 < chunks) tmem_ld_32x32(tacc + (c + 1) * 32, vb);
+        if (c + 1 < chunks_run) tmem_ld_32x32(tacc + (c + 1) * 32, vb);
         finish_chunk(c, va);
-        if (c + 1 < chunks) {
+        if (c + 1 < chunks_run) {
           tmem_ld_wait(vb);
-          if (c + 2 < chunks) tmem_ld_32x32(tacc + (c + 2) * 32, va);
+          if (c + 2 < chunks_run) tmem_ld_32x32(tacc + (c + 2) * 32, va);
           finish_chunk(c + 1, vb);
         }
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+      if (lane == 0) {
+        if constexpr (CTAS == 2) {
+          mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[acc]), 0));
+        } else {
+          mbar_arrive(&acc_empty_bar[acc]);
+        }
+      }
     }
-    // Stores in flight still read this CTA's shared memory.
-    if (lane == 0) tma_store_wait_all();
     if (!ok && lane == 0) {
       abort_flag = 1;
       atomicCAS(p.status, 0u, static_cast<uint32_t>(kStatusEpilogueTimeout));
@@ -472,10 +552,22 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     for (int i = 0; i < 64; ++i) __nanosleep(2000);
     __syncthreads();
   }
+  // In a pair the leader's UMMAs read the other CTA's shared memory and both CTAs signal each
+  // other's barriers, so neither may leave or free tensor memory before both are done.
+  if constexpr (CTAS == 2) cluster_sync_all();
   if (warp == kMmaWarp) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    tmem_dealloc<CTAS>(tmem_base, Cfg::kTmemCols);
   }
+#ifdef FLSM100_PROBE
+  if ((p.probe & 16) && blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    const long long c1 = clock64();
+    printf("probe: %lld cycles in %llu ns = %.3f GHz\n", c1 - probe_c0, t1 - probe_t0,
+           double(c1 - probe_c0) / double(t1 - probe_t0));
+  }
+#endif
 }
 
 // ---- host side ------------------------------------------------------------------------------
@@ -498,40 +590,31 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// A (rows, row_bytes) byte matrix cut into boxes of (box_rows, box_bytes): operands use 128-byte
-// boxes in the 128-byte swizzle, the output 64-byte boxes in the 64-byte swizzle.
-bool make_tmap(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
-               uint32_t box_bytes = kRowBytes) {
+// A (rows, row_bytes) byte matrix cut into boxes of (box_rows, 128 bytes) in the 128-byte swizzle.
+bool make_tmap(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {row_bytes, rows};
   cuuint64_t strides[1] = {row_bytes};
-  cuuint32_t box[2] = {box_bytes, box_rows};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kRowBytes), box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
-template <int KIND, int BLOCK_N>
-cudaError_t launch_one(const GemmArgs &a, const KernelParams &kp, uint64_t row_bytes, const char **why) {
-  using Cfg = Config<BLOCK_N, KIND == kKindNvf4>;
-  CUtensorMap ta, tb, tout;
-  if (!make_tmap(&ta, a.a, a.m, row_bytes, kBlockM) || !make_tmap(&tb, a.b, a.n, row_bytes, BLOCK_N)) {
+template <int KIND, int BLOCK_N, int CTAS>
+cudaError_t launch_one(const GemmArgs &a, KernelParams kp, uint64_t row_bytes, const char **why) {
+  using Cfg = Config<BLOCK_N, KIND == kKindNvf4, CTAS>;
+  kp.tiles_m = (a.m + kBlockM * CTAS - 1) / (kBlockM * CTAS);
+  kp.tiles_n = (a.n + BLOCK_N - 1) / BLOCK_N;
+  CUtensorMap ta, tb;
+  if (!make_tmap(&ta, a.a, a.m, row_bytes, kBlockM) || !make_tmap(&tb, a.b, a.n, row_bytes, Cfg::kBRows)) {
     *why = "cuTensorMapEncodeTiled refused the operand";
     return cudaErrorInvalidValue;
   }
-  if (kp.tma_store) {
-    if (!make_tmap(&tout, a.out, a.m, static_cast<uint64_t>(a.n) * 2, 32, 64)) {
-      *why = "cuTensorMapEncodeTiled refused the output";
-      return cudaErrorInvalidValue;
-    }
-  } else {
-    tout = ta;  // never dereferenced
-  }
-  auto kernel = gemm_tn_kernel<KIND, BLOCK_N>;
+  auto kernel = gemm_tn_kernel<KIND, BLOCK_N, CTAS>;
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
@@ -541,11 +624,25 @@ cudaError_t launch_one(const GemmArgs &a, const KernelParams &kp, uint64_t row_b
     }
     attr_set = true;
   }
-  int grid = kp.tiles_m * kp.tiles_n;
-  int sms = sm_count();
-  if (grid > sms) grid = sms;
-  kernel<<<grid, kNumThreads, Cfg::kSmemBytes, a.stream>>>(ta, tb, tout, kp);
-  cudaError_t e = cudaGetLastError();
+  int units = kp.tiles_m * kp.tiles_n;
+  const int max_units = sm_count() / CTAS;
+  if (units > max_units) units = max_units;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(units * CTAS), 1, 1);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = a.stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  // Programmatic dependent launch: the prologue may run while the previous kernel drains.
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, kp);
   if (e != cudaSuccess) *why = "kernel launch failed";
   return e;
 }
@@ -587,7 +684,7 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
   kp.m = a.m;
   kp.n = a.n;
   kp.num_kb = static_cast<int>((row_bytes + kRowBytes - 1) / kRowBytes);
-  kp.tiles_m = (a.m + kBlockM - 1) / kBlockM;
+  kp.tiles_m = kp.tiles_n = 0;  // set per instantiation
   kp.sfa = a.sfa;
   kp.sfb = a.sfb;
   kp.sf_k_tiles = a.sf_k_tiles;
@@ -602,32 +699,30 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
   kp.act = a.act;
   kp.out_bf16 = a.out_bf16;
   kp.out = a.out;
-  kp.tma_store = (reinterpret_cast<uintptr_t>(a.out) & 15) == 0 ? 1 : 0;
+  kp.out_vector = (reinterpret_cast<uintptr_t>(a.out) & 15) == 0 ? 1 : 0;
   kp.status = a.status;
+  kp.probe = 0;
+#ifdef FLSM100_PROBE
+  if (const char *v = std::getenv("FLSM100_PROBE")) kp.probe = std::atoi(v);
+#endif
 
-  if (a.kind == kGemmNvf4) {
-    constexpr int BN = 192;
-    kp.tiles_n = (a.n + BN - 1) / BN;
-    return launch_one<kKindNvf4, BN>(a, kp, row_bytes, why);
-  }
-  // Narrow outputs use the narrower tile so that fewer columns of the MMA are padding.
+  if (a.kind == kGemmNvf4) return launch_one<kKindNvf4, 192, 1>(a, kp, row_bytes, why);
+  // A pair of CTAs per 256 x 256 tile halves the B bytes each SM pulls from L2; it needs two row
+  // blocks to share the B tile between. Narrow outputs use the narrower single-CTA tile so that
+  // fewer columns of the MMA are padding.
+  const bool pair = a.m > kBlockM && a.n > 128 && !a.force_single_cta;
   const bool narrow = a.n <= 128;
-  if (a.kind == kGemmE4M3) {
-    if (narrow) {
-      kp.tiles_n = (a.n + 127) / 128;
-      return launch_one<kKindF8, 128>(a, kp, row_bytes, why);
-    }
-    kp.tiles_n = (a.n + 255) / 256;
-    return launch_one<kKindF8, 256>(a, kp, row_bytes, why);
+  switch (a.kind) {
+    case kGemmE4M3:
+      if (pair) return launch_one<kKindF8, 256, 2>(a, kp, row_bytes, why);
+      return narrow ? launch_one<kKindF8, 128, 1>(a, kp, row_bytes, why) : launch_one<kKindF8, 256, 1>(a, kp, row_bytes, why);
+    case kGemmBF16:
+      if (pair) return launch_one<kKindBF16, 256, 2>(a, kp, row_bytes, why);
+      return narrow ? launch_one<kKindBF16, 128, 1>(a, kp, row_bytes, why) : launch_one<kKindBF16, 256, 1>(a, kp, row_bytes, why);
+    default:
+      if (pair) return launch_one<kKindF16, 256, 2>(a, kp, row_bytes, why);
+      return narrow ? launch_one<kKindF16, 128, 1>(a, kp, row_bytes, why) : launch_one<kKindF16, 256, 1>(a, kp, row_bytes, why);
   }
-  if (narrow) {
-    kp.tiles_n = (a.n + 127) / 128;
-    return a.kind == kGemmBF16 ? launch_one<kKindBF16, 128>(a, kp, row_bytes, why)
-                               : launch_one<kKindF16, 128>(a, kp, row_bytes, why);
-  }
-  kp.tiles_n = (a.n + 255) / 256;
-  return a.kind == kGemmBF16 ? launch_one<kKindBF16, 256>(a, kp, row_bytes, why)
-                             : launch_one<kKindF16, 256>(a, kp, row_bytes, why);
 }
 
 }  // namespace flsm100

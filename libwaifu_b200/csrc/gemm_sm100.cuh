@@ -52,6 +52,7 @@ struct GemmArgs {
   int out_bf16;                // 1 bf16, 0 fp16
   void *out;                   // (m, n), pitch n
   uint32_t *status;            // device word, zeroed by the caller; non-zero after a failed wait
+  int force_single_cta;        // 1: never pair CTAs (for tests that compare the two forms)
   cudaStream_t stream;
 };
 

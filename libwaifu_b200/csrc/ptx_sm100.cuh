@@ -21,6 +21,38 @@ __device__ __forceinline__ uint32_t lane_id() {
   return l;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+
+// Blocks until the grid this one was launched behind (same stream, programmatic serialization)
+// has completed and its writes are visible. A no-op for an ordinary launch.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next grid in the stream start its own prologue while this one is still running.
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---- thread-block clusters -----------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// The shared::cluster address of the location `smem_addr` (a shared::cta address) in CTA `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+
+// Barrier over every thread of every CTA of the cluster. Unbounded, so it is only used where
+// every path that leads to it is itself bounded (set-up and teardown).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // ---- mbarrier ----------------------------------------------------------------------------
 
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
@@ -42,6 +74,11 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t by
 
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Arrival on a barrier given by a shared::cluster address (possibly in the other CTA of the pair).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
@@ -89,6 +126,17 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *d
       : "memory");
 }
 
+// The same load issued by one CTA of a cta_group::2 pair: the bytes land in this CTA's shared
+// memory while the completion is counted on a barrier that may live in the other CTA of the pair
+// (`bar_cluster_addr` is a shared::cluster address). One CTA's own memory only.
+__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *desc, uint32_t bar_cluster_addr,
+                                                 int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+
 // 1-D bulk copy global -> shared (16-byte aligned on both sides, size a multiple of 16).
 __device__ __forceinline__ void bulk_load_1d(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar) {
   asm volatile(
@@ -97,43 +145,37 @@ __device__ __forceinline__ void bulk_load_1d(void *smem_dst, const void *gmem_sr
       : "memory");
 }
 
-// 2-D tiled store shared -> global (bulk async-group completion). Rows or columns of the box
-// that fall outside the tensor are clipped by the hardware.
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *desc, const void *smem_src, int32_t x, int32_t y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-               ::"l"(reinterpret_cast<uint64_t>(desc)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// Waits until at most N of this thread's committed store groups still have shared memory to read.
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
-// Barrier among `count` threads of the CTA (a multiple of 32), on hardware barrier `id` (1..15).
-__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-
 // ---- tcgen05: tensor memory --------------------------------------------------------------
 
-// Whole-warp instructions. `ncols` a power of two in [32, 512].
+// Whole-warp instructions. `ncols` a power of two in [32, 512]. With CTAS == 2 the same warp of
+// both CTAs of the pair executes them and each CTA gets the same columns of its own tensor memory.
+template <int CTAS>
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_result, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
-               "r"(ncols)
-               : "memory");
+  if constexpr (CTAS == 2) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+                 "r"(ncols)
+                 : "memory");
+  } else {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+                 "r"(ncols)
+                 : "memory");
+  }
 }
+template <int CTAS>
 __device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if constexpr (CTAS == 2) {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  } else {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
 }
+template <int CTAS>
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+  if constexpr (CTAS == 2) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+  } else {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+  }
 }
 
 __device__ __forceinline__ void tc_fence_before_sync() {
@@ -183,6 +225,26 @@ __host__ __device__ constexpr uint32_t umma_idesc_nvf4(uint32_t m, uint32_t n) {
 
 enum : int { kKindF16 = 0, kKindBF16 = 1, kKindF8 = 2, kKindNvf4 = 3 };
 
+// The pair form: issued by the leader CTA only, it multiplies the 256 x N tile whose A rows and B
+// rows are split between the two CTAs' shared memories and accumulates into both tensor memories.
+template <int KIND>
+__device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  if constexpr (KIND == kKindF16 || KIND == kKindBF16) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
 template <int KIND>
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                         uint32_t accumulate) {
@@ -214,6 +276,15 @@ __device__ __forceinline__ void umma_nvf4_ss(uint32_t d_tmem, uint64_t adesc, ui
 // (finished reading shared memory and writing tensor memory).
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+// The pair form of the commit: tracks the leader's cta_group::2 UMMAs and arrives once on the
+// barrier at `bar`'s offset in both CTAs of the pair (CTA mask 0b11).
+__device__ __forceinline__ void umma_commit_pair_both(uint64_t *bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask)
                : "memory");
 }
 

@@ -1,8 +1,11 @@
 // Helper kernels of the quantized-linear path. All of them are HBM-bound streaming kernels:
 // 16-byte vector accesses, one pass where the row fits in registers' reach of L1, grids sized by
-// rows. Divisions are IEEE (this file is compiled without fast-math) because the codes must be
-// bit-identical to the CPU oracle's.
+// rows. Divisions and reciprocals are IEEE (this file is compiled without fast-math) because the
+// codes must be bit-identical to the CPU oracle's; the dynamic quantisers take one reciprocal per
+// row or block and multiply by it, which is what keeps them bandwidth-bound.
 #include "quant_sm100.cuh"
+
+#include "ptx_sm100.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -48,6 +51,21 @@ __device__ __forceinline__ float e4m3_value(uint8_t code) {
   return __half2float(__half(h));
 }
 
+// Eight 16-bit values times `inv`, as eight e4m3 codes in memory order.
+__device__ __forceinline__ uint2 e4m3x8_of(uint4 q, int is_bf16, float inv) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  uint32_t out[2] = {0, 0};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 pair = make_float2(__fmul_rn(widen(static_cast<uint16_t>(w[j] & 0xffff), is_bf16), inv),
+                                    __fmul_rn(widen(static_cast<uint16_t>(w[j] >> 16), is_bf16), inv));
+    // x in the low byte, y in the high byte
+    const uint32_t two = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(pair, __NV_SATFINITE, __NV_E4M3));
+    out[j >> 1] |= (two & 0xffff) << ((j & 1) * 16);
+  }
+  return make_uint2(out[0], out[1]);
+}
+
 // ---- per-row e4m3 ----------------------------------------------------------------------------
 
 // One CTA per row. Pass 1 finds amax, pass 2 re-reads the row (an L1/L2 hit: a row is a few KB)
@@ -56,6 +74,7 @@ template <bool VEC>
 __global__ void __launch_bounds__(128) quantize_fp8_act_kernel(const uint16_t *__restrict__ x, int is_bf16, int k,
                                                              uint8_t *__restrict__ codes,
                                                              float *__restrict__ scales) {
+  griddep_wait();
   __shared__ float red[4];
   const int64_t row = blockIdx.x;
   const uint16_t *xr = x + row * k;
@@ -77,25 +96,55 @@ __global__ void __launch_bounds__(128) quantize_fp8_act_kernel(const uint16_t *_
   }
   amax = block_max(amax, red);
   const float scale = __fdiv_rn(amax, 448.0f);
-  const float divisor = scale > 0.0f ? scale : 1.0f;
+  const float inv = __frcp_rn(scale > 0.0f ? scale : 1.0f);
   if (threadIdx.x == 0) scales[row] = scale;
+  griddep_launch_dependents();
   if (VEC) {
     const uint4 *xv = reinterpret_cast<const uint4 *>(xr);
     uint2 *cv = reinterpret_cast<uint2 *>(cr);
-    for (int i = threadIdx.x; i < k / 8; i += blockDim.x) {
-      uint4 q = xv[i];
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-      uint32_t out[2] = {0, 0};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint32_t lo = e4m3_of(__fdiv_rn(widen(static_cast<uint16_t>(w[j] & 0xffff), is_bf16), divisor));
-        uint32_t hi = e4m3_of(__fdiv_rn(widen(static_cast<uint16_t>(w[j] >> 16), is_bf16), divisor));
-        out[j >> 1] |= (lo | (hi << 8)) << ((j & 1) * 16);
-      }
-      cv[i] = make_uint2(out[0], out[1]);
-    }
+    for (int i = threadIdx.x; i < k / 8; i += blockDim.x) cv[i] = e4m3x8_of(xv[i], is_bf16, inv);
   } else {
-    for (int i = threadIdx.x; i < k; i += blockDim.x) cr[i] = e4m3_of(__fdiv_rn(widen(xr[i], is_bf16), divisor));
+    for (int i = threadIdx.x; i < k; i += blockDim.x) cr[i] = e4m3_of(__fmul_rn(widen(xr[i], is_bf16), inv));
+  }
+}
+
+// The same for rows short enough to stay in registers between the two passes (k <= 2048 * VPT):
+// one global read of the row, 256 threads, VPT 16-byte vectors per thread.
+template <int VPT>
+__global__ void __launch_bounds__(256) quantize_fp8_act_reg_kernel(const uint16_t *__restrict__ x, int is_bf16, int k,
+                                                                 uint8_t *__restrict__ codes,
+                                                                 float *__restrict__ scales) {
+  griddep_wait();
+  __shared__ float red[8];
+  const int64_t row = blockIdx.x;
+  const uint4 *xv = reinterpret_cast<const uint4 *>(x + row * k);
+  uint2 *cv = reinterpret_cast<uint2 *>(codes + row * k);
+  const int nvec = k / 8;
+  uint4 q[VPT];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * 256;
+    q[i] = (v < nvec) ? xv[v] : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const uint32_t w[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      amax = fmaxf(amax, fabsf(widen(static_cast<uint16_t>(w[j] & 0xffff), is_bf16)));
+      amax = fmaxf(amax, fabsf(widen(static_cast<uint16_t>(w[j] >> 16), is_bf16)));
+    }
+  }
+  amax = block_max(amax, red);
+  const float scale = __fdiv_rn(amax, 448.0f);
+  const float inv = __frcp_rn(scale > 0.0f ? scale : 1.0f);
+  if (threadIdx.x == 0) scales[row] = scale;
+  griddep_launch_dependents();
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < nvec) cv[v] = e4m3x8_of(q[i], is_bf16, inv);
   }
 }
 
@@ -129,9 +178,10 @@ __device__ __forceinline__ uint8_t nvfp4_block(const float (&v)[16], float globa
   const float denom = __fmul_rn(e4m3_value(sc), global);
   packed[0] = packed[1] = 0;
   if (!(denom > 0.0f)) return 0;
+  const float inv = __frcp_rn(denom);
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    float2 pair = make_float2(__fdiv_rn(v[2 * j], denom), __fdiv_rn(v[2 * j + 1], denom));
+    float2 pair = make_float2(__fmul_rn(v[2 * j], inv), __fmul_rn(v[2 * j + 1], inv));
     uint32_t byte = static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(pair, __NV_E2M1, cudaRoundNearest));
     packed[j >> 2] |= (byte & 0xff) << ((j & 3) * 8);
   }
@@ -292,10 +342,30 @@ cudaError_t quantize_fp8_act(const void *x, int is_bf16, int m, int k, uint8_t *
                              cudaStream_t stream) {
   const bool vec = aligned16(x) && aligned16(codes) && (k % 16 == 0);
   const uint16_t *xs = static_cast<const uint16_t *>(x);
-  if (vec) quantize_fp8_act_kernel<true><<<m, 128, 0, stream>>>(xs, is_bf16, k, codes, scales);
-  else quantize_fp8_act_kernel<false><<<m, 128, 0, stream>>>(xs, is_bf16, k, codes, scales);
+  // Launched behind the previous kernel in the stream with programmatic serialization, so that
+  // its blocks are resident and waiting when that kernel's results become visible.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(m), 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e;
+  if (vec && k <= 2048 * 8) {
+    cfg.blockDim = dim3(256, 1, 1);
+    if (k <= 2048 * 2) e = cudaLaunchKernelEx(&cfg, quantize_fp8_act_reg_kernel<2>, xs, is_bf16, k, codes, scales);
+    else if (k <= 2048 * 4) e = cudaLaunchKernelEx(&cfg, quantize_fp8_act_reg_kernel<4>, xs, is_bf16, k, codes, scales);
+    else if (k <= 2048 * 6) e = cudaLaunchKernelEx(&cfg, quantize_fp8_act_reg_kernel<6>, xs, is_bf16, k, codes, scales);
+    else e = cudaLaunchKernelEx(&cfg, quantize_fp8_act_reg_kernel<8>, xs, is_bf16, k, codes, scales);
+  } else {
+    cfg.blockDim = dim3(128, 1, 1);
+    if (vec) e = cudaLaunchKernelEx(&cfg, quantize_fp8_act_kernel<true>, xs, is_bf16, k, codes, scales);
+    else e = cudaLaunchKernelEx(&cfg, quantize_fp8_act_kernel<false>, xs, is_bf16, k, codes, scales);
+  }
   ++g_helper_launches;
-  return cudaGetLastError();
+  return e;
 }
 
 cudaError_t quantize_fp8_rows_f32(const float *w, int rows, int k, uint8_t *codes, float *scales,

@@ -8,8 +8,9 @@
 
 namespace flsm100 {
 
-// Per-row (token) e4m3: scales[r] = amax_r / 448, codes = e4m3_rn_sat(x / scales[r]); a zero
-// row gives scale 0 and codes 0 (the zero rule of tools/model_writer.py:162-170).
+// Per-row (token) e4m3: scales[r] = amax_r / 448, codes = e4m3_rn_sat(x * (1 / scales[r])) with
+// one IEEE reciprocal per row; a zero row gives scale 0 and codes 0 (the zero rule of
+// tools/model_writer.py:162-170). The weight quantiser below divides, as that recipe does.
 cudaError_t quantize_fp8_act(const void *x, int is_bf16, int m, int k, uint8_t *codes, float *scales,
                              cudaStream_t stream);
 cudaError_t quantize_fp8_rows_f32(const float *w, int rows, int k, uint8_t *codes, float *scales,

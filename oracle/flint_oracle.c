@@ -172,7 +172,7 @@ void fo_quantize_fp8_act(const uint16_t *x, int is_bf16, int rows, int k, uint8_
   for (r = 0; r < rows; ++r) {
     const uint16_t *row = x + (int64_t)r * k;
     uint8_t *out = codes + (int64_t)r * k;
-    float amax = 0.0f, s, divisor;
+    float amax = 0.0f, s, divisor, inv;
     int j;
     for (j = 0; j < k; ++j) {
       float a = fabsf(widen16(row[j], is_bf16));
@@ -180,14 +180,15 @@ void fo_quantize_fp8_act(const uint16_t *x, int is_bf16, int rows, int k, uint8_
     }
     s = amax / 448.0f;
     divisor = s > 0.0f ? s : 1.0f;
-    for (j = 0; j < k; ++j) out[j] = fo_e4m3_encode(widen16(row[j], is_bf16) / divisor);
+    inv = 1.0f / divisor; /* one IEEE reciprocal per row, then one multiply per element */
+    for (j = 0; j < k; ++j) out[j] = fo_e4m3_encode(widen16(row[j], is_bf16) * inv);
     scales[r] = s;
   }
 }
 
 static void nvfp4_block(const float *v, float global, uint8_t *codes8, uint8_t *scale_code) {
   /* 16 values -> 8 bytes of e2m1 pairs + one unsigned e4m3 block scale. */
-  float amax = 0.0f, sdec, denom;
+  float amax = 0.0f, sdec, denom, inv;
   uint8_t sc;
   int j;
   for (j = 0; j < 16; ++j) {
@@ -202,9 +203,10 @@ static void nvfp4_block(const float *v, float global, uint8_t *codes8, uint8_t *
     *scale_code = 0;
     return;
   }
+  inv = 1.0f / denom; /* one IEEE reciprocal per block, then one multiply per element */
   for (j = 0; j < 8; ++j) {
-    uint8_t lo = fo_e2m1_encode(v[2 * j] / denom);
-    uint8_t hi = fo_e2m1_encode(v[2 * j + 1] / denom);
+    uint8_t lo = fo_e2m1_encode(v[2 * j] * inv);
+    uint8_t hi = fo_e2m1_encode(v[2 * j + 1] * inv);
     codes8[j] = (uint8_t)(lo | (hi << 4));
   }
   *scale_code = sc;

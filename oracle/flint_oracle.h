@@ -45,15 +45,17 @@ void fo_quantize_fp8_tensor(const float *w, int64_t numel, uint8_t *codes, float
 /* The same rule applied to each row on its own (one fp32 scale per output channel). */
 void fo_quantize_fp8_rows(const float *w, int rows, int k, uint8_t *codes, float *scales);
 /* Dynamic per-token quantisation of a 16-bit activation (is_bf16: 1 bf16, 0 fp16):
- * amax over the row in fp32, scale = amax/448, code = e4m3(x / scale); zero row -> scale 0. */
+ * amax over the row in fp32, scale = amax/448, code = e4m3(x * (1/scale)) with the reciprocal
+ * taken once per row in IEEE fp32; zero row -> scale 0, codes 0. */
 void fo_quantize_fp8_act(const uint16_t *x, int is_bf16, int rows, int k, uint8_t *codes,
                          float *scales);
 /* NVFP4 weight: g = amax/(448*6); per 16 consecutive k: s = e4m3(amax_b/(6 g)) (unsigned),
- * code = e2m1(w/(decode(s) g)); zero block -> s = 0, codes 0. codes: two per byte, low nibble
+ * code = e2m1(w * (1/(decode(s) g))), the reciprocal taken once per block in IEEE fp32; zero
+ * block -> s = 0, codes 0. codes: two per byte, low nibble
  * is the even k. block_scales (rows, k/16) row-major. k must be a multiple of 16. */
 void fo_quantize_nvfp4_weight(const float *w, int rows, int k, uint8_t *codes,
                               uint8_t *block_scales, float *global_scale);
-/* NVFP4 activation from 16-bit input, global scale 1: s = e4m3(amax_b/6), code = e2m1(x/s). */
+/* NVFP4 activation from 16-bit input, global scale 1: s = e4m3(amax_b/6), code = e2m1(x * (1/s)). */
 void fo_quantize_nvfp4_act(const uint16_t *x, int is_bf16, int rows, int k, uint8_t *codes,
                            uint8_t *block_scales);
 
