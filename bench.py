@@ -49,7 +49,11 @@ FALLBACK_BF16_TFLOPS = 1590.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch from the committed ncu captures
 # (profiles/), keyed by workload; None until a capture of that workload exists.
-NCU_TRAFFIC_BYTES = {"c2_mlp": None, "c1_linear": None, "c3_nvfp4_qkv": None}
+NCU_TRAFFIC_BYTES = {
+    "c2_mlp": (51.7e6 + 55.0e6 + 164.1e6 + 12.0e6) / 2,  # mean of the up and the down launch
+    "c1_linear": 22.1e6,                                 # the bf16 output stays dirty in L2
+    "c3_nvfp4_qkv": 24.0e6 + 25.5e6,
+}
 
 
 def flops_per_step(wl, m=None):

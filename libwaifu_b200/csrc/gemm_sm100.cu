@@ -41,9 +41,12 @@ constexpr int kEpilogueWarps = 8;
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr int kNumThreads = 320;
-// Tiles are walked in bands of this many tile columns, rows fastest inside a band, so that the
-// tiles in flight at one time share a compact set of A and B rows in L2.
+// Tiles are walked in bands of tile columns, columns fastest inside a band, so that the tiles in
+// flight at one time share a compact set of A and B rows in L2. A matrix up to kBandMax tile
+// columns wide is one band (every A row block is then fetched from HBM once); wider ones are cut
+// into bands of kBandTiles.
 constexpr int kBandTiles = 8;
+constexpr int kBandMax = 16;
 
 struct KernelParams {
   int m, n;
@@ -133,14 +136,15 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi, int is_bf16) {
   return *reinterpret_cast<uint32_t *>(&v);
 }
 
-// Tile index -> (row tile, column tile): bands of kBandTiles tile columns, rows fastest.
+// Tile index -> (row tile, column tile).
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int *tm, int *tn) {
-  const int per_band = kBandTiles * tiles_m;
+  const int band_tiles = tiles_n <= kBandMax ? tiles_n : kBandTiles;
+  const int per_band = band_tiles * tiles_m;
   const int band = tile / per_band;
   const int r = tile - band * per_band;
-  const int width = min(kBandTiles, tiles_n - band * kBandTiles);
+  const int width = min(band_tiles, tiles_n - band * band_tiles);
   *tm = r / width;
-  *tn = band * kBandTiles + (r - (*tm) * width);
+  *tn = band * band_tiles + (r - (*tm) * width);
 }
 
 template <int KIND, int BLOCK_N, int CTAS>
