@@ -279,7 +279,44 @@ def run_ours(args, wl):
         operand_sets.append((wrap(x, bf), layers, bias))
     outs = [F.Tensor.empty((m, n), bf) for (n, _) in wl["gemms"]]
 
+    nsplit = args.parallel == "nsplit"
+    if nsplit:
+        # Strong scaling of one MLP: every rank holds a slice of each weight's output channels,
+        # multiplies the whole activation by it and all-gathers the slices (H, then Y) over NCCL.
+        if not (wl["kind"] == "fp8" and len(wl["gemms"]) == 2 and dist is not None):
+            raise SystemExit("--parallel nsplit needs the c2_mlp workload and more than one GPU")
+        from libwaifu_b200 import sharding
+        (n_up, k_up), (n_dn, k_dn) = wl["gemms"]
+        up_a, up_b = sharding.column_shard(n_up, world, rank, 128)
+        dn_a, dn_b = sharding.column_shard(n_dn, world, rank, 128)
+        up_sizes = sharding.column_sizes(n_up, world, 128)
+        dn_sizes = sharding.column_sizes(n_dn, world, 128)
+        g2 = torch.Generator(device="cuda").manual_seed(77)
+        x_t = torch.randn(m, k_up, device="cuda", dtype=torch.bfloat16, generator=g2)
+        x_cols_t = x_t[:, dn_a:dn_b].contiguous()
+        w_up = torch.randn(up_b - up_a, k_up, device="cuda", dtype=torch.float32, generator=gen) * 0.02
+        w_dn = torch.randn(dn_b - dn_a, k_dn, device="cuda", dtype=torch.float32, generator=gen) * 0.02
+        up_q = F.quantize_fp8_rows(wrap(w_up, F.DType.FLOAT))
+        dn_q = F.quantize_fp8_rows(wrap(w_dn, F.DType.FLOAT))
+        F.synchronize()
+        del w_up, w_dn
+        h_loc_t = torch.empty(m, up_b - up_a, device="cuda", dtype=torch.bfloat16)
+        h_t = torch.empty(m, n_up, device="cuda", dtype=torch.bfloat16)
+        y_loc_t = torch.empty(m, dn_b - dn_a, device="cuda", dtype=torch.bfloat16)
+        y_t = torch.empty(m, n_dn, device="cuda", dtype=torch.bfloat16)
+        x_w, x_cols_w = wrap(x_t, bf), wrap(x_cols_t, bf)
+        h_loc_w, h_w, y_loc_w = wrap(h_loc_t, bf), wrap(h_t, bf), wrap(y_loc_t, bf)
+
+        def nsplit_step():
+            F.fp8_linear(x_w, up_q[0], up_q[1], None, None, F.ACT_GELU_TANH, h_loc_w)
+            sharding.all_gather_columns(dist, h_loc_t, up_sizes, h_t)
+            F.fp8_linear(h_w, dn_q[0], dn_q[1], None, x_cols_w, F.ACT_NONE, y_loc_w)
+            sharding.all_gather_columns(dist, y_loc_t, dn_sizes, y_t)
+
     def step(i, x_override=None):
+        if nsplit:
+            nsplit_step()
+            return
         x, layers, bias = operand_sets[i % sets]
         if x_override is not None:
             x = x_override
@@ -322,7 +359,8 @@ def run_ours(args, wl):
     launches = F.launch_count() - launches0
     F.synchronize()
     ms_step = max_over_ranks(ms_total / args.steps)
-    value = world * flops_per_step(wl) / (ms_step * 1e-3) / 1e12
+    work_units = 1 if nsplit else world  # nsplit: one MLP shared by all ranks (strong scaling)
+    value = work_units * flops_per_step(wl) / (ms_step * 1e-3) / 1e12
 
     # ---- the same K steps again with every GEMM launch bracketed by its own events -------------
     # (kept out of the region above: an event between two kernels stops the second from starting
@@ -365,12 +403,12 @@ def run_ours(args, wl):
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
-    e2e_value = world * flops_per_step(wl) / (e2e_ms * 1e-3) / 1e12
+    e2e_value = work_units * flops_per_step(wl) / (e2e_ms * 1e-3) / 1e12
 
     # ---- roofline of the dominant kernel (the tcgen05 GEMM), from its own events ---------------
     bf16_peak, hbm_peak, peak_kind = measured_peaks()
     peak = PEAK_MULT[wl["kind"]] * bf16_peak
-    gemm_tflops = flops_per_step(wl) * args.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+    gemm_tflops = (flops_per_step(wl) / (world if nsplit else 1)) * args.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
     traffic = NCU_TRAFFIC_BYTES.get(args.workload)
     roofline = {
         "bound": "tensor", "kernel": "gemm_tn_kernel", "achieved": gemm_tflops, "peak": peak, "unit": UNIT,
@@ -401,10 +439,12 @@ def run_ours(args, wl):
         touched = sets * (m * k0 * 2 + sum(n * k * (1 if wl["kind"] == "fp8" else 0.5625) for (n, k) in wl["gemms"]))
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if nsplit else "weak",
+            "vs_baseline": None,
             "dtype": "e4m3" if wl["kind"] == "fp8" else "e2m1", "data": "synthetic",
             "config": {"workload": args.workload, "what": wl["desc"], "m_per_gpu": m,
-                       "parallelism": f"batch-sharded x{world}, weights replicated, no collective",
+                       "parallelism": (f"weights split by output channel x{world}, NCCL all-gather of H and Y"
+                                       if nsplit else f"batch-sharded x{world}, weights replicated, no collective"),
                        "l2": f"{sets} rotating operand sets ({touched / 1e6:.0f} MB of inputs) > 126 MB L2",
                        "accumulate": "fp32", "out": "bf16"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": m * k0 * 2,
@@ -431,6 +471,9 @@ def main():
     ap.add_argument("--rows", type=int, default=None, help="override the workload's row count (for small profile captures)")
     ap.add_argument("--reference-rows", type=int, default=1088, help="rows of the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallel", default="batch", choices=["batch", "nsplit"],
+                    help="batch: rows sharded, no collective (weak scaling); nsplit: one MLP with its weights "
+                         "split by output channel and NCCL all-gathers (strong scaling)")
     args = ap.parse_args()
     wl = dict(WORKLOADS[args.workload])
     if args.rows:

@@ -75,7 +75,6 @@ struct KernelParams {
 // each CTA stages its own 128 rows of A and its own half of the BLOCK_N rows of B.
 template <int BLOCK_N, bool NVF4, int CTAS = 1>
 struct Config {
-  static_assert(CTAS == 1 || !NVF4, "the pair form is not built for the block-scaled kind");
   static_assert(BLOCK_N % 64 == 0, "each epilogue warp takes whole 32-column chunks of half a tile");
   static constexpr int kABytes = kBlockM * kRowBytes;
   static constexpr int kBRows = BLOCK_N / CTAS;
@@ -95,12 +94,15 @@ struct Config {
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kColParamOffset = kStages * kStageBytes;
   static constexpr int kSmemBytes = kColParamOffset + kColParamBytes + 1024;  // + slack to align to 1024
-  // Tensor memory columns: two accumulators, then the scale factors of one stage.
+  // Tensor memory columns: two accumulators, then the scale factors of one stage. (Neither a
+  // second set of scale-factor columns nor copying a stage ahead of its MMAs was measurably
+  // faster: the copies and the MMAs of one issuing thread execute in order.)
   static constexpr int kAccCols = 2 * BLOCK_N;
   static constexpr int kSfaCols = NVF4 ? kMmasPerStage * 4 : 0;
   static constexpr int kSfbColsPerMma = NVF4 ? kSfbGroups * 4 : 0;
   static constexpr int kSfbCols = kMmasPerStage * kSfbColsPerMma;
-  static constexpr int kUsedCols = kAccCols + kSfaCols + kSfbCols;
+  static constexpr int kSfSetCols = kSfaCols + kSfbCols;
+  static constexpr int kUsedCols = kAccCols + kSfSetCols;
   static constexpr int kTmemCols = kUsedCols <= 32 ? 32 : kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128
                                    : kUsedCols <= 256 ? 256 : 512;
   static_assert(kUsedCols <= 512, "tensor memory holds 512 columns");
@@ -150,6 +152,7 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 template <int KIND, int BLOCK_N, int CTAS>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                const KernelParams p) {
   constexpr bool NVF4 = (KIND == kKindNvf4);
   using Cfg = Config<BLOCK_N, NVF4, CTAS>;
@@ -244,6 +247,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             continue;
           }
 #endif
+          // Scale-factor tiles of this k block (NVFP4): kMmasPerStage consecutive 512-byte tiles
+          // per 128-row group, addressed as rows of a (groups * sf_k_tiles, 512 byte) matrix. A
+          // CTA loads the group of its own A rows and every group its tile's B columns touch (in
+          // a pair both CTAs need all of B's factors, since each multiplies its rows by all
+          // BLOCK_N columns).
+          const int sfa_row = (tm * CTAS + static_cast<int>(cta_rank)) * p.sf_k_tiles + kb * kMmasPerStage;
+          const int sfb_row0 = (n0 / 128) * p.sf_k_tiles + kb * kMmasPerStage;
           if constexpr (CTAS == 2) {
             // Both CTAs' bytes are counted on the leader's barrier, which the leader arms.
             if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
@@ -251,23 +261,25 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tma_load_2d_pair(stage_a(stage), &tmap_a, bar, kb * kRowBytes, m0);
             tma_load_2d_pair(stage_b(stage), &tmap_b, bar, kb * kRowBytes,
                              n0 + static_cast<int>(cta_rank) * Cfg::kBRows);
+            if constexpr (NVF4) {
+              tma_load_2d_pair(stage_sfa(stage), &tmap_sfa, bar, 0, sfa_row);
+#pragma unroll
+              for (int g = 0; g < Cfg::kSfbGroups; ++g) {
+                tma_load_2d_pair(stage_sfb(stage) + g * kMmasPerStage * kSfTileBytes, &tmap_sfb, bar, 0,
+                                 sfb_row0 + g * p.sf_k_tiles);
+              }
+            }
           } else {
             mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
             tma_load_2d(stage_a(stage), &tmap_a, &full_bar[stage], kb * kRowBytes, m0);
             tma_load_2d(stage_b(stage), &tmap_b, &full_bar[stage], kb * kRowBytes, n0);
-          }
-          if constexpr (NVF4) {
-            // Scale-factor tiles of this k block: kMmasPerStage consecutive 512-byte tiles per
-            // 128-row group.
-            const long long ktile = static_cast<long long>(kb) * kMmasPerStage;
-            const uint8_t *src_a = p.sfa + (static_cast<long long>(tm) * p.sf_k_tiles + ktile) * kSfTileBytes;
-            bulk_load_1d(stage_sfa(stage), src_a, Cfg::kSfaBytes, &full_bar[stage]);
-            const int group0 = n0 / 128;
-            for (int g = 0; g < Cfg::kSfbGroups; ++g) {
-              const uint8_t *src_b =
-                  p.sfb + (static_cast<long long>(group0 + g) * p.sf_k_tiles + ktile) * kSfTileBytes;
-              bulk_load_1d(stage_sfb(stage) + g * kMmasPerStage * kSfTileBytes, src_b,
-                           kMmasPerStage * kSfTileBytes, &full_bar[stage]);
+            if constexpr (NVF4) {
+              tma_load_2d(stage_sfa(stage), &tmap_sfa, &full_bar[stage], 0, sfa_row);
+#pragma unroll
+              for (int g = 0; g < Cfg::kSfbGroups; ++g) {
+                tma_load_2d(stage_sfb(stage) + g * kMmasPerStage * kSfTileBytes, &tmap_sfb, &full_bar[stage], 0,
+                            sfb_row0 + g * p.sf_k_tiles);
+              }
             }
           }
           if (++stage == STAGES) {
@@ -287,13 +299,47 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // e4m3 is format 0 of kind::f8f6f4; fp16 / bf16 are formats 0 / 1 of kind::f16.
       constexpr uint32_t kFmt = (KIND == kKindBF16) ? 1u : 0u;
       constexpr uint32_t idesc =
-          NVF4 ? umma_idesc_nvf4(kBlockM, BLOCK_N) : umma_idesc(kBlockM * CTAS, BLOCK_N, kFmt, kFmt);
+          NVF4 ? umma_idesc_nvf4(kBlockM * CTAS, BLOCK_N) : umma_idesc(kBlockM * CTAS, BLOCK_N, kFmt, kFmt);
       // Hands a barrier (same offset in every CTA of the pair) the completion of the UMMAs so far.
       auto commit_to = [&](uint64_t *bar) {
         if constexpr (CTAS == 2) {
           umma_commit_pair_both(bar);
         } else {
           umma_commit(bar);
+        }
+      };
+      // This loop is one thread feeding the tensor pipe, so its own instruction count is on the
+      // critical path: every descriptor is the stage-0 descriptor plus a per-stage step (only the
+      // 14-bit address field changes, and shared memory is below 2^18 bytes so it cannot carry).
+      const uint64_t adesc0 = umma_desc_sw128(smem_u32(stage_a(0)));
+      const uint64_t bdesc0 = umma_desc_sw128(smem_u32(stage_b(0)));
+      const uint64_t sfa_desc0 = NVF4 ? umma_desc_sf(smem_u32(stage_sfa(0))) : 0;
+      const uint64_t sfb_desc0 = NVF4 ? umma_desc_sf(smem_u32(stage_sfb(0))) : 0;
+      constexpr uint64_t kStageStep = Cfg::kStageBytes >> 4;
+      constexpr uint64_t kMmaStep = kMmaKBytes >> 4;
+      constexpr uint64_t kSfTileStep = kSfTileBytes >> 4;
+      // NVFP4: one stage's scale factors go shared -> tensor memory right before its MMAs.
+      auto copy_scale_factors = [&](int st) {
+        const uint64_t sfa_desc = sfa_desc0 + st * kStageStep;
+        const uint64_t sfb_desc = sfb_desc0 + st * kStageStep;
+        const uint32_t sfa_tmem = tmem_base + Cfg::kAccCols;
+        const uint32_t sfb_tmem = sfa_tmem + Cfg::kSfaCols;
+#pragma unroll
+        for (int j = 0; j < kMmasPerStage; ++j) {
+          if constexpr (CTAS == 2) {
+            tmem_cp_sf_pair(sfa_tmem + j * 4, sfa_desc + j * kSfTileStep);
+          } else {
+            tmem_cp_sf(sfa_tmem + j * 4, sfa_desc + j * kSfTileStep);
+          }
+#pragma unroll
+          for (int g = 0; g < Cfg::kSfbGroups; ++g) {
+            const uint64_t d = sfb_desc + (g * kMmasPerStage + j) * kSfTileStep;
+            if constexpr (CTAS == 2) {
+              tmem_cp_sf_pair(sfb_tmem + j * Cfg::kSfbColsPerMma + g * 4, d);
+            } else {
+              tmem_cp_sf(sfb_tmem + j * Cfg::kSfbColsPerMma + g * 4, d);
+            }
+          }
         }
       };
       int stage = 0;
@@ -303,6 +349,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
+        // A tile that starts 64 rows into a 128-row scale group reads its B scale factors two
+        // tensor-memory columns further on (32 rows per column).
+        uint32_t sfb_skip = 0;
+        if constexpr (NVF4) {
+          int tm, tn;
+          tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
+          sfb_skip = ((tn * BLOCK_N) % 128) / 32;
+        }
         if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, &abort_flag)) {
           ok = false;
           break;
@@ -315,42 +369,32 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             break;
           }
           tc_fence_after_sync();
-          const uint64_t adesc = umma_desc_sw128(smem_u32(stage_a(stage)));
-          const uint64_t bdesc = umma_desc_sw128(smem_u32(stage_b(stage)));
+          const uint64_t adesc = adesc0 + stage * kStageStep;
+          const uint64_t bdesc = bdesc0 + stage * kStageStep;
           if constexpr (NVF4) {
             const uint32_t sfa_tmem = tmem_base + Cfg::kAccCols;
             const uint32_t sfb_tmem = sfa_tmem + Cfg::kSfaCols;
-            const uint32_t sfa_smem = smem_u32(stage_sfa(stage));
-            const uint32_t sfb_smem = smem_u32(stage_sfb(stage));
+#ifdef FLSM100_PROBE
+            if (!(p.probe & 8))  // timing probe: no scale-factor copies
+#endif
+              copy_scale_factors(stage);
 #pragma unroll
             for (int j = 0; j < kMmasPerStage; ++j) {
-              tmem_cp_sf(sfa_tmem + j * 4, umma_desc_sf(sfa_smem + j * kSfTileBytes));
-#pragma unroll
-              for (int g = 0; g < Cfg::kSfbGroups; ++g) {
-                tmem_cp_sf(sfb_tmem + j * Cfg::kSfbColsPerMma + g * 4,
-                           umma_desc_sf(sfb_smem + (g * kMmasPerStage + j) * kSfTileBytes));
+              if constexpr (CTAS == 2) {
+                umma_nvf4_ss_pair(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, (kb | j) != 0 ? 1u : 0u,
+                                  sfa_tmem + j * 4, sfb_tmem + j * Cfg::kSfbColsPerMma + sfb_skip);
+              } else {
+                umma_nvf4_ss(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, (kb | j) != 0 ? 1u : 0u,
+                             sfa_tmem + j * 4, sfb_tmem + j * Cfg::kSfbColsPerMma + sfb_skip);
               }
-            }
-            // A tile that starts 64 rows into a 128-row group reads its scale factors two
-            // columns further on (32 rows per column).
-            int tm, tn;
-            tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
-            const uint32_t sfb_skip = ((tn * BLOCK_N) % 128) / 32;
-#pragma unroll
-            for (int j = 0; j < kMmasPerStage; ++j) {
-              umma_nvf4_ss(d_tmem, adesc + j * (kMmaKBytes >> 4), bdesc + j * (kMmaKBytes >> 4), idesc,
-                           (kb | j) != 0 ? 1u : 0u, sfa_tmem + j * 4,
-                           sfb_tmem + j * Cfg::kSfbColsPerMma + sfb_skip);
             }
           } else {
 #pragma unroll
             for (int j = 0; j < kMmasPerStage; ++j) {
               if constexpr (CTAS == 2) {
-                umma_ss_pair<KIND>(d_tmem, adesc + j * (kMmaKBytes >> 4), bdesc + j * (kMmaKBytes >> 4), idesc,
-                                   (kb | j) != 0 ? 1u : 0u);
+                umma_ss_pair<KIND>(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, (kb | j) != 0 ? 1u : 0u);
               } else {
-                umma_ss<KIND>(d_tmem, adesc + j * (kMmaKBytes >> 4), bdesc + j * (kMmaKBytes >> 4), idesc,
-                              (kb | j) != 0 ? 1u : 0u);
+                umma_ss<KIND>(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, (kb | j) != 0 ? 1u : 0u);
               }
             }
           }
@@ -608,6 +652,21 @@ bool make_tmap(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_b
   return r == CUDA_SUCCESS;
 }
 
+// The scale-factor tiles of one operand as a (tiles, 512 byte) matrix of 32-bit words, read in
+// boxes of kMmasPerStage tiles (the factors of one K stage of one 128-row group), unswizzled.
+bool make_tmap_sf(CUtensorMap *map, const void *base, uint64_t tiles) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {kSfTileBytes / 4, tiles};
+  cuuint64_t strides[1] = {kSfTileBytes};
+  cuuint32_t box[2] = {kSfTileBytes / 4, static_cast<cuuint32_t>(kMmasPerStage)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 template <int KIND, int BLOCK_N, int CTAS>
 cudaError_t launch_one(const GemmArgs &a, KernelParams kp, uint64_t row_bytes, const char **why) {
   using Cfg = Config<BLOCK_N, KIND == kKindNvf4, CTAS>;
@@ -617,6 +676,15 @@ cudaError_t launch_one(const GemmArgs &a, KernelParams kp, uint64_t row_bytes, c
   if (!make_tmap(&ta, a.a, a.m, row_bytes, kBlockM) || !make_tmap(&tb, a.b, a.n, row_bytes, Cfg::kBRows)) {
     *why = "cuTensorMapEncodeTiled refused the operand";
     return cudaErrorInvalidValue;
+  }
+  CUtensorMap tsfa = ta, tsfb = tb;  // only dereferenced by the block-scaled kind
+  if constexpr (KIND == kKindNvf4) {
+    const uint64_t k_tiles = static_cast<uint64_t>(a.sf_k_tiles);
+    if (!make_tmap_sf(&tsfa, a.sfa, static_cast<uint64_t>((a.m + 127) / 128) * k_tiles) ||
+        !make_tmap_sf(&tsfb, a.sfb, static_cast<uint64_t>((a.n + 127) / 128 + 1) * k_tiles)) {
+      *why = "cuTensorMapEncodeTiled refused the scale factors";
+      return cudaErrorInvalidValue;
+    }
   }
   auto kernel = gemm_tn_kernel<KIND, BLOCK_N, CTAS>;
   static bool attr_set = false;  // per instantiation
@@ -646,7 +714,7 @@ cudaError_t launch_one(const GemmArgs &a, KernelParams kp, uint64_t row_bytes, c
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, kp);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tsfa, tsfb, kp);
   if (e != cudaSuccess) *why = "kernel launch failed";
   return e;
 }
@@ -710,11 +778,17 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
   if (const char *v = std::getenv("FLSM100_PROBE")) kp.probe = std::atoi(v);
 #endif
 
-  if (a.kind == kGemmNvf4) return launch_one<kKindNvf4, 192, 1>(a, kp, row_bytes, why);
-  // A pair of CTAs per 256 x 256 tile halves the B bytes each SM pulls from L2; it needs two row
+  // A pair of CTAs per 256-row tile halves the B bytes each SM pulls from L2; it needs two row
   // blocks to share the B tile between. Narrow outputs use the narrower single-CTA tile so that
   // fewer columns of the MMA are padding.
   const bool pair = a.m > kBlockM && a.n > 128 && !a.force_single_cta;
+  if (a.kind == kGemmNvf4) {
+    if ((reinterpret_cast<uintptr_t>(a.sfa) & 15) || (reinterpret_cast<uintptr_t>(a.sfb) & 15)) {
+      *why = "scale-factor base is not 16-byte aligned";
+      return cudaErrorInvalidValue;
+    }
+    return pair ? launch_one<kKindNvf4, 192, 2>(a, kp, row_bytes, why) : launch_one<kKindNvf4, 192, 1>(a, kp, row_bytes, why);
+  }
   const bool narrow = a.n <= 128;
   switch (a.kind) {
     case kGemmE4M3:

@@ -272,6 +272,15 @@ __device__ __forceinline__ void umma_nvf4_ss(uint32_t d_tmem, uint64_t adesc, ui
       : "memory");
 }
 
+__device__ __forceinline__ void umma_nvf4_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                  uint32_t accumulate, uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+
 // Makes `bar` receive one arrival once every UMMA issued so far by this thread has finished
 // (finished reading shared memory and writing tensor memory).
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
@@ -292,6 +301,12 @@ __device__ __forceinline__ void umma_commit_pair_both(uint64_t *bar) {
 // four 32-lane quarters of tensor memory.
 __device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+// The pair form: each CTA of the pair copies from its own shared memory (same offset) into its
+// own tensor memory (same address).
+__device__ __forceinline__ void tmem_cp_sf_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 
 // ---- tcgen05: tensor memory -> registers ---------------------------------------------------

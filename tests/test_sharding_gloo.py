@@ -1,0 +1,89 @@
+"""The multi-GPU splits of the path, checked on CPU with two gloo ranks: each rank's arithmetic is
+the CPU oracle, so what is under test is the host-side sharding (ranges, gathers, layouts) that the
+GPU ranks use unchanged. Rows and output channels are independent in a quantized linear (the
+activation is quantised per row, the weight per channel), so the sharded results must equal the
+unsharded ones bit for bit."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _as_t(a16):
+    # gloo carries no 16-bit types: one 16-bit pattern per int32 for the trip
+    return torch.from_numpy(np.ascontiguousarray(a16).astype(np.int32))
+
+
+def _as_np(t):
+    return np.ascontiguousarray(t.numpy()).astype(np.uint16)
+
+
+def _worker(rank, world, port, ragged):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from libwaifu_b200 import sharding
+    from oracle import oracle as O
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(99)  # the same on every rank
+        m, k, n_up = 96, 128, (264 if ragged else 256)
+        x = O.narrow(rng.standard_normal((m, k)).astype(np.float32), True)
+        up_c, up_s = O.quantize_fp8_rows((rng.standard_normal((n_up, k)) * 0.02).astype(np.float32))
+        dn_c, dn_s = O.quantize_fp8_rows((rng.standard_normal((k, n_up)) * 0.02).astype(np.float32))
+        bias = O.narrow((rng.standard_normal(n_up) * 0.01).astype(np.float32), True)
+        h_ref = O.fp8_linear(x, up_c, up_s, bias, None, O.ACT_GELU_TANH)
+        y_ref = O.fp8_linear(h_ref, dn_c, dn_s, None, x, O.ACT_NONE)
+
+        # ---- rows: no exchange until the results are collected
+        sizes = [b - a for a, b in (sharding.row_shard(m, world, r, granule=16) for r in range(world))]
+        a, b = sharding.row_shard(m, world, rank, granule=16)
+        h_rows = O.fp8_linear(x[a:b], up_c, up_s, bias, None, O.ACT_GELU_TANH)
+        y_rows = O.fp8_linear(h_rows, dn_c, dn_s, None, x[a:b], O.ACT_NONE)
+        y_all = _as_np(sharding.gather_rows(dist, _as_t(y_rows), sizes))
+        assert np.array_equal(y_all, y_ref), "row-sharded MLP differs from the unsharded one"
+
+        # ---- output channels: all-gather after each linear
+        def linear(xt, w, s, bt, rt, act):
+            out = O.fp8_linear(_as_np(xt), w, s, None if bt is None else _as_np(bt), None if rt is None else _as_np(rt), act)
+            return _as_t(out)
+
+        up = sharding.ColumnSplitLinear(dist, n_up, linear)
+        assert sum(up.sizes) == n_up and all(s % 8 == 0 for s in up.sizes)
+        h = up.forward(_as_t(x), up.slice_of(up_c), up.slice_of(up_s), up.slice_of(_as_t(bias)), None, O.ACT_GELU_TANH)
+        assert np.array_equal(_as_np(h), h_ref), "column-split up projection differs"
+        down = sharding.ColumnSplitLinear(dist, k, linear)
+        xt = _as_t(x)
+        y = down.forward(h, down.slice_of(dn_c), down.slice_of(dn_s), None, down.columns_of(xt).contiguous(), O.ACT_NONE)
+        assert np.array_equal(_as_np(y), y_ref), "column-split down projection differs"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("ragged", [False, True])
+def test_two_ranks_match_one(ragged):
+    import torch.multiprocessing as mp
+    mp.spawn(_worker, args=(2, _free_port(), ragged), nprocs=2, join=True)
+
+
+def test_shard_ranges_cover_and_align():
+    from libwaifu_b200 import sharding
+    for m, world, g in [(4352, 8, 1), (4352 * 2, 8, 4352), (16, 3, 1), (9216, 8, 128), (12288, 7, 8)]:
+        spans = [sharding.row_shard(m, world, r, g) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == m
+        for (a0, b0), (a1, b1) in zip(spans, spans[1:]):
+            assert b0 == a1
+        assert all((b - a) % g == 0 for a, b in spans)
+        assert max(b - a for a, b in spans) - min(b - a for a, b in spans) <= g
+    with pytest.raises(ValueError):
+        sharding.column_shard(100, 4, 0, multiple=8)
