@@ -41,6 +41,9 @@ WORKLOADS = {
                    desc="FP8 MLP 4352x3072 -> 12288 (GELU-tanh) -> 3072 (+residual)"),
     "c1_linear": dict(m=4096, gemms=[(3072, 3072)], kind="fp8", desc="FP8 linear 4096x3072x3072 + bias"),
     "c3_nvfp4_qkv": dict(m=4352, gemms=[(9216, 3072)], kind="nvfp4", desc="NVFP4 fused-QKV 4352x9216x3072"),
+    # handled by run_mmdit(): the whole 60-block denoise step, metric "ms per MMDiT denoise step"
+    "c4_mmdit_step": dict(m=2 * 4352, gemms=[], kind="fp8",
+                          desc="60-block MMDiT denoise step, hidden 3072, 24x128 heads, MLP 12288, 256+4096 tokens, batch 2"),
 }
 
 NOMINAL_PEAK = {"fp8": 4500.0, "nvfp4": 9000.0}   # dense TFLOP/s, NVIDIA's B200 figures
@@ -379,7 +382,8 @@ def run_ours(args, wl):
     n_last = wl["gemms"][-1][0]
     host_x = F.Tensor.empty((m, k0), bf, F.Device.CUDA_HOST)
     host_y = F.Tensor.empty((m, n_last), bf, F.Device.CUDA_HOST)
-    dev_x = F.Tensor.empty((m, k0), bf)
+    dev_x = x_w if nsplit else F.Tensor.empty((m, k0), bf)
+    result = wrap(y_t, bf) if nsplit else outs[-1]
     import ctypes
     import numpy as np
     p = ctypes.c_void_p()
@@ -391,7 +395,7 @@ def run_ours(args, wl):
     def e2e_step(i):
         F.check(F.lib().fl_transfer(ops, host_x.raw(), dev_x.raw()))
         step(i, x_override=dev_x)
-        F.check(F.lib().fl_transfer(ops, outs[-1].raw(), host_y.raw()))  # synchronises
+        F.check(F.lib().fl_transfer(ops, result.raw(), host_y.raw()))  # synchronises
 
     e2e_steps = max(3, min(args.steps, 20))
     for i in range(3):
@@ -460,6 +464,105 @@ def run_ours(args, wl):
         dist.destroy_process_group()
 
 
+def run_mmdit(args):
+    """The C4 workload: ms per denoise step of the 60-block MMDiT with every linear on the FP8 path
+    (attention, norms and rotary embedding are torch). N > 1: every rank runs its own batch."""
+    import torch
+    from libwaifu_b200 import flint as F
+    from libwaifu_b200.mmdit import MMDiT, MMDiTConfig, FlintBackend
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    F.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cfg = MMDiTConfig()
+    if args.blocks:
+        cfg.blocks = args.blocks
+    model = MMDiT(cfg, FlintBackend(), seed=0)
+    g = torch.Generator(device="cuda").manual_seed(1 + rank)
+    x = torch.randn(cfg.batch, cfg.tokens, cfg.hidden, device="cuda", dtype=torch.bfloat16, generator=g)
+    temb = torch.randn(cfg.batch, cfg.hidden, device="cuda", dtype=torch.bfloat16, generator=g)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.no_grad():
+        for _ in range(args.warmup):
+            model.step(x, temb)
+        barrier()
+        sampler = ClockSampler(local)
+        sampler.start()
+        launches0 = F.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            y = model.step(x, temb)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / args.steps
+        launches = F.launch_count() - launches0
+        F.gemm_timing(True)
+        F.gemm_timing_read()
+        model.step(x, temb)
+        gemm_ms, gemm_launches = F.gemm_timing_read()
+        F.gemm_timing(False)
+        sampler.stop_flag.set()
+        sampler.join(timeout=5)
+        # end to end: the latent and timestep embedding from pinned host memory, the result back
+        hx = x.cpu().pin_memory()
+        ht = temb.cpu().pin_memory()
+        hy = torch.empty_like(hx).pin_memory()
+        for _ in range(2):
+            model.step(hx.cuda(non_blocking=True), ht.cuda(non_blocking=True))
+        barrier()
+        e0.record()
+        e2e_steps = max(2, min(args.steps, 5))
+        for _ in range(e2e_steps):
+            y = model.step(hx.cuda(non_blocking=True), ht.cuda(non_blocking=True))
+            hy.copy_(y, non_blocking=False)
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    bf16_peak, _, peak_kind = measured_peaks()
+    gemm_tflops = cfg.gemm_flops() / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+    if rank == 0:
+        line = {
+            "metric": "ms per MMDiT denoise step", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "e4m3", "data": "synthetic",
+            "config": {"workload": "c4_mmdit_step", "what": WORKLOADS["c4_mmdit_step"]["desc"], "blocks": cfg.blocks,
+                       "parallelism": f"batch-sharded x{world} (each rank its own CFG pair), weights replicated",
+                       "l2": f"{cfg.blocks} blocks x 170 MB of FP8 weights stream through the 126 MB L2 every step",
+                       "outside_the_path": "layer norm, q/k norm, rotary embedding and attention are torch bf16"},
+            "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": int(hx.numel() * 2 + ht.numel() * 2),
+                    "d2h_bytes_per_step": int(hy.numel() * 2), "steps": e2e_steps},
+            "gpu_launches": launches,
+            "clocks": sampler.summary(),
+            "roofline": {"bound": "tensor", "kernel": "gemm_tn_kernel", "achieved": gemm_tflops, "peak": 2.0 * bf16_peak,
+                         "unit": UNIT, "frac": gemm_tflops / (2.0 * bf16_peak) if gemm_tflops else None,
+                         "peak_source": f"2 x bf16 cuBLAS burst, of {peak_kind}", "launches": gemm_launches,
+                         "gemm_ms_per_step": gemm_ms, "gemm_share_of_step": gemm_ms / ms if ms else None,
+                         "traffic": None},
+            "cpu_baseline": None,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -474,7 +577,12 @@ def main():
     ap.add_argument("--parallel", default="batch", choices=["batch", "nsplit"],
                     help="batch: rows sharded, no collective (weak scaling); nsplit: one MLP with its weights "
                          "split by output channel and NCCL all-gathers (strong scaling)")
+    ap.add_argument("--blocks", type=int, default=None, help="c4_mmdit_step: run this many blocks instead of 60")
     args = ap.parse_args()
+    if args.workload == "c4_mmdit_step" and args.impl == "ours":
+        if args.steps == 1000:
+            args.steps = 10
+        return run_mmdit(args)
     wl = dict(WORKLOADS[args.workload])
     if args.rows:
         wl["m"] = args.rows

@@ -782,6 +782,10 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
   // blocks to share the B tile between. Narrow outputs use the narrower single-CTA tile so that
   // fewer columns of the MMA are padding.
   const bool pair = a.m > kBlockM && a.n > 128 && !a.force_single_cta;
+  // One row block (the skinny case: decode rows, adaLN modulation) is bound by streaming the
+  // weight from HBM, so what matters is how many SMs pull on it: 128-wide tiles give twice as
+  // many CTAs as 256-wide ones until the grid is full.
+  const bool skinny = a.m <= kBlockM && (a.n + 255) / 256 < sm_count();
   if (a.kind == kGemmNvf4) {
     if ((reinterpret_cast<uintptr_t>(a.sfa) & 15) || (reinterpret_cast<uintptr_t>(a.sfb) & 15)) {
       *why = "scale-factor base is not 16-byte aligned";
@@ -789,7 +793,7 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
     }
     return pair ? launch_one<kKindNvf4, 192, 2>(a, kp, row_bytes, why) : launch_one<kKindNvf4, 192, 1>(a, kp, row_bytes, why);
   }
-  const bool narrow = a.n <= 128;
+  const bool narrow = a.n <= 128 || skinny;
   switch (a.kind) {
     case kGemmE4M3:
       if (pair) return launch_one<kKindF8, 256, 2>(a, kp, row_bytes, why);
