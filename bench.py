@@ -282,7 +282,8 @@ def run_ours(args, wl):
         operand_sets.append((wrap(x, bf), layers, bias))
     outs = [F.Tensor.empty((m, n), bf) for (n, _) in wl["gemms"]]
 
-    nsplit = args.parallel == "nsplit"
+    nsplit = args.parallel in ("nsplit", "nsplit_push")
+    push = args.parallel == "nsplit_push"
     if nsplit:
         # Strong scaling of one MLP: every rank holds a slice of each weight's output channels,
         # multiplies the whole activation by it and all-gathers the slices (H, then Y) over NCCL.
@@ -315,6 +316,28 @@ def run_ours(args, wl):
             sharding.all_gather_columns(dist, h_loc_t, up_sizes, h_t)
             F.fp8_linear(h_w, dn_q[0], dn_q[1], None, x_cols_w, F.ACT_NONE, y_loc_w)
             sharding.all_gather_columns(dist, y_loc_t, dn_sizes, y_t)
+
+        if push:
+            # The all-gathers fused into the GEMMs: every rank's epilogue writes its column block
+            # into every rank's full-width H and Y over NVLink (peer-mapped storage), and a
+            # one-element all-reduce on the stream orders the ranks before the result is read.
+            h_own = F.Tensor.empty((m, n_up), bf)
+            y_own = F.Tensor.empty((m, n_dn), bf)
+            handles = [None] * world
+            dist.all_gather_object(handles, (F.ipc_export(h_own), F.ipc_export(y_own)))
+            h_dests, y_dests = [h_own], [y_own]
+            for r in range(world):
+                if r != rank:
+                    h_dests.append(F.ipc_import(handles[r][0], (m, n_up), bf))
+                    y_dests.append(F.ipc_import(handles[r][1], (m, n_dn), bf))
+            flag = torch.zeros(1, device="cuda", dtype=torch.float32)
+
+            def nsplit_step():  # noqa: F811
+                F.fp8_linear_scatter(x_w, up_q[0], up_q[1], h_dests, up_a, None, None, F.ACT_GELU_TANH)
+                dist.all_reduce(flag)
+                F.fp8_linear_scatter(h_own, dn_q[0], dn_q[1], y_dests, dn_a, None, x_cols_w, F.ACT_NONE)
+                dist.all_reduce(flag)
+            y_result = y_own
 
     def step(i, x_override=None):
         if nsplit:
@@ -383,7 +406,7 @@ def run_ours(args, wl):
     host_x = F.Tensor.empty((m, k0), bf, F.Device.CUDA_HOST)
     host_y = F.Tensor.empty((m, n_last), bf, F.Device.CUDA_HOST)
     dev_x = x_w if nsplit else F.Tensor.empty((m, k0), bf)
-    result = wrap(y_t, bf) if nsplit else outs[-1]
+    result = (y_own if push else wrap(y_t, bf)) if nsplit else outs[-1]
     import ctypes
     import numpy as np
     p = ctypes.c_void_p()
@@ -447,7 +470,8 @@ def run_ours(args, wl):
             "vs_baseline": None,
             "dtype": "e4m3" if wl["kind"] == "fp8" else "e2m1", "data": "synthetic",
             "config": {"workload": args.workload, "what": wl["desc"], "m_per_gpu": m,
-                       "parallelism": (f"weights split by output channel x{world}, NCCL all-gather of H and Y"
+                       "parallelism": ((f"weights split by output channel x{world}, epilogue pushes H and Y to peers over NVLink"
+                                        if push else f"weights split by output channel x{world}, NCCL all-gather of H and Y")
                                        if nsplit else f"batch-sharded x{world}, weights replicated, no collective"),
                        "l2": f"{sets} rotating operand sets ({touched / 1e6:.0f} MB of inputs) > 126 MB L2",
                        "accumulate": "fp32", "out": "bf16"},
@@ -574,7 +598,7 @@ def main():
     ap.add_argument("--rows", type=int, default=None, help="override the workload's row count (for small profile captures)")
     ap.add_argument("--reference-rows", type=int, default=1088, help="rows of the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--parallel", default="batch", choices=["batch", "nsplit"],
+    ap.add_argument("--parallel", default="batch", choices=["batch", "nsplit", "nsplit_push"],
                     help="batch: rows sharded, no collective (weak scaling); nsplit: one MLP with its weights "
                          "split by output channel and NCCL all-gathers (strong scaling)")
     ap.add_argument("--blocks", type=int, default=None, help="c4_mmdit_step: run this many blocks instead of 60")

@@ -175,6 +175,25 @@ FLAPI int32_t fl_fp8_linear_static(fl_tensor_view_t a, fl_tensor_view_t data, fl
                                    fl_tensor_view_t bias, fl_tensor_view_t residual, int32_t act,
                                    fl_tensor_view_t out);
 
+/* fl_fp8_linear() whose result lands, straight from the GEMM's epilogue, in columns
+ * [col0, col0 + rows) of each of `n_dest` (1..8) row-major matrices (..., ld): this GPU's own
+ * and, through fl_sm100_ipc_import(), its peers'. This is the all-gather of an output-channel
+ * split fused into the product: every rank multiplies by its slice of the weight and writes its
+ * column block into every rank's full-width matrix over NVLink with plain stores, tile by tile,
+ * while the main loop runs on. The caller orders the ranks afterwards (a barrier or any
+ * collective on the stream) before any of them reads the gathered matrix. ld and col0 are
+ * multiples of 8. No counterpart in the reference, which runs on one GPU
+ * (flint/cuda/cuda_operators.cc:91-96). */
+FLAPI int32_t fl_fp8_linear_scatter(fl_tensor_view_t a, fl_tensor_view_t data, fl_tensor_view_t scales,
+                                    fl_tensor_view_t bias, fl_tensor_view_t residual, int32_t act,
+                                    const fl_tensor_view_t *dests, int32_t n_dest, int32_t col0);
+
+/* Device storage shared between the processes of one box (one process per GPU): export writes
+ * the 64-byte handle of storage made by fl_tensor_data_create(FL_DEVICE_CUDA, ...); import maps
+ * another process's storage here (peer access over NVLink); fl_tensor_data_destroy() unmaps. */
+FLAPI int32_t fl_sm100_ipc_export(fl_tensor_data_t data, void *handle_out);
+FLAPI int32_t fl_sm100_ipc_import(const void *handle, fl_dtype_t dtype, int64_t numel, fl_tensor_data_t *out);
+
 /* 1 where fl_nvfp4_linear can run (the same cards as fl_fp8_available). */
 FLAPI int32_t fl_nvfp4_available(fl_device_type_t device, int32_t *out);
 

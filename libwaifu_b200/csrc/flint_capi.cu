@@ -25,6 +25,7 @@ struct fl_tensor_data_impl_t {
   fl_dtype_t dtype = FL_DTYPE_UNKNOWN;
   fl_device_type_t device = FL_DEVICE_UNKNOWN;
   bool owned = false;
+  bool ipc_mapped = false;  // another process's device storage, opened through its IPC handle
 };
 
 struct fl_tensor_view_impl_t {
@@ -410,6 +411,12 @@ AddendPlan plan_addend(const fl_tensor_view_impl_t &addend, const fl_tensor_view
 }
 
 struct Epilogue {
+  // Scatter form: the product is columns [out_col0, out_col0 + n) of matrices of pitch out_ld,
+  // `extra_out` being the peers' copies.
+  void *extra_out[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int num_extra_out = 0;
+  int64_t out_ld = 0;
+  int out_col0 = 0;
   const float *row_scale = nullptr;
   const float *col_scale = nullptr;
   int col_scale_scalar = 0;
@@ -444,6 +451,10 @@ void run_gemm(GemmKind kind, int m, int n, int k, const void *a, const void *b, 
   g.act = ep.act;
   g.out_bf16 = out_bf16;
   g.out = out;
+  for (int i = 0; i < 7; ++i) g.extra_out[i] = ep.extra_out[i];
+  g.num_extra_out = ep.num_extra_out;
+  g.out_ld = ep.out_ld;
+  g.out_col0 = ep.out_col0;
   g.status = status_word();
   g.stream = 0;
   // FLINT_SM100_SINGLE_CTA=1 keeps every GEMM on the single-CTA kernel (for A/B measurements).
@@ -622,6 +633,7 @@ int32_t fl_tensor_data_borrow(const void *data, fl_dtype_t dtype, int64_t numel,
 
 void fl_tensor_data_destroy(fl_tensor_data_t data) {
   if (!data) return;
+  if (data->ipc_mapped && data->ptr) cudaIpcCloseMemHandle(data->ptr);
   if (data->owned && data->ptr) {
     switch (data->device) {
       case FL_DEVICE_CPU: free(data->ptr); break;
@@ -847,6 +859,137 @@ int32_t fl_fp8_linear(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_v
     }
     ep.act = act;
     run_gemm(kGemmE4M3, m, rows, k, codes, w_ptr, nullptr, nullptr, ep, is_bf16, raw_ptr(out));
+    return clear_error();
+  });
+}
+
+int32_t fl_fp8_linear_scatter(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_view_t scales_h,
+                              fl_tensor_view_t bias_h, fl_tensor_view_t residual_h, int32_t act,
+                              const fl_tensor_view_t *dests, int32_t n_dest, int32_t col0) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &weight = deref(data_h);
+    const fl_tensor_view_impl_t &scales = deref(scales_h);
+    check_fp8_weight(weight, scales, /*per_channel_ok=*/true);
+    const fl_device_type_t device = device_of(weight);
+    const int rows = weight.shape[0];
+    const int k = weight.shape[1];
+    const fl_tensor_view_impl_t &a = deref(a_h);
+    check_activation(a, device, "the left operand");
+    if (a.shape.back() != k) invalid("the two operands disagree about k");
+    if (act != FL_ACT_NONE && act != FL_ACT_GELU_TANH) invalid("unknown activation");
+    if (!dests || n_dest < 1 || n_dest > kMaxGemmOutputs) {
+      invalid("scatter: between 1 and " + std::to_string(kMaxGemmOutputs) + " destinations are needed");
+    }
+    // Every destination is a contiguous (..., ld) matrix with the left operand's leading
+    // dimensions, of its type, on the device; the product lands in columns [col0, col0 + rows).
+    const fl_tensor_view_impl_t &first = deref(dests[0]);
+    if (first.shape.size() != a.shape.size()) invalid("scatter: a destination has not the left operand's rank");
+    const int64_t ld = first.shape.back();
+    if (col0 < 0 || col0 + static_cast<int64_t>(rows) > ld) invalid("scatter: the column block does not fit the destination");
+    if (ld % 8 != 0 || col0 % 8 != 0) invalid("scatter: the destination's width and the column offset are multiples of 8");
+    for (int i = 0; i < n_dest; ++i) {
+      const fl_tensor_view_impl_t &d = deref(dests[i]);
+      if (device_of(d) != device || dtype_of(d) != dtype_of(a) || !is_contiguous(d) || d.shape != first.shape) {
+        invalid("scatter: the destinations are not contiguous matrices of one shape, of the left operand's type, on the device");
+      }
+      for (size_t j = 0; j + 1 < a.shape.size(); ++j) {
+        if (d.shape[j] != a.shape[j]) invalid("scatter: a destination has not the left operand's leading dimensions");
+      }
+      if (!aligned16(raw_ptr(d))) invalid("scatter: a destination's first element is not 16-byte aligned");
+    }
+    const fl_tensor_view_impl_t *bias = bias_h ? &deref(bias_h) : nullptr;
+    const fl_tensor_view_impl_t *residual = residual_h ? &deref(residual_h) : nullptr;
+    if (bias) {
+      if (device_of(*bias) != device || dtype_of(*bias) != dtype_of(a) || numel_of(*bias) != rows || !is_contiguous(*bias)) {
+        invalid("the bias is not a contiguous (rows) vector of the product's type on the weight's device");
+      }
+    }
+    if (residual) {
+      std::vector<int32_t> shape = a.shape;
+      shape.back() = rows;
+      if (device_of(*residual) != device || dtype_of(*residual) != dtype_of(a) || !is_contiguous(*residual)) {
+        invalid("the residual is not contiguous, of the product's type, on the weight's device");
+      }
+      check_shape(*residual, shape, "the residual");
+    }
+    if (device != FL_DEVICE_CUDA) invalid("the fp8 operand is on a device with no FP8 kernels");
+    check_tiles(rows, k, 16);
+    require_kernels();
+    check_earlier_kernel_status();
+
+    const int64_t m64 = leading_rows(a);
+    if (m64 == 0) return clear_error();
+    if (m64 > INT32_MAX) invalid("the left operand has more rows than the kernels can index");
+    const int m = static_cast<int>(m64);
+    const int is_bf16 = dtype_of(a) == FL_DTYPE_BFLOAT16;
+
+    Scratch scratch;
+    const size_t codes_off = scratch.reserve(static_cast<size_t>(m) * k);
+    const size_t scales_off = scratch.reserve(static_cast<size_t>(m) * 4);
+    size_t w_off = 0;
+    const bool w_misaligned = !aligned16(raw_ptr(weight));
+    if (w_misaligned) w_off = scratch.reserve(static_cast<size_t>(rows) * k);
+    uint8_t *base = scratch.commit();
+    uint8_t *codes = base + codes_off;
+    float *row_scales = reinterpret_cast<float *>(base + scales_off);
+    cuda_check(quantize_fp8_act(raw_ptr(a), is_bf16, m, k, codes, row_scales, 0), "quantising the activation");
+    const void *w_ptr = raw_ptr(weight);
+    if (w_misaligned) {
+      cuda_check(cudaMemcpyAsync(base + w_off, w_ptr, static_cast<size_t>(rows) * k, cudaMemcpyDeviceToDevice, 0),
+                 "staging the weight");
+      w_ptr = base + w_off;
+    }
+    Epilogue ep;
+    ep.row_scale = row_scales;
+    ep.col_scale = reinterpret_cast<const float *>(raw_ptr(scales));
+    ep.col_scale_scalar = numel_of(scales) == 1 ? 1 : 0;
+    ep.bias = bias ? raw_ptr(*bias) : nullptr;
+    if (residual) {
+      ep.residual = raw_ptr(*residual);
+      ep.residual_rows = m;
+      ep.residual_ld = rows;
+    }
+    ep.act = act;
+    ep.out_ld = ld;
+    ep.out_col0 = col0;
+    for (int i = 1; i < n_dest; ++i) ep.extra_out[ep.num_extra_out++] = raw_ptr(deref(dests[i]));
+    run_gemm(kGemmE4M3, m, rows, k, codes, w_ptr, nullptr, nullptr, ep, is_bf16, raw_ptr(first));
+    return clear_error();
+  });
+}
+
+int32_t fl_sm100_ipc_export(fl_tensor_data_t data, void *handle_out) {
+  return guard([&]() -> int32_t {
+    fl_tensor_data_impl_t &d = deref(data);
+    if (!handle_out) invalid("handle_out is null");
+    if (d.device != FL_DEVICE_CUDA || !d.owned) invalid("only device storage made by fl_tensor_data_create can be exported");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is documented as 64 bytes");
+    cudaIpcMemHandle_t h;
+    cuda_check(cudaIpcGetMemHandle(&h, d.ptr), "cudaIpcGetMemHandle");
+    std::memcpy(handle_out, &h, sizeof(h));
+    return clear_error();
+  });
+}
+
+int32_t fl_sm100_ipc_import(const void *handle, fl_dtype_t dtype, int64_t numel, fl_tensor_data_t *out) {
+  return guard([&]() -> int32_t {
+    if (!handle) invalid("handle is null");
+    if (!out) invalid("out is null");
+    if (numel < 1) invalid("storage holds at least one element");
+    dtype_size(dtype);
+    require_kernels();
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof(h));
+    void *ptr = nullptr;
+    cuda_check(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+    auto *d = new fl_tensor_data_impl_t();
+    d->ptr = ptr;
+    d->numel = numel;
+    d->dtype = dtype;
+    d->device = FL_DEVICE_CUDA;
+    d->owned = false;
+    d->ipc_mapped = true;
+    *out = d;
     return clear_error();
   });
 }

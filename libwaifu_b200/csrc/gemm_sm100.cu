@@ -65,8 +65,11 @@ struct KernelParams {
   long long residual_ld;
   int act;
   int out_bf16;
-  void *out;
-  int out_vector;  // the output's base is 16-byte aligned: 16-byte stores; else 2-byte stores
+  void *out[kMaxGemmOutputs];  // destinations of every tile: one, or this GPU's and its peers' copies
+  int num_out;
+  long long out_ld;            // pitch of the destination matrices in elements
+  int out_col0;                // first destination column of this product
+  int out_vector;  // the outputs' bases are 16-byte aligned: 16-byte stores; else 2-byte stores
   uint32_t *status;
   int probe;  // development builds (-DFLSM100_PROBE) only: bit 0 skips the loads, bit 1 the epilogue
 };
@@ -462,7 +465,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const float rs_cs = rs * cs_scalar;
       const long long res_row =
           (has_res && row_ok) ? static_cast<long long>(row % p.residual_rows) * p.residual_ld : 0;
-      uint16_t *out_row = reinterpret_cast<uint16_t *>(p.out) + static_cast<long long>(row) * p.n;
+      const long long out_off = static_cast<long long>(row) * p.out_ld + p.out_col0;
       int chunks = (p.n - n0 + 31) / 32;  // chunks of this warp's half that hold a valid column
       chunks = chunks < 0 ? 0 : (chunks > HALF_CHUNKS ? HALF_CHUNKS : chunks);
       const uint32_t tacc = tmem_base + ((quarter * 32) << 16) + acc * BLOCK_N + half * HALF_N;
@@ -537,20 +540,25 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (p.probe & 4) return;  // timing probe: no stores
 #endif
         if (!row_ok) return;
-        if (out_vector) {
-          // 64 contiguous bytes of this thread's row, as four 16-byte stores.
+        // Every destination (one, or this GPU's matrix and its peers' over NVLink) gets the chunk.
+#pragma unroll 1
+        for (int d = 0; d < p.num_out; ++d) {
+          uint16_t *out_row = reinterpret_cast<uint16_t *>(p.out[d]) + out_off;
+          if (out_vector) {
+            // 64 contiguous bytes of this thread's row, as four 16-byte stores.
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (nc + g * 8 < p.n) {  // n is a multiple of 8: a group of 8 is whole or absent
-              *reinterpret_cast<uint4 *>(out_row + nc + g * 8) =
-                  make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+            for (int g = 0; g < 4; ++g) {
+              if (nc + g * 8 < p.n) {  // n is a multiple of 8: a group of 8 is whole or absent
+                *reinterpret_cast<uint4 *>(out_row + nc + g * 8) =
+                    make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+              }
             }
-          }
-        } else {
+          } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (nc + j < p.n) {
-              out_row[nc + j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffff));
+            for (int j = 0; j < 32; ++j) {
+              if (nc + j < p.n) {
+                out_row[nc + j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffff));
+              }
             }
           }
         }
@@ -770,8 +778,18 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
   kp.residual_ld = a.residual_ld;
   kp.act = a.act;
   kp.out_bf16 = a.out_bf16;
-  kp.out = a.out;
-  kp.out_vector = (reinterpret_cast<uintptr_t>(a.out) & 15) == 0 ? 1 : 0;
+  kp.num_out = 0;
+  kp.out[kp.num_out++] = a.out;
+  for (int i = 0; i < a.num_extra_out && kp.num_out < kMaxGemmOutputs; ++i) {
+    if (a.extra_out[i]) kp.out[kp.num_out++] = a.extra_out[i];
+  }
+  for (int i = kp.num_out; i < kMaxGemmOutputs; ++i) kp.out[i] = nullptr;
+  kp.out_ld = a.out_ld > 0 ? a.out_ld : a.n;
+  kp.out_col0 = a.out_ld > 0 ? a.out_col0 : 0;
+  kp.out_vector = (kp.out_ld % 8 == 0 && kp.out_col0 % 8 == 0) ? 1 : 0;
+  for (int i = 0; i < kp.num_out; ++i) {
+    if (reinterpret_cast<uintptr_t>(kp.out[i]) & 15) kp.out_vector = 0;
+  }
   kp.status = a.status;
   kp.probe = 0;
 #ifdef FLSM100_PROBE

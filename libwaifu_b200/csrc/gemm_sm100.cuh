@@ -18,6 +18,8 @@ enum GemmKind : int {
 
 enum Activation : int { kActNone = 0, kActGeluTanh = 1 };
 
+constexpr int kMaxGemmOutputs = 8;
+
 // Status words the kernels write when a bounded wait runs out.
 enum : uint32_t {
   kStatusOk = 0,
@@ -50,7 +52,15 @@ struct GemmArgs {
   int64_t residual_ld;
   int act;
   int out_bf16;                // 1 bf16, 0 fp16
-  void *out;                   // (m, n), pitch n
+  void *out;                   // (m, n), pitch n -- or, with out_ld != 0, columns [out_col0, out_col0 + n)
+                               // of a row-major matrix of pitch out_ld
+  // Scatter form (the fused all-gather of an output-channel split): up to kMaxGemmOutputs
+  // matrices of the same pitch, this GPU's own and its peers' (peer-mapped device memory), each
+  // of which receives the tile from the epilogue with plain stores. extra_out[i] may be NULL.
+  void *extra_out[7];
+  int num_extra_out;
+  int64_t out_ld;              // 0: pitch n
+  int out_col0;
   uint32_t *status;            // device word, zeroed by the caller; non-zero after a failed wait
   int force_single_cta;        // 1: never pair CTAs (for tests that compare the two forms)
   cudaStream_t stream;

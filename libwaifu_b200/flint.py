@@ -101,6 +101,10 @@ def lib() -> ctypes.CDLL:
     L.fl_nvfp4_linear.argtypes = [V, V, V, V, V, V, c_int32, V]
     L.fl_fp8_linear_static.argtypes = [V, V, V, V, V, c_int32, V]
     L.fl_fp8_linear_static.restype = c_int32
+    L.fl_fp8_linear_scatter.argtypes = [V, V, V, V, V, c_int32, POINTER(V), c_int32, c_int32]
+    L.fl_fp8_linear_scatter.restype = c_int32
+    L.fl_sm100_ipc_export.argtypes = [V, V]; L.fl_sm100_ipc_export.restype = c_int32
+    L.fl_sm100_ipc_import.argtypes = [V, c_int32, c_int64, POINTER(V)]; L.fl_sm100_ipc_import.restype = c_int32
     L.fl_quantize_fp8_rows.argtypes = [V, V, V]
     L.fl_quantize_fp8_activation.argtypes = [V, V, V]
     L.fl_quantize_nvfp4.argtypes = [V, V, V, V]
@@ -382,6 +386,31 @@ def fp8_linear_static(a: Tensor, weight: Tensor, scales: Tensor, bias: Optional[
     check(lib().fl_fp8_linear_static(a.raw(), weight.raw(), scales.raw(), bias.raw() if bias else None,
                                      residual.raw() if residual else None, int(act), out.raw()))
     return out
+
+
+def fp8_linear_scatter(a: Tensor, weight: Tensor, scales: Tensor, dests: Sequence[Tensor], col0: int,
+                       bias: Optional[Tensor] = None, residual: Optional[Tensor] = None, act: int = ACT_NONE) -> None:
+    """fp8_linear whose result is written by the epilogue into columns [col0, col0 + rows) of every
+    matrix in `dests` (this GPU's and its peers'): the fused all-gather of an output-channel split."""
+    arr = (c_void_p * len(dests))(*[d.raw() for d in dests])
+    check(lib().fl_fp8_linear_scatter(a.raw(), weight.raw(), scales.raw(), bias.raw() if bias else None,
+                                      residual.raw() if residual else None, int(act), arr, len(dests), int(col0)))
+
+
+def ipc_export(t: Tensor) -> bytes:
+    """The 64-byte handle of a device tensor made by Tensor.empty(), for a peer process."""
+    buf = ctypes.create_string_buffer(64)
+    check(lib().fl_sm100_ipc_export(t._data, buf))
+    return bytes(buf.raw)
+
+
+def ipc_import(handle: bytes, shape: Sequence[int], dtype: int) -> Tensor:
+    """Maps a peer process's device tensor (same box) from its handle."""
+    numel = int(np.prod(shape))
+    data = c_void_p()
+    buf = ctypes.create_string_buffer(handle, 64)
+    check(lib().fl_sm100_ipc_import(buf, dtype, max(numel, 1), byref(data)))
+    return Tensor._over(data, shape, _contiguous_strides(shape), 0, dtype, Device.CUDA, True)
 
 
 def nvfp4_linear(a: Tensor, codes: Tensor, block_scales: Tensor, global_scale: Tensor,
