@@ -107,6 +107,16 @@ FLAPI void fl_tensor_view_destroy(fl_tensor_view_t view);
 /* flint/capi.h:254. Contiguous src -> contiguous dest on another device, same shape and dtype. */
 FLAPI int32_t fl_transfer(fl_operators_t operators, fl_tensor_view_t src, fl_tensor_view_t dest);
 
+/* flint/capi.h:440-446 and 448-456, for the linear-layer case only: a <float16|bfloat16>(..., k)
+ * contiguous, b (k, n) the transposed view (strides 1, k) of a contiguous (n, k) weight of the
+ * same type -- what an unquantised Linear passes (waifu/src/layers.rs:230-246) -- out (..., n);
+ * n and k multiples of 8. fl_matmul_add adds a bias (n) or a residual broadcast over out's leading
+ * dimensions to the fp32 sum, one rounding (flint/capi.h:448-452). Float32 operands, batched or
+ * row-major right operands are not implemented here and are refused with FL_ERROR_INVALID_ARG. */
+FLAPI int32_t fl_matmul(fl_operators_t operators, fl_tensor_view_t a, fl_tensor_view_t b, fl_tensor_view_t out);
+FLAPI int32_t fl_matmul_add(fl_operators_t operators, fl_tensor_view_t a, fl_tensor_view_t b, fl_tensor_view_t addend,
+                            fl_tensor_view_t out);
+
 /* flint/capi.h:458-460, flint/capi.cc:1039-1045. 1 for FL_DEVICE_CUDA on compute capability 10.x,
  * 0 for every other device or card, never an error for a missing device. */
 FLAPI int32_t fl_fp8_available(fl_device_type_t device, int32_t *out);

@@ -788,6 +788,87 @@ int32_t fl_fp8_matmul_add(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tens
   });
 }
 
+int32_t fl_matmul_add(fl_operators_t operators, fl_tensor_view_t a_h, fl_tensor_view_t b_h, fl_tensor_view_t addend_h,
+                      fl_tensor_view_t out_h);
+
+int32_t fl_matmul(fl_operators_t operators, fl_tensor_view_t a, fl_tensor_view_t b, fl_tensor_view_t out) {
+  return fl_matmul_add(operators, a, b, nullptr, out);
+}
+
+// The linear-layer case of flint's matmul on 16-bit operands: `b` is the transposed view of a
+// weight stored (n, k) row-major, which is how an unquantised Linear hands its weight over
+// (waifu/src/layers.rs:230-246). Other operand layouts of the reference's matmul are not served by
+// this library and are refused as such.
+int32_t fl_matmul_add(fl_operators_t operators, fl_tensor_view_t a_h, fl_tensor_view_t b_h, fl_tensor_view_t addend_h,
+                      fl_tensor_view_t out_h) {
+  return guard([&]() -> int32_t {
+    if (!operators) invalid("operators is null");
+    const fl_tensor_view_impl_t &a = deref(a_h);
+    const fl_tensor_view_impl_t &b = deref(b_h);
+    const fl_tensor_view_impl_t &out = deref(out_h);
+    if (numel_of(a) == 0) invalid("the left operand is empty");
+    if (numel_of(b) == 0) invalid("the right operand is empty");
+    for (const fl_tensor_view_impl_t *v : {&a, &b, &out}) {
+      if (device_of(*v) != FL_DEVICE_CUDA) invalid("an operand is not on the operators' device");
+    }
+    if (!is_half_type(dtype_of(a)) || dtype_of(b) != dtype_of(a) || dtype_of(out) != dtype_of(a)) {
+      invalid("matmul: this library multiplies <float16> or <bfloat16> operands of one type");
+    }
+    if (a.shape.size() < 2 || !is_contiguous(a)) invalid("matmul: the left operand is not a contiguous (..., k)");
+    if (b.shape.size() != 2) invalid("matmul: this library takes a two-dimensional right operand");
+    const int k = b.shape[0], n = b.shape[1];
+    if (a.shape.back() != k) invalid("the two operands disagree about k");
+    // (k, n) with strides (1, k): the transpose of a contiguous (n, k) weight.
+    const bool k_major = (b.stride[0] == 1 || k == 1) && (b.stride[1] == k || n == 1);
+    if (!k_major) {
+      invalid("matmul: the right operand is not the transposed view of a contiguous (n, k) weight; "
+              "other layouts are not implemented in this library");
+    }
+    if (!is_contiguous(out)) invalid("out is not contiguous");
+    std::vector<int32_t> shape = a.shape;
+    shape.back() = n;
+    check_shape(out, shape, "out");
+    if (n % 8 != 0 || k % 8 != 0) invalid("matmul: n and k are multiples of 8 in this library");
+    const fl_tensor_view_impl_t *addend = addend_h ? &deref(addend_h) : nullptr;
+    if (addend) {
+      if (device_of(*addend) != FL_DEVICE_CUDA || dtype_of(*addend) != dtype_of(out) ||
+          addend->shape.size() > out.shape.size()) {
+        invalid("the addend is not of out's type on the device, of out's shape");
+      }
+    }
+    require_kernels();
+    check_earlier_kernel_status();
+    const int64_t m64 = leading_rows(a);
+    if (m64 > INT32_MAX) invalid("the left operand has more rows than the kernels can index");
+    const int m = static_cast<int>(m64);
+    const int is_bf16 = dtype_of(a) == FL_DTYPE_BFLOAT16;
+
+    Scratch scratch;
+    size_t a_off = 0, b_off = 0;
+    const bool a_misaligned = !aligned16(raw_ptr(a));
+    const bool b_misaligned = !aligned16(raw_ptr(b));
+    if (a_misaligned) a_off = scratch.reserve(static_cast<size_t>(m) * k * 2);
+    if (b_misaligned) b_off = scratch.reserve(static_cast<size_t>(n) * k * 2);
+    AddendResolver res;
+    res.prepare(addend, out, &scratch);
+    uint8_t *base = scratch.used ? scratch.commit() : nullptr;
+    const void *a_ptr = raw_ptr(a);
+    const void *b_ptr = raw_ptr(b);
+    if (a_misaligned) {
+      cuda_check(cudaMemcpyAsync(base + a_off, a_ptr, static_cast<size_t>(m) * k * 2, cudaMemcpyDeviceToDevice, 0), "staging");
+      a_ptr = base + a_off;
+    }
+    if (b_misaligned) {
+      cuda_check(cudaMemcpyAsync(base + b_off, b_ptr, static_cast<size_t>(n) * k * 2, cudaMemcpyDeviceToDevice, 0), "staging");
+      b_ptr = base + b_off;
+    }
+    Epilogue ep;
+    res.resolve(base, m, n, &ep);
+    run_gemm(is_bf16 ? kGemmBF16 : kGemmF16, m, n, k, a_ptr, b_ptr, nullptr, nullptr, ep, is_bf16, raw_ptr(out));
+    return clear_error();
+  });
+}
+
 // ============================ Part 2 ==========================================================
 
 int32_t fl_fp8_linear(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_view_t scales_h,

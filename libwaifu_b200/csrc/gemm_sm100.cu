@@ -1,7 +1,7 @@
 // The sm_100a GEMM kernels behind flint's quantized matmul (replaces the CUTLASS 2.x Sm80
 // mma.sync kernel of flint/cuda/gemm_fp8_cutlass.cu:94-197,267-305).
 //
-// One persistent CTA per SM (or one pair of CTAs per two SMs), ten warps:
+// One persistent CTA per SM (or one pair of CTAs per two SMs), twelve warps:
 //   warps 0-7  epilogue: tensor memory -> registers -> scale/bias/GELU/residual -> 16-bit stores.
 //              Warp w reads the 32 accumulator rows of lane quarter (w & 3) and the column half
 //              (w >> 2) of the tile.
@@ -10,6 +10,9 @@
 //   warp  9    MMA: one thread issues tcgen05.mma on the staged tiles, accumulating in tensor
 //              memory; tcgen05.commit hands stages back to the producer and finished
 //              accumulators to the epilogue
+//   warps 10-11 pushers, only at work in the scatter form (a product gathered on several GPUs):
+//              once the epilogue has written a tile into this GPU's matrix they copy its rows to
+//              the peers' matrices, 512 contiguous bytes per store instruction, over NVLink
 // The accumulator is double-buffered in tensor memory so the epilogue of tile i overlaps the
 // main loop of tile i+1.
 //
@@ -40,7 +43,9 @@ constexpr int kSfTileBytes = 512;       // 128 rows x 4 scale factors
 constexpr int kEpilogueWarps = 8;
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
-constexpr int kNumThreads = 320;
+constexpr int kPusherWarp0 = 10;
+constexpr int kPusherWarps = 2;
+constexpr int kNumThreads = 384;
 // Tiles are walked in bands of tile columns, columns fastest inside a band, so that the tiles in
 // flight at one time share a compact set of A and B rows in L2. A matrix up to kBandMax tile
 // columns wide is one band (every A row block is then fetched from HBM once); wider ones are cut
@@ -174,12 +179,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
   __shared__ __align__(8) uint64_t acc_full_bar[2];
   __shared__ __align__(8) uint64_t acc_empty_bar[2];
+  __shared__ __align__(8) uint64_t tile_done_bar[2];  // epilogue -> pushers: the tile is in this GPU's matrix
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile uint32_t abort_flag;
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
+  const bool scatter = p.num_out > 1;
 #ifdef FLSM100_PROBE
   long long probe_c0 = 0;
   unsigned long long probe_t0 = 0;
@@ -197,7 +204,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&acc_full_bar[s], 1);
-      mbar_init(&acc_empty_bar[s], kEpilogueWarps * CTAS);  // in a pair both CTAs' epilogues report to the leader
+      // In a pair both CTAs' epilogues report to the leader. In the scatter form the pushers hold
+      // the accumulator too, which keeps the epilogue from running two tiles ahead of them.
+      mbar_init(&acc_empty_bar[s], (kEpilogueWarps + (scatter ? kPusherWarps : 0)) * CTAS);
+      mbar_init(&tile_done_bar[s], kEpilogueWarps);
     }
     fence_barrier_init();
   }
@@ -415,6 +425,64 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         atomicCAS(p.status, 0u, static_cast<uint32_t>(kStatusMmaTimeout));
       }
     }
+  } else if (warp >= kPusherWarp0) {
+    // ------------------------------------------------------------------ pushers (scatter form)
+    if (scatter && p.out_vector) {
+      bool ok = true;
+      int local = 0;
+      const int pw = static_cast<int>(warp) - kPusherWarp0;
+      const int col = static_cast<int>(lane) * 8;  // 8 elements = 16 bytes per lane, 512 bytes per row per warp
+      for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
+        const int m0 = tm * (kBlockM * CTAS) + static_cast<int>(cta_rank) * kBlockM;
+        const int n0 = tn * BLOCK_N;
+        if (!mbar_wait(&tile_done_bar[acc], acc_phase, &abort_flag)) {
+          ok = false;
+          break;
+        }
+        const bool col_ok = col < BLOCK_N && n0 + col < p.n;
+        constexpr int kRowsInFlight = 8;
+#pragma unroll 1
+        for (int r0 = pw * kRowsInFlight; r0 < kBlockM; r0 += kPusherWarps * kRowsInFlight) {
+          uint4 q[kRowsInFlight];
+          bool live[kRowsInFlight];
+#pragma unroll
+          for (int i = 0; i < kRowsInFlight; ++i) {
+            const int row = m0 + r0 + i;
+            live[i] = col_ok && row < p.m;
+            if (live[i]) {
+              const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.out[0]) +
+                                                                 static_cast<long long>(row) * p.out_ld + p.out_col0 + n0 + col);
+              q[i] = __ldcg(src);  // from L2, where the epilogue's stores are
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < kRowsInFlight; ++i) {
+            if (live[i]) {
+              const long long off = static_cast<long long>(m0 + r0 + i) * p.out_ld + p.out_col0 + n0 + col;
+              for (int d = 1; d < p.num_out; ++d) {
+                *reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(p.out[d]) + off) = q[i];
+              }
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CTAS == 2) {
+            mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[acc]), 0));
+          } else {
+            mbar_arrive(&acc_empty_bar[acc]);
+          }
+        }
+      }
+      if (!ok && lane == 0) {
+        abort_flag = 1;
+        atomicCAS(p.status, 0u, static_cast<uint32_t>(kStatusEpilogueTimeout));
+      }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue
     constexpr int HALF_N = Cfg::kHalfN;
@@ -540,10 +608,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (p.probe & 4) return;  // timing probe: no stores
 #endif
         if (!row_ok) return;
-        // Every destination (one, or this GPU's matrix and its peers' over NVLink) gets the chunk.
-#pragma unroll 1
-        for (int d = 0; d < p.num_out; ++d) {
-          uint16_t *out_row = reinterpret_cast<uint16_t *>(p.out[d]) + out_off;
+        // (In the scatter form the peers' copies are made by the pusher warps from this one.)
+        {
+          uint16_t *out_row = reinterpret_cast<uint16_t *>(p.out[0]) + out_off;
           if (out_vector) {
             // 64 contiguous bytes of this thread's row, as four 16-byte stores.
 #pragma unroll
@@ -584,8 +651,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
       }
       tc_fence_before_sync();
+      if (scatter) __threadfence();  // the tile's stores are visible before the pushers are told
       __syncwarp();
       if (lane == 0) {
+        if (scatter) mbar_arrive(&tile_done_bar[acc]);
         if constexpr (CTAS == 2) {
           mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[acc]), 0));
         } else {
@@ -789,6 +858,10 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
   kp.out_vector = (kp.out_ld % 8 == 0 && kp.out_col0 % 8 == 0) ? 1 : 0;
   for (int i = 0; i < kp.num_out; ++i) {
     if (reinterpret_cast<uintptr_t>(kp.out[i]) & 15) kp.out_vector = 0;
+  }
+  if (kp.num_out > 1 && !kp.out_vector) {
+    *why = "scatter destinations need 16-byte aligned bases and a pitch and column offset that are multiples of 8";
+    return cudaErrorInvalidValue;
   }
   kp.status = a.status;
   kp.probe = 0;

@@ -96,6 +96,8 @@ def lib() -> ctypes.CDLL:
     L.fl_fp8_available.argtypes = [c_int32, POINTER(c_int32)]
     L.fl_nvfp4_available.argtypes = [c_int32, POINTER(c_int32)]
     L.fl_fp8_matmul.argtypes = [V, V, V, V]
+    L.fl_matmul.argtypes = [V, V, V, V]; L.fl_matmul.restype = c_int32
+    L.fl_matmul_add.argtypes = [V, V, V, V, V]; L.fl_matmul_add.restype = c_int32
     L.fl_fp8_matmul_add.argtypes = [V, V, V, V, V]
     L.fl_fp8_linear.argtypes = [V, V, V, V, V, c_int32, V]
     L.fl_nvfp4_linear.argtypes = [V, V, V, V, V, V, c_int32, V]
@@ -341,6 +343,20 @@ def _broadcast_to(addend: Tensor, out: Tensor) -> Tensor:
         else:
             raise FlintError(FL_ERROR_INVALID_ARG, f"fp8_matmul_add: {ashape} does not broadcast to {oshape}")
     return addend.view_as(shape, stride, 0)
+
+
+def linear_16(a: Tensor, weight: Tensor, addend: Optional[Tensor] = None) -> Tensor:
+    """An unquantised linear layer as the reference's graph spells it (waifu/src/layers.rs:230-246):
+    matmul (or matmul_add) of `a` (..., k) by the transposed view of `weight` (n, k)."""
+    n, k = weight.shape
+    wt = weight.view_as((k, n), (1, k), 0)
+    out = Tensor.empty(tuple(a.shape[:-1]) + (n,), a.dtype, Device.CUDA)
+    if addend is None:
+        check(lib().fl_matmul(operators(), a.raw(), wt.raw(), out.raw()))
+    else:
+        ad = _broadcast_to(addend, out)  # held in a name: the view has to outlive the call
+        check(lib().fl_matmul_add(operators(), a.raw(), wt.raw(), ad.raw(), out.raw()))
+    return out
 
 
 def fp8_matmul(a: Tensor, weight: Tensor, scale: Tensor) -> Tensor:
