@@ -16,6 +16,7 @@
 
 #include "gemm_sm100.cuh"
 #include "quant_sm100.cuh"
+#include "skinny_sm100.cuh"
 
 using namespace flsm100;
 
@@ -760,6 +761,28 @@ int32_t fl_fp8_matmul_add(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tens
     const int m = static_cast<int>(m64);
     const int is_bf16 = dtype_of(a) == FL_DTYPE_BFLOAT16;
 
+    // A handful of rows (the reference's decode shape): one bandwidth-shaped launch that widens
+    // the weight in registers, with no scratch. An addend no epilogue can index goes the long way.
+    {
+      static const bool no_skinny = []() {
+        const char *v = std::getenv("FLINT_SM100_NO_SKINNY");
+        return v && v[0] == '1';
+      }();
+      AddendPlan quick;
+      std::vector<int32_t> bs;
+      std::vector<int64_t> bt;
+      if (addend) quick = plan_addend(*addend, out, &bs, &bt);
+      if (!no_skinny && !quick.needs_expand &&
+          skinny_upcast_supported(m, rows, k, raw_ptr(a), raw_ptr(weight), raw_ptr(out))) {
+        cuda_check(skinny_upcast_matmul(raw_ptr(a), is_bf16, m, rows, k, raw_ptr(weight),
+                                        reinterpret_cast<const float *>(raw_ptr(scale)), quick.bias, quick.residual,
+                                        quick.residual_rows, quick.residual_ld, raw_ptr(out), 0),
+                   "skinny FP8 matmul");
+        ++g_gemm_launches;
+        return clear_error();
+      }
+    }
+
     // The weight is widened to the activation's 16-bit type (exactly) into scratch, then
     // multiplied by the 16-bit tcgen05 kernel; the scale and the addend go into the epilogue.
     Scratch scratch;
@@ -910,6 +933,22 @@ int32_t fl_fp8_linear(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_v
     if (m64 > INT32_MAX) invalid("the left operand has more rows than the kernels can index");
     const int m = static_cast<int>(m64);
     const int is_bf16 = dtype_of(a) == FL_DTYPE_BFLOAT16;
+
+    // A handful of rows: one bandwidth-shaped launch that quantises, streams the weight once and
+    // applies the epilogue, with no scratch at all.
+    static const bool no_skinny = []() {
+      const char *v = std::getenv("FLINT_SM100_NO_SKINNY");
+      return v && v[0] == '1';
+    }();
+    if (!no_skinny && skinny_fp8_supported(m, rows, k, raw_ptr(a), raw_ptr(weight), raw_ptr(out))) {
+      cuda_check(skinny_fp8_linear(raw_ptr(a), is_bf16, m, rows, k, raw_ptr(weight),
+                                   reinterpret_cast<const float *>(raw_ptr(scales)), numel_of(scales) == 1 ? 1 : 0,
+                                   bias ? raw_ptr(*bias) : nullptr, residual ? raw_ptr(*residual) : nullptr, act,
+                                   raw_ptr(out), 0),
+                 "skinny FP8 linear");
+      ++g_gemm_launches;
+      return clear_error();
+    }
 
     Scratch scratch;
     const size_t codes_off = scratch.reserve(static_cast<size_t>(m) * k);

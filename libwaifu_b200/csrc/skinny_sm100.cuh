@@ -1,0 +1,28 @@
+// The bandwidth-shaped FP8 linear for at most 16 activation rows (see skinny_sm100.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace flsm100 {
+
+// Whether the skinny kernel takes this shape: 1..16 rows, n a multiple of 8, k of 16, the
+// quantised rows fitting shared memory, and a 16-byte aligned weight.
+bool skinny_fp8_supported(int m, int n, int k, const void *x, const void *w, const void *out);
+
+// out = round16( act( (x_q . w) * (row scale * channel scale) + bias ) + residual ), with x
+// quantised per row inside the kernel exactly as quantize_fp8_act does. One launch, no scratch.
+cudaError_t skinny_fp8_linear(const void *x, int is_bf16, int m, int n, int k, const uint8_t *w, const float *col_scale,
+                              int col_scale_scalar, const void *bias, const void *residual, int act, void *out,
+                              cudaStream_t stream);
+
+// The reference-compatible product for at most 16 rows: the activation is not narrowed, the e4m3
+// weight is widened to the activation's 16-bit type in registers, one <float> scale, an optional
+// bias (n) and/or residual rows (period residual_rows over m, pitch residual_ld) added to the fp32
+// sum, one rounding (flint/cuda/gemm_fp8_cutlass.cu:107-125).
+bool skinny_upcast_supported(int m, int n, int k, const void *x, const void *w, const void *out);
+cudaError_t skinny_upcast_matmul(const void *x, int is_bf16, int m, int n, int k, const uint8_t *w, const float *scale,
+                                 const void *bias, const void *residual, int residual_rows, int64_t residual_ld,
+                                 void *out, cudaStream_t stream);
+
+}  // namespace flsm100

@@ -217,3 +217,34 @@ def test_bf16_variant(flint, oracle):
     bias = oracle.narrow(rng.standard_normal(n).astype(np.float32), True)
     got = run(flint, a, codes, K_SCALE, bias, dtype=flint.DType.BFLOAT16)
     check_parity(oracle, got, oracle.fp8_matmul(a, codes, [K_SCALE], bias, is_bf16=True), True, what="bf16")
+
+
+@pytest.mark.parametrize("m,n,k,bf16", [(1, 16384, 3072, False), (16, 264, 3072, True), (9, 72, 12288, False),
+                                        (5, 4096, 80, True)])
+def test_few_rows(flint, oracle, m, n, k, bf16):
+    """At most 16 rows take the one-launch path that widens the weight in registers; the first
+    shape is the reference's decode benchmark (docs/fp8.md:225-244)."""
+    rng = np.random.default_rng(16 + m + n + k)
+    a = oracle.narrow(rng.standard_normal((m, k)).astype(np.float32), bf16)
+    codes = random_codes(rng, n, k)
+    dtype = flint.DType.BFLOAT16 if bf16 else flint.DType.FLOAT16
+    want = oracle.fp8_matmul(a, codes, [K_SCALE], is_bf16=bf16)
+    check_parity(oracle, run(flint, a, codes, K_SCALE, dtype=dtype), want, bf16, what=f"few rows {m}x{n}x{k}")
+    for ashape in ((n,), (m, n)):
+        addend = oracle.narrow(rng.standard_normal(ashape).astype(np.float32), bf16)
+        got = run(flint, a, codes, K_SCALE, addend, dtype=dtype, expand=False)
+        want = oracle.fp8_matmul(a, codes, [K_SCALE], addend, is_bf16=bf16)
+        check_parity(oracle, got, want, bf16, what=f"few rows {m}x{n}x{k}+{ashape}")
+
+
+def test_few_rows_in_place_residual(flint):
+    F = flint
+    m, n, k = 4, 136, 32
+    codes = np.zeros((n, k), np.uint8)
+    codes[:, 0], codes[:, 1] = 0x78, 0x20
+    a = np.zeros((m, k), np.float32)
+    a[:, 0] = a[:, 1] = 1.0
+    res = dev(F, f16(np.ones((m, n))), F.DType.FLOAT16)
+    ad, wd, sd = dev(F, f16(a), F.DType.FLOAT16), dev(F, codes, F.DType.FP8E4M3), dev(F, np.array([8.0], np.float32), F.DType.FLOAT)
+    F.check(F.lib().fl_fp8_matmul_add(ad.raw(), wd.raw(), sd.raw(), res.raw(), res.raw()))
+    assert np.all(from_f16(res.numpy()) == 2050.0)
