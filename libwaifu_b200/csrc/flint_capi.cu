@@ -773,10 +773,10 @@ int32_t fl_fp8_matmul_add(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tens
       std::vector<int64_t> bt;
       if (addend) quick = plan_addend(*addend, out, &bs, &bt);
       if (!no_skinny && !quick.needs_expand &&
-          skinny_upcast_supported(m, rows, k, raw_ptr(a), raw_ptr(weight), raw_ptr(out))) {
+          skinny_upcast_supported(m, rows, k, raw_ptr(a), raw_ptr(weight), raw_ptr(out), quick.residual != nullptr)) {
         cuda_check(skinny_upcast_matmul(raw_ptr(a), is_bf16, m, rows, k, raw_ptr(weight),
                                         reinterpret_cast<const float *>(raw_ptr(scale)), quick.bias, quick.residual,
-                                        quick.residual_rows, quick.residual_ld, raw_ptr(out), 0),
+                                        quick.residual_rows, quick.residual_ld, raw_ptr(out), status_word(), 0),
                    "skinny FP8 matmul");
         ++g_gemm_launches;
         return clear_error();
@@ -934,17 +934,18 @@ int32_t fl_fp8_linear(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_v
     const int m = static_cast<int>(m64);
     const int is_bf16 = dtype_of(a) == FL_DTYPE_BFLOAT16;
 
-    // A handful of rows: one bandwidth-shaped launch that quantises, streams the weight once and
-    // applies the epilogue, with no scratch at all.
+    // One to four rows: one bandwidth-shaped launch that quantises, streams the weight once and
+    // applies the epilogue, with no scratch at all. From five rows on, every CTA quantising all
+    // the rows for itself costs more than the separate quantiser launch of the tile path saves.
     static const bool no_skinny = []() {
       const char *v = std::getenv("FLINT_SM100_NO_SKINNY");
       return v && v[0] == '1';
     }();
-    if (!no_skinny && skinny_fp8_supported(m, rows, k, raw_ptr(a), raw_ptr(weight), raw_ptr(out))) {
+    if (!no_skinny && m <= 4 && skinny_fp8_supported(m, rows, k, raw_ptr(a), raw_ptr(weight), raw_ptr(out), residual != nullptr)) {
       cuda_check(skinny_fp8_linear(raw_ptr(a), is_bf16, m, rows, k, raw_ptr(weight),
                                    reinterpret_cast<const float *>(raw_ptr(scales)), numel_of(scales) == 1 ? 1 : 0,
                                    bias ? raw_ptr(*bias) : nullptr, residual ? raw_ptr(*residual) : nullptr, act,
-                                   raw_ptr(out), 0),
+                                   raw_ptr(out), status_word(), 0),
                  "skinny FP8 linear");
       ++g_gemm_launches;
       return clear_error();

@@ -6,23 +6,25 @@
 
 namespace flsm100 {
 
-// Whether the skinny kernel takes this shape: 1..16 rows, n a multiple of 8, k of 16, the
-// quantised rows fitting shared memory, and a 16-byte aligned weight.
-bool skinny_fp8_supported(int m, int n, int k, const void *x, const void *w, const void *out);
+// Whether the skinny kernel takes this shape: 1..16 rows, n a multiple of 8, k of 16, a 16-byte
+// aligned weight, and activation rows (and residual rows, if any) that leave shared memory for at
+// least three ring stages.
+// `status` in the calls below is the device-visible word a bounded wait that gave up reports to.
+bool skinny_fp8_supported(int m, int n, int k, const void *x, const void *w, const void *out, bool has_residual);
 
 // out = round16( act( (x_q . w) * (row scale * channel scale) + bias ) + residual ), with x
 // quantised per row inside the kernel exactly as quantize_fp8_act does. One launch, no scratch.
 cudaError_t skinny_fp8_linear(const void *x, int is_bf16, int m, int n, int k, const uint8_t *w, const float *col_scale,
                               int col_scale_scalar, const void *bias, const void *residual, int act, void *out,
-                              cudaStream_t stream);
+                              uint32_t *status, cudaStream_t stream);
 
 // The reference-compatible product for at most 16 rows: the activation is not narrowed, the e4m3
 // weight is widened to the activation's 16-bit type in registers, one <float> scale, an optional
 // bias (n) and/or residual rows (period residual_rows over m, pitch residual_ld) added to the fp32
 // sum, one rounding (flint/cuda/gemm_fp8_cutlass.cu:107-125).
-bool skinny_upcast_supported(int m, int n, int k, const void *x, const void *w, const void *out);
+bool skinny_upcast_supported(int m, int n, int k, const void *x, const void *w, const void *out, bool has_residual);
 cudaError_t skinny_upcast_matmul(const void *x, int is_bf16, int m, int n, int k, const uint8_t *w, const float *scale,
                                  const void *bias, const void *residual, int residual_rows, int64_t residual_ld,
-                                 void *out, cudaStream_t stream);
+                                 void *out, uint32_t *status, cudaStream_t stream);
 
 }  // namespace flsm100

@@ -85,6 +85,38 @@ def test_epilogue_variants(flint, oracle, act, is_bf16):
         check_parity(oracle, got, want, is_bf16, what=f"act={act} bias={bias} res={residual} pt={per_tensor}")
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 18432, 3072), (2, 264, 80), (3, 4096, 12288), (4, 72, 3088), (2, 8, 16),
+                                   (4, 1184, 592)])
+@pytest.mark.parametrize("is_bf16", [True, False])
+def test_few_rows(flint, oracle, m, n, k, is_bf16):
+    """One to four rows take the one-launch kernel that quantises the rows itself: every epilogue
+    form, k that is not a multiple of a step, a zero row, per-tensor scale."""
+    rng = np.random.default_rng(51 + m + n + k)
+    for act, bias, residual, per_tensor in [(0, False, False, False), (1, True, False, False), (0, True, True, True),
+                                            (1, False, True, False)]:
+        x, codes, scales, b, r = make_case(oracle, rng, m, n, k, is_bf16, bias, residual, per_tensor)
+        if m > 1:
+            x[m - 1] = 0
+        got = run(flint, x, codes, scales, b, r, act, is_bf16)
+        want = oracle.fp8_linear(x, codes, scales, b, r, act, is_bf16)
+        check_parity(oracle, got, want, is_bf16, what=f"few rows {m}x{n}x{k} act={act} bias={bias} res={residual}")
+
+
+def test_few_rows_match_the_tile_path_quantiser(flint, oracle):
+    """The in-kernel quantiser of the few-row kernel is the activation quantiser's arithmetic: with
+    a weight of exact small integers the two paths (m = 4 and the same rows inside m = 64) agree
+    to the last bit."""
+    rng = np.random.default_rng(52)
+    F = flint
+    n, k = 136, 1040
+    x = oracle.narrow(randn(rng, (64, k)), True)
+    codes = np.where(rng.random((n, k)) < 0.5, 0x38, 0xb8).astype(np.uint8)  # +-1
+    scales = np.full(n, 0.5, np.float32)
+    few = run(F, x[:4], codes, scales, None, None, 0)
+    many = run(F, x, codes, scales, None, None, 0)
+    assert np.array_equal(few, many[:4])
+
+
 def test_zero_rows_and_outliers(flint, oracle):
     rng = np.random.default_rng(41)
     x, codes, scales, b, r = make_case(oracle, rng, 96, 136, 128, bias=True)
