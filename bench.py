@@ -44,6 +44,10 @@ WORKLOADS = {
     # handled by run_mmdit(): the whole 60-block denoise step, metric "ms per MMDiT denoise step"
     "c4_mmdit_step": dict(m=2 * 4352, gemms=[], kind="fp8",
                           desc="60-block MMDiT denoise step, hidden 3072, 24x128 heads, MLP 12288, 256+4096 tokens, batch 2"),
+    # handled by run_skinny(): the reference's own decode benchmark shape (docs/fp8.md:225-244), one
+    # 16-bit activation row against an e4m3 weight through the unchanged fl_fp8_matmul; HBM-bound
+    "skinny_decode": dict(m=1, gemms=[(16384, 3072)], kind="fp8_upcast",
+                          desc="fl_fp8_matmul 1x16384x3072, fp16 activation x e4m3 weight, one scale"),
 }
 
 NOMINAL_PEAK = {"fp8": 4500.0, "nvfp4": 9000.0}   # dense TFLOP/s, NVIDIA's B200 figures
@@ -56,6 +60,7 @@ NCU_TRAFFIC_BYTES = {
     "c2_mlp": (51.7e6 + 55.0e6 + 164.1e6 + 12.0e6) / 2,  # mean of the up and the down launch
     "c1_linear": 22.1e6,                                 # the bf16 output stays dirty in L2
     "c3_nvfp4_qkv": 24.0e6 + 25.5e6,
+    "skinny_decode": 50.38e6 + 7.0e6,                    # the weight once; the writes are older dirty lines leaving L2
 }
 
 
@@ -169,11 +174,14 @@ def cpu_reference_step_factory(wl, rows):
     O.lib()
     kind = "reference" if O.have_ref() else "port"
     rng = np.random.default_rng(0)
-    x = O.narrow(rng.standard_normal((rows, wl["gemms"][0][1])).astype(np.float32), True)
+    x = O.narrow(rng.standard_normal((rows, wl["gemms"][0][1])).astype(np.float32), wl["kind"] != "fp8_upcast")
     weights = []
     for (n, k) in wl["gemms"]:
         w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
-        if wl["kind"] == "fp8":
+        if wl["kind"] == "fp8_upcast":
+            codes, scale = O.quantize_fp8_tensor(w)
+            weights.append((O.decode_e4m3(codes), scale))
+        elif wl["kind"] == "fp8":
             codes, scales = O.quantize_fp8_rows(w)
             weights.append((O.decode_e4m3(codes), scales))
         else:
@@ -181,7 +189,11 @@ def cpu_reference_step_factory(wl, rows):
             weights.append((O.decode_nvfp4(codes, sf), g))
 
     def step():
-        if wl["kind"] == "fp8":
+        if wl["kind"] == "fp8_upcast":
+            (wdec, scale), = weights
+            acc = O.gemm_f32_nt(O.widen(x, False), wdec, kind)
+            O.epilogue(acc, None, None, float(scale[0]), None, None, O.ACT_NONE, False)
+        elif wl["kind"] == "fp8":
             cur = x
             for i, (wdec, scales) in enumerate(weights):
                 xc, xs = O.quantize_fp8_act(cur, True)
@@ -587,6 +599,147 @@ def run_mmdit(args):
         dist.destroy_process_group()
 
 
+def run_skinny(args):
+    """The skinny_decode workload: one activation row against a weight too large for L2, through
+    fl_fp8_matmul. Every rank runs its own replica (the path does not shard at one row). The
+    roofline is HBM: each call has to read the weight once."""
+    import ctypes
+    import numpy as np
+    import torch
+    from libwaifu_b200 import flint as F
+    wl = WORKLOADS["skinny_decode"]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    torch.cuda.set_device(local)
+    F.set_device(local)
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl")
+        dist = dist_mod
+    m = wl["m"]
+    (n, k), = wl["gemms"]
+    sets = 4  # 4 x 50 MB of weights in rotation: nothing a call reads is left in the 126 MB L2
+    gen = torch.Generator(device="cuda").manual_seed(rank)
+
+    def wrap(t, dt):
+        return F.Tensor.from_device_ptr(t.data_ptr(), tuple(t.shape), dt, keepalive=t)
+
+    xs = [torch.randn(m, k, device="cuda", dtype=torch.float16, generator=gen) for _ in range(sets)]
+    ws = []
+    for _ in range(sets):
+        w = torch.randn(n, k, device="cuda", dtype=torch.float32, generator=gen) * 0.02
+        codes, _ = F.quantize_fp8_rows(wrap(w, F.DType.FLOAT))  # e4m3 codes of a Gaussian weight
+        ws.append(codes)
+        del w
+    F.synchronize()
+    scale = wrap(torch.full((1,), 0.02 / 448.0 * 4.0, device="cuda", dtype=torch.float32), F.DType.FLOAT)
+    out = F.Tensor.empty((m, n), F.DType.FLOAT16)
+    x_w = [wrap(x, F.DType.FLOAT16) for x in xs]
+    L = F.lib()
+
+    def step(i, x_override=None):
+        x = x_override if x_override is not None else x_w[i % sets]
+        F.check(L.fl_fp8_matmul(x.raw(), ws[i % sets].raw(), scale.raw(), out.raw()))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = F.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    e1.record()
+    barrier()
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    launches = F.launch_count() - launches0
+    F.synchronize()
+    sampler.stop_flag.set()
+    sampler.join(timeout=5)
+    value = world * flops_per_step(wl) / (ms_step * 1e-3) / 1e12
+
+    # end to end: the row from pinned host memory, the result row back to the host
+    host_x = F.Tensor.empty((m, k), F.DType.FLOAT16, F.Device.CUDA_HOST)
+    host_y = F.Tensor.empty((m, n), F.DType.FLOAT16, F.Device.CUDA_HOST)
+    dev_x = F.Tensor.empty((m, k), F.DType.FLOAT16)
+    p = ctypes.c_void_p()
+    F.check(L.fl_tensor_data_get_host_ptr(host_x._data, ctypes.byref(p)))
+    hx = np.ctypeslib.as_array(ctypes.cast(p.value, ctypes.POINTER(ctypes.c_uint16)), shape=(m * k,))
+    hx[:] = np.random.default_rng(7 + rank).standard_normal(m * k).astype(np.float16).view(np.uint16)
+    ops = F.operators()
+
+    def e2e_step(i):
+        F.check(L.fl_transfer(ops, host_x.raw(), dev_x.raw()))
+        step(i, x_override=dev_x)
+        F.check(L.fl_transfer(ops, out.raw(), host_y.raw()))  # synchronises
+
+    e2e_steps = max(3, min(args.steps, 200))
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    e0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
+
+    _, hbm_peak, peak_kind = measured_peaks()
+    alg_bytes = n * k + m * k * 2 + m * n * 2 + 4
+    achieved = alg_bytes / (ms_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "skinny_fp8_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                "frac": achieved / hbm_peak, "peak_source": f"stream copy, of {peak_kind}", "launches": launches,
+                "avg_launch_ms": ms_step, "traffic": NCU_TRAFFIC_BYTES.get("skinny_decode"),
+                "algorithmic_bytes_per_step": alg_bytes,
+                "note": "one launch per step; the launch time is the step time of the back-to-back timed region"}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cstep, kind, cores = cpu_reference_step_factory(wl, m)
+        cstep()
+        best = None
+        for _ in range(5):
+            t0 = time.perf_counter()
+            cstep()
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        cpu_baseline = {"value": flops_per_step(wl) / best / 1e12, "unit": UNIT, "cores": cores, "kind": kind,
+                        "sample": "the whole call (widen, fp32 GEMM, scale) on the host, best of 5"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 x e4m3 -> f32 accumulate", "data": "synthetic",
+            "config": {"workload": "skinny_decode", "what": wl["desc"], "parallelism": f"replicas{world}",
+                       "l2": f"{sets} rotating weights of {n * k / 1e6:.0f} MB, larger than L2 together",
+                       "published": "the reference reports 130.6 us for this shape on an RTX 5060 Ti (docs/fp8.md), other hardware"},
+            "e2e": {"value": world * flops_per_step(wl) / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": m * k * 2, "d2h_bytes_per_step": m * n * 2},
+            "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu_baseline, "clocks": sampler.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -603,6 +756,11 @@ def main():
                          "split by output channel and NCCL all-gathers (strong scaling)")
     ap.add_argument("--blocks", type=int, default=None, help="c4_mmdit_step: run this many blocks instead of 60")
     args = ap.parse_args()
+    if args.workload == "skinny_decode" and args.impl == "ours":
+        args.warmup = max(args.warmup, 3)
+        if args.steps == 1000:
+            args.steps = 20000  # 20 us a step: long enough for the clock sampler to see the run
+        return run_skinny(args)
     if args.workload == "c4_mmdit_step" and args.impl == "ours":
         if args.steps == 1000:
             args.steps = 10
