@@ -581,7 +581,7 @@ def run_mmdit(args):
             "config": {"workload": "c4_mmdit_step", "what": WORKLOADS["c4_mmdit_step"]["desc"], "blocks": cfg.blocks,
                        "parallelism": f"batch-sharded x{world} (each rank its own CFG pair), weights replicated",
                        "l2": f"{cfg.blocks} blocks x 170 MB of FP8 weights stream through the 126 MB L2 every step",
-                       "outside_the_path": "layer norm, q/k norm, rotary embedding and attention are torch bf16"},
+                       "outside_the_path": "attention (torch SDPA, bf16) and the SiLU of the timestep embedding"},
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": int(hx.numel() * 2 + ht.numel() * 2),
                     "d2h_bytes_per_step": int(hy.numel() * 2), "steps": e2e_steps},
             "gpu_launches": launches,

@@ -227,6 +227,37 @@ FLAPI int32_t fl_quantize_nvfp4(fl_tensor_view_t w, fl_tensor_view_t codes, fl_t
  * a <float16|bfloat16>(m, k) -> codes <fp8e4m3>(m, k), scales <float>(m). */
 FLAPI int32_t fl_quantize_fp8_activation(fl_tensor_view_t a, fl_tensor_view_t codes, fl_tensor_view_t scales);
 
+/* The step before a block's projection, fused with its quantiser (the consumer the reference
+ * builds from layer_norm, mul, add and cast nodes: waifu/src/qwen_image/dit.rs:179-184, over
+ * flint's layerNorm, flint/cpu/normalizations.cc:98-140): per row of x <float16|bfloat16>(..., k),
+ *   n = (x - mean) * (1 / sqrt(var + eps))    fp32 sums; mean = sum / k, var = sumsq / k - mean^2
+ *                                             (eps alone where that is not positive), no affine
+ *   h = round16( n * scale_g + n + shift_g )  scale, shift: (k) or (groups, k) of x's type, or
+ *                                             NULL; row r belongs to group r / (rows / groups)
+ *   codes, row_scales = per-row e4m3 of h     exactly fl_quantize_fp8_activation(h)
+ * One pass over x; h is never written. codes <fp8e4m3> of x's shape, row_scales <float>(rows). */
+FLAPI int32_t fl_fp8_layernorm_quantize(fl_tensor_view_t x, fl_tensor_view_t scale, fl_tensor_view_t shift, float eps,
+                                        fl_tensor_view_t codes, fl_tensor_view_t row_scales);
+/* fl_fp8_linear for an activation that is quantised already (by fl_fp8_layernorm_quantize or
+ * fl_quantize_fp8_activation): codes <fp8e4m3>(..., k) with row_scales <float>(rows); out
+ * <float16|bfloat16>(..., n) chooses the type of bias, residual and result. */
+FLAPI int32_t fl_fp8_linear_quantized(fl_tensor_view_t codes, fl_tensor_view_t row_scales, fl_tensor_view_t data,
+                                      fl_tensor_view_t scales, fl_tensor_view_t bias, fl_tensor_view_t residual,
+                                      int32_t act, fl_tensor_view_t out);
+
+/* The step between the fused q/k/v projection and attention, in place on the projection's output
+ * qkv <float16|bfloat16>(..., 3 * heads * head_dim) (q heads, k heads, v heads along the last
+ * dimension; head_dim 64, 128 or 256; 8-byte aligned): per row and q or k head,
+ *   n = round16( x * w * (1 / sqrt(mean(x^2) + eps)) )   flint's rmsNorm, flint/cpu/normalizations.cc:33-70,
+ *                                                   one reciprocal per head instead of a division per
+ *                                                   element; w = q_weight / k_weight (head_dim) or NULL
+ *   (n_2j, n_2j+1) <- round16( n_2j cos_j - n_2j+1 sin_j,  n_2j sin_j + n_2j+1 cos_j )
+ *                                                   waifu/src/krea2/dit.rs:260-275
+ * with cos, sin <float>(tokens, head_dim / 2) and row r at position r % tokens. v is left as it
+ * is, so attention can read q, k and v as strided views of the one buffer. */
+FLAPI int32_t fl_qk_norm_rope(fl_tensor_view_t qkv, fl_tensor_view_t q_weight, fl_tensor_view_t k_weight,
+                              fl_tensor_view_t cos, fl_tensor_view_t sin, float eps, int32_t heads);
+
 /* Storage over device memory the caller already owns (for instance a torch tensor's): nothing
  * is copied and nothing is freed on destroy. The device counterpart of fl_tensor_data_borrow(). */
 FLAPI int32_t fl_tensor_data_borrow_device(void *device_ptr, fl_dtype_t dtype, int64_t numel, fl_tensor_data_t *out);

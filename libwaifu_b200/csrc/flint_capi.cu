@@ -16,6 +16,7 @@
 
 #include "gemm_sm100.cuh"
 #include "quant_sm100.cuh"
+#include "block_sm100.cuh"
 #include "skinny_sm100.cuh"
 
 using namespace flsm100;
@@ -137,6 +138,7 @@ struct DeviceState {
 std::mutex g_mutex;
 DeviceState g_dev;
 std::atomic<int64_t> g_gemm_launches{0};
+std::atomic<int64_t> g_block_launches{0};  // kernels of block_sm100.cu
 
 // Optional per-launch timing of the GEMM kernel alone (events on the launching stream), so a
 // benchmark can separate it from the quantisation kernels launched by the same entry point.
@@ -1244,6 +1246,195 @@ int32_t fl_quantize_fp8_activation(fl_tensor_view_t a_h, fl_tensor_view_t codes_
   });
 }
 
+int32_t fl_fp8_layernorm_quantize(fl_tensor_view_t x_h, fl_tensor_view_t scale_h, fl_tensor_view_t shift_h, float eps,
+                                  fl_tensor_view_t codes_h, fl_tensor_view_t row_scales_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &x = deref(x_h);
+    const fl_tensor_view_impl_t &codes = deref(codes_h);
+    const fl_tensor_view_impl_t &row_scales = deref(row_scales_h);
+    if (!is_half_type(dtype_of(x)) || x.shape.size() < 2 || !is_contiguous(x)) {
+      invalid("x is not a contiguous <float16> or <bfloat16> tensor of at least two dimensions");
+    }
+    if (dtype_of(codes) != FL_DTYPE_FP8E4M3 || codes.shape != x.shape || !is_contiguous(codes)) {
+      invalid("codes is not a contiguous <fp8e4m3> tensor of x's shape");
+    }
+    const int64_t m64 = leading_rows(x);
+    const int k = x.shape.back();
+    if (dtype_of(row_scales) != FL_DTYPE_FLOAT || numel_of(row_scales) != m64 || !is_contiguous(row_scales)) {
+      invalid("row_scales is not a contiguous <float> tensor of one value per row of x");
+    }
+    if (!(eps >= 0.0f)) invalid("eps is negative or not a number");
+    int64_t groups = 1;
+    const fl_tensor_view_impl_t *mods[2] = {scale_h ? &deref(scale_h) : nullptr, shift_h ? &deref(shift_h) : nullptr};
+    for (const fl_tensor_view_impl_t *v : mods) {
+      if (!v) continue;
+      if (dtype_of(*v) != dtype_of(x) || v->shape.empty() || v->shape.size() > 2 || v->shape.back() != k || !is_contiguous(*v)) {
+        invalid("scale/shift is not a contiguous (k) or (groups, k) tensor of x's type");
+      }
+      const int64_t g = v->shape.size() == 2 ? v->shape[0] : 1;
+      if (groups != 1 && g != 1 && g != groups) invalid("scale and shift disagree about the number of groups");
+      if (g != 1) groups = g;
+    }
+    for (const fl_tensor_view_impl_t *v : mods) {
+      if (v && groups != 1 && (v->shape.size() == 2 ? v->shape[0] : 1) != groups) {
+        invalid("scale and shift disagree about the number of groups");
+      }
+    }
+    if (m64 > 0 && m64 % groups != 0) invalid("the rows of x do not divide into the groups of scale/shift");
+    for (const fl_tensor_view_impl_t *v : {&x, &codes, &row_scales}) {
+      if (device_of(*v) != FL_DEVICE_CUDA) invalid("the operands are not all on cuda");
+    }
+    for (const fl_tensor_view_impl_t *v : mods) {
+      if (v && device_of(*v) != FL_DEVICE_CUDA) invalid("the operands are not all on cuda");
+    }
+    require_kernels();
+    if (m64 == 0) return clear_error();
+    if (m64 > INT32_MAX) invalid("x has more rows than the kernels can index");
+    cuda_check(ln_modulate_quantize_fp8(raw_ptr(x), dtype_of(x) == FL_DTYPE_BFLOAT16, static_cast<int>(m64), k,
+                                        mods[0] ? raw_ptr(*mods[0]) : nullptr, mods[1] ? raw_ptr(*mods[1]) : nullptr,
+                                        static_cast<int>(m64 / groups), eps, raw_ptr(codes),
+                                        reinterpret_cast<float *>(raw_ptr(row_scales)), 0),
+               "layer norm and quantisation");
+    return clear_error();
+  });
+}
+
+int32_t fl_fp8_linear_quantized(fl_tensor_view_t codes_h, fl_tensor_view_t row_scales_h, fl_tensor_view_t data_h,
+                                fl_tensor_view_t scales_h, fl_tensor_view_t bias_h, fl_tensor_view_t residual_h,
+                                int32_t act, fl_tensor_view_t out_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &weight = deref(data_h);
+    const fl_tensor_view_impl_t &scales = deref(scales_h);
+    check_fp8_weight(weight, scales, /*per_channel_ok=*/true);
+    const fl_device_type_t device = device_of(weight);
+    const int rows = weight.shape[0];
+    const int k = weight.shape[1];
+    const fl_tensor_view_impl_t &a = deref(codes_h);
+    const fl_tensor_view_impl_t &row_scales = deref(row_scales_h);
+    if (dtype_of(a) != FL_DTYPE_FP8E4M3 || a.shape.size() < 2 || !is_contiguous(a) || device_of(a) != device) {
+      invalid("the left operand is not a contiguous <fp8e4m3> tensor of at least two dimensions on the weight's device");
+    }
+    if (a.shape.back() != k) invalid("the two operands disagree about k");
+    const int64_t m64 = leading_rows(a);
+    if (dtype_of(row_scales) != FL_DTYPE_FLOAT || numel_of(row_scales) != m64 || !is_contiguous(row_scales) ||
+        device_of(row_scales) != device) {
+      invalid("row_scales is not a contiguous <float> tensor of one value per row on the weight's device");
+    }
+    const fl_tensor_view_impl_t &out = deref(out_h);
+    if (!is_half_type(dtype_of(out)) || device_of(out) != device || !is_contiguous(out)) {
+      invalid("out is not a contiguous <float16> or <bfloat16> tensor on the weight's device");
+    }
+    {
+      std::vector<int32_t> want(a.shape.begin(), a.shape.end());
+      want.back() = rows;
+      check_shape(out, want, "out");
+    }
+    if (act != FL_ACT_NONE && act != FL_ACT_GELU_TANH) invalid("unknown activation");
+    const fl_tensor_view_impl_t *bias = bias_h ? &deref(bias_h) : nullptr;
+    const fl_tensor_view_impl_t *residual = residual_h ? &deref(residual_h) : nullptr;
+    if (bias) {
+      if (device_of(*bias) != device || dtype_of(*bias) != dtype_of(out) || numel_of(*bias) != rows ||
+          !is_contiguous(*bias)) {
+        invalid("the bias is not a contiguous (rows) vector of out's type on the weight's device");
+      }
+    }
+    if (residual) {
+      if (device_of(*residual) != device || dtype_of(*residual) != dtype_of(out) || !is_contiguous(*residual)) {
+        invalid("the residual is not contiguous, of out's type, on the weight's device");
+      }
+      check_shape(*residual, out.shape, "the residual");
+    }
+    if (device != FL_DEVICE_CUDA) invalid("the fp8 operand is on a device with no FP8 kernels");
+    check_tiles(rows, k, 16);
+    require_kernels();
+    check_earlier_kernel_status();
+    if (m64 == 0) return clear_error();
+    if (m64 > INT32_MAX) invalid("the left operand has more rows than the kernels can index");
+    const int m = static_cast<int>(m64);
+
+    // TMA wants 16-byte aligned bases; a view that starts elsewhere is staged.
+    Scratch scratch;
+    size_t a_off = 0, w_off = 0;
+    const bool a_misaligned = !aligned16(raw_ptr(a));
+    const bool w_misaligned = !aligned16(raw_ptr(weight));
+    if (a_misaligned) a_off = scratch.reserve(static_cast<size_t>(m) * k);
+    if (w_misaligned) w_off = scratch.reserve(static_cast<size_t>(rows) * k);
+    const void *a_ptr = raw_ptr(a);
+    const void *w_ptr = raw_ptr(weight);
+    if (a_misaligned || w_misaligned) {
+      uint8_t *base = scratch.commit();
+      if (a_misaligned) {
+        cuda_check(cudaMemcpyAsync(base + a_off, a_ptr, static_cast<size_t>(m) * k, cudaMemcpyDeviceToDevice, 0),
+                   "staging the left operand");
+        a_ptr = base + a_off;
+      }
+      if (w_misaligned) {
+        cuda_check(cudaMemcpyAsync(base + w_off, w_ptr, static_cast<size_t>(rows) * k, cudaMemcpyDeviceToDevice, 0),
+                   "staging the weight");
+        w_ptr = base + w_off;
+      }
+    }
+    Epilogue ep;
+    ep.row_scale = reinterpret_cast<const float *>(raw_ptr(row_scales));
+    ep.col_scale = reinterpret_cast<const float *>(raw_ptr(scales));
+    ep.col_scale_scalar = numel_of(scales) == 1 ? 1 : 0;
+    ep.bias = bias ? raw_ptr(*bias) : nullptr;
+    if (residual) {
+      ep.residual = raw_ptr(*residual);
+      ep.residual_rows = m;
+      ep.residual_ld = rows;
+    }
+    ep.act = act;
+    run_gemm(kGemmE4M3, m, rows, k, a_ptr, w_ptr, nullptr, nullptr, ep, dtype_of(out) == FL_DTYPE_BFLOAT16, raw_ptr(out));
+    return clear_error();
+  });
+}
+
+int32_t fl_qk_norm_rope(fl_tensor_view_t qkv_h, fl_tensor_view_t q_weight_h, fl_tensor_view_t k_weight_h,
+                        fl_tensor_view_t cos_h, fl_tensor_view_t sin_h, float eps, int32_t heads) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &qkv = deref(qkv_h);
+    const fl_tensor_view_impl_t &cos = deref(cos_h);
+    const fl_tensor_view_impl_t &sin = deref(sin_h);
+    if (!is_half_type(dtype_of(qkv)) || qkv.shape.size() < 2 || !is_contiguous(qkv)) {
+      invalid("qkv is not a contiguous <float16> or <bfloat16> tensor of at least two dimensions");
+    }
+    if (heads <= 0 || qkv.shape.back() % (3 * heads) != 0) invalid("qkv's last dimension is not 3 * heads * head_dim");
+    const int head_dim = qkv.shape.back() / (3 * heads);
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256) invalid("head_dim is not 64, 128 or 256");
+    for (const fl_tensor_view_impl_t *v : {&cos, &sin}) {
+      if (dtype_of(*v) != FL_DTYPE_FLOAT || v->shape.size() != 2 || v->shape[1] != head_dim / 2 || !is_contiguous(*v)) {
+        invalid("cos/sin is not a contiguous <float>(tokens, head_dim / 2)");
+      }
+    }
+    if (cos.shape != sin.shape) invalid("cos and sin differ in shape");
+    const int tokens = cos.shape[0];
+    const int64_t rows = leading_rows(qkv);
+    if (tokens <= 0 || rows % tokens != 0) invalid("the rows of qkv are not whole sequences of cos/sin's tokens");
+    const fl_tensor_view_impl_t *weights[2] = {q_weight_h ? &deref(q_weight_h) : nullptr,
+                                               k_weight_h ? &deref(k_weight_h) : nullptr};
+    for (const fl_tensor_view_impl_t *w : weights) {
+      if (w && (dtype_of(*w) != dtype_of(qkv) || numel_of(*w) != head_dim || !is_contiguous(*w) ||
+                device_of(*w) != FL_DEVICE_CUDA)) {
+        invalid("a norm weight is not a contiguous (head_dim) vector of qkv's type on cuda");
+      }
+    }
+    if (!(eps >= 0.0f)) invalid("eps is negative or not a number");
+    for (const fl_tensor_view_impl_t *v : {&qkv, &cos, &sin}) {
+      if (device_of(*v) != FL_DEVICE_CUDA) invalid("the operands are not all on cuda");
+    }
+    if (reinterpret_cast<uintptr_t>(raw_ptr(qkv)) & 7) invalid("qkv does not start on an 8-byte boundary");
+    require_kernels();
+    if (rows == 0) return clear_error();
+    cuda_check(qk_norm_rope(raw_ptr(qkv), dtype_of(qkv) == FL_DTYPE_BFLOAT16, rows, heads, head_dim, tokens,
+                            weights[0] ? raw_ptr(*weights[0]) : nullptr, weights[1] ? raw_ptr(*weights[1]) : nullptr,
+                            reinterpret_cast<const float *>(raw_ptr(cos)), reinterpret_cast<const float *>(raw_ptr(sin)), eps, 0),
+               "q/k norm and rotation");
+    ++g_block_launches;
+    return clear_error();
+  });
+}
+
 int32_t fl_quantize_nvfp4(fl_tensor_view_t w_h, fl_tensor_view_t codes_h, fl_tensor_view_t block_scales_h,
                           fl_tensor_view_t global_scale_h) {
   return guard([&]() -> int32_t {
@@ -1349,7 +1540,7 @@ int32_t fl_sm100_gemm_timing_read(double *total_ms, int64_t *launches) {
   });
 }
 
-int64_t fl_sm100_launch_count(void) { return g_gemm_launches.load() + helper_launch_count(); }
+int64_t fl_sm100_launch_count(void) { return g_gemm_launches.load() + g_block_launches.load() + helper_launch_count(); }
 
 
 }  // extern "C"

@@ -148,6 +148,174 @@ __global__ void __launch_bounds__(256) quantize_fp8_act_reg_kernel(const uint16_
   }
 }
 
+// ---- layer norm -> modulate -> per-row e4m3, one pass ----------------------------------------
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Two sums at once: one pair of barriers for both.
+__device__ __forceinline__ float2 block_sum2(float a, float b, float2 *red) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  if (lane == 0) red[warp] = make_float2(a, b);
+  __syncthreads();
+  float2 r = (lane < nwarps) ? red[lane] : make_float2(0.0f, 0.0f);
+  r.x = warp_sum(r.x);
+  r.y = warp_sum(r.y);
+  __syncthreads();
+  return r;
+}
+
+// The reference's statistics (flint/cpu/normalizations.cc:126-137): mean = sum / k,
+// variance = sumsq / k - mean^2, 1 / sqrt(variance + eps), with eps alone where rounding left the
+// variance at or below zero.
+__device__ __forceinline__ float2 mean_rstd(float2 sums, int k, float eps) {
+  const float mean = __fdiv_rn(sums.x, static_cast<float>(k));
+  const float var = __fsub_rn(__fdiv_rn(sums.y, static_cast<float>(k)), __fmul_rn(mean, mean));
+  return make_float2(mean, __frcp_rn(__fsqrt_rn(var > 0.0f ? __fadd_rn(var, eps) : eps)));
+}
+
+__device__ __forceinline__ uint16_t narrow(float v, int is_bf16) {
+  return is_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+}
+
+// One element of the modulated row: ((v - mean) rstd) (x) (1 + s) (+) t, every operation rounded
+// on its own in the order the reference's graph applies them (normed * scale + normed, then the
+// cast to the narrow type; waifu/src/qwen_image/dit.rs:179-184), as a 16-bit value.
+__device__ __forceinline__ uint16_t modulated(float v, float mean, float rstd, const uint16_t *s, const uint16_t *t,
+                                              int i, int is_bf16) {
+  float y = __fmul_rn(__fsub_rn(v, mean), rstd);
+  if (s) y = __fadd_rn(__fmul_rn(y, widen(__ldg(s + i), is_bf16)), y);
+  if (t) y = __fadd_rn(y, widen(__ldg(t + i), is_bf16));
+  return narrow(y, is_bf16);
+}
+
+// One CTA of 256 threads per row, the row in registers throughout (k <= 2048 VPT): one read of x,
+// one block reduction for the two sums of the statistics, one for amax of the modulated 16-bit
+// row, one write of the codes.
+template <int VPT>
+__global__ void __launch_bounds__(256) ln_modulate_quantize_reg_kernel(const uint16_t *__restrict__ x, int is_bf16, int k,
+                                                                     const uint16_t *__restrict__ scale,
+                                                                     const uint16_t *__restrict__ shift,
+                                                                     int rows_per_group, float eps,
+                                                                     uint8_t *__restrict__ codes,
+                                                                     float *__restrict__ row_scales) {
+  griddep_wait();
+  __shared__ float red[8];
+  __shared__ float2 red2[8];
+  const int64_t row = blockIdx.x;
+  const uint4 *xv = reinterpret_cast<const uint4 *>(x + row * k);
+  uint2 *cv = reinterpret_cast<uint2 *>(codes + row * k);
+  const int64_t group = row / rows_per_group;
+  const uint16_t *s = scale ? scale + group * k : nullptr;
+  const uint16_t *t = shift ? shift + group * k : nullptr;
+  const int nvec = k / 8;
+  uint4 q[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * 256;
+    q[i] = (v < nvec) ? xv[v] : make_uint4(0, 0, 0, 0);
+  }
+  float sum = 0.0f, sq = 0.0f;  // the zero padding of the last vectors adds nothing to either
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const uint32_t w[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float lo = widen(static_cast<uint16_t>(w[j] & 0xffff), is_bf16);
+      const float hi = widen(static_cast<uint16_t>(w[j] >> 16), is_bf16);
+      sum += lo + hi;
+      sq += lo * lo + hi * hi;
+    }
+  }
+  const float2 stats = mean_rstd(block_sum2(sum, sq, red2), k, eps);
+  const float mean = stats.x, rstd = stats.y;
+  // The modulated row replaces x in the registers, already narrowed to the 16-bit type. scale and
+  // shift come as the same 16-byte vectors as x (their rows are 16-byte aligned: the host checks).
+  float amax = 0.0f;
+  const uint4 *sv = reinterpret_cast<const uint4 *>(s);
+  const uint4 *tv = reinterpret_cast<const uint4 *>(t);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < nvec) {
+      const uint32_t w[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+      const uint4 s4 = s ? __ldg(sv + v) : make_uint4(0, 0, 0, 0);
+      const uint4 t4 = t ? __ldg(tv + v) : make_uint4(0, 0, 0, 0);
+      const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
+      const uint32_t tw[4] = {t4.x, t4.y, t4.z, t4.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint16_t h[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int sh = half * 16;
+          float y = __fmul_rn(__fsub_rn(widen(static_cast<uint16_t>(w[j] >> sh), is_bf16), mean), rstd);
+          if (s) y = __fadd_rn(__fmul_rn(y, widen(static_cast<uint16_t>(sw[j] >> sh), is_bf16)), y);
+          if (t) y = __fadd_rn(y, widen(static_cast<uint16_t>(tw[j] >> sh), is_bf16));
+          h[half] = narrow(y, is_bf16);
+          amax = fmaxf(amax, fabsf(widen(h[half], is_bf16)));
+        }
+        o[j] = h[0] | (static_cast<uint32_t>(h[1]) << 16);
+      }
+      q[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+  amax = block_max(amax, red);
+  const float qscale = __fdiv_rn(amax, 448.0f);
+  const float inv = __frcp_rn(qscale > 0.0f ? qscale : 1.0f);
+  if (threadIdx.x == 0) row_scales[row] = qscale;
+  griddep_launch_dependents();
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < nvec) cv[v] = e4m3x8_of(q[i], is_bf16, inv);
+  }
+}
+
+// The same arithmetic for rows of any length and any alignment: the row is read three times (an
+// L1/L2 hit after the first) and the modulated value is computed twice.
+__global__ void __launch_bounds__(256) ln_modulate_quantize_kernel(const uint16_t *__restrict__ x, int is_bf16, int k,
+                                                                 const uint16_t *__restrict__ scale,
+                                                                 const uint16_t *__restrict__ shift, int rows_per_group,
+                                                                 float eps, uint8_t *__restrict__ codes,
+                                                                 float *__restrict__ row_scales) {
+  griddep_wait();
+  __shared__ float red[8];
+  __shared__ float2 red2[8];
+  const int64_t row = blockIdx.x;
+  const uint16_t *xr = x + row * k;
+  const int64_t group = row / rows_per_group;
+  const uint16_t *s = scale ? scale + group * k : nullptr;
+  const uint16_t *t = shift ? shift + group * k : nullptr;
+  float sum = 0.0f, sq = 0.0f;
+  for (int i = threadIdx.x; i < k; i += blockDim.x) {
+    const float v = widen(xr[i], is_bf16);
+    sum += v;
+    sq += v * v;
+  }
+  const float2 stats = mean_rstd(block_sum2(sum, sq, red2), k, eps);
+  const float mean = stats.x, rstd = stats.y;
+  float amax = 0.0f;
+  for (int i = threadIdx.x; i < k; i += blockDim.x) {
+    amax = fmaxf(amax, fabsf(widen(modulated(widen(xr[i], is_bf16), mean, rstd, s, t, i, is_bf16), is_bf16)));
+  }
+  amax = block_max(amax, red);
+  const float qscale = __fdiv_rn(amax, 448.0f);
+  const float inv = __frcp_rn(qscale > 0.0f ? qscale : 1.0f);
+  if (threadIdx.x == 0) row_scales[row] = qscale;
+  griddep_launch_dependents();
+  for (int i = threadIdx.x; i < k; i += blockDim.x) {
+    const float h = widen(modulated(widen(xr[i], is_bf16), mean, rstd, s, t, i, is_bf16), is_bf16);
+    codes[row * k + i] = e4m3_of(__fmul_rn(h, inv));
+  }
+}
+
 __global__ void __launch_bounds__(128) quantize_fp8_rows_f32_kernel(const float *__restrict__ w, int k,
                                                                   uint8_t *__restrict__ codes,
                                                                   float *__restrict__ scales) {
@@ -363,6 +531,36 @@ cudaError_t quantize_fp8_act(const void *x, int is_bf16, int m, int k, uint8_t *
     cfg.blockDim = dim3(128, 1, 1);
     if (vec) e = cudaLaunchKernelEx(&cfg, quantize_fp8_act_kernel<true>, xs, is_bf16, k, codes, scales);
     else e = cudaLaunchKernelEx(&cfg, quantize_fp8_act_kernel<false>, xs, is_bf16, k, codes, scales);
+  }
+  ++g_helper_launches;
+  return e;
+}
+
+cudaError_t ln_modulate_quantize_fp8(const void *x, int is_bf16, int m, int k, const void *scale, const void *shift,
+                                     int rows_per_group, float eps, uint8_t *codes, float *row_scales,
+                                     cudaStream_t stream) {
+  const bool vec = aligned16(x) && aligned16(codes) && (k % 8 == 0) && aligned16(scale) && aligned16(shift);
+  const uint16_t *xs = static_cast<const uint16_t *>(x);
+  const uint16_t *sc = static_cast<const uint16_t *>(scale);
+  const uint16_t *sh = static_cast<const uint16_t *>(shift);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(m), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e;
+  if (vec && k <= 2048 * 2) {
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<2>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
+  } else if (vec && k <= 2048 * 4) {
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<4>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
+  } else if (vec && k <= 2048 * 8) {
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<8>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
+  } else {
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_kernel, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
   }
   ++g_helper_launches;
   return e;

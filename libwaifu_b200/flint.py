@@ -110,6 +110,12 @@ def lib() -> ctypes.CDLL:
     L.fl_quantize_fp8_rows.argtypes = [V, V, V]
     L.fl_quantize_fp8_activation.argtypes = [V, V, V]
     L.fl_quantize_nvfp4.argtypes = [V, V, V, V]
+    L.fl_fp8_layernorm_quantize.argtypes = [V, V, V, ctypes.c_float, V, V]
+    L.fl_fp8_layernorm_quantize.restype = c_int32
+    L.fl_fp8_linear_quantized.argtypes = [V, V, V, V, V, V, c_int32, V]
+    L.fl_fp8_linear_quantized.restype = c_int32
+    L.fl_qk_norm_rope.argtypes = [V, V, V, V, V, ctypes.c_float, c_int32]
+    L.fl_qk_norm_rope.restype = c_int32
     L.fl_sm100_set_device.argtypes = [c_int32]
     L.fl_sm100_synchronize.argtypes = [POINTER(c_int32)]
     L.fl_sm100_launch_count.restype = c_int64
@@ -447,6 +453,40 @@ def quantize_fp8_rows(w: Tensor):
     scales = Tensor.empty((rows,), DType.FLOAT)
     check(lib().fl_quantize_fp8_rows(w.raw(), codes.raw(), scales.raw()))
     return codes, scales
+
+
+def fp8_layernorm_quantize(x: Tensor, scale: Optional[Tensor] = None, shift: Optional[Tensor] = None,
+                           eps: float = 1e-6, codes: Optional[Tensor] = None, row_scales: Optional[Tensor] = None):
+    """Layer norm over the last dimension, adaLN modulation n * scale + n + shift, narrowing to x's
+    type and per-row e4m3 quantisation in one pass; returns (codes, row_scales)."""
+    rows = 1
+    for d in x.shape[:-1]:
+        rows *= d
+    if codes is None:
+        codes = Tensor.empty(tuple(x.shape), DType.FP8E4M3)
+    if row_scales is None:
+        row_scales = Tensor.empty((rows,), DType.FLOAT)
+    check(lib().fl_fp8_layernorm_quantize(x.raw(), scale.raw() if scale else None, shift.raw() if shift else None,
+                                          float(eps), codes.raw(), row_scales.raw()))
+    return codes, row_scales
+
+
+def fp8_linear_quantized(codes: Tensor, row_scales: Tensor, weight: Tensor, scales: Tensor, bias: Optional[Tensor],
+                         residual: Optional[Tensor], act: int, out: Tensor) -> Tensor:
+    """fp8_linear for an activation that is e4m3 codes with per-row scales already."""
+    check(lib().fl_fp8_linear_quantized(codes.raw(), row_scales.raw(), weight.raw(), scales.raw(),
+                                        bias.raw() if bias else None, residual.raw() if residual else None, int(act),
+                                        out.raw()))
+    return out
+
+
+def qk_norm_rope(qkv: Tensor, cos: Tensor, sin: Tensor, heads: int, eps: float = 1e-6,
+                 q_weight: Optional[Tensor] = None, k_weight: Optional[Tensor] = None) -> Tensor:
+    """In place on a fused projection's output (..., 3 * heads * head_dim): per-head RMS norm of the
+    q and k thirds and the rotation of their even/odd pairs; returns qkv."""
+    check(lib().fl_qk_norm_rope(qkv.raw(), q_weight.raw() if q_weight else None, k_weight.raw() if k_weight else None,
+                                cos.raw(), sin.raw(), float(eps), int(heads)))
+    return qkv
 
 
 def quantize_fp8_activation(a: Tensor):

@@ -6,10 +6,16 @@ norm of q and k, rotary embedding, attention over the joined sequence, gated res
 adaLN modulation of the timestep embedding) with the widths of the benchmark configuration
 (hidden 3072, 24 heads of 128, MLP 12288 with GELU-tanh, 256 text + 4096 image tokens, 60 blocks).
 
-Only the five linears of a block are this library's work: the modulation (M = batch), the fused
-QKV projection, the attention output projection, and the MLP up (GELU fused in the epilogue) and
-down projections. Layer norm, modulation arithmetic, q/k norm, rotary embedding and attention are
-plain torch, and are inside the timed step but outside the graded path.
+The five linears of a block are this library's work: the modulation (M = batch), the fused QKV
+projection, the attention output projection, and the MLP up (GELU fused in the epilogue) and down
+projections, together with the steps either side of them: layer norm, adaLN modulation and the
+activation quantiser run as one kernel in front of the QKV and up projections
+(fl_fp8_layernorm_quantize), and the gated residual `x + gate * linear(a)` behind the output and
+down projections is folded into the projection's epilogue (the gate multiplies the per-channel
+scale and the bias, the stream is the residual), and the per-head RMS norm of q and k with their
+rotary embedding runs in place on the QKV projection's output (fl_qk_norm_rope), which attention
+then reads as three strided views. Attention itself and the SiLU of the timestep embedding are
+plain torch, inside the timed step but outside the graded path.
 
 The same block code runs over two backends: ``FlintBackend`` (the C ABI on the GPU) and
 ``OracleBackend`` (the CPU oracle, for the parity test at a reduced size).
@@ -47,8 +53,12 @@ LAYER_SHAPES = lambda c: {"mod": (6 * c.hidden, c.hidden), "qkv": (3 * c.hidden,
                           "out": (c.hidden, c.hidden), "up": (c.mlp, c.hidden), "down": (c.hidden, c.mlp)}
 
 
+LN_EPS = 1e-6
+
+
 class FlintBackend:
-    """Linears through libflint_sm100 (fl_quantize_fp8_rows at load, fl_fp8_linear per call)."""
+    """Linears through libflint_sm100 (fl_quantize_fp8_rows at load; per call fl_fp8_linear, or
+    fl_fp8_layernorm_quantize + fl_fp8_linear_quantized where a layer norm feeds the linear)."""
 
     def __init__(self):
         import torch
@@ -61,22 +71,75 @@ class FlintBackend:
         return self.F.Tensor.from_device_ptr(t.data_ptr(), tuple(t.shape), dt, keepalive=t)
 
     def make_layer(self, w_f32, bias_bf16):
-        codes, scales = self.F.quantize_fp8_rows(self._wrap(w_f32, self.F.DType.FLOAT))
-        self.F.synchronize()
-        return (codes, scales, None if bias_bf16 is None else self._wrap(bias_bf16, self.F.DType.BFLOAT16), bias_bf16)
+        torch, F = self.torch, self.F
+        n, k = w_f32.shape
+        codes_t = torch.empty((n, k), dtype=torch.uint8, device="cuda")
+        scales_t = torch.empty((n,), dtype=torch.float32, device="cuda")
+        codes, scales = self._wrap(codes_t, F.DType.FP8E4M3), self._wrap(scales_t, F.DType.FLOAT)
+        w = self._wrap(w_f32, F.DType.FLOAT)
+        F.check(F.lib().fl_quantize_fp8_rows(w.raw(), codes.raw(), scales.raw()))
+        F.synchronize()
+        return (codes, scales, None if bias_bf16 is None else self._wrap(bias_bf16, F.DType.BFLOAT16), bias_bf16, scales_t)
 
     def linear(self, x2d, layer, act: int = 0, residual2d=None):
         torch, F = self.torch, self.F
-        codes, scales, bias, _ = layer
+        codes, scales, bias = layer[:3]
         out = torch.empty((x2d.shape[0], codes.shape[0]), dtype=torch.bfloat16, device=x2d.device)
         F.fp8_linear(self._wrap(x2d, F.DType.BFLOAT16), codes, scales, bias,
                      None if residual2d is None else self._wrap(residual2d, F.DType.BFLOAT16), act,
                      self._wrap(out, F.DType.BFLOAT16))
         return out
 
+    def modulated_linear(self, x3d, scale, shift, layer, act: int = 0):
+        """linear(round16(LN(x) * scale + LN(x) + shift)) with scale, shift (batch, hidden): one
+        kernel reads x and writes the e4m3 rows, the GEMM takes them as they are."""
+        torch, F = self.torch, self.F
+        codes, scales, bias = layer[:3]
+        b, t, d = x3d.shape
+        q = torch.empty((b * t, d), dtype=torch.uint8, device=x3d.device)
+        rs = torch.empty((b * t,), dtype=torch.float32, device=x3d.device)
+        qw, rsw = self._wrap(q, F.DType.FP8E4M3), self._wrap(rs, F.DType.FLOAT)
+        F.fp8_layernorm_quantize(self._wrap(x3d.reshape(b * t, d), F.DType.BFLOAT16), self._wrap(scale.contiguous(), F.DType.BFLOAT16),
+                                 self._wrap(shift.contiguous(), F.DType.BFLOAT16), LN_EPS, qw, rsw)
+        out = torch.empty((b * t, codes.shape[0]), dtype=torch.bfloat16, device=x3d.device)
+        F.fp8_linear_quantized(qw, rsw, codes, scales, bias, None, act, self._wrap(out, F.DType.BFLOAT16))
+        return out
+
+    def qk_norm_rope(self, qkv2d, cos, sin, heads):
+        """In place: per-head RMS norm of q and k, then their rotary embedding."""
+        F = self.F
+        F.qk_norm_rope(self._wrap(qkv2d, F.DType.BFLOAT16), self._wrap(cos, F.DType.FLOAT), self._wrap(sin, F.DType.FLOAT),
+                       heads, LN_EPS)
+        return qkv2d
+
+    def gated_linear(self, a2d, layer, gate, stream3d):
+        """stream + gate * linear(a), gate (batch, n): per batch row block one GEMM whose per-channel
+        scale and bias carry the gate and whose residual is the stream, so the product is rounded
+        once and no elementwise pass follows it."""
+        torch, F = self.torch, self.F
+        codes, scales, bias, bias_t, scales_t = layer
+        b, t, n = stream3d.shape
+        out = torch.empty((b, t, n), dtype=torch.bfloat16, device=a2d.device)
+        g32 = gate.float()
+        gated_scales = (g32 * scales_t[None, :]).contiguous()                       # (b, n) fp32
+        gated_bias = None if bias_t is None else (g32 * bias_t.float()[None, :]).to(torch.bfloat16).contiguous()
+        k = a2d.shape[1]
+        q = torch.empty((b * t, k), dtype=torch.uint8, device=a2d.device)
+        rs = torch.empty((b * t,), dtype=torch.float32, device=a2d.device)
+        aw, qw, rsw = self._wrap(a2d, F.DType.BFLOAT16), self._wrap(q, F.DType.FP8E4M3), self._wrap(rs, F.DType.FLOAT)
+        F.check(F.lib().fl_quantize_fp8_activation(aw.raw(), qw.raw(), rsw.raw()))  # the views outlive the call
+        for i in range(b):
+            rows = slice(i * t, (i + 1) * t)
+            F.fp8_linear_quantized(self._wrap(q[rows], F.DType.FP8E4M3), self._wrap(rs[rows], F.DType.FLOAT), codes,
+                                   self._wrap(gated_scales[i], F.DType.FLOAT),
+                                   None if gated_bias is None else self._wrap(gated_bias[i], F.DType.BFLOAT16),
+                                   self._wrap(stream3d[i], F.DType.BFLOAT16), 0, self._wrap(out[i], F.DType.BFLOAT16))
+        return out
+
 
 class OracleBackend:
-    """The same linears on the CPU through the test oracle (only tests construct this)."""
+    """The same linears on the CPU through the test oracle (only tests construct this), each fused
+    step spelled out as the separate operations it stands for."""
 
     def __init__(self, oracle_module):
         import torch
@@ -87,6 +150,9 @@ class OracleBackend:
     def _bits(self, t):
         return t.contiguous().view(self.torch.int16).numpy().view("uint16")
 
+    def _tensor(self, bits):
+        return self.torch.from_numpy(bits.view("int16").copy()).view(self.torch.bfloat16)
+
     def make_layer(self, w_f32, bias_bf16):
         codes, scales = self.O.quantize_fp8_rows(w_f32.cpu().numpy())
         return (codes, scales, None if bias_bf16 is None else self._bits(bias_bf16.cpu()))
@@ -95,16 +161,19 @@ class OracleBackend:
         codes, scales, bias = layer
         y = self.O.fp8_linear(self._bits(x2d), codes, scales, bias,
                               None if residual2d is None else self._bits(residual2d), act, True)
-        return self.torch.from_numpy(y.view("int16").copy()).view(self.torch.bfloat16)
+        return self._tensor(y)
 
+    def modulated_linear(self, x3d, scale, shift, layer, act: int = 0):
+        b, t, d = x3d.shape
+        h = self.O.layernorm_modulate(self._bits(x3d.reshape(b * t, d)), self._bits(scale), self._bits(shift), LN_EPS, True)
+        return self.linear(self._tensor(h), layer, act)
 
-def _rope(x, cos, sin):
-    # x: (b, heads, tokens, head_dim); rotate pairs (even, odd)
-    x1, x2 = x[..., 0::2], x[..., 1::2]
-    out = x.new_empty(x.shape)
-    out[..., 0::2] = x1 * cos - x2 * sin
-    out[..., 1::2] = x1 * sin + x2 * cos
-    return out
+    def qk_norm_rope(self, qkv2d, cos, sin, heads):
+        return self._tensor(self.O.qk_norm_rope(self._bits(qkv2d), cos.numpy(), sin.numpy(), heads, LN_EPS, True))
+
+    def gated_linear(self, a2d, layer, gate, stream3d):
+        b, t, n = stream3d.shape
+        return stream3d + gate[:, None, :] * self.linear(a2d, layer).view(b, t, n)
 
 
 class MMDiT:
@@ -138,8 +207,8 @@ class MMDiT:
         pos = torch.arange(cfg.tokens, dtype=torch.float32)
         freq = torch.exp(-math.log(10000.0) * torch.arange(half, dtype=torch.float32) / half)
         ang = pos[:, None] * freq[None, :]
-        self.cos = ang.cos().to(dev).to(torch.bfloat16)
-        self.sin = ang.sin().to(dev).to(torch.bfloat16)
+        self.cos = ang.cos().contiguous().to(dev)  # float32 (tokens, head_dim / 2)
+        self.sin = ang.sin().contiguous().to(dev)
 
     def block(self, x, temb, layers):
         torch = self.torch
@@ -148,22 +217,21 @@ class MMDiT:
         b, t, d = x.shape
         lin = self.backend.linear
         mod = lin(Fn.silu(temb), layers["mod"])  # (b, 6 d): the M = batch skinny linear
-        shift1, scale1, gate1, shift2, scale2, gate2 = [m[:, None, :] for m in mod.chunk(6, dim=1)]
+        shift1, scale1, gate1, shift2, scale2, gate2 = mod.chunk(6, dim=1)
 
-        h = Fn.layer_norm(x, (d,)) * (1 + scale1) + shift1
-        qkv = lin(h.reshape(b * t, d).contiguous(), layers["qkv"]).view(b, t, 3, c.heads, c.head_dim)
+        qkv = self.backend.modulated_linear(x, scale1, shift1, layers["qkv"])  # (b t, 3 d)
+        qkv = self.backend.qk_norm_rope(qkv, self.cos, self.sin, c.heads).view(b, t, 3, c.heads, c.head_dim)
+        # q, k, v as (b, heads, t, head_dim) views of the one buffer: nothing is copied, and the
+        # attention output comes back token-major, which is the layout the next projection reads
         q, k, v = qkv[:, :, 0].transpose(1, 2), qkv[:, :, 1].transpose(1, 2), qkv[:, :, 2].transpose(1, 2)
-        q = Fn.rms_norm(q, (c.head_dim,))
-        k = Fn.rms_norm(k, (c.head_dim,))
-        q = _rope(q, self.cos, self.sin)
-        k = _rope(k, self.cos, self.sin)
         a = Fn.scaled_dot_product_attention(q, k, v)  # joint attention over text + image tokens
-        a = a.transpose(1, 2).reshape(b * t, d).contiguous()
-        x = x + gate1 * lin(a, layers["out"]).view(b, t, d)
+        a = a.transpose(1, 2).reshape(b * t, d)
+        if not a.is_contiguous():
+            a = a.contiguous()
+        x = self.backend.gated_linear(a, layers["out"], gate1, x)
 
-        h2 = (Fn.layer_norm(x, (d,)) * (1 + scale2) + shift2).reshape(b * t, d).contiguous()
-        u = lin(h2, layers["up"], act=1)  # GELU-tanh fused into the epilogue
-        x = x + gate2 * lin(u, layers["down"]).view(b, t, d)
+        u = self.backend.modulated_linear(x, scale2, shift2, layers["up"], act=1)  # GELU-tanh in the epilogue
+        x = self.backend.gated_linear(u, layers["down"], gate2, x)
         return x
 
     def step(self, x, temb):

@@ -158,6 +158,78 @@ def quantize_nvfp4_act(x16: np.ndarray, is_bf16: bool):
     return codes, sf
 
 
+def layernorm_modulate(x16: np.ndarray, scale16, shift16, eps: float, is_bf16: bool) -> np.ndarray:
+    """The consumer in front of a block's projection, as 16-bit values (m, k): flint's layerNorm
+    without affine (float32: mean = sum / k, variance = sumsq / k - mean^2 with eps added where
+    that is positive and standing alone where it is not, flint/cpu/normalizations.cc:98-140, the
+    division by the deviation taken as one reciprocal per row; the two sums here are summed in
+    float64 and rounded to float32 once, the value every float32 summation order approximates),
+    then the reference's
+    modulate, `normed * scale + normed` with each operation rounded to float32, an optional shift,
+    and the cast to the narrow type (waifu/src/qwen_image/dit.rs:179-184). scale16/shift16 are
+    (k) or (groups, k) bit patterns or None; row r belongs to group r // (m // groups)."""
+    x16 = np.ascontiguousarray(x16, dtype=np.uint16)
+    m, k = x16.shape
+    v = widen(x16, is_bf16)
+    total = v.astype(np.float64).sum(axis=1).astype(np.float32)
+    total_sq = (v.astype(np.float64) ** 2).sum(axis=1).astype(np.float32)
+    mean = (total / np.float32(k)).astype(np.float32)
+    var = ((total_sq / np.float32(k)).astype(np.float32) - (mean * mean).astype(np.float32)).astype(np.float32)
+    var = np.where(var > 0, (var + np.float32(eps)).astype(np.float32), np.float32(eps)).astype(np.float32)
+    rstd = (np.float32(1.0) / np.sqrt(var, dtype=np.float32)).astype(np.float32)
+    y = ((v - mean[:, None]).astype(np.float32) * rstd[:, None]).astype(np.float32)
+
+    def rows_of(mod):
+        mod = widen(np.ascontiguousarray(mod, dtype=np.uint16).reshape(-1, k), is_bf16)
+        groups = mod.shape[0]
+        if m % groups:
+            raise ValueError("rows do not divide into groups")
+        return np.repeat(mod, m // groups, axis=0)
+
+    if scale16 is not None:
+        y = ((y * rows_of(scale16)).astype(np.float32) + y).astype(np.float32)
+    if shift16 is not None:
+        y = (y + rows_of(shift16)).astype(np.float32)
+    return narrow(y, is_bf16)
+
+
+def qk_norm_rope(qkv16: np.ndarray, cos: np.ndarray, sin: np.ndarray, heads: int, eps: float, is_bf16: bool,
+                 q_weight16=None, k_weight16=None) -> np.ndarray:
+    """The step between a fused q/k/v projection and attention on (rows, 3 * heads * head_dim) bit
+    patterns: per row and q or k head flint's rmsNorm (`a * w / sqrt(mean(a^2) + eps)`, float32,
+    flint/cpu/normalizations.cc:33-70; the mean of squares summed in float64 and rounded once)
+    narrowed to the 16-bit type, then the even/odd pair rotation of waifu/src/krea2/dit.rs:260-275
+    with every operation rounded to float32 and one final narrowing. cos, sin are float32
+    (tokens, head_dim / 2); row r sits at position r % tokens. The v third is returned as it is."""
+    qkv16 = np.ascontiguousarray(qkv16, dtype=np.uint16)
+    rows, width = qkv16.shape
+    head_dim = width // (3 * heads)
+    tokens = cos.shape[0]
+    out = qkv16.copy()
+    x = widen(qkv16[:, :2 * heads * head_dim], is_bf16).reshape(rows, 2 * heads, head_dim)
+    ms = ((x.astype(np.float64) ** 2).sum(axis=2) / head_dim).astype(np.float32)
+    rms = np.sqrt(ms + np.float32(eps), dtype=np.float32)
+    y = x
+    if q_weight16 is not None or k_weight16 is not None:
+        w = np.ones((2 * heads, head_dim), np.float32)
+        if q_weight16 is not None:
+            w[:heads] = widen(np.asarray(q_weight16, np.uint16), is_bf16)
+        if k_weight16 is not None:
+            w[heads:] = widen(np.asarray(k_weight16, np.uint16), is_bf16)
+        y = (x * w[None]).astype(np.float32)
+    inv = (np.float32(1.0) / rms).astype(np.float32)  # one reciprocal per head, as the GPU path takes it
+    n = widen(narrow((y * inv[:, :, None]).astype(np.float32), is_bf16), is_bf16).reshape(rows, 2 * heads, head_dim // 2, 2)
+    pos = np.arange(rows) % tokens
+    c = np.asarray(cos, np.float32)[pos][:, None, :]
+    s_ = np.asarray(sin, np.float32)[pos][:, None, :]
+    even, odd = n[..., 0], n[..., 1]
+    left = ((even * c).astype(np.float32) - (odd * s_).astype(np.float32)).astype(np.float32)
+    right = ((even * s_).astype(np.float32) + (odd * c).astype(np.float32)).astype(np.float32)
+    rot = np.stack([left, right], axis=-1).reshape(rows, 2 * heads * head_dim)
+    out[:, :2 * heads * head_dim] = narrow(rot, is_bf16)
+    return out
+
+
 def decode_e4m3(codes: np.ndarray) -> np.ndarray:
     codes = np.ascontiguousarray(codes, dtype=np.uint8)
     out = np.empty(codes.shape, dtype=np.float32)
