@@ -19,16 +19,17 @@ __device__ __forceinline__ uint16_t narrow(float v, int is_bf16) {
   return is_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
 }
 
-// A warp takes kUnits consecutive (row, q or k, head) units, EPL = head_dim / 32 consecutive
-// elements (EPL / 2 pairs) per lane and unit: all the units' vector loads are issued before the
-// first is used, which is what keeps enough bytes in flight for a kernel with this little work per
-// byte. Consecutive units are consecutive heads of a row, so a CTA reads and writes one contiguous
-// run of the buffer (the v third aside).
+// One CTA row of the grid per row of qkv; a warp takes kUnits consecutive q or k heads of it,
+// EPL = head_dim / 32 consecutive elements (EPL / 2 pairs) per lane and head: all the heads' vector
+// loads are issued before the first is used, which is what keeps enough bytes in flight for a
+// kernel with this little work per byte, and no index needs a division. A CTA reads and writes
+// one contiguous run of the row (the v third aside).
 constexpr int kUnits = 4;
+constexpr int kMaxWarps = 16;
 
 template <int EPL>
-__global__ void __launch_bounds__(256) qk_norm_rope_kernel(uint16_t *__restrict__ qkv, int is_bf16, int64_t units,
-                                                         int heads, int tokens, const uint16_t *__restrict__ q_weight,
+__global__ void __launch_bounds__(kMaxWarps * 32) qk_norm_rope_kernel(uint16_t *__restrict__ qkv, int is_bf16,
+                                                                    int heads, int tokens, const uint16_t *__restrict__ q_weight,
                                                          const uint16_t *__restrict__ k_weight,
                                                          const float *__restrict__ cos, const float *__restrict__ sin,
                                                          float eps) {
@@ -37,18 +38,18 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(uint16_t *__restrict_
   constexpr int HEAD_DIM = EPL * 32;
   constexpr int VEC = EPL == 2 ? 1 : EPL / 4;  // 8-byte vectors per lane and unit (one 4-byte word when EPL == 2)
   const int lane = threadIdx.x & 31;
-  const int64_t first = (static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5)) * kUnits;
   const int per_row = 2 * heads;  // q heads then k heads: the first two thirds of the row
+  const int first = (blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5)) * kUnits;
+  const int64_t row = blockIdx.x;
+  const int pos = static_cast<int>(blockIdx.x % static_cast<unsigned>(tokens));
 
   uint16_t *p[kUnits];
   uint2 raw[kUnits][VEC];
 #pragma unroll
   for (int u = 0; u < kUnits; ++u) {
-    const int64_t unit = first + u;
+    const int slot = first + u;
     p[u] = nullptr;
-    if (unit < units) {
-      const int64_t row = unit / per_row;
-      const int slot = static_cast<int>(unit - row * per_row);
+    if (slot < per_row) {
       p[u] = qkv + row * (3LL * heads * HEAD_DIM) + static_cast<int64_t>(slot) * HEAD_DIM + lane * EPL;
       if constexpr (EPL == 2) {
         raw[u][0] = make_uint2(*reinterpret_cast<const uint32_t *>(p[u]), 0);
@@ -62,11 +63,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(uint16_t *__restrict_
 #pragma unroll
   for (int u = 0; u < kUnits; ++u) {
     if (!p[u]) continue;  // warp-uniform
-    const int64_t unit = first + u;
-    const int64_t row = unit / per_row;
-    const int slot = static_cast<int>(unit - row * per_row);
-    const uint16_t *weight = slot < heads ? q_weight : k_weight;
-    const int pos = static_cast<int>(row % tokens);
+    const uint16_t *weight = first + u < heads ? q_weight : k_weight;
     uint16_t e[EPL];
     if constexpr (EPL == 2) {
       e[0] = static_cast<uint16_t>(raw[u][0].x & 0xffff);
@@ -122,17 +119,19 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(uint16_t *__restrict_
 template <int EPL>
 cudaError_t launch(void *qkv, int is_bf16, int64_t rows, int heads, int tokens, const void *qw, const void *kw,
                    const float *cos, const float *sin, float eps, cudaStream_t stream) {
-  const int64_t units = rows * 2 * heads;
+  const int per_row = 2 * heads;
+  int warps = (per_row + kUnits - 1) / kUnits;
+  if (warps > kMaxWarps) warps = kMaxWarps;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>((units + 8 * kUnits - 1) / (8 * kUnits)), 1, 1);
-  cfg.blockDim = dim3(256, 1, 1);
+  cfg.gridDim = dim3(static_cast<unsigned>(rows), static_cast<unsigned>((per_row + warps * kUnits - 1) / (warps * kUnits)), 1);
+  cfg.blockDim = dim3(static_cast<unsigned>(warps * 32), 1, 1);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, qk_norm_rope_kernel<EPL>, static_cast<uint16_t *>(qkv), is_bf16, units, heads, tokens,
+  return cudaLaunchKernelEx(&cfg, qk_norm_rope_kernel<EPL>, static_cast<uint16_t *>(qkv), is_bf16, heads, tokens,
                             static_cast<const uint16_t *>(qw), static_cast<const uint16_t *>(kw), cos, sin, eps);
 }
 

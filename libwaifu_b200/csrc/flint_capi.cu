@@ -1426,6 +1426,7 @@ int32_t fl_qk_norm_rope(fl_tensor_view_t qkv_h, fl_tensor_view_t q_weight_h, fl_
     if (reinterpret_cast<uintptr_t>(raw_ptr(qkv)) & 7) invalid("qkv does not start on an 8-byte boundary");
     require_kernels();
     if (rows == 0) return clear_error();
+    if (rows > INT32_MAX) invalid("qkv has more rows than the kernel can index");
     cuda_check(qk_norm_rope(raw_ptr(qkv), dtype_of(qkv) == FL_DTYPE_BFLOAT16, rows, heads, head_dim, tokens,
                             weights[0] ? raw_ptr(*weights[0]) : nullptr, weights[1] ? raw_ptr(*weights[1]) : nullptr,
                             reinterpret_cast<const float *>(raw_ptr(cos)), reinterpret_cast<const float *>(raw_ptr(sin)), eps, 0),
