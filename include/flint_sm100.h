@@ -238,6 +238,13 @@ FLAPI int32_t fl_quantize_fp8_activation(fl_tensor_view_t a, fl_tensor_view_t co
  * One pass over x; h is never written. codes <fp8e4m3> of x's shape, row_scales <float>(rows). */
 FLAPI int32_t fl_fp8_layernorm_quantize(fl_tensor_view_t x, fl_tensor_view_t scale, fl_tensor_view_t shift, float eps,
                                         fl_tensor_view_t codes, fl_tensor_view_t row_scales);
+/* The step between a gated MLP's two projections, fused with the second one's quantiser: flint's
+ * swiglu (flint/cpu/glu.cc:36-67; the first half of the last dimension is the gate, the second the
+ * value) on x <float16|bfloat16>(..., 2 h),
+ *   y = round16( g / (1 + exp(-g)) * v )
+ * then codes, row_scales = per-row e4m3 of y (..., h), exactly fl_quantize_fp8_activation(y).
+ * One pass over x; y is never written. */
+FLAPI int32_t fl_fp8_swiglu_quantize(fl_tensor_view_t x, fl_tensor_view_t codes, fl_tensor_view_t row_scales);
 /* fl_fp8_linear for an activation that is quantised already (by fl_fp8_layernorm_quantize or
  * fl_quantize_fp8_activation): codes <fp8e4m3>(..., k) with row_scales <float>(rows); out
  * <float16|bfloat16>(..., n) chooses the type of bias, residual and result. */

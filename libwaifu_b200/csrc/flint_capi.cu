@@ -1390,6 +1390,36 @@ int32_t fl_fp8_linear_quantized(fl_tensor_view_t codes_h, fl_tensor_view_t row_s
   });
 }
 
+int32_t fl_fp8_swiglu_quantize(fl_tensor_view_t x_h, fl_tensor_view_t codes_h, fl_tensor_view_t row_scales_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &x = deref(x_h);
+    const fl_tensor_view_impl_t &codes = deref(codes_h);
+    const fl_tensor_view_impl_t &row_scales = deref(row_scales_h);
+    if (!is_half_type(dtype_of(x)) || x.shape.size() < 2 || !is_contiguous(x) || x.shape.back() % 2 != 0) {
+      invalid("x is not a contiguous <float16> or <bfloat16> tensor of at least two dimensions with an even last one");
+    }
+    std::vector<int32_t> want(x.shape.begin(), x.shape.end());
+    want.back() /= 2;
+    if (dtype_of(codes) != FL_DTYPE_FP8E4M3 || codes.shape != want || !is_contiguous(codes)) {
+      invalid("codes is not a contiguous <fp8e4m3> tensor of x's shape with half the last dimension");
+    }
+    const int64_t m64 = leading_rows(x);
+    if (dtype_of(row_scales) != FL_DTYPE_FLOAT || numel_of(row_scales) != m64 || !is_contiguous(row_scales)) {
+      invalid("row_scales is not a contiguous <float> tensor of one value per row of x");
+    }
+    for (const fl_tensor_view_impl_t *v : {&x, &codes, &row_scales}) {
+      if (device_of(*v) != FL_DEVICE_CUDA) invalid("the operands are not all on cuda");
+    }
+    require_kernels();
+    if (m64 == 0 || want.back() == 0) return clear_error();
+    if (m64 > INT32_MAX) invalid("x has more rows than the kernels can index");
+    cuda_check(swiglu_quantize_fp8(raw_ptr(x), dtype_of(x) == FL_DTYPE_BFLOAT16, static_cast<int>(m64), want.back(),
+                                   raw_ptr(codes), reinterpret_cast<float *>(raw_ptr(row_scales)), 0),
+               "swiglu and quantisation");
+    return clear_error();
+  });
+}
+
 int32_t fl_qk_norm_rope(fl_tensor_view_t qkv_h, fl_tensor_view_t q_weight_h, fl_tensor_view_t k_weight_h,
                         fl_tensor_view_t cos_h, fl_tensor_view_t sin_h, float eps, int32_t heads) {
   return guard([&]() -> int32_t {

@@ -102,15 +102,16 @@ struct Config {
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kColParamOffset = kStages * kStageBytes;
   static constexpr int kSmemBytes = kColParamOffset + kColParamBytes + 1024;  // + slack to align to 1024
-  // Tensor memory columns: two accumulators, then the scale factors of one stage. (Neither a
-  // second set of scale-factor columns nor copying a stage ahead of its MMAs was measurably
-  // faster: the copies and the MMAs of one issuing thread execute in order.)
+  // Tensor memory columns: two accumulators, then two sets of one stage's scale factors. The
+  // copies into a set are issued by a thread of their own, a stage ahead of the MMAs that read
+  // the other set: issued by the MMA thread itself they execute in order with its MMAs, and
+  // cost as much as those.
   static constexpr int kAccCols = 2 * BLOCK_N;
   static constexpr int kSfaCols = NVF4 ? kMmasPerStage * 4 : 0;
   static constexpr int kSfbColsPerMma = NVF4 ? kSfbGroups * 4 : 0;
   static constexpr int kSfbCols = kMmasPerStage * kSfbColsPerMma;
   static constexpr int kSfSetCols = kSfaCols + kSfbCols;
-  static constexpr int kUsedCols = kAccCols + kSfSetCols;
+  static constexpr int kUsedCols = kAccCols + 2 * kSfSetCols;
   static constexpr int kTmemCols = kUsedCols <= 32 ? 32 : kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128
                                    : kUsedCols <= 256 ? 256 : 512;
   static_assert(kUsedCols <= 512, "tensor memory holds 512 columns");
@@ -180,6 +181,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __shared__ __align__(8) uint64_t acc_full_bar[2];
   __shared__ __align__(8) uint64_t acc_empty_bar[2];
   __shared__ __align__(8) uint64_t tile_done_bar[2];  // epilogue -> pushers: the tile is in this GPU's matrix
+  __shared__ __align__(8) uint64_t sf_full_bar[2];    // NVFP4: a set of scale factors is in tensor memory
+  __shared__ __align__(8) uint64_t sf_empty_bar[2];   // NVFP4: the MMAs that read the set are done
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile uint32_t abort_flag;
 
@@ -208,6 +211,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // the accumulator too, which keeps the epilogue from running two tiles ahead of them.
       mbar_init(&acc_empty_bar[s], (kEpilogueWarps + (scatter ? kPusherWarps : 0)) * CTAS);
       mbar_init(&tile_done_bar[s], kEpilogueWarps);
+      mbar_init(&sf_full_bar[s], 1);
+      mbar_init(&sf_empty_bar[s], 1);
     }
     fence_barrier_init();
   }
@@ -331,30 +336,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       constexpr uint64_t kStageStep = Cfg::kStageBytes >> 4;
       constexpr uint64_t kMmaStep = kMmaKBytes >> 4;
       constexpr uint64_t kSfTileStep = kSfTileBytes >> 4;
-      // NVFP4: one stage's scale factors go shared -> tensor memory right before its MMAs.
-      auto copy_scale_factors = [&](int st) {
-        const uint64_t sfa_desc = sfa_desc0 + st * kStageStep;
-        const uint64_t sfb_desc = sfb_desc0 + st * kStageStep;
-        const uint32_t sfa_tmem = tmem_base + Cfg::kAccCols;
-        const uint32_t sfb_tmem = sfa_tmem + Cfg::kSfaCols;
-#pragma unroll
-        for (int j = 0; j < kMmasPerStage; ++j) {
-          if constexpr (CTAS == 2) {
-            tmem_cp_sf_pair(sfa_tmem + j * 4, sfa_desc + j * kSfTileStep);
-          } else {
-            tmem_cp_sf(sfa_tmem + j * 4, sfa_desc + j * kSfTileStep);
-          }
-#pragma unroll
-          for (int g = 0; g < Cfg::kSfbGroups; ++g) {
-            const uint64_t d = sfb_desc + (g * kMmasPerStage + j) * kSfTileStep;
-            if constexpr (CTAS == 2) {
-              tmem_cp_sf_pair(sfb_tmem + j * Cfg::kSfbColsPerMma + g * 4, d);
-            } else {
-              tmem_cp_sf(sfb_tmem + j * Cfg::kSfbColsPerMma + g * 4, d);
-            }
-          }
-        }
-      };
+      (void)sfa_desc0;
+      (void)sfb_desc0;
+      (void)kSfTileStep;
+      uint32_t sf_it = 0;  // NVFP4: K stages so far, over all tiles: picks the scale-factor set and its phase
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -385,12 +370,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint64_t adesc = adesc0 + stage * kStageStep;
           const uint64_t bdesc = bdesc0 + stage * kStageStep;
           if constexpr (NVF4) {
-            const uint32_t sfa_tmem = tmem_base + Cfg::kAccCols;
+            const uint32_t sf_set = sf_it & 1;
+            const uint32_t sfa_tmem = tmem_base + Cfg::kAccCols + sf_set * Cfg::kSfSetCols;
             const uint32_t sfb_tmem = sfa_tmem + Cfg::kSfaCols;
 #ifdef FLSM100_PROBE
             if (!(p.probe & 8))  // timing probe: no scale-factor copies
 #endif
-              copy_scale_factors(stage);
+            {
+              if (!mbar_wait(&sf_full_bar[sf_set], (sf_it >> 1) & 1, &abort_flag)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after_sync();
+            }
 #pragma unroll
             for (int j = 0; j < kMmasPerStage; ++j) {
               if constexpr (CTAS == 2) {
@@ -412,6 +404,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
           }
           commit_to(&empty_bar[stage]);
+          if constexpr (NVF4) {
+            commit_to(&sf_empty_bar[sf_it & 1]);
+            ++sf_it;
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -419,6 +415,75 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         if (!ok) break;
         commit_to(&acc_full_bar[acc]);
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(p.status, 0u, static_cast<uint32_t>(kStatusMmaTimeout));
+      }
+    }
+  } else if (NVF4 && warp == kPusherWarp0) {
+    // ------------------------------------------------------------------ scale-factor copier (NVFP4)
+    // One thread of the leader moves every stage's scale factors shared -> tensor memory, into
+    // the set the MMAs are not reading, and hands the set over with a commit.
+    bool copies = lane == 0 && leader;
+#ifdef FLSM100_PROBE
+    if (p.probe & 8) copies = false;  // timing probe: no scale-factor copies
+#endif
+    if (copies) {
+      constexpr uint64_t kStageStep = Cfg::kStageBytes >> 4;
+      constexpr uint64_t kSfTileStep = kSfTileBytes >> 4;
+      const uint64_t sfa_desc0 = umma_desc_sf(smem_u32(stage_sfa(0)));
+      const uint64_t sfb_desc0 = umma_desc_sf(smem_u32(stage_sfb(0)));
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const uint32_t set = it & 1;
+          if (!mbar_wait(&full_bar[stage], phase, &abort_flag) ||
+              !mbar_wait(&sf_empty_bar[set], ((it >> 1) & 1) ^ 1, &abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint64_t sfa_desc = sfa_desc0 + stage * kStageStep;
+          const uint64_t sfb_desc = sfb_desc0 + stage * kStageStep;
+          const uint32_t sfa_tmem = tmem_base + Cfg::kAccCols + set * Cfg::kSfSetCols;
+          const uint32_t sfb_tmem = sfa_tmem + Cfg::kSfaCols;
+#pragma unroll
+          for (int j = 0; j < kMmasPerStage; ++j) {
+#ifdef FLSM100_PROBE
+            if ((p.probe & 32) && j > 0) break;  // timing probe: a twelfth of the copies
+#endif
+            if constexpr (CTAS == 2) {
+              tmem_cp_sf_pair(sfa_tmem + j * 4, sfa_desc + j * kSfTileStep);
+            } else {
+              tmem_cp_sf(sfa_tmem + j * 4, sfa_desc + j * kSfTileStep);
+            }
+#ifdef FLSM100_PROBE
+            if (p.probe & 32) break;
+#endif
+#pragma unroll
+            for (int g = 0; g < Cfg::kSfbGroups; ++g) {
+              const uint64_t d = sfb_desc + (g * kMmasPerStage + j) * kSfTileStep;
+              if constexpr (CTAS == 2) {
+                tmem_cp_sf_pair(sfb_tmem + j * Cfg::kSfbColsPerMma + g * 4, d);
+              } else {
+                tmem_cp_sf(sfb_tmem + j * Cfg::kSfbColsPerMma + g * 4, d);
+              }
+            }
+          }
+          if constexpr (CTAS == 2) {
+            umma_commit_pair_both(&sf_full_bar[set]);
+          } else {
+            umma_commit(&sf_full_bar[set]);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
       }
       if (!ok) {
         abort_flag = 1;

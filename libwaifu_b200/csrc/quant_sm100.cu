@@ -316,6 +316,85 @@ __global__ void __launch_bounds__(256) ln_modulate_quantize_kernel(const uint16_
   }
 }
 
+// ---- swiglu -> per-row e4m3, one pass -----------------------------------------------------------
+
+// flint's swiglu on one element pair (flint/cpu/glu.cc:36-67): the first half of the row is the
+// gate, the second the value; silu(g) * v with silu(g) = g / (1 + exp(-g)), fp32, narrowed to the
+// row's 16-bit type as the operator's output is.
+__device__ __forceinline__ uint16_t swiglu16(uint16_t gate, uint16_t value, int is_bf16) {
+  const float g = widen(gate, is_bf16);
+  const float silu = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
+  return narrow(__fmul_rn(silu, widen(value, is_bf16)), is_bf16);
+}
+
+// One CTA of 256 threads per row of (2 h): VPT vectors of the gate half and VPT of the value half
+// per thread (h <= 2048 VPT), the gated row kept in registers as 16-bit values between the amax
+// reduction and the quantisation. One read of the input, one write of the codes.
+template <int VPT>
+__global__ void __launch_bounds__(256) swiglu_quantize_reg_kernel(const uint16_t *__restrict__ x, int is_bf16, int h,
+                                                                uint8_t *__restrict__ codes,
+                                                                float *__restrict__ row_scales) {
+  griddep_wait();
+  __shared__ float red[8];
+  const int64_t row = blockIdx.x;
+  const uint4 *gv = reinterpret_cast<const uint4 *>(x + row * 2 * h);
+  const uint4 *vv = reinterpret_cast<const uint4 *>(x + row * 2 * h + h);
+  uint2 *cv = reinterpret_cast<uint2 *>(codes + row * h);
+  const int nvec = h / 8;
+  uint4 gq[VPT], vq[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * 256;
+    gq[i] = (v < nvec) ? gv[v] : make_uint4(0, 0, 0, 0);
+    vq[i] = (v < nvec) ? vv[v] : make_uint4(0, 0, 0, 0);
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const uint32_t g[4] = {gq[i].x, gq[i].y, gq[i].z, gq[i].w};
+    const uint32_t v[4] = {vq[i].x, vq[i].y, vq[i].z, vq[i].w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint16_t lo = swiglu16(static_cast<uint16_t>(g[j] & 0xffff), static_cast<uint16_t>(v[j] & 0xffff), is_bf16);
+      const uint16_t hi = swiglu16(static_cast<uint16_t>(g[j] >> 16), static_cast<uint16_t>(v[j] >> 16), is_bf16);
+      amax = fmaxf(amax, fmaxf(fabsf(widen(lo, is_bf16)), fabsf(widen(hi, is_bf16))));
+      o[j] = lo | (static_cast<uint32_t>(hi) << 16);
+    }
+    gq[i] = make_uint4(o[0], o[1], o[2], o[3]);  // zero padding gates to zero
+  }
+  amax = block_max(amax, red);
+  const float qscale = __fdiv_rn(amax, 448.0f);
+  const float inv = __frcp_rn(qscale > 0.0f ? qscale : 1.0f);
+  if (threadIdx.x == 0) row_scales[row] = qscale;
+  griddep_launch_dependents();
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < nvec) cv[v] = e4m3x8_of(gq[i], is_bf16, inv);
+  }
+}
+
+// Any length and alignment: the gated value is computed twice.
+__global__ void __launch_bounds__(256) swiglu_quantize_kernel(const uint16_t *__restrict__ x, int is_bf16, int h,
+                                                            uint8_t *__restrict__ codes,
+                                                            float *__restrict__ row_scales) {
+  griddep_wait();
+  __shared__ float red[8];
+  const int64_t row = blockIdx.x;
+  const uint16_t *xr = x + row * 2 * h;
+  float amax = 0.0f;
+  for (int i = threadIdx.x; i < h; i += blockDim.x) amax = fmaxf(amax, fabsf(widen(swiglu16(xr[i], xr[i + h], is_bf16), is_bf16)));
+  amax = block_max(amax, red);
+  const float qscale = __fdiv_rn(amax, 448.0f);
+  const float inv = __frcp_rn(qscale > 0.0f ? qscale : 1.0f);
+  if (threadIdx.x == 0) row_scales[row] = qscale;
+  griddep_launch_dependents();
+  for (int i = threadIdx.x; i < h; i += blockDim.x) {
+    codes[row * h + i] = e4m3_of(__fmul_rn(widen(swiglu16(xr[i], xr[i + h], is_bf16), is_bf16), inv));
+  }
+}
+
 __global__ void __launch_bounds__(128) quantize_fp8_rows_f32_kernel(const float *__restrict__ w, int k,
                                                                   uint8_t *__restrict__ codes,
                                                                   float *__restrict__ scales) {
@@ -561,6 +640,33 @@ cudaError_t ln_modulate_quantize_fp8(const void *x, int is_bf16, int m, int k, c
     e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<8>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
   } else {
     e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_kernel, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
+  }
+  ++g_helper_launches;
+  return e;
+}
+
+cudaError_t swiglu_quantize_fp8(const void *x, int is_bf16, int m, int h, uint8_t *codes, float *row_scales,
+                                cudaStream_t stream) {
+  const bool vec = aligned16(x) && aligned16(codes) && (h % 8 == 0);
+  const uint16_t *xs = static_cast<const uint16_t *>(x);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(m), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e;
+  if (vec && h <= 2048 * 2) {
+    e = cudaLaunchKernelEx(&cfg, swiglu_quantize_reg_kernel<2>, xs, is_bf16, h, codes, row_scales);
+  } else if (vec && h <= 2048 * 4) {
+    e = cudaLaunchKernelEx(&cfg, swiglu_quantize_reg_kernel<4>, xs, is_bf16, h, codes, row_scales);
+  } else if (vec && h <= 2048 * 7) {
+    e = cudaLaunchKernelEx(&cfg, swiglu_quantize_reg_kernel<7>, xs, is_bf16, h, codes, row_scales);
+  } else {
+    e = cudaLaunchKernelEx(&cfg, swiglu_quantize_kernel, xs, is_bf16, h, codes, row_scales);
   }
   ++g_helper_launches;
   return e;

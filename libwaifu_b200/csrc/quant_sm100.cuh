@@ -44,6 +44,12 @@ cudaError_t quantize_nvfp4_weight_f32(const float *w, int rows, int k, uint8_t *
 // Plain (rows, k/16) scale factors -> tile layout (`sf_tiled` zeroed by the caller).
 cudaError_t pack_scale_factors(const uint8_t *sf_plain, int rows, int k, uint8_t *sf_tiled, cudaStream_t stream);
 
+// flint's swiglu (first half of the last dimension the gate, second the value; silu(g) * v in fp32,
+// narrowed to 16 bits: flint/cpu/glu.cc:36-67) on x (m, 2 h), then per-row e4m3 of the (m, h)
+// result exactly as quantize_fp8_act. One pass; the gated row never reaches memory.
+cudaError_t swiglu_quantize_fp8(const void *x, int is_bf16, int m, int h, uint8_t *codes, float *row_scales,
+                                cudaStream_t stream);
+
 // codes -> fp16 / bf16 values (exact), the widening flint's kernel does in registers
 // (flint/cuda/gemm_fp8_cutlass.cu:20-29).
 cudaError_t widen_e4m3(const uint8_t *codes, int64_t numel, void *out16, int out_bf16, cudaStream_t stream);

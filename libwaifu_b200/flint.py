@@ -114,6 +114,8 @@ def lib() -> ctypes.CDLL:
     L.fl_fp8_layernorm_quantize.restype = c_int32
     L.fl_fp8_linear_quantized.argtypes = [V, V, V, V, V, V, c_int32, V]
     L.fl_fp8_linear_quantized.restype = c_int32
+    L.fl_fp8_swiglu_quantize.argtypes = [V, V, V]
+    L.fl_fp8_swiglu_quantize.restype = c_int32
     L.fl_qk_norm_rope.argtypes = [V, V, V, V, V, ctypes.c_float, c_int32]
     L.fl_qk_norm_rope.restype = c_int32
     L.fl_sm100_set_device.argtypes = [c_int32]
@@ -468,6 +470,20 @@ def fp8_layernorm_quantize(x: Tensor, scale: Optional[Tensor] = None, shift: Opt
         row_scales = Tensor.empty((rows,), DType.FLOAT)
     check(lib().fl_fp8_layernorm_quantize(x.raw(), scale.raw() if scale else None, shift.raw() if shift else None,
                                           float(eps), codes.raw(), row_scales.raw()))
+    return codes, row_scales
+
+
+def fp8_swiglu_quantize(x: Tensor, codes: Optional[Tensor] = None, row_scales: Optional[Tensor] = None):
+    """silu(gate) * value over the two halves of the last dimension, narrowed to x's type, then
+    per-row e4m3 in the same pass; returns (codes, row_scales)."""
+    rows = 1
+    for d in x.shape[:-1]:
+        rows *= d
+    if codes is None:
+        codes = Tensor.empty(tuple(x.shape[:-1]) + (x.shape[-1] // 2,), DType.FP8E4M3)
+    if row_scales is None:
+        row_scales = Tensor.empty((rows,), DType.FLOAT)
+    check(lib().fl_fp8_swiglu_quantize(x.raw(), codes.raw(), row_scales.raw()))
     return codes, row_scales
 
 

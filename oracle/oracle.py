@@ -193,6 +193,19 @@ def layernorm_modulate(x16: np.ndarray, scale16, shift16, eps: float, is_bf16: b
     return narrow(y, is_bf16)
 
 
+def swiglu(x16: np.ndarray, is_bf16: bool) -> np.ndarray:
+    """flint's swiglu on (m, 2 h) bit patterns -> (m, h): the first half of a row is the gate, the
+    second the value; `g / (1 + exp(-g)) * v` in float32, each operation rounded, then the cast to
+    the 16-bit type (flint/cpu/glu.cc:36-67)."""
+    x16 = np.ascontiguousarray(x16, dtype=np.uint16)
+    h = x16.shape[1] // 2
+    g, v = widen(x16[:, :h], is_bf16), widen(x16[:, h:], is_bf16)
+    with np.errstate(over="ignore"):
+        e = np.exp(-g.astype(np.float64)).astype(np.float32)  # the correctly rounded float32 exponential
+        silu = (g / (np.float32(1.0) + e).astype(np.float32)).astype(np.float32)
+    return narrow((silu * v).astype(np.float32), is_bf16)
+
+
 def qk_norm_rope(qkv16: np.ndarray, cos: np.ndarray, sin: np.ndarray, heads: int, eps: float, is_bf16: bool,
                  q_weight16=None, k_weight16=None) -> np.ndarray:
     """The step between a fused q/k/v projection and attention on (rows, 3 * heads * head_dim) bit
