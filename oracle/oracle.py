@@ -275,6 +275,9 @@ class _Ref:
         L.fl_tensor_view_create.argtypes = [c_void_p, POINTER(c_int32), POINTER(c_int32), c_int32, c_int64, POINTER(c_void_p)]
         L.fl_tensor_view_destroy.argtypes = [c_void_p]; L.fl_tensor_view_destroy.restype = None
         L.fl_matmul.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p]
+        L.fl_layer_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p]
+        L.fl_rms_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_float, c_void_p]
+        L.fl_swiglu.argtypes = [c_void_p, c_void_p, c_void_p]
         try:
             L.fl_set_log_level.argtypes = [c_int32]
             L.fl_set_log_level.restype = None
@@ -314,6 +317,44 @@ class _Ref:
             for d in (da, db, do):
                 self.L.fl_tensor_data_destroy(d)
         return out
+
+
+    def _unary(self, call, x: np.ndarray, out_cols: int, extra=()) -> np.ndarray:
+        """Runs one of the reference's row operators on a float32 (rows, cols) array."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        rows, cols = x.shape
+        out = np.empty((rows, out_cols), dtype=np.float32)
+        dx, vx = self._view(x, (rows, cols), (cols, 1))
+        do, vo = self._view(out, (rows, out_cols), (out_cols, 1))
+        held = [(dx, vx), (do, vo)]
+        try:
+            args = []
+            for e in extra:
+                if isinstance(e, np.ndarray):
+                    d, v = self._view(e, e.shape, (1,))
+                    held.append((d, v))
+                    args.append(v)
+                else:
+                    args.append(e)
+            self._check(call(vx, args, vo))
+        finally:
+            for d, v in held:
+                self.L.fl_tensor_view_destroy(v)
+                self.L.fl_tensor_data_destroy(d)
+        return out
+
+    def layer_norm(self, x: np.ndarray, eps: float) -> np.ndarray:
+        """fl_layer_norm without weight and bias (flint/capi.h:320-328)."""
+        return self._unary(lambda vx, a, vo: self.L.fl_layer_norm(self.ops, vx, None, None, c_float(eps), vo), x, x.shape[1])
+
+    def rms_norm(self, x: np.ndarray, weight: np.ndarray, eps: float) -> np.ndarray:
+        """fl_rms_norm (flint/capi.h:312-318); the weight is required there."""
+        w = np.ascontiguousarray(weight, dtype=np.float32)
+        return self._unary(lambda vx, a, vo: self.L.fl_rms_norm(self.ops, vx, a[0], c_float(eps), vo), x, x.shape[1], (w,))
+
+    def swiglu(self, x: np.ndarray) -> np.ndarray:
+        """fl_swiglu (flint/capi.h:517-519)."""
+        return self._unary(lambda vx, a, vo: self.L.fl_swiglu(self.ops, vx, vo), x, x.shape[1] // 2)
 
 
 _ref = None

@@ -223,3 +223,58 @@ def test_nvfp4_quantizer_roundtrip_properties(oracle):
     blocks_d = deq.reshape(16, 4, 16)
     amax = np.max(np.abs(blocks_w), axis=2, keepdims=True)
     assert np.all(np.abs(blocks_d - blocks_w) <= amax * (1.0 / 6.0 + 0.07) + 1e-12)
+
+
+# ---- the block-step restatements against the reference's own CPU operators ----------------------
+
+def _needs_ref(oracle):
+    if not oracle.have_ref():
+        pytest.skip("the reference's CPU build is not present")
+
+
+def test_layernorm_restatement_against_the_reference_operator(oracle):
+    """layernorm_modulate with no scale and shift is the reference's fl_layer_norm narrowed to 16
+    bits. The reference sums in float32 in row order and the restatement in float64, so a value on
+    a 16-bit rounding boundary may fall either way: at most one step, nearly all identical."""
+    _needs_ref(oracle)
+    rng = np.random.default_rng(101)
+    for k in (16, 1040, 3072):
+        x16 = oracle.narrow((rng.standard_normal((33, k)) * 1.7 + 0.3).astype(np.float32), True)
+        want = oracle.narrow(oracle.ref().layer_norm(oracle.widen(x16, True), 1e-6), True)
+        got = oracle.layernorm_modulate(x16, None, None, 1e-6, True)
+        assert np.mean(got == want) >= 0.995
+        g, w = oracle.widen(got, True), oracle.widen(want, True)
+        assert np.all(np.abs(g - w) <= np.maximum(np.abs(w), 2.0 ** -14) * 2.0 ** -7 * 1.01)
+    # a constant row: the variance is zero or a rounding residue, eps carries the root
+    x16 = oracle.narrow(np.full((2, 64), 3.0, np.float32), True)
+    assert not oracle.widen(oracle.layernorm_modulate(x16, None, None, 1e-6, True), True).any()
+    assert not oracle.ref().layer_norm(oracle.widen(x16, True), 1e-6).any()
+
+
+def test_rms_norm_restatement_against_the_reference_operator(oracle):
+    """qk_norm_rope with cos = 1, sin = 0 is the reference's fl_rms_norm per head, narrowed (the
+    restatement multiplies by one reciprocal per head where the reference divides per element)."""
+    _needs_ref(oracle)
+    rng = np.random.default_rng(102)
+    heads, head_dim, rows = 3, 128, 20
+    qkv = oracle.narrow((rng.standard_normal((rows, 3 * heads * head_dim)) * 2).astype(np.float32), True)
+    w = oracle.narrow((1.0 + 0.1 * rng.standard_normal(head_dim)).astype(np.float32), True)
+    ones, zeros = np.ones((5, head_dim // 2), np.float32), np.zeros((5, head_dim // 2), np.float32)
+    got = oracle.qk_norm_rope(qkv, ones, zeros, heads, 1e-6, True, w, w)
+    x = oracle.widen(qkv[:, :2 * heads * head_dim], True).reshape(rows * 2 * heads, head_dim)
+    want = oracle.narrow(oracle.ref().rms_norm(x, oracle.widen(w, True), 1e-6), True).reshape(rows, 2 * heads * head_dim)
+    assert np.array_equal(got[:, 2 * heads * head_dim:], qkv[:, 2 * heads * head_dim:])
+    assert np.mean(got[:, :2 * heads * head_dim] == want) >= 0.99
+    g, r = oracle.widen(got[:, :2 * heads * head_dim], True), oracle.widen(want, True)
+    assert np.all(np.abs(g - r) <= np.maximum(np.abs(r), 2.0 ** -14) * 2.0 ** -7 * 1.01)
+
+
+def test_swiglu_restatement_against_the_reference_operator(oracle):
+    _needs_ref(oracle)
+    rng = np.random.default_rng(103)
+    x16 = oracle.narrow((rng.standard_normal((17, 2 * 520)) * 3).astype(np.float32), True)
+    want = oracle.narrow(oracle.ref().swiglu(oracle.widen(x16, True)), True)
+    got = oracle.swiglu(x16, True)
+    assert np.mean(got == want) >= 0.995
+    g, w = oracle.widen(got, True), oracle.widen(want, True)
+    assert np.all(np.abs(g - w) <= np.maximum(np.abs(w), 2.0 ** -14) * 2.0 ** -7 * 1.01)
