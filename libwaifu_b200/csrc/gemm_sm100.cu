@@ -947,6 +947,12 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
       *why = "scale-factor base is not 16-byte aligned";
       return cudaErrorInvalidValue;
     }
+#ifdef FLSM100_PROBE
+    if (const char *v = std::getenv("FLSM100_NVF4_BLOCK_N")) {  // development builds: the instruction's time against N
+      if (std::atoi(v) == 128) return launch_one<kKindNvf4, 128, 2>(a, kp, row_bytes, why);
+      if (std::atoi(v) == 64) return launch_one<kKindNvf4, 64, 2>(a, kp, row_bytes, why);
+    }
+#endif
     return pair ? launch_one<kKindNvf4, 192, 2>(a, kp, row_bytes, why) : launch_one<kKindNvf4, 192, 1>(a, kp, row_bytes, why);
   }
   const bool narrow = a.n <= 128 || skinny;
