@@ -388,6 +388,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               if constexpr (CTAS == 2) {
                 umma_nvf4_ss_pair(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, (kb | j) != 0 ? 1u : 0u,
                                   sfa_tmem + j * 4, sfb_tmem + j * Cfg::kSfbColsPerMma + sfb_skip);
+#ifdef FLSM100_PROBE
+                if (p.probe & 64) {  // timing probe: the same instruction again into the other accumulator
+                  umma_nvf4_ss_pair(tmem_base + (acc ^ 1) * BLOCK_N, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc,
+                                    (kb | j) != 0 ? 1u : 0u, sfa_tmem + j * 4, sfb_tmem + j * Cfg::kSfbColsPerMma + sfb_skip);
+                }
+#endif
               } else {
                 umma_nvf4_ss(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, (kb | j) != 0 ? 1u : 0u,
                              sfa_tmem + j * 4, sfb_tmem + j * Cfg::kSfbColsPerMma + sfb_skip);
