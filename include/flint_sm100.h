@@ -254,7 +254,7 @@ FLAPI int32_t fl_fp8_linear_quantized(fl_tensor_view_t codes, fl_tensor_view_t r
 
 /* The step between the fused q/k/v projection and attention, in place on the projection's output
  * qkv <float16|bfloat16>(..., 3 * heads * head_dim) (q heads, k heads, v heads along the last
- * dimension; head_dim 64, 128 or 256; 8-byte aligned): per row and q or k head,
+ * dimension; head_dim 64, 128 or 256; every operand 16-byte aligned): per row and q or k head,
  *   n = round16( x * w * (1 / sqrt(mean(x^2) + eps)) )   flint's rmsNorm, flint/cpu/normalizations.cc:33-70,
  *                                                   one reciprocal per head instead of a division per
  *                                                   element; w = q_weight / k_weight (head_dim) or NULL

@@ -14,7 +14,7 @@ namespace flsm100 {
 // type as the norm's output is, then the rotation of even/odd pairs
 // (left = even cos - odd sin, right = even sin + odd cos: waifu/src/krea2/dit.rs:260-275) in fp32
 // with one rounding. Row r has position r % tokens; cos and sin are <float>(tokens, head_dim / 2).
-// The v third is not touched. head_dim 64, 128 or 256; qkv 8-byte aligned.
+// The v third is not touched. head_dim 64, 128 or 256; every operand 16-byte aligned.
 cudaError_t qk_norm_rope(void *qkv, int is_bf16, int64_t rows, int heads, int head_dim, int tokens,
                          const void *q_weight, const void *k_weight, const float *cos, const float *sin, float eps,
                          cudaStream_t stream);

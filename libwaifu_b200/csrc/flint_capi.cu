@@ -868,6 +868,27 @@ int32_t fl_matmul_add(fl_operators_t operators, fl_tensor_view_t a_h, fl_tensor_
     const int m = static_cast<int>(m64);
     const int is_bf16 = dtype_of(a) == FL_DTYPE_BFLOAT16;
 
+    // A handful of rows (the reference keeps a GEMV for this, flint/cuda/matvec.cu): one
+    // bandwidth-shaped launch with the bias or residual in its epilogue, no scratch.
+    if (m <= 16) {
+      static const bool no_skinny = []() {
+        const char *v = std::getenv("FLINT_SM100_NO_SKINNY");
+        return v && v[0] == '1';
+      }();
+      AddendPlan quick;
+      std::vector<int32_t> bs;
+      std::vector<int64_t> bt;
+      if (addend) quick = plan_addend(*addend, out, &bs, &bt);
+      if (!no_skinny && !quick.needs_expand &&
+          skinny_w16_supported(m, n, k, raw_ptr(a), raw_ptr(b), raw_ptr(out), quick.residual != nullptr)) {
+        cuda_check(skinny_w16_matmul(raw_ptr(a), is_bf16, m, n, k, raw_ptr(b), quick.bias, quick.residual, quick.residual_rows,
+                                     quick.residual_ld, raw_ptr(out), status_word(), 0),
+                   "few-row matmul");
+        ++g_gemm_launches;
+        return clear_error();
+      }
+    }
+
     Scratch scratch;
     size_t a_off = 0, b_off = 0;
     const bool a_misaligned = !aligned16(raw_ptr(a));
@@ -1453,7 +1474,12 @@ int32_t fl_qk_norm_rope(fl_tensor_view_t qkv_h, fl_tensor_view_t q_weight_h, fl_
     for (const fl_tensor_view_impl_t *v : {&qkv, &cos, &sin}) {
       if (device_of(*v) != FL_DEVICE_CUDA) invalid("the operands are not all on cuda");
     }
-    if (reinterpret_cast<uintptr_t>(raw_ptr(qkv)) & 7) invalid("qkv does not start on an 8-byte boundary");
+    for (const fl_tensor_view_impl_t *v : {&qkv, &cos, &sin}) {
+      if (!aligned16(raw_ptr(*v))) invalid("qkv, cos and sin have to start on 16-byte boundaries");
+    }
+    for (const fl_tensor_view_impl_t *w : weights) {
+      if (w && !aligned16(raw_ptr(*w))) invalid("a norm weight does not start on a 16-byte boundary");
+    }
     require_kernels();
     if (rows == 0) return clear_error();
     if (rows > INT32_MAX) invalid("qkv has more rows than the kernel can index");

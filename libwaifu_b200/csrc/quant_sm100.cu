@@ -194,11 +194,12 @@ __device__ __forceinline__ uint16_t modulated(float v, float mean, float rstd, c
   return narrow(y, is_bf16);
 }
 
-// One CTA of 256 threads per row, the row in registers throughout (k <= 2048 VPT): one read of x,
+// One CTA of THREADS threads per row, the row in registers throughout (k <= 8 THREADS VPT): one read of x,
 // one block reduction for the two sums of the statistics, one for amax of the modulated 16-bit
-// row, one write of the codes.
-template <int VPT>
-__global__ void __launch_bounds__(256) ln_modulate_quantize_reg_kernel(const uint16_t *__restrict__ x, int is_bf16, int k,
+// row, one write of the codes. Short rows take 128 threads: more rows in flight per SM, which is
+// what a kernel made of a load, two barriers and a store needs to fill the memory pipe.
+template <int VPT, int THREADS>
+__global__ void __launch_bounds__(THREADS) ln_modulate_quantize_reg_kernel(const uint16_t *__restrict__ x, int is_bf16, int k,
                                                                      const uint16_t *__restrict__ scale,
                                                                      const uint16_t *__restrict__ shift,
                                                                      int rows_per_group, float eps,
@@ -217,7 +218,7 @@ __global__ void __launch_bounds__(256) ln_modulate_quantize_reg_kernel(const uin
   uint4 q[VPT];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = threadIdx.x + i * 256;
+    const int v = threadIdx.x + i * THREADS;
     q[i] = (v < nvec) ? xv[v] : make_uint4(0, 0, 0, 0);
   }
   float sum = 0.0f, sq = 0.0f;  // the zero padding of the last vectors adds nothing to either
@@ -241,7 +242,7 @@ __global__ void __launch_bounds__(256) ln_modulate_quantize_reg_kernel(const uin
   const uint4 *tv = reinterpret_cast<const uint4 *>(t);
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = threadIdx.x + i * 256;
+    const int v = threadIdx.x + i * THREADS;
     if (v < nvec) {
       const uint32_t w[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
       const uint4 s4 = s ? __ldg(sv + v) : make_uint4(0, 0, 0, 0);
@@ -273,7 +274,7 @@ __global__ void __launch_bounds__(256) ln_modulate_quantize_reg_kernel(const uin
   griddep_launch_dependents();
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int v = threadIdx.x + i * 256;
+    const int v = threadIdx.x + i * THREADS;
     if (v < nvec) cv[v] = e4m3x8_of(q[i], is_bf16, inv);
   }
 }
@@ -632,12 +633,15 @@ cudaError_t ln_modulate_quantize_fp8(const void *x, int is_bf16, int m, int k, c
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e;
-  if (vec && k <= 2048 * 2) {
-    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<2>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
+  if (vec && k <= 1024 * 3) {
+    cfg.blockDim = dim3(128, 1, 1);
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<3, 128>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
+  } else if (vec && k <= 2048 * 2) {
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<2, 256>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
   } else if (vec && k <= 2048 * 4) {
-    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<4>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<4, 256>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
   } else if (vec && k <= 2048 * 8) {
-    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<8>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<8, 256>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
   } else {
     e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_kernel, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
   }

@@ -108,7 +108,8 @@ struct SkinnyParams {
   int act;
   uint16_t *out;         // (m, n)
   int m, n, k;
-  int k_pad;             // every K position a step can touch (>= k, a multiple of 64)
+  int kb;                // bytes of a weight row: k for e4m3, 2 k for a 16-bit weight
+  int k_pad;             // every K position a step can touch, in elements (>= k)
   int pitch_x;           // bytes between activation rows in shared memory
   int x_vec;             // x is 16-byte aligned: 16-byte reads of the activation
   int out_pair;          // out is 4-byte aligned: two adjacent results go out as one store
@@ -205,7 +206,9 @@ __device__ __forceinline__ void widen_e4m3x4(uint32_t w, uint32_t &p01, uint32_t
 
 // QUANT: the activation rows are quantised per token to e4m3 first (and kept as halves); else
 // they stay as they are. BF16: the product runs on bfloat16 instructions (never with QUANT).
-template <bool QUANT, bool BF16>
+// W16: the weight itself is 16-bit (the unquantised linear layer of fl_matmul): no widening, eight
+// K positions per 16-byte piece instead of sixteen.
+template <bool QUANT, bool BF16, bool W16>
 __global__ void __launch_bounds__(kThreads, 2) skinny_fp8_kernel(const SkinnyParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int x_bytes = (p.m * p.pitch_x + 127) / 128 * 128;
@@ -271,16 +274,16 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_fp8_kernel(const SkinnyPar
           break;
         }
         const int k0 = kc * chunk_bytes;
-        const uint32_t bytes = static_cast<uint32_t>(min(chunk_bytes, p.k - k0));
+        const uint32_t bytes = static_cast<uint32_t>(min(chunk_bytes, p.kb - k0));
         if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], bytes * rows);
         __syncwarp();
         uint8_t *dst = ring + stage * p.stage_stride;
         if (p.one_copy) {
           // A stage holds whole channels, which are contiguous in the weight: one copy for all.
-          if (lane == 0) bulk_load_1d(dst, p.w + static_cast<long long>(row0) * p.k, bytes * rows, &full_bar[stage]);
+          if (lane == 0) bulk_load_1d(dst, p.w + static_cast<long long>(row0) * p.kb, bytes * rows, &full_bar[stage]);
         } else {
           for (int r = lane; r < rows; r += 32) {
-            bulk_load_1d(dst + r * pitch_w, p.w + static_cast<long long>(row0 + r) * p.k + k0, bytes, &full_bar[stage]);
+            bulk_load_1d(dst + r * pitch_w, p.w + static_cast<long long>(row0 + r) * p.kb + k0, bytes, &full_bar[stage]);
           }
         }
         armed |= 1u << stage;
@@ -318,6 +321,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_fp8_kernel(const SkinnyPar
   const long long probe_start = clock64();
   long long probe_wait = 0, probe_prologue = 0;
 #endif
+  constexpr float kUnfoldStage = (BF16 || W16) ? 1.0f : 256.0f;  // see kUnfold below
   // ---- 0. this CTA's channel scales and bias: issued now, stored after the activation rows
   const bool vector_scale = p.col_scale && !p.col_scale_scalar;
   auto channel_of = [&](int i) {  // i = local unit * unit_rows + channel in unit; -1 when there is none
@@ -392,12 +396,12 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_fp8_kernel(const SkinnyPar
     }
   }
   if (threadIdx.x < p.cpc) {
-    cs_s[threadIdx.x] = first_cs * (BF16 ? 1.0f : 256.0f);
+    cs_s[threadIdx.x] = first_cs * kUnfoldStage;
     bias_s[threadIdx.x] = first_bias;
   }
   for (int i = threadIdx.x + kConsumers; i < p.cpc; i += kConsumers) {
     const int ch = channel_of(i);
-    cs_s[i] = ((ch >= 0 && vector_scale) ? __ldg(p.col_scale + ch) : 1.0f) * (BF16 ? 1.0f : 256.0f);
+    cs_s[i] = ((ch >= 0 && vector_scale) ? __ldg(p.col_scale + ch) : 1.0f) * kUnfoldStage;
     bias_s[i] = (ch >= 0 && p.bias) ? load16(p.bias, ch, p.is_bf16) : 0.0f;
   }
   if (p.residual) {
@@ -424,7 +428,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_fp8_kernel(const SkinnyPar
   const bool row_hi = g + 8 < p.m;
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
   // The half path multiplies weight values scaled by 2^-8; the scale gives the 2^8 back (exactly).
-  constexpr float kUnfold = BF16 ? 1.0f : 256.0f;
+  constexpr float kUnfold = (BF16 || W16) ? 1.0f : 256.0f;
   const float scalar_scale = ((p.col_scale && p.col_scale_scalar) ? __ldg(p.col_scale) : 1.0f) * kUnfold;
 
   int stage = 0;
@@ -481,33 +485,55 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_fp8_kernel(const SkinnyPar
       // sums are never stored.
       const int kb0 = kc * chunk_bytes + wk * p.slice_bytes + q * 16;  // this thread's K byte in step 0
       const uint8_t *wrow = ring + stage * p.stage_stride + (wn * 8 + g) * pitch_w + wk * p.slice_bytes + q * 16;
-      const uint8_t *xlo = xq + (row_lo ? g : 0) * p.pitch_x + 2 * kb0;
-      const uint8_t *xhi = xq + (row_hi ? g + 8 : 0) * p.pitch_x + 2 * kb0;
+      // the activation's byte offset for weight byte kb0: two bytes per e4m3 byte, one per byte of a 16-bit weight
+      const int xoff = W16 ? kb0 : 2 * kb0;
+      const uint8_t *xlo = xq + (row_lo ? g : 0) * p.pitch_x + xoff;
+      const uint8_t *xhi = xq + (row_hi ? g + 8 : 0) * p.pitch_x + xoff;
 #pragma unroll
       for (int s = 0; s < kSteps; ++s) {
         if (s < steps) {
-          const uint4 wv = *reinterpret_cast<const uint4 *>(wrow + s * kKStep);
-          // 16 elements of row g (and g + 8) for this thread's 16 K positions.
-          const uint4 xa0 = *reinterpret_cast<const uint4 *>(xlo + 2 * s * kKStep);
-          const uint4 xa1 = *reinterpret_cast<const uint4 *>(xlo + 2 * s * kKStep + 16);
-          uint4 xb0 = zero4, xb1 = zero4;
-          if (p.m > 8) {
-            xb0 = *reinterpret_cast<const uint4 *>(xhi + 2 * s * kKStep);
-            xb1 = *reinterpret_cast<const uint4 *>(xhi + 2 * s * kKStep + 16);
-          }
-          const uint32_t al[8] = {xa0.x, xa0.y, xa0.z, xa0.w, xa1.x, xa1.y, xa1.z, xa1.w};
-          const uint32_t ah[8] = {xb0.x, xb0.y, xb0.z, xb0.w, xb1.x, xb1.y, xb1.z, xb1.w};
-          const uint32_t wb[4] = {wv.x, wv.y, wv.z, wv.w};
-          // Instruction i takes K positions 4i..4i+3 of the thread's 16: the first pair is its
-          // "low" half and the second its "high" half, for A and for B alike, so every product
-          // pairs the same physical k whatever order the instruction gives them.
+          uint4 wv = *reinterpret_cast<const uint4 *>(wrow + s * kKStep);
+          if constexpr (W16) {
+            // Past the end of the row the stage holds stale bytes, which as 16-bit floats may be
+            // NaN or infinite and would not multiply the activation's zeros to zero.
+            if (kb0 + s * kKStep >= min(p.kb, (kc + 1) * chunk_bytes)) wv = zero4;
+            // 8 elements of row g (and g + 8) for this thread's 8 K positions; instruction i takes
+            // positions 4i..4i+3, the first pair its "low" half, the second its "high" half.
+            const uint4 xa = *reinterpret_cast<const uint4 *>(xlo + s * kKStep);
+            uint4 xb = zero4;
+            if (p.m > 8) xb = *reinterpret_cast<const uint4 *>(xhi + s * kKStep);
+            float(&c0)[4] = acc[((s & 3) << 1)];
+            float(&c1)[4] = acc[((s & 3) << 1) | 1];
+            if constexpr (BF16) {
+              mma_bf16(c0, xa.x, xb.x, xa.y, xb.y, wv.x, wv.y);
+              mma_bf16(c1, xa.z, xb.z, xa.w, xb.w, wv.z, wv.w);
+            } else {
+              mma_f16(c0, xa.x, xb.x, xa.y, xb.y, wv.x, wv.y);
+              mma_f16(c1, xa.z, xb.z, xa.w, xb.w, wv.z, wv.w);
+            }
+          } else {
+            // 16 elements of row g (and g + 8) for this thread's 16 K positions.
+            const uint4 xa0 = *reinterpret_cast<const uint4 *>(xlo + 2 * s * kKStep);
+            const uint4 xa1 = *reinterpret_cast<const uint4 *>(xlo + 2 * s * kKStep + 16);
+            uint4 xb0 = zero4, xb1 = zero4;
+            if (p.m > 8) {
+              xb0 = *reinterpret_cast<const uint4 *>(xhi + 2 * s * kKStep);
+              xb1 = *reinterpret_cast<const uint4 *>(xhi + 2 * s * kKStep + 16);
+            }
+            const uint32_t al[8] = {xa0.x, xa0.y, xa0.z, xa0.w, xa1.x, xa1.y, xa1.z, xa1.w};
+            const uint32_t ah[8] = {xb0.x, xb0.y, xb0.z, xb0.w, xb1.x, xb1.y, xb1.z, xb1.w};
+            const uint32_t wb[4] = {wv.x, wv.y, wv.z, wv.w};
+            // Instruction i takes K positions 4i..4i+3 of the thread's 16: the first pair is its
+            // "low" half and the second its "high" half, for A and for B alike, so every product
+            // pairs the same physical k whatever order the instruction gives them.
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t w0, w1;
-            widen_e4m3x4<BF16>(wb[i], w0, w1);
-            float(&chain)[4] = acc[((s & 1) << 2) | i];
-            if constexpr (BF16) mma_bf16(chain, al[2 * i], ah[2 * i], al[2 * i + 1], ah[2 * i + 1], w0, w1);
-            else mma_f16(chain, al[2 * i], ah[2 * i], al[2 * i + 1], ah[2 * i + 1], w0, w1);
+            for (int i = 0; i < 4; ++i) {
+              uint32_t w0, w1;
+              widen_e4m3x4<BF16>(wb[i], w0, w1);
+              float(&chain)[4] = acc[((s & 1) << 2) | i];
+              if constexpr (BF16) mma_bf16(chain, al[2 * i], ah[2 * i], al[2 * i + 1], ah[2 * i + 1], w0, w1);
+              else mma_f16(chain, al[2 * i], ah[2 * i], al[2 * i + 1], ah[2 * i + 1], w0, w1);
+            }
           }
         }
       }
@@ -617,7 +643,7 @@ KSplit k_split(int k, int wn_log2) {
 
 // Bytes between the 16-bit activation rows in shared memory: 16 mod 32, so that the 16-byte reads
 // a quarter warp makes of two rows (pieces 32 bytes apart) fall into distinct banks.
-int row_pitch(int k_pad) { return 2 * k_pad + 16; }
+int row_pitch(int k_pad_elements) { return 2 * k_pad_elements + 16; }
 
 struct Geometry {
   int ctas, wn_log2, units, grid, cpc, ep_bytes, x_bytes, stages, stage_stride, pitch_w, one_copy;
@@ -627,24 +653,25 @@ struct Geometry {
 int pick_wn_log2(int k);
 
 // Shared-memory plan of one CTA when `ctas` CTAs share an SM.
-Geometry geometry_with(int m, int n, int k, bool has_residual, int ctas) {
+Geometry geometry_with(int m, int n, int k, int wbytes, bool has_residual, int ctas) {
   Geometry g;
   g.ctas = ctas;
-  g.wn_log2 = pick_wn_log2(k);
+  const int kb = k * wbytes;  // bytes of a weight row
+  g.wn_log2 = pick_wn_log2(kb);
   const int rows = 8 << g.wn_log2;
   const int slots = sm_count_cached() * ctas;
   g.units = (n + rows - 1) / rows;
   g.grid = g.units < slots ? g.units : slots;
   g.cpc = (g.units + g.grid - 1) / g.grid * rows;
   g.ep_bytes = (g.cpc * 8 + (has_residual ? m * g.cpc * 2 : 0) + 127) / 128 * 128;
-  g.ks = k_split(k, g.wn_log2);
-  g.x_bytes = (m * row_pitch(g.ks.k_pad) + 127) / 128 * 128;
+  g.ks = k_split(kb, g.wn_log2);
+  g.x_bytes = (m * row_pitch(g.ks.k_pad / wbytes) + 127) / 128 * 128;
   // With all of K in one stage the channels of a stage are one contiguous piece of the weight and
   // a single large copy brings them; the price is a two-way bank conflict on the weight reads
   // when k is a multiple of 128, far from what limits the kernel. Otherwise a channel's piece is
   // padded to 64 mod 128 bytes so that the reads of two channels miss each other.
   g.one_copy = g.ks.k_chunks == 1 ? 1 : 0;
-  g.pitch_w = g.one_copy ? k : (g.ks.chunk_bytes + 127) / 128 * 128 + 64;
+  g.pitch_w = g.one_copy ? kb : (g.ks.chunk_bytes + 127) / 128 * 128 + 64;
   g.stage_stride = (rows * g.pitch_w + 127) / 128 * 128;
   const long long budget = kSmemBudget / ctas - (ctas > 1 ? 1024 : 0);  // less the per-CTA reserve
   const long long left = budget - kFixedSmem - g.x_bytes - g.ep_bytes;
@@ -655,9 +682,9 @@ Geometry geometry_with(int m, int n, int k, bool has_residual, int ctas) {
 // The consumers are bound by instruction latency, not by issue slots, so two CTAs per SM (twice
 // the warps, half the shared memory each) stream faster than one; a shape whose activation rows
 // leave a half too small for three stages gets one CTA per SM.
-Geometry geometry_for(int m, int n, int k, bool has_residual) {
-  const Geometry two = geometry_with(m, n, k, has_residual, 2);
-  return two.stages >= 3 ? two : geometry_with(m, n, k, has_residual, 1);
+Geometry geometry_for(int m, int n, int k, int wbytes, bool has_residual) {
+  const Geometry two = geometry_with(m, n, k, wbytes, has_residual, 2);
+  return two.stages >= 3 ? two : geometry_with(m, n, k, wbytes, has_residual, 1);
 }
 
 // Channel groups per unit. A channel's K bytes arrive as one bulk copy per stage, and long copies
@@ -668,11 +695,13 @@ int pick_wn_log2(int k) {
   return slices >= 5 ? 0 : slices >= 3 ? 1 : slices == 2 ? 2 : 3;
 }
 
-template <bool QUANT, bool BF16>
+template <bool QUANT, bool BF16, bool W16>
 cudaError_t launch(SkinnyParams &p, cudaStream_t stream) {
+  constexpr int wbytes = W16 ? 2 : 1;
+  p.kb = p.k * wbytes;
   p.x_vec = (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 ? 1 : 0;
   p.out_pair = (reinterpret_cast<uintptr_t>(p.out) & 3) == 0 ? 1 : 0;
-  const Geometry geo = geometry_for(p.m, p.n, p.k, p.residual != nullptr);
+  const Geometry geo = geometry_for(p.m, p.n, p.k, wbytes, p.residual != nullptr);
   p.wn_log2 = geo.wn_log2;
   p.stages = geo.stages;
   p.units = geo.units;
@@ -682,7 +711,7 @@ cudaError_t launch(SkinnyParams &p, cudaStream_t stream) {
   p.k_chunks = geo.ks.k_chunks;
   p.chunk_bytes = geo.ks.chunk_bytes;
   p.slice_bytes = geo.ks.slice_bytes;
-  p.k_pad = geo.ks.k_pad;
+  p.k_pad = geo.ks.k_pad / wbytes;
   p.pitch_x = row_pitch(p.k_pad);
   p.pitch_w = geo.pitch_w;
   p.one_copy = geo.one_copy;
@@ -692,7 +721,7 @@ cudaError_t launch(SkinnyParams &p, cudaStream_t stream) {
 #ifdef FLSM100_PROBE
   if (const char *v = std::getenv("FLSM100_PROBE")) p.probe = std::atoi(v);
 #endif
-  auto kernel = skinny_fp8_kernel<QUANT, BF16>;
+  auto kernel = skinny_fp8_kernel<QUANT, BF16, W16>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
@@ -714,22 +743,26 @@ cudaError_t launch(SkinnyParams &p, cudaStream_t stream) {
   return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
-bool supported(int m, int n, int k, const void *x, const void *w, const void *out, bool has_residual) {
-  if (m < 1 || m > 16 || n < 8 || n % 8 != 0 || k < 16 || k % 16 != 0) return false;
+bool supported(int m, int n, int k, int wbytes, const void *x, const void *w, const void *out, bool has_residual) {
+  if (m < 1 || m > 16 || n < 8 || n % 8 != 0 || k < 16 || (k * wbytes) % 16 != 0) return false;
   if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 1) || (reinterpret_cast<uintptr_t>(out) & 1)) {
     return false;
   }
-  return geometry_for(m, n, k, has_residual).stages >= 3;
+  return geometry_for(m, n, k, wbytes, has_residual).stages >= 3;
 }
 
 }  // namespace
 
 bool skinny_fp8_supported(int m, int n, int k, const void *x, const void *w, const void *out, bool has_residual) {
-  return supported(m, n, k, x, w, out, has_residual);
+  return supported(m, n, k, 1, x, w, out, has_residual);
 }
 
 bool skinny_upcast_supported(int m, int n, int k, const void *x, const void *w, const void *out, bool has_residual) {
-  return supported(m, n, k, x, w, out, has_residual);
+  return supported(m, n, k, 1, x, w, out, has_residual);
+}
+
+bool skinny_w16_supported(int m, int n, int k, const void *x, const void *w, const void *out, bool has_residual) {
+  return supported(m, n, k, 2, x, w, out, has_residual);
 }
 
 cudaError_t skinny_fp8_linear(const void *x, int is_bf16, int m, int n, int k, const uint8_t *w, const float *col_scale,
@@ -751,7 +784,7 @@ cudaError_t skinny_fp8_linear(const void *x, int is_bf16, int m, int n, int k, c
   p.n = n;
   p.k = k;
   p.status = status;
-  return launch<true, false>(p, stream);
+  return launch<true, false, false>(p, stream);
 }
 
 cudaError_t skinny_upcast_matmul(const void *x, int is_bf16, int m, int n, int k, const uint8_t *w, const float *scale,
@@ -773,7 +806,29 @@ cudaError_t skinny_upcast_matmul(const void *x, int is_bf16, int m, int n, int k
   p.n = n;
   p.k = k;
   p.status = status;
-  return is_bf16 ? launch<false, true>(p, stream) : launch<false, false>(p, stream);
+  return is_bf16 ? launch<false, true, false>(p, stream) : launch<false, false, false>(p, stream);
+}
+
+cudaError_t skinny_w16_matmul(const void *x, int is_bf16, int m, int n, int k, const void *w, const void *bias,
+                              const void *residual, int residual_rows, int64_t residual_ld, void *out,
+                              uint32_t *status, cudaStream_t stream) {
+  SkinnyParams p;
+  p.x = static_cast<const uint16_t *>(x);
+  p.is_bf16 = is_bf16;
+  p.w = static_cast<const uint8_t *>(w);
+  p.col_scale = nullptr;
+  p.col_scale_scalar = 0;
+  p.bias = bias;
+  p.residual = residual;
+  p.residual_rows = residual_rows > 0 ? residual_rows : m;
+  p.residual_ld = residual_ld;
+  p.act = 0;
+  p.out = static_cast<uint16_t *>(out);
+  p.m = m;
+  p.n = n;
+  p.k = k;
+  p.status = status;
+  return is_bf16 ? launch<false, true, true>(p, stream) : launch<false, false, true>(p, stream);
 }
 
 }  // namespace flsm100

@@ -27,4 +27,13 @@ cudaError_t skinny_upcast_matmul(const void *x, int is_bf16, int m, int n, int k
                                  const void *bias, const void *residual, int residual_rows, int64_t residual_ld,
                                  void *out, uint32_t *status, cudaStream_t stream);
 
+// The unquantised linear layer for at most 16 rows: x (m, k) times the transpose of a 16-bit
+// weight (n, k) of the same type, fp32 accumulation, an optional bias (n) and/or residual rows
+// added to the fp32 sum, one rounding (the GEMV of flint/cuda/matvec.cu and the bias-in-epilogue
+// of flint/cuda/gemm_cutlass.cu:208-235 in one kernel).
+bool skinny_w16_supported(int m, int n, int k, const void *x, const void *w, const void *out, bool has_residual);
+cudaError_t skinny_w16_matmul(const void *x, int is_bf16, int m, int n, int k, const void *w, const void *bias,
+                              const void *residual, int residual_rows, int64_t residual_ld, void *out,
+                              uint32_t *status, cudaStream_t stream);
+
 }  // namespace flsm100
