@@ -623,9 +623,9 @@ int sm_count_cached() {
 }
 
 // K split: WK warps share a stage's K bytes; K goes in equal chunks of at most 512 WK bytes, a
-// chunk in equal slices of at most 512 bytes, both in whole steps, so that every warp is busy and
-// every stage carries the same load. k_pad is every K position a step can touch: the activation
-// rows are zero from k up to there, and whatever the weight's stage holds there multiplies zero.
+// chunk in WK equal slices of whole steps, so that every warp is busy and every stage carries the
+// same load. k_pad is every K position a step can touch: the activation rows are zero from k up
+// to there, and whatever the weight's stage holds there multiplies zero.
 struct KSplit {
   int k_chunks, chunk_bytes, slice_bytes, k_pad;
 };
@@ -633,17 +633,21 @@ struct KSplit {
 KSplit k_split(int k, int wn_log2) {
   const int wk = kConsumerWarps >> wn_log2;
   KSplit s;
-  s.k_chunks = (k + kWarpSlice * wk - 1) / (kWarpSlice * wk);
-  s.chunk_bytes = ((k + s.k_chunks - 1) / s.k_chunks + kKStep - 1) / kKStep * kKStep;
-  s.slice_bytes = ((s.chunk_bytes + wk - 1) / wk + kKStep - 1) / kKStep * kKStep;
-  s.k_pad = (s.k_chunks - 1) * s.chunk_bytes + wk * s.slice_bytes;
-  if (s.k_pad < k) s.k_pad = (k + kKStep - 1) / kKStep * kKStep;
+  // A chunk is WK whole slices and a slice whole steps, so that the slices of a full chunk end
+  // where the chunk ends: a read past the end of a chunk can only happen in the last one, past k.
+  const int chunks = (k + kWarpSlice * wk - 1) / (kWarpSlice * wk);
+  s.chunk_bytes = ((k + chunks - 1) / chunks + kKStep * wk - 1) / (kKStep * wk) * (kKStep * wk);
+  s.slice_bytes = s.chunk_bytes / wk;
+  s.k_chunks = (k + s.chunk_bytes - 1) / s.chunk_bytes;
+  s.k_pad = s.k_chunks * s.chunk_bytes;
   return s;
 }
 
 // Bytes between the 16-bit activation rows in shared memory: 16 mod 32, so that the 16-byte reads
 // a quarter warp makes of two rows (pieces 32 bytes apart) fall into distinct banks.
 int row_pitch(int k_pad_elements) { return 2 * k_pad_elements + 16; }
+
+inline int wk_of(int wn_log2) { return kConsumerWarps >> wn_log2; }
 
 struct Geometry {
   int ctas, wn_log2, units, grid, cpc, ep_bytes, x_bytes, stages, stage_stride, pitch_w, one_copy;
@@ -671,8 +675,15 @@ Geometry geometry_with(int m, int n, int k, int wbytes, bool has_residual, int c
   // when k is a multiple of 128, far from what limits the kernel. Otherwise a channel's piece is
   // padded to 64 mod 128 bytes so that the reads of two channels miss each other.
   g.one_copy = g.ks.k_chunks == 1 ? 1 : 0;
-  g.pitch_w = g.one_copy ? kb : (g.ks.chunk_bytes + 127) / 128 * 128 + 64;
-  g.stage_stride = (rows * g.pitch_w + 127) / 128 * 128;
+  // The warps of a stage read WK whole slices of every channel, which can reach past the bytes a
+  // chunk carries (the slices are whole steps): the pitch covers that reach, and where the pitch is
+  // the row itself (one copy) the stage ends that much after its last channel, so that every read
+  // stays inside the stage.
+  const int reach = wk_of(g.wn_log2) * g.ks.slice_bytes;
+  const int span = reach > g.ks.chunk_bytes ? reach : g.ks.chunk_bytes;
+  g.pitch_w = g.one_copy ? kb : (span + 127) / 128 * 128 + 64;
+  const int last = g.pitch_w > reach ? g.pitch_w : reach;
+  g.stage_stride = ((rows - 1) * g.pitch_w + last + 127) / 128 * 128;
   const long long budget = kSmemBudget / ctas - (ctas > 1 ? 1024 : 0);  // less the per-CTA reserve
   const long long left = budget - kFixedSmem - g.x_bytes - g.ep_bytes;
   g.stages = left < 0 ? 0 : (left / g.stage_stride > kMaxStages ? kMaxStages : static_cast<int>(left / g.stage_stride));

@@ -86,7 +86,7 @@ def test_epilogue_variants(flint, oracle, act, is_bf16):
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 18432, 3072), (2, 264, 80), (3, 4096, 12288), (4, 72, 3088), (2, 8, 16),
-                                   (4, 1184, 592)])
+                                   (4, 1184, 592), (2, 136, 4112), (3, 72, 8208)])
 @pytest.mark.parametrize("is_bf16", [True, False])
 def test_few_rows(flint, oracle, m, n, k, is_bf16):
     """One to four rows take the one-launch kernel that quantises the rows itself: every epilogue

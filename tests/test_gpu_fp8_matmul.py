@@ -220,7 +220,7 @@ def test_bf16_variant(flint, oracle):
 
 
 @pytest.mark.parametrize("m,n,k,bf16", [(1, 16384, 3072, False), (16, 264, 3072, True), (9, 72, 12288, False),
-                                        (5, 4096, 80, True)])
+                                        (5, 4096, 80, True), (2, 64, 4112, False), (7, 72, 6160, True), (3, 136, 1040, False)])
 def test_few_rows(flint, oracle, m, n, k, bf16):
     """At most 16 rows take the one-launch path that widens the weight in registers; the first
     shape is the reference's decode benchmark (docs/fp8.md:225-244)."""
