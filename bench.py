@@ -220,6 +220,12 @@ def run_reference(args, wl):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun pins every rank to one OpenMP thread; the reference arm is rank 0 alone with all the
+    # host cores it may use, so say so before the reference's library starts its OpenMP runtime.
+    try:
+        os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
+    except Exception:
+        os.environ.pop("OMP_NUM_THREADS", None)
     rows = min(wl["m"], args.reference_rows)
     step, kind, cores = cpu_reference_step_factory(wl, rows)
     for _ in range(args.warmup):
