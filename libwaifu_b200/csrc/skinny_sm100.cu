@@ -4,29 +4,30 @@
 // shaped for bandwidth, not for the tensor pipe:
 //
 //   * one launch does everything, with no scratch: the CTA's eight consumer warps first put the
-//     activation rows into shared memory, quantised per token to e4m3 with the same arithmetic as
-//     quantize_fp8_act and kept as halves (every e4m3 value is one exactly), while the producer
-//     warp is already streaming the weight;
-//   * persistent CTAs, one per SM. The weight is (n, k) row-major e4m3, so the K bytes of an
+//     activation rows into shared memory, quantised per token to e4m3 codes with the same
+//     arithmetic as quantize_fp8_act, while the producer warp is already streaming the weight;
+//   * persistent CTAs, two per SM where the rows leave room (else one). The weight is (n, k)
+//     row-major, so the K bytes of an
 //     output channel are contiguous: the producer warp brings 8 x WN channels x up to 512 x WK
-//     bytes per stage (WN x WK = 8) with one bulk copy (cp.async.bulk, no tensor map) per channel
-//     into a ring of shared-memory stages that holds well over the bandwidth-delay product of
-//     the SM;
-//   * consumer warp (wn, wk) owns 8 channels and one K slice of each stage. The arithmetic is the
-//     warp-level mma.sync m16n8k16 on halves with fp32 accumulation (exact products). The e4m3
-//     bytes of the weight become halves with a few integer instructions (the FP8 form of mma.sync
-//     and cvt are both conversion-bound on this part); the K order inside an instruction is
-//     permuted so that a thread's 16 contiguous weight bytes feed four instructions straight
+//     bytes per stage (WN x WK = 8) with one bulk copy (cp.async.bulk, no tensor map) per stage
+//     or per channel into a ring of shared-memory stages that holds well over the
+//     bandwidth-delay product of the SM;
+//   * consumer warp (wn, wk) owns 8 channels and one K slice of each stage. With a quantised
+//     activation the arithmetic is the warp-level mma.sync m16n8k32 e4m3 x e4m3 -> fp32 (exact
+//     products, fp32 accumulation) straight from the bytes, no widening; the K order inside an
+//     instruction is permuted so that a thread's 16 contiguous weight bytes feed two instructions
 //     from one 16-byte shared-memory read, each into its own accumulator chain;
 //   * with WK > 1 the partial sums of the K slices meet in shared memory once per unit of 8 x WN
 //     channels, and the fused epilogue (row and channel scales, bias, GELU-tanh, residual, one
 //     rounding) writes the 16-bit result. Its operands are staged in shared memory at the start.
 //
 // The same kernel serves the reference-compatible fl_fp8_matmul[_add], whose activation is not
-// narrowed (flint/capi.cc:1011-1016): the rows go to shared memory as they are, and the weight is
-// widened to half or bfloat16 in registers as the reference's kernel does
-// (flint/cuda/gemm_fp8_cutlass.cu:20-29). This is the reference's decode shape
-// (1 x 16384 x 3072, docs/fp8.md:225-244).
+// narrowed (flint/capi.cc:1011-1016): the rows go to shared memory as they are, the arithmetic is
+// m16n8k16 on halves or bfloat16, and the weight's e4m3 bytes are widened in registers as the
+// reference's kernel does (flint/cuda/gemm_fp8_cutlass.cu:20-29), with a few integer instructions
+// (cvt makes the stream ALU-bound). This is the reference's decode shape (1 x 16384 x 3072,
+// docs/fp8.md:225-244). And it serves the unquantised linear of fl_matmul[_add] (a 16-bit weight,
+// no widening).
 //
 // Every wait on an mbarrier is bounded; a wait that gives up raises the CTA's abort flag, records
 // a status code and the CTA leaves after a bounded wait for its copies in flight.
@@ -160,19 +161,26 @@ __device__ __forceinline__ float amax8(const uint4 v, int is_bf16) {
   return a;
 }
 
-// Eight 16-bit elements -> the eight e4m3 values of x * inv (round to nearest even, saturating),
-// held as halves: every e4m3 value is a half exactly.
-__device__ __forceinline__ uint4 quantise8(const uint4 v, float inv, int is_bf16) {
+// Eight 16-bit elements -> the eight e4m3 codes of x * inv (round to nearest even, saturating).
+__device__ __forceinline__ uint2 quantise8(const uint4 v, float inv, int is_bf16) {
   const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
-  uint32_t h[4];
+  uint32_t two[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const float2 pair = make_float2(__fmul_rn(widen16(static_cast<uint16_t>(w4[j] & 0xffff), is_bf16), inv),
                                     __fmul_rn(widen16(static_cast<uint16_t>(w4[j] >> 16), is_bf16), inv));
-    const uint16_t codes = static_cast<uint16_t>(__nv_cvt_float2_to_fp8x2(pair, __NV_SATFINITE, __NV_E4M3));
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h[j]) : "h"(codes));
+    two[j] = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(pair, __NV_SATFINITE, __NV_E4M3)) & 0xffff;
   }
-  return make_uint4(h[0], h[1], h[2], h[3]);
+  return make_uint2(two[0] | (two[1] << 16), two[2] | (two[3] << 16));
+}
+
+__device__ __forceinline__ void mma_e4m3(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // Four e4m3 bytes -> two registers of two 16-bit floats each, with integer instructions only (a
@@ -204,8 +212,9 @@ __device__ __forceinline__ void widen_e4m3x4(uint32_t w, uint32_t &p01, uint32_t
   }
 }
 
-// QUANT: the activation rows are quantised per token to e4m3 first (and kept as halves); else
-// they stay as they are. BF16: the product runs on bfloat16 instructions (never with QUANT).
+// QUANT: the activation rows are quantised per token to e4m3 first, kept as codes and multiplied
+// on the FP8 form of mma.sync; else they stay 16-bit. BF16: the 16-bit product runs on bfloat16
+// instructions (never with QUANT).
 // W16: the weight itself is 16-bit (the unquantised linear layer of fl_matmul): no widening, eight
 // K positions per 16-byte piece instead of sixteen.
 template <bool QUANT, bool BF16, bool W16>
@@ -321,7 +330,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_fp8_kernel(const SkinnyPar
   const long long probe_start = clock64();
   long long probe_wait = 0, probe_prologue = 0;
 #endif
-  constexpr float kUnfoldStage = (BF16 || W16) ? 1.0f : 256.0f;  // see kUnfold below
+  constexpr float kUnfoldStage = (BF16 || W16 || QUANT) ? 1.0f : 256.0f;  // see kUnfold below
   // ---- 0. this CTA's channel scales and bias: issued now, stored after the activation rows
   const bool vector_scale = p.col_scale && !p.col_scale_scalar;
   auto channel_of = [&](int i) {  // i = local unit * unit_rows + channel in unit; -1 when there is none
@@ -375,13 +384,14 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_fp8_kernel(const SkinnyPar
       if (lane == 0 && tw == 0) row_scale[r] = scale;
       uint8_t *dst = xq + r * p.pitch_x;
       // zeros past k (a group of 8 is whole or absent)
-      if (i0 < p.k_pad) *reinterpret_cast<uint4 *>(dst + 2 * i0) = i0 < p.k ? quantise8(keep0, inv, p.is_bf16) : zero;
+      const uint2 none = make_uint2(0, 0);
+      if (i0 < p.k_pad) *reinterpret_cast<uint2 *>(dst + i0) = i0 < p.k ? quantise8(keep0, inv, p.is_bf16) : none;
       if (i0 + stride < p.k_pad) {
-        *reinterpret_cast<uint4 *>(dst + 2 * (i0 + stride)) = i0 + stride < p.k ? quantise8(keep1, inv, p.is_bf16) : zero;
+        *reinterpret_cast<uint2 *>(dst + i0 + stride) = i0 + stride < p.k ? quantise8(keep1, inv, p.is_bf16) : none;
       }
 #pragma unroll 4
       for (int i = i0 + 2 * stride; i < p.k_pad; i += stride) {
-        *reinterpret_cast<uint4 *>(dst + 2 * i) = i < p.k ? quantise8(load_x8(src, i, p.x_vec), inv, p.is_bf16) : zero;
+        *reinterpret_cast<uint2 *>(dst + i) = i < p.k ? quantise8(load_x8(src, i, p.x_vec), inv, p.is_bf16) : none;
       }
     }
   } else {
@@ -428,7 +438,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_fp8_kernel(const SkinnyPar
   const bool row_hi = g + 8 < p.m;
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
   // The half path multiplies weight values scaled by 2^-8; the scale gives the 2^8 back (exactly).
-  constexpr float kUnfold = (BF16 || W16) ? 1.0f : 256.0f;
+  constexpr float kUnfold = (BF16 || W16 || QUANT) ? 1.0f : 256.0f;
   const float scalar_scale = ((p.col_scale && p.col_scale_scalar) ? __ldg(p.col_scale) : 1.0f) * kUnfold;
 
   int stage = 0;
@@ -486,14 +496,26 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_fp8_kernel(const SkinnyPar
       const int kb0 = kc * chunk_bytes + wk * p.slice_bytes + q * 16;  // this thread's K byte in step 0
       const uint8_t *wrow = ring + stage * p.stage_stride + (wn * 8 + g) * pitch_w + wk * p.slice_bytes + q * 16;
       // the activation's byte offset for weight byte kb0: two bytes per e4m3 byte, one per byte of a 16-bit weight
-      const int xoff = W16 ? kb0 : 2 * kb0;
+      const int xoff = (W16 || QUANT) ? kb0 : 2 * kb0;  // QUANT keeps the rows as e4m3 codes, one byte each
       const uint8_t *xlo = xq + (row_lo ? g : 0) * p.pitch_x + xoff;
       const uint8_t *xhi = xq + (row_hi ? g + 8 : 0) * p.pitch_x + xoff;
 #pragma unroll
       for (int s = 0; s < kSteps; ++s) {
         if (s < steps) {
           uint4 wv = *reinterpret_cast<const uint4 *>(wrow + s * kKStep);
-          if constexpr (W16) {
+          if constexpr (QUANT) {
+            // e4m3 x e4m3 on the FP8 form of the instruction: no widening at all. A stale byte past
+            // the end of the row may be a NaN code, which would not multiply a zero to zero.
+            if (kb0 + s * kKStep >= min(p.kb, (kc + 1) * chunk_bytes)) wv = zero4;
+            const uint4 xa = *reinterpret_cast<const uint4 *>(xlo + s * kKStep);
+            uint4 xb = zero4;
+            if (p.m > 8) xb = *reinterpret_cast<const uint4 *>(xhi + s * kKStep);
+            // Logical k of an instruction <-> physical byte: registers (x, y) of the 16 bytes are
+            // the "low" and "high" halves of the first instruction, (z, w) of the second; the same
+            // permutation on both operands, so every product pairs the same physical k.
+            mma_e4m3(acc[((s & 3) << 1)], xa.x, xb.x, xa.y, xb.y, wv.x, wv.y);
+            mma_e4m3(acc[((s & 3) << 1) | 1], xa.z, xb.z, xa.w, xb.w, wv.z, wv.w);
+          } else if constexpr (W16) {
             // Past the end of the row the stage holds stale bytes, which as 16-bit floats may be
             // NaN or infinite and would not multiply the activation's zeros to zero.
             if (kb0 + s * kKStep >= min(p.kb, (kc + 1) * chunk_bytes)) wv = zero4;
@@ -643,9 +665,14 @@ KSplit k_split(int k, int wn_log2) {
   return s;
 }
 
-// Bytes between the 16-bit activation rows in shared memory: 16 mod 32, so that the 16-byte reads
-// a quarter warp makes of two rows (pieces 32 bytes apart) fall into distinct banks.
-int row_pitch(int k_pad_elements) { return 2 * k_pad_elements + 16; }
+// Bytes between the activation rows in shared memory, chosen so that the 16-byte reads a quarter
+// warp makes of two rows fall into distinct banks: 16 mod 32 for 16-bit rows (pieces 32 bytes
+// apart), 64 mod 128 for rows of e4m3 codes.
+int row_pitch(int k_pad_elements, int xbytes) {
+  if (xbytes == 2) return 2 * k_pad_elements + 16;
+  // e4m3 rows: four 16-byte pieces per row and step, so 64 mod 128
+  return k_pad_elements + (k_pad_elements % 128 == 0 ? 64 : 0);
+}
 
 inline int wk_of(int wn_log2) { return kConsumerWarps >> wn_log2; }
 
@@ -657,7 +684,7 @@ struct Geometry {
 int pick_wn_log2(int k);
 
 // Shared-memory plan of one CTA when `ctas` CTAs share an SM.
-Geometry geometry_with(int m, int n, int k, int wbytes, bool has_residual, int ctas) {
+Geometry geometry_with(int m, int n, int k, int wbytes, int xbytes, bool has_residual, int ctas) {
   Geometry g;
   g.ctas = ctas;
   const int kb = k * wbytes;  // bytes of a weight row
@@ -669,7 +696,7 @@ Geometry geometry_with(int m, int n, int k, int wbytes, bool has_residual, int c
   g.cpc = (g.units + g.grid - 1) / g.grid * rows;
   g.ep_bytes = (g.cpc * 8 + (has_residual ? m * g.cpc * 2 : 0) + 127) / 128 * 128;
   g.ks = k_split(kb, g.wn_log2);
-  g.x_bytes = (m * row_pitch(g.ks.k_pad / wbytes) + 127) / 128 * 128;
+  g.x_bytes = (m * row_pitch(g.ks.k_pad / wbytes, xbytes) + 127) / 128 * 128;
   // With all of K in one stage the channels of a stage are one contiguous piece of the weight and
   // a single large copy brings them; the price is a two-way bank conflict on the weight reads
   // when k is a multiple of 128, far from what limits the kernel. Otherwise a channel's piece is
@@ -693,9 +720,9 @@ Geometry geometry_with(int m, int n, int k, int wbytes, bool has_residual, int c
 // The consumers are bound by instruction latency, not by issue slots, so two CTAs per SM (twice
 // the warps, half the shared memory each) stream faster than one; a shape whose activation rows
 // leave a half too small for three stages gets one CTA per SM.
-Geometry geometry_for(int m, int n, int k, int wbytes, bool has_residual) {
-  const Geometry two = geometry_with(m, n, k, wbytes, has_residual, 2);
-  return two.stages >= 3 ? two : geometry_with(m, n, k, wbytes, has_residual, 1);
+Geometry geometry_for(int m, int n, int k, int wbytes, int xbytes, bool has_residual) {
+  const Geometry two = geometry_with(m, n, k, wbytes, xbytes, has_residual, 2);
+  return two.stages >= 3 ? two : geometry_with(m, n, k, wbytes, xbytes, has_residual, 1);
 }
 
 // Channel groups per unit. A channel's K bytes arrive as one bulk copy per stage, and long copies
@@ -709,10 +736,11 @@ int pick_wn_log2(int k) {
 template <bool QUANT, bool BF16, bool W16>
 cudaError_t launch(SkinnyParams &p, cudaStream_t stream) {
   constexpr int wbytes = W16 ? 2 : 1;
+  constexpr int xbytes = QUANT ? 1 : 2;
   p.kb = p.k * wbytes;
   p.x_vec = (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 ? 1 : 0;
   p.out_pair = (reinterpret_cast<uintptr_t>(p.out) & 3) == 0 ? 1 : 0;
-  const Geometry geo = geometry_for(p.m, p.n, p.k, wbytes, p.residual != nullptr);
+  const Geometry geo = geometry_for(p.m, p.n, p.k, wbytes, xbytes, p.residual != nullptr);
   p.wn_log2 = geo.wn_log2;
   p.stages = geo.stages;
   p.units = geo.units;
@@ -723,7 +751,7 @@ cudaError_t launch(SkinnyParams &p, cudaStream_t stream) {
   p.chunk_bytes = geo.ks.chunk_bytes;
   p.slice_bytes = geo.ks.slice_bytes;
   p.k_pad = geo.ks.k_pad / wbytes;
-  p.pitch_x = row_pitch(p.k_pad);
+  p.pitch_x = row_pitch(p.k_pad, xbytes);
   p.pitch_w = geo.pitch_w;
   p.one_copy = geo.one_copy;
   const size_t smem = static_cast<size_t>(geo.x_bytes) + kFixedSmem + geo.ep_bytes + static_cast<size_t>(p.stages) * geo.stage_stride;
@@ -754,26 +782,26 @@ cudaError_t launch(SkinnyParams &p, cudaStream_t stream) {
   return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
-bool supported(int m, int n, int k, int wbytes, const void *x, const void *w, const void *out, bool has_residual) {
+bool supported(int m, int n, int k, int wbytes, int xbytes, const void *x, const void *w, const void *out, bool has_residual) {
   if (m < 1 || m > 16 || n < 8 || n % 8 != 0 || k < 16 || (k * wbytes) % 16 != 0) return false;
   if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 1) || (reinterpret_cast<uintptr_t>(out) & 1)) {
     return false;
   }
-  return geometry_for(m, n, k, wbytes, has_residual).stages >= 3;
+  return geometry_for(m, n, k, wbytes, xbytes, has_residual).stages >= 3;
 }
 
 }  // namespace
 
 bool skinny_fp8_supported(int m, int n, int k, const void *x, const void *w, const void *out, bool has_residual) {
-  return supported(m, n, k, 1, x, w, out, has_residual);
+  return supported(m, n, k, 1, 1, x, w, out, has_residual);
 }
 
 bool skinny_upcast_supported(int m, int n, int k, const void *x, const void *w, const void *out, bool has_residual) {
-  return supported(m, n, k, 1, x, w, out, has_residual);
+  return supported(m, n, k, 1, 2, x, w, out, has_residual);
 }
 
 bool skinny_w16_supported(int m, int n, int k, const void *x, const void *w, const void *out, bool has_residual) {
-  return supported(m, n, k, 2, x, w, out, has_residual);
+  return supported(m, n, k, 2, 2, x, w, out, has_residual);
 }
 
 cudaError_t skinny_fp8_linear(const void *x, int is_bf16, int m, int n, int k, const uint8_t *w, const float *col_scale,
