@@ -265,6 +265,18 @@ FLAPI int32_t fl_fp8_linear_quantized(fl_tensor_view_t codes, fl_tensor_view_t r
 FLAPI int32_t fl_qk_norm_rope(fl_tensor_view_t qkv, fl_tensor_view_t q_weight, fl_tensor_view_t k_weight,
                               fl_tensor_view_t cos, fl_tensor_view_t sin, float eps, int32_t heads);
 
+/* The plan the few-row kernel (at most 16 activation rows) would run a shape with; host arithmetic
+ * only, no GPU needed, so that its index arithmetic can be checked anywhere. weight_bytes 1 (e4m3)
+ * or 2 (16-bit), activation_bytes 1 (quantised rows) or 2. plan[16]: [0] CTAs per SM (0: the shape
+ * goes to the tile kernel and the rest is 0), [1] channels per unit, [2] K slices per stage,
+ * [3] stages per unit, [4] weight bytes of a stage per channel, [5] of a slice, [6] K positions a
+ * step can touch (in weight bytes), [7] bytes between channels in a stage, [8] bytes of a stage,
+ * [9] ring depth, [10] one bulk copy per stage, [11] bytes between activation rows, [12] bytes of
+ * the activation rows, [13] of the staged epilogue operands, [14] CTAs, [15] dynamic shared
+ * memory of a CTA. */
+FLAPI int32_t fl_sm100_few_rows_plan(int32_t m, int32_t n, int32_t k, int32_t weight_bytes, int32_t activation_bytes,
+                                     int32_t has_residual, int32_t *plan);
+
 /* Storage over device memory the caller already owns (for instance a torch tensor's): nothing
  * is copied and nothing is freed on destroy. The device counterpart of fl_tensor_data_borrow(). */
 FLAPI int32_t fl_tensor_data_borrow_device(void *device_ptr, fl_dtype_t dtype, int64_t numel, fl_tensor_data_t *out);

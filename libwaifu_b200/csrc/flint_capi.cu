@@ -1597,6 +1597,19 @@ int32_t fl_sm100_gemm_timing_read(double *total_ms, int64_t *launches) {
   });
 }
 
+int32_t fl_sm100_few_rows_plan(int32_t m, int32_t n, int32_t k, int32_t weight_bytes, int32_t activation_bytes,
+                               int32_t has_residual, int32_t *plan) {
+  return guard([&]() -> int32_t {
+    if (!plan) invalid("plan is null");
+    if ((weight_bytes != 1 && weight_bytes != 2) || (activation_bytes != 1 && activation_bytes != 2)) {
+      invalid("weight_bytes and activation_bytes are 1 or 2");
+    }
+    for (int i = 0; i < 16; ++i) plan[i] = 0;
+    skinny_plan(m, n, k, weight_bytes, activation_bytes, has_residual, plan);
+    return clear_error();
+  });
+}
+
 int64_t fl_sm100_launch_count(void) { return g_gemm_launches.load() + g_block_launches.load() + helper_launch_count(); }
 
 

@@ -792,6 +792,29 @@ bool supported(int m, int n, int k, int wbytes, int xbytes, const void *x, const
 
 }  // namespace
 
+int skinny_plan(int m, int n, int k, int wbytes, int xbytes, int has_residual, int32_t *out) {
+  if (m < 1 || m > 16 || n < 8 || n % 8 != 0 || k < 16 || (k * wbytes) % 16 != 0) return 0;
+  const Geometry g = geometry_for(m, n, k, wbytes, xbytes, has_residual != 0);
+  if (g.stages < 3) return 0;
+  out[0] = g.ctas;
+  out[1] = 8 << g.wn_log2;           // channels per unit
+  out[2] = wk_of(g.wn_log2);         // K slices per stage
+  out[3] = g.ks.k_chunks;
+  out[4] = g.ks.chunk_bytes;
+  out[5] = g.ks.slice_bytes;
+  out[6] = g.ks.k_pad;               // in weight bytes
+  out[7] = g.pitch_w;
+  out[8] = g.stage_stride;
+  out[9] = g.stages;
+  out[10] = g.one_copy;
+  out[11] = row_pitch(g.ks.k_pad / wbytes, xbytes);
+  out[12] = g.x_bytes;
+  out[13] = g.ep_bytes;
+  out[14] = g.grid;
+  out[15] = static_cast<int32_t>(g.x_bytes + kFixedSmem + g.ep_bytes + static_cast<long long>(g.stages) * g.stage_stride);
+  return 1;
+}
+
 bool skinny_fp8_supported(int m, int n, int k, const void *x, const void *w, const void *out, bool has_residual) {
   return supported(m, n, k, 1, 1, x, w, out, has_residual);
 }

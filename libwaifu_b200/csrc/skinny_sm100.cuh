@@ -36,4 +36,9 @@ cudaError_t skinny_w16_matmul(const void *x, int is_bf16, int m, int n, int k, c
                               const void *residual, int residual_rows, int64_t residual_ld, void *out,
                               uint32_t *status, cudaStream_t stream);
 
+// The shared-memory and K-split plan the kernel would run a shape with (host arithmetic only, for
+// checks that need no GPU): 16 values, see fl_sm100_few_rows_plan. Returns 0 when the shape is
+// not taken.
+int skinny_plan(int m, int n, int k, int wbytes, int xbytes, int has_residual, int32_t *out);
+
 }  // namespace flsm100
