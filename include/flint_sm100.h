@@ -232,8 +232,9 @@ FLAPI int32_t fl_quantize_fp8_activation(fl_tensor_view_t a, fl_tensor_view_t co
  * flint's layerNorm, flint/cpu/normalizations.cc:98-140): per row of x <float16|bfloat16>(..., k),
  *   n = (x - mean) * (1 / sqrt(var + eps))    fp32 sums; mean = sum / k, var = sumsq / k - mean^2
  *                                             (eps alone where that is not positive), no affine
- *   h = round16( n * scale_g + n + shift_g )  scale, shift: (k) or (groups, k) of x's type, or
- *                                             NULL; row r belongs to group r / (rows / groups)
+ *   h = round16( n * scale_g + n + shift_g )  scale, shift: (k) or (groups, k) of x's type (the rows
+ *                                             contiguous, any stride between them), or NULL;
+ *                                             row r belongs to group r / (rows / groups)
  *   codes, row_scales = per-row e4m3 of h     exactly fl_quantize_fp8_activation(h)
  * One pass over x; h is never written. codes <fp8e4m3> of x's shape, row_scales <float>(rows). */
 FLAPI int32_t fl_fp8_layernorm_quantize(fl_tensor_view_t x, fl_tensor_view_t scale, fl_tensor_view_t shift, float eps,

@@ -1267,6 +1267,14 @@ int32_t fl_quantize_fp8_activation(fl_tensor_view_t a_h, fl_tensor_view_t codes_
   });
 }
 
+namespace {
+// Elements between the rows of a (groups, k) modulation tensor (k for a plain vector).
+int64_t group_pitch(const fl_tensor_view_impl_t *v, int k) {
+  if (!v || v->shape.size() < 2 || v->shape[0] == 1) return k;
+  return v->stride[0];
+}
+}  // namespace
+
 int32_t fl_fp8_layernorm_quantize(fl_tensor_view_t x_h, fl_tensor_view_t scale_h, fl_tensor_view_t shift_h, float eps,
                                   fl_tensor_view_t codes_h, fl_tensor_view_t row_scales_h) {
   return guard([&]() -> int32_t {
@@ -1289,8 +1297,11 @@ int32_t fl_fp8_layernorm_quantize(fl_tensor_view_t x_h, fl_tensor_view_t scale_h
     const fl_tensor_view_impl_t *mods[2] = {scale_h ? &deref(scale_h) : nullptr, shift_h ? &deref(shift_h) : nullptr};
     for (const fl_tensor_view_impl_t *v : mods) {
       if (!v) continue;
-      if (dtype_of(*v) != dtype_of(x) || v->shape.empty() || v->shape.size() > 2 || v->shape.back() != k || !is_contiguous(*v)) {
-        invalid("scale/shift is not a contiguous (k) or (groups, k) tensor of x's type");
+      // (k), or (groups, k) whose rows may be slices of a wider tensor (any row stride, unit
+      // column stride): the modulation vectors are chunks of one projection's output.
+      if (dtype_of(*v) != dtype_of(x) || v->shape.empty() || v->shape.size() > 2 || v->shape.back() != k ||
+          (k > 1 && v->stride.back() != 1)) {
+        invalid("scale/shift is not a (k) or (groups, k) tensor of x's type with contiguous rows");
       }
       const int64_t g = v->shape.size() == 2 ? v->shape[0] : 1;
       if (groups != 1 && g != 1 && g != groups) invalid("scale and shift disagree about the number of groups");
@@ -1312,7 +1323,8 @@ int32_t fl_fp8_layernorm_quantize(fl_tensor_view_t x_h, fl_tensor_view_t scale_h
     if (m64 == 0) return clear_error();
     if (m64 > INT32_MAX) invalid("x has more rows than the kernels can index");
     cuda_check(ln_modulate_quantize_fp8(raw_ptr(x), dtype_of(x) == FL_DTYPE_BFLOAT16, static_cast<int>(m64), k,
-                                        mods[0] ? raw_ptr(*mods[0]) : nullptr, mods[1] ? raw_ptr(*mods[1]) : nullptr,
+                                        mods[0] ? raw_ptr(*mods[0]) : nullptr, group_pitch(mods[0], k),
+                                        mods[1] ? raw_ptr(*mods[1]) : nullptr, group_pitch(mods[1], k),
                                         static_cast<int>(m64 / groups), eps, raw_ptr(codes),
                                         reinterpret_cast<float *>(raw_ptr(row_scales)), 0),
                "layer norm and quantisation");

@@ -202,7 +202,8 @@ template <int VPT, int THREADS>
 __global__ void __launch_bounds__(THREADS) ln_modulate_quantize_reg_kernel(const uint16_t *__restrict__ x, int is_bf16, int k,
                                                                      const uint16_t *__restrict__ scale,
                                                                      const uint16_t *__restrict__ shift,
-                                                                     int rows_per_group, float eps,
+                                                                     int rows_per_group, int64_t scale_pitch,
+                                                                     int64_t shift_pitch, float eps,
                                                                      uint8_t *__restrict__ codes,
                                                                      float *__restrict__ row_scales) {
   griddep_wait();
@@ -212,8 +213,8 @@ __global__ void __launch_bounds__(THREADS) ln_modulate_quantize_reg_kernel(const
   const uint4 *xv = reinterpret_cast<const uint4 *>(x + row * k);
   uint2 *cv = reinterpret_cast<uint2 *>(codes + row * k);
   const int64_t group = row / rows_per_group;
-  const uint16_t *s = scale ? scale + group * k : nullptr;
-  const uint16_t *t = shift ? shift + group * k : nullptr;
+  const uint16_t *s = scale ? scale + group * scale_pitch : nullptr;  // a group's row may sit in a wider tensor
+  const uint16_t *t = shift ? shift + group * shift_pitch : nullptr;
   const int nvec = k / 8;
   uint4 q[VPT];
 #pragma unroll
@@ -284,7 +285,8 @@ __global__ void __launch_bounds__(THREADS) ln_modulate_quantize_reg_kernel(const
 __global__ void __launch_bounds__(256) ln_modulate_quantize_kernel(const uint16_t *__restrict__ x, int is_bf16, int k,
                                                                  const uint16_t *__restrict__ scale,
                                                                  const uint16_t *__restrict__ shift, int rows_per_group,
-                                                                 float eps, uint8_t *__restrict__ codes,
+                                                                 int64_t scale_pitch, int64_t shift_pitch, float eps,
+                                                                 uint8_t *__restrict__ codes,
                                                                  float *__restrict__ row_scales) {
   griddep_wait();
   __shared__ float red[8];
@@ -292,8 +294,8 @@ __global__ void __launch_bounds__(256) ln_modulate_quantize_kernel(const uint16_
   const int64_t row = blockIdx.x;
   const uint16_t *xr = x + row * k;
   const int64_t group = row / rows_per_group;
-  const uint16_t *s = scale ? scale + group * k : nullptr;
-  const uint16_t *t = shift ? shift + group * k : nullptr;
+  const uint16_t *s = scale ? scale + group * scale_pitch : nullptr;  // a group's row may sit in a wider tensor
+  const uint16_t *t = shift ? shift + group * shift_pitch : nullptr;
   float sum = 0.0f, sq = 0.0f;
   for (int i = threadIdx.x; i < k; i += blockDim.x) {
     const float v = widen(xr[i], is_bf16);
@@ -616,10 +618,11 @@ cudaError_t quantize_fp8_act(const void *x, int is_bf16, int m, int k, uint8_t *
   return e;
 }
 
-cudaError_t ln_modulate_quantize_fp8(const void *x, int is_bf16, int m, int k, const void *scale, const void *shift,
-                                     int rows_per_group, float eps, uint8_t *codes, float *row_scales,
-                                     cudaStream_t stream) {
-  const bool vec = aligned16(x) && aligned16(codes) && (k % 8 == 0) && aligned16(scale) && aligned16(shift);
+cudaError_t ln_modulate_quantize_fp8(const void *x, int is_bf16, int m, int k, const void *scale, int64_t scale_pitch,
+                                     const void *shift, int64_t shift_pitch, int rows_per_group, float eps,
+                                     uint8_t *codes, float *row_scales, cudaStream_t stream) {
+  const bool vec = aligned16(x) && aligned16(codes) && (k % 8 == 0) && aligned16(scale) && aligned16(shift) &&
+                   scale_pitch % 8 == 0 && shift_pitch % 8 == 0;
   const uint16_t *xs = static_cast<const uint16_t *>(x);
   const uint16_t *sc = static_cast<const uint16_t *>(scale);
   const uint16_t *sh = static_cast<const uint16_t *>(shift);
@@ -635,15 +638,15 @@ cudaError_t ln_modulate_quantize_fp8(const void *x, int is_bf16, int m, int k, c
   cudaError_t e;
   if (vec && k <= 1024 * 3) {
     cfg.blockDim = dim3(128, 1, 1);
-    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<3, 128>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<3, 128>, xs, is_bf16, k, sc, sh, rows_per_group, scale_pitch, shift_pitch, eps, codes, row_scales);
   } else if (vec && k <= 2048 * 2) {
-    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<2, 256>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<2, 256>, xs, is_bf16, k, sc, sh, rows_per_group, scale_pitch, shift_pitch, eps, codes, row_scales);
   } else if (vec && k <= 2048 * 4) {
-    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<4, 256>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<4, 256>, xs, is_bf16, k, sc, sh, rows_per_group, scale_pitch, shift_pitch, eps, codes, row_scales);
   } else if (vec && k <= 2048 * 8) {
-    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<8, 256>, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<8, 256>, xs, is_bf16, k, sc, sh, rows_per_group, scale_pitch, shift_pitch, eps, codes, row_scales);
   } else {
-    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_kernel, xs, is_bf16, k, sc, sh, rows_per_group, eps, codes, row_scales);
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_kernel, xs, is_bf16, k, sc, sh, rows_per_group, scale_pitch, shift_pitch, eps, codes, row_scales);
   }
   ++g_helper_launches;
   return e;

@@ -18,12 +18,13 @@ cudaError_t quantize_fp8_rows_f32(const float *w, int rows, int k, uint8_t *code
 
 // Layer norm over the last dimension (no affine; fp32 sums, mean = sum / k, variance =
 // sumsq / k - mean^2, eps inside the root: flint/cpu/normalizations.cc:98-140), then the adaLN modulation
-// h = round16(n * scale + n [+ shift]) with `scale`/`shift` (groups, k) 16-bit or null and row r
-// in group r / rows_per_group (waifu/src/qwen_image/dit.rs:179-184), then per-row e4m3 of h
+// h = round16(n * scale + n [+ shift]) with `scale`/`shift` (groups, k) 16-bit or null, a group's
+// row `scale_pitch` / `shift_pitch` elements after the previous one's, and row r in group
+// r / rows_per_group (waifu/src/qwen_image/dit.rs:179-184), then per-row e4m3 of h
 // exactly as quantize_fp8_act. One pass over x; the modulated row never reaches memory.
-cudaError_t ln_modulate_quantize_fp8(const void *x, int is_bf16, int m, int k, const void *scale, const void *shift,
-                                     int rows_per_group, float eps, uint8_t *codes, float *row_scales,
-                                     cudaStream_t stream);
+cudaError_t ln_modulate_quantize_fp8(const void *x, int is_bf16, int m, int k, const void *scale, int64_t scale_pitch,
+                                     const void *shift, int64_t shift_pitch, int rows_per_group, float eps,
+                                     uint8_t *codes, float *row_scales, cudaStream_t stream);
 
 // Scale factors of a (rows, k/16) operand in the tile layout the block-scaled MMA reads: tiles
 // of 128 rows x 4 factors (512 bytes), byte (r % 32) * 16 + ((r % 128) / 32) * 4 + (b % 4) of

@@ -68,7 +68,9 @@ class FlintBackend:
         self.device = "cuda"
 
     def _wrap(self, t, dt):
-        return self.F.Tensor.from_device_ptr(t.data_ptr(), tuple(t.shape), dt, keepalive=t)
+        """A view of a torch tensor's memory with its own strides (a column slice stays a slice)."""
+        return self.F.Tensor.from_device_ptr(t.data_ptr(), tuple(t.shape), dt, keepalive=t, stride=tuple(t.stride()),
+                                             numel=(t.shape[0] - 1) * t.stride(0) + t.shape[-1] if t.dim() == 2 and not t.is_contiguous() else None)
 
     def make_layer(self, w_f32, bias_bf16):
         torch, F = self.torch, self.F
@@ -79,7 +81,8 @@ class FlintBackend:
         w = self._wrap(w_f32, F.DType.FLOAT)
         F.check(F.lib().fl_quantize_fp8_rows(w.raw(), codes.raw(), scales.raw()))
         F.synchronize()
-        return (codes, scales, None if bias_bf16 is None else self._wrap(bias_bf16, F.DType.BFLOAT16), bias_bf16, scales_t)
+        return (codes, scales, None if bias_bf16 is None else self._wrap(bias_bf16, F.DType.BFLOAT16),
+                None if bias_bf16 is None else bias_bf16.float(), scales_t)
 
     def linear(self, x2d, layer, act: int = 0, residual2d=None):
         torch, F = self.torch, self.F
@@ -99,8 +102,9 @@ class FlintBackend:
         q = torch.empty((b * t, d), dtype=torch.uint8, device=x3d.device)
         rs = torch.empty((b * t,), dtype=torch.float32, device=x3d.device)
         qw, rsw = self._wrap(q, F.DType.FP8E4M3), self._wrap(rs, F.DType.FLOAT)
-        F.fp8_layernorm_quantize(self._wrap(x3d.reshape(b * t, d), F.DType.BFLOAT16), self._wrap(scale.contiguous(), F.DType.BFLOAT16),
-                                 self._wrap(shift.contiguous(), F.DType.BFLOAT16), LN_EPS, qw, rsw)
+        # scale and shift are column slices of the modulation linear's output: passed as they lie
+        F.fp8_layernorm_quantize(self._wrap(x3d.reshape(b * t, d), F.DType.BFLOAT16), self._wrap(scale, F.DType.BFLOAT16),
+                                 self._wrap(shift, F.DType.BFLOAT16), LN_EPS, qw, rsw)
         out = torch.empty((b * t, codes.shape[0]), dtype=torch.bfloat16, device=x3d.device)
         F.fp8_linear_quantized(qw, rsw, codes, scales, bias, None, act, self._wrap(out, F.DType.BFLOAT16))
         return out
@@ -117,12 +121,12 @@ class FlintBackend:
         scale and bias carry the gate and whose residual is the stream, so the product is rounded
         once and no elementwise pass follows it."""
         torch, F = self.torch, self.F
-        codes, scales, bias, bias_t, scales_t = layer
+        codes, scales, bias, bias_f32, scales_t = layer
         b, t, n = stream3d.shape
         out = torch.empty((b, t, n), dtype=torch.bfloat16, device=a2d.device)
-        g32 = gate.float()
-        gated_scales = (g32 * scales_t[None, :]).contiguous()                       # (b, n) fp32
-        gated_bias = None if bias_t is None else (g32 * bias_t.float()[None, :]).to(torch.bfloat16).contiguous()
+        g32 = gate if gate.dtype == torch.float32 else gate.float()
+        gated_scales = torch.mul(g32, scales_t)                                      # (b, n) fp32, contiguous
+        gated_bias = None if bias_f32 is None else torch.mul(g32, bias_f32).to(torch.bfloat16)
         k = a2d.shape[1]
         q = torch.empty((b * t, k), dtype=torch.uint8, device=a2d.device)
         rs = torch.empty((b * t,), dtype=torch.float32, device=a2d.device)
@@ -173,7 +177,8 @@ class OracleBackend:
 
     def gated_linear(self, a2d, layer, gate, stream3d):
         b, t, n = stream3d.shape
-        return stream3d + gate[:, None, :] * self.linear(a2d, layer).view(b, t, n)
+        y = self.linear(a2d, layer).view(b, t, n).float()
+        return (stream3d.float() + gate[:, None, :].float() * y).to(self.torch.bfloat16)
 
 
 class MMDiT:
@@ -217,7 +222,9 @@ class MMDiT:
         b, t, d = x.shape
         lin = self.backend.linear
         mod = lin(Fn.silu(temb), layers["mod"])  # (b, 6 d): the M = batch skinny linear
-        shift1, scale1, gate1, shift2, scale2, gate2 = mod.chunk(6, dim=1)
+        shift1, scale1, _, shift2, scale2, _ = mod.chunk(6, dim=1)   # column slices, not copies
+        modf = mod.float()                                             # the gates multiply fp32 scales
+        gate1, gate2 = modf[:, 2 * d:3 * d], modf[:, 5 * d:6 * d]
 
         qkv = self.backend.modulated_linear(x, scale1, shift1, layers["qkv"])  # (b t, 3 d)
         qkv = self.backend.qk_norm_rope(qkv, self.cos, self.sin, c.heads).view(b, t, 3, c.heads, c.head_dim)

@@ -108,3 +108,22 @@ def test_refusals(flint):
         F.fp8_layernorm_quantize(x, None, None, 1e-6, codes, F.Tensor.empty((5,), F.DType.FLOAT))
     with pytest.raises(F.FlintError):  # negative eps
         F.fp8_layernorm_quantize(x, None, None, -1.0, codes, rs)
+
+
+def test_modulation_vectors_as_column_slices(flint, oracle):
+    """scale and shift are usually chunks of one projection's output (groups, 6 k): a (groups, k)
+    view with the wide tensor's row stride gives the same codes as contiguous copies."""
+    F = flint
+    rng = np.random.default_rng(63)
+    m, k, groups = 12, 1040, 3
+    bf = F.DType.BFLOAT16
+    x = oracle.narrow(randn(rng, (m, k)) * 1.3, True)
+    wide = oracle.narrow(randn(rng, (groups, 6 * k), 0.3), True)
+    scale, shift = wide[:, k:2 * k].copy(), wide[:, 3 * k:4 * k].copy()
+    wide_dev = dev(F, wide, bf)
+    scale_view = wide_dev.view_as((groups, k), (6 * k, 1), k)
+    shift_view = wide_dev.view_as((groups, k), (6 * k, 1), 3 * k)
+    c1, s1 = F.fp8_layernorm_quantize(dev(F, x, bf), scale_view, shift_view, 1e-6)
+    c2, s2 = F.fp8_layernorm_quantize(dev(F, x, bf), dev(F, scale, bf), dev(F, shift, bf), 1e-6)
+    assert np.array_equal(c1.numpy(), c2.numpy()) and np.array_equal(s1.numpy(), s2.numpy())
+    F.synchronize()
