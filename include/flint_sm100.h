@@ -117,6 +117,27 @@ FLAPI int32_t fl_matmul(fl_operators_t operators, fl_tensor_view_t a, fl_tensor_
 FLAPI int32_t fl_matmul_add(fl_operators_t operators, fl_tensor_view_t a, fl_tensor_view_t b, fl_tensor_view_t addend,
                             fl_tensor_view_t out);
 
+/* flint/capi.h:118-133. Which keys a query may see in fl_attention(): query i sits at position
+ * p = i + S - L. */
+typedef enum fl_mask_type_t {
+  FL_MASK_NONE = 0,           /* every key; block_size 0 */
+  FL_MASK_CAUSAL = 1,         /* keys 0..p; block_size 0; needs S >= L */
+  FL_MASK_BLOCK_CAUSAL = 2,   /* not implemented in this library: refused with the reason */
+  FL_MASK_BLOCK_DIAGONAL = 3, /* not implemented in this library: refused with the reason */
+} fl_mask_type_t;
+
+/* flint/capi.h:532-544. Scaled dot product attention: q (N, heads, L, D), k and v (N, kv_heads, S, D)
+ * with kv_heads dividing heads, out (N, heads, L, D); <float16> or <bfloat16>, one type. The last
+ * dimension is contiguous; the other strides are free (a (N, L, heads, D) tensor transposed is
+ * taken as it is) but multiples of 8 elements, and every operand starts on a 16-byte boundary. D is
+ * 64 or 128. Softmax in float over scores scaled by 1/sqrt(D); probabilities rounded to the
+ * operands' type before the second product (flint/cuda/attention.cu:30-70). A mask that is not one
+ * (a block size beside NONE or CAUSAL, none beside a block mask, keys too few) is
+ * FL_ERROR_INVALID_ARG, and so is what this library has no kernel for, with the reason. Two
+ * launches (a transposition of v into scratch, the attention kernel), no host synchronisation. */
+FLAPI int32_t fl_attention(fl_operators_t operators, fl_tensor_view_t q, fl_tensor_view_t k, fl_tensor_view_t v,
+                           fl_mask_type_t mask_type, int32_t block_size, fl_tensor_view_t out);
+
 /* flint/capi.h:458-460, flint/capi.cc:1039-1045. 1 for FL_DEVICE_CUDA on compute capability 10.x,
  * 0 for every other device or card, never an error for a missing device. */
 FLAPI int32_t fl_fp8_available(fl_device_type_t device, int32_t *out);

@@ -10,8 +10,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libflint_sm100.so")
-SOURCES = ["gemm_sm100.cu", "quant_sm100.cu", "skinny_sm100.cu", "block_sm100.cu", "flint_capi.cu"]
-HEADERS = ["gemm_sm100.cuh", "quant_sm100.cuh", "skinny_sm100.cuh", "block_sm100.cuh", "ptx_sm100.cuh", os.path.join("..", "..", "include", "flint_sm100.h")]
+SOURCES = ["gemm_sm100.cu", "quant_sm100.cu", "skinny_sm100.cu", "block_sm100.cu", "attention_sm100.cu", "flint_capi.cu"]
+HEADERS = ["gemm_sm100.cuh", "quant_sm100.cuh", "skinny_sm100.cuh", "block_sm100.cuh", "attention_sm100.cuh", "ptx_sm100.cuh", os.path.join("..", "..", "include", "flint_sm100.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

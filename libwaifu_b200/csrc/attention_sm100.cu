@@ -1,0 +1,612 @@
+// Scaled dot product attention on sm_100a.
+//
+// A CTA owns 128 queries of one head and walks that head's keys 128 at a time. Per block of keys:
+//   S = Q K^T      tcgen05.mma kind::f16, 128 x 128 x head_dim, into one of two score buffers in
+//                  tensor memory (the next block's product runs beside this block's softmax);
+//   softmax        four warps, one thread per query: the thread reads its row of S from tensor
+//                  memory (a row is a lane, so no shuffles), keeps the running maximum and sum,
+//                  and writes P = exp2(S' - max) as 16-bit values into shared memory in the layout
+//                  the next product reads its A operand in (128-byte swizzle, K-major);
+//   O_blk = P V    tcgen05.mma, 128 x head_dim x 128, into tensor memory; the threads add it to
+//                  their output rows in registers, rescaled as the online softmax has it.
+// K and V blocks arrive by TMA into two-stage rings. V is the B operand of the second product and
+// is read K-major, i.e. as V^T: a small kernel transposes it into scratch first.
+//
+// The arithmetic follows flint/cuda/attention.cu:30-70 (scores scaled by log2(e)/sqrt(head_dim)
+// into exp2, float maximum, sum and output, 16-bit probabilities into the second product).
+//
+// Every wait is bounded: a role that gives up raises the CTA's abort flag, records a status word
+// and the CTA leaves through the common teardown with its tensor memory freed.
+
+#include "attention_sm100.cuh"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx_sm100.cuh"
+
+namespace flsm100 {
+
+namespace {
+
+constexpr int kBlockQ = 128;   // queries per CTA = lanes of tensor memory
+constexpr int kBlockKv = 128;  // keys per step
+constexpr int kAtomBytes = 128;  // one swizzle atom: 64 16-bit elements of K
+constexpr int kAtomElems = 64;
+constexpr int kMmaKBytes = 32;   // one kind::f16 instruction: 16 elements of K
+constexpr int kSoftmaxWarps = 4;
+constexpr int kProducerWarp = 4;
+constexpr int kMmaWarp = 5;
+constexpr int kThreads = 6 * 32;
+constexpr int kKvStages = 2;
+constexpr int kPadKv = 64;  // the transposed v's rows are padded to whole swizzle atoms
+
+template <int D>
+struct Layout {
+  static constexpr int kQAtoms = D / kAtomElems;                  // atoms along head_dim
+  static constexpr int kQBytes = kQAtoms * kBlockQ * kAtomBytes;  // 128 rows x head_dim
+  static constexpr int kKBytes = kQAtoms * kBlockKv * kAtomBytes;
+  static constexpr int kVAtoms = kBlockKv / kAtomElems;           // atoms along the keys
+  static constexpr int kVAtomBytes = D * kAtomBytes;              // head_dim rows x 64 keys
+  static constexpr int kVBytes = kVAtoms * kVAtomBytes;
+  static constexpr int kPAtomBytes = kBlockQ * kAtomBytes;
+  static constexpr int kPBytes = kVAtoms * kPAtomBytes;
+  static constexpr int kQOff = 0;
+  static constexpr int kKOff = kQOff + kQBytes;
+  static constexpr int kVOff = kKOff + kKvStages * kKBytes;
+  static constexpr int kPOff = kVOff + kKvStages * kVBytes;
+  static constexpr int kSmemBytes = kPOff + kPBytes + 1024;  // + slack to align to 1024
+  // Tensor memory: two score buffers, then the block's output.
+  static constexpr int kSCols = kBlockKv;
+  static constexpr int kOCol = 2 * kSCols;
+  static constexpr int kTmemCols = 512;
+  static_assert(kOCol + D <= kTmemCols, "tensor memory holds 512 columns");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory");
+};
+
+struct KernelParams {
+  void *out;
+  int64_t out_stride[3];
+  int is_bf16;
+  int heads, group;  // group = heads / kv_heads
+  int kv_heads;
+  int q_len, kv_len;
+  int causal;
+  float scale_log2;
+  uint32_t *status;
+};
+
+__device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *desc, uint64_t *bar, int32_t c0,
+                                            int32_t c1, int32_t c2, int32_t c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(desc)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+      "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *desc, uint64_t *bar, int32_t c0,
+                                            int32_t c1, int32_t c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(desc)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack16(float a, float b, int is_bf16) {
+  if (is_bf16) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t *>(&h);
+  }
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+// v (batch, kv_heads, kv_len, d) with strides -> vt (batch * kv_heads, d, kv_pad), zeros past kv_len.
+// 64 x 64 tiles through shared memory; both sides coalesced.
+__global__ void __launch_bounds__(256) transpose_v_kernel(const uint16_t *__restrict__ v, int64_t sb, int64_t sh,
+                                                          int64_t sl, int kv_heads, int kv_len, int kv_pad, int d,
+                                                          uint16_t *__restrict__ vt) {
+  __shared__ uint16_t tile[64][66];
+  const int bh = blockIdx.z;
+  const int b = bh / kv_heads, h = bh % kv_heads;
+  const int l0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+  const uint16_t *src = v + b * sb + h * sh;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  for (int r = ty; r < 64; r += 4) {
+    const int l = l0 + r;
+    tile[r][tx] = (l < kv_len) ? src[static_cast<int64_t>(l) * sl + d0 + tx] : static_cast<uint16_t>(0);
+  }
+  __syncthreads();
+  uint16_t *dst = vt + static_cast<int64_t>(bh) * d * kv_pad;
+  for (int r = ty; r < 64; r += 4) {
+    const int l = l0 + tx;
+    if (l < kv_pad) dst[static_cast<int64_t>(d0 + r) * kv_pad + l] = tile[tx][r];
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                 const __grid_constant__ CUtensorMap tmap_vt, const KernelParams p) {
+  using L = Layout<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  __shared__ __align__(8) uint64_t q_full_bar;
+  __shared__ __align__(8) uint64_t k_full_bar[kKvStages], k_empty_bar[kKvStages];
+  __shared__ __align__(8) uint64_t v_full_bar[kKvStages], v_empty_bar[kKvStages];
+  __shared__ __align__(8) uint64_t s_full_bar[2], s_empty_bar[2];  // the two score buffers
+  __shared__ __align__(8) uint64_t p_full_bar;   // softmax -> MMA: the probabilities are in shared memory
+  __shared__ __align__(8) uint64_t pv_done_bar;  // MMA -> softmax: the block's output is in tensor memory, P is free
+  __shared__ __align__(8) uint64_t o_empty_bar;  // softmax -> MMA: the block's output has been read
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ volatile uint32_t abort_flag;
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * kBlockQ;
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int kv_head = head / p.group;
+  const int offset = p.kv_len - p.q_len;  // query i sits at key position i + offset
+  // Keys this CTA's queries can see: all of them, or up to its last query's position.
+  int kv_end = p.kv_len;
+  if (p.causal) {
+    const int last_q = min(q0 + kBlockQ, p.q_len) - 1;
+    kv_end = min(p.kv_len, last_q + offset + 1);
+  }
+  const int num_blocks = (kv_end + kBlockKv - 1) / kBlockKv;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&q_full_bar, 1);
+    for (int s = 0; s < kKvStages; ++s) {
+      mbar_init(&k_full_bar[s], 1);
+      mbar_init(&k_empty_bar[s], 1);
+      mbar_init(&v_full_bar[s], 1);
+      mbar_init(&v_empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full_bar[s], 1);
+      mbar_init(&s_empty_bar[s], kSoftmaxWarps);
+    }
+    mbar_init(&p_full_bar, kSoftmaxWarps);
+    mbar_init(&pv_done_bar, 1);
+    mbar_init(&o_empty_bar, kSoftmaxWarps);
+    fence_barrier_init();
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_vt);
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc<1>(&tmem_base_slot, L::kTmemCols);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  uint8_t *q_smem = smem + L::kQOff;
+  auto k_stage = [&](int s) { return smem + L::kKOff + s * L::kKBytes; };
+  auto v_stage = [&](int s) { return smem + L::kVOff + s * L::kVBytes; };
+  uint8_t *p_smem = smem + L::kPOff;
+
+  if (warp == kProducerWarp) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      bool ok = true;
+      mbar_arrive_expect_tx(&q_full_bar, L::kQBytes);
+#pragma unroll
+      for (int a = 0; a < L::kQAtoms; ++a) {
+        tma_load_4d(q_smem + a * kBlockQ * kAtomBytes, &tmap_q, &q_full_bar, a * kAtomBytes, q0, head, batch);
+      }
+      for (int j = 0; j < num_blocks && ok; ++j) {
+        const int st = j % kKvStages;
+        const uint32_t ph = (j / kKvStages) & 1;
+        if (!mbar_wait(&k_empty_bar[st], ph ^ 1, &abort_flag)) {
+          ok = false;
+          break;
+        }
+        mbar_arrive_expect_tx(&k_full_bar[st], L::kKBytes);
+#pragma unroll
+        for (int a = 0; a < L::kQAtoms; ++a) {
+          tma_load_4d(k_stage(st) + a * kBlockKv * kAtomBytes, &tmap_k, &k_full_bar[st], a * kAtomBytes, j * kBlockKv,
+                      kv_head, batch);
+        }
+        if (!mbar_wait(&v_empty_bar[st], ph ^ 1, &abort_flag)) {
+          ok = false;
+          break;
+        }
+        mbar_arrive_expect_tx(&v_full_bar[st], L::kVBytes);
+#pragma unroll
+        for (int a = 0; a < L::kVAtoms; ++a) {
+          tma_load_3d(v_stage(st) + a * L::kVAtomBytes, &tmap_vt, &v_full_bar[st],
+                      (j * kBlockKv + a * kAtomElems) * 2, 0, batch * p.kv_heads + kv_head);
+        }
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(p.status, 0u, kStatusAttentionTimeout);
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t fmt = p.is_bf16 ? 1u : 0u;
+      const uint32_t idesc_s = umma_idesc(kBlockQ, kBlockKv, fmt, fmt);
+      const uint32_t idesc_o = umma_idesc(kBlockQ, D, fmt, fmt);
+      const uint64_t qdesc0 = umma_desc_sw128(smem_u32(q_smem));
+      const uint64_t pdesc0 = umma_desc_sw128(smem_u32(p_smem));
+      constexpr uint64_t kMmaStep = kMmaKBytes >> 4;
+      constexpr int kMmasPerAtom = kAtomBytes / kMmaKBytes;
+      bool ok = true;
+      // S_j = Q K_j^T into score buffer j & 1.
+      auto issue_scores = [&](int j) -> bool {
+        const int st = j % kKvStages;
+        const uint32_t ph = (j / kKvStages) & 1;
+        if (!mbar_wait(&k_full_bar[st], ph, &abort_flag)) return false;
+        if (!mbar_wait(&s_empty_bar[j & 1], ((j >> 1) & 1) ^ 1, &abort_flag)) return false;
+        tc_fence_after_sync();
+        const uint64_t kdesc0 = umma_desc_sw128(smem_u32(k_stage(st)));
+        const uint32_t d_tmem = tmem_base + (j & 1) * L::kSCols;
+#pragma unroll
+        for (int a = 0; a < L::kQAtoms; ++a) {
+#pragma unroll
+          for (int i = 0; i < kMmasPerAtom; ++i) {
+            const uint64_t qd = qdesc0 + ((a * kBlockQ * kAtomBytes) >> 4) + i * kMmaStep;
+            const uint64_t kd = kdesc0 + ((a * kBlockKv * kAtomBytes) >> 4) + i * kMmaStep;
+            if (p.is_bf16) {
+              umma_ss<kKindBF16>(d_tmem, qd, kd, idesc_s, (a | i) != 0 ? 1u : 0u);
+            } else {
+              umma_ss<kKindF16>(d_tmem, qd, kd, idesc_s, (a | i) != 0 ? 1u : 0u);
+            }
+          }
+        }
+        umma_commit(&k_empty_bar[st]);
+        umma_commit(&s_full_bar[j & 1]);
+        return true;
+      };
+      if (!mbar_wait(&q_full_bar, 0, &abort_flag)) ok = false;
+      if (ok) ok = issue_scores(0);
+      for (int j = 0; j < num_blocks && ok; ++j) {
+        if (j + 1 < num_blocks && !issue_scores(j + 1)) {
+          ok = false;
+          break;
+        }
+        const int st = j % kKvStages;
+        const uint32_t ph = (j / kKvStages) & 1;
+        if (!mbar_wait(&p_full_bar, j & 1, &abort_flag) || !mbar_wait(&v_full_bar[st], ph, &abort_flag) ||
+            !mbar_wait(&o_empty_bar, (j & 1) ^ 1, &abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint64_t vdesc0 = umma_desc_sw128(smem_u32(v_stage(st)));
+        const uint32_t d_tmem = tmem_base + L::kOCol;
+#pragma unroll
+        for (int a = 0; a < L::kVAtoms; ++a) {
+#pragma unroll
+          for (int i = 0; i < kMmasPerAtom; ++i) {
+            const uint64_t pd = pdesc0 + ((a * L::kPAtomBytes) >> 4) + i * kMmaStep;
+            const uint64_t vd = vdesc0 + ((a * L::kVAtomBytes) >> 4) + i * kMmaStep;
+            if (p.is_bf16) {
+              umma_ss<kKindBF16>(d_tmem, pd, vd, idesc_o, (a | i) != 0 ? 1u : 0u);
+            } else {
+              umma_ss<kKindF16>(d_tmem, pd, vd, idesc_o, (a | i) != 0 ? 1u : 0u);
+            }
+          }
+        }
+        umma_commit(&v_empty_bar[st]);
+        umma_commit(&pv_done_bar);
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(p.status, 0u, kStatusAttentionTimeout);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax and output
+    const int row = static_cast<int>(warp) * 32 + static_cast<int>(lane);  // query within the CTA = lane of tensor memory
+    const int q_pos = q0 + row + offset;                                   // the last key this query sees under the causal mask
+    const uint32_t t_lane = tmem_base + ((warp * 32u) << 16);
+    // Where this row's 16-byte pieces go in an atom of P: piece c of row r sits at c ^ (r & 7).
+    uint8_t *p_row = p_smem + (row >> 3) * 1024 + (row & 7) * kAtomBytes;
+    const uint32_t p_xor = static_cast<uint32_t>(row & 7);
+    float o_acc[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o_acc[i] = 0.0f;
+    float m_run = -INFINITY;  // running maximum of the scaled scores
+    float l_run = 0.0f;       // running sum of exp2(score - maximum)
+    float alpha_prev = 0.0f;  // what the output so far is scaled by when the pending block is added
+    bool ok = true;
+    uint32_t v[32];
+
+    // o_acc = o_acc * alpha + (the block's output in tensor memory), then the buffer is handed back.
+    auto add_block_output = [&](int j, float alpha) -> bool {
+      if (!mbar_wait(&pv_done_bar, j & 1, &abort_flag)) return false;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        tmem_ld_32x32(t_lane + L::kOCol + c * 32, v);
+        tmem_ld_wait(v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha, __uint_as_float(v[i]));
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&o_empty_bar);
+      return true;
+    };
+
+    for (int j = 0; j < num_blocks && ok; ++j) {
+      const int key0 = j * kBlockKv;
+      const uint32_t t_s = t_lane + (j & 1) * L::kSCols;
+      // Does any key of this block need masking for any row of the CTA?
+      const bool edge = (key0 + kBlockKv > p.kv_len) || (p.causal && key0 + kBlockKv - 1 > q0 + offset);
+      const int key_limit = p.causal ? min(p.kv_len - 1, q_pos) : p.kv_len - 1;  // last key this row sees
+      if (!mbar_wait(&s_full_bar[j & 1], (j >> 1) & 1, &abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      // Pass 1: the row's maximum over the block.
+      float m_blk = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < kBlockKv / 32; ++c) {
+        tmem_ld_32x32(t_s + c * 32, v);
+        tmem_ld_wait(v);
+        if (edge) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (key0 + c * 32 + i <= key_limit) m_blk = fmaxf(m_blk, __uint_as_float(v[i]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) m_blk = fmaxf(m_blk, __uint_as_float(v[i]));
+        }
+      }
+      const float m_new = fmaxf(m_run, m_blk * p.scale_log2);
+      // A row that has seen no key yet (its keys start in a later block) keeps a zero sum.
+      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+      const float alpha = exp2f(m_run - m_use);
+      // The previous block's output, before its P is overwritten.
+      if (j > 0) {
+        if (!add_block_output(j - 1, alpha_prev)) {
+          ok = false;
+          break;
+        }
+      }
+      alpha_prev = alpha;
+      // Pass 2: the probabilities, into shared memory as the A operand of P V.
+      float sum = 0.0f;
+#pragma unroll
+      for (int c = 0; c < kBlockKv / 32; ++c) {
+        tmem_ld_32x32(t_s + c * 32, v);
+        tmem_ld_wait(v);
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float e0 = exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
+          float e1 = exp2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
+          if (edge) {
+            if (key0 + c * 32 + i > key_limit) e0 = 0.0f;
+            if (key0 + c * 32 + i + 1 > key_limit) e1 = 0.0f;
+          }
+          sum += e0 + e1;
+          packed[i >> 1] = pack16(e0, e1, p.is_bf16);
+        }
+        uint8_t *atom = p_row + (c >> 1) * L::kPAtomBytes;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint32_t piece = static_cast<uint32_t>((c & 1) * 4 + g) ^ p_xor;
+          *reinterpret_cast<uint4 *>(atom + piece * 16) =
+              make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+        }
+      }
+      l_run = fmaf(l_run, alpha, sum);
+      m_run = m_new;
+      fence_proxy_async_smem();  // the stores above, before the MMA's reads of them
+      tc_fence_before_sync();    // this thread's reads of S are done
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&p_full_bar);
+        mbar_arrive(&s_empty_bar[j & 1]);
+      }
+    }
+    if (ok && !add_block_output(num_blocks - 1, alpha_prev)) ok = false;
+    if (ok && q0 + row < p.q_len) {
+      const float inv = 1.0f / l_run;
+      uint16_t *dst = reinterpret_cast<uint16_t *>(p.out) + batch * p.out_stride[0] + head * p.out_stride[1] +
+                      static_cast<int64_t>(q0 + row) * p.out_stride[2];
+#pragma unroll
+      for (int g = 0; g < D / 8; ++g) {
+        uint4 w;
+        w.x = pack16(o_acc[g * 8 + 0] * inv, o_acc[g * 8 + 1] * inv, p.is_bf16);
+        w.y = pack16(o_acc[g * 8 + 2] * inv, o_acc[g * 8 + 3] * inv, p.is_bf16);
+        w.z = pack16(o_acc[g * 8 + 4] * inv, o_acc[g * 8 + 5] * inv, p.is_bf16);
+        w.w = pack16(o_acc[g * 8 + 6] * inv, o_acc[g * 8 + 7] * inv, p.is_bf16);
+        *reinterpret_cast<uint4 *>(dst + g * 8) = w;
+      }
+    }
+    if (!ok && lane == 0) {
+      abort_flag = 1;
+      atomicCAS(p.status, 0u, kStatusAttentionTimeout);
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (abort_flag != 0) {
+    // A wait gave up: give copies that may still be in flight time to land before the shared
+    // memory they target is released.
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    __syncthreads();
+  }
+  if (warp == kMmaWarp) {
+    tc_fence_after_sync();
+    tmem_dealloc<1>(tmem_base, L::kTmemCols);
+  }
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      return reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return static_cast<EncodeTiledFn>(nullptr);
+  }();
+  return fn;
+}
+
+// A byte tensor of `rank` dimensions, innermost contiguous, read in boxes of 128 bytes x box_rows
+// rows of the second dimension, 128-byte swizzle, zeros outside.
+bool make_tmap(CUtensorMap *map, const void *base, int rank, const uint64_t *dims, const uint64_t *strides_bytes,
+               uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t d[4];
+  cuuint64_t s[3];
+  cuuint32_t box[4] = {static_cast<cuuint32_t>(kAtomBytes), box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  for (int i = 0; i < rank; ++i) d[i] = dims[i];
+  for (int i = 0; i + 1 < rank; ++i) s[i] = strides_bytes[i];
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, static_cast<cuuint32_t>(rank), const_cast<void *>(base), d, s, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+int round_up(int x, int to) { return (x + to - 1) / to * to; }
+
+template <int D>
+cudaError_t launch(const AttentionArgs &a, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tvt,
+                   const KernelParams &kp, const char **why) {
+  using L = Layout<D>;
+  auto kernel = attention_kernel<D>;
+  static bool attr_set = false;  // per instantiation
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes);
+    if (e != cudaSuccess) {
+      *why = "cudaFuncSetAttribute(max dynamic shared memory) failed";
+      return e;
+    }
+    attr_set = true;
+  }
+  const dim3 grid(static_cast<unsigned>((a.q_len + kBlockQ - 1) / kBlockQ), static_cast<unsigned>(a.heads),
+                  static_cast<unsigned>(a.batch));
+  kernel<<<grid, kThreads, L::kSmemBytes, a.stream>>>(tq, tk, tvt, kp);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool attention_supported(const AttentionArgs &a, const char **why) {
+  auto fail = [&](const char *m) {
+    *why = m;
+    return false;
+  };
+  if (a.head_dim != 64 && a.head_dim != 128) return fail("head_dim is not 64 or 128");
+  if (a.batch < 0 || a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads != 0) return fail("heads is not a multiple of kv_heads");
+  if (a.batch > 65535 || a.heads > 65535) return fail("more than 65535 heads or batches");
+  if (a.q_len < 0 || a.kv_len <= 0) return fail("no keys");
+  if (a.causal && a.kv_len < a.q_len) return fail("the causal mask needs at least as many keys as queries");
+  const void *ptrs[4] = {a.q, a.k, a.v, a.out};
+  for (const void *ptr : ptrs) {
+    if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail("an operand does not start on a 16-byte boundary");
+  }
+  const int64_t *strides[4] = {a.q_stride, a.k_stride, a.v_stride, a.out_stride};
+  for (const int64_t *s : strides) {
+    for (int i = 0; i < 3; ++i) {
+      if (s[i] < 0 || s[i] % 8 != 0) return fail("a stride is negative or not a multiple of 8 elements");
+    }
+  }
+  return true;
+}
+
+size_t attention_scratch_bytes(int batch, int kv_heads, int kv_len, int head_dim) {
+  return static_cast<size_t>(batch) * kv_heads * head_dim * round_up(kv_len, kPadKv) * 2;
+}
+
+cudaError_t attention(const AttentionArgs &a, const char **why) {
+  *why = "";
+  if (!attention_supported(a, why)) return cudaErrorInvalidValue;
+  if (a.batch == 0 || a.q_len == 0) return cudaSuccess;
+  const int d = a.head_dim;
+  const int kv_pad = round_up(a.kv_len, kPadKv);
+
+  const dim3 tgrid(static_cast<unsigned>(kv_pad / 64), static_cast<unsigned>(d / 64),
+                   static_cast<unsigned>(a.batch * a.kv_heads));
+  transpose_v_kernel<<<tgrid, 256, 0, a.stream>>>(reinterpret_cast<const uint16_t *>(a.v), a.v_stride[0], a.v_stride[1],
+                                                  a.v_stride[2], a.kv_heads, a.kv_len, kv_pad, d,
+                                                  reinterpret_cast<uint16_t *>(a.v_transposed));
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    *why = "launching the transposition of v";
+    return e;
+  }
+
+  // q and k as (head_dim bytes, positions, heads, batch); a size-1 dimension's stride is never used
+  // but has to pass the encoder's checks.
+  auto dims4 = [&](int len, int heads, uint64_t *dims) {
+    dims[0] = static_cast<uint64_t>(d) * 2;
+    dims[1] = static_cast<uint64_t>(len);
+    dims[2] = static_cast<uint64_t>(heads);
+    dims[3] = static_cast<uint64_t>(a.batch);
+  };
+  auto strides4 = [&](const int64_t *s, uint64_t *out) {
+    out[0] = static_cast<uint64_t>(s[2] > 0 ? s[2] : d) * 2;
+    out[1] = static_cast<uint64_t>(s[1] > 0 ? s[1] : d) * 2;
+    out[2] = static_cast<uint64_t>(s[0] > 0 ? s[0] : d) * 2;
+  };
+  uint64_t dims[4], strides[3];
+  CUtensorMap tq, tk, tvt;
+  dims4(a.q_len, a.heads, dims);
+  strides4(a.q_stride, strides);
+  if (!make_tmap(&tq, a.q, 4, dims, strides, kBlockQ)) {
+    *why = "cuTensorMapEncodeTiled refused q";
+    return cudaErrorInvalidValue;
+  }
+  dims4(a.kv_len, a.kv_heads, dims);
+  strides4(a.k_stride, strides);
+  if (!make_tmap(&tk, a.k, 4, dims, strides, kBlockKv)) {
+    *why = "cuTensorMapEncodeTiled refused k";
+    return cudaErrorInvalidValue;
+  }
+  uint64_t vdims[3] = {static_cast<uint64_t>(kv_pad) * 2, static_cast<uint64_t>(d),
+                       static_cast<uint64_t>(a.batch) * a.kv_heads};
+  uint64_t vstrides[2] = {static_cast<uint64_t>(kv_pad) * 2, static_cast<uint64_t>(d) * kv_pad * 2};
+  if (!make_tmap(&tvt, a.v_transposed, 3, vdims, vstrides, static_cast<uint32_t>(d))) {
+    *why = "cuTensorMapEncodeTiled refused the transposed v";
+    return cudaErrorInvalidValue;
+  }
+
+  KernelParams kp = {};
+  kp.out = a.out;
+  for (int i = 0; i < 3; ++i) kp.out_stride[i] = a.out_stride[i];
+  kp.is_bf16 = a.is_bf16;
+  kp.heads = a.heads;
+  kp.kv_heads = a.kv_heads;
+  kp.group = a.heads / a.kv_heads;
+  kp.q_len = a.q_len;
+  kp.kv_len = a.kv_len;
+  kp.causal = a.causal;
+  kp.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(d));
+  kp.status = a.status;
+  if (d == 64) return launch<64>(a, tq, tk, tvt, kp, why);
+  return launch<128>(a, tq, tk, tvt, kp, why);
+}
+
+}  // namespace flsm100

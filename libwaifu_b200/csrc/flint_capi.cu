@@ -18,6 +18,7 @@
 #include "quant_sm100.cuh"
 #include "block_sm100.cuh"
 #include "skinny_sm100.cuh"
+#include "attention_sm100.cuh"
 
 using namespace flsm100;
 
@@ -1500,6 +1501,75 @@ int32_t fl_qk_norm_rope(fl_tensor_view_t qkv_h, fl_tensor_view_t q_weight_h, fl_
                             reinterpret_cast<const float *>(raw_ptr(cos)), reinterpret_cast<const float *>(raw_ptr(sin)), eps, 0),
                "q/k norm and rotation");
     ++g_block_launches;
+    return clear_error();
+  });
+}
+
+// flint/capi.h:532-544 for the masks none and causal. The block masks have no kernel here and are
+// refused with the reason, as the reference's devices without one refuse them.
+int32_t fl_attention(fl_operators_t operators, fl_tensor_view_t q_h, fl_tensor_view_t k_h, fl_tensor_view_t v_h,
+                     fl_mask_type_t mask_type, int32_t block_size, fl_tensor_view_t out_h) {
+  return guard([&]() -> int32_t {
+    if (!operators) invalid("operators is null");
+    const fl_tensor_view_impl_t &q = deref(q_h);
+    const fl_tensor_view_impl_t &k = deref(k_h);
+    const fl_tensor_view_impl_t &v = deref(v_h);
+    const fl_tensor_view_impl_t &out = deref(out_h);
+    if (mask_type < FL_MASK_NONE || mask_type > FL_MASK_BLOCK_DIAGONAL) invalid("attention: unknown mask type");
+    if (mask_type == FL_MASK_NONE || mask_type == FL_MASK_CAUSAL) {
+      if (block_size != 0) invalid("attention: a block size beside a mask that has no blocks");
+    } else {
+      if (block_size <= 0) invalid("attention: a block mask without a block size");
+      invalid("attention: the block masks are not implemented in this library");
+    }
+    for (const fl_tensor_view_impl_t *t : {&q, &k, &v, &out}) {
+      if (t->shape.size() != 4) invalid("attention: q, k, v and out are four-dimensional");
+      if (device_of(*t) != FL_DEVICE_CUDA) invalid("an operand is not on the operators' device");
+      if (!is_half_type(dtype_of(*t)) || dtype_of(*t) != dtype_of(q)) {
+        invalid("attention: this library takes <float16> or <bfloat16> operands of one type");
+      }
+      if (t->shape[3] > 1 && t->stride[3] != 1) invalid("attention: the last dimension is not contiguous");
+    }
+    const int batch = q.shape[0], heads = q.shape[1], q_len = q.shape[2], d = q.shape[3];
+    const int kv_heads = k.shape[1], kv_len = k.shape[2];
+    if (k.shape[0] != batch || k.shape[3] != d || v.shape != k.shape) invalid("attention: k and v disagree with q or each other");
+    if (out.shape != q.shape) invalid("attention: out is not of q's shape");
+    if (kv_heads <= 0 || heads % kv_heads != 0) invalid("attention: the query heads are not a multiple of the key-value heads");
+    if (kv_len <= 0) invalid("attention: no keys");
+    if (mask_type == FL_MASK_CAUSAL && kv_len < q_len) invalid("attention: keys too few for the causal mask");
+    require_kernels();
+    check_earlier_kernel_status();
+    if (batch == 0 || q_len == 0) return clear_error();
+
+    AttentionArgs a = {};
+    a.q = raw_ptr(q);
+    a.k = raw_ptr(k);
+    a.v = raw_ptr(v);
+    a.out = raw_ptr(out);
+    a.is_bf16 = dtype_of(q) == FL_DTYPE_BFLOAT16;
+    a.batch = batch;
+    a.heads = heads;
+    a.kv_heads = kv_heads;
+    a.q_len = q_len;
+    a.kv_len = kv_len;
+    a.head_dim = d;
+    for (int i = 0; i < 3; ++i) {
+      a.q_stride[i] = q.stride[i];
+      a.k_stride[i] = k.stride[i];
+      a.v_stride[i] = v.stride[i];
+      a.out_stride[i] = out.stride[i];
+    }
+    a.causal = mask_type == FL_MASK_CAUSAL;
+    a.status = status_word();
+    a.stream = 0;
+    const char *why = "";
+    if (!attention_supported(a, &why)) invalid(std::string("attention: ") + why + " (not implemented in this library)");
+    Scratch scratch;
+    const size_t vt_off = scratch.reserve(attention_scratch_bytes(batch, kv_heads, kv_len, d));
+    a.v_transposed = scratch.commit() + vt_off;
+    cudaError_t e = attention(a, &why);
+    if (e != cudaSuccess) cuda_check(e, (std::string("attention: ") + why).c_str());
+    g_block_launches += 2;
     return clear_error();
   });
 }

@@ -118,6 +118,8 @@ def lib() -> ctypes.CDLL:
     L.fl_fp8_swiglu_quantize.restype = c_int32
     L.fl_qk_norm_rope.argtypes = [V, V, V, V, V, ctypes.c_float, c_int32]
     L.fl_qk_norm_rope.restype = c_int32
+    L.fl_attention.argtypes = [V, V, V, V, c_int32, c_int32, V]
+    L.fl_attention.restype = c_int32
     L.fl_sm100_set_device.argtypes = [c_int32]
     L.fl_sm100_synchronize.argtypes = [POINTER(c_int32)]
     L.fl_sm100_launch_count.restype = c_int64
@@ -503,6 +505,24 @@ def qk_norm_rope(qkv: Tensor, cos: Tensor, sin: Tensor, heads: int, eps: float =
     check(lib().fl_qk_norm_rope(qkv.raw(), q_weight.raw() if q_weight else None, k_weight.raw() if k_weight else None,
                                 cos.raw(), sin.raw(), float(eps), int(heads)))
     return qkv
+
+
+class MaskType:
+    """fl_mask_type_t (flint/capi.h:118-133)."""
+    NONE = 0
+    CAUSAL = 1
+    BLOCK_CAUSAL = 2
+    BLOCK_DIAGONAL = 3
+
+
+def attention(q: Tensor, k: Tensor, v: Tensor, mask_type: int = MaskType.NONE, block_size: int = 0,
+              out: Optional[Tensor] = None) -> Tensor:
+    """fl_attention (flint/capi.h:532-544): q (N, heads, L, D), k and v (N, kv_heads, S, D), any
+    strides with a contiguous last dimension; out (N, heads, L, D), contiguous when made here."""
+    if out is None:
+        out = Tensor.empty(tuple(q.shape), q.dtype)
+    check(lib().fl_attention(operators(), q.raw(), k.raw(), v.raw(), int(mask_type), int(block_size), out.raw()))
+    return out
 
 
 def quantize_fp8_activation(a: Tensor):

@@ -243,6 +243,34 @@ def qk_norm_rope(qkv16: np.ndarray, cos: np.ndarray, sin: np.ndarray, heads: int
     return out
 
 
+def attention(q16: np.ndarray, k16: np.ndarray, v16: np.ndarray, causal: bool, is_bf16: bool) -> np.ndarray:
+    """Scaled dot product attention on 16-bit bit patterns, q (N, heads, L, D), k and v
+    (N, kv_heads, S, D) with kv_heads dividing heads (query head h reads key-value head
+    h // (heads / kv_heads), flint/operators.h:255-260): softmax(q k^T / sqrt(D)) v in float64,
+    under the causal mask query i seeing keys 0 .. i + S - L (flint/capi.h:118-126). Returns
+    float64; no intermediate is rounded, so a kernel that rounds its probabilities to 16 bits
+    (flint/cuda/attention.cu:30-70, flint/operators.cc:170-175) agrees to that rounding."""
+    q = widen(np.asarray(q16, np.uint16), is_bf16).astype(np.float64)
+    k = widen(np.asarray(k16, np.uint16), is_bf16).astype(np.float64)
+    v = widen(np.asarray(v16, np.uint16), is_bf16).astype(np.float64)
+    n, heads, L, d = q.shape
+    kv_heads, S = k.shape[1], k.shape[2]
+    group = heads // kv_heads
+    out = np.empty((n, heads, L, d), np.float64)
+    keep = None
+    if causal:
+        keep = np.arange(S)[None, :] <= (np.arange(L)[:, None] + (S - L))
+    for b in range(n):
+        for h in range(heads):
+            s = q[b, h] @ k[b, h // group].T / np.sqrt(float(d))
+            if keep is not None:
+                s = np.where(keep, s, -np.inf)
+            s -= s.max(axis=1, keepdims=True)
+            p = np.exp(s)
+            out[b, h] = (p @ v[b, h // group]) / p.sum(axis=1, keepdims=True)
+    return out
+
+
 def decode_e4m3(codes: np.ndarray) -> np.ndarray:
     codes = np.ascontiguousarray(codes, dtype=np.uint8)
     out = np.empty(codes.shape, dtype=np.float32)
@@ -278,6 +306,7 @@ class _Ref:
         L.fl_layer_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p]
         L.fl_rms_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_float, c_void_p]
         L.fl_swiglu.argtypes = [c_void_p, c_void_p, c_void_p]
+        L.fl_attention.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
         try:
             L.fl_set_log_level.argtypes = [c_int32]
             L.fl_set_log_level.restype = None
@@ -355,6 +384,23 @@ class _Ref:
     def swiglu(self, x: np.ndarray) -> np.ndarray:
         """fl_swiglu (flint/capi.h:517-519)."""
         return self._unary(lambda vx, a, vo: self.L.fl_swiglu(self.ops, vx, vo), x, x.shape[1] // 2)
+
+    def attention(self, q: np.ndarray, k: np.ndarray, v: np.ndarray, causal: bool) -> np.ndarray:
+        """fl_attention on the CPU device with float32 operands (flint/capi.h:532-544): q
+        (N, heads, L, D), k and v (N, kv_heads, S, D), contiguous."""
+        arrs = [np.ascontiguousarray(t, dtype=np.float32) for t in (q, k, v)]
+        out = np.empty(arrs[0].shape, dtype=np.float32)
+        held = []
+        try:
+            for t in arrs + [out]:
+                stride = [int(np.prod(t.shape[i + 1:])) for i in range(4)]
+                held.append(self._view(t, t.shape, stride))
+            self._check(self.L.fl_attention(self.ops, held[0][1], held[1][1], held[2][1], 1 if causal else 0, 0, held[3][1]))
+        finally:
+            for d, vw in held:
+                self.L.fl_tensor_view_destroy(vw)
+                self.L.fl_tensor_data_destroy(d)
+        return out
 
 
 _ref = None
