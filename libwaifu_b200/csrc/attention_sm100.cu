@@ -7,8 +7,9 @@
 //                  memory (a row is a lane, so no shuffles), keeps the running maximum and sum,
 //                  and writes P = exp2(S' - max) as 16-bit values into shared memory in the layout
 //                  the next product reads its A operand in (128-byte swizzle, K-major);
-//   O_blk = P V    tcgen05.mma, 128 x head_dim x 128, into tensor memory; the threads add it to
-//                  their output rows in registers, rescaled as the online softmax has it.
+//   O += P V       tcgen05.mma, 128 x head_dim x 128, accumulating in tensor memory; when a row's
+//                  maximum has grown enough to matter the threads rescale their output rows
+//                  there (tcgen05.ld / st) before handing P over.
 // K and V blocks arrive by TMA into two-stage rings. V is the B operand of the second product and
 // is read K-major, i.e. as V^T: a small kernel transposes it into scratch first.
 //
@@ -139,8 +140,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   __shared__ __align__(8) uint64_t v_full_bar[kKvStages], v_empty_bar[kKvStages];
   __shared__ __align__(8) uint64_t s_full_bar[2], s_empty_bar[2];  // the two score buffers
   __shared__ __align__(8) uint64_t p_full_bar;   // softmax -> MMA: the probabilities are in shared memory
-  __shared__ __align__(8) uint64_t pv_done_bar;  // MMA -> softmax: the block's output is in tensor memory, P is free
-  __shared__ __align__(8) uint64_t o_empty_bar;  // softmax -> MMA: the block's output has been read
+  __shared__ __align__(8) uint64_t pv_done_bar;  // MMA -> softmax: the block is in the output, P is free
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile uint32_t abort_flag;
 
@@ -174,7 +174,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
     mbar_init(&p_full_bar, kSoftmaxWarps);
     mbar_init(&pv_done_bar, 1);
-    mbar_init(&o_empty_bar, kSoftmaxWarps);
     fence_barrier_init();
   }
   if (warp == kProducerWarp && lane == 0) {
@@ -280,8 +279,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         const int st = j % kKvStages;
         const uint32_t ph = (j / kKvStages) & 1;
-        if (!mbar_wait(&p_full_bar, j & 1, &abort_flag) || !mbar_wait(&v_full_bar[st], ph, &abort_flag) ||
-            !mbar_wait(&o_empty_bar, (j & 1) ^ 1, &abort_flag)) {
+        if (!mbar_wait(&p_full_bar, j & 1, &abort_flag) || !mbar_wait(&v_full_bar[st], ph, &abort_flag)) {
           ok = false;
           break;
         }
@@ -295,9 +293,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             const uint64_t pd = pdesc0 + ((a * L::kPAtomBytes) >> 4) + i * kMmaStep;
             const uint64_t vd = vdesc0 + ((a * L::kVAtomBytes) >> 4) + i * kMmaStep;
             if (p.is_bf16) {
-              umma_ss<kKindBF16>(d_tmem, pd, vd, idesc_o, (a | i) != 0 ? 1u : 0u);
+              umma_ss<kKindBF16>(d_tmem, pd, vd, idesc_o, (j | a | i) != 0 ? 1u : 0u);
             } else {
-              umma_ss<kKindF16>(d_tmem, pd, vd, idesc_o, (a | i) != 0 ? 1u : 0u);
+              umma_ss<kKindF16>(d_tmem, pd, vd, idesc_o, (j | a | i) != 0 ? 1u : 0u);
             }
           }
         }
@@ -317,31 +315,17 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     // Where this row's 16-byte pieces go in an atom of P: piece c of row r sits at c ^ (r & 7).
     uint8_t *p_row = p_smem + (row >> 3) * 1024 + (row & 7) * kAtomBytes;
     const uint32_t p_xor = static_cast<uint32_t>(row & 7);
-    float o_acc[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o_acc[i] = 0.0f;
-    float m_run = -INFINITY;  // running maximum of the scaled scores
-    float l_run = 0.0f;       // running sum of exp2(score - maximum)
-    float alpha_prev = 0.0f;  // what the output so far is scaled by when the pending block is added
+    // The probabilities and the output in tensor memory are relative to m_used, which follows the
+    // row's running maximum only when that has grown by more than kRescaleStep (in log2 units)
+    // for some row of the warp: until then exp2(score - m_used) <= 2^kRescaleStep, which every
+    // type here holds, and the output needs no rescaling. The normalisation at the end divides by
+    // the sum taken relative to the same m_used, so the result is the same quotient.
+    constexpr float kRescaleStep = 8.0f;
+    float m_used = -INFINITY;
+    float l_run = 0.0f;
     bool ok = true;
+    uint32_t sc[kBlockKv / 32][32];  // this row's scores of the block
     uint32_t v[32];
-
-    // o_acc = o_acc * alpha + (the block's output in tensor memory), then the buffer is handed back.
-    auto add_block_output = [&](int j, float alpha) -> bool {
-      if (!mbar_wait(&pv_done_bar, j & 1, &abort_flag)) return false;
-      tc_fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        tmem_ld_32x32(t_lane + L::kOCol + c * 32, v);
-        tmem_ld_wait(v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha, __uint_as_float(v[i]));
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&o_empty_bar);
-      return true;
-    };
 
     for (int j = 0; j < num_blocks && ok; ++j) {
       const int key0 = j * kBlockKv;
@@ -349,54 +333,62 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // Does any key of this block need masking for any row of the CTA?
       const bool edge = (key0 + kBlockKv > p.kv_len) || (p.causal && key0 + kBlockKv - 1 > q0 + offset);
       const int key_limit = p.causal ? min(p.kv_len - 1, q_pos) : p.kv_len - 1;  // last key this row sees
-      if (!mbar_wait(&s_full_bar[j & 1], (j >> 1) & 1, &abort_flag)) {
-        ok = false;
-        break;
-      }
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full_bar[j & 1], (j >> 1) & 1, &abort_flag));
+      if (!ok) break;
       tc_fence_after_sync();
-      // Pass 1: the row's maximum over the block.
+      // The whole row into registers in one round trip; the buffer goes back to the MMAs at once.
+#pragma unroll
+      for (int c = 0; c < kBlockKv / 32; ++c) tmem_ld_32x32(t_s + c * 32, sc[c]);
+#pragma unroll
+      for (int c = 0; c < kBlockKv / 32; ++c) tmem_ld_wait(sc[c]);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty_bar[j & 1]);
+      // Scaled to log2 units, masked, and the row's maximum over the block.
       float m_blk = -INFINITY;
 #pragma unroll
       for (int c = 0; c < kBlockKv / 32; ++c) {
-        tmem_ld_32x32(t_s + c * 32, v);
-        tmem_ld_wait(v);
-        if (edge) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (key0 + c * 32 + i <= key_limit) m_blk = fmaxf(m_blk, __uint_as_float(v[i]));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) m_blk = fmaxf(m_blk, __uint_as_float(v[i]));
+        for (int i = 0; i < 32; ++i) {
+          float x = __uint_as_float(sc[c][i]) * p.scale_log2;
+          if (edge && key0 + c * 32 + i > key_limit) x = -INFINITY;
+          sc[c][i] = __float_as_uint(x);
+          m_blk = fmaxf(m_blk, x);
         }
       }
-      const float m_new = fmaxf(m_run, m_blk * p.scale_log2);
-      // A row that has seen no key yet (its keys start in a later block) keeps a zero sum.
-      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
-      const float alpha = exp2f(m_run - m_use);
-      // The previous block's output, before its P is overwritten.
+      // The previous block's P V is done: P may be overwritten and the output is complete so far.
       if (j > 0) {
-        if (!add_block_output(j - 1, alpha_prev)) {
-          ok = false;
-          break;
-        }
+        ok = __all_sync(0xffffffffu, mbar_wait(&pv_done_bar, (j - 1) & 1, &abort_flag));
+        if (!ok) break;
+        tc_fence_after_sync();
       }
-      alpha_prev = alpha;
-      // Pass 2: the probabilities, into shared memory as the A operand of P V.
+      if (__any_sync(0xffffffffu, m_blk > m_used + kRescaleStep)) {
+        const float m_new = fmaxf(m_used, m_blk);
+        const float alpha = exp2f(m_used - ((m_new == -INFINITY) ? 0.0f : m_new));  // 0 for a row's first keys
+        l_run *= alpha;
+        if (j > 0) {
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            tmem_ld_32x32(t_lane + L::kOCol + c * 32, v);
+            tmem_ld_wait(v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32(t_lane + L::kOCol + c * 32, v);
+          }
+          tmem_st_wait();
+        }
+        m_used = m_new;
+      }
+      const float m_sub = (m_used == -INFINITY) ? 0.0f : m_used;  // a row that has seen no key yet: every score is -inf
+      // The probabilities, into shared memory as the A operand of P V.
       float sum = 0.0f;
 #pragma unroll
       for (int c = 0; c < kBlockKv / 32; ++c) {
-        tmem_ld_32x32(t_s + c * 32, v);
-        tmem_ld_wait(v);
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float e0 = exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
-          float e1 = exp2f(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
-          if (edge) {
-            if (key0 + c * 32 + i > key_limit) e0 = 0.0f;
-            if (key0 + c * 32 + i + 1 > key_limit) e1 = 0.0f;
-          }
+          const float e0 = exp2f(__uint_as_float(sc[c][i]) - m_sub);
+          const float e1 = exp2f(__uint_as_float(sc[c][i + 1]) - m_sub);
           sum += e0 + e1;
           packed[i >> 1] = pack16(e0, e1, p.is_bf16);
         }
@@ -408,29 +400,34 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
               make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
         }
       }
-      l_run = fmaf(l_run, alpha, sum);
-      m_run = m_new;
+      l_run += sum;
       fence_proxy_async_smem();  // the stores above, before the MMA's reads of them
-      tc_fence_before_sync();    // this thread's reads of S are done
+      tc_fence_before_sync();    // and the rescaled output, before the MMA accumulates into it
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&p_full_bar);
-        mbar_arrive(&s_empty_bar[j & 1]);
-      }
+      if (lane == 0) mbar_arrive(&p_full_bar);
     }
-    if (ok && !add_block_output(num_blocks - 1, alpha_prev)) ok = false;
-    if (ok && q0 + row < p.q_len) {
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&pv_done_bar, (num_blocks - 1) & 1, &abort_flag));
+    if (ok) {
+      tc_fence_after_sync();
+      const bool live = q0 + row < p.q_len;
       const float inv = 1.0f / l_run;
       uint16_t *dst = reinterpret_cast<uint16_t *>(p.out) + batch * p.out_stride[0] + head * p.out_stride[1] +
                       static_cast<int64_t>(q0 + row) * p.out_stride[2];
 #pragma unroll
-      for (int g = 0; g < D / 8; ++g) {
-        uint4 w;
-        w.x = pack16(o_acc[g * 8 + 0] * inv, o_acc[g * 8 + 1] * inv, p.is_bf16);
-        w.y = pack16(o_acc[g * 8 + 2] * inv, o_acc[g * 8 + 3] * inv, p.is_bf16);
-        w.z = pack16(o_acc[g * 8 + 4] * inv, o_acc[g * 8 + 5] * inv, p.is_bf16);
-        w.w = pack16(o_acc[g * 8 + 6] * inv, o_acc[g * 8 + 7] * inv, p.is_bf16);
-        *reinterpret_cast<uint4 *>(dst + g * 8) = w;
+      for (int c = 0; c < D / 32; ++c) {
+        tmem_ld_32x32(t_lane + L::kOCol + c * 32, v);
+        tmem_ld_wait(v);
+        if (live) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = pack16(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv, p.is_bf16);
+            w.y = pack16(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv, p.is_bf16);
+            w.z = pack16(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv, p.is_bf16);
+            w.w = pack16(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv, p.is_bf16);
+            *reinterpret_cast<uint4 *>(dst + c * 32 + g * 8) = w;
+          }
+        }
       }
     }
     if (!ok && lane == 0) {
