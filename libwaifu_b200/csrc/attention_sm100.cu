@@ -25,11 +25,20 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "ptx_sm100.cuh"
 
 namespace flsm100 {
 
 namespace {
+
+#ifdef FLSM100_PROBE
+#ifndef FLSM100_ATT_PROBE
+#define FLSM100_ATT_PROBE 0
+#endif
+constexpr int kAttProbe = FLSM100_ATT_PROBE;  // development builds: parts compiled out for timing
+#endif
 
 constexpr int kBlockQ = 128;   // queries per CTA = lanes of tensor memory
 constexpr int kBlockKv = 128;  // keys per step
@@ -57,7 +66,8 @@ struct Layout {
   static constexpr int kKOff = kQOff + kQBytes;
   static constexpr int kVOff = kKOff + kKvStages * kKBytes;
   static constexpr int kPOff = kVOff + kKvStages * kVBytes;
-  static constexpr int kSmemBytes = kPOff + kPBytes + 1024;  // + slack to align to 1024
+  static constexpr int kPBuffers = 2;  // the softmax of block j + 1 writes beside the product that reads block j's
+  static constexpr int kSmemBytes = kPOff + kPBuffers * kPBytes + 1024;  // + slack to align to 1024
   // Tensor memory: two score buffers, then the block's output.
   static constexpr int kSCols = kBlockKv;
   static constexpr int kOCol = 2 * kSCols;
@@ -76,6 +86,7 @@ struct KernelParams {
   int causal;
   float scale_log2;
   uint32_t *status;
+  int probe;  // development builds (-DFLSM100_PROBE) only: parts switched off for timing
 };
 
 __device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *desc, uint64_t *bar, int32_t c0,
@@ -140,7 +151,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   __shared__ __align__(8) uint64_t v_full_bar[kKvStages], v_empty_bar[kKvStages];
   __shared__ __align__(8) uint64_t s_full_bar[2], s_empty_bar[2];  // the two score buffers
   __shared__ __align__(8) uint64_t p_full_bar;   // softmax -> MMA: the probabilities are in shared memory
-  __shared__ __align__(8) uint64_t pv_done_bar;  // MMA -> softmax: the block is in the output, P is free
+  // MMA -> softmax: the block is in the output and its P buffer is free. One barrier per P buffer:
+  // the softmax runs up to two products ahead of the one it waits for, and a waiter may lag an
+  // mbarrier by less than two phases.
+  __shared__ __align__(8) uint64_t pv_done_bar[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile uint32_t abort_flag;
 
@@ -173,7 +187,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       mbar_init(&s_empty_bar[s], kSoftmaxWarps);
     }
     mbar_init(&p_full_bar, kSoftmaxWarps);
-    mbar_init(&pv_done_bar, 1);
+    mbar_init(&pv_done_bar[0], 1);
+    mbar_init(&pv_done_bar[1], 1);
     fence_barrier_init();
   }
   if (warp == kProducerWarp && lane == 0) {
@@ -211,6 +226,17 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           ok = false;
           break;
         }
+#ifdef FLSM100_PROBE
+        if (kAttProbe & 64) {  // timing probe: hand the stages over without loading them
+          mbar_arrive(&k_full_bar[st]);
+          if (!mbar_wait(&v_empty_bar[st], ph ^ 1, &abort_flag)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive(&v_full_bar[st]);
+          continue;
+        }
+#endif
         mbar_arrive_expect_tx(&k_full_bar[st], L::kKBytes);
 #pragma unroll
         for (int a = 0; a < L::kQAtoms; ++a) {
@@ -259,6 +285,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           for (int i = 0; i < kMmasPerAtom; ++i) {
             const uint64_t qd = qdesc0 + ((a * kBlockQ * kAtomBytes) >> 4) + i * kMmaStep;
             const uint64_t kd = kdesc0 + ((a * kBlockKv * kAtomBytes) >> 4) + i * kMmaStep;
+#ifdef FLSM100_PROBE
+            if (kAttProbe & 8) continue;
+#endif
             if (p.is_bf16) {
               umma_ss<kKindBF16>(d_tmem, qd, kd, idesc_s, (a | i) != 0 ? 1u : 0u);
             } else {
@@ -290,8 +319,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         for (int a = 0; a < L::kVAtoms; ++a) {
 #pragma unroll
           for (int i = 0; i < kMmasPerAtom; ++i) {
-            const uint64_t pd = pdesc0 + ((a * L::kPAtomBytes) >> 4) + i * kMmaStep;
+            const uint64_t pd = pdesc0 + (((j & 1) * L::kPBytes + a * L::kPAtomBytes) >> 4) + i * kMmaStep;
             const uint64_t vd = vdesc0 + ((a * L::kVAtomBytes) >> 4) + i * kMmaStep;
+#ifdef FLSM100_PROBE
+            if (kAttProbe & 4) continue;
+#endif
             if (p.is_bf16) {
               umma_ss<kKindBF16>(d_tmem, pd, vd, idesc_o, (j | a | i) != 0 ? 1u : 0u);
             } else {
@@ -300,7 +332,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           }
         }
         umma_commit(&v_empty_bar[st]);
-        umma_commit(&pv_done_bar);
+        umma_commit(&pv_done_bar[j & 1]);
       }
       if (!ok) {
         abort_flag = 1;
@@ -326,6 +358,18 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     bool ok = true;
     uint32_t sc[kBlockKv / 32][32];  // this row's scores of the block
     uint32_t v[32];
+    // Waits, in order and each once, until `count` of the P V products have completed.
+    int products_seen = 0;
+    auto wait_products = [&](int count) -> bool {
+      while (products_seen < count) {
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(&pv_done_bar[products_seen & 1], (products_seen >> 1) & 1, &abort_flag));
+        if (!ok) return false;
+        ++products_seen;
+      }
+      tc_fence_after_sync();
+      return true;
+    };
 
     for (int j = 0; j < num_blocks && ok; ++j) {
       const int key0 = j * kBlockKv;
@@ -337,6 +381,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (!ok) break;
       tc_fence_after_sync();
       // The whole row into registers in one round trip; the buffer goes back to the MMAs at once.
+#ifdef FLSM100_PROBE
+      if (!(kAttProbe & 32))
+#endif
 #pragma unroll
       for (int c = 0; c < kBlockKv / 32; ++c) tmem_ld_32x32(t_s + c * 32, sc[c]);
 #pragma unroll
@@ -345,7 +392,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty_bar[j & 1]);
       // Scaled to log2 units, masked, and the row's maximum over the block.
-      float m_blk = -INFINITY;
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
+#ifdef FLSM100_PROBE
+      if (kAttProbe & 16) m4[0] = 0.0f;
+      if (!(kAttProbe & 16))
+#endif
 #pragma unroll
       for (int c = 0; c < kBlockKv / 32; ++c) {
 #pragma unroll
@@ -353,16 +404,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           float x = __uint_as_float(sc[c][i]) * p.scale_log2;
           if (edge && key0 + c * 32 + i > key_limit) x = -INFINITY;
           sc[c][i] = __float_as_uint(x);
-          m_blk = fmaxf(m_blk, x);
+          m4[i & 3] = fmaxf(m4[i & 3], x);
         }
       }
-      // The previous block's P V is done: P may be overwritten and the output is complete so far.
-      if (j > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&pv_done_bar, (j - 1) & 1, &abort_flag));
-        if (!ok) break;
-        tc_fence_after_sync();
-      }
+      const float m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      // P V of block j - 2 is done: its P buffer, which this block takes, may be overwritten.
+      if (!wait_products(j - 1)) break;
       if (__any_sync(0xffffffffu, m_blk > m_used + kRescaleStep)) {
+        // The output is about to be rescaled: it has to be complete up to the previous block.
+        if (!wait_products(j)) break;
         const float m_new = fmaxf(m_used, m_blk);
         const float alpha = exp2f(m_used - ((m_new == -INFINITY) ? 0.0f : m_new));  // 0 for a row's first keys
         l_run *= alpha;
@@ -381,18 +431,29 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
       const float m_sub = (m_used == -INFINITY) ? 0.0f : m_used;  // a row that has seen no key yet: every score is -inf
       // The probabilities, into shared memory as the A operand of P V.
-      float sum = 0.0f;
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int c = 0; c < kBlockKv / 32; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
+#ifdef FLSM100_PROBE
+          const float e0 = (kAttProbe & 1) ? __uint_as_float(sc[c][i]) - m_sub : exp2f(__uint_as_float(sc[c][i]) - m_sub);
+          const float e1 = (kAttProbe & 1) ? __uint_as_float(sc[c][i + 1]) - m_sub : exp2f(__uint_as_float(sc[c][i + 1]) - m_sub);
+#else
           const float e0 = exp2f(__uint_as_float(sc[c][i]) - m_sub);
           const float e1 = exp2f(__uint_as_float(sc[c][i + 1]) - m_sub);
-          sum += e0 + e1;
+#endif
+          sum4[(i >> 1) & 3] += e0 + e1;
           packed[i >> 1] = pack16(e0, e1, p.is_bf16);
         }
-        uint8_t *atom = p_row + (c >> 1) * L::kPAtomBytes;
+        uint8_t *atom = p_row + (j & 1) * L::kPBytes + (c >> 1) * L::kPAtomBytes;
+#ifdef FLSM100_PROBE
+        if (kAttProbe & 2) {
+          if (packed[0] == 0x12345678u) atom[0] = 1;  // keeps the arithmetic alive
+          continue;
+        }
+#endif
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const uint32_t piece = static_cast<uint32_t>((c & 1) * 4 + g) ^ p_xor;
@@ -400,15 +461,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
               make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
         }
       }
-      l_run += sum;
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       fence_proxy_async_smem();  // the stores above, before the MMA's reads of them
       tc_fence_before_sync();    // and the rescaled output, before the MMA accumulates into it
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full_bar);
     }
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&pv_done_bar, (num_blocks - 1) & 1, &abort_flag));
+    if (ok) wait_products(num_blocks);
     if (ok) {
-      tc_fence_after_sync();
       const bool live = q0 + row < p.q_len;
       const float inv = 1.0f / l_run;
       uint16_t *dst = reinterpret_cast<uint16_t *>(p.out) + batch * p.out_stride[0] + head * p.out_stride[1] +
@@ -602,6 +662,9 @@ cudaError_t attention(const AttentionArgs &a, const char **why) {
   kp.causal = a.causal;
   kp.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(d));
   kp.status = a.status;
+#ifdef FLSM100_PROBE
+  if (const char *v = std::getenv("FLSM100_PROBE")) kp.probe = std::atoi(v);
+#endif
   if (d == 64) return launch<64>(a, tq, tk, tvt, kp, why);
   return launch<128>(a, tq, tk, tvt, kp, why);
 }
