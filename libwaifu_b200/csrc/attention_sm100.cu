@@ -3,10 +3,12 @@
 // A CTA owns 128 queries of one head and walks that head's keys 128 at a time. Per block of keys:
 //   S = Q K^T      tcgen05.mma kind::f16, 128 x 128 x head_dim, into one of two score buffers in
 //                  tensor memory (the next block's product runs beside this block's softmax);
-//   softmax        four warps, one thread per query: the thread reads its row of S from tensor
-//                  memory (a row is a lane, so no shuffles), keeps the running maximum and sum,
-//                  and writes P = exp2(S' - max) as 16-bit values into shared memory in the layout
-//                  the next product reads its A operand in (128-byte swizzle, K-major);
+//   softmax        eight warps, two threads per query (each half of the block's keys): a thread
+//                  reads its part of the row of S from tensor memory (a row is a lane, so no
+//                  shuffles; the two halves' maxima meet through shared memory), keeps the running
+//                  maximum and its half of the sum, and writes P = exp2(S' - max) as 16-bit values
+//                  into shared memory in the layout the next product reads its A operand in
+//                  (128-byte swizzle, K-major);
 //   O += P V       tcgen05.mma, 128 x head_dim x 128, accumulating in tensor memory; when a row's
 //                  maximum has grown enough to matter the threads rescale their output rows
 //                  there (tcgen05.ld / st) before handing P over.
@@ -25,32 +27,41 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include <cstdlib>
-
 #include "ptx_sm100.cuh"
 
 namespace flsm100 {
 
 namespace {
 
-#ifdef FLSM100_PROBE
-#ifndef FLSM100_ATT_PROBE
-#define FLSM100_ATT_PROBE 0
-#endif
-constexpr int kAttProbe = FLSM100_ATT_PROBE;  // development builds: parts compiled out for timing
-#endif
-
 constexpr int kBlockQ = 128;   // queries per CTA = lanes of tensor memory
 constexpr int kBlockKv = 128;  // keys per step
 constexpr int kAtomBytes = 128;  // one swizzle atom: 64 16-bit elements of K
 constexpr int kAtomElems = 64;
 constexpr int kMmaKBytes = 32;   // one kind::f16 instruction: 16 elements of K
-constexpr int kSoftmaxWarps = 4;
-constexpr int kProducerWarp = 4;
-constexpr int kMmaWarp = 5;
-constexpr int kThreads = 6 * 32;
+constexpr int kSoftmaxWarps = 8;  // two per 32 queries
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kThreads = 10 * 32;
 constexpr int kKvStages = 2;
 constexpr int kPadKv = 64;  // the transposed v's rows are padded to whole swizzle atoms
+
+// Barriers and the exchange buffers sit behind the tiles in dynamic shared memory, so that the
+// tiles start at the CTA's first byte, which is 1024-byte aligned (checked at entry).
+struct Tail {
+  uint64_t q_full_bar;
+  uint64_t k_full_bar[kKvStages], k_empty_bar[kKvStages];
+  uint64_t v_full_bar[kKvStages], v_empty_bar[kKvStages];
+  uint64_t s_full_bar[2], s_empty_bar[2];  // the two score buffers
+  uint64_t p_full_bar;                     // softmax -> MMA: the probabilities are in shared memory
+  // MMA -> softmax: the block is in the output and its P buffer is free. One barrier per P buffer:
+  // the softmax runs up to two products ahead of the one it waits for, and a waiter may lag an
+  // mbarrier by less than two phases.
+  uint64_t pv_done_bar[2];
+  uint64_t pair_bar[4];  // the two warps that share 32 rows have both written their halves' maxima
+  uint32_t tmem_base_slot;
+  uint32_t abort_flag;
+  float pair_value[2][2][kBlockQ];  // [block parity][column half][row]
+};
 
 template <int D>
 struct Layout {
@@ -67,7 +78,8 @@ struct Layout {
   static constexpr int kVOff = kKOff + kKvStages * kKBytes;
   static constexpr int kPOff = kVOff + kKvStages * kVBytes;
   static constexpr int kPBuffers = 2;  // the softmax of block j + 1 writes beside the product that reads block j's
-  static constexpr int kSmemBytes = kPOff + kPBuffers * kPBytes + 1024;  // + slack to align to 1024
+  static constexpr int kTailOff = kPOff + kPBuffers * kPBytes;
+  static constexpr int kSmemBytes = kTailOff + static_cast<int>(sizeof(Tail));
   // Tensor memory: two score buffers, then the block's output.
   static constexpr int kSCols = kBlockKv;
   static constexpr int kOCol = 2 * kSCols;
@@ -86,7 +98,6 @@ struct KernelParams {
   int causal;
   float scale_log2;
   uint32_t *status;
-  int probe;  // development builds (-DFLSM100_PROBE) only: parts switched off for timing
 };
 
 __device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *desc, uint64_t *bar, int32_t c0,
@@ -143,23 +154,16 @@ __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_vt, const KernelParams p) {
   using L = Layout<D>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-
-  __shared__ __align__(8) uint64_t q_full_bar;
-  __shared__ __align__(8) uint64_t k_full_bar[kKvStages], k_empty_bar[kKvStages];
-  __shared__ __align__(8) uint64_t v_full_bar[kKvStages], v_empty_bar[kKvStages];
-  __shared__ __align__(8) uint64_t s_full_bar[2], s_empty_bar[2];  // the two score buffers
-  __shared__ __align__(8) uint64_t p_full_bar;   // softmax -> MMA: the probabilities are in shared memory
-  // MMA -> softmax: the block is in the output and its P buffer is free. One barrier per P buffer:
-  // the softmax runs up to two products ahead of the one it waits for, and a waiter may lag an
-  // mbarrier by less than two phases.
-  __shared__ __align__(8) uint64_t pv_done_bar[2];
-  __shared__ uint32_t tmem_base_slot;
-  __shared__ volatile uint32_t abort_flag;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  Tail &t = *reinterpret_cast<Tail *>(smem + L::kTailOff);
+  volatile uint32_t &abort_flag = *reinterpret_cast<volatile uint32_t *>(&t.abort_flag);
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
+  if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need it; uniform over the grid
+    if (threadIdx.x == 0) atomicCAS(p.status, 0u, kStatusAttentionLayout);
+    return;
+  }
   const int q0 = blockIdx.x * kBlockQ;
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
@@ -174,21 +178,21 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int num_blocks = (kv_end + kBlockKv - 1) / kBlockKv;
 
   if (threadIdx.x == 0) {
-    abort_flag = 0;
-    mbar_init(&q_full_bar, 1);
+    t.abort_flag = 0;
+    mbar_init(&t.q_full_bar, 1);
     for (int s = 0; s < kKvStages; ++s) {
-      mbar_init(&k_full_bar[s], 1);
-      mbar_init(&k_empty_bar[s], 1);
-      mbar_init(&v_full_bar[s], 1);
-      mbar_init(&v_empty_bar[s], 1);
+      mbar_init(&t.k_full_bar[s], 1);
+      mbar_init(&t.k_empty_bar[s], 1);
+      mbar_init(&t.v_full_bar[s], 1);
+      mbar_init(&t.v_empty_bar[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&s_full_bar[s], 1);
-      mbar_init(&s_empty_bar[s], kSoftmaxWarps);
+      mbar_init(&t.s_full_bar[s], 1);
+      mbar_init(&t.s_empty_bar[s], kSoftmaxWarps);
+      mbar_init(&t.pv_done_bar[s], 1);
     }
-    mbar_init(&p_full_bar, kSoftmaxWarps);
-    mbar_init(&pv_done_bar[0], 1);
-    mbar_init(&pv_done_bar[1], 1);
+    mbar_init(&t.p_full_bar, kSoftmaxWarps);
+    for (int s = 0; s < 4; ++s) mbar_init(&t.pair_bar[s], 2);
     fence_barrier_init();
   }
   if (warp == kProducerWarp && lane == 0) {
@@ -197,13 +201,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     tma_prefetch_desc(&tmap_vt);
   }
   if (warp == kMmaWarp) {
-    tmem_alloc<1>(&tmem_base_slot, L::kTmemCols);
+    tmem_alloc<1>(&t.tmem_base_slot, L::kTmemCols);
     tmem_relinquish<1>();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = tmem_base_slot;
+  const uint32_t tmem_base = t.tmem_base_slot;
 
   uint8_t *q_smem = smem + L::kQOff;
   auto k_stage = [&](int s) { return smem + L::kKOff + s * L::kKBytes; };
@@ -214,45 +218,39 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
       bool ok = true;
-      mbar_arrive_expect_tx(&q_full_bar, L::kQBytes);
+      mbar_arrive_expect_tx(&t.q_full_bar, L::kQBytes);
 #pragma unroll
       for (int a = 0; a < L::kQAtoms; ++a) {
-        tma_load_4d(q_smem + a * kBlockQ * kAtomBytes, &tmap_q, &q_full_bar, a * kAtomBytes, q0, head, batch);
+        tma_load_4d(q_smem + a * kBlockQ * kAtomBytes, &tmap_q, &t.q_full_bar, a * kAtomBytes, q0, head, batch);
       }
-      for (int j = 0; j < num_blocks && ok; ++j) {
+      // K runs ahead of V: the scores of block j + 2 are multiplied beside P V of block j.
+      auto load_k = [&](int j) -> bool {
         const int st = j % kKvStages;
-        const uint32_t ph = (j / kKvStages) & 1;
-        if (!mbar_wait(&k_empty_bar[st], ph ^ 1, &abort_flag)) {
-          ok = false;
-          break;
-        }
-#ifdef FLSM100_PROBE
-        if (kAttProbe & 64) {  // timing probe: hand the stages over without loading them
-          mbar_arrive(&k_full_bar[st]);
-          if (!mbar_wait(&v_empty_bar[st], ph ^ 1, &abort_flag)) {
-            ok = false;
-            break;
-          }
-          mbar_arrive(&v_full_bar[st]);
-          continue;
-        }
-#endif
-        mbar_arrive_expect_tx(&k_full_bar[st], L::kKBytes);
+        if (!mbar_wait(&t.k_empty_bar[st], ((j / kKvStages) & 1) ^ 1, &abort_flag)) return false;
+        mbar_arrive_expect_tx(&t.k_full_bar[st], L::kKBytes);
 #pragma unroll
         for (int a = 0; a < L::kQAtoms; ++a) {
-          tma_load_4d(k_stage(st) + a * kBlockKv * kAtomBytes, &tmap_k, &k_full_bar[st], a * kAtomBytes, j * kBlockKv,
+          tma_load_4d(k_stage(st) + a * kBlockKv * kAtomBytes, &tmap_k, &t.k_full_bar[st], a * kAtomBytes, j * kBlockKv,
                       kv_head, batch);
         }
-        if (!mbar_wait(&v_empty_bar[st], ph ^ 1, &abort_flag)) {
-          ok = false;
-          break;
-        }
-        mbar_arrive_expect_tx(&v_full_bar[st], L::kVBytes);
+        return true;
+      };
+      auto load_v = [&](int j) -> bool {
+        const int st = j % kKvStages;
+        if (!mbar_wait(&t.v_empty_bar[st], ((j / kKvStages) & 1) ^ 1, &abort_flag)) return false;
+        mbar_arrive_expect_tx(&t.v_full_bar[st], L::kVBytes);
 #pragma unroll
         for (int a = 0; a < L::kVAtoms; ++a) {
-          tma_load_3d(v_stage(st) + a * L::kVAtomBytes, &tmap_vt, &v_full_bar[st],
+          tma_load_3d(v_stage(st) + a * L::kVAtomBytes, &tmap_vt, &t.v_full_bar[st],
                       (j * kBlockKv + a * kAtomElems) * 2, 0, batch * p.kv_heads + kv_head);
         }
+        return true;
+      };
+      ok = load_k(0);
+      if (ok && num_blocks > 1) ok = load_k(1);
+      for (int j = 0; j < num_blocks && ok; ++j) {
+        ok = load_v(j);
+        if (ok && j + 2 < num_blocks) ok = load_k(j + 2);
       }
       if (!ok) {
         abort_flag = 1;
@@ -269,70 +267,72 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const uint64_t pdesc0 = umma_desc_sw128(smem_u32(p_smem));
       constexpr uint64_t kMmaStep = kMmaKBytes >> 4;
       constexpr int kMmasPerAtom = kAtomBytes / kMmaKBytes;
+      constexpr int kScoreMmas = L::kQAtoms * kMmasPerAtom;  // per block
+      constexpr int kOutMmas = L::kVAtoms * kMmasPerAtom;
       bool ok = true;
-      // S_j = Q K_j^T into score buffer j & 1.
-      auto issue_scores = [&](int j) -> bool {
-        const int st = j % kKvStages;
-        const uint32_t ph = (j / kKvStages) & 1;
-        if (!mbar_wait(&k_full_bar[st], ph, &abort_flag)) return false;
-        if (!mbar_wait(&s_empty_bar[j & 1], ((j >> 1) & 1) ^ 1, &abort_flag)) return false;
-        tc_fence_after_sync();
-        const uint64_t kdesc0 = umma_desc_sw128(smem_u32(k_stage(st)));
-        const uint32_t d_tmem = tmem_base + (j & 1) * L::kSCols;
-#pragma unroll
-        for (int a = 0; a < L::kQAtoms; ++a) {
-#pragma unroll
-          for (int i = 0; i < kMmasPerAtom; ++i) {
-            const uint64_t qd = qdesc0 + ((a * kBlockQ * kAtomBytes) >> 4) + i * kMmaStep;
-            const uint64_t kd = kdesc0 + ((a * kBlockKv * kAtomBytes) >> 4) + i * kMmaStep;
-#ifdef FLSM100_PROBE
-            if (kAttProbe & 8) continue;
-#endif
-            if (p.is_bf16) {
-              umma_ss<kKindBF16>(d_tmem, qd, kd, idesc_s, (a | i) != 0 ? 1u : 0u);
-            } else {
-              umma_ss<kKindF16>(d_tmem, qd, kd, idesc_s, (a | i) != 0 ? 1u : 0u);
-            }
-          }
+      auto mma = [&](uint32_t d, uint64_t ad, uint64_t bd, uint32_t idesc, uint32_t acc) {
+        if (p.is_bf16) {
+          umma_ss<kKindBF16>(d, ad, bd, idesc, acc);
+        } else {
+          umma_ss<kKindF16>(d, ad, bd, idesc, acc);
         }
-        umma_commit(&k_empty_bar[st]);
-        umma_commit(&s_full_bar[j & 1]);
-        return true;
       };
-      if (!mbar_wait(&q_full_bar, 0, &abort_flag)) ok = false;
-      if (ok) ok = issue_scores(0);
+      // Instruction i of S_j = Q K_j^T (into score buffer j & 1) and of O += P_j V_j.
+      auto score_mma = [&](int j, int i) {
+        const int a = i / kMmasPerAtom, s = i % kMmasPerAtom;
+        const uint64_t kdesc0 = umma_desc_sw128(smem_u32(k_stage(j % kKvStages)));
+        mma(tmem_base + (j & 1) * L::kSCols, qdesc0 + ((a * kBlockQ * kAtomBytes) >> 4) + s * kMmaStep,
+            kdesc0 + ((a * kBlockKv * kAtomBytes) >> 4) + s * kMmaStep, idesc_s, i != 0 ? 1u : 0u);
+      };
+      auto out_mma = [&](int j, int i) {
+        const int a = i / kMmasPerAtom, s = i % kMmasPerAtom;
+        const uint64_t vdesc0 = umma_desc_sw128(smem_u32(v_stage(j % kKvStages)));
+        mma(tmem_base + L::kOCol, pdesc0 + (((j & 1) * L::kPBytes + a * L::kPAtomBytes) >> 4) + s * kMmaStep,
+            vdesc0 + ((a * L::kVAtomBytes) >> 4) + s * kMmaStep, idesc_o, (j | i) != 0 ? 1u : 0u);
+      };
+      auto wait_scores_operands = [&](int j) -> bool {
+        return mbar_wait(&t.k_full_bar[j % kKvStages], (j / kKvStages) & 1, &abort_flag) &&
+               mbar_wait(&t.s_empty_bar[j & 1], ((j >> 1) & 1) ^ 1, &abort_flag);
+      };
+      auto commit_scores = [&](int j) {
+        umma_commit(&t.k_empty_bar[j % kKvStages]);
+        umma_commit(&t.s_full_bar[j & 1]);
+      };
+      ok = mbar_wait(&t.q_full_bar, 0, &abort_flag);
+      // The first two blocks' scores.
+      for (int j = 0; j < 2 && j < num_blocks && ok; ++j) {
+        ok = wait_scores_operands(j);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int i = 0; i < kScoreMmas; ++i) score_mma(j, i);
+        commit_scores(j);
+      }
       for (int j = 0; j < num_blocks && ok; ++j) {
-        if (j + 1 < num_blocks && !issue_scores(j + 1)) {
+        const bool ahead = j + 2 < num_blocks;
+        if (ahead && !wait_scores_operands(j + 2)) {
           ok = false;
           break;
         }
-        const int st = j % kKvStages;
-        const uint32_t ph = (j / kKvStages) & 1;
-        if (!mbar_wait(&p_full_bar, j & 1, &abort_flag) || !mbar_wait(&v_full_bar[st], ph, &abort_flag)) {
+        if (!mbar_wait(&t.p_full_bar, j & 1, &abort_flag) ||
+            !mbar_wait(&t.v_full_bar[j % kKvStages], (j / kKvStages) & 1, &abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint64_t vdesc0 = umma_desc_sw128(smem_u32(v_stage(st)));
-        const uint32_t d_tmem = tmem_base + L::kOCol;
+        // Two independent accumulator chains, issued in turn: an instruction into an accumulator
+        // waits for the one before it, so in turn they take the time of one chain.
+        static_assert(kScoreMmas == kOutMmas || kScoreMmas * 2 == kOutMmas, "interleave below");
+        constexpr int kOutPerScore = kOutMmas / kScoreMmas;
 #pragma unroll
-        for (int a = 0; a < L::kVAtoms; ++a) {
+        for (int i = 0; i < kScoreMmas; ++i) {
 #pragma unroll
-          for (int i = 0; i < kMmasPerAtom; ++i) {
-            const uint64_t pd = pdesc0 + (((j & 1) * L::kPBytes + a * L::kPAtomBytes) >> 4) + i * kMmaStep;
-            const uint64_t vd = vdesc0 + ((a * L::kVAtomBytes) >> 4) + i * kMmaStep;
-#ifdef FLSM100_PROBE
-            if (kAttProbe & 4) continue;
-#endif
-            if (p.is_bf16) {
-              umma_ss<kKindBF16>(d_tmem, pd, vd, idesc_o, (j | a | i) != 0 ? 1u : 0u);
-            } else {
-              umma_ss<kKindF16>(d_tmem, pd, vd, idesc_o, (j | a | i) != 0 ? 1u : 0u);
-            }
-          }
+          for (int o = 0; o < kOutPerScore; ++o) out_mma(j, i * kOutPerScore + o);
+          if (ahead) score_mma(j + 2, i);
         }
-        umma_commit(&v_empty_bar[st]);
-        umma_commit(&pv_done_bar[j & 1]);
+        umma_commit(&t.v_empty_bar[j % kKvStages]);
+        umma_commit(&t.pv_done_bar[j & 1]);
+        if (ahead) commit_scores(j + 2);
       }
       if (!ok) {
         abort_flag = 1;
@@ -341,64 +341,77 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------------ softmax and output
-    const int row = static_cast<int>(warp) * 32 + static_cast<int>(lane);  // query within the CTA = lane of tensor memory
-    const int q_pos = q0 + row + offset;                                   // the last key this query sees under the causal mask
-    const uint32_t t_lane = tmem_base + ((warp * 32u) << 16);
+    // Two warps share 32 queries (warps w and w + 4 reach the same lanes of tensor memory): each
+    // takes half of a block's keys, and half of the output's columns at the end.
+    const uint32_t quarter = warp & 3;
+    const uint32_t half = warp >> 2;
+    constexpr int kMyKeys = kBlockKv / 2;  // = one swizzle atom of P
+    static_assert(kMyKeys == kAtomElems, "a warp writes one atom of P");
+    const int row = static_cast<int>(quarter) * 32 + static_cast<int>(lane);  // query within the CTA = lane of tensor memory
+    const int q_pos = q0 + row + offset;  // the last key this query sees under the causal mask
+    const uint32_t t_lane = tmem_base + ((quarter * 32u) << 16);
     // Where this row's 16-byte pieces go in an atom of P: piece c of row r sits at c ^ (r & 7).
-    uint8_t *p_row = p_smem + (row >> 3) * 1024 + (row & 7) * kAtomBytes;
+    uint8_t *p_row = p_smem + half * L::kPAtomBytes + (row >> 3) * 1024 + (row & 7) * kAtomBytes;
     const uint32_t p_xor = static_cast<uint32_t>(row & 7);
     // The probabilities and the output in tensor memory are relative to m_used, which follows the
     // row's running maximum only when that has grown by more than kRescaleStep (in log2 units)
     // for some row of the warp: until then exp2(score - m_used) <= 2^kRescaleStep, which every
     // type here holds, and the output needs no rescaling. The normalisation at the end divides by
-    // the sum taken relative to the same m_used, so the result is the same quotient.
+    // the sum taken relative to the same m_used, so the result is the same quotient. Both warps
+    // of a pair see the same maxima, so they take the same decisions.
     constexpr float kRescaleStep = 8.0f;
     float m_used = -INFINITY;
-    float l_run = 0.0f;
+    float l_run = 0.0f;  // this thread's half of the row's sum
     bool ok = true;
-    uint32_t sc[kBlockKv / 32][32];  // this row's scores of the block
+    uint32_t sc[kMyKeys / 32][32];  // this thread's scores of the block
     uint32_t v[32];
     // Waits, in order and each once, until `count` of the P V products have completed.
     int products_seen = 0;
     auto wait_products = [&](int count) -> bool {
       while (products_seen < count) {
         ok = __all_sync(0xffffffffu,
-                        mbar_wait(&pv_done_bar[products_seen & 1], (products_seen >> 1) & 1, &abort_flag));
+                        mbar_wait(&t.pv_done_bar[products_seen & 1], (products_seen >> 1) & 1, &abort_flag));
         if (!ok) return false;
         ++products_seen;
       }
       tc_fence_after_sync();
       return true;
     };
+    // Hands `mine` to the other warp of the pair and returns what that warp handed over; `n` counts
+    // the exchanges (one mbarrier phase each).
+    int exchanges = 0;
+    auto exchange = [&](float mine, float *theirs) -> bool {
+      t.pair_value[exchanges & 1][half][row] = mine;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&t.pair_bar[quarter]);
+      ok = __all_sync(0xffffffffu, mbar_wait(&t.pair_bar[quarter], exchanges & 1, &abort_flag));
+      if (!ok) return false;
+      *theirs = t.pair_value[exchanges & 1][half ^ 1][row];
+      ++exchanges;
+      return true;
+    };
 
     for (int j = 0; j < num_blocks && ok; ++j) {
-      const int key0 = j * kBlockKv;
-      const uint32_t t_s = t_lane + (j & 1) * L::kSCols;
+      const int key0 = j * kBlockKv + static_cast<int>(half) * kMyKeys;  // this thread's first key
+      const uint32_t t_s = t_lane + (j & 1) * L::kSCols + half * kMyKeys;
       // Does any key of this block need masking for any row of the CTA?
-      const bool edge = (key0 + kBlockKv > p.kv_len) || (p.causal && key0 + kBlockKv - 1 > q0 + offset);
+      const bool edge = (j * kBlockKv + kBlockKv > p.kv_len) || (p.causal && j * kBlockKv + kBlockKv - 1 > q0 + offset);
       const int key_limit = p.causal ? min(p.kv_len - 1, q_pos) : p.kv_len - 1;  // last key this row sees
-      ok = __all_sync(0xffffffffu, mbar_wait(&s_full_bar[j & 1], (j >> 1) & 1, &abort_flag));
+      ok = __all_sync(0xffffffffu, mbar_wait(&t.s_full_bar[j & 1], (j >> 1) & 1, &abort_flag));
       if (!ok) break;
       tc_fence_after_sync();
-      // The whole row into registers in one round trip; the buffer goes back to the MMAs at once.
-#ifdef FLSM100_PROBE
-      if (!(kAttProbe & 32))
-#endif
+      // This thread's scores into registers in one round trip; the buffer goes back to the MMAs.
 #pragma unroll
-      for (int c = 0; c < kBlockKv / 32; ++c) tmem_ld_32x32(t_s + c * 32, sc[c]);
+      for (int c = 0; c < kMyKeys / 32; ++c) tmem_ld_32x32(t_s + c * 32, sc[c]);
 #pragma unroll
-      for (int c = 0; c < kBlockKv / 32; ++c) tmem_ld_wait(sc[c]);
+      for (int c = 0; c < kMyKeys / 32; ++c) tmem_ld_wait(sc[c]);
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty_bar[j & 1]);
-      // Scaled to log2 units, masked, and the row's maximum over the block.
+      if (lane == 0) mbar_arrive(&t.s_empty_bar[j & 1]);
+      // Scaled to log2 units, masked, and the maximum over this thread's keys.
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
-#ifdef FLSM100_PROBE
-      if (kAttProbe & 16) m4[0] = 0.0f;
-      if (!(kAttProbe & 16))
-#endif
 #pragma unroll
-      for (int c = 0; c < kBlockKv / 32; ++c) {
+      for (int c = 0; c < kMyKeys / 32; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float x = __uint_as_float(sc[c][i]) * p.scale_log2;
@@ -407,7 +420,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           m4[i & 3] = fmaxf(m4[i & 3], x);
         }
       }
-      const float m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      float m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      float m_other;
+      if (!exchange(m_blk, &m_other)) break;
+      m_blk = fmaxf(m_blk, m_other);
       // P V of block j - 2 is done: its P buffer, which this block takes, may be overwritten.
       if (!wait_products(j - 1)) break;
       if (__any_sync(0xffffffffu, m_blk > m_used + kRescaleStep)) {
@@ -418,12 +434,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         l_run *= alpha;
         if (j > 0) {
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            tmem_ld_32x32(t_lane + L::kOCol + c * 32, v);
+          for (int c = 0; c < D / 64; ++c) {  // this warp's half of the output's columns
+            const uint32_t t_o = t_lane + L::kOCol + half * (D / 2) + c * 32;
+            tmem_ld_32x32(t_o, v);
             tmem_ld_wait(v);
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st_32x32(t_lane + L::kOCol + c * 32, v);
+            tmem_st_32x32(t_o, v);
           }
           tmem_st_wait();
         }
@@ -432,31 +449,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const float m_sub = (m_used == -INFINITY) ? 0.0f : m_used;  // a row that has seen no key yet: every score is -inf
       // The probabilities, into shared memory as the A operand of P V.
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      uint8_t *atom = p_row + (j & 1) * L::kPBytes;
 #pragma unroll
-      for (int c = 0; c < kBlockKv / 32; ++c) {
+      for (int c = 0; c < kMyKeys / 32; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-#ifdef FLSM100_PROBE
-          const float e0 = (kAttProbe & 1) ? __uint_as_float(sc[c][i]) - m_sub : exp2f(__uint_as_float(sc[c][i]) - m_sub);
-          const float e1 = (kAttProbe & 1) ? __uint_as_float(sc[c][i + 1]) - m_sub : exp2f(__uint_as_float(sc[c][i + 1]) - m_sub);
-#else
           const float e0 = exp2f(__uint_as_float(sc[c][i]) - m_sub);
           const float e1 = exp2f(__uint_as_float(sc[c][i + 1]) - m_sub);
-#endif
           sum4[(i >> 1) & 3] += e0 + e1;
           packed[i >> 1] = pack16(e0, e1, p.is_bf16);
         }
-        uint8_t *atom = p_row + (j & 1) * L::kPBytes + (c >> 1) * L::kPAtomBytes;
-#ifdef FLSM100_PROBE
-        if (kAttProbe & 2) {
-          if (packed[0] == 0x12345678u) atom[0] = 1;  // keeps the arithmetic alive
-          continue;
-        }
-#endif
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const uint32_t piece = static_cast<uint32_t>((c & 1) * 4 + g) ^ p_xor;
+          const uint32_t piece = static_cast<uint32_t>(c * 4 + g) ^ p_xor;
           *reinterpret_cast<uint4 *>(atom + piece * 16) =
               make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
         }
@@ -465,17 +471,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       fence_proxy_async_smem();  // the stores above, before the MMA's reads of them
       tc_fence_before_sync();    // and the rescaled output, before the MMA accumulates into it
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full_bar);
+      if (lane == 0) mbar_arrive(&t.p_full_bar);
     }
     if (ok) wait_products(num_blocks);
+    float l_other = 0.0f;
+    if (ok) exchange(l_run, &l_other);
     if (ok) {
       const bool live = q0 + row < p.q_len;
-      const float inv = 1.0f / l_run;
+      const float inv = 1.0f / (l_run + l_other);
       uint16_t *dst = reinterpret_cast<uint16_t *>(p.out) + batch * p.out_stride[0] + head * p.out_stride[1] +
-                      static_cast<int64_t>(q0 + row) * p.out_stride[2];
+                      static_cast<int64_t>(q0 + row) * p.out_stride[2] + half * (D / 2);
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        tmem_ld_32x32(t_lane + L::kOCol + c * 32, v);
+      for (int c = 0; c < D / 64; ++c) {
+        tmem_ld_32x32(t_lane + L::kOCol + half * (D / 2) + c * 32, v);
         tmem_ld_wait(v);
         if (live) {
 #pragma unroll
@@ -662,9 +670,6 @@ cudaError_t attention(const AttentionArgs &a, const char **why) {
   kp.causal = a.causal;
   kp.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(d));
   kp.status = a.status;
-#ifdef FLSM100_PROBE
-  if (const char *v = std::getenv("FLSM100_PROBE")) kp.probe = std::atoi(v);
-#endif
   if (d == 64) return launch<64>(a, tq, tk, tvt, kp, why);
   return launch<128>(a, tq, tk, tvt, kp, why);
 }

@@ -33,5 +33,6 @@ size_t attention_scratch_bytes(int batch, int kv_heads, int kv_len, int head_dim
 cudaError_t attention(const AttentionArgs &a, const char **why);
 
 constexpr uint32_t kStatusAttentionTimeout = 0x41;
+constexpr uint32_t kStatusAttentionLayout = 0x42;  // dynamic shared memory did not start on a 1024-byte boundary
 
 }  // namespace flsm100
