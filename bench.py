@@ -536,7 +536,7 @@ def run_mmdit(args):
     cfg = MMDiTConfig()
     if args.blocks:
         cfg.blocks = args.blocks
-    model = MMDiT(cfg, FlintBackend(), seed=0)
+    model = MMDiT(cfg, FlintBackend(args.attention), seed=0)
     g = torch.Generator(device="cuda").manual_seed(1 + rank)
     x = torch.randn(cfg.batch, cfg.tokens, cfg.hidden, device="cuda", dtype=torch.bfloat16, generator=g)
     temb = torch.randn(cfg.batch, cfg.hidden, device="cuda", dtype=torch.bfloat16, generator=g)
@@ -597,7 +597,8 @@ def run_mmdit(args):
             "config": {"workload": "c4_mmdit_step", "what": WORKLOADS["c4_mmdit_step"]["desc"], "blocks": cfg.blocks,
                        "parallelism": f"batch-sharded x{world} (each rank its own CFG pair), weights replicated",
                        "l2": f"{cfg.blocks} blocks x 170 MB of FP8 weights stream through the 126 MB L2 every step",
-                       "outside_the_path": "attention (torch SDPA, bf16) and the SiLU of the timestep embedding"},
+                       "attention": "torch SDPA, bf16" if args.attention == "sdpa" else "fl_attention (this library), bf16",
+                       "outside_the_path": "attention and the SiLU of the timestep embedding"},
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": int(hx.numel() * 2 + ht.numel() * 2),
                     "d2h_bytes_per_step": int(hy.numel() * 2), "steps": e2e_steps},
             "gpu_launches": launches,
@@ -771,6 +772,8 @@ def main():
                     help="batch: rows sharded, no collective (weak scaling); nsplit: one MLP with its weights "
                          "split by output channel and NCCL all-gathers (strong scaling)")
     ap.add_argument("--blocks", type=int, default=None, help="c4_mmdit_step: run this many blocks instead of 60")
+    ap.add_argument("--attention", default="sdpa", choices=["sdpa", "flint"],
+                    help="c4_mmdit_step: torch's attention, or this library's fl_attention")
     args = ap.parse_args()
     if args.workload == "skinny_decode" and args.impl == "ours":
         args.warmup = max(args.warmup, 3)

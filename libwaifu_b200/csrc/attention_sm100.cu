@@ -117,6 +117,13 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *d
       : "memory");
 }
 
+// 2^x for x <= 2^kRescaleStep's exponent: the hardware approximation (relative error 2^-22), -inf -> 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ uint32_t pack16(float a, float b, int is_bf16) {
   if (is_bf16) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
@@ -391,16 +398,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       return true;
     };
 
-    for (int j = 0; j < num_blocks && ok; ++j) {
-      const int key0 = j * kBlockKv + static_cast<int>(half) * kMyKeys;  // this thread's first key
-      const uint32_t t_s = t_lane + (j & 1) * L::kSCols + half * kMyKeys;
-      // Does any key of this block need masking for any row of the CTA?
-      const bool edge = (j * kBlockKv + kBlockKv > p.kv_len) || (p.causal && j * kBlockKv + kBlockKv - 1 > q0 + offset);
-      const int key_limit = p.causal ? min(p.kv_len - 1, q_pos) : p.kv_len - 1;  // last key this row sees
+    // This thread's scores of block j into registers in one round trip; the buffer goes back to
+    // the MMAs at once.
+    auto fetch_scores = [&](int j) -> bool {
       ok = __all_sync(0xffffffffu, mbar_wait(&t.s_full_bar[j & 1], (j >> 1) & 1, &abort_flag));
-      if (!ok) break;
+      if (!ok) return false;
       tc_fence_after_sync();
-      // This thread's scores into registers in one round trip; the buffer goes back to the MMAs.
+      const uint32_t t_s = t_lane + (j & 1) * L::kSCols + half * kMyKeys;
 #pragma unroll
       for (int c = 0; c < kMyKeys / 32; ++c) tmem_ld_32x32(t_s + c * 32, sc[c]);
 #pragma unroll
@@ -408,6 +412,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&t.s_empty_bar[j & 1]);
+      return true;
+    };
+
+    fetch_scores(0);
+    for (int j = 0; j < num_blocks && ok; ++j) {
+      const int key0 = j * kBlockKv + static_cast<int>(half) * kMyKeys;  // this thread's first key
+      // Does any key of this block need masking for any row of the CTA?
+      const bool edge = (j * kBlockKv + kBlockKv > p.kv_len) || (p.causal && j * kBlockKv + kBlockKv - 1 > q0 + offset);
+      const int key_limit = p.causal ? min(p.kv_len - 1, q_pos) : p.kv_len - 1;  // last key this row sees
       // Scaled to log2 units, masked, and the maximum over this thread's keys.
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
 #pragma unroll
@@ -455,8 +468,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float e0 = exp2f(__uint_as_float(sc[c][i]) - m_sub);
-          const float e1 = exp2f(__uint_as_float(sc[c][i + 1]) - m_sub);
+          const float e0 = fast_exp2(__uint_as_float(sc[c][i]) - m_sub);
+          const float e1 = fast_exp2(__uint_as_float(sc[c][i + 1]) - m_sub);
           sum4[(i >> 1) & 3] += e0 + e1;
           packed[i >> 1] = pack16(e0, e1, p.is_bf16);
         }
@@ -468,6 +481,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
       }
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      // The next block's scores (ready since the product before last) are read before P is handed
+      // over: the products that the hand-over starts would otherwise be under way when the read
+      // is issued.
+      if (j + 1 < num_blocks && !fetch_scores(j + 1)) break;
       fence_proxy_async_smem();  // the stores above, before the MMA's reads of them
       tc_fence_before_sync();    // and the rescaled output, before the MMA accumulates into it
       __syncwarp();

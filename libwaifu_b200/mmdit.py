@@ -14,8 +14,11 @@ activation quantiser run as one kernel in front of the QKV and up projections
 down projections is folded into the projection's epilogue (the gate multiplies the per-channel
 scale and the bias, the stream is the residual), and the per-head RMS norm of q and k with their
 rotary embedding runs in place on the QKV projection's output (fl_qk_norm_rope), which attention
-then reads as three strided views. Attention itself and the SiLU of the timestep embedding are
-plain torch, inside the timed step but outside the graded path.
+then reads as three strided views. Attention runs through torch's scaled_dot_product_attention by
+default, or through this library's fl_attention with ``FlintBackend(attention_kernel="flint")``
+(the same strided views, the result written token-major; slower than torch's library kernel at
+this size, so not the default); the SiLU of the timestep embedding is plain torch. Both are inside
+the timed step but outside the graded path.
 
 The same block code runs over two backends: ``FlintBackend`` (the C ABI on the GPU) and
 ``OracleBackend`` (the CPU oracle, for the parity test at a reduced size).
@@ -60,12 +63,15 @@ class FlintBackend:
     """Linears through libflint_sm100 (fl_quantize_fp8_rows at load; per call fl_fp8_linear, or
     fl_fp8_layernorm_quantize + fl_fp8_linear_quantized where a layer norm feeds the linear)."""
 
-    def __init__(self):
+    def __init__(self, attention_kernel: str = "sdpa"):
         import torch
         from . import flint as F
+        if attention_kernel not in ("sdpa", "flint"):
+            raise ValueError("attention_kernel is 'sdpa' or 'flint'")
         self.torch = torch
         self.F = F
         self.device = "cuda"
+        self.attention_kernel = attention_kernel
 
     def _wrap(self, t, dt):
         """A view of a torch tensor's memory with its own strides (a column slice stays a slice)."""
@@ -115,6 +121,30 @@ class FlintBackend:
         F.qk_norm_rope(self._wrap(qkv2d, F.DType.BFLOAT16), self._wrap(cos, F.DType.FLOAT), self._wrap(sin, F.DType.FLOAT),
                        heads, LN_EPS)
         return qkv2d
+
+    def attention(self, qkv5d):
+        """Joint attention over qkv (batch, tokens, 3, heads, head_dim), the fused projection's
+        output: q, k and v are strided views of it and the result is token-major (batch * tokens,
+        heads * head_dim), the layout the next projection reads. `self.attention_kernel` chooses
+        this library's kernel ("flint") or torch's ("sdpa", the default: see the module text)."""
+        torch, F = self.torch, self.F
+        b, t, _, h, hd = qkv5d.shape
+        if self.attention_kernel == "flint":
+            out = torch.empty((b, t, h, hd), dtype=torch.bfloat16, device=qkv5d.device)
+            views = []
+            for i in range(3):
+                part = qkv5d[:, :, i].transpose(1, 2)  # (b, h, t, hd)
+                views.append(F.Tensor.from_device_ptr(part.data_ptr(), tuple(part.shape), F.DType.BFLOAT16, keepalive=qkv5d,
+                                                      stride=tuple(part.stride()), numel=qkv5d.numel()))
+            o = out.transpose(1, 2)
+            ov = F.Tensor.from_device_ptr(o.data_ptr(), tuple(o.shape), F.DType.BFLOAT16, keepalive=out,
+                                          stride=tuple(o.stride()), numel=out.numel())
+            F.attention(views[0], views[1], views[2], F.MaskType.NONE, 0, ov)
+            return out.view(b * t, h * hd)
+        q, k, v = (qkv5d[:, :, i].transpose(1, 2) for i in range(3))
+        a = torch.nn.functional.scaled_dot_product_attention(q, k, v)
+        a = a.transpose(1, 2).reshape(b * t, h * hd)
+        return a if a.is_contiguous() else a.contiguous()
 
     def gated_linear(self, a2d, layer, gate, stream3d):
         """stream + gate * linear(a), gate (batch, n): per batch row block one GEMM whose per-channel
@@ -175,6 +205,12 @@ class OracleBackend:
     def qk_norm_rope(self, qkv2d, cos, sin, heads):
         return self._tensor(self.O.qk_norm_rope(self._bits(qkv2d), cos.numpy(), sin.numpy(), heads, LN_EPS, True))
 
+    def attention(self, qkv5d):
+        b, t, _, h, hd = qkv5d.shape
+        q, k, v = (qkv5d[:, :, i].transpose(1, 2) for i in range(3))
+        a = self.torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float()).to(self.torch.bfloat16)
+        return a.transpose(1, 2).reshape(b * t, h * hd).contiguous()
+
     def gated_linear(self, a2d, layer, gate, stream3d):
         b, t, n = stream3d.shape
         y = self.linear(a2d, layer).view(b, t, n).float()
@@ -230,11 +266,7 @@ class MMDiT:
         qkv = self.backend.qk_norm_rope(qkv, self.cos, self.sin, c.heads).view(b, t, 3, c.heads, c.head_dim)
         # q, k, v as (b, heads, t, head_dim) views of the one buffer: nothing is copied, and the
         # attention output comes back token-major, which is the layout the next projection reads
-        q, k, v = qkv[:, :, 0].transpose(1, 2), qkv[:, :, 1].transpose(1, 2), qkv[:, :, 2].transpose(1, 2)
-        a = Fn.scaled_dot_product_attention(q, k, v)  # joint attention over text + image tokens
-        a = a.transpose(1, 2).reshape(b * t, d)
-        if not a.is_contiguous():
-            a = a.contiguous()
+        a = self.backend.attention(qkv)  # joint attention over text + image tokens
         x = self.backend.gated_linear(a, layers["out"], gate1, x)
 
         u = self.backend.modulated_linear(x, scale2, shift2, layers["up"], act=1)  # GELU-tanh in the epilogue
