@@ -48,6 +48,9 @@ WORKLOADS = {
     # 16-bit activation row against an e4m3 weight through the unchanged fl_fp8_matmul; HBM-bound
     "skinny_decode": dict(m=1, gemms=[(16384, 3072)], kind="fp8_upcast",
                           desc="fl_fp8_matmul 1x16384x3072, fp16 activation x e4m3 weight, one scale"),
+    # handled by run_attention(): the denoise step's joint attention through fl_attention
+    "attention_step": dict(m=2 * 4352, gemms=[], kind="bf16",
+                           desc="fl_attention 2 x 24 heads x 4352 tokens x 128, bf16, no mask (the denoise step's attention)"),
 }
 
 NOMINAL_PEAK = {"fp8": 4500.0, "nvfp4": 9000.0}   # dense TFLOP/s, NVIDIA's B200 figures
@@ -61,6 +64,7 @@ NCU_TRAFFIC_BYTES = {
     "c1_linear": 22.1e6,                                 # the bf16 output stays dirty in L2
     "c3_nvfp4_qkv": 24.0e6 + 25.5e6,
     "skinny_decode": 50.38e6 + 7.0e6,                    # the weight once; the writes are older dirty lines leaving L2
+    "attention_step": 161.1e6 + 35.9e6,                  # q, k, v once (K and V re-reads hit L2); the output partly stays in L2
 }
 
 
@@ -757,6 +761,168 @@ def run_skinny(args):
         dist.destroy_process_group()
 
 
+def run_attention(args):
+    """The attention_step workload: the denoise step's joint attention (batch 2, 24 heads of 128,
+    4352 tokens, no mask) through fl_attention on q, k, v laid out as the fused projection leaves
+    them, (batch, tokens, 3, heads, head_dim), the result token-major. Every rank runs its own
+    batch (rows shard with no exchange). Tensor-bound: 4 N h L^2 D flops against the measured bf16
+    GEMM throughput. Four sets of operands in rotation keep a call's inputs out of L2."""
+    import torch
+    from libwaifu_b200 import flint as F
+    wl = WORKLOADS["attention_step"]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    torch.cuda.set_device(local)
+    F.set_device(local)
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl")
+        dist = dist_mod
+    n, h, L, d = 2, 24, 4352, 128
+    sets = 4  # 4 x 160 MB
+    gen = torch.Generator(device="cuda").manual_seed(rank)
+    qkvs = [torch.randn(n, L, 3, h, d, device="cuda", dtype=torch.bfloat16, generator=gen) for _ in range(sets)]
+    out = torch.empty(n, L, h, d, device="cuda", dtype=torch.bfloat16)
+
+    def view(t5, i):
+        part = t5[:, :, i].transpose(1, 2)
+        return F.Tensor.from_device_ptr(part.data_ptr(), tuple(part.shape), F.DType.BFLOAT16, keepalive=t5,
+                                        stride=tuple(part.stride()), numel=t5.numel())
+
+    ops_in = [[view(t, i) for i in range(3)] for t in qkvs]
+    o = out.transpose(1, 2)
+    out_v = F.Tensor.from_device_ptr(o.data_ptr(), tuple(o.shape), F.DType.BFLOAT16, keepalive=out, stride=tuple(o.stride()),
+                                     numel=out.numel())
+
+    def step(i):
+        q, k, v = ops_in[i % sets]
+        F.attention(q, k, v, F.MaskType.NONE, 0, out_v)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = F.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    e1.record()
+    barrier()
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    launches = F.launch_count() - launches0
+    sampler.stop_flag.set()
+    sampler.join(timeout=5)
+    flops = 4.0 * n * h * L * L * d
+    value = world * flops / (ms_step * 1e-3) / 1e12
+
+    # end to end: q, k, v from pinned host memory, the result back to the host
+    host_in = torch.empty(n, L, 3, h, d, dtype=torch.bfloat16).pin_memory()
+    host_in.copy_(qkvs[0].cpu())
+    host_out = torch.empty(n, L, h, d, dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(3, min(args.steps, 20))
+
+    def e2e_step():
+        qkvs[0].copy_(host_in, non_blocking=True)
+        step(0)
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
+
+    bf16_peak, _, peak_kind = measured_peaks(sampler.summary())
+    achieved = flops / (ms_step * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "attention_kernel", "achieved": achieved, "peak": bf16_peak, "unit": "TFLOP/s",
+                "frac": achieved / bf16_peak, "peak_source": f"bf16 cuBLAS, of {peak_kind}", "launches": launches,
+                "avg_launch_ms": ms_step, "traffic": NCU_TRAFFIC_BYTES.get("attention_step"),
+                "algorithmic_bytes_per_step": 4 * n * h * L * d * 2,
+                "note": "two launches per step (the transposition of v, then the attention kernel); "
+                        "the step time stands for the attention kernel's, which is 97 % of it"}
+    if rank == 0:
+        line = {
+            "metric": METRIC.replace("quantized GEMM", "attention"), "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 -> f32 accumulate", "data": "synthetic",
+            "config": {"workload": "attention_step", "what": wl["desc"], "parallelism": f"batch-sharded x{world}",
+                       "l2": f"{sets} rotating operand sets of 160 MB, larger than L2"},
+            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": int(host_in.numel() * 2), "d2h_bytes_per_step": int(host_out.numel() * 2)},
+            "gpu_launches": launches, "roofline": roofline, "cpu_baseline": None, "clocks": sampler.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_attention_reference(args):
+    """The reference arm of attention_step: the reference's own CPU fl_attention (float32, the
+    composition of flint/operators.cc:148-230) on a bounded sample of the workload, all host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    try:
+        os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
+    except Exception:
+        os.environ.pop("OMP_NUM_THREADS", None)
+    import numpy as np
+    sys.path.insert(0, ROOT)
+    from oracle import oracle as O
+    wl = WORKLOADS["attention_step"]
+    line = {"impl": "reference", "config": {"workload": "attention_step", "what": wl["desc"]}}
+    if not O.have_ref():
+        line["unavailable"] = "the reference's CPU library (oracle/_ref) is not built here"
+        print(json.dumps(line), flush=True)
+        return
+    heads, q_len, kv_len, d = 4, 1088, 4352, 128
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((1, heads, q_len, d)).astype(np.float32)
+    k = rng.standard_normal((1, heads, kv_len, d)).astype(np.float32)
+    v = rng.standard_normal((1, heads, kv_len, d)).astype(np.float32)
+    R = O.ref()
+    for _ in range(args.warmup):
+        R.attention(q, k, v, False)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        R.attention(q, k, v, False)
+    ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    value = 4.0 * heads * q_len * kv_len * d / (ms * 1e-3) / 1e12
+    cores = len(os.sched_getaffinity(0))
+    sample = f"{heads} of 48 (batch, head) pairs, {q_len} of 4352 queries over all 4352 keys per step, float32"
+    line.update({
+        "metric": METRIC.replace("quantized GEMM", "attention"), "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "reference", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    })
+    line["config"]["sample"] = sample
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -780,6 +946,15 @@ def main():
         if args.steps == 1000:
             args.steps = 20000  # 20 us a step: long enough for the clock sampler to see the run
         return run_skinny(args)
+    if args.workload == "attention_step" and args.impl == "reference":
+        if args.steps == 1000:
+            args.steps = 3
+        return run_attention_reference(args)
+    if args.workload == "attention_step" and args.impl == "ours":
+        args.warmup = max(args.warmup, 3)
+        if args.steps == 1000:
+            args.steps = 50
+        return run_attention(args)
     if args.workload == "c4_mmdit_step" and args.impl == "ours":
         if args.steps == 1000:
             args.steps = 10
