@@ -637,7 +637,7 @@ def run_skinny(args):
     F.set_device(local)
     if world > 1:
         import torch.distributed as dist_mod
-        dist_mod.init_process_group("nccl")
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist = dist_mod
     m = wl["m"]
     (n, k), = wl["gemms"]
@@ -778,7 +778,7 @@ def run_attention(args):
     F.set_device(local)
     if world > 1:
         import torch.distributed as dist_mod
-        dist_mod.init_process_group("nccl")
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist = dist_mod
     n, h, L, d = 2, 24, 4352, 128
     sets = 4  # 4 x 160 MB
