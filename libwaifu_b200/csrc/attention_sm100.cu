@@ -277,25 +277,25 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       constexpr int kScoreMmas = L::kQAtoms * kMmasPerAtom;  // per block
       constexpr int kOutMmas = L::kVAtoms * kMmasPerAtom;
       bool ok = true;
-      auto mma = [&](uint32_t d, uint64_t ad, uint64_t bd, uint32_t idesc, uint32_t acc) {
-        if (p.is_bf16) {
-          umma_ss<kKindBF16>(d, ad, bd, idesc, acc);
-        } else {
-          umma_ss<kKindF16>(d, ad, bd, idesc, acc);
-        }
-      };
-      // Instruction i of S_j = Q K_j^T (into score buffer j & 1) and of O += P_j V_j.
-      auto score_mma = [&](int j, int i) {
+      // Everything an instruction needs is a per-parity base (stage, score buffer and P buffer all
+      // alternate with the block index) plus a compile-time offset, so that the single issuing
+      // thread spends its time on the instructions. (kind::f16 covers half and bfloat16: the
+      // instruction descriptor carries the format.)
+      static_assert(kKvStages == 2, "the stage of block j is j & 1");
+      const uint64_t kdesc_0 = umma_desc_sw128(smem_u32(k_stage(0))), kdesc_1 = umma_desc_sw128(smem_u32(k_stage(1)));
+      const uint64_t vdesc_0 = umma_desc_sw128(smem_u32(v_stage(0))), vdesc_1 = umma_desc_sw128(smem_u32(v_stage(1)));
+      const uint64_t pdesc_1 = pdesc0 + (L::kPBytes >> 4);
+      const uint32_t o_tmem = tmem_base + L::kOCol;
+      // Instruction i of S = Q K^T (into the score buffer at s_tmem) and of O += P V.
+      auto score_mma = [&](uint32_t s_tmem, uint64_t kd, int i) {
         const int a = i / kMmasPerAtom, s = i % kMmasPerAtom;
-        const uint64_t kdesc0 = umma_desc_sw128(smem_u32(k_stage(j % kKvStages)));
-        mma(tmem_base + (j & 1) * L::kSCols, qdesc0 + ((a * kBlockQ * kAtomBytes) >> 4) + s * kMmaStep,
-            kdesc0 + ((a * kBlockKv * kAtomBytes) >> 4) + s * kMmaStep, idesc_s, i != 0 ? 1u : 0u);
+        umma_ss<kKindF16>(s_tmem, qdesc0 + (((a * kBlockQ * kAtomBytes) >> 4) + s * kMmaStep),
+                          kd + (((a * kBlockKv * kAtomBytes) >> 4) + s * kMmaStep), idesc_s, i != 0 ? 1u : 0u);
       };
-      auto out_mma = [&](int j, int i) {
+      auto out_mma = [&](uint64_t pd, uint64_t vd, int i, uint32_t first_block) {
         const int a = i / kMmasPerAtom, s = i % kMmasPerAtom;
-        const uint64_t vdesc0 = umma_desc_sw128(smem_u32(v_stage(j % kKvStages)));
-        mma(tmem_base + L::kOCol, pdesc0 + (((j & 1) * L::kPBytes + a * L::kPAtomBytes) >> 4) + s * kMmaStep,
-            vdesc0 + ((a * L::kVAtomBytes) >> 4) + s * kMmaStep, idesc_o, (j | i) != 0 ? 1u : 0u);
+        umma_ss<kKindF16>(o_tmem, pd + (((a * L::kPAtomBytes) >> 4) + s * kMmaStep),
+                          vd + (((a * L::kVAtomBytes) >> 4) + s * kMmaStep), idesc_o, i != 0 ? 1u : (first_block ^ 1u));
       };
       auto wait_scores_operands = [&](int j) -> bool {
         return mbar_wait(&t.k_full_bar[j % kKvStages], (j / kKvStages) & 1, &abort_flag) &&
@@ -312,7 +312,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (!ok) break;
         tc_fence_after_sync();
 #pragma unroll
-        for (int i = 0; i < kScoreMmas; ++i) score_mma(j, i);
+        for (int i = 0; i < kScoreMmas; ++i) score_mma(tmem_base + (j & 1) * L::kSCols, (j & 1) ? kdesc_1 : kdesc_0, i);
         commit_scores(j);
       }
       for (int j = 0; j < num_blocks && ok; ++j) {
@@ -331,11 +331,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         // waits for the one before it, so in turn they take the time of one chain.
         static_assert(kScoreMmas == kOutMmas || kScoreMmas * 2 == kOutMmas, "interleave below");
         constexpr int kOutPerScore = kOutMmas / kScoreMmas;
+        const bool odd = (j & 1) != 0;
+        const uint32_t first_block = j == 0 ? 1u : 0u;
+        const uint32_t s_tmem = tmem_base + (odd ? L::kSCols : 0);
+        const uint64_t kd = odd ? kdesc_1 : kdesc_0, vd = odd ? vdesc_1 : vdesc_0, pd = odd ? pdesc_1 : pdesc0;
+        if (ahead) {
 #pragma unroll
-        for (int i = 0; i < kScoreMmas; ++i) {
+          for (int i = 0; i < kScoreMmas; ++i) {
 #pragma unroll
-          for (int o = 0; o < kOutPerScore; ++o) out_mma(j, i * kOutPerScore + o);
-          if (ahead) score_mma(j + 2, i);
+            for (int o = 0; o < kOutPerScore; ++o) out_mma(pd, vd, i * kOutPerScore + o, first_block);
+            score_mma(s_tmem, kd, i);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < kOutMmas; ++i) out_mma(pd, vd, i, first_block);
         }
         umma_commit(&t.v_empty_bar[j % kKvStages]);
         umma_commit(&t.pv_done_bar[j & 1]);
