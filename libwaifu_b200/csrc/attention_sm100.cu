@@ -430,19 +430,25 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // Does any key of this block need masking for any row of the CTA?
       const bool edge = (j * kBlockKv + kBlockKv > p.kv_len) || (p.causal && j * kBlockKv + kBlockKv - 1 > q0 + offset);
       const int key_limit = p.causal ? min(p.kv_len - 1, q_pos) : p.kv_len - 1;  // last key this row sees
-      // Scaled to log2 units, masked, and the maximum over this thread's keys.
+      // Masked (edge blocks only), and the maximum over this thread's keys; the scale to log2
+      // units is positive, so it is applied to the maximum here and to the scores inside the
+      // exponent's multiply-add below.
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
+      if (edge) {
+#pragma unroll
+        for (int c = 0; c < kMyKeys / 32; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (key0 + c * 32 + i > key_limit) sc[c][i] = __float_as_uint(-INFINITY);
+          }
+        }
+      }
 #pragma unroll
       for (int c = 0; c < kMyKeys / 32; ++c) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(sc[c][i]) * p.scale_log2;
-          if (edge && key0 + c * 32 + i > key_limit) x = -INFINITY;
-          sc[c][i] = __float_as_uint(x);
-          m4[i & 3] = fmaxf(m4[i & 3], x);
-        }
+        for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sc[c][i]));
       }
-      float m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      float m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
       float m_other;
       if (!exchange(m_blk, &m_other)) break;
       m_blk = fmaxf(m_blk, m_other);
@@ -477,8 +483,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float e0 = fast_exp2(__uint_as_float(sc[c][i]) - m_sub);
-          const float e1 = fast_exp2(__uint_as_float(sc[c][i + 1]) - m_sub);
+          const float e0 = fast_exp2(fmaf(__uint_as_float(sc[c][i]), p.scale_log2, -m_sub));
+          const float e1 = fast_exp2(fmaf(__uint_as_float(sc[c][i + 1]), p.scale_log2, -m_sub));
           sum4[(i >> 1) & 3] += e0 + e1;
           packed[i >> 1] = pack16(e0, e1, p.is_bf16);
         }

@@ -53,6 +53,7 @@ SHAPES = [
     (1, 8, 1, 1, 517, 128),      # one query (a decode step), multi-query
     (2, 2, 2, 300, 8, 64),       # fewer keys than a block
     (1, 2, 2, 513, 640, 128),
+    (1, 2, 1, 640, 4224, 64),    # many blocks: the rings and the score buffers wrap many times
 ]
 
 
