@@ -27,6 +27,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "ptx_sm100.cuh"
 
 namespace flsm100 {
@@ -122,6 +124,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// max(a, b, c) in one instruction.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
 }
 
 __device__ __forceinline__ uint32_t pack16(float a, float b, int is_bf16) {
@@ -446,7 +455,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
       for (int c = 0; c < kMyKeys / 32; ++c) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sc[c][i]));
+        for (int i = 0; i < 32; i += 2) {
+          m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], __uint_as_float(sc[c][i]), __uint_as_float(sc[c][i + 1]));
+        }
       }
       float m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
       float m_other;
@@ -478,22 +489,32 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // The probabilities, into shared memory as the A operand of P V.
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       uint8_t *atom = p_row + (j & 1) * L::kPBytes;
+      // (One copy of the loop per 16-bit type, so that the choice is made once per block and not
+      // once per pair of values.)
+      auto emit = [&](auto bf16_tag) {
+        constexpr int kBf16 = decltype(bf16_tag)::value ? 1 : 0;
 #pragma unroll
-      for (int c = 0; c < kMyKeys / 32; ++c) {
-        uint32_t packed[16];
+        for (int c = 0; c < kMyKeys / 32; ++c) {
+          uint32_t packed[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float e0 = fast_exp2(fmaf(__uint_as_float(sc[c][i]), p.scale_log2, -m_sub));
-          const float e1 = fast_exp2(fmaf(__uint_as_float(sc[c][i + 1]), p.scale_log2, -m_sub));
-          sum4[(i >> 1) & 3] += e0 + e1;
-          packed[i >> 1] = pack16(e0, e1, p.is_bf16);
+          for (int i = 0; i < 32; i += 2) {
+            const float e0 = fast_exp2(fmaf(__uint_as_float(sc[c][i]), p.scale_log2, -m_sub));
+            const float e1 = fast_exp2(fmaf(__uint_as_float(sc[c][i + 1]), p.scale_log2, -m_sub));
+            sum4[(i >> 1) & 3] += e0 + e1;
+            packed[i >> 1] = pack16(e0, e1, kBf16);
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint32_t piece = static_cast<uint32_t>(c * 4 + g) ^ p_xor;
+            *reinterpret_cast<uint4 *>(atom + piece * 16) =
+                make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+          }
         }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const uint32_t piece = static_cast<uint32_t>(c * 4 + g) ^ p_xor;
-          *reinterpret_cast<uint4 *>(atom + piece * 16) =
-              make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
-        }
+      };
+      if (p.is_bf16) {
+        emit(std::true_type{});
+      } else {
+        emit(std::false_type{});
       }
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       // The next block's scores (ready since the product before last) are read before P is handed
