@@ -64,7 +64,7 @@ NCU_TRAFFIC_BYTES = {
     "c1_linear": 22.1e6,                                 # the bf16 output stays dirty in L2
     "c3_nvfp4_qkv": 24.0e6 + 25.5e6,
     "skinny_decode": 50.38e6 + 7.0e6,                    # the weight once; the writes are older dirty lines leaving L2
-    "attention_step": 161.1e6 + 35.9e6,                  # q, k, v once (K and V re-reads hit L2); the output partly stays in L2
+    "attention_step": 160.5e6 + 33.5e6,                  # q, k, v once (K and V re-reads hit L2); the output partly stays in L2
 }
 
 
