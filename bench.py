@@ -352,8 +352,8 @@ def run_ours(args, wl):
             # The all-gathers fused into the GEMMs: every rank's epilogue writes its column block
             # into every rank's full-width H and Y over NVLink (peer-mapped storage), and a
             # one-element all-reduce on the stream orders the ranks before the result is read.
-            h_own = F.Tensor.empty((m, n_up), bf)
-            y_own = F.Tensor.empty((m, n_dn), bf)
+            h_own = F.Tensor.empty((m, n_up), bf, hint=F.AllocHint.WEIGHT)  # memory of its own: exportable
+            y_own = F.Tensor.empty((m, n_dn), bf, hint=F.AllocHint.WEIGHT)
             handles = [None] * world
             dist.all_gather_object(handles, (F.ipc_export(h_own), F.ipc_export(y_own)))
             h_dests, y_dests = [h_own], [y_own]

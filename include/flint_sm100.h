@@ -43,6 +43,8 @@ extern "C" {
 typedef struct fl_tensor_data_impl_t *fl_tensor_data_t;
 typedef struct fl_tensor_view_impl_t *fl_tensor_view_t;
 typedef struct fl_operators_impl_t *fl_operators_t;
+/* flint/capi.h:71-73. A copy that is still on its way. */
+typedef struct fl_transfer_impl_t *fl_transfer_t;
 
 /* flint/capi.h:84-94. 5 and 7 are holes in the reference and stay holes. 11 and 12 are additive. */
 typedef enum fl_dtype_t {
@@ -92,7 +94,10 @@ FLAPI int32_t fl_operators_create(fl_device_type_t device, fl_operators_t *out);
 FLAPI void fl_operators_destroy(fl_operators_t operators);
 FLAPI int32_t fl_operators_get_device(fl_operators_t operators, fl_device_type_t *out);
 
-/* flint/capi.h:185-213 (storage) */
+/* flint/capi.h:185-213 (storage). On FL_DEVICE_CUDA the memory comes from the device's stream-ordered
+ * pool in the compute stream's order and goes back to it the same way, so neither call makes the
+ * host or the device wait; only a weight (FL_ALLOC_WEIGHT) of 2 MiB or more gets memory of its own
+ * (flint/cuda/cuda_tensor_data.cc:36-77). At most 2^30 elements (flint/tensor.h:41). */
 FLAPI int32_t fl_tensor_data_create(fl_device_type_t device, fl_dtype_t dtype, int64_t numel, fl_alloc_hint_t hint,
                                     fl_tensor_data_t *out);
 FLAPI int32_t fl_tensor_data_borrow(const void *data, fl_dtype_t dtype, int64_t numel, fl_tensor_data_t *out);
@@ -104,8 +109,28 @@ FLAPI int32_t fl_tensor_view_create(fl_tensor_data_t data, const int32_t *shape,
                                     int64_t offset, fl_tensor_view_t *out);
 FLAPI void fl_tensor_view_destroy(fl_tensor_view_t view);
 
+/* flint/capi.h:246. src into dest, same shape and dtype, any strides, both on the device. */
+FLAPI int32_t fl_copy(fl_operators_t operators, fl_tensor_view_t src, fl_tensor_view_t dest);
+/* flint/capi.h:249. Between <float>, <float16> and <bfloat16> here. */
+FLAPI int32_t fl_cast(fl_operators_t operators, fl_tensor_view_t input, fl_tensor_view_t out);
+
 /* flint/capi.h:254. Contiguous src -> contiguous dest on another device, same shape and dtype. */
 FLAPI int32_t fl_transfer(fl_operators_t operators, fl_tensor_view_t src, fl_tensor_view_t dest);
+
+/* flint/capi.h:256-264. Starts copying contiguous `src`, in page-locked host memory, to `device`
+ * (FL_DEVICE_CUDA) and returns before it has arrived. The storage it fills comes back in `dest`,
+ * owned by the caller; it must not be read before the transfer has been waited on, and `src`'s
+ * storage has to stay alive until then. The copy runs on a stream of its own, beside the kernels. */
+FLAPI int32_t fl_transfer_async(fl_tensor_view_t src, fl_device_type_t device, fl_tensor_data_t *dest, fl_transfer_t *out);
+/* flint/capi.h:266-268. Orders the work that follows behind the copy, without stopping the caller. */
+FLAPI int32_t fl_transfer_wait(fl_transfer_t transfer);
+/* flint/capi.h:270-272. The same, but does not return until the copy has finished. */
+FLAPI int32_t fl_transfer_wait_sync(fl_transfer_t transfer);
+/* flint/capi.h:274-276. Frees the handle, waited on or not. */
+FLAPI void fl_transfer_destroy(fl_transfer_t transfer);
+
+/* flint/capi.h:279. <float>, <float16> and <bfloat16> tensors here. */
+FLAPI int32_t fl_fill(fl_operators_t operators, fl_tensor_view_t tensor, float value);
 
 /* flint/capi.h:440-446 and 448-456, for the linear-layer case only: a <float16|bfloat16>(..., k)
  * contiguous, b (k, n) the transposed view (strides 1, k) of a contiguous (n, k) weight of the
@@ -116,6 +141,10 @@ FLAPI int32_t fl_transfer(fl_operators_t operators, fl_tensor_view_t src, fl_ten
 FLAPI int32_t fl_matmul(fl_operators_t operators, fl_tensor_view_t a, fl_tensor_view_t b, fl_tensor_view_t out);
 FLAPI int32_t fl_matmul_add(fl_operators_t operators, fl_tensor_view_t a, fl_tensor_view_t b, fl_tensor_view_t addend,
                             fl_tensor_view_t out);
+
+/* flint/capi.h:480-483. `b` and `out` have `a`'s shape (a broadcast operand is handed over as an
+ * expanded view); <float>, <float16> or <bfloat16>, one type; the sum is rounded once. */
+FLAPI int32_t fl_add(fl_operators_t operators, fl_tensor_view_t a, fl_tensor_view_t b, fl_tensor_view_t out);
 
 /* flint/capi.h:118-133. Which keys a query may see in fl_attention(): query i sits at position
  * p = i + S - L. */
@@ -185,7 +214,11 @@ FLAPI int32_t fl_fp8_linear(fl_tensor_view_t a, fl_tensor_view_t data, fl_tensor
  * How: the quantised activation (m * k bytes), its m row scales and the kernels' status word live
  * in one fixed device array compiled into the library, about 16.3 MiB, which every GPU that loads
  * the library holds until the process ends. The call makes no cudaMalloc, cudaFree, cudaHostAlloc
- * or other allocating call. Arguments, checks, arithmetic and results are fl_fp8_linear()'s.
+ * or other allocating call. Arguments and checks are fl_fp8_linear()'s; the arithmetic is that of
+ * fl_fp8_linear()'s tile path (quantiser kernel, then the tcgen05 GEMM) for every row count, so
+ * from five rows on the results are bit-identical to fl_fp8_linear()'s, and for one to four rows,
+ * where fl_fp8_linear() takes its few-row kernel with another summation order, they agree within
+ * the path's tolerance. FLINT_SM100_SINGLE_CTA and fl_sm100_gemm_timing() do not apply here.
  *
  * Limits, refused with FL_ERROR_INVALID_ARG before anything is launched: at most 65536 activation
  * rows (the product of a's leading dimensions), at most 16 Mi elements in m * k (4352 x 3072 fits),
@@ -197,11 +230,13 @@ FLAPI int32_t fl_fp8_linear(fl_tensor_view_t a, fl_tensor_view_t data, fl_tensor
  * library is ever driven on more than its one stream) race on it and must be serialised by the
  * caller. To report a kernel that gave up on a wait, each call first reads the previous call's
  * status word back, which waits for that call's kernels: consecutive calls do not overlap their
- * launches the way fl_fp8_linear() calls do.
+ * launches the way fl_fp8_linear() calls do. The last call's status word is reported by
+ * fl_sm100_synchronize() and by a fl_transfer() towards the host.
  *
  * First call: on each device, the first call looks the array's device address up (once, with that
  * device current) and, like any first launch, loads the kernels. Make that first call before
- * beginning any stream capture on that device. */
+ * beginning any stream capture on that device. (Every call also makes one small synchronous copy
+ * on the legacy stream, the read-back above.) */
 FLAPI int32_t fl_fp8_linear_static(fl_tensor_view_t a, fl_tensor_view_t data, fl_tensor_view_t scales,
                                    fl_tensor_view_t bias, fl_tensor_view_t residual, int32_t act,
                                    fl_tensor_view_t out);
@@ -220,7 +255,8 @@ FLAPI int32_t fl_fp8_linear_scatter(fl_tensor_view_t a, fl_tensor_view_t data, f
                                     const fl_tensor_view_t *dests, int32_t n_dest, int32_t col0);
 
 /* Device storage shared between the processes of one box (one process per GPU): export writes
- * the 64-byte handle of storage made by fl_tensor_data_create(FL_DEVICE_CUDA, ...); import maps
+ * the 64-byte handle of storage made by fl_tensor_data_create(FL_DEVICE_CUDA, ..., FL_ALLOC_WEIGHT, ...)
+ * of 2 MiB or more (memory of its own; blocks of the stream-ordered pool have no handle); import maps
  * another process's storage here (peer access over NVLink); fl_tensor_data_destroy() unmaps. */
 FLAPI int32_t fl_sm100_ipc_export(fl_tensor_data_t data, void *handle_out);
 FLAPI int32_t fl_sm100_ipc_import(const void *handle, fl_dtype_t dtype, int64_t numel, fl_tensor_data_t *out);
@@ -303,10 +339,19 @@ FLAPI int32_t fl_sm100_few_rows_plan(int32_t m, int32_t n, int32_t k, int32_t we
  * is copied and nothing is freed on destroy. The device counterpart of fl_tensor_data_borrow(). */
 FLAPI int32_t fl_tensor_data_borrow_device(void *device_ptr, fl_dtype_t dtype, int64_t numel, fl_tensor_data_t *out);
 
-/* Selects the CUDA device this thread's later calls use (one process per GPU sets its own). */
+/* The download fl_transfer_async() has no counterpart for in the reference (whose device-to-host copy
+ * is synchronous, flint/cuda/to_device.cc:60-66): contiguous device `src` into page-locked host
+ * `dest` of the same shape and dtype, on a stream of its own, ordered behind the work queued so far.
+ * The host may read `dest` once fl_transfer_wait_sync() on the handle has returned; `src` has to
+ * stay alive until then. Free the handle with fl_transfer_destroy(). */
+FLAPI int32_t fl_sm100_transfer_to_host_async(fl_tensor_view_t src, fl_tensor_view_t dest, fl_transfer_t *out);
+
+/* Selects the CUDA device of this process (one process per GPU). Allowed before the first
+ * operation, or again with the same ordinal; a second device in one process is refused. */
 FLAPI int32_t fl_sm100_set_device(int32_t ordinal);
-/* Waits for the default stream, then reports the kernels' status word: 0, or the code of the
- * bounded wait that gave up inside a kernel (the call then also returns FL_ERROR_ABORTED). */
+/* Waits for the default stream, then reports the kernels' status word (the library's, and the one
+ * fl_fp8_linear_static()'s kernels use): 0, or the code of the bounded wait that gave up inside a
+ * kernel (the call then also returns FL_ERROR_ABORTED). */
 FLAPI int32_t fl_sm100_synchronize(int32_t *kernel_status);
 /* Per-launch timing of the GEMM kernel alone: while enabled, every GEMM launch is bracketed by
  * CUDA events on its stream; fl_sm100_gemm_timing_read() waits for the stream, returns the summed
@@ -315,6 +360,15 @@ FLAPI int32_t fl_sm100_gemm_timing(int32_t enable);
 FLAPI int32_t fl_sm100_gemm_timing_read(double *total_ms, int64_t *launches);
 /* How many kernels of this library the calling process has launched so far. */
 FLAPI int64_t fl_sm100_launch_count(void);
+
+/* Self-tests of the error path, for this library's own tests. Neither faults nor hangs anything.
+ * fl_sm100_selftest_wait_timeout() launches one warp that waits, with a limit of `polls` (1..4096)
+ * polls, on a barrier nothing ever arrives on, and reports status 0x51 the way the GEMM and attention
+ * kernels report a wait that gave up: the next fl_sm100_synchronize() returns FL_ERROR_ABORTED with
+ * that status, and the call after it succeeds. fl_sm100_selftest_set_static_status() writes `code`
+ * into the status word of fl_fp8_linear_static()'s array, as one of its kernels would. */
+FLAPI int32_t fl_sm100_selftest_wait_timeout(int32_t polls);
+FLAPI int32_t fl_sm100_selftest_set_static_status(uint32_t code);
 
 #ifdef __cplusplus
 }

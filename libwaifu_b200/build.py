@@ -10,8 +10,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libflint_sm100.so")
-SOURCES = ["gemm_sm100.cu", "quant_sm100.cu", "skinny_sm100.cu", "block_sm100.cu", "attention_sm100.cu", "flint_capi.cu"]
-HEADERS = ["gemm_sm100.cuh", "quant_sm100.cuh", "skinny_sm100.cuh", "block_sm100.cuh", "attention_sm100.cuh", "ptx_sm100.cuh", os.path.join("..", "..", "include", "flint_sm100.h")]
+SOURCES = ["gemm_sm100.cu", "quant_sm100.cu", "skinny_sm100.cu", "block_sm100.cu", "attention_sm100.cu", "elementwise_sm100.cu",
+           "selftest_sm100.cu", "flint_capi.cu"]
+HEADERS = ["gemm_sm100.cuh", "quant_sm100.cuh", "skinny_sm100.cuh", "block_sm100.cuh", "attention_sm100.cuh", "elementwise_sm100.cuh",
+           "selftest_sm100.cuh", "ptx_sm100.cuh", os.path.join("..", "..", "include", "flint_sm100.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -42,15 +44,19 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return LIB_PATH
     os.makedirs(LIB_DIR, exist_ok=True)
     nvcc = _nvcc()
-    objs = []
-    for src in SOURCES:
+    from concurrent.futures import ThreadPoolExecutor
+
+    def compile_one(src: str) -> str:
         obj = os.path.join(LIB_DIR, src.replace(".cu", ".o"))
         cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
         subprocess.run(cmd, check=True)
-        objs.append(obj)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as pool:
+        objs = list(pool.map(compile_one, SOURCES))
     subprocess.run([nvcc, "-shared", "-cudart", "static", "-Wno-deprecated-gpu-targets", "-o", LIB_PATH, *objs, "-lpthread", "-ldl", "-lrt"], check=True)
     return LIB_PATH
 

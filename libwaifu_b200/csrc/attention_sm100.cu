@@ -651,6 +651,17 @@ bool attention_supported(const AttentionArgs &a, const char **why) {
       if (s[i] < 0 || s[i] % 8 != 0) return fail("a stride is negative or not a multiple of 8 elements");
     }
   }
+  // q, k and out are read and written through tensor maps, which cannot repeat a dimension: a
+  // stride of 0 (a broadcast view) over an extent above 1 is refused here rather than read at the
+  // wrong addresses. Only a dimension of extent 1, whose stride indexes nothing, may carry one.
+  // (v is gathered by the transposing kernel with its true strides and may repeat.)
+  const int q_extent[3] = {a.batch, a.heads, a.q_len};
+  const int k_extent[3] = {a.batch, a.kv_heads, a.kv_len};
+  for (int i = 0; i < 3; ++i) {
+    if ((q_extent[i] > 1 && (a.q_stride[i] == 0 || a.out_stride[i] == 0)) || (k_extent[i] > 1 && a.k_stride[i] == 0)) {
+      return fail("q, k or out repeats a dimension through a stride of 0 (a broadcast view)");
+    }
+  }
   return true;
 }
 

@@ -19,6 +19,8 @@
 #include "block_sm100.cuh"
 #include "skinny_sm100.cuh"
 #include "attention_sm100.cuh"
+#include "elementwise_sm100.cuh"
+#include "selftest_sm100.cuh"
 
 using namespace flsm100;
 
@@ -29,6 +31,18 @@ struct fl_tensor_data_impl_t {
   fl_device_type_t device = FL_DEVICE_UNKNOWN;
   bool owned = false;
   bool ipc_mapped = false;  // another process's device storage, opened through its IPC handle
+  // Device storage from the stream-ordered pool is given back in the order of the stream that
+  // last owned its bytes (flint/cuda/cuda_tensor_data.cc:62-77); `resident` storage is a weight's
+  // own cudaMalloc (flint/cuda/cuda_tensor_data.cc:44-48) and the only kind that can be exported.
+  bool pooled = false;
+  bool resident = false;
+  cudaStream_t stream = nullptr;
+};
+
+// flint/capi.cc:530-535: the event that marks the end of a copy, and the storage it fills.
+struct fl_transfer_impl_t {
+  cudaEvent_t event = nullptr;
+  fl_tensor_data_impl_t *dest = nullptr;  // null for a copy towards the host
 };
 
 struct fl_tensor_view_impl_t {
@@ -134,6 +148,14 @@ struct DeviceState {
   // All work is ordered on the legacy default stream, so one arena can be reused call after call.
   uint8_t *scratch = nullptr;
   size_t scratch_cap = 0;
+  // Set by the first call that touches the GPU: from then on this process belongs to that device
+  // (per-process caches in the kernel modules assume one), and fl_sm100_set_device() refuses another.
+  int device_in_use = -1;
+  bool pool_ready = false;
+  // Non-blocking streams the asynchronous transfers run on (flint/cuda/copy_stream.cc:31), one
+  // per direction so that uploads and downloads share the full-duplex link.
+  cudaStream_t upload_stream = nullptr;
+  cudaStream_t download_stream = nullptr;
 };
 
 std::mutex g_mutex;
@@ -176,6 +198,37 @@ void require_kernels() {
   DeviceState &d = device_state();
   if (!d.present) aborted("no CUDA device is present");
   if (!d.sm100) aborted("the CUDA device is not compute capability 10.x; these kernels are sm_100a only");
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (d.device_in_use < 0) {
+    int dev = 0;
+    cuda_check(cudaGetDevice(&dev), "cudaGetDevice");
+    d.device_in_use = dev;
+  }
+}
+
+// The stream-ordered pool every activation and temporary comes from: the device's default pool,
+// told to keep what is freed instead of handing it back to the driver at the next
+// synchronisation (flint/cuda/cuda_operators.cc:91-98).
+void ensure_pool() {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_dev.pool_ready) return;
+  int dev = 0;
+  cuda_check(cudaGetDevice(&dev), "cudaGetDevice");
+  int supported = 0;
+  cuda_check(cudaDeviceGetAttribute(&supported, cudaDevAttrMemoryPoolsSupported, dev), "cudaDeviceGetAttribute");
+  if (!supported) aborted("the CUDA device does not support stream-ordered memory allocation");
+  cudaMemPool_t pool;
+  uint64_t threshold = UINT64_MAX;
+  cuda_check(cudaDeviceGetDefaultMemPool(&pool, dev), "cudaDeviceGetDefaultMemPool");
+  cuda_check(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold), "cudaMemPoolSetAttribute");
+  g_dev.pool_ready = true;
+}
+
+cudaStream_t copy_stream(bool upload) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  cudaStream_t &st = upload ? g_dev.upload_stream : g_dev.download_stream;
+  if (!st) cuda_check(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking), "cudaStreamCreateWithFlags");
+  return st;
 }
 
 uint32_t *status_word() {
@@ -191,6 +244,11 @@ uint32_t *status_word() {
   }
   return g_dev.status_dev;
 }
+
+// The status word of fl_fp8_linear_static()'s kernels, which lives in that entry point's fixed
+// device array: read back and cleared (4 bytes each way, no allocation) once the array's address
+// has been looked up on this device, 0 before. The caller has synchronised the stream.
+uint32_t take_static_status();
 
 // A kernel that gave up on a wait in an earlier call is reported by the next call.
 void check_earlier_kernel_status() {
@@ -216,19 +274,22 @@ struct Scratch {
     used = off + bytes;
     return off;
   }
-  // Grows the arena if needed (a rare, synchronising event) and returns its base.
+  // Grows the arena if needed (a rare event) and returns its base. The old block goes back to the
+  // pool and the new one comes from it in stream 0's order (flint's temporaries do the same through
+  // llynCudaAlloc, flint/cuda/common.h:197-202), so growing does not make the host or the device wait:
+  // kernels already queued keep the old block until the stream reaches the free.
   uint8_t *commit() {
+    if (used > g_dev.scratch_cap) ensure_pool();
     std::lock_guard<std::mutex> lock(g_mutex);
     if (used > g_dev.scratch_cap) {
       size_t cap = used + used / 4 + (1 << 20);
       if (g_dev.scratch) {
-        cuda_check(cudaStreamSynchronize(0), "cudaStreamSynchronize before regrowing scratch");
-        cuda_check(cudaFree(g_dev.scratch), "cudaFree(scratch)");
+        cuda_check(cudaFreeAsync(g_dev.scratch, 0), "cudaFreeAsync(scratch)");
         g_dev.scratch = nullptr;
         g_dev.scratch_cap = 0;
       }
       void *p = nullptr;
-      cuda_check(cudaMalloc(&p, cap), "cudaMalloc(scratch)");
+      cuda_check(cudaMallocAsync(&p, cap, 0), "cudaMallocAsync(scratch)");
       g_dev.scratch = static_cast<uint8_t *>(p);
       g_dev.scratch_cap = cap;
     }
@@ -279,6 +340,9 @@ uint8_t *raw_ptr(const fl_tensor_view_impl_t &v) {
 
 fl_dtype_t dtype_of(const fl_tensor_view_impl_t &v) { return v.data->dtype; }
 fl_device_type_t device_of(const fl_tensor_view_impl_t &v) { return v.data->device; }
+
+constexpr int64_t kMaxStorageElements = int64_t(1) << 30;  // TensorData::MaxNumEl, flint/tensor.h:41
+constexpr size_t kResidentWeightBytes = size_t(2) << 20;   // flint/cuda/common.h:167
 
 bool is_half_type(fl_dtype_t t) { return t == FL_DTYPE_FLOAT16 || t == FL_DTYPE_BFLOAT16; }
 
@@ -583,20 +647,31 @@ int32_t fl_operators_get_device(fl_operators_t operators, fl_device_type_t *out)
 
 int32_t fl_tensor_data_create(fl_device_type_t device, fl_dtype_t dtype, int64_t numel, fl_alloc_hint_t hint,
                               fl_tensor_data_t *out) {
-  (void)hint;
   return guard([&]() {
     if (!out) invalid("out is null");
     if (numel < 1) invalid("storage holds at least one element");
-    if (numel > (int64_t(1) << 30) * 4) invalid("too many elements");
+    if (numel > kMaxStorageElements) invalid("too many elements");  // flint/tensor.h:41
+    if (hint < FL_ALLOC_ACTIVATION || hint > FL_ALLOC_TEMPORARY_WEIGHT) invalid("unknown allocation hint");
     const size_t bytes = static_cast<size_t>(numel * dtype_size(dtype));
     void *p = nullptr;
+    bool pooled = false, resident = false;
     switch (device) {
       case FL_DEVICE_CPU:
         if (posix_memalign(&p, 64, bytes < 64 ? 64 : bytes) != 0) throw FlError{FL_ERROR_OUT_OF_MEMORY, "host allocation failed"};
         break;
       case FL_DEVICE_CUDA:
         require_kernels();
-        cuda_check(cudaMalloc(&p, bytes), "cudaMalloc");
+        // flint/cuda/cuda_tensor_data.cc:36-52: a weight of 2 MiB or more gets memory of its own (it
+        // stays until it is let go of, and then goes back to the driver whole); everything else
+        // comes from the pool in stream 0's order, which makes neither the host nor the device wait.
+        resident = hint == FL_ALLOC_WEIGHT && bytes >= kResidentWeightBytes;
+        if (resident) {
+          cuda_check(cudaMalloc(&p, bytes), "cudaMalloc");
+        } else {
+          ensure_pool();
+          cuda_check(cudaMallocAsync(&p, bytes, 0), "cudaMallocAsync");
+          pooled = true;
+        }
         break;
       case FL_DEVICE_CUDA_HOST:
         require_kernels();
@@ -610,6 +685,8 @@ int32_t fl_tensor_data_create(fl_device_type_t device, fl_dtype_t dtype, int64_t
     d->dtype = dtype;
     d->device = device;
     d->owned = true;
+    d->pooled = pooled;
+    d->resident = resident;
     *out = d;
     return clear_error();
   });
@@ -620,6 +697,7 @@ int32_t fl_tensor_data_borrow(const void *data, fl_dtype_t dtype, int64_t numel,
     if (!out) invalid("out is null");
     if (!data) invalid("data is null");
     if (numel < 1) invalid("storage holds at least one element");
+    if (numel > kMaxStorageElements) invalid("too many elements");
     const int64_t alignment = dtype_size(dtype);
     if (reinterpret_cast<uintptr_t>(data) % alignment != 0) {
       invalid("data is not aligned to its " + std::to_string(alignment) + "-byte elements");
@@ -641,7 +719,15 @@ void fl_tensor_data_destroy(fl_tensor_data_t data) {
   if (data->owned && data->ptr) {
     switch (data->device) {
       case FL_DEVICE_CPU: free(data->ptr); break;
-      case FL_DEVICE_CUDA: cudaFree(data->ptr); break;  // synchronises with outstanding work
+      case FL_DEVICE_CUDA:
+        // In the order of the stream that last owned the bytes, so nothing waits; a weight's own
+        // memory goes back with cudaFree, which waits for the device (flint/cuda/cuda_tensor_data.cc:62-77).
+        if (data->pooled) {
+          cudaFreeAsync(data->ptr, data->stream);
+        } else {
+          cudaFree(data->ptr);
+        }
+        break;
       case FL_DEVICE_CUDA_HOST: cudaFreeHost(data->ptr); break;
       default: break;
     }
@@ -711,9 +797,128 @@ int32_t fl_transfer(fl_operators_t operators, fl_tensor_view_t src_h, fl_tensor_
                                src_host ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, 0),
                "cudaMemcpyAsync");
     if (dest_host) {
+      // The host is about to read the bytes: wait for them, and do not hand back the output of a
+      // kernel that gave up on a wait, whichever status word it reported through.
       cuda_check(cudaStreamSynchronize(0), "cudaStreamSynchronize");
       check_earlier_kernel_status();
+      const uint32_t code = take_static_status();
+      if (code != 0) {
+        aborted("a kernel of fl_fp8_linear_static gave up on a bounded wait (status " + std::to_string(code) + ")");
+      }
     }
+    return clear_error();
+  });
+}
+
+// flint/capi.h:256-264, flint/cuda/to_device.cc:143-181. Page-locked host memory to the GPU, on
+// the upload stream, into storage allocated in that stream's order; every other direction is
+// refused rather than quietly done synchronously.
+int32_t fl_transfer_async(fl_tensor_view_t src_h, fl_device_type_t device, fl_tensor_data_t *dest, fl_transfer_t *out) {
+  return guard([&]() -> int32_t {
+    if (!dest || !out) invalid("out is null");
+    const fl_tensor_view_impl_t &src = deref(src_h);
+    if (device != FL_DEVICE_CUDA || device_of(src) != FL_DEVICE_CUDA_HOST) {
+      invalid(std::string("an asynchronous copy goes from cuda-host to cuda, not from ") + device_name(device_of(src)) +
+              " to " + device_name(device));
+    }
+    if (!is_contiguous(src)) invalid("an asynchronous copy reads one contiguous run");
+    require_kernels();
+    ensure_pool();
+    cudaStream_t stream = copy_stream(/*upload=*/true);
+    const int64_t numel = numel_of(src);
+    const size_t bytes = static_cast<size_t>(numel * dtype_size(dtype_of(src)));
+    void *p = nullptr;
+    cuda_check(cudaMallocAsync(&p, bytes ? bytes : 1, stream), "cudaMallocAsync");
+    auto *d = new fl_tensor_data_impl_t();
+    d->ptr = p;
+    d->numel = numel > 0 ? numel : 1;
+    d->dtype = dtype_of(src);
+    d->device = FL_DEVICE_CUDA;
+    d->owned = true;
+    d->pooled = true;
+    d->stream = stream;  // until the transfer is waited on, the copy stream owns the bytes
+    auto *t = new fl_transfer_impl_t();
+    t->dest = d;
+    cudaError_t e = bytes ? cudaMemcpyAsync(p, raw_ptr(src), bytes, cudaMemcpyHostToDevice, stream) : cudaSuccess;
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&t->event, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventRecord(t->event, stream);
+    if (e != cudaSuccess) {
+      if (t->event) cudaEventDestroy(t->event);
+      delete t;
+      fl_tensor_data_destroy(d);
+      cuda_check(e, "starting the asynchronous copy");
+    }
+    *dest = d;
+    *out = t;
+    return clear_error();
+  });
+}
+
+namespace {
+// flint/cuda/to_device.cc:183-195: the compute stream waits rather than the host, unless the host
+// is about to read the bytes itself; the storage then belongs to the compute stream.
+int32_t wait_transfer(fl_transfer_t transfer, bool sync) {
+  return guard([&]() -> int32_t {
+    if (!transfer) invalid("transfer is null");
+    if (transfer->event) {
+      if (sync) {
+        cuda_check(cudaEventSynchronize(transfer->event), "cudaEventSynchronize");
+      } else {
+        cuda_check(cudaStreamWaitEvent(0, transfer->event, 0), "cudaStreamWaitEvent");
+      }
+      if (transfer->dest) transfer->dest->stream = nullptr;
+      cudaEventDestroy(transfer->event);
+      transfer->event = nullptr;
+    }
+    return clear_error();
+  });
+}
+}  // namespace
+
+int32_t fl_transfer_wait(fl_transfer_t transfer) { return wait_transfer(transfer, false); }
+int32_t fl_transfer_wait_sync(fl_transfer_t transfer) { return wait_transfer(transfer, true); }
+
+void fl_transfer_destroy(fl_transfer_t transfer) {
+  if (!transfer) return;
+  if (transfer->event) cudaEventDestroy(transfer->event);  // a pending event goes once the device has reached it
+  delete transfer;
+}
+
+// The other direction, which the reference only has synchronously (flint/cuda/to_device.cc:60-66):
+// contiguous device `src` into page-locked host `dest`, on the download stream, ordered behind the
+// work queued on the compute stream so far. fl_transfer_wait_sync() on the handle is when the host
+// may read `dest`; `src` has to stay alive until then.
+int32_t fl_sm100_transfer_to_host_async(fl_tensor_view_t src_h, fl_tensor_view_t dest_h, fl_transfer_t *out) {
+  return guard([&]() -> int32_t {
+    if (!out) invalid("out is null");
+    const fl_tensor_view_impl_t &src = deref(src_h);
+    const fl_tensor_view_impl_t &dest = deref(dest_h);
+    if (device_of(src) != FL_DEVICE_CUDA || device_of(dest) != FL_DEVICE_CUDA_HOST) {
+      invalid(std::string("an asynchronous download goes from cuda to cuda-host, not from ") + device_name(device_of(src)) +
+              " to " + device_name(device_of(dest)));
+    }
+    if (!is_contiguous(src) || !is_contiguous(dest)) invalid("transfer: both views have to be contiguous");
+    if (src.shape != dest.shape) invalid("transfer: the shapes differ");
+    if (dtype_of(src) != dtype_of(dest)) invalid("transfer: the dtypes differ");
+    require_kernels();
+    check_earlier_kernel_status();
+    cudaStream_t stream = copy_stream(/*upload=*/false);
+    const size_t bytes = static_cast<size_t>(numel_of(src) * dtype_size(dtype_of(src)));
+    auto *t = new fl_transfer_impl_t();
+    cudaEvent_t produced = nullptr;
+    cudaError_t e = cudaEventCreateWithFlags(&produced, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventRecord(produced, 0);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(stream, produced, 0);
+    if (produced) cudaEventDestroy(produced);
+    if (e == cudaSuccess && bytes) e = cudaMemcpyAsync(raw_ptr(dest), raw_ptr(src), bytes, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&t->event, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventRecord(t->event, stream);
+    if (e != cudaSuccess) {
+      if (t->event) cudaEventDestroy(t->event);
+      delete t;
+      cuda_check(e, "starting the asynchronous download");
+    }
+    *out = t;
     return clear_error();
   });
 }
@@ -916,6 +1121,115 @@ int32_t fl_matmul_add(fl_operators_t operators, fl_tensor_view_t a_h, fl_tensor_
   });
 }
 
+// ---- the elementwise operators around the path (flint/capi.h:246-249,279,483) -------------------
+
+namespace {
+
+bool elem_kind_of(fl_dtype_t t, ElemKind *kind) {
+  switch (t) {
+    case FL_DTYPE_FLOAT: *kind = kElemF32; return true;
+    case FL_DTYPE_FLOAT16: *kind = kElemF16; return true;
+    case FL_DTYPE_BFLOAT16: *kind = kElemBF16; return true;
+    default: return false;
+  }
+}
+
+ElemView elem_view(const fl_tensor_view_impl_t &v, const char *what) {
+  if (v.shape.size() > static_cast<size_t>(kMaxElemDims)) {
+    invalid(std::string(what) + " has more than " + std::to_string(kMaxElemDims) + " dimensions");
+  }
+  ElemView e = {};
+  e.base = raw_ptr(v);
+  e.ndim = static_cast<int>(v.shape.size());
+  for (int d = 0; d < e.ndim; ++d) {
+    e.shape[d] = v.shape[d];
+    e.stride[d] = v.stride[d];
+  }
+  e.contiguous = is_contiguous(v);
+  return e;
+}
+
+// flint/capi.cc:176-189 (checkOnDevice): every view of an operation is on the operators' device.
+void check_on_cuda(fl_operators_t operators, const fl_tensor_view_impl_t &v, const char *what) {
+  if (!operators) invalid("operators is null");
+  if (device_of(v) != FL_DEVICE_CUDA) invalid(std::string(what) + " is not on the operators' device");
+}
+
+}  // namespace
+
+// flint/capi.h:246, flint/capi.cc:478-501. Same shape and dtype; any strides.
+int32_t fl_copy(fl_operators_t operators, fl_tensor_view_t src_h, fl_tensor_view_t dest_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &src = deref(src_h);
+    const fl_tensor_view_impl_t &dest = deref(dest_h);
+    check_on_cuda(operators, src, "the source");
+    check_on_cuda(operators, dest, "the destination");
+    if (dtype_of(src) != dtype_of(dest)) invalid("the source and the destination hold different types");
+    check_shape(dest, src.shape, "the destination");
+    require_kernels();
+    cuda_check(elementwise_copy(elem_view(src, "the source"), elem_view(dest, "the destination"),
+                                static_cast<int>(dtype_size(dtype_of(src))), numel_of(src), 0),
+               "copy");
+    return clear_error();
+  });
+}
+
+// flint/capi.h:249, flint/capi.cc:503-507. Between <float>, <float16> and <bfloat16>, any strides
+// (the reference's CUDA cast serves float <-> float16 on contiguous views, flint/cuda/cast.cu:70-95).
+int32_t fl_cast(fl_operators_t operators, fl_tensor_view_t input_h, fl_tensor_view_t out_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &x = deref(input_h);
+    const fl_tensor_view_impl_t &y = deref(out_h);
+    check_on_cuda(operators, x, "the input");
+    check_on_cuda(operators, y, "out");
+    check_shape(y, x.shape, "out");
+    ElemKind from, to;
+    if (!elem_kind_of(dtype_of(x), &from) || !elem_kind_of(dtype_of(y), &to)) {
+      invalid("cast: this library converts between <float>, <float16> and <bfloat16>");
+    }
+    require_kernels();
+    cuda_check(elementwise_cast(elem_view(x, "the input"), from, elem_view(y, "out"), to, numel_of(x), 0), "cast");
+    return clear_error();
+  });
+}
+
+// flint/capi.h:279, flint/capi.cc:620-624.
+int32_t fl_fill(fl_operators_t operators, fl_tensor_view_t tensor_h, float value) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &t = deref(tensor_h);
+    check_on_cuda(operators, t, "the tensor");
+    ElemKind kind;
+    if (!elem_kind_of(dtype_of(t), &kind)) invalid("fill: this library fills <float>, <float16> and <bfloat16> tensors");
+    require_kernels();
+    cuda_check(elementwise_fill(elem_view(t, "the tensor"), kind, numel_of(t), value, 0), "fill");
+    return clear_error();
+  });
+}
+
+// flint/capi.h:480-483, flint/capi.cc:226-252. `b` and `out` have `a`'s shape (a caller broadcasting
+// a smaller operand hands over an expanded view of it); one dtype.
+int32_t fl_add(fl_operators_t operators, fl_tensor_view_t a_h, fl_tensor_view_t b_h, fl_tensor_view_t out_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &a = deref(a_h);
+    const fl_tensor_view_impl_t &b = deref(b_h);
+    const fl_tensor_view_impl_t &out = deref(out_h);
+    check_on_cuda(operators, a, "the left operand");
+    check_on_cuda(operators, b, "the right operand");
+    check_on_cuda(operators, out, "out");
+    check_shape(b, a.shape, "the right operand");
+    check_shape(out, a.shape, "out");
+    ElemKind kind;
+    if (!elem_kind_of(dtype_of(a), &kind) || dtype_of(b) != dtype_of(a) || dtype_of(out) != dtype_of(a)) {
+      invalid("add: this library adds <float>, <float16> or <bfloat16> operands of one type");
+    }
+    require_kernels();
+    cuda_check(elementwise_add(elem_view(a, "the left operand"), elem_view(b, "the right operand"), elem_view(out, "out"),
+                               kind, numel_of(a), 0),
+               "add");
+    return clear_error();
+  });
+}
+
 // ============================ Part 2 ==========================================================
 
 int32_t fl_fp8_linear(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_view_t scales_h,
@@ -1107,7 +1421,10 @@ int32_t fl_sm100_ipc_export(fl_tensor_data_t data, void *handle_out) {
   return guard([&]() -> int32_t {
     fl_tensor_data_impl_t &d = deref(data);
     if (!handle_out) invalid("handle_out is null");
-    if (d.device != FL_DEVICE_CUDA || !d.owned) invalid("only device storage made by fl_tensor_data_create can be exported");
+    if (d.device != FL_DEVICE_CUDA || !d.owned || !d.resident) {
+      invalid("only device storage made by fl_tensor_data_create with FL_ALLOC_WEIGHT, of 2 MiB or more, can be exported "
+              "(memory of the stream-ordered pool has no inter-process handle)");
+    }
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is documented as 64 bytes");
     cudaIpcMemHandle_t h;
     cuda_check(cudaIpcGetMemHandle(&h, d.ptr), "cudaIpcGetMemHandle");
@@ -1624,8 +1941,14 @@ int32_t fl_tensor_data_borrow_device(void *device_ptr, fl_dtype_t dtype, int64_t
 int32_t fl_sm100_set_device(int32_t ordinal) {
   return guard([&]() {
     {
+      // One process drives one GPU: the kernel modules cache per-process facts about the device
+      // (its SM count, which kernels had their shared-memory limit raised), so a second device
+      // is refused here instead of failing at some later launch.
       std::lock_guard<std::mutex> lock(g_mutex);
-      if (g_dev.scratch || g_dev.status_host) invalid("the device has to be chosen before the first operation");
+      if (g_dev.device_in_use >= 0 && g_dev.device_in_use != ordinal) {
+        invalid("this process already runs on cuda device " + std::to_string(g_dev.device_in_use) +
+                "; the library drives one device per process and the device has to be chosen before the first operation");
+      }
     }
     cuda_check(cudaSetDevice(ordinal), "cudaSetDevice");
     {
@@ -1648,6 +1971,8 @@ int32_t fl_sm100_synchronize(int32_t *kernel_status) {
         *reinterpret_cast<volatile uint32_t *>(g_dev.status_host) = 0;
       }
     }
+    // fl_fp8_linear_static()'s kernels report through a word of their own, in the static array.
+    if (code == 0) code = take_static_status();
     if (kernel_status) *kernel_status = static_cast<int32_t>(code);
     if (code != 0) aborted("a kernel gave up on a bounded wait (status " + std::to_string(code) + ")");
     return clear_error();
@@ -1692,7 +2017,9 @@ int32_t fl_sm100_few_rows_plan(int32_t m, int32_t n, int32_t k, int32_t weight_b
   });
 }
 
-int64_t fl_sm100_launch_count(void) { return g_gemm_launches.load() + g_block_launches.load() + helper_launch_count(); }
+int64_t fl_sm100_launch_count(void) {
+  return g_gemm_launches.load() + g_block_launches.load() + helper_launch_count() + elementwise_launch_count();
+}
 
 
 }  // extern "C"
@@ -1740,9 +2067,48 @@ uint8_t *static_scratch_base() {
   return g_static_base[dev];
 }
 
+uint32_t take_static_status() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) return 0;
+  uint8_t *base;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    base = g_static_base[dev];
+  }
+  if (!base) return 0;  // no static call has run on this device
+  uint32_t code = 0;
+  cuda_check(cudaMemcpy(&code, base, sizeof(code), cudaMemcpyDeviceToHost), "reading the static status word");
+  if (code != 0) cuda_check(cudaMemsetAsync(base, 0, sizeof(uint32_t), 0), "clearing the static status word");
+  return code;
+}
+
 }  // namespace
 
 extern "C" {
+
+// Test hooks (declared in the header's last section). The first writes `code` into the static
+// array's status word as a kernel that gave up would; the second runs a one-warp kernel that waits,
+// with a limit of `polls` polls, on a barrier nothing ever arrives on and reports through the
+// library's ordinary status word. Neither faults nor hangs anything.
+int32_t fl_sm100_selftest_set_static_status(uint32_t code) {
+  return guard([&]() -> int32_t {
+    require_kernels();
+    uint8_t *base = static_scratch_base();
+    cuda_check(cudaMemcpy(base, &code, sizeof(code), cudaMemcpyHostToDevice), "writing the static status word");
+    return clear_error();
+  });
+}
+
+int32_t fl_sm100_selftest_wait_timeout(int32_t polls) {
+  return guard([&]() -> int32_t {
+    if (polls < 1 || polls > 4096) invalid("polls is between 1 and 4096");
+    require_kernels();
+    check_earlier_kernel_status();
+    cuda_check(selftest_wait_timeout(static_cast<uint32_t>(polls), status_word(), 0), "launching the wait self-test");
+    ++g_block_launches;
+    return clear_error();
+  });
+}
 
 int32_t fl_fp8_linear_static(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_view_t scales_h,
                              fl_tensor_view_t bias_h, fl_tensor_view_t residual_h, int32_t act,

@@ -25,8 +25,6 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include <cstdio>
-#include <cstdlib>
 #include <mutex>
 
 #include "ptx_sm100.cuh"
@@ -76,7 +74,6 @@ struct KernelParams {
   int out_col0;                // first destination column of this product
   int out_vector;  // the outputs' bases are 16-byte aligned: 16-byte stores; else 2-byte stores
   uint32_t *status;
-  int probe;  // development builds (-DFLSM100_PROBE) only: bit 0 skips the loads, bit 1 the epilogue
 };
 
 // CTAS == 2: a pair of CTAs (one cluster) shares a 256 x BLOCK_N tile through cta_group::2 UMMAs;
@@ -190,14 +187,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const uint32_t lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
   const bool scatter = p.num_out > 1;
-#ifdef FLSM100_PROBE
-  long long probe_c0 = 0;
-  unsigned long long probe_t0 = 0;
-  if ((p.probe & 16) && blockIdx.x == 0 && threadIdx.x == 0) {
-    probe_c0 = clock64();
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(probe_t0));
-  }
-#endif
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -255,16 +244,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             ok = false;
             break;
           }
-#ifdef FLSM100_PROBE
-          if (p.probe & 1) {  // timing probe: hand over the stage without loading it
-            if (leader) mbar_arrive(&full_bar[stage]);
-            if (++stage == STAGES) {
-              stage = 0;
-              phase ^= 1;
-            }
-            continue;
-          }
-#endif
           // Scale-factor tiles of this k block (NVFP4): kMmasPerStage consecutive 512-byte tiles
           // per 128-row group, addressed as rows of a (groups * sf_k_tiles, 512 byte) matrix. A
           // CTA loads the group of its own A rows and every group its tile's B columns touch (in
@@ -373,27 +352,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t sf_set = sf_it & 1;
             const uint32_t sfa_tmem = tmem_base + Cfg::kAccCols + sf_set * Cfg::kSfSetCols;
             const uint32_t sfb_tmem = sfa_tmem + Cfg::kSfaCols;
-#ifdef FLSM100_PROBE
-            if (!(p.probe & 8))  // timing probe: no scale-factor copies
-#endif
-            {
-              if (!mbar_wait(&sf_full_bar[sf_set], (sf_it >> 1) & 1, &abort_flag)) {
-                ok = false;
-                break;
-              }
-              tc_fence_after_sync();
+            if (!mbar_wait(&sf_full_bar[sf_set], (sf_it >> 1) & 1, &abort_flag)) {
+              ok = false;
+              break;
             }
+            tc_fence_after_sync();
 #pragma unroll
             for (int j = 0; j < kMmasPerStage; ++j) {
               if constexpr (CTAS == 2) {
                 umma_nvf4_ss_pair(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, (kb | j) != 0 ? 1u : 0u,
                                   sfa_tmem + j * 4, sfb_tmem + j * Cfg::kSfbColsPerMma + sfb_skip);
-#ifdef FLSM100_PROBE
-                if (p.probe & 64) {  // timing probe: the same instruction again into the other accumulator
-                  umma_nvf4_ss_pair(tmem_base + (acc ^ 1) * BLOCK_N, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc,
-                                    (kb | j) != 0 ? 1u : 0u, sfa_tmem + j * 4, sfb_tmem + j * Cfg::kSfbColsPerMma + sfb_skip);
-                }
-#endif
               } else {
                 umma_nvf4_ss(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, (kb | j) != 0 ? 1u : 0u,
                              sfa_tmem + j * 4, sfb_tmem + j * Cfg::kSfbColsPerMma + sfb_skip);
@@ -431,11 +399,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // ------------------------------------------------------------------ scale-factor copier (NVFP4)
     // One thread of the leader moves every stage's scale factors shared -> tensor memory, into
     // the set the MMAs are not reading, and hands the set over with a commit.
-    bool copies = lane == 0 && leader;
-#ifdef FLSM100_PROBE
-    if (p.probe & 8) copies = false;  // timing probe: no scale-factor copies
-#endif
-    if (copies) {
+    if (lane == 0 && leader) {
       constexpr uint64_t kStageStep = Cfg::kStageBytes >> 4;
       constexpr uint64_t kSfTileStep = kSfTileBytes >> 4;
       const uint64_t sfa_desc0 = umma_desc_sf(smem_u32(stage_sfa(0)));
@@ -459,17 +423,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t sfb_tmem = sfa_tmem + Cfg::kSfaCols;
 #pragma unroll
           for (int j = 0; j < kMmasPerStage; ++j) {
-#ifdef FLSM100_PROBE
-            if ((p.probe & 32) && j > 0) break;  // timing probe: a twelfth of the copies
-#endif
             if constexpr (CTAS == 2) {
               tmem_cp_sf_pair(sfa_tmem + j * 4, sfa_desc + j * kSfTileStep);
             } else {
               tmem_cp_sf(sfa_tmem + j * 4, sfa_desc + j * kSfTileStep);
             }
-#ifdef FLSM100_PROBE
-            if (p.probe & 32) break;
-#endif
 #pragma unroll
             for (int g = 0; g < Cfg::kSfbGroups; ++g) {
               const uint64_t d = sfb_desc + (g * kMmasPerStage + j) * kSfTileStep;
@@ -675,9 +633,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         uint32_t packed[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) packed[j] = pack16(x[2 * j], x[2 * j + 1], is_bf16);
-#ifdef FLSM100_PROBE
-        if (p.probe & 4) return;  // timing probe: no stores
-#endif
         if (!row_ok) return;
         // (In the scatter form the peers' copies are made by the pusher warps from this one.)
         {
@@ -704,11 +659,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
       // Tensor-memory loads run one chunk ahead of the arithmetic.
       uint32_t va[32], vb[32];
-#ifdef FLSM100_PROBE
-      const int chunks_run = (p.probe & 2) ? 0 : chunks;  // timing probe: release the accumulator unread
-#else
       const int chunks_run = chunks;
-#endif
       if (chunks_run > 0) tmem_ld_32x32(tacc, va);
 #pragma unroll 1
       for (int c = 0; c < chunks_run; c += 2) {
@@ -755,15 +706,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     tc_fence_after_sync();
     tmem_dealloc<CTAS>(tmem_base, Cfg::kTmemCols);
   }
-#ifdef FLSM100_PROBE
-  if ((p.probe & 16) && blockIdx.x == 0 && threadIdx.x == 0) {
-    unsigned long long t1;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-    const long long c1 = clock64();
-    printf("probe: %lld cycles in %llu ns = %.3f GHz\n", c1 - probe_c0, t1 - probe_t0,
-           double(c1 - probe_c0) / double(t1 - probe_t0));
-  }
-#endif
 }
 
 // ---- host side ------------------------------------------------------------------------------
@@ -935,10 +877,6 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
     return cudaErrorInvalidValue;
   }
   kp.status = a.status;
-  kp.probe = 0;
-#ifdef FLSM100_PROBE
-  if (const char *v = std::getenv("FLSM100_PROBE")) kp.probe = std::atoi(v);
-#endif
 
   // A pair of CTAs per 256-row tile halves the B bytes each SM pulls from L2; it needs two row
   // blocks to share the B tile between. Narrow outputs use the narrower single-CTA tile so that
@@ -953,12 +891,6 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
       *why = "scale-factor base is not 16-byte aligned";
       return cudaErrorInvalidValue;
     }
-#ifdef FLSM100_PROBE
-    if (const char *v = std::getenv("FLSM100_NVF4_BLOCK_N")) {  // development builds: the instruction's time against N
-      if (std::atoi(v) == 128) return launch_one<kKindNvf4, 128, 2>(a, kp, row_bytes, why);
-      if (std::atoi(v) == 64) return launch_one<kKindNvf4, 64, 2>(a, kp, row_bytes, why);
-    }
-#endif
     return pair ? launch_one<kKindNvf4, 192, 2>(a, kp, row_bytes, why) : launch_one<kKindNvf4, 192, 1>(a, kp, row_bytes, why);
   }
   const bool narrow = a.n <= 128 || skinny;

@@ -101,13 +101,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 constexpr uint32_t kWaitPollLimit = 1u << 20;
 
 // Waits for the phase with the given parity to complete. Returns false when it gave up, either
-// because the poll budget ran out or because another role raised the CTA's abort flag.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag) {
-  for (uint32_t polls = 0; polls < kWaitPollLimit; ++polls) {
+// because the poll budget (`limit` polls) ran out or because another role raised the CTA's abort flag.
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                                  uint32_t limit) {
+  for (uint32_t polls = 0; polls < limit; ++polls) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((polls & 0x3ff) == 0x3ff && *abort_flag != 0) return false;
   }
   return false;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag) {
+  return mbar_wait_limited(bar, parity, abort_flag, kWaitPollLimit);
 }
 
 // ---- TMA ---------------------------------------------------------------------------------

@@ -93,6 +93,17 @@ def lib() -> ctypes.CDLL:
     L.fl_tensor_view_create.argtypes = [V, POINTER(c_int32), POINTER(c_int32), c_int32, c_int64, POINTER(V)]
     L.fl_tensor_view_destroy.argtypes = [V]; L.fl_tensor_view_destroy.restype = None
     L.fl_transfer.argtypes = [V, V, V]
+    L.fl_transfer_async.argtypes = [V, c_int32, POINTER(V), POINTER(V)]; L.fl_transfer_async.restype = c_int32
+    L.fl_transfer_wait.argtypes = [V]; L.fl_transfer_wait.restype = c_int32
+    L.fl_transfer_wait_sync.argtypes = [V]; L.fl_transfer_wait_sync.restype = c_int32
+    L.fl_transfer_destroy.argtypes = [V]; L.fl_transfer_destroy.restype = None
+    L.fl_sm100_transfer_to_host_async.argtypes = [V, V, POINTER(V)]; L.fl_sm100_transfer_to_host_async.restype = c_int32
+    for name in ("fl_copy", "fl_cast"):
+        getattr(L, name).argtypes = [V, V, V]; getattr(L, name).restype = c_int32
+    L.fl_fill.argtypes = [V, V, ctypes.c_float]; L.fl_fill.restype = c_int32
+    L.fl_add.argtypes = [V, V, V, V]; L.fl_add.restype = c_int32
+    L.fl_sm100_selftest_wait_timeout.argtypes = [c_int32]; L.fl_sm100_selftest_wait_timeout.restype = c_int32
+    L.fl_sm100_selftest_set_static_status.argtypes = [ctypes.c_uint32]; L.fl_sm100_selftest_set_static_status.restype = c_int32
     L.fl_fp8_available.argtypes = [c_int32, POINTER(c_int32)]
     L.fl_nvfp4_available.argtypes = [c_int32, POINTER(c_int32)]
     L.fl_fp8_matmul.argtypes = [V, V, V, V]
@@ -154,6 +165,14 @@ def set_device(ordinal: int) -> None:
 def synchronize() -> None:
     status = c_int32(0)
     check(lib().fl_sm100_synchronize(byref(status)))
+
+
+class AllocHint:
+    """fl_alloc_hint_t (flint/capi.h:137-147)."""
+    ACTIVATION = 0
+    WEIGHT = 1
+    OTHER = 2
+    TEMPORARY_WEIGHT = 3
 
 
 def gemm_timing(enable: bool) -> None:
@@ -228,10 +247,13 @@ class Tensor:
 
     # -- construction ---------------------------------------------------------------------
     @staticmethod
-    def empty(shape: Sequence[int], dtype: int, device: int = Device.CUDA) -> "Tensor":
+    def empty(shape: Sequence[int], dtype: int, device: int = Device.CUDA, hint: int = 0) -> "Tensor":
+        """Uninitialised storage and a contiguous view of it. On the device it comes from the
+        stream-ordered pool, except that `hint=AllocHint.WEIGHT` gives 2 MiB or more memory of its
+        own (the kind fl_sm100_ipc_export can share)."""
         numel = int(np.prod(shape)) if len(shape) else 1
         data = c_void_p()
-        check(lib().fl_tensor_data_create(device, dtype, max(numel, 1), 0, byref(data)))
+        check(lib().fl_tensor_data_create(device, dtype, max(numel, 1), int(hint), byref(data)))
         return Tensor._over(data, shape, _contiguous_strides(shape), 0, dtype, device, True)
 
     @staticmethod
@@ -323,6 +345,75 @@ class Tensor:
                 self._data = None
         except Exception:
             pass
+
+
+class Transfer:
+    """A copy that is still on its way (fl_transfer_t, flint/capi.h:71-73)."""
+
+    def __init__(self, handle: c_void_p, keepalive=None):
+        self._handle = handle
+        self._keepalive = keepalive
+
+    def wait(self) -> None:
+        """Orders the compute stream's later work behind the copy; the caller does not stop."""
+        check(lib().fl_transfer_wait(self._handle))
+
+    def wait_sync(self) -> None:
+        """Returns once the copy has finished."""
+        check(lib().fl_transfer_wait_sync(self._handle))
+
+    def __del__(self):
+        try:
+            if _lib is not None and self._handle:
+                _lib.fl_transfer_destroy(self._handle)
+                self._handle = None
+        except Exception:
+            pass
+
+
+def transfer_async(src: Tensor):
+    """fl_transfer_async (flint/capi.h:256-264): starts the upload of a page-locked host tensor and
+    returns (device tensor of the same shape, Transfer); wait on the transfer before using the tensor."""
+    data, handle = c_void_p(), c_void_p()
+    check(lib().fl_transfer_async(src.raw(), Device.CUDA, byref(data), byref(handle)))
+    dev = Tensor._over(data, src.shape, _contiguous_strides(src.shape), 0, src.dtype, Device.CUDA, True)
+    return dev, Transfer(handle, keepalive=src)
+
+
+def transfer_to_host_async(src: Tensor, dest: Tensor) -> Transfer:
+    """Starts the download of a contiguous device tensor into a page-locked host tensor behind the
+    work queued so far; `wait_sync()` on the result is when the host may read `dest`."""
+    handle = c_void_p()
+    check(lib().fl_sm100_transfer_to_host_async(src.raw(), dest.raw(), byref(handle)))
+    return Transfer(handle, keepalive=(src, dest))
+
+
+def copy(src: Tensor, dest: Tensor) -> Tensor:
+    check(lib().fl_copy(operators(), src.raw(), dest.raw()))
+    return dest
+
+
+def cast(x: Tensor, dtype: int, out: Optional[Tensor] = None) -> Tensor:
+    """fl_cast (flint/capi.h:249) between FLOAT, FLOAT16 and BFLOAT16."""
+    if out is None:
+        out = Tensor.empty(tuple(x.shape), dtype)
+    check(lib().fl_cast(operators(), x.raw(), out.raw()))
+    return out
+
+
+def fill(t: Tensor, value: float) -> Tensor:
+    check(lib().fl_fill(operators(), t.raw(), float(value)))
+    return t
+
+
+def add(a: Tensor, b: Tensor, out: Optional[Tensor] = None) -> Tensor:
+    """fl_add (flint/capi.h:483); `b` is expanded to `a`'s shape as a view first, as the Rust wrapper
+    does (waifu/src/flint/functional.rs:80-108)."""
+    if out is None:
+        out = Tensor.empty(tuple(a.shape), a.dtype)
+    bb = b if tuple(b.shape) == tuple(a.shape) else _broadcast_to(b, a)
+    check(lib().fl_add(operators(), a.raw(), bb.raw(), out.raw()))
+    return out
 
 
 def _fp8_result(a: Tensor, rows: int) -> Tensor:
@@ -424,7 +515,8 @@ def fp8_linear_scatter(a: Tensor, weight: Tensor, scales: Tensor, dests: Sequenc
 
 
 def ipc_export(t: Tensor) -> bytes:
-    """The 64-byte handle of a device tensor made by Tensor.empty(), for a peer process."""
+    """The 64-byte handle of a device tensor made by Tensor.empty(..., hint=AllocHint.WEIGHT) of
+    2 MiB or more, for a peer process."""
     buf = ctypes.create_string_buffer(64)
     check(lib().fl_sm100_ipc_export(t._data, buf))
     return bytes(buf.raw)

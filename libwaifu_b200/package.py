@@ -116,16 +116,23 @@ def read_safetensors(path: str) -> Tuple[Dict[str, StoredTensor], Dict[str, str]
 
 # ---- the pairing rules ------------------------------------------------------------------------
 
-def check_pairs(tensors: Dict[str, StoredTensor], weight_format: str) -> None:
+def check_pairs(tensors: Dict[str, StoredTensor], weight_format: str, quantized: Optional[Iterable[str]] = None) -> None:
     """What the reference's check_fp8_pairs enforces (tensor_file.rs:283-336), for each format: every
     quantized matrix has the scale tensors its format needs beside it, of the right type and shape.
     Run over a whole model, since a weight and its scale may sit in different files. A tensor whose
-    name merely ends in ".scale" is an ordinary tensor, as in the reference."""
+    name merely ends in ".scale" is an ordinary tensor, as in the reference.
+
+    NVFP4 codes are plain U8 bytes, which nothing tells apart from an ordinary uint8 tensor, so a
+    package of that format names its quantized matrices (`quantized`, the "quantized" list of the
+    file's metadata): each of them must be there with both companions. Without the list, every
+    ".block_scale" tensor and every F32[1] ".scale" beside a U8 matrix is followed to its codes."""
     if weight_format not in WEIGHT_FORMATS:
         raise PackageError(f"weight_format {weight_format!r} is not one of {WEIGHT_FORMATS}")
     for name, t in tensors.items():
-        if t.dtype != "F8_E4M3" or name.endswith(BLOCK_SCALE_SUFFIX):
+        if t.dtype != "F8_E4M3":
             continue
+        if weight_format == "nvfp4" and name.endswith(BLOCK_SCALE_SUFFIX):
+            continue  # the block scales of an nvfp4 weight; checked with their codes below
         if weight_format in ("float", "nvfp4"):
             raise PackageError(f"tensor {name!r} is float8_e4m3 in a package whose weight_format is {weight_format!r}")
         scale = tensors.get(name + SCALE_SUFFIX)
@@ -141,19 +148,33 @@ def check_pairs(tensors: Dict[str, StoredTensor], weight_format: str) -> None:
                     else "; one scale for the whole weight is weight_format fp8_tensor_scale")
             raise PackageError(f"tensor {name + SCALE_SUFFIX!r} is {scale.dtype}{list(scale.shape)}, and the scale of "
                                f"{name!r} has to be F32{list(want)} under {weight_format}{hint}")
-    if weight_format == "nvfp4":
-        for name, t in tensors.items():
-            if not name.endswith(BLOCK_SCALE_SUFFIX):
-                continue
-            base = name[:-len(BLOCK_SCALE_SUFFIX)]
-            codes, scale = tensors.get(base), tensors.get(base + SCALE_SUFFIX)
-            if codes is None or scale is None:
-                raise PackageError(f"{name!r} has no {base!r} and {base + SCALE_SUFFIX!r} beside it")
-            if t.dtype != "F8_E4M3" or codes.dtype != "U8" or scale.dtype != "F32" or scale.shape != (1,):
-                raise PackageError(f"the nvfp4 weight {base!r} is not U8 codes, F8_E4M3 block scales and an F32[1] scale")
-            if len(codes.shape) != 2 or t.shape != (codes.shape[0], codes.shape[1] * 2 // NVFP4_BLOCK):
-                raise PackageError(f"the nvfp4 weight {base!r} has codes {list(codes.shape)} and block scales "
-                                   f"{list(t.shape)}; the latter has to be [rows, k / 16] for codes [rows, k / 2]")
+    if weight_format != "nvfp4":
+        return
+    bases = set(quantized) if quantized is not None else set()
+    for name, t in tensors.items():
+        if name.endswith(BLOCK_SCALE_SUFFIX):
+            bases.add(name[:-len(BLOCK_SCALE_SUFFIX)])
+        elif name.endswith(SCALE_SUFFIX) and t.dtype == "F32" and t.shape == (1,):
+            base = tensors.get(name[:-len(SCALE_SUFFIX)])
+            if base is not None and base.dtype == "U8" and len(base.shape) == 2:
+                bases.add(name[:-len(SCALE_SUFFIX)])
+    for base in sorted(bases):
+        codes, block, scale = tensors.get(base), tensors.get(base + BLOCK_SCALE_SUFFIX), tensors.get(base + SCALE_SUFFIX)
+        if codes is None:
+            raise PackageError(f"the nvfp4 weight {base!r} has scales but no codes tensor {base!r}")
+        if block is None:
+            raise PackageError(f"the nvfp4 weight {base!r} has no {base + BLOCK_SCALE_SUFFIX!r} beside it")
+        if scale is None:
+            raise PackageError(f"the nvfp4 weight {base!r} has no {base + SCALE_SUFFIX!r} beside it")
+        if codes.dtype != "U8" or len(codes.shape) != 2:
+            raise PackageError(f"the codes of the nvfp4 weight {base!r} are {codes.dtype}{list(codes.shape)}, not a U8 matrix")
+        if block.dtype != "F8_E4M3":
+            raise PackageError(f"{base + BLOCK_SCALE_SUFFIX!r} is {block.dtype}, and block scales are F8_E4M3")
+        if scale.dtype != "F32" or scale.shape != (1,):
+            raise PackageError(f"{base + SCALE_SUFFIX!r} is {scale.dtype}{list(scale.shape)}, and the global scale is F32[1]")
+        if block.shape != (codes.shape[0], codes.shape[1] * 2 // NVFP4_BLOCK) or (codes.shape[1] * 2) % NVFP4_BLOCK:
+            raise PackageError(f"the nvfp4 weight {base!r} has codes {list(codes.shape)} and block scales "
+                               f"{list(block.shape)}; the latter has to be [rows, k / 16] for codes [rows, k / 2]")
 
 
 # ---- the exporter's arithmetic ----------------------------------------------------------------
@@ -290,9 +311,11 @@ def quantize_matrices(tensors: Dict[str, np.ndarray], names: Iterable[str], weig
 
 def write_package(path: str, tensors: Dict[str, np.ndarray], names: Iterable[str], weight_format: str) -> None:
     """One safetensors file whose metadata carries the manifest's `weight_format`."""
+    names = [n for n in names]
     stored = quantize_matrices(tensors, names, weight_format)
-    check_pairs(stored, weight_format)
-    write_safetensors(path, stored, {"weight_format": weight_format})
+    quantized = sorted(n for n in names if n in tensors) if weight_format != "float" else []
+    check_pairs(stored, weight_format, quantized)
+    write_safetensors(path, stored, {"weight_format": weight_format, "quantized": json.dumps(quantized)})
 
 
 def read_package(path: str, weight_format: Optional[str] = None) -> Tuple[Dict[str, StoredTensor], str]:
@@ -300,7 +323,13 @@ def read_package(path: str, weight_format: Optional[str] = None) -> Tuple[Dict[s
     metadata, else "float")."""
     tensors, metadata = read_safetensors(path)
     fmt = weight_format or metadata.get("weight_format", "float")
-    check_pairs(tensors, fmt)
+    quantized = None
+    if "quantized" in metadata:
+        try:
+            quantized = [str(n) for n in json.loads(metadata["quantized"])]
+        except (ValueError, TypeError):
+            raise PackageError(f"{path}: the metadata's list of quantized matrices is not a JSON list") from None
+    check_pairs(tensors, fmt, quantized)
     return tensors, fmt
 
 
@@ -311,6 +340,11 @@ def upload_linear(tensors: Dict[str, StoredTensor], name: str, weight_format: st
     FL_ALLOC_WEIGHT hint): fp8_tensor_scale / fp8_row_scale -> (codes, scales) for fl_fp8_matmul /
     fl_fp8_linear; nvfp4 -> (codes, block_scales, global_scale) for fl_nvfp4_linear."""
     from . import flint as F
+    needs = {"fp8_tensor_scale": (SCALE_SUFFIX,), "fp8_row_scale": (SCALE_SUFFIX,),
+             "nvfp4": (BLOCK_SCALE_SUFFIX, SCALE_SUFFIX)}.get(weight_format, ())
+    for suffix in ("",) + needs:
+        if name + suffix not in tensors:
+            raise PackageError(f"{name + suffix!r} is not in the package")
     t = tensors[name]
     if weight_format in ("fp8_tensor_scale", "fp8_row_scale"):
         codes = F.Tensor.from_numpy(t.array, F.DType.FP8E4M3, F.Device.CUDA)

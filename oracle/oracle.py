@@ -24,11 +24,24 @@ ACT_NONE = 0
 ACT_GELU_TANH = 1
 
 
+def reference_dir():
+    """The reference checkout to compile the checker from: $FLINT_REFERENCE_DIR, else a directory
+    named `reference` beside this repository; None where neither exists (the prebuilt library under
+    _ref/, if any, is then used as it is)."""
+    named = os.environ.get("FLINT_REFERENCE_DIR")
+    candidates = [named] if named else [os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for c in candidates:
+        if c and os.path.isfile(os.path.join(c, "flint", "capi.h")):
+            return os.path.abspath(c)
+    return None
+
+
 def build(ref: bool = True) -> None:
     """Compile the C restatement, and the reference's CPU library where its checkout exists."""
     subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
-    if ref and os.path.isdir(os.environ.get("FLINT_REFERENCE_DIR", "/root/reference")):
-        subprocess.run(["make", "-s", "-C", HERE, "ref", "-j8"], check=True)
+    ref_dir = reference_dir() if ref else None
+    if ref_dir:
+        subprocess.run(["make", "-s", "-C", HERE, "ref", "-j8", f"REF={ref_dir}"], check=True)
 
 
 _lib = None

@@ -157,3 +157,68 @@ def test_no_gpu_means_a_loud_failure_not_a_fallback(flint):
     assert not flint.fp8_available(flint.Device.CUDA)
     with pytest.raises(flint.FlintError):
         flint.Tensor.empty((2, 2), flint.DType.FLOAT16, flint.Device.CUDA)
+
+
+def _prototypes(text):
+    """name -> 'return-type name(parameters)' with whitespace squeezed, of every FLAPI declaration."""
+    text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
+    text = re.sub(r"//[^\n]*", " ", text)
+    out = {}
+    for m in re.finditer(r"FLAPI\s+([^;{]+?\b(fl_\w+)\s*\([^;{]*?\))\s*;", text, flags=re.S):
+        proto = re.sub(r"\s+", " ", m.group(1)).strip()
+        proto = re.sub(r"\(\s+", "(", proto)
+        proto = re.sub(r"\s+\)", ")", proto)
+        proto = re.sub(r",\s*\)", ")", proto)
+        out[m.group(2)] = proto
+    return out
+
+
+def test_part_one_prototypes_equal_the_reference_headers(oracle):
+    """Every declaration of the header's first part is, token for token, the declaration of the same
+    name in the reference's flint/capi.h (return type, parameter types and parameter names)."""
+    ref_dir = oracle.reference_dir()
+    if not ref_dir:
+        pytest.skip("no reference checkout here")
+    ours_text = open(os.path.join(ROOT, "include", "flint_sm100.h")).read()
+    part1 = ours_text.split("Part 2: additive entry points")[0]
+    ours = _prototypes(part1)
+    theirs = _prototypes(open(os.path.join(ref_dir, "flint", "capi.h")).read())
+    assert len(ours) >= 25
+    for name, proto in ours.items():
+        assert name in theirs, f"{name} is in part 1 but the reference does not declare it"
+        assert proto == theirs[name], f"{name}:\n  ours      {proto}\n  reference {theirs[name]}"
+    # the part-1 enum values, against the reference's own enumerators
+    ref_text = open(os.path.join(ref_dir, "flint", "capi.h")).read()
+    for enumerator in re.findall(r"\b(FL_(?:DTYPE|DEVICE|ALLOC|MASK)_\w+)\s*=\s*(\d+)", part1):
+        m = re.search(r"\b%s\s*=\s*(\d+)" % enumerator[0], ref_text)
+        if m:  # the two additive dtypes have no counterpart
+            assert m.group(1) == enumerator[1], enumerator
+    for code in re.findall(r"#define\s+(FL_\w+)\s+(\w+)", part1):
+        m = re.search(r"#define\s+%s\s+(\w+)" % code[0], ref_text)
+        if m:
+            assert int(m.group(1), 0) == int(code[1], 0), code
+
+
+def test_storage_bound_is_the_reference_one(flint):
+    # flint/tensor.h:41: storage holds at most 2^30 elements; refused before anything is allocated
+    L = flint.lib()
+    data = c_void_p()
+    assert L.fl_tensor_data_create(flint.Device.CPU, flint.DType.UINT8, (1 << 30) + 1, 0, byref(data)) == flint.FL_ERROR_INVALID_ARG
+    assert b"too many elements" in L.fl_get_last_error_message()
+    assert L.fl_tensor_data_create(flint.Device.CPU, flint.DType.UINT8, 16, 9, byref(data)) == flint.FL_ERROR_INVALID_ARG
+
+
+def test_asynchronous_copy_refuses_every_direction_but_its_own(flint):
+    # flint/cuda/to_device.cc:143-160: page-locked host memory to the GPU, nothing else
+    F, L = flint, flint.lib()
+    src = cpu(F, np.zeros((4, 4), np.float32), F.DType.FLOAT)
+    dest, handle = c_void_p(), c_void_p()
+    assert L.fl_transfer_async(src.raw(), F.Device.CUDA, byref(dest), byref(handle)) == F.FL_ERROR_INVALID_ARG
+    assert b"from cuda-host to cuda, not from cpu to cuda" in L.fl_get_last_error_message()
+    assert L.fl_transfer_async(src.raw(), F.Device.CUDA, None, byref(handle)) == F.FL_ERROR_INVALID_ARG
+    assert L.fl_transfer_wait(None) == F.FL_ERROR_INVALID_ARG
+    L.fl_transfer_destroy(None)
+    # the elementwise operators want every view on the operators' device
+    assert L.fl_add(None, src.raw(), src.raw(), src.raw()) == F.FL_ERROR_INVALID_ARG
+    assert L.fl_cast(c_void_p(1), src.raw(), src.raw()) == F.FL_ERROR_INVALID_ARG
+    assert b"not on the operators' device" in L.fl_get_last_error_message()

@@ -141,3 +141,38 @@ def test_step_size_properties(flint, oracle):
     assert np.array_equal(oracle.widen(got2, True), 2.0 * oracle.widen(got, True))
     want = oracle.attention(q[1:, 5:6], k[1:, 5:6], v[1:, 5:6], False, True)
     check(oracle, got[1:, 5:6], want, True, "one head of the step")
+
+
+def test_broadcast_views_are_refused_or_read_correctly(flint, oracle):
+    """A stride of 0 over an extent above 1 (one k shared by both batch rows through an expanded
+    view): q, k and out go through tensor maps, which cannot repeat a dimension, so such a view is
+    refused with the reason; v, which is gathered with its true strides, may repeat, and a
+    dimension of extent 1 may carry any stride."""
+    F = flint
+    rng = np.random.default_rng(31)
+    n, h, L, S, d = 2, 2, 40, 72, 64
+    q, k, v = make(oracle, rng, n, h, h, L, S, d, True)
+    bf = F.DType.BFLOAT16
+    tq = F.Tensor.from_numpy(q, bf, F.Device.CUDA)
+    tk = F.Tensor.from_numpy(k, bf, F.Device.CUDA)
+    k1 = F.Tensor.from_numpy(k[:1].copy(), bf, F.Device.CUDA)
+    v1 = F.Tensor.from_numpy(v[:1].copy(), bf, F.Device.CUDA)
+    k_shared = k1.view_as((n, h, S, d), (0, S * d, d, 1))
+    v_shared = v1.view_as((n, h, S, d), (0, S * d, d, 1))
+    with pytest.raises(F.FlintError) as e:
+        F.attention(tq, k_shared, v_shared, F.MaskType.NONE, 0)
+    assert e.value.code == F.FL_ERROR_INVALID_ARG and "stride of 0" in e.value.message
+    out_shared = F.Tensor.empty((1, h, L, d), bf).view_as((n, h, L, d), (0, L * d, d, 1))
+    tv = F.Tensor.from_numpy(v, bf, F.Device.CUDA)
+    with pytest.raises(F.FlintError):
+        F.attention(tq, tk, tv, F.MaskType.NONE, 0, out_shared)
+    # v alone shared between the batch rows: read with its true strides
+    got = F.attention(tq, tk, v_shared, F.MaskType.NONE, 0).numpy()
+    F.synchronize()
+    v_rep = np.concatenate([v[:1], v[:1]], axis=0)
+    check(oracle, got, oracle.attention(q, k, v_rep, False, True), True, "v shared by the batch rows")
+    # extent 1 with stride 0 indexes nothing
+    q1 = F.Tensor.from_numpy(q[:1].copy(), bf, F.Device.CUDA).view_as((1, h, L, d), (0, L * d, d, 1))
+    got1 = F.attention(q1, k1, v1, F.MaskType.NONE, 0).numpy()
+    F.synchronize()
+    check(oracle, got1, oracle.attention(q[:1], k[:1], v[:1], False, True), True, "batch of one, stride 0")

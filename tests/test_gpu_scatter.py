@@ -64,10 +64,15 @@ def _worker(rank, world, port):
         codes, scales = O.quantize_fp8_rows((rng.standard_normal((n, k)) * 0.02).astype(np.float32))
         a, b = sharding.column_shard(n, world, rank, 128)
         bf = F.DType.BFLOAT16
-        own = F.Tensor.empty((m, n), bf)
+        # storage another process can map is a weight's own memory, 2 MiB or more: the (m, n) matrix
+        # is the head of such a block
+        big_rows = 2056
+        own_block = F.Tensor.empty((big_rows, n), bf, hint=F.AllocHint.WEIGHT)
+        own = own_block.view_as((m, n), (n, 1))
         handles = [None] * world
-        dist.all_gather_object(handles, F.ipc_export(own))
-        dests = [own] + [F.ipc_import(handles[r], (m, n), bf) for r in range(world) if r != rank]
+        dist.all_gather_object(handles, F.ipc_export(own_block))
+        peers = [F.ipc_import(handles[r], (big_rows, n), bf) for r in range(world) if r != rank]
+        dests = [own] + [p.view_as((m, n), (n, 1)) for p in peers]
         F.fp8_linear_scatter(F.Tensor.from_numpy(x, bf), F.Tensor.from_numpy(codes[a:b], F.DType.FP8E4M3),
                              F.Tensor.from_numpy(scales[a:b], F.DType.FLOAT), dests, a, None, None, F.ACT_GELU_TANH)
         flag = torch.zeros(1, device="cuda")
@@ -76,7 +81,7 @@ def _worker(rank, world, port):
         got = own.numpy()
         check(O, got, O.fp8_linear(x, codes, scales, None, None, O.ACT_GELU_TANH), True, what=f"rank {rank}")
         dist.barrier()
-        del dests
+        del dests, peers
     finally:
         dist.destroy_process_group()
 

@@ -278,3 +278,44 @@ def test_swiglu_restatement_against_the_reference_operator(oracle):
     assert np.mean(got == want) >= 0.995
     g, w = oracle.widen(got, True), oracle.widen(want, True)
     assert np.all(np.abs(g - w) <= np.maximum(np.abs(w), 2.0 ** -14) * 2.0 ** -7 * 1.01)
+
+
+def test_reciprocal_form_of_the_activation_quantiser_against_the_exporters_division(oracle):
+    """The dynamic activation quantiser multiplies by one reciprocal per row where the exporter's
+    rule (tools/model_writer.py:164-174) divides every element by the scale. The reference never
+    narrows an activation, so nothing of its own pins this choice; this states how far the two
+    forms are apart on the benchmark's distribution. The scales are identical. The codes differ only
+    at exact ties: where x / s is exactly the midpoint of two codes (which bf16 inputs and a scale
+    with few significant bits produce), the division rounds the tie to even and the product with the
+    rounded reciprocal, one float32 step above or below the midpoint, rounds to the nearer code. On
+    this sample that is about one code in a thousand, all in the few rows whose scale makes ties,
+    each by one code step; a product taken with either set of codes agrees to within the path's
+    own tolerance. Both are correct roundings of x / s to within half a step plus one float32 ulp."""
+    rng = np.random.default_rng(99)
+    m, k = 256, 3072
+    x16 = oracle.narrow(rng.standard_normal((m, k)).astype(np.float32), True)
+    x = oracle.widen(x16, True)
+    codes, scales = oracle.quantize_fp8_act(x16, True)
+    amax = np.abs(x).max(axis=1)
+    s = (amax / np.float32(448.0)).astype(np.float32)
+    assert np.array_equal(scales, s)
+    encode = oracle.lib().fo_e4m3_encode
+    rows = range(0, m, 16)
+    quotient = np.stack([(x[r] / s[r]).astype(np.float32) for r in rows])
+    div = np.array([[encode(float(v)) for v in row] for row in quotient], np.uint8)
+    rec = codes[0:m:16]
+    differ = div != rec
+    frac = differ.mean()
+    assert 0 < frac <= 2e-3, f"{frac:.2e} of the codes differ between the two forms"
+    # where they differ it is by one step of the code, never more (sign-magnitude codes of one sign) ...
+    assert np.all(np.abs(div[differ].astype(np.int16) - rec[differ].astype(np.int16)) == 1)
+    # ... and only at exact ties: the quotient has at most five significant bits there
+    tie = quotient[differ].astype(np.float64)
+    mant, _ = np.frexp(np.abs(tie))
+    assert np.all(mant * 32 == np.floor(mant * 32)), "a code differs away from an exact tie"
+    # a product taken with either set of codes is the same to within the path's tolerance
+    w = (rng.standard_normal((64, k)) * 0.02).astype(np.float32)
+    a = oracle.decode_e4m3(div).astype(np.float64) @ w.T.astype(np.float64)
+    b = oracle.decode_e4m3(rec).astype(np.float64) @ w.T.astype(np.float64)
+    assert oracle.rel_l2(a, b) <= 5e-3
+    print(f"reciprocal vs division: {int(differ.sum())} of {differ.size} codes differ ({frac:.2e})")

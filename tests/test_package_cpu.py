@@ -111,3 +111,39 @@ def test_pairing_rules(tmp_path):
     bad.write_bytes(b"\x10\x00\x00\x00\x00\x00\x00\x00not json at all!")
     with pytest.raises(P.PackageError, match="not JSON"):
         P.read_safetensors(str(bad))
+
+
+def test_pairing_rules_catch_mis_named_and_lost_companions(tmp_path):
+    """A ".block_scale" name excuses an F8_E4M3 tensor from its ".scale" only in an nvfp4 package, and
+    an nvfp4 weight whose block scales or global scale were lost or renamed is caught by name."""
+    rng = np.random.default_rng(85)
+    w = randn(rng, (16, 32), 0.02)
+    codes, row = P.quantize_fp8_row_scale(w)
+    f8 = P.StoredTensor("F8_E4M3", codes)
+    for fmt in ("fp8_tensor_scale", "fp8_row_scale"):
+        with pytest.raises(P.PackageError, match="no 'w.block_scale.scale' beside it"):
+            P.check_pairs({"w.block_scale": f8}, fmt)
+    packed, block, g = P.quantize_nvfp4(w)
+    nv = {"w": P.StoredTensor("U8", packed), "w.block_scale": P.StoredTensor("F8_E4M3", block), "w.scale": P.StoredTensor("F32", g)}
+    # the block scales lost: found through the F32[1] scale beside the U8 matrix, and through the list
+    lost = {k: v for k, v in nv.items() if k != "w.block_scale"}
+    with pytest.raises(P.PackageError, match="no 'w.block_scale' beside it"):
+        P.check_pairs(lost, "nvfp4")
+    with pytest.raises(P.PackageError, match="no 'w.block_scale' beside it"):
+        P.check_pairs({"w": nv["w"]}, "nvfp4", ["w"])
+    with pytest.raises(P.PackageError, match="no 'w.scale' beside it"):
+        P.check_pairs({k: v for k, v in nv.items() if k != "w.scale"}, "nvfp4", ["w"])
+    with pytest.raises(P.PackageError, match="block scales are F8_E4M3"):
+        P.check_pairs(dict(nv, **{"w.block_scale": P.StoredTensor("U8", block)}), "nvfp4")
+    with pytest.raises(P.PackageError, match="no codes tensor"):
+        P.check_pairs({k: v for k, v in nv.items() if k != "w"}, "nvfp4")
+    # the written file names its quantized matrices, so a reader notices a companion that went missing
+    path = str(tmp_path / "nv.safetensors")
+    P.write_package(path, {"w": w, "b": randn(rng, (16,), 0.01)}, ["w"], "nvfp4")
+    tensors, fmt = P.read_package(path)
+    assert fmt == "nvfp4" and set(tensors) == {"w", "w.block_scale", "w.scale", "b"}
+    stored, meta = P.read_safetensors(path)
+    del stored["w.block_scale"], stored["w.scale"]
+    P.write_safetensors(path, stored, meta)
+    with pytest.raises(P.PackageError, match="no 'w.block_scale' beside it"):
+        P.read_package(path)

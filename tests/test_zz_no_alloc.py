@@ -2,10 +2,12 @@
 whole card is budgeted to resident weights, or an allocation's device-wide stall is not
 affordable mid-pass) -- against fl_fp8_linear, through the C ABI.
 
-Both run the same quantiser and the same GEMM, one over the library's growable arena and one over
-the fixed array compiled into the library, so their outputs must be identical bit for bit. Two
-calls in a row with different shapes check that the array, which keeps the previous call's
-contents, is not read where this call did not write it. The file is named to be collected last."""
+From five rows on both run the same quantiser and the same GEMM, one over the library's growable
+arena and one over the fixed array compiled into the library, so their outputs must be identical
+bit for bit. Two calls in a row with different shapes check that the array, which keeps the
+previous call's contents, is not read where this call did not write it. A call at the array's
+full size checks the property the entry point exists for: the card's free memory does not move.
+The file is named to be collected last."""
 import numpy as np
 import pytest
 
@@ -61,3 +63,46 @@ def test_static_entry_point_refuses_what_does_not_fit(flint, oracle):
         F.fp8_linear_static(rows, F.Tensor.empty((8, 16), F.DType.FP8E4M3), sd, None, None, F.ACT_NONE,
                             F.Tensor.empty((65552, 8), bf))
     assert e.value.code == F.FL_ERROR_INVALID_ARG and "rows exceed" in e.value.message
+
+
+def test_static_entry_point_with_a_few_rows_matches_the_oracle(flint, oracle):
+    """For one to four rows fl_fp8_linear takes its few-row kernel, whose summation order differs;
+    the static entry point stays on the tile path, so here it is held to the oracle instead."""
+    F = flint
+    rng = np.random.default_rng(2025)
+    bf = F.DType.BFLOAT16
+    m, n, k = 2, 264, 1024
+    x, codes, scales, bias, res = case(oracle, rng, m, n, k)
+    out = F.Tensor.empty((m, n), bf)
+    F.fp8_linear_static(dev(F, x, bf), dev(F, codes, F.DType.FP8E4M3), dev(F, scales, F.DType.FLOAT), dev(F, bias, bf),
+                        dev(F, res, bf), F.ACT_GELU_TANH, out)
+    got = out.numpy()
+    F.synchronize()
+    check_parity(oracle, got, oracle.fp8_linear(x, codes, scales, bias, res, F.ACT_GELU_TANH), True, what="static 2 rows")
+
+
+def test_static_entry_point_leaves_the_cards_free_memory_alone(flint, oracle):
+    """A call that fills the whole static array (m * k = 16 Mi elements, more than any call this
+    file made before) between two readings of cudaMemGetInfo: every operand and the output exist
+    before the first reading, so any byte the entry point allocated would show."""
+    import torch
+    F = flint
+    bf = F.DType.BFLOAT16
+    m, n, k = 4096, 256, 4096
+    rng = np.random.default_rng(2026)
+    x = oracle.narrow(randn(rng, (m, k)), True)
+    codes, scales = oracle.quantize_fp8_rows(randn(rng, (n, k), 0.02))
+    xd, cd, sd = dev(F, x, bf), dev(F, codes, F.DType.FP8E4M3), dev(F, scales, F.DType.FLOAT)
+    out = F.Tensor.empty((m, n), bf)
+    small = F.Tensor.empty((8, n), bf)
+    F.fp8_linear_static(xd.view_as((8, k), (k, 1)), cd, sd, None, None, F.ACT_NONE, small)  # first call: kernels loaded
+    F.synchronize()
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    F.fp8_linear_static(xd, cd, sd, None, None, F.ACT_NONE, out)
+    F.synchronize()
+    free_after = torch.cuda.mem_get_info()[0]
+    assert free_after == free_before, f"free device memory moved by {free_before - free_after} bytes across the call"
+    got = out.numpy()
+    rows = slice(0, 64)
+    check_parity(oracle, got[rows], oracle.fp8_linear(x[rows], codes, scales, None, None, 0), True, what="static, full array")
