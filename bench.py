@@ -57,8 +57,24 @@ NOMINAL_PEAK = {"fp8": 4500.0, "nvfp4": 9000.0}   # dense TFLOP/s, NVIDIA's B200
 PEAK_MULT = {"fp8": 2.0, "nvfp4": 4.0}            # relative to the measured bf16 cuBLAS throughput
 FALLBACK_BF16_TFLOPS = 1590.0
 
-# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch from the committed ncu captures
-# (profiles/), keyed by workload; None until a capture of that workload exists.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, copied from the
+# committed ncu captures (profiles/); a bench run measures none of this itself, and the line says
+# so (`traffic_source`). None until a capture of that workload exists.
+NCU_TRAFFIC_SOURCE = {
+    "c2_mlp": "profiles/gemm_tn_kernel_fp8_c2_mlp.md",
+    "c1_linear": "profiles/gemm_tn_kernel_fp8_c2_mlp.md",
+    "c3_nvfp4_qkv": "profiles/gemm_tn_kernel_nvfp4_c3_qkv.md",
+    "skinny_decode": "profiles/skinny_fp8_kernel_decode_1x16384x3072.md",
+    "attention_step": "profiles/attention_kernel_denoise_step.md",
+}
+
+
+def traffic_fields(workload):
+    src = NCU_TRAFFIC_SOURCE.get(workload)
+    return {"traffic": NCU_TRAFFIC_BYTES.get(workload),
+            "traffic_source": (f"an earlier ncu capture summarised in {src}; not measured by this run" if src else None)}
+
+
 NCU_TRAFFIC_BYTES = {
     "c2_mlp": (51.7e6 + 55.0e6 + 164.1e6 + 12.0e6) / 2,  # mean of the up and the down launch
     "c1_linear": 22.1e6,                                 # the bf16 output stays dirty in L2
@@ -154,6 +170,33 @@ class ClockSampler(threading.Thread):
         reasons = sorted(set().union(*[s[3] for s in self.samples]))
         return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(s[1] for s in self.samples),
                 "reasons": reasons, "samples": len(self.samples), "power_w_max": max(watts)}
+
+
+def bind_to_gpu_numa_node(local_index):
+    """Best effort: runs this process on the CPUs of the NUMA node its GPU hangs off, so that the
+    page-locked buffers allocated afterwards are local to the GPU's PCIe root (eight ranks copying
+    through one socket's memory is what limits end-to-end scaling). Returns a short description."""
+    try:
+        import torch
+        props = torch.cuda.get_device_properties(local_index)
+        bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return "the GPU reports no NUMA node; not bound"
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            text = f.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & set(os.sched_getaffinity(0))
+        if not allowed:
+            return f"NUMA node {node} has no CPU this process may use; not bound"
+        os.sched_setaffinity(0, allowed)
+        return f"pinned buffers allocated from NUMA node {node} ({len(allowed)} CPUs), the GPU's own"
+    except Exception as e:  # no sysfs, no permission: the run goes on unbound
+        return f"not bound ({type(e).__name__})"
 
 
 def measured_peaks(clocks=None):
@@ -370,21 +413,26 @@ def run_ours(args, wl):
                 dist.all_reduce(flag)
             y_result = y_own
 
-    def step(i, x_override=None):
+    def step(i, x_override=None, alloc=False):
+        """One step on operand set i. `alloc`: the outputs are allocated by the call, as the
+        reference's wrapper allocates `out` for every linear (waifu/src/flint/functional.rs:655-680),
+        and the last one is returned; otherwise they land in buffers made once."""
         if nsplit:
             nsplit_step()
-            return
+            return None
         x, layers, bias = operand_sets[i % sets]
         if x_override is not None:
             x = x_override
+        o = [None] * len(layers) if alloc else outs
+        if x_override is not None and x.shape[0] != m and not alloc:
+            raise ValueError("a row chunk needs per-call outputs")
         if wl["kind"] == "nvfp4":
             codes, sf, g = layers[0]
-            F.nvfp4_linear(x, codes, sf, g, None, None, F.ACT_NONE, outs[0])
-        elif len(layers) == 2:
-            F.fp8_linear(x, layers[0][0], layers[0][1], None, None, F.ACT_GELU_TANH, outs[0])
-            F.fp8_linear(outs[0], layers[1][0], layers[1][1], None, x, F.ACT_NONE, outs[1])
-        else:
-            F.fp8_linear(x, layers[0][0], layers[0][1], bias, None, F.ACT_NONE, outs[0])
+            return F.nvfp4_linear(x, codes, sf, g, None, None, F.ACT_NONE, o[0])
+        if len(layers) == 2:
+            h = F.fp8_linear(x, layers[0][0], layers[0][1], None, None, F.ACT_GELU_TANH, o[0])
+            return F.fp8_linear(h, layers[1][0], layers[1][1], None, x, F.ACT_NONE, o[1])
+        return F.fp8_linear(x, layers[0][0], layers[0][1], bias, None, F.ACT_NONE, o[0])
 
     def barrier():
         if dist is not None:
@@ -431,13 +479,69 @@ def run_ours(args, wl):
     sampler.stop_flag.set()
     sampler.join(timeout=5)
 
+    # ---- the same K steps with every output allocated by its call (the reference wrapper's way) ----
+    alloc_check = None
+    if not nsplit:
+        for i in range(3):
+            step(i, alloc=True)
+        barrier()
+        e0.record()
+        for i in range(args.steps):
+            step(args.warmup + i, alloc=True)
+        e1.record()
+        barrier()
+        alloc_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+        alloc_check = {"ms_per_step": alloc_ms, "value": work_units * flops_per_step(wl) / (alloc_ms * 1e-3) / 1e12,
+                       "ratio_to_preallocated": ms_step / alloc_ms,
+                       "what": "out allocated per call by fl_tensor_data_create (stream-ordered pool) and destroyed after, "
+                               "as waifu/src/flint/functional.rs:655-680 does"}
+
+    # ---- a second of back-to-back steps: the power-capped regime a 20-step region cannot show ------
+    sustained = None
+    if not nsplit and args.sustained_seconds > 0:
+        n_sus = max(args.steps, int(args.sustained_seconds * 1e3 / ms_step) + 1)
+        sus_sampler = ClockSampler(local)
+        sus_sampler.start()
+        barrier()
+        e0.record()
+        for i in range(n_sus):
+            step(i)
+        e1.record()
+        barrier()
+        sus_ms = max_over_ranks(e0.elapsed_time(e1) / n_sus)
+        F.gemm_timing(True)
+        F.gemm_timing_read()
+        for i in range(n_sus):
+            step(i)
+        sus_gemm_ms, sus_gemm_launches = F.gemm_timing_read()
+        F.gemm_timing(False)
+        sus_sampler.stop_flag.set()
+        sus_sampler.join(timeout=5)
+        sus_clocks = sus_sampler.summary()
+        sus_bf16, _, sus_kind = measured_peaks(sus_clocks)
+        sus_tflops = flops_per_step(wl) * n_sus / (sus_gemm_ms * 1e-3) / 1e12 if sus_gemm_ms > 0 else None
+        sustained = {"steps": n_sus, "ms_per_step": sus_ms, "value": work_units * flops_per_step(wl) / (sus_ms * 1e-3) / 1e12,
+                     "achieved": sus_tflops, "peak": PEAK_MULT[wl["kind"]] * sus_bf16,
+                     "frac": sus_tflops / (PEAK_MULT[wl["kind"]] * sus_bf16) if sus_tflops else None,
+                     "frac_of_nominal": sus_tflops / NOMINAL_PEAK[wl["kind"]] if sus_tflops else None,
+                     "peak_source": f"{PEAK_MULT[wl['kind']]:.0f} x bf16 cuBLAS, of {sus_kind}", "launches": sus_gemm_launches,
+                     "clocks": sus_clocks}
+
     # ---- end to end through the C ABI with host buffers ----------------------------------------
+    # The step's rows are cut into chunks and pipelined: every chunk's upload is started at once
+    # (fl_transfer_async: page-locked memory, the upload stream), chunk j's linears wait for chunk
+    # j's upload only (fl_transfer_wait), run while chunk j+1 is still crossing, and hand their
+    # result to the download stream (fl_sm100_transfer_to_host_async) while chunk j+1 computes.
+    # The host waits once, for the last download. Every device tensor of the step -- the uploaded
+    # rows, H, Y -- is allocated by the call that produces it and destroyed at the end of the step.
     k0 = wl["gemms"][0][1]
     n_last = wl["gemms"][-1][0]
+    affinity = os.sched_getaffinity(0)
+    bind_note = bind_to_gpu_numa_node(local)
     host_x = F.Tensor.empty((m, k0), bf, F.Device.CUDA_HOST)
     host_y = F.Tensor.empty((m, n_last), bf, F.Device.CUDA_HOST)
-    dev_x = x_w if nsplit else F.Tensor.empty((m, k0), bf)
-    result = (y_own if push else wrap(y_t, bf)) if nsplit else outs[-1]
+    os.sched_setaffinity(0, affinity)  # only the allocation (and its first touch) needed the binding
+    result = (y_own if push else wrap(y_t, bf)) if nsplit else None
     import ctypes
     import numpy as np
     p = ctypes.c_void_p()
@@ -445,11 +549,31 @@ def run_ours(args, wl):
     hx = np.ctypeslib.as_array(ctypes.cast(p.value, ctypes.POINTER(ctypes.c_uint16)), shape=(m * k0,))
     hx[:] = (np.random.default_rng(7 + rank).standard_normal(m * k0).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
     ops = F.operators()
+    chunks = 1 if nsplit else max(1, min(args.e2e_chunks, m // 128))
+    bounds = [min(m, ((m * c // chunks) + 255) // 256 * 256) for c in range(chunks)] + [m]  # whole 256-row tiles
+    bounds[0] = 0
+    bounds = sorted(set(bounds))
+    chunks = len(bounds) - 1
+    x_chunks = [host_x.view_as((bounds[c + 1] - bounds[c], k0), (k0, 1), bounds[c] * k0) for c in range(chunks)]
+    y_chunks = [host_y.view_as((bounds[c + 1] - bounds[c], n_last), (n_last, 1), bounds[c] * n_last) for c in range(chunks)]
 
     def e2e_step(i):
-        F.check(F.lib().fl_transfer(ops, host_x.raw(), dev_x.raw()))
-        step(i, x_override=dev_x)
-        F.check(F.lib().fl_transfer(ops, result.raw(), host_y.raw()))  # synchronises
+        if nsplit:
+            F.check(F.lib().fl_transfer(ops, host_x.raw(), x_w.raw()))
+            step(i)
+            F.check(F.lib().fl_transfer(ops, result.raw(), host_y.raw()))  # synchronises
+            return
+        uploads = [F.transfer_async(xc) for xc in x_chunks]
+        downloads, alive = [], []
+        for c in range(chunks):
+            xd, pending = uploads[c]
+            pending.wait()
+            y = step(i, x_override=xd, alloc=True)
+            downloads.append(F.transfer_to_host_async(y, y_chunks[c]))
+            alive.append(y)
+        downloads[-1].wait_sync()   # downloads complete in order on their stream
+        for d in downloads[:-1]:
+            d.wait_sync()
 
     e2e_steps = max(3, min(args.steps, 20))
     for i in range(3):
@@ -468,7 +592,6 @@ def run_ours(args, wl):
     bf16_peak, hbm_peak, peak_kind = measured_peaks(clocks)
     peak = PEAK_MULT[wl["kind"]] * bf16_peak
     gemm_tflops = (flops_per_step(wl) / (world if nsplit else 1)) * args.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
-    traffic = NCU_TRAFFIC_BYTES.get(args.workload)
     roofline = {
         "bound": "tensor", "kernel": "gemm_tn_kernel", "achieved": gemm_tflops, "peak": peak, "unit": UNIT,
         "frac": (gemm_tflops / peak) if gemm_tflops else None,
@@ -476,7 +599,8 @@ def run_ours(args, wl):
         "frac_of_nominal": (gemm_tflops / NOMINAL_PEAK[wl["kind"]]) if gemm_tflops else None,
         "nominal_peak": NOMINAL_PEAK[wl["kind"]],
         "launches": gemm_launches, "avg_launch_ms": gemm_ms / gemm_launches if gemm_launches else None,
-        "traffic": traffic, "algorithmic_bytes_per_step": algorithmic_bytes_per_step(wl),
+        **traffic_fields(args.workload), "algorithmic_bytes_per_step": algorithmic_bytes_per_step(wl),
+        "sustained": sustained,
     }
 
     # ---- CPU baseline on a bounded sample (rank 0, N = 1 only) ---------------------------------
@@ -508,7 +632,11 @@ def run_ours(args, wl):
                        "l2": f"{sets} rotating operand sets ({touched / 1e6:.0f} MB of inputs) > 126 MB L2",
                        "accumulate": "fp32", "out": "bf16"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": m * k0 * 2,
-                    "d2h_bytes_per_step": m * n_last * 2, "steps": e2e_steps},
+                    "d2h_bytes_per_step": m * n_last * 2, "steps": e2e_steps, "chunks": chunks,
+                    "how": "rows in chunks: uploads on a copy stream (fl_transfer_async), linears per chunk behind "
+                           "fl_transfer_wait, downloads on a second copy stream; outputs allocated per call; one host wait per step",
+                    "host_memory": bind_note},
+            "per_call_alloc": alloc_check,
             "gpu_launches": launches,
             "clocks": sampler.summary(),
             "roofline": roofline,
@@ -520,9 +648,84 @@ def run_ours(args, wl):
         dist.destroy_process_group()
 
 
+def mmdit_cpu_sample(steps_hint=1):
+    """The CPU side of the c4 workload on a bounded sample: one block of the sixty on one of the two
+    classifier-free-guidance rows (4352 tokens) at the benchmark's widths, plus the linears around
+    the blocks for that row, through the oracle's restated quantisers with the reference's own CPU
+    fl_matmul and fl_attention (oracle/_ref) doing the products where that library was built.
+    Blocks and batch rows cost the same each, so a step is (block x 60 + outer) x 2.
+    Returns (closure that runs the sample and returns (block seconds, outer seconds), kind, cores, text)."""
+    import torch
+    from oracle import oracle as O
+    from oracle.mmdit_oracle import OracleBackend
+    from libwaifu_b200.mmdit import MMDiT, MMDiTConfig
+    O.lib()
+    kind = "reference" if O.have_ref() else "port"
+    cfg = MMDiTConfig(blocks=1, batch=1)
+    model = MMDiT(cfg, OracleBackend(O), seed=0, cpu_init=True)
+    g = torch.Generator().manual_seed(3)
+    tokens = torch.randn(1, cfg.image_tokens, cfg.latent_channels, generator=g).bfloat16()
+    context = torch.randn(1, cfg.text_tokens, cfg.context_size, generator=g).bfloat16()
+    sinusoid = torch.randn(1, cfg.timestep_embed_dim, generator=g).bfloat16()
+
+    def sample():
+        with torch.no_grad():
+            t0 = time.perf_counter()
+            x, emb = model.embed(tokens, context, sinusoid)
+            t1 = time.perf_counter()
+            x = model.blocks(x, emb)
+            t2 = time.perf_counter()
+            model.final(x, emb)
+            t3 = time.perf_counter()
+        return t2 - t1, (t1 - t0) + (t3 - t2)
+
+    cores = os.cpu_count() or 1
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except Exception:
+        pass
+    text = ("1 of 60 blocks and the outer linears on 1 of the 2 batch rows (4352 tokens) at the benchmark's widths, "
+            "whole sample on the host (quantisers, fp32 GEMMs, fp32 attention, norms); a step is (block x 60 + outer) x 2")
+    return sample, kind, cores, text
+
+
+def run_mmdit_reference(args):
+    """The reference arm of c4_mmdit_step: the CPU sample above, timed per step and extrapolated."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    try:
+        os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
+    except Exception:
+        os.environ.pop("OMP_NUM_THREADS", None)
+    sample, kind, cores, text = mmdit_cpu_sample()
+    for _ in range(args.warmup):
+        sample()
+    block_s = outer_s = 0.0
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        b, o = sample()
+        block_s += b
+        outer_s += o
+    sample_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    step_ms = (block_s * 60 + outer_s) * 2 / args.steps * 1e3
+    line = {
+        "impl": "reference", "metric": "ms per MMDiT denoise step", "value": step_ms, "unit": "ms", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sample_ms, "higher_is_better": False, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "c4_mmdit_step", "what": WORKLOADS["c4_mmdit_step"]["desc"], "sample": text,
+                   "extrapolated": "value = (block time x 60 + outer time) x 2 from the timed sample; ms_per_step is the sample's own time"},
+        "cpu_baseline": {"value": step_ms, "unit": "ms", "cores": cores, "kind": kind, "sample": text},
+        "e2e": {"value": step_ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_mmdit(args):
-    """The C4 workload: ms per denoise step of the 60-block MMDiT with every linear on the FP8 path
-    (attention, norms and rotary embedding are torch). N > 1: every rank runs its own batch."""
+    """The C4 workload: ms per denoise step of the 60-block MMDiT, every linear on the FP8 path and
+    every kernel of a block this library's own (fl_attention included; torch's attention is timed
+    beside it as a yardstick). N > 1: every rank runs its own batch."""
     import torch
     from libwaifu_b200 import flint as F
     from libwaifu_b200.mmdit import MMDiT, MMDiTConfig, FlintBackend
@@ -540,60 +743,84 @@ def run_mmdit(args):
     cfg = MMDiTConfig()
     if args.blocks:
         cfg.blocks = args.blocks
-    model = MMDiT(cfg, FlintBackend(args.attention), seed=0)
+    backend = FlintBackend(args.attention)
+    model = MMDiT(cfg, backend, seed=0)
     g = torch.Generator(device="cuda").manual_seed(1 + rank)
-    x = torch.randn(cfg.batch, cfg.tokens, cfg.hidden, device="cuda", dtype=torch.bfloat16, generator=g)
-    temb = torch.randn(cfg.batch, cfg.hidden, device="cuda", dtype=torch.bfloat16, generator=g)
+    tokens = torch.randn(cfg.batch, cfg.image_tokens, cfg.latent_channels, device="cuda", dtype=torch.bfloat16, generator=g)
+    context = torch.randn(cfg.batch, cfg.text_tokens, cfg.context_size, device="cuda", dtype=torch.bfloat16, generator=g)
+    sinusoid = torch.randn(cfg.batch, cfg.timestep_embed_dim, device="cuda", dtype=torch.bfloat16, generator=g)
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def timed(steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            model.step(tokens, context, sinusoid)
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1) / steps
+
     with torch.no_grad():
         for _ in range(args.warmup):
-            model.step(x, temb)
+            model.step(tokens, context, sinusoid)
         barrier()
         sampler = ClockSampler(local)
         sampler.start()
         launches0 = F.launch_count()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            y = model.step(x, temb)
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1) / args.steps
+        ms = timed(args.steps)
         launches = F.launch_count() - launches0
         F.gemm_timing(True)
         F.gemm_timing_read()
-        model.step(x, temb)
+        model.step(tokens, context, sinusoid)
         gemm_ms, gemm_launches = F.gemm_timing_read()
         F.gemm_timing(False)
         sampler.stop_flag.set()
         sampler.join(timeout=5)
-        # end to end: the latent and timestep embedding from pinned host memory, the result back
-        hx = x.cpu().pin_memory()
-        ht = temb.cpu().pin_memory()
-        hy = torch.empty_like(hx).pin_memory()
+        # the other attention kernel beside it, a few steps
+        other = "sdpa" if args.attention == "flint" else "flint"
+        backend.attention_kernel = other
+        model.step(tokens, context, sinusoid)
+        other_ms = timed(max(2, min(args.steps, 3)))
+        backend.attention_kernel = args.attention
+        # end to end: latent tokens, prompt states and sinusoid from pinned host memory, the velocity back
+        host_in = [t.cpu().pin_memory() for t in (tokens, context, sinusoid)]
+        hy = torch.empty(cfg.batch, cfg.image_tokens, cfg.latent_channels, dtype=torch.bfloat16).pin_memory()
         for _ in range(2):
-            model.step(hx.cuda(non_blocking=True), ht.cuda(non_blocking=True))
+            model.step(*[t.cuda(non_blocking=True) for t in host_in])
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record()
         e2e_steps = max(2, min(args.steps, 5))
         for _ in range(e2e_steps):
-            y = model.step(hx.cuda(non_blocking=True), ht.cuda(non_blocking=True))
+            y = model.step(*[t.cuda(non_blocking=True) for t in host_in])
             hy.copy_(y, non_blocking=False)
         e1.record()
         barrier()
         e2e_ms = e0.elapsed_time(e1) / e2e_steps
     if dist is not None:
-        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        t = torch.tensor([ms, e2e_ms, other_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
+        ms, e2e_ms, other_ms = float(t[0]), float(t[1]), float(t[2])
     bf16_peak, _, peak_kind = measured_peaks(sampler.summary())
     gemm_tflops = cfg.gemm_flops() / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sample, kind, cores, text = mmdit_cpu_sample()
+        best = None
+        for _ in range(2):
+            b, o = sample()
+            step_ms = (b * 60 + o) * 2 * 1e3
+            best = step_ms if best is None else min(best, step_ms)
+        cpu_baseline = {"value": best, "unit": "ms", "cores": cores, "kind": kind, "sample": text + "; best of 2"}
+
     if rank == 0:
+        names = {"flint": "fl_attention (this library), bf16", "sdpa": "torch SDPA (a library kernel), bf16"}
         line = {
             "metric": "ms per MMDiT denoise step", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
@@ -601,9 +828,10 @@ def run_mmdit(args):
             "config": {"workload": "c4_mmdit_step", "what": WORKLOADS["c4_mmdit_step"]["desc"], "blocks": cfg.blocks,
                        "parallelism": f"batch-sharded x{world} (each rank its own CFG pair), weights replicated",
                        "l2": f"{cfg.blocks} blocks x 170 MB of FP8 weights stream through the 126 MB L2 every step",
-                       "attention": "torch SDPA, bf16" if args.attention == "sdpa" else "fl_attention (this library), bf16",
-                       "outside_the_path": "attention and the SiLU of the timestep embedding"},
-            "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": int(hx.numel() * 2 + ht.numel() * 2),
+                       "attention": names[args.attention],
+                       "yardstick": {"attention": names[other], "ms_per_step": other_ms},
+                       "outside_the_path": "the SiLU of the embeddings and the RMS norm of the prompt's 512 rows (torch)"},
+            "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": int(sum(t.numel() for t in host_in) * 2),
                     "d2h_bytes_per_step": int(hy.numel() * 2), "steps": e2e_steps},
             "gpu_launches": launches,
             "clocks": sampler.summary(),
@@ -612,7 +840,7 @@ def run_mmdit(args):
                          "peak_source": f"2 x bf16 cuBLAS, of {peak_kind}", "launches": gemm_launches,
                          "gemm_ms_per_step": gemm_ms, "gemm_share_of_step": gemm_ms / ms if ms else None,
                          "traffic": None},
-            "cpu_baseline": None,
+            "cpu_baseline": cpu_baseline,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -727,7 +955,7 @@ def run_skinny(args):
     achieved = alg_bytes / (ms_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": "skinny_fp8_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                 "frac": achieved / hbm_peak, "peak_source": f"stream copy, of {peak_kind}", "launches": launches,
-                "avg_launch_ms": ms_step, "traffic": NCU_TRAFFIC_BYTES.get("skinny_decode"),
+                "avg_launch_ms": ms_step, **traffic_fields("skinny_decode"),
                 "algorithmic_bytes_per_step": alg_bytes,
                 "note": "one launch per step; the launch time is the step time of the back-to-back timed region"}
 
@@ -858,7 +1086,7 @@ def run_attention(args):
     achieved = flops / (ms_step * 1e-3) / 1e12
     roofline = {"bound": "tensor", "kernel": "attention_kernel", "achieved": achieved, "peak": bf16_peak, "unit": "TFLOP/s",
                 "frac": achieved / bf16_peak, "peak_source": f"bf16 cuBLAS, of {peak_kind}", "launches": launches,
-                "avg_launch_ms": ms_step, "traffic": NCU_TRAFFIC_BYTES.get("attention_step"),
+                "avg_launch_ms": ms_step, **traffic_fields("attention_step"),
                 "algorithmic_bytes_per_step": 4 * n * h * L * d * 2,
                 "note": "two launches per step (the transposition of v, then the attention kernel); "
                         "the step time stands for the attention kernel's, which is 97 % of it"}
@@ -934,12 +1162,16 @@ def main():
     ap.add_argument("--rows", type=int, default=None, help="override the workload's row count (for small profile captures)")
     ap.add_argument("--reference-rows", type=int, default=1088, help="rows of the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-chunks", type=int, default=4, help="row chunks the end-to-end step is pipelined in")
+    ap.add_argument("--sustained-seconds", type=float, default=1.0,
+                    help="length of the extra back-to-back loop behind roofline.sustained (0: skip it)")
     ap.add_argument("--parallel", default="batch", choices=["batch", "nsplit", "nsplit_push"],
                     help="batch: rows sharded, no collective (weak scaling); nsplit: one MLP with its weights "
                          "split by output channel and NCCL all-gathers (strong scaling)")
     ap.add_argument("--blocks", type=int, default=None, help="c4_mmdit_step: run this many blocks instead of 60")
-    ap.add_argument("--attention", default="sdpa", choices=["sdpa", "flint"],
-                    help="c4_mmdit_step: torch's attention, or this library's fl_attention")
+    ap.add_argument("--attention", default="flint", choices=["sdpa", "flint"],
+                    help="c4_mmdit_step: this library's fl_attention (the reported number), or torch's attention; "
+                         "the other one is timed beside it as a yardstick")
     args = ap.parse_args()
     if args.workload == "skinny_decode" and args.impl == "ours":
         args.warmup = max(args.warmup, 3)
@@ -959,6 +1191,10 @@ def main():
         if args.steps == 1000:
             args.steps = 10
         return run_mmdit(args)
+    if args.workload == "c4_mmdit_step" and args.impl == "reference":
+        if args.steps == 1000:
+            args.steps = 3
+        return run_mmdit_reference(args)
     wl = dict(WORKLOADS[args.workload])
     if args.rows:
         wl["m"] = args.rows

@@ -1,5 +1,12 @@
 """A denoise step of an MMDiT whose linears all run on the quantized-linear path.
 
+The step follows the reference's denoiser (waifu/src/qwen_image/dit.rs:448-578): the timestep's
+sinusoid goes through the two time-embed linears (M = batch rows), the prompt's encoder states
+through an RMS norm and the two `txt_in` linears, the latent tokens through `img_in` (64 -> hidden),
+text and image rows are joined (prompt first) and walked through the blocks, and the last layer
+reads the picture's rows only: a scale off the step's own embedding, layer norm times (1 + scale),
+and the projection back to the latent's 64 channels.
+
 The block follows the reference's joint text+image transformer block
 (waifu/src/qwen_image/dit.rs:220-345: one projection shared by text and image rows, per-head RMS
 norm of q and k, rotary embedding, attention over the joined sequence, gated residuals driven by an
@@ -14,14 +21,13 @@ activation quantiser run as one kernel in front of the QKV and up projections
 down projections is folded into the projection's epilogue (the gate multiplies the per-channel
 scale and the bias, the stream is the residual), and the per-head RMS norm of q and k with their
 rotary embedding runs in place on the QKV projection's output (fl_qk_norm_rope), which attention
-then reads as three strided views. Attention runs through torch's scaled_dot_product_attention by
-default, or through this library's fl_attention with ``FlintBackend(attention_kernel="flint")``
-(the same strided views, the result written token-major; slower than torch's library kernel at
-this size, so not the default); the SiLU of the timestep embedding is plain torch. Both are inside
-the timed step but outside the graded path.
+then reads as three strided views. Attention runs through this library's fl_attention by default
+(the same strided views, the result written token-major); ``FlintBackend(attention_kernel="sdpa")``
+swaps in torch's scaled_dot_product_attention, a library kernel kept as a yardstick. The SiLU of
+the embeddings and the RMS norm of the prompt's states (0.3 % of a step's rows) are plain torch.
 
-The same block code runs over two backends: ``FlintBackend`` (the C ABI on the GPU) and
-``OracleBackend`` (the CPU oracle, for the parity test at a reduced size).
+The block code runs over any backend with FlintBackend's methods; the CPU restatement the parity
+tests and the CPU baseline use lives with the oracle, outside this package.
 """
 from __future__ import annotations
 
@@ -40,20 +46,40 @@ class MMDiTConfig:
     text_tokens: int = 256
     image_tokens: int = 4096
     batch: int = 2  # the two classifier-free-guidance rows
+    latent_channels: int = 64      # a 2 x 2 patch of the 16-channel latent
+    context_size: int = 3584       # width of the prompt encoder's states
+    timestep_embed_dim: int = 256
 
     @property
     def tokens(self) -> int:
         return self.text_tokens + self.image_tokens
 
-    def gemm_flops(self) -> float:
-        """2 m n k over the four big linears of every block (the modulation's are negligible)."""
+    def block_gemm_flops(self) -> float:
+        """2 m n k over the four big linears of one block (the modulation's are negligible)."""
         m = self.batch * self.tokens
-        per_block = 2.0 * m * self.hidden * (3 * self.hidden + self.hidden + 2 * self.mlp)
-        return per_block * self.blocks
+        return 2.0 * m * self.hidden * (3 * self.hidden + self.hidden + 2 * self.mlp)
+
+    def outer_gemm_flops(self) -> float:
+        """The linears outside the blocks: txt_in (two), img_in and the final projection."""
+        mt, mi, d = self.batch * self.text_tokens, self.batch * self.image_tokens, self.hidden
+        return 2.0 * (mt * d * (self.context_size + d) + 2 * mi * d * self.latent_channels)
+
+    def gemm_flops(self, blocks: Optional[int] = None) -> float:
+        return self.block_gemm_flops() * (self.blocks if blocks is None else blocks) + self.outer_gemm_flops()
+
+    def attention_flops(self, blocks: Optional[int] = None) -> float:
+        per_block = 4.0 * self.batch * self.heads * self.tokens * self.tokens * self.head_dim
+        return per_block * (self.blocks if blocks is None else blocks)
 
 
 LAYER_SHAPES = lambda c: {"mod": (6 * c.hidden, c.hidden), "qkv": (3 * c.hidden, c.hidden),
                           "out": (c.hidden, c.hidden), "up": (c.mlp, c.hidden), "down": (c.hidden, c.mlp)}
+
+# The linears around the blocks (waifu/src/qwen_image/dit.rs:464-475,497-512,565-578), (n, k).
+OUTER_SHAPES = lambda c: {"time1": (c.hidden, c.timestep_embed_dim), "time2": (c.hidden, c.hidden),
+                          "txt1": (c.hidden, c.context_size), "txt2": (c.hidden, c.hidden),
+                          "img_in": (c.hidden, c.latent_channels),
+                          "final_lin": (c.hidden, c.hidden), "final_proj": (c.latent_channels, c.hidden)}
 
 
 LN_EPS = 1e-6
@@ -63,7 +89,7 @@ class FlintBackend:
     """Linears through libflint_sm100 (fl_quantize_fp8_rows at load; per call fl_fp8_linear, or
     fl_fp8_layernorm_quantize + fl_fp8_linear_quantized where a layer norm feeds the linear)."""
 
-    def __init__(self, attention_kernel: str = "sdpa"):
+    def __init__(self, attention_kernel: str = "flint"):
         import torch
         from . import flint as F
         if attention_kernel not in ("sdpa", "flint"):
@@ -110,10 +136,20 @@ class FlintBackend:
         qw, rsw = self._wrap(q, F.DType.FP8E4M3), self._wrap(rs, F.DType.FLOAT)
         # scale and shift are column slices of the modulation linear's output: passed as they lie
         F.fp8_layernorm_quantize(self._wrap(x3d.reshape(b * t, d), F.DType.BFLOAT16), self._wrap(scale, F.DType.BFLOAT16),
-                                 self._wrap(shift, F.DType.BFLOAT16), LN_EPS, qw, rsw)
+                                 None if shift is None else self._wrap(shift, F.DType.BFLOAT16), LN_EPS, qw, rsw)
         out = torch.empty((b * t, codes.shape[0]), dtype=torch.bfloat16, device=x3d.device)
         F.fp8_linear_quantized(qw, rsw, codes, scales, bias, None, act, self._wrap(out, F.DType.BFLOAT16))
         return out
+
+    def silu(self, x):
+        return self.torch.nn.functional.silu(x)
+
+    def rms_norm(self, x2d, weight_f32, eps):
+        """flint's rmsNorm in float32 (a * w / sqrt(mean(a^2) + eps), flint/cpu/normalizations.cc:33-70),
+        narrowed once: the prompt's way in (waifu/src/qwen_image/dit.rs:481-495)."""
+        torch = self.torch
+        a = x2d.float()
+        return (a * weight_f32 / torch.sqrt(a.pow(2).mean(dim=1, keepdim=True) + eps)).to(torch.bfloat16)
 
     def qk_norm_rope(self, qkv2d, cos, sin, heads):
         """In place: per-head RMS norm of q and k, then their rotary embedding."""
@@ -126,7 +162,7 @@ class FlintBackend:
         """Joint attention over qkv (batch, tokens, 3, heads, head_dim), the fused projection's
         output: q, k and v are strided views of it and the result is token-major (batch * tokens,
         heads * head_dim), the layout the next projection reads. `self.attention_kernel` chooses
-        this library's kernel ("flint") or torch's ("sdpa", the default: see the module text)."""
+        this library's kernel ("flint", the default) or torch's ("sdpa", a yardstick)."""
         torch, F = self.torch, self.F
         b, t, _, h, hd = qkv5d.shape
         if self.attention_kernel == "flint":
@@ -171,52 +207,6 @@ class FlintBackend:
         return out
 
 
-class OracleBackend:
-    """The same linears on the CPU through the test oracle (only tests construct this), each fused
-    step spelled out as the separate operations it stands for."""
-
-    def __init__(self, oracle_module):
-        import torch
-        self.torch = torch
-        self.O = oracle_module
-        self.device = "cpu"
-
-    def _bits(self, t):
-        return t.contiguous().view(self.torch.int16).numpy().view("uint16")
-
-    def _tensor(self, bits):
-        return self.torch.from_numpy(bits.view("int16").copy()).view(self.torch.bfloat16)
-
-    def make_layer(self, w_f32, bias_bf16):
-        codes, scales = self.O.quantize_fp8_rows(w_f32.cpu().numpy())
-        return (codes, scales, None if bias_bf16 is None else self._bits(bias_bf16.cpu()))
-
-    def linear(self, x2d, layer, act: int = 0, residual2d=None):
-        codes, scales, bias = layer
-        y = self.O.fp8_linear(self._bits(x2d), codes, scales, bias,
-                              None if residual2d is None else self._bits(residual2d), act, True)
-        return self._tensor(y)
-
-    def modulated_linear(self, x3d, scale, shift, layer, act: int = 0):
-        b, t, d = x3d.shape
-        h = self.O.layernorm_modulate(self._bits(x3d.reshape(b * t, d)), self._bits(scale), self._bits(shift), LN_EPS, True)
-        return self.linear(self._tensor(h), layer, act)
-
-    def qk_norm_rope(self, qkv2d, cos, sin, heads):
-        return self._tensor(self.O.qk_norm_rope(self._bits(qkv2d), cos.numpy(), sin.numpy(), heads, LN_EPS, True))
-
-    def attention(self, qkv5d):
-        b, t, _, h, hd = qkv5d.shape
-        q, k, v = (qkv5d[:, :, i].transpose(1, 2) for i in range(3))
-        a = self.torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float()).to(self.torch.bfloat16)
-        return a.transpose(1, 2).reshape(b * t, h * hd).contiguous()
-
-    def gated_linear(self, a2d, layer, gate, stream3d):
-        b, t, n = stream3d.shape
-        y = self.linear(a2d, layer).view(b, t, n).float()
-        return (stream3d.float() + gate[:, None, :].float() * y).to(self.torch.bfloat16)
-
-
 class MMDiT:
     """Random-init weights (N(0, 0.02^2), seed 0) quantised to e4m3 with per-row scales."""
 
@@ -244,6 +234,18 @@ class MMDiT:
                 block[name] = backend.make_layer(w, b)
                 del w
             self.layers.append(block)
+        self.outer = {}
+        for name, (n, k) in OUTER_SHAPES(cfg).items():
+            if dev == "cuda" and not cpu_init:
+                g = torch.Generator(device="cuda").manual_seed(int(torch.randint(0, 2 ** 31, (1,), generator=gen)))
+                w = torch.randn(n, k, device="cuda", dtype=torch.float32, generator=g) * 0.02
+                b = (torch.randn(n, device="cuda", dtype=torch.float32, generator=g) * 0.01).bfloat16()
+            else:
+                w = (torch.randn(n, k, generator=gen) * 0.02).to(dev)
+                b = (torch.randn(n, generator=gen) * 0.01).bfloat16().to(dev)
+            self.outer[name] = backend.make_layer(w, b)
+            del w
+        self.txt_norm = (1.0 + 0.1 * torch.randn(cfg.context_size, generator=gen)).to(dev)  # float32, as the reference keeps it
         half = cfg.head_dim // 2
         pos = torch.arange(cfg.tokens, dtype=torch.float32)
         freq = torch.exp(-math.log(10000.0) * torch.arange(half, dtype=torch.float32) / half)
@@ -252,12 +254,10 @@ class MMDiT:
         self.sin = ang.sin().contiguous().to(dev)
 
     def block(self, x, temb, layers):
-        torch = self.torch
-        Fn = torch.nn.functional
         c = self.cfg
         b, t, d = x.shape
         lin = self.backend.linear
-        mod = lin(Fn.silu(temb), layers["mod"])  # (b, 6 d): the M = batch skinny linear
+        mod = lin(self.backend.silu(temb), layers["mod"])  # (b, 6 d): the M = batch skinny linear
         shift1, scale1, _, shift2, scale2, _ = mod.chunk(6, dim=1)   # column slices, not copies
         modf = mod.float()                                             # the gates multiply fp32 scales
         gate1, gate2 = modf[:, 2 * d:3 * d], modf[:, 5 * d:6 * d]
@@ -273,8 +273,39 @@ class MMDiT:
         x = self.backend.gated_linear(u, layers["down"], gate2, x)
         return x
 
-    def step(self, x, temb):
+    def embed(self, tokens, context, sinusoid):
+        """The ways in (waifu/src/qwen_image/dit.rs:464-512): tokens (batch, image_tokens,
+        latent_channels), context (batch, text_tokens, context_size) and sinusoid (batch,
+        timestep_embed_dim), all 16-bit -> the joined stream (batch, tokens, hidden), prompt rows
+        first, and the timestep embedding (batch, hidden)."""
+        torch, c, be = self.torch, self.cfg, self.backend
+        lin = be.linear
+        b = tokens.shape[0]
+        emb = lin(be.silu(lin(sinusoid, self.outer["time1"])), self.outer["time2"])
+        normed = be.rms_norm(context.reshape(b * c.text_tokens, c.context_size), self.txt_norm, LN_EPS)
+        text = lin(lin(normed, self.outer["txt1"], act=1), self.outer["txt2"])  # GELU-tanh between, in the epilogue
+        image = lin(tokens.reshape(b * c.image_tokens, c.latent_channels), self.outer["img_in"])
+        x = torch.cat([text.view(b, c.text_tokens, c.hidden), image.view(b, c.image_tokens, c.hidden)], dim=1)
+        return x, emb
+
+    def final(self, x, emb):
+        """The last layer (waifu/src/qwen_image/dit.rs:565-578) on the picture's rows only: a scale
+        off the step's embedding, layer norm times (1 + scale), the projection to the latent."""
+        c, be = self.cfg, self.backend
+        b = x.shape[0]
+        scale = be.linear(be.silu(emb), self.outer["final_lin"])  # (batch, hidden)
+        image = x[:, c.text_tokens:].contiguous()
+        v = be.modulated_linear(image, scale, None, self.outer["final_proj"])
+        return v.view(b, c.image_tokens, c.latent_channels)
+
+    def blocks(self, x, temb):
         """x (batch, tokens, hidden) bf16, temb (batch, hidden) bf16 -> the same shape as x."""
         for layers in self.layers:
             x = self.block(x, temb, layers)
         return x
+
+    def step(self, tokens, context, sinusoid):
+        """One denoise step: latent tokens, prompt states and the timestep's sinusoid in, the
+        velocity (batch, image_tokens, latent_channels) out."""
+        x, emb = self.embed(tokens, context, sinusoid)
+        return self.final(self.blocks(x, emb), emb)

@@ -280,6 +280,12 @@ void fo_widen_16(const uint16_t *x, int is_bf16, int64_t numel, float *out) {
   for (i = 0; i < numel; ++i) out[i] = widen16(x[i], is_bf16);
 }
 
+void fo_narrow_16(const float *x, int is_bf16, int64_t numel, uint16_t *out) {
+  int64_t i;
+#pragma omp parallel for schedule(static)
+  for (i = 0; i < numel; ++i) out[i] = is_bf16 ? fo_bf16_from_f32(x[i]) : fo_f16_from_f32(x[i]);
+}
+
 /* ---- products -------------------------------------------------------------------------- */
 
 void fo_gemm_f32_nt(const float *a, const float *b, float *c, int m, int n, int k) {

@@ -65,6 +65,8 @@ void fo_decode_e4m3(const uint8_t *codes, int64_t numel, float *out);
 void fo_decode_nvfp4(const uint8_t *codes, const uint8_t *block_scales, int rows, int k,
                      float *out);
 void fo_widen_16(const uint16_t *x, int is_bf16, int64_t numel, float *out);
+/* float32 -> bf16 / fp16 bit patterns, round to nearest even (the scalar helpers above, over an array). */
+void fo_narrow_16(const float *x, int is_bf16, int64_t numel, uint16_t *out);
 
 /* ---- the products ---------------------------------------------------------------------- */
 

@@ -70,6 +70,7 @@ def lib() -> ctypes.CDLL:
         L.fo_decode_e4m3.argtypes = [u8p, c_int64, f32p]
         L.fo_decode_nvfp4.argtypes = [u8p, u8p, c_int, c_int, f32p]
         L.fo_widen_16.argtypes = [u16p, c_int, c_int64, f32p]
+        L.fo_narrow_16.argtypes = [f32p, c_int, c_int64, u16p]
         L.fo_gemm_f32_nt.argtypes = [f32p, f32p, f32p, c_int, c_int, c_int]
         L.fo_gemm_f64_nt.argtypes = [f32p, f32p, f64p, c_int, c_int, c_int]
         L.fo_epilogue.argtypes = [f32p, c_int, c_int, f32p, f32p, c_int, c_float, u16p, u16p,
@@ -111,7 +112,15 @@ def widen(x16: np.ndarray, is_bf16: bool) -> np.ndarray:
 
 
 def narrow(x: np.ndarray, is_bf16: bool) -> np.ndarray:
-    """float32 -> bf16/fp16 bit patterns, RNE (vectorised restatement for bf16; scalar for fp16)."""
+    """float32 -> bf16/fp16 bit patterns, RNE (the C restatement's scalar helpers over the array;
+    `narrow_numpy` is the independent vectorised form the pins compare it with)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint16)
+    lib().fo_narrow_16(_p(x, c_float), int(is_bf16), x.size, _p(out, c_uint16))
+    return out
+
+
+def narrow_numpy(x: np.ndarray, is_bf16: bool) -> np.ndarray:
     x = np.ascontiguousarray(x, dtype=np.float32)
     if is_bf16:
         bits = x.view(np.uint32).astype(np.uint64)
@@ -119,7 +128,7 @@ def narrow(x: np.ndarray, is_bf16: bool) -> np.ndarray:
         rounded = (bits + 0x7FFF + ((bits >> 16) & 1)) >> 16
         rounded = np.where(nan, (bits >> 16) | 0x40, rounded)
         return rounded.astype(np.uint16)
-    return x.astype(np.float16).view(np.uint16)  # numpy's cast is RNE; checked against fo_f16_from_f32
+    return x.astype(np.float16).view(np.uint16)  # numpy's cast is RNE
 
 
 # ---- quantizers ---------------------------------------------------------------------------

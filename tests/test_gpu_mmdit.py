@@ -1,37 +1,100 @@
-"""The MMDiT step harness on the GPU (C-ABI linears, torch for the rest) against the same blocks
-on the CPU (oracle linears, torch for the rest) at a reduced size with identical weights. This
-checks the composition -- that every linear of a block reaches the new path with the right
-operands, and that the fused steps (layer norm + modulation + quantiser in front of a projection,
-the gate folded into a projection's scale and bias) equal the separate operations the CPU side
-spells out -- not kernel parity, which the per-kernel tests hold to 5e-3: attention runs in bf16
-in two different torch backends here, and the gated residual
-is rounded once on the GPU and three times on the CPU, so the bound is the looser 3e-2 relative
-L2."""
+"""The MMDiT denoise step on the GPU (C-ABI linears, row kernels and attention) against the same
+step on the CPU (oracle linears, the reference's CPU attention, numpy for the rest) with identical
+weights.
+
+Two sizes. A reduced one checks the composition and counts the launches. The benchmark's own widths
+(hidden 3072, 24 heads of 128, MLP 12288, every outer linear) on a token count the host can afford
+check each stage on identical inputs -- the ways in, every block, the last layer -- and then the
+whole chain.
+
+Bounds, relative L2 of bfloat16 outputs, and why they are what they are. Per-kernel parity is held
+to 5e-3 by the kernels' own tests; here a stage chains several quantised linears, and a
+per-token quantiser is discontinuous: a last-bit difference in a row's largest value moves that
+row's scale and with it many codes. On identical inputs a stage stays within 1e-2 (the ways in and
+the last layer, two linears deep, within 5e-3); the chain of every stage, where each side quantises
+its own slightly different activations, within 3e-2. The gated residual is rounded once on the GPU
+(in the projection's epilogue) and three times in the CPU's spelled-out form."""
 import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
 
 
+def inputs(torch, cfg, seed):
+    g = torch.Generator().manual_seed(seed)
+    tokens = torch.randn(cfg.batch, cfg.image_tokens, cfg.latent_channels, generator=g).bfloat16()
+    context = torch.randn(cfg.batch, cfg.text_tokens, cfg.context_size, generator=g).bfloat16()
+    sinusoid = torch.randn(cfg.batch, cfg.timestep_embed_dim, generator=g).bfloat16()
+    return tokens, context, sinusoid
+
+
+def rel(oracle, a, b):
+    return oracle.rel_l2(a.float().cpu().numpy(), b.float().cpu().numpy())
+
+
 @pytest.mark.parametrize("attention_kernel", ["sdpa", "flint"])
 def test_two_blocks_match_the_cpu_composition(flint, oracle, attention_kernel):
     import torch
-    from libwaifu_b200.mmdit import MMDiT, MMDiTConfig, FlintBackend, OracleBackend
-    cfg = MMDiTConfig(hidden=256, heads=2, head_dim=128, mlp=1024, blocks=2, text_tokens=32, image_tokens=96, batch=2)
+    from libwaifu_b200.mmdit import MMDiT, MMDiTConfig, FlintBackend
+    from oracle.mmdit_oracle import OracleBackend
+    cfg = MMDiTConfig(hidden=256, heads=2, head_dim=128, mlp=1024, blocks=2, text_tokens=32, image_tokens=96, batch=2,
+                      latent_channels=64, context_size=192, timestep_embed_dim=64)
     gpu = MMDiT(cfg, FlintBackend(attention_kernel), seed=0, cpu_init=True)
     cpu = MMDiT(cfg, OracleBackend(oracle), seed=0, cpu_init=True)
-    g = torch.Generator().manual_seed(5)
-    x = torch.randn(cfg.batch, cfg.tokens, cfg.hidden, generator=g).bfloat16()
-    temb = torch.randn(cfg.batch, cfg.hidden, generator=g).bfloat16()
-    launches0 = flint.launch_count()
+    tokens, context, sinusoid = inputs(torch, cfg, 5)
     with torch.no_grad():
-        y_gpu = gpu.step(x.cuda(), temb.cuda()).float().cpu().numpy()
-        y_cpu = cpu.step(x, temb).float().numpy()
+        x, emb = gpu.embed(tokens.cuda(), context.cuda(), sinusoid.cuda())
+        launches0 = flint.launch_count()
+        y = gpu.blocks(x, emb)
+        flint.synchronize()
+        # per block: the M = 2 modulation linear (one launch), QKV and up (fused layer norm + quantiser, GEMM),
+        # the q/k norm + rotation, out and down (quantiser, one gated GEMM per batch row block)
+        # (+ with this library's attention: the transposition of v and the attention kernel)
+        assert flint.launch_count() - launches0 == 2 * (1 + 2 + 1 + 3 + 2 + 3 + (2 if attention_kernel == "flint" else 0))
+        v_gpu = gpu.step(tokens.cuda(), context.cuda(), sinusoid.cuda())
+        v_cpu = cpu.step(tokens, context, sinusoid)
     flint.synchronize()
-    # per block: the M = 2 modulation linear (one launch), QKV and up (fused layer norm + quantiser, GEMM),
-    # the q/k norm + rotation, out and down (quantiser, one gated GEMM per batch row block)
-    # (+ with this library's attention: the transposition of v and the attention kernel)
-    assert flint.launch_count() - launches0 == 2 * (1 + 2 + 1 + 3 + 2 + 3 + (2 if attention_kernel == "flint" else 0))
-    assert np.all(np.isfinite(y_gpu))
-    r = oracle.rel_l2(y_gpu, y_cpu)
+    assert v_gpu.shape == (cfg.batch, cfg.image_tokens, cfg.latent_channels)
+    assert torch.isfinite(v_gpu.float()).all() and torch.isfinite(y.float()).all()
+    r = rel(oracle, v_gpu, v_cpu)
     assert r <= 3e-2, f"relative L2 {r}"
+
+
+def test_benchmark_widths_stage_by_stage_and_chained(flint, oracle):
+    """Hidden 3072, 24 x 128 heads, MLP 12288, context 3584, 64 latent channels: the benchmark's
+    widths, two of its sixty blocks, 2 x (32 + 480) rows instead of 2 x (256 + 4096). Attention on
+    the CPU side is the reference's own fl_attention where its library was built."""
+    import torch
+    from libwaifu_b200.mmdit import MMDiT, MMDiTConfig, FlintBackend
+    from oracle.mmdit_oracle import OracleBackend
+    cfg = MMDiTConfig(blocks=2, text_tokens=32, image_tokens=480)
+    assert (cfg.hidden, cfg.heads, cfg.head_dim, cfg.mlp, cfg.context_size, cfg.latent_channels) == (3072, 24, 128, 12288, 3584, 64)
+    gpu = MMDiT(cfg, FlintBackend("flint"), seed=0, cpu_init=True)
+    cpu = MMDiT(cfg, OracleBackend(oracle), seed=0, cpu_init=True)
+    tokens, context, sinusoid = inputs(torch, cfg, 6)
+    errors = {}
+    with torch.no_grad():
+        # the ways in, on identical inputs
+        x_g, emb_g = gpu.embed(tokens.cuda(), context.cuda(), sinusoid.cuda())
+        x_c, emb_c = cpu.embed(tokens, context, sinusoid)
+        errors["embed: stream"] = (rel(oracle, x_g, x_c), 5e-3)
+        errors["embed: timestep"] = (rel(oracle, emb_g, emb_c), 5e-3)
+        # every block on the GPU's own input
+        x = x_g
+        for i, (lg, lc) in enumerate(zip(gpu.layers, cpu.layers)):
+            y_g = gpu.block(x, emb_g, lg)
+            y_c = cpu.block(x.cpu(), emb_g.cpu(), lc)
+            errors[f"block {i}"] = (rel(oracle, y_g, y_c), 1e-2)
+            x = y_g
+        # the last layer on the GPU's own input
+        v_g = gpu.final(x, emb_g)
+        v_c = cpu.final(x.cpu(), emb_g.cpu())
+        errors["final"] = (rel(oracle, v_g, v_c), 5e-3)
+        # and everything chained, each side on its own activations
+        errors["chained step"] = (rel(oracle, gpu.step(tokens.cuda(), context.cuda(), sinusoid.cuda()),
+                                      cpu.step(tokens, context, sinusoid)), 3e-2)
+    flint.synchronize()
+    report = ", ".join(f"{k} {v[0]:.2e}" for k, v in errors.items())
+    print("relative L2 per stage:", report)
+    for name, (err, bound) in errors.items():
+        assert np.isfinite(err) and err <= bound, f"{name}: relative L2 {err:.3e} > {bound} ({report})"

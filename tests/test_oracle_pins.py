@@ -77,8 +77,10 @@ def test_16bit_narrowing_matches_torch_and_numpy(oracle):
     bf = np.array([L.fo_bf16_from_f32(float(v)) for v in y], dtype=np.uint16)
     assert np.array_equal(bf, torch.from_numpy(y).bfloat16().view(torch.uint16).numpy())
     assert np.array_equal(bf, oracle.narrow(y, True))
+    assert np.array_equal(bf, oracle.narrow_numpy(y, True))
     with np.errstate(over="ignore"):
         h = y.astype(np.float16).view(np.uint16)
+    assert np.array_equal(h, oracle.narrow(y, False))
     assert np.array_equal(np.array([L.fo_f16_from_f32(float(v)) for v in y], dtype=np.uint16), h)
     back = np.array([L.fo_f16_to_f32(int(v)) for v in h[:5000]], dtype=np.float32)
     assert np.array_equal(back, h[:5000].view(np.float16).astype(np.float32))
