@@ -335,6 +335,17 @@ FLAPI int32_t fl_qk_norm_rope(fl_tensor_view_t qkv, fl_tensor_view_t q_weight, f
 FLAPI int32_t fl_sm100_few_rows_plan(int32_t m, int32_t n, int32_t k, int32_t weight_bytes, int32_t activation_bytes,
                                      int32_t has_residual, int32_t *plan);
 
+/* Which tile kernel a product of `kind` (0 half, 1 bfloat16, 2 e4m3, 3 nvfp4) and shape would run on
+ * and how its tiles are dealt out over a device of `sms` SMs; host arithmetic only, no GPU needed, so
+ * that the schedule can be checked anywhere. plan[8]: [0] CTAs per unit (2: a cluster pair sharing a
+ * 256-row tile), [1] tile width, [2] tiles, [3] K stages (128 bytes of K each) per tile, [4] units,
+ * [5] rounds of whole tiles (tile = round * units + unit), [6] tiles of the stream-K part that
+ * follows, from tile [7] on: their K stages are pooled and unit u computes pool positions
+ * [total * u / units, total * (u + 1) / units), total = [6] * [3]. [6] is 0 (no such part: the last
+ * round is simply partly filled) or at least [4]. */
+FLAPI int32_t fl_sm100_gemm_plan(int32_t kind, int32_t m, int32_t n, int32_t k, int32_t sms, int32_t allow_stream_k,
+                                 int32_t *plan);
+
 /* Storage over device memory the caller already owns (for instance a torch tensor's): nothing
  * is copied and nothing is freed on destroy. The device counterpart of fl_tensor_data_borrow(). */
 FLAPI int32_t fl_tensor_data_borrow_device(void *device_ptr, fl_dtype_t dtype, int64_t numel, fl_tensor_data_t *out);

@@ -156,6 +156,10 @@ struct DeviceState {
   // per direction so that uploads and downloads share the full-duplex link.
   cudaStream_t upload_stream = nullptr;
   cudaStream_t download_stream = nullptr;
+  // Workspace of the GEMM's stream-K schedule: accumulator parts and the counters beside them
+  // (zero between launches). Made once, on the first GEMM, and kept.
+  float *sk_partials = nullptr;
+  uint32_t *sk_counters = nullptr;
 };
 
 std::mutex g_mutex;
@@ -250,6 +254,12 @@ uint32_t *status_word() {
 // has been looked up on this device, 0 before. The caller has synchronised the stream.
 uint32_t take_static_status();
 
+// A GEMM that gave up on a wait may have left some of the stream-K counters counted up.
+void rezero_stream_k_counters() {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_dev.sk_counters) cudaMemsetAsync(g_dev.sk_counters, 0, gemm_stream_k_counter_words() * sizeof(uint32_t), 0);
+}
+
 // A kernel that gave up on a wait in an earlier call is reported by the next call.
 void check_earlier_kernel_status() {
   uint32_t *h;
@@ -260,6 +270,7 @@ void check_earlier_kernel_status() {
   if (h && *reinterpret_cast<volatile uint32_t *>(h) != 0) {
     uint32_t code = *reinterpret_cast<volatile uint32_t *>(h);
     *reinterpret_cast<volatile uint32_t *>(h) = 0;
+    rezero_stream_k_counters();
     aborted("an earlier kernel gave up on a bounded wait (status " + std::to_string(code) + ")");
   }
 }
@@ -496,6 +507,31 @@ struct Epilogue {
   int act = 0;
 };
 
+// The stream-K workspace, from the pool in stream 0's order the first time a GEMM runs (38 MB on a
+// 148-SM card), kept for the life of the process.
+void stream_k_workspace(GemmArgs *g) {
+  ensure_pool();
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_dev.sk_partials) {
+    void *parts = nullptr, *counters = nullptr;
+    const size_t counter_bytes = gemm_stream_k_counter_words() * sizeof(uint32_t);
+    cuda_check(cudaMallocAsync(&parts, gemm_stream_k_partial_floats() * sizeof(float), 0), "cudaMallocAsync(stream-K parts)");
+    cudaError_t e = cudaMallocAsync(&counters, counter_bytes, 0);
+    if (e == cudaSuccess) e = cudaMemsetAsync(counters, 0, counter_bytes, 0);
+    if (e != cudaSuccess) {
+      cudaFreeAsync(parts, 0);
+      if (counters) cudaFreeAsync(counters, 0);
+      cuda_check(e, "cudaMallocAsync(stream-K counters)");
+    }
+    g_dev.sk_partials = static_cast<float *>(parts);
+    g_dev.sk_counters = static_cast<uint32_t *>(counters);
+  }
+  g->sk_partials = g_dev.sk_partials;
+  g->sk_partial_floats = gemm_stream_k_partial_floats();
+  g->sk_counters = g_dev.sk_counters;
+  g->sk_counter_words = gemm_stream_k_counter_words();
+}
+
 void run_gemm(GemmKind kind, int m, int n, int k, const void *a, const void *b, const uint8_t *sfa,
               const uint8_t *sfb, const Epilogue &ep, int out_bf16, void *out) {
   GemmArgs g{};
@@ -531,6 +567,11 @@ void run_gemm(GemmKind kind, int m, int n, int k, const void *a, const void *b, 
     return v && v[0] == '1';
   }();
   g.force_single_cta = single_cta ? 1 : 0;
+  // FLINT_SM100_NO_STREAM_K=1 keeps every tile whole (for A/B measurements and the parity tests
+  // that compare the two schedules).
+  const char *no_sk = std::getenv("FLINT_SM100_NO_STREAM_K");
+  g.no_stream_k = (no_sk && no_sk[0] == '1') ? 1 : 0;
+  if (!g.no_stream_k) stream_k_workspace(&g);
   const char *why = "";
   std::pair<cudaEvent_t, cudaEvent_t> ev{nullptr, nullptr};
   if (g_timing.enabled) {
@@ -1974,6 +2015,7 @@ int32_t fl_sm100_synchronize(int32_t *kernel_status) {
     // fl_fp8_linear_static()'s kernels report through a word of their own, in the static array.
     if (code == 0) code = take_static_status();
     if (kernel_status) *kernel_status = static_cast<int32_t>(code);
+    if (code != 0) rezero_stream_k_counters();
     if (code != 0) aborted("a kernel gave up on a bounded wait (status " + std::to_string(code) + ")");
     return clear_error();
   });
@@ -2013,6 +2055,18 @@ int32_t fl_sm100_few_rows_plan(int32_t m, int32_t n, int32_t k, int32_t weight_b
     }
     for (int i = 0; i < 16; ++i) plan[i] = 0;
     skinny_plan(m, n, k, weight_bytes, activation_bytes, has_residual, plan);
+    return clear_error();
+  });
+}
+
+int32_t fl_sm100_gemm_plan(int32_t kind, int32_t m, int32_t n, int32_t k, int32_t sms, int32_t allow_stream_k, int32_t *plan) {
+  return guard([&]() -> int32_t {
+    if (!plan) invalid("plan is null");
+    if (kind < kGemmF16 || kind > kGemmNvf4) invalid("kind is 0 (half), 1 (bfloat16), 2 (e4m3) or 3 (nvfp4)");
+    if (m < 1 || n < 1 || k < 1 || sms < 2) invalid("m, n, k are positive and the device has at least two SMs");
+    int out[8];
+    gemm_plan(static_cast<GemmKind>(kind), m, n, k, sms, allow_stream_k, out);
+    for (int i = 0; i < 8; ++i) plan[i] = out[i];
     return clear_error();
   });
 }

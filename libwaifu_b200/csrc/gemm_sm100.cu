@@ -16,6 +16,18 @@
 // The accumulator is double-buffered in tensor memory so the epilogue of tile i overlaps the
 // main loop of tile i+1.
 //
+// Schedule. Tiles are handed out round by round, one per unit (a CTA or a CTA pair). When the
+// tile count is not a multiple of the unit count the last round would run nearly empty (816 pair
+// tiles on 74 pairs: eleven full rounds and one of two tiles), so, given a workspace, the last
+// full round and the remainder are pooled and their K stages dealt out evenly instead ("stream-K"
+// over the last one-and-a-bit rounds): every unit gets a contiguous run of stages of that pool,
+// which is the end of one tile, possibly whole tiles, and the beginning of another. A tile that is
+// cut this way has exactly two holders (a run is at least one tile long). Each holder's epilogue
+// warps dump their part of the fp32 accumulator into the workspace and count themselves in on a
+// per-tile, per-warp counter; whoever comes second adds the two parts (head + tail, so the sum
+// does not depend on who that was) and runs the ordinary epilogue on it. Nobody waits for
+// anybody: there is no spin on another unit's progress anywhere.
+//
 // Every operand row in a stage is 128 bytes (64 half / 128 e4m3 / 256 e2m1 elements) in the
 // 128-byte swizzle, and one tcgen05.mma consumes 32 bytes of K from every row, so the three
 // element kinds share all of the addressing and differ only in the instruction issued.
@@ -74,6 +86,55 @@ struct KernelParams {
   int out_col0;                // first destination column of this product
   int out_vector;  // the outputs' bases are 16-byte aligned: 16-byte stores; else 2-byte stores
   uint32_t *status;
+  // Schedule: `dp_rounds` rounds of whole tiles (tile = round * units + unit), then `sk_tiles`
+  // tiles from `sk_first_tile` on whose K stages are dealt out evenly over the units (0: none).
+  int dp_rounds;
+  int sk_tiles;
+  int sk_first_tile;
+  float *sk_partials;     // units * 2 slots of one tile's fp32 accumulator each (per CTA: 128 x BLOCK_N)
+  uint32_t *sk_counters;  // sk_tiles * CTAS * 8 counters, zero between launches
+};
+
+// One piece of work of a unit: the K stages [kb0, kb1) of a tile.
+struct WorkItem {
+  int tile;
+  int kb0, kb1;
+  int sk_tile;   // index among the stream-K tiles (counters), -1 for a whole tile of the data-parallel rounds
+  bool partial;  // part of a tile: the accumulator goes to the workspace
+  bool head;     // partial only: this is the tile's first part (else its last)
+};
+
+// The sequence of a unit's work items; every role of a CTA walks the same sequence.
+struct WorkWalk {
+  int unit, num_units, num_tiles, num_kb, dp_rounds, sk_first_tile;
+  long long sk_pos, sk_end;
+  int round;
+
+  __device__ __forceinline__ WorkWalk(const KernelParams &p, int unit_, int num_units_)
+      : unit(unit_), num_units(num_units_), num_tiles(p.tiles_m * p.tiles_n), num_kb(p.num_kb), dp_rounds(p.dp_rounds),
+        sk_first_tile(p.sk_first_tile), round(0) {
+    const long long total = static_cast<long long>(p.sk_tiles) * p.num_kb;
+    sk_pos = total * unit_ / num_units_;
+    sk_end = total * (unit_ + 1) / num_units_;
+  }
+
+  __device__ __forceinline__ bool next(WorkItem *it) {
+    if (round < dp_rounds) {
+      const int tile = round * num_units + unit;
+      ++round;
+      if (tile >= num_tiles) return false;  // only in the last round of a schedule without a stream-K part
+      *it = WorkItem{tile, 0, num_kb, -1, false, false};
+      return true;
+    }
+    if (sk_pos >= sk_end) return false;
+    const int t = static_cast<int>(sk_pos / num_kb);
+    const int kb0 = static_cast<int>(sk_pos - static_cast<long long>(t) * num_kb);
+    const long long left = sk_end - sk_pos;
+    const int len = left < num_kb - kb0 ? static_cast<int>(left) : num_kb - kb0;
+    *it = WorkItem{sk_first_tile + t, kb0, kb0 + len, t, len != num_kb, kb0 == 0};
+    sk_pos += len;
+    return true;
+  }
 };
 
 // CTAS == 2: a pair of CTAs (one cluster) shares a 256 x BLOCK_N tile through cta_group::2 UMMAs;
@@ -185,7 +246,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
   const bool scatter = p.num_out > 1;
 
   if (threadIdx.x == 0) {
@@ -234,12 +294,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
+      WorkWalk walk(p, unit, num_units);
+      WorkItem item;
+      while (ok && walk.next(&item)) {
         int tm, tn;
-        tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
+        tile_coords(item.tile, p.tiles_m, p.tiles_n, &tm, &tn);
         const int m0 = tm * (kBlockM * CTAS) + static_cast<int>(cta_rank) * kBlockM;
         const int n0 = tn * BLOCK_N;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = item.kb0; kb < item.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, &abort_flag)) {
             ok = false;
             break;
@@ -323,7 +385,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       int local = 0;
-      for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++local) {
+      WorkWalk walk(p, unit, num_units);
+      WorkItem item;
+      for (; ok && walk.next(&item); ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         // A tile that starts 64 rows into a 128-row scale group reads its B scale factors two
@@ -331,7 +395,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         uint32_t sfb_skip = 0;
         if constexpr (NVF4) {
           int tm, tn;
-          tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
+          tile_coords(item.tile, p.tiles_m, p.tiles_n, &tm, &tn);
           sfb_skip = ((tn * BLOCK_N) % 128) / 32;
         }
         if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, &abort_flag)) {
@@ -340,7 +404,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        const int kb_first = item.kb0;  // the item's first UMMA overwrites the accumulator
+        for (int kb = item.kb0; kb < item.kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) {
             ok = false;
             break;
@@ -360,10 +425,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
             for (int j = 0; j < kMmasPerStage; ++j) {
               if constexpr (CTAS == 2) {
-                umma_nvf4_ss_pair(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, (kb | j) != 0 ? 1u : 0u,
+                umma_nvf4_ss_pair(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, ((kb - kb_first) | j) != 0 ? 1u : 0u,
                                   sfa_tmem + j * 4, sfb_tmem + j * Cfg::kSfbColsPerMma + sfb_skip);
               } else {
-                umma_nvf4_ss(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, (kb | j) != 0 ? 1u : 0u,
+                umma_nvf4_ss(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, ((kb - kb_first) | j) != 0 ? 1u : 0u,
                              sfa_tmem + j * 4, sfb_tmem + j * Cfg::kSfbColsPerMma + sfb_skip);
               }
             }
@@ -371,9 +436,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
             for (int j = 0; j < kMmasPerStage; ++j) {
               if constexpr (CTAS == 2) {
-                umma_ss_pair<KIND>(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, (kb | j) != 0 ? 1u : 0u);
+                umma_ss_pair<KIND>(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, ((kb - kb_first) | j) != 0 ? 1u : 0u);
               } else {
-                umma_ss<KIND>(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, (kb | j) != 0 ? 1u : 0u);
+                umma_ss<KIND>(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, ((kb - kb_first) | j) != 0 ? 1u : 0u);
               }
             }
           }
@@ -408,8 +473,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t phase = 0;
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
-        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+      WorkWalk walk(p, unit, num_units);
+      WorkItem item;
+      while (ok && walk.next(&item)) {
+        for (int kb = item.kb0; kb < item.kb1; ++kb, ++it) {
           const uint32_t set = it & 1;
           if (!mbar_wait(&full_bar[stage], phase, &abort_flag) ||
               !mbar_wait(&sf_empty_bar[set], ((it >> 1) & 1) ^ 1, &abort_flag)) {
@@ -461,11 +528,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int local = 0;
       const int pw = static_cast<int>(warp) - kPusherWarp0;
       const int col = static_cast<int>(lane) * 8;  // 8 elements = 16 bytes per lane, 512 bytes per row per warp
-      for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++local) {
+      WorkWalk walk(p, unit, num_units);
+      WorkItem item;
+      for (; ok && walk.next(&item); ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         int tm, tn;
-        tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
+        tile_coords(item.tile, p.tiles_m, p.tiles_n, &tm, &tn);
         const int m0 = tm * (kBlockM * CTAS) + static_cast<int>(cta_rank) * kBlockM;
         const int n0 = tn * BLOCK_N;
         if (!mbar_wait(&tile_done_bar[acc], acc_phase, &abort_flag)) {
@@ -532,11 +601,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     float *cs_t = reinterpret_cast<float *>(smem + Cfg::kColParamOffset) + warp * 2 * HALF_N;
     float *bias_t = cs_t + HALF_N;
 
-    for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++local) {
+    WorkWalk walk(p, unit, num_units);
+    WorkItem item;
+    for (; ok && walk.next(&item); ++local) {
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
+      tile_coords(item.tile, p.tiles_m, p.tiles_n, &tm, &tn);
       const int row = tm * (kBlockM * CTAS) + static_cast<int>(cta_rank) * kBlockM + quarter * 32 + lane;
       const int n0 = tn * BLOCK_N + half * HALF_N;  // first column this warp owns
 
@@ -657,8 +728,73 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
       };
 
-      // Tensor-memory loads run one chunk ahead of the arithmetic.
       uint32_t va[32], vb[32];
+      if (item.partial) {
+        // Part of a tile's K range (the stream-K rounds): this warp's 32 rows x HALF_N columns of
+        // the accumulator go to the workspace as they are, the accumulator is handed back, and
+        // the warp counts itself in. The tile has exactly two parts; whichever warp comes second
+        // adds them, head first, and finishes the sum like any other accumulator. A partial lies
+        // chunk by chunk, four columns of 32 rows to a 512-byte line, so every store and load of
+        // a warp is one contiguous line.
+        constexpr int kWarpFloats = HALF_N * 32;
+        constexpr int kSlotFloats = CTAS * kEpilogueWarps * kWarpFloats;  // one unit's part of one tile
+        const int within = (static_cast<int>(cta_rank) * kEpilogueWarps + static_cast<int>(warp)) * kWarpFloats;
+        float *mine = p.sk_partials + (static_cast<long long>(unit) * 2 + (item.head ? 1 : 0)) * kSlotFloats + within;
+        tmem_ld_32x32(tacc, va);
+#pragma unroll 1
+        for (int c = 0; c < HALF_CHUNKS; ++c) {
+          tmem_ld_wait(va);
+          float4 *dst = reinterpret_cast<float4 *>(mine + c * 1024) + lane;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            dst[j * 32] = make_float4(__uint_as_float(va[4 * j]), __uint_as_float(va[4 * j + 1]), __uint_as_float(va[4 * j + 2]),
+                                      __uint_as_float(va[4 * j + 3]));
+          }
+          if (c + 1 < HALF_CHUNKS) tmem_ld_32x32(tacc + (c + 1) * 32, va);
+        }
+        tc_fence_before_sync();
+        __threadfence();  // this lane's part of the partial is visible before the count below says so
+        __syncwarp();
+        uint32_t arrived = 0;
+        uint32_t *counter = p.sk_counters + (item.sk_tile * CTAS + static_cast<int>(cta_rank)) * kEpilogueWarps + warp;
+        if (lane == 0) {
+          if constexpr (CTAS == 2) {
+            mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[acc]), 0));
+          } else {
+            mbar_arrive(&acc_empty_bar[acc]);
+          }
+          arrived = atomicAdd(counter, 1u);
+        }
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        if (arrived == 0) continue;  // the other holder of this tile will finish it
+        __threadfence();
+        // The other part: the tile's head is the last item of the unit before the one that holds
+        // its tail, in slot 1; the tail is that next unit's first item, in slot 0.
+        const float *other = p.sk_partials +
+                             (static_cast<long long>(item.head ? unit + 1 : unit - 1) * 2 + (item.head ? 0 : 1)) * kSlotFloats + within;
+        const float *head_part = item.head ? mine : other;
+        const float *tail_part = item.head ? other : mine;
+#pragma unroll 1
+        for (int c = 0; c < chunks; ++c) {
+          const float4 *hp = reinterpret_cast<const float4 *>(head_part + c * 1024) + lane;
+          const float4 *tp = reinterpret_cast<const float4 *>(tail_part + c * 1024) + lane;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 h4 = __ldcg(hp + j * 32);
+            const float4 t4 = __ldcg(tp + j * 32);
+            va[4 * j] = __float_as_uint(__fadd_rn(h4.x, t4.x));
+            va[4 * j + 1] = __float_as_uint(__fadd_rn(h4.y, t4.y));
+            va[4 * j + 2] = __float_as_uint(__fadd_rn(h4.z, t4.z));
+            va[4 * j + 3] = __float_as_uint(__fadd_rn(h4.w, t4.w));
+          }
+          finish_chunk(c, va);
+        }
+        __syncwarp();
+        if (lane == 0) *counter = 0;  // ready for the next launch
+        continue;
+      }
+
+      // Tensor-memory loads run one chunk ahead of the arithmetic.
       const int chunks_run = chunks;
       if (chunks_run > 0) tmem_ld_32x32(tacc, va);
 #pragma unroll 1
@@ -786,9 +922,18 @@ cudaError_t launch_one(const GemmArgs &a, KernelParams kp, uint64_t row_bytes, c
     }
     attr_set = true;
   }
-  int units = kp.tiles_m * kp.tiles_n;
-  const int max_units = sm_count() / CTAS;
-  if (units > max_units) units = max_units;
+  const int tiles = kp.tiles_m * kp.tiles_n;
+  const size_t part_floats_per_unit = static_cast<size_t>(2) * CTAS * kEpilogueWarps * (BLOCK_N / 2) * 32;
+  const bool may_stream_k = a.sk_partials && a.sk_counters && !a.no_stream_k && kp.num_out == 1 &&
+                            part_floats_per_unit * (sm_count() / CTAS) <= a.sk_partial_floats &&
+                            static_cast<size_t>(2) * sm_count() * kEpilogueWarps <= a.sk_counter_words;
+  const GemmSchedule sch = gemm_schedule(tiles, sm_count() / CTAS, kp.num_kb, may_stream_k);
+  const int units = sch.units;
+  kp.dp_rounds = sch.dp_rounds;
+  kp.sk_tiles = sch.sk_tiles;
+  kp.sk_first_tile = sch.sk_first_tile;
+  kp.sk_partials = sch.sk_tiles ? a.sk_partials : nullptr;
+  kp.sk_counters = sch.sk_tiles ? a.sk_counters : nullptr;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(units * CTAS), 1, 1);
   cfg.blockDim = dim3(kNumThreads, 1, 1);
@@ -824,6 +969,43 @@ int sm_count() {
   }
   return cached;
 }
+
+// The schedule (see the head of this file). The stream-K part pays for itself when the last round
+// would be less than 85 % full; it needs whole rounds before it and tiles of a few stages at least.
+GemmSchedule gemm_schedule(int tiles, int max_units, int num_kb, bool allow_stream_k) {
+  GemmSchedule s = {};
+  s.units = tiles < max_units ? tiles : max_units;
+  if (s.units < 1) s.units = 1;
+  const int full_rounds = tiles / s.units;
+  const int remainder = tiles % s.units;
+  if (allow_stream_k && full_rounds >= 1 && remainder > 0 && remainder * 100 <= s.units * 85 && num_kb >= 4) {
+    s.dp_rounds = full_rounds - 1;
+    s.sk_tiles = remainder + s.units;
+    s.sk_first_tile = s.dp_rounds * s.units;
+  } else {
+    s.dp_rounds = (tiles + s.units - 1) / s.units;
+  }
+  return s;
+}
+
+// Which kernel a product runs on, and its schedule; host arithmetic only.
+void gemm_plan(GemmKind kind, int m, int n, int k, int sms, int allow_stream_k, int *plan) {
+  const int row_bytes = kind == kGemmE4M3 ? k : kind == kGemmNvf4 ? k / 2 : k * 2;
+  const int num_kb = (row_bytes + kRowBytes - 1) / kRowBytes;
+  const bool pair = m > kBlockM && n > 128;
+  const bool skinny = m <= kBlockM && (n + 255) / 256 < sms;
+  const int ctas = pair ? 2 : 1;
+  const int block_n = kind == kGemmNvf4 ? 192 : (pair ? 256 : ((n <= 128 || skinny) ? 128 : 256));
+  const int tiles = ((m + kBlockM * ctas - 1) / (kBlockM * ctas)) * ((n + block_n - 1) / block_n);
+  const GemmSchedule s = gemm_schedule(tiles, sms / ctas, num_kb, allow_stream_k != 0);
+  plan[0] = ctas, plan[1] = block_n, plan[2] = tiles, plan[3] = num_kb;
+  plan[4] = s.units, plan[5] = s.dp_rounds, plan[6] = s.sk_tiles, plan[7] = s.sk_first_tile;
+}
+
+// Two parts per SM of 128 rows x 256 columns at most; a counter per epilogue warp of every tile of
+// the stream-K part, which has fewer than two rounds of tiles.
+size_t gemm_stream_k_partial_floats() { return static_cast<size_t>(sm_count()) * 2 * kBlockM * 256; }
+size_t gemm_stream_k_counter_words() { return static_cast<size_t>(sm_count()) * 2 * kEpilogueWarps; }
 
 cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
   *why = "";

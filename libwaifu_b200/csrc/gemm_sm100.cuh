@@ -63,6 +63,15 @@ struct GemmArgs {
   int out_col0;
   uint32_t *status;            // device word, zeroed by the caller; non-zero after a failed wait
   int force_single_cta;        // 1: never pair CTAs (for tests that compare the two forms)
+  // Workspace of the stream-K part of the schedule (the K stages of the last, partly filled rounds
+  // dealt out evenly over all SMs); without one every tile is computed whole by one unit.
+  // sk_partials: room for fp32 accumulator parts, gemm_stream_k_partial_floats() of them at most;
+  // sk_counters: words that are zero between launches (the kernel leaves them zero).
+  float *sk_partials;
+  size_t sk_partial_floats;
+  uint32_t *sk_counters;
+  size_t sk_counter_words;
+  int no_stream_k;             // 1: never use the workspace (for tests that compare the two schedules)
   cudaStream_t stream;
 };
 
@@ -72,5 +81,25 @@ cudaError_t launch_gemm(const GemmArgs &args, const char **why);
 
 // Number of SMs the persistent grid is sized for on the current device.
 int sm_count();
+
+// How a product's tiles are dealt out: `dp_rounds` rounds of whole tiles over `units` units
+// (tile = round * units + unit), then, from tile `sk_first_tile` on, `sk_tiles` tiles whose
+// `num_kb` K stages each are pooled and cut into `units` contiguous runs of equal length (unit u:
+// pool positions [total * u / units, total * (u + 1) / units)). sk_tiles is 0 or at least `units`,
+// so a run is at least one tile long and a tile is cut into two parts at most.
+struct GemmSchedule {
+  int units;
+  int dp_rounds;
+  int sk_tiles;
+  int sk_first_tile;
+};
+GemmSchedule gemm_schedule(int tiles, int max_units, int num_kb, bool allow_stream_k);
+// plan[8]: CTAs per unit, BLOCK_N, tiles, K stages per tile, units, dp_rounds, sk_tiles, sk_first_tile
+// for a product of the given kind and shape on a device of `sms` SMs. Host arithmetic only.
+void gemm_plan(GemmKind kind, int m, int n, int k, int sms, int allow_stream_k, int *plan);
+
+// The most workspace any launch on this device uses for its stream-K part.
+size_t gemm_stream_k_partial_floats();
+size_t gemm_stream_k_counter_words();
 
 }  // namespace flsm100

@@ -102,6 +102,7 @@ def lib() -> ctypes.CDLL:
         getattr(L, name).argtypes = [V, V, V]; getattr(L, name).restype = c_int32
     L.fl_fill.argtypes = [V, V, ctypes.c_float]; L.fl_fill.restype = c_int32
     L.fl_add.argtypes = [V, V, V, V]; L.fl_add.restype = c_int32
+    L.fl_sm100_gemm_plan.argtypes = [c_int32] * 6 + [POINTER(c_int32)]; L.fl_sm100_gemm_plan.restype = c_int32
     L.fl_sm100_selftest_wait_timeout.argtypes = [c_int32]; L.fl_sm100_selftest_wait_timeout.restype = c_int32
     L.fl_sm100_selftest_set_static_status.argtypes = [ctypes.c_uint32]; L.fl_sm100_selftest_set_static_status.restype = c_int32
     L.fl_fp8_available.argtypes = [c_int32, POINTER(c_int32)]

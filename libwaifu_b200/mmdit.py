@@ -253,24 +253,29 @@ class MMDiT:
         self.cos = ang.cos().contiguous().to(dev)  # float32 (tokens, head_dim / 2)
         self.sin = ang.sin().contiguous().to(dev)
 
-    def block(self, x, temb, layers):
+    def block(self, x, temb, layers, tap=None):
+        """One block. `tap(name, tensor) -> tensor`, when given, sees every intermediate in turn
+        (mod, qkv, qk, attention, x1, up, x2) and what it returns is used in its place: a test
+        records one backend's intermediates with it and feeds them to the other backend, so that
+        each stage of the two is compared on identical inputs."""
         c = self.cfg
         b, t, d = x.shape
         lin = self.backend.linear
-        mod = lin(self.backend.silu(temb), layers["mod"])  # (b, 6 d): the M = batch skinny linear
+        see = tap if tap is not None else (lambda name, value: value)
+        mod = see("mod", lin(self.backend.silu(temb), layers["mod"]))  # (b, 6 d): the M = batch skinny linear
         shift1, scale1, _, shift2, scale2, _ = mod.chunk(6, dim=1)   # column slices, not copies
         modf = mod.float()                                             # the gates multiply fp32 scales
         gate1, gate2 = modf[:, 2 * d:3 * d], modf[:, 5 * d:6 * d]
 
-        qkv = self.backend.modulated_linear(x, scale1, shift1, layers["qkv"])  # (b t, 3 d)
-        qkv = self.backend.qk_norm_rope(qkv, self.cos, self.sin, c.heads).view(b, t, 3, c.heads, c.head_dim)
+        qkv = see("qkv", self.backend.modulated_linear(x, scale1, shift1, layers["qkv"]))  # (b t, 3 d)
+        qkv = see("qk", self.backend.qk_norm_rope(qkv, self.cos, self.sin, c.heads)).view(b, t, 3, c.heads, c.head_dim)
         # q, k, v as (b, heads, t, head_dim) views of the one buffer: nothing is copied, and the
         # attention output comes back token-major, which is the layout the next projection reads
-        a = self.backend.attention(qkv)  # joint attention over text + image tokens
-        x = self.backend.gated_linear(a, layers["out"], gate1, x)
+        a = see("attention", self.backend.attention(qkv))  # joint attention over text + image tokens
+        x = see("x1", self.backend.gated_linear(a, layers["out"], gate1, x))
 
-        u = self.backend.modulated_linear(x, scale2, shift2, layers["up"], act=1)  # GELU-tanh in the epilogue
-        x = self.backend.gated_linear(u, layers["down"], gate2, x)
+        u = see("up", self.backend.modulated_linear(x, scale2, shift2, layers["up"], act=1))  # GELU-tanh in the epilogue
+        x = see("x2", self.backend.gated_linear(u, layers["down"], gate2, x))
         return x
 
     def embed(self, tokens, context, sinusoid):

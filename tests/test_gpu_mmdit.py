@@ -7,13 +7,17 @@ Two sizes. A reduced one checks the composition and counts the launches. The ben
 check each stage on identical inputs -- the ways in, every block, the last layer -- and then the
 whole chain.
 
-Bounds, relative L2 of bfloat16 outputs, and why they are what they are. Per-kernel parity is held
-to 5e-3 by the kernels' own tests; here a stage chains several quantised linears, and a
-per-token quantiser is discontinuous: a last-bit difference in a row's largest value moves that
-row's scale and with it many codes. On identical inputs a stage stays within 1e-2 (the ways in and
-the last layer, two linears deep, within 5e-3); the chain of every stage, where each side quantises
-its own slightly different activations, within 3e-2. The gated residual is rounded once on the GPU
-(in the projection's epilogue) and three times in the CPU's spelled-out form."""
+Bounds, relative L2 of bfloat16 outputs, and why they are what they are. A per-token quantiser is
+discontinuous: an input that differs in its last 16-bit place lands on another e4m3 code one time in
+sixteen, and a row whose largest value moved gets another scale altogether; each flipped code is an
+error of a whole e4m3 step (6 %) in that element. So the test gives every stage of the CPU side the
+GPU's own output of the stage before it: on identical inputs every stage -- each linear with its
+fused step, the q/k norm and rotation, attention, the gated residuals, the ways in, the last
+layer -- stays within the kernels' own 5e-3. Chained, each side quantising its own slightly
+different activations, two blocks come to a few per cent (measured 4.6e-2 at these widths); the
+chained bound of 8e-2 is there to catch a wrong operand or a missing term, which give O(1). The
+gated residual is rounded once on the GPU (in the projection's epilogue) and three times in the
+CPU's spelled-out form."""
 import numpy as np
 import pytest
 
@@ -79,12 +83,21 @@ def test_benchmark_widths_stage_by_stage_and_chained(flint, oracle):
         x_c, emb_c = cpu.embed(tokens, context, sinusoid)
         errors["embed: stream"] = (rel(oracle, x_g, x_c), 5e-3)
         errors["embed: timestep"] = (rel(oracle, emb_g, emb_c), 5e-3)
-        # every block on the GPU's own input
+        # every stage of every block on the GPU's own output of the stage before it
         x = x_g
         for i, (lg, lc) in enumerate(zip(gpu.layers, cpu.layers)):
-            y_g = gpu.block(x, emb_g, lg)
-            y_c = cpu.block(x.cpu(), emb_g.cpu(), lc)
-            errors[f"block {i}"] = (rel(oracle, y_g, y_c), 1e-2)
+            seen = {}
+
+            def record(name, value):
+                seen[name] = value.clone()  # the q/k norm and rotation works in place on the qkv buffer
+                return value
+
+            def compare_and_replace(name, value, i=i, seen=seen):
+                errors[f"block {i}: {name}"] = (rel(oracle, seen[name], value), 5e-3)
+                return seen[name].cpu()
+
+            y_g = gpu.block(x, emb_g, lg, tap=record)
+            cpu.block(x.cpu(), emb_g.cpu(), lc, tap=compare_and_replace)
             x = y_g
         # the last layer on the GPU's own input
         v_g = gpu.final(x, emb_g)
@@ -92,7 +105,7 @@ def test_benchmark_widths_stage_by_stage_and_chained(flint, oracle):
         errors["final"] = (rel(oracle, v_g, v_c), 5e-3)
         # and everything chained, each side on its own activations
         errors["chained step"] = (rel(oracle, gpu.step(tokens.cuda(), context.cuda(), sinusoid.cuda()),
-                                      cpu.step(tokens, context, sinusoid)), 3e-2)
+                                      cpu.step(tokens, context, sinusoid)), 8e-2)
     flint.synchronize()
     report = ", ".join(f"{k} {v[0]:.2e}" for k, v in errors.items())
     print("relative L2 per stage:", report)
