@@ -48,6 +48,11 @@ WORKLOADS = {
     # 16-bit activation row against an e4m3 weight through the unchanged fl_fp8_matmul; HBM-bound
     "skinny_decode": dict(m=1, gemms=[(16384, 3072)], kind="fp8_upcast",
                           desc="fl_fp8_matmul 1x16384x3072, fp16 activation x e4m3 weight, one scale"),
+    # handled by run_legacy(): the reference's own entry point and benchmark shapes
+    # (flint/cuda/gemm_fp8_cutlass_test.cc:365-406): a half activation that is NOT narrowed against an
+    # e4m3 weight with one scale and a bias, through the unchanged fl_fp8_matmul_add
+    "legacy_fp8_matmul": dict(m=4096, gemms=[(12288, 3072)], kind="fp8_upcast",
+                              desc="fl_fp8_matmul_add 4096x12288x3072, fp16 activation x e4m3 weight, one scale, bias"),
     # handled by run_attention(): the denoise step's joint attention through fl_attention
     "attention_step": dict(m=2 * 4352, gemms=[], kind="bf16",
                            desc="fl_attention 2 x 24 heads x 4352 tokens x 128, bf16, no mask (the denoise step's attention)"),
@@ -989,6 +994,159 @@ def run_skinny(args):
         dist.destroy_process_group()
 
 
+def run_legacy(args):
+    """The legacy_fp8_matmul workload: flint's own fl_fp8_matmul_add (fp16 activation kept in half,
+    e4m3 weight widened inside the kernel, one fp32 scale, a bias pre-expanded to the product's
+    shape as the Rust wrapper hands it over) on the reference's benchmark shapes. Tensor-bound on
+    the 16-bit tcgen05 kind: the roofline is the measured bf16 GEMM throughput. Every rank runs
+    its own batch of rows."""
+    import ctypes
+    import numpy as np
+    import torch
+    from libwaifu_b200 import flint as F
+    wl = dict(WORKLOADS["legacy_fp8_matmul"])
+    if args.rows:
+        wl["m"] = args.rows
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    torch.cuda.set_device(local)
+    F.set_device(local)
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+    f16 = F.DType.FLOAT16
+    gen = torch.Generator(device="cuda").manual_seed(rank)
+    L = F.lib()
+
+    def wrap(t, dt):
+        return F.Tensor.from_device_ptr(t.data_ptr(), tuple(t.shape), dt, keepalive=t)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def make(m, n, k, sets):
+        xs = [wrap(torch.randn(m, k, device="cuda", dtype=torch.float16, generator=gen), f16) for _ in range(sets)]
+        ws = []
+        for _ in range(sets):
+            w = torch.randn(n, k, device="cuda", dtype=torch.float32, generator=gen) * 0.02
+            codes, _ = F.quantize_fp8_rows(wrap(w, F.DType.FLOAT))
+            ws.append(codes)
+            del w
+        F.synchronize()
+        scale = wrap(torch.full((1,), 0.02 * 4.0 / 448.0, device="cuda", dtype=torch.float32), F.DType.FLOAT)
+        bias = wrap(torch.randn(n, device="cuda", dtype=torch.float16, generator=gen) * 0.01, f16)
+        out = F.Tensor.empty((m, n), f16)
+        expanded = F._broadcast_to(bias, out)  # a zero-stride view, waifu/src/flint/functional.rs:80-108,698
+
+        def call(i):
+            F.check(L.fl_fp8_matmul_add(xs[i % sets].raw(), ws[i % sets].raw(), scale.raw(), expanded.raw(), out.raw()))
+        return call, out, (xs, ws, scale, bias, expanded)
+
+    def time_calls(call, warmup, steps):
+        for i in range(warmup):
+            call(i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for i in range(steps):
+            call(warmup + i)
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1) / steps)
+
+    m = wl["m"]
+    (n, k), = wl["gemms"]
+    call, out, keep = make(m, n, k, args.rotate)
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = F.launch_count()
+    ms_step = time_calls(call, max(args.warmup, 3), args.steps)
+    launches = F.launch_count() - launches0
+    F.gemm_timing(True)
+    F.gemm_timing_read()
+    for i in range(args.steps):
+        call(i)
+    gemm_ms, gemm_launches = F.gemm_timing_read()
+    F.gemm_timing(False)
+    sampler.stop_flag.set()
+    sampler.join(timeout=5)
+    flops = 2.0 * m * n * k
+    value = world * flops / (ms_step * 1e-3) / 1e12
+
+    others = {}
+    for (m2, n2, k2) in [(256, 3072, 3072), (4096, 3072, 3072)]:
+        c2, _, keep2 = make(m2, n2, k2, 4)
+        t = time_calls(c2, 3, max(20, min(args.steps, 200)))
+        others[f"{m2}x{n2}x{k2}"] = {"ms": t, "tflops": 2.0 * m2 * n2 * k2 / (t * 1e-3) / 1e12}
+        del c2, keep2
+
+    # end to end: the activation from pinned host memory, the product back
+    host_x = F.Tensor.empty((m, k), f16, F.Device.CUDA_HOST)
+    host_y = F.Tensor.empty((m, n), f16, F.Device.CUDA_HOST)
+    p = ctypes.c_void_p()
+    F.check(L.fl_tensor_data_get_host_ptr(host_x._data, ctypes.byref(p)))
+    hx = np.ctypeslib.as_array(ctypes.cast(p.value, ctypes.POINTER(ctypes.c_uint16)), shape=(m * k,))
+    hx[:] = np.random.default_rng(7 + rank).standard_normal(m * k).astype(np.float16).view(np.uint16)
+    xs, ws, scale, bias, expanded = keep
+
+    def e2e_step(i):
+        xd, pending = F.transfer_async(host_x)
+        pending.wait()
+        F.check(L.fl_fp8_matmul_add(xd.raw(), ws[i % len(ws)].raw(), scale.raw(), expanded.raw(), out.raw()))
+        F.transfer_to_host_async(out, host_y).wait_sync()
+
+    e2e_ms = time_calls(e2e_step, 2, max(3, min(args.steps, 20)))
+
+    bf16_peak, _, peak_kind = measured_peaks(sampler.summary())
+    achieved = flops * args.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+    roofline = {"bound": "tensor", "kernel": "gemm_tn_kernel (16-bit kind, e4m3 weight widened in shared memory)",
+                "achieved": achieved, "peak": bf16_peak, "unit": UNIT, "frac": achieved / bf16_peak if achieved else None,
+                "peak_source": f"bf16 cuBLAS, of {peak_kind}", "launches": gemm_launches,
+                "avg_launch_ms": gemm_ms / gemm_launches if gemm_launches else None, "traffic": None,
+                "algorithmic_bytes_per_step": m * k * 2 + n * k + m * n * 2 + n * 2 + 4}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        rows = min(m, args.reference_rows)
+        cstep, kind, cores = cpu_reference_step_factory(wl, rows)
+        cstep()
+        best = None
+        for _ in range(3):
+            t0 = time.perf_counter()
+            cstep()
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        cpu_baseline = {"value": 2.0 * rows * n * k / best / 1e12, "unit": UNIT, "cores": cores, "kind": kind,
+                        "sample": f"{rows} of {m} rows, the whole call (widen, fp32 GEMM, scale) on the host, best of 3"}
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 x e4m3 -> f32 accumulate", "data": "synthetic",
+            "config": {"workload": "legacy_fp8_matmul", "what": wl["desc"], "parallelism": f"batch-sharded x{world}",
+                       "l2": f"{args.rotate} rotating operand sets", "other_shapes": others,
+                       "published": "the reference reports 44-46 TFLOP/s for these shapes on an RTX 5060 Ti (docs/fp8.md), other hardware"},
+            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": m * k * 2, "d2h_bytes_per_step": m * n * 2},
+            "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu_baseline, "clocks": sampler.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def run_attention(args):
     """The attention_step workload: the denoise step's joint attention (batch 2, 24 heads of 128,
     4352 tokens, no mask) through fl_attention on q, k, v laid out as the fused projection leaves
@@ -1178,6 +1336,10 @@ def main():
         if args.steps == 1000:
             args.steps = 20000  # 20 us a step: long enough for the clock sampler to see the run
         return run_skinny(args)
+    if args.workload == "legacy_fp8_matmul" and args.impl == "ours":
+        if args.steps == 1000:
+            args.steps = 200
+        return run_legacy(args)
     if args.workload == "attention_step" and args.impl == "reference":
         if args.steps == 1000:
             args.steps = 3

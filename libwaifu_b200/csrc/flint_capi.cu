@@ -533,8 +533,9 @@ void stream_k_workspace(GemmArgs *g) {
 }
 
 void run_gemm(GemmKind kind, int m, int n, int k, const void *a, const void *b, const uint8_t *sfa,
-              const uint8_t *sfb, const Epilogue &ep, int out_bf16, void *out) {
+              const uint8_t *sfb, const Epilogue &ep, int out_bf16, void *out, bool b_is_e4m3 = false) {
   GemmArgs g{};
+  g.b_is_e4m3 = b_is_e4m3 ? 1 : 0;
   g.kind = kind;
   g.m = m;
   g.n = n;
@@ -1032,30 +1033,50 @@ int32_t fl_fp8_matmul_add(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tens
       }
     }
 
-    // The weight is widened to the activation's 16-bit type (exactly) into scratch, then
-    // multiplied by the 16-bit tcgen05 kernel; the scale and the addend go into the epilogue.
+    // Half activations (the reference's contract): the 16-bit tcgen05 kernel in its mixed form. The
+    // weight reaches shared memory as e4m3 bytes and is widened there, exactly, to half (flint widens
+    // in registers inside its main loop, flint/cuda/gemm_fp8_cutlass.cu:142-149); the scale and the
+    // addend go into the epilogue; no widened copy of the weight exists anywhere. Scratch is only
+    // needed for operands whose view starts off a 16-byte boundary and for an addend no epilogue
+    // can index.
+    // bfloat16 activations (additive; the reference has none): one UMMA takes both operands in one
+    // 16-bit format, and e4m3 -> bfloat16 has no conversion instruction, so the weight is widened
+    // to bfloat16 by a pass of its own into scratch (rows * k * 2 bytes) and the plain kernel runs.
     Scratch scratch;
-    const size_t w_off = scratch.reserve(static_cast<size_t>(rows) * k * 2);
-    size_t a_off = 0;
+    size_t a_off = 0, w_off = 0;
     const bool a_misaligned = !aligned16(raw_ptr(a));
+    const bool w_misaligned = !aligned16(raw_ptr(weight));
     if (a_misaligned) a_off = scratch.reserve(static_cast<size_t>(m) * k * 2);
+    if (is_bf16) {
+      w_off = scratch.reserve(static_cast<size_t>(rows) * k * 2);
+    } else if (w_misaligned) {
+      w_off = scratch.reserve(static_cast<size_t>(rows) * k);
+    }
     AddendResolver res;
     res.prepare(addend, out, &scratch);
-    uint8_t *base = scratch.commit();
+    uint8_t *base = scratch.used ? scratch.commit() : nullptr;
 
-    cuda_check(widen_e4m3(raw_ptr(weight), static_cast<int64_t>(rows) * k, base + w_off, is_bf16, 0), "widening");
     const void *a_ptr = raw_ptr(a);
+    const void *w_ptr = raw_ptr(weight);
     if (a_misaligned) {
       cuda_check(cudaMemcpyAsync(base + a_off, a_ptr, static_cast<size_t>(m) * k * 2, cudaMemcpyDeviceToDevice, 0),
                  "staging the left operand");
       a_ptr = base + a_off;
     }
+    if (is_bf16) {
+      cuda_check(widen_e4m3(raw_ptr(weight), static_cast<int64_t>(rows) * k, base + w_off, 1, 0), "widening");
+      w_ptr = base + w_off;
+    } else if (w_misaligned) {
+      cuda_check(cudaMemcpyAsync(base + w_off, w_ptr, static_cast<size_t>(rows) * k, cudaMemcpyDeviceToDevice, 0),
+                 "staging the weight");
+      w_ptr = base + w_off;
+    }
     Epilogue ep;
     ep.col_scale = reinterpret_cast<const float *>(raw_ptr(scale));
     ep.col_scale_scalar = 1;
     res.resolve(base, m, rows, &ep);
-    run_gemm(is_bf16 ? kGemmBF16 : kGemmF16, m, rows, k, a_ptr, base + w_off, nullptr, nullptr, ep, is_bf16,
-             raw_ptr(out));
+    run_gemm(is_bf16 ? kGemmBF16 : kGemmF16, m, rows, k, a_ptr, w_ptr, nullptr, nullptr, ep, is_bf16, raw_ptr(out),
+             /*b_is_e4m3=*/!is_bf16);
     return clear_error();
   });
 }

@@ -12,7 +12,12 @@
 //              accumulators to the epilogue
 //   warps 10-11 pushers, only at work in the scatter form (a product gathered on several GPUs):
 //              once the epilogue has written a tile into this GPU's matrix they copy its rows to
-//              the peers' matrices, 512 contiguous bytes per store instruction, over NVLink
+//              the peers' matrices, 512 contiguous bytes per store instruction, over NVLink.
+//              In the mixed form (a 16-bit activation against an e4m3 weight that is NOT narrowed,
+//              flint's fl_fp8_matmul) they are the converters instead: the weight tile arrives
+//              as e4m3 bytes, they widen it exactly to half into the swizzled 16-bit tile the
+//              UMMA reads, so the weight crosses HBM and L2 once, as bytes (the reference widens
+//              in registers inside its main loop, flint/cuda/gemm_fp8_cutlass.cu:142-149)
 // The accumulator is double-buffered in tensor memory so the epilogue of tile i overlaps the
 // main loop of tile i+1.
 //
@@ -22,11 +27,13 @@
 // full round and the remainder are pooled and their K stages dealt out evenly instead ("stream-K"
 // over the last one-and-a-bit rounds): every unit gets a contiguous run of stages of that pool,
 // which is the end of one tile, possibly whole tiles, and the beginning of another. A tile that is
-// cut this way has exactly two holders (a run is at least one tile long). Each holder's epilogue
-// warps dump their part of the fp32 accumulator into the workspace and count themselves in on a
-// per-tile, per-warp counter; whoever comes second adds the two parts (head + tail, so the sum
-// does not depend on who that was) and runs the ordinary epilogue on it. Nobody waits for
-// anybody: there is no spin on another unit's progress anywhere.
+// cut this way has exactly two holders (a run is at least one tile long). A holder's epilogue
+// warps look at a per-tile, per-warp counter: if the other holder has not counted itself in yet,
+// they write their part of the fp32 accumulator to the workspace and count themselves in; if it
+// has, they add its part to their accumulator (head + tail, the same sum whoever comes second)
+// and run the ordinary epilogue on it. A unit computes its head piece first and its tail piece
+// last, so the write happens early, under the main loops that follow, and the end of the kernel
+// only has the read. Nobody waits for anybody: there is no spin on another unit's progress.
 //
 // Every operand row in a stage is 128 bytes (64 half / 128 e4m3 / 256 e2m1 elements) in the
 // 128-byte swizzle, and one tcgen05.mma consumes 32 bytes of K from every row, so the three
@@ -60,6 +67,7 @@ constexpr int kNumThreads = 384;
 // flight at one time share a compact set of A and B rows in L2. A matrix up to kBandMax tile
 // columns wide is one band (every A row block is then fetched from HBM once); wider ones are cut
 // into bands of kBandTiles.
+constexpr int kStreamKMinSavedStages = 40;
 constexpr int kBandTiles = 8;
 constexpr int kBandMax = 16;
 
@@ -85,6 +93,7 @@ struct KernelParams {
   long long out_ld;            // pitch of the destination matrices in elements
   int out_col0;                // first destination column of this product
   int out_vector;  // the outputs' bases are 16-byte aligned: 16-byte stores; else 2-byte stores
+  int out_staged;  // results leave through shared memory and TMA stores (tmap_out), residual rows come in coalesced
   uint32_t *status;
   // Schedule: `dp_rounds` rounds of whole tiles (tile = round * units + unit), then `sk_tiles`
   // tiles from `sk_first_tile` on whose K stages are dealt out evenly over the units (0: none).
@@ -104,18 +113,27 @@ struct WorkItem {
   bool head;     // partial only: this is the tile's first part (else its last)
 };
 
-// The sequence of a unit's work items; every role of a CTA walks the same sequence.
+// The sequence of a unit's work items; every role of a CTA walks the same sequence: the rounds of
+// whole tiles, then the unit's run [sk_begin, sk_end) of the stream-K pool in this order: the
+// beginning of the tile the run ends in (a head), the whole tiles inside the run, the end of the
+// tile the run starts in (a tail). That order makes every cut tile's head the first thing its
+// holder does in this part and its tail the last thing the other holder does: the head's
+// accumulator goes to the workspace early, under the main loops that follow, and at the end of the
+// kernel a unit only reads one finished part back.
 struct WorkWalk {
   int unit, num_units, num_tiles, num_kb, dp_rounds, sk_first_tile;
-  long long sk_pos, sk_end;
+  long long sk_begin, sk_end;
   int round;
+  int phase;       // of the stream-K part: 0 head, 1 whole tiles, 2 tail, 3 done
+  int whole_tile;  // next whole tile of the run (index within the stream-K tiles)
 
   __device__ __forceinline__ WorkWalk(const KernelParams &p, int unit_, int num_units_)
       : unit(unit_), num_units(num_units_), num_tiles(p.tiles_m * p.tiles_n), num_kb(p.num_kb), dp_rounds(p.dp_rounds),
-        sk_first_tile(p.sk_first_tile), round(0) {
+        sk_first_tile(p.sk_first_tile), round(0), phase(p.sk_tiles > 0 ? 0 : 3) {
     const long long total = static_cast<long long>(p.sk_tiles) * p.num_kb;
-    sk_pos = total * unit_ / num_units_;
+    sk_begin = total * unit_ / num_units_;
     sk_end = total * (unit_ + 1) / num_units_;
+    whole_tile = static_cast<int>((sk_begin + num_kb - 1) / num_kb);
   }
 
   __device__ __forceinline__ bool next(WorkItem *it) {
@@ -126,21 +144,41 @@ struct WorkWalk {
       *it = WorkItem{tile, 0, num_kb, -1, false, false};
       return true;
     }
-    if (sk_pos >= sk_end) return false;
-    const int t = static_cast<int>(sk_pos / num_kb);
-    const int kb0 = static_cast<int>(sk_pos - static_cast<long long>(t) * num_kb);
-    const long long left = sk_end - sk_pos;
-    const int len = left < num_kb - kb0 ? static_cast<int>(left) : num_kb - kb0;
-    *it = WorkItem{sk_first_tile + t, kb0, kb0 + len, t, len != num_kb, kb0 == 0};
-    sk_pos += len;
-    return true;
+    if (phase == 0) {
+      phase = 1;
+      const int t = static_cast<int>(sk_end / num_kb);
+      const int len = static_cast<int>(sk_end - static_cast<long long>(t) * num_kb);
+      if (len > 0) {  // the run ends inside tile t: its first `len` stages
+        *it = WorkItem{sk_first_tile + t, 0, len, t, true, true};
+        return true;
+      }
+    }
+    if (phase == 1) {
+      if (static_cast<long long>(whole_tile + 1) * num_kb <= sk_end) {
+        *it = WorkItem{sk_first_tile + whole_tile, 0, num_kb, whole_tile, false, false};
+        ++whole_tile;
+        return true;
+      }
+      phase = 2;
+    }
+    if (phase == 2) {
+      phase = 3;
+      const int t = static_cast<int>(sk_begin / num_kb);
+      const int kb0 = static_cast<int>(sk_begin - static_cast<long long>(t) * num_kb);
+      if (kb0 > 0) {  // the run starts inside tile t: its stages from kb0 on
+        *it = WorkItem{sk_first_tile + t, kb0, num_kb, t, true, false};
+        return true;
+      }
+    }
+    return false;
   }
 };
 
 // CTAS == 2: a pair of CTAs (one cluster) shares a 256 x BLOCK_N tile through cta_group::2 UMMAs;
 // each CTA stages its own 128 rows of A and its own half of the BLOCK_N rows of B.
-template <int BLOCK_N, bool NVF4, int CTAS = 1>
+template <int BLOCK_N, bool NVF4, int CTAS = 1, bool B8 = false>
 struct Config {
+  static_assert(!(NVF4 && B8), "the mixed form is a 16-bit kind");
   static_assert(BLOCK_N % 64 == 0, "each epilogue warp takes whole 32-column chunks of half a tile");
   static constexpr int kABytes = kBlockM * kRowBytes;
   static constexpr int kBRows = BLOCK_N / CTAS;
@@ -150,16 +188,27 @@ struct Config {
   static constexpr int kSfbGroups = NVF4 ? (BLOCK_N + 127) / 128 : 0;
   static constexpr int kSfaBytes = NVF4 ? kMmasPerStage * kSfTileBytes : 0;
   static constexpr int kSfbBytes = NVF4 ? kSfbGroups * kMmasPerStage * kSfTileBytes : 0;
-  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  // Mixed form: 64 raw e4m3 bytes per B row per stage (the 64 K positions a 16-bit stage holds).
+  static constexpr int kRawRowBytes = 64;
+  static constexpr int kRawBytes = B8 ? kBRows * kRawRowBytes : 0;
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes + kRawBytes;
   // Each epilogue warp keeps its own copy of its columns' scale and bias as fp32 (a private copy
   // needs no barrier between warps, so no wait in the epilogue is unbounded).
   static constexpr int kHalfN = BLOCK_N / 2;
   static constexpr int kColParamBytes = kEpilogueWarps * 2 * kHalfN * 4;
-  static constexpr int kSmemBudget = 227 * 1024 - 2048 - kColParamBytes;
+  // Each epilogue warp also has 32 rows x 64 bytes of its own (one 32-column chunk of 16-bit
+  // results in the 64-byte swizzle) through which results leave by TMA store and residual rows
+  // arrive by coalesced loads: a lane owns a row of the accumulator, and 16-byte accesses to 32
+  // different rows of global memory per instruction are what bounded the epilogue before.
+  static constexpr int kOutStageBytesPerWarp = 32 * 64;
+  static constexpr int kOutStageBytes = kEpilogueWarps * kOutStageBytesPerWarp;
+  static constexpr int kSmemBudget = 227 * 1024 - 2048 - kColParamBytes - kOutStageBytes;
   static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kColParamOffset = kStages * kStageBytes;
+  static constexpr int kOutStageOffset = kStages * kStageBytes;  // 1024-byte aligned (stage sizes are)
+  static constexpr int kColParamOffset = kOutStageOffset + kOutStageBytes;
   static constexpr int kSmemBytes = kColParamOffset + kColParamBytes + 1024;  // + slack to align to 1024
+  static_assert(kStageBytes % 512 == 0, "the output staging behind the stages has to stay 512-byte aligned");
   // Tensor memory columns: two accumulators, then two sets of one stage's scale factors. The
   // copies into a set are issued by a thread of their own, a stage ahead of the MMAs that read
   // the other set: issued by the MMA thread itself they execute in order with its MMAs, and
@@ -216,13 +265,13 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   *tn = band * band_tiles + (r - (*tm) * width);
 }
 
-template <int KIND, int BLOCK_N, int CTAS>
+template <int KIND, int BLOCK_N, int CTAS, bool B8>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-               const KernelParams p) {
+               const __grid_constant__ CUtensorMap tmap_out, const KernelParams p) {
   constexpr bool NVF4 = (KIND == kKindNvf4);
-  using Cfg = Config<BLOCK_N, NVF4, CTAS>;
+  using Cfg = Config<BLOCK_N, NVF4, CTAS, B8>;
   constexpr int STAGES = Cfg::kStages;
   // A work unit is one CTA, or one pair of CTAs; rank 0 of a pair is its leader: it owns the
   // barriers both producers signal and it alone issues the UMMAs.
@@ -241,6 +290,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __shared__ __align__(8) uint64_t tile_done_bar[2];  // epilogue -> pushers: the tile is in this GPU's matrix
   __shared__ __align__(8) uint64_t sf_full_bar[2];    // NVFP4: a set of scale factors is in tensor memory
   __shared__ __align__(8) uint64_t sf_empty_bar[2];   // NVFP4: the MMAs that read the set are done
+  __shared__ __align__(8) uint64_t raw_full_bar[B8 ? STAGES : 1];  // mixed form: a stage's e4m3 weight bytes have landed
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile uint32_t abort_flag;
 
@@ -251,8 +301,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
+      // Mixed form: a stage is full when the A bytes have landed (the producer's arrival with
+      // its byte count) and every converter warp of the unit has written its share of B.
+      mbar_init(&full_bar[s], B8 ? 1 + kPusherWarps * CTAS : 1);
       mbar_init(&empty_bar[s], 1);
+      if constexpr (B8) mbar_init(&raw_full_bar[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&acc_full_bar[s], 1);
@@ -268,6 +321,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == kProducerWarp && lane == 0) {
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (p.out_staged) tma_prefetch_desc(&tmap_out);
   }
   if (warp == kMmaWarp) {
     tmem_alloc<CTAS>(&tmem_base_slot, Cfg::kTmemCols);
@@ -287,6 +341,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   auto stage_b = [&](int s) { return smem + s * Cfg::kStageBytes + Cfg::kABytes; };
   auto stage_sfa = [&](int s) { return smem + s * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBBytes; };
   auto stage_sfb = [&](int s) { return smem + s * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBBytes + Cfg::kSfaBytes; };
+  auto stage_raw = [&](int s) { return smem + s * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBBytes; };
+  (void)stage_raw;
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ producer
@@ -313,7 +369,20 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           // BLOCK_N columns).
           const int sfa_row = (tm * CTAS + static_cast<int>(cta_rank)) * p.sf_k_tiles + kb * kMmasPerStage;
           const int sfb_row0 = (n0 / 128) * p.sf_k_tiles + kb * kMmasPerStage;
-          if constexpr (CTAS == 2) {
+          if constexpr (B8) {
+            // The weight's bytes go to the raw part of the stage under a barrier of this CTA's own,
+            // which its converter warps wait on; only A counts on the stage's barrier.
+            mbar_arrive_expect_tx(&raw_full_bar[stage], Cfg::kRawBytes);
+            tma_load_2d(stage_raw(stage), &tmap_b, &raw_full_bar[stage], kb * Cfg::kRawRowBytes,
+                        n0 + static_cast<int>(cta_rank) * Cfg::kBRows);
+            if constexpr (CTAS == 2) {
+              if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kABytes);
+              tma_load_2d_pair(stage_a(stage), &tmap_a, map_to_cta(smem_u32(&full_bar[stage]), 0), kb * kRowBytes, m0);
+            } else {
+              mbar_arrive_expect_tx(&full_bar[stage], Cfg::kABytes);
+              tma_load_2d(stage_a(stage), &tmap_a, &full_bar[stage], kb * kRowBytes, m0);
+            }
+          } else if constexpr (CTAS == 2) {
             // Both CTAs' bytes are counted on the leader's barrier, which the leader arms.
             if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
             const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
@@ -356,6 +425,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0 && leader) {
       // e4m3 is format 0 of kind::f8f6f4; fp16 / bf16 are formats 0 / 1 of kind::f16.
+      // (The mixed form exists for half only: both operands of a UMMA share one 16-bit format.)
       constexpr uint32_t kFmt = (KIND == kKindBF16) ? 1u : 0u;
       constexpr uint32_t idesc =
           NVF4 ? umma_idesc_nvf4(kBlockM * CTAS, BLOCK_N) : umma_idesc(kBlockM * CTAS, BLOCK_N, kFmt, kFmt);
@@ -406,7 +476,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
         const int kb_first = item.kb0;  // the item's first UMMA overwrites the accumulator
         for (int kb = item.kb0; kb < item.kb1; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) {
+          // (mixed form in a pair: the other CTA's converters wrote its half of B and arrived from there)
+          if (!((B8 && CTAS == 2) ? mbar_wait_cluster(&full_bar[stage], phase, &abort_flag)
+                                  : mbar_wait(&full_bar[stage], phase, &abort_flag))) {
             ok = false;
             break;
           }
@@ -521,6 +593,58 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         atomicCAS(p.status, 0u, static_cast<uint32_t>(kStatusMmaTimeout));
       }
     }
+  } else if (B8 && warp >= kPusherWarp0) {
+    // ------------------------------------------------------------------ converters (mixed form)
+    // 16 e4m3 bytes of a row -> 16 halves = two 16-byte pieces of the row's 128 bytes in the
+    // 128-byte swizzle (piece index xor row % 8). A warp's 32 lanes take 8 rows x 4 pieces: the
+    // reads are 512 contiguous bytes, the writes touch every bank four times, which is the least
+    // 512 bytes can.
+    const int cw = static_cast<int>(warp) - kPusherWarp0;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    WorkWalk walk(p, unit, num_units);
+    WorkItem item;
+    while (ok && walk.next(&item)) {
+      for (int kb = item.kb0; kb < item.kb1; ++kb) {
+        if (!mbar_wait(&raw_full_bar[stage], phase, &abort_flag)) {
+          ok = false;
+          break;
+        }
+        const uint8_t *raw = stage_raw(stage);
+        uint8_t *b16 = stage_b(stage);
+#pragma unroll 4
+        for (int piece = cw * 32 + static_cast<int>(lane); piece < Cfg::kBRows * 4; piece += kPusherWarps * 32) {
+          const uint32_t r = static_cast<uint32_t>(piece) >> 2, q = static_cast<uint32_t>(piece) & 3;
+          const uint4 v = *reinterpret_cast<const uint4 *>(raw + piece * 16);
+          uint4 lo, hi;
+          e4m3x4_to_f16x4(v.x, &lo.x, &lo.y);
+          e4m3x4_to_f16x4(v.y, &lo.z, &lo.w);
+          e4m3x4_to_f16x4(v.z, &hi.x, &hi.y);
+          e4m3x4_to_f16x4(v.w, &hi.z, &hi.w);
+          uint8_t *row_base = b16 + r * kRowBytes;
+          *reinterpret_cast<uint4 *>(row_base + (((2 * q) ^ (r & 7)) << 4)) = lo;
+          *reinterpret_cast<uint4 *>(row_base + (((2 * q + 1) ^ (r & 7)) << 4)) = hi;
+        }
+        fence_proxy_async_smem();  // the UMMA reads these bytes through the async proxy
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CTAS == 2) {
+            mbar_arrive_cluster(map_to_cta(smem_u32(&full_bar[stage]), 0));
+          } else {
+            mbar_arrive(&full_bar[stage]);
+          }
+        }
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    if (!ok && lane == 0) {
+      abort_flag = 1;
+      atomicCAS(p.status, 0u, static_cast<uint32_t>(kStatusProducerTimeout));
+    }
   } else if (warp >= kPusherWarp0) {
     // ------------------------------------------------------------------ pushers (scatter form)
     if (scatter && p.out_vector) {
@@ -600,6 +724,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const bool res_vec_ok = has_res && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0 && (p.residual_ld % 8) == 0;
     float *cs_t = reinterpret_cast<float *>(smem + Cfg::kColParamOffset) + warp * 2 * HALF_N;
     float *bias_t = cs_t + HALF_N;
+    const bool staged = p.out_staged != 0;
+    uint8_t *obuf = smem + Cfg::kOutStageOffset + warp * Cfg::kOutStageBytesPerWarp;
+    // Where this lane's row keeps its four 16-byte pieces in the warp's buffer (64-byte swizzle:
+    // piece index xor bits 7-8 of the address), and where the pieces this lane fetches of other
+    // lanes' rows go: piece (lane & 3) of rows (lane >> 2) + 8 i.
+    const uint32_t own_row_off = lane * 64;
+    const uint32_t own_swz = (lane >> 1) & 3;
+    const uint32_t fetch_piece = lane & 3;
+    const uint32_t fetch_row = lane >> 2;
 
     WorkWalk walk(p, unit, num_units);
     WorkItem item;
@@ -642,6 +775,26 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       auto finish_chunk = [&](int c, uint32_t (&v)[32]) {
         const int nc = n0 + c * 32;
         float x[32];
+        // Staged form: once the store of the chunk before has read the warp's buffer, the
+        // residual's 32 rows x 64 bytes are fetched into it with four coalesced 16-byte copies per
+        // lane (8 rows x 64 bytes per instruction) that bypass the registers; the arithmetic below
+        // runs while they are on their way.
+        if (staged) {
+          if (lane == 0) bulk_wait_group_read0();
+          __syncwarp();
+          if (has_res) {
+            const int col = nc + static_cast<int>(fetch_piece) * 8;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t r = i * 8 + fetch_row;
+              const int grow = row - static_cast<int>(lane) + static_cast<int>(r);
+              const bool live = grow < p.m && col < p.n;
+              const uint16_t *src = reinterpret_cast<const uint16_t *>(p.residual) +
+                                    (live ? static_cast<long long>(grow) * p.residual_ld + col : 0);
+              cp_async_16(obuf + r * 64 + ((fetch_piece ^ ((r >> 1) & 3)) << 4), src, live ? 16u : 0u);
+            }
+          }
+        }
         if (has_cs_vec) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
@@ -672,6 +825,43 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (p.act == kActGeluTanh) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) x[j] = gelu_tanh(x[j]);
+        }
+        if (staged) {
+          if (has_res) {
+            cp_async_wait_all();
+            __syncwarp();
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const uint4 q = *reinterpret_cast<const uint4 *>(obuf + own_row_off + ((g ^ own_swz) << 4));
+              const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                if (is_bf16) {
+                  x[g * 8 + 2 * h] += __uint_as_float(w[h] << 16);
+                  x[g * 8 + 2 * h + 1] += __uint_as_float(w[h] & 0xffff0000u);
+                } else {
+                  const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[h]));
+                  x[g * 8 + 2 * h] += f.x;
+                  x[g * 8 + 2 * h + 1] += f.y;
+                }
+              }
+            }
+            // (a lane's row is read by that lane only, so it may be overwritten without another barrier)
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            *reinterpret_cast<uint4 *>(obuf + own_row_off + ((g ^ own_swz) << 4)) =
+                make_uint4(pack16(x[8 * g], x[8 * g + 1], is_bf16), pack16(x[8 * g + 2], x[8 * g + 3], is_bf16),
+                           pack16(x[8 * g + 4], x[8 * g + 5], is_bf16), pack16(x[8 * g + 6], x[8 * g + 7], is_bf16));
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          // Rows past m and columns past n are not written: the tensor map ends there.
+          if (lane == 0) {
+            tma_store_2d(&tmap_out, obuf, nc, row - static_cast<int>(lane));
+            bulk_commit_group();
+          }
+          return;
         }
         if (has_res && row_ok) {
           if (res_vec_ok) {
@@ -740,6 +930,57 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         constexpr int kSlotFloats = CTAS * kEpilogueWarps * kWarpFloats;  // one unit's part of one tile
         const int within = (static_cast<int>(cta_rank) * kEpilogueWarps + static_cast<int>(warp)) * kWarpFloats;
         float *mine = p.sk_partials + (static_cast<long long>(unit) * 2 + (item.head ? 1 : 0)) * kSlotFloats + within;
+        // The other part: the tile's head belongs to the unit before the one that holds its tail
+        // (slot 1 of that unit), the tail to the unit after (its slot 0).
+        const float *other = p.sk_partials +
+                             (static_cast<long long>(item.head ? unit + 1 : unit - 1) * 2 + (item.head ? 0 : 1)) * kSlotFloats + within;
+        uint32_t *counter = p.sk_counters + (item.sk_tile * CTAS + static_cast<int>(cta_rank)) * kEpilogueWarps + warp;
+        // Has the other holder counted itself in already? (It has when this is a tail, a unit's
+        // last item: the tile's head was the first thing its holder did in this part of the
+        // schedule.) Then this warp's part never goes to memory: the other part is added to the
+        // accumulator as it comes out of tensor memory.
+        uint32_t there = 0;
+        if (lane == 0) there = *reinterpret_cast<volatile uint32_t *>(counter);
+        there = __shfl_sync(0xffffffffu, there, 0);
+        if (there != 0) {
+          __threadfence();  // the other part's stores are ordered before its count, which was just read
+          float4 pre[8];
+          const float4 *op = reinterpret_cast<const float4 *>(other) + lane;
+          if (chunks > 0) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) pre[j] = __ldcg(op + j * 32);
+          }
+#pragma unroll 1
+          for (int c = 0; c < chunks; ++c) {
+            tmem_ld_32x32(tacc + c * 32, va);
+            tmem_ld_wait(va);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              // head + tail in that order, whichever of the two this warp holds (the sum is the same
+              // either way round, bit for bit)
+              va[4 * j] = __float_as_uint(__fadd_rn(__uint_as_float(va[4 * j]), pre[j].x));
+              va[4 * j + 1] = __float_as_uint(__fadd_rn(__uint_as_float(va[4 * j + 1]), pre[j].y));
+              va[4 * j + 2] = __float_as_uint(__fadd_rn(__uint_as_float(va[4 * j + 2]), pre[j].z));
+              va[4 * j + 3] = __float_as_uint(__fadd_rn(__uint_as_float(va[4 * j + 3]), pre[j].w));
+            }
+            if (c + 1 < chunks) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) pre[j] = __ldcg(op + (c + 1) * 256 + j * 32);
+            }
+            finish_chunk(c, va);
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (CTAS == 2) {
+              mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[acc]), 0));
+            } else {
+              mbar_arrive(&acc_empty_bar[acc]);
+            }
+            *counter = 0;  // ready for the next launch
+          }
+          continue;
+        }
         tmem_ld_32x32(tacc, va);
 #pragma unroll 1
         for (int c = 0; c < HALF_CHUNKS; ++c) {
@@ -756,7 +997,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         __threadfence();  // this lane's part of the partial is visible before the count below says so
         __syncwarp();
         uint32_t arrived = 0;
-        uint32_t *counter = p.sk_counters + (item.sk_tile * CTAS + static_cast<int>(cta_rank)) * kEpilogueWarps + warp;
         if (lane == 0) {
           if constexpr (CTAS == 2) {
             mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[acc]), 0));
@@ -768,10 +1008,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         arrived = __shfl_sync(0xffffffffu, arrived, 0);
         if (arrived == 0) continue;  // the other holder of this tile will finish it
         __threadfence();
-        // The other part: the tile's head is the last item of the unit before the one that holds
-        // its tail, in slot 1; the tail is that next unit's first item, in slot 0.
-        const float *other = p.sk_partials +
-                             (static_cast<long long>(item.head ? unit + 1 : unit - 1) * 2 + (item.head ? 0 : 1)) * kSlotFloats + within;
         const float *head_part = item.head ? mine : other;
         const float *tail_part = item.head ? other : mine;
 #pragma unroll 1
@@ -820,6 +1056,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
       }
     }
+    if (staged && lane == 0) bulk_wait_group0();  // this warp's stores have left its buffer and landed
     if (!ok && lane == 0) {
       abort_flag = 1;
       atomicCAS(p.status, 0u, static_cast<uint32_t>(kStatusEpilogueTimeout));
@@ -878,6 +1115,21 @@ bool make_tmap(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_b
   return r == CUDA_SUCCESS;
 }
 
+// An e4m3 (rows, k) weight read in boxes of (box_rows, 64 bytes), as it lies (no swizzle): the
+// converter warps of the mixed form re-lay it.
+bool make_tmap_raw(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 // The scale-factor tiles of one operand as a (tiles, 512 byte) matrix of 32-bit words, read in
 // boxes of kMmasPerStage tiles (the factors of one K stage of one 128-row group), unswizzled.
 bool make_tmap_sf(CUtensorMap *map, const void *base, uint64_t tiles) {
@@ -893,13 +1145,28 @@ bool make_tmap_sf(CUtensorMap *map, const void *base, uint64_t tiles) {
   return r == CUDA_SUCCESS;
 }
 
-template <int KIND, int BLOCK_N, int CTAS>
+// The (m, n) matrix of 16-bit results with `ld` elements between rows, written in boxes of 32 rows
+// x 32 columns (64 bytes) from shared memory in the 64-byte swizzle.
+bool make_tmap_out(CUtensorMap *map, void *base, uint64_t m, uint64_t n, uint64_t ld) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {n, m};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int KIND, int BLOCK_N, int CTAS, bool B8 = false>
 cudaError_t launch_one(const GemmArgs &a, KernelParams kp, uint64_t row_bytes, const char **why) {
-  using Cfg = Config<BLOCK_N, KIND == kKindNvf4, CTAS>;
+  using Cfg = Config<BLOCK_N, KIND == kKindNvf4, CTAS, B8>;
   kp.tiles_m = (a.m + kBlockM * CTAS - 1) / (kBlockM * CTAS);
   kp.tiles_n = (a.n + BLOCK_N - 1) / BLOCK_N;
   CUtensorMap ta, tb;
-  if (!make_tmap(&ta, a.a, a.m, row_bytes, kBlockM) || !make_tmap(&tb, a.b, a.n, row_bytes, Cfg::kBRows)) {
+  const bool b_ok = B8 ? make_tmap_raw(&tb, a.b, a.n, row_bytes / 2, Cfg::kBRows) : make_tmap(&tb, a.b, a.n, row_bytes, Cfg::kBRows);
+  if (!make_tmap(&ta, a.a, a.m, row_bytes, kBlockM) || !b_ok) {
     *why = "cuTensorMapEncodeTiled refused the operand";
     return cudaErrorInvalidValue;
   }
@@ -912,7 +1179,19 @@ cudaError_t launch_one(const GemmArgs &a, KernelParams kp, uint64_t row_bytes, c
       return cudaErrorInvalidValue;
     }
   }
-  auto kernel = gemm_tn_kernel<KIND, BLOCK_N, CTAS>;
+  // Results leave through per-warp shared-memory buffers and TMA stores when the destination can
+  // be described by a tensor map (one 16-byte aligned matrix, pitch a multiple of 8 elements) and
+  // the residual, if any, is a plain 16-byte aligned matrix of out's rows; otherwise every lane
+  // stores (and loads the residual of) its own row.
+  CUtensorMap tout = ta;
+  kp.out_staged = 0;
+  if (kp.out_vector && kp.num_out == 1 &&
+      (!kp.residual || (kp.residual_rows == a.m && (reinterpret_cast<uintptr_t>(kp.residual) & 15) == 0 &&
+                        kp.residual_ld % 8 == 0))) {
+    void *base = reinterpret_cast<uint16_t *>(kp.out[0]) + kp.out_col0;
+    if (make_tmap_out(&tout, base, a.m, a.n, kp.out_ld)) kp.out_staged = 1;
+  }
+  auto kernel = gemm_tn_kernel<KIND, BLOCK_N, CTAS, B8>;
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
@@ -949,7 +1228,7 @@ cudaError_t launch_one(const GemmArgs &a, KernelParams kp, uint64_t row_bytes, c
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tsfa, tsfb, kp);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tsfa, tsfb, tout, kp);
   if (e != cudaSuccess) *why = "kernel launch failed";
   return e;
 }
@@ -970,15 +1249,20 @@ int sm_count() {
   return cached;
 }
 
-// The schedule (see the head of this file). The stream-K part pays for itself when the last round
-// would be less than 85 % full; it needs whole rounds before it and tiles of a few stages at least.
+// The schedule (see the head of this file). What the stream-K part can save is the idle share of
+// the last round, (units - remainder) / units of a tile's main loop; what it costs, measured, is
+// about ten microseconds of a launch (two more epilogue-side passes per unit, the second of them
+// exposed at the end), that is some thirty K stages. It is used where the saving is forty stages
+// or more: long-K products whose last round is poorly filled (8704 x 3072 x 12288: 408 tiles on 74
+// pairs, 248 -> 232 us); with 3072-deep tiles it never is.
 GemmSchedule gemm_schedule(int tiles, int max_units, int num_kb, bool allow_stream_k) {
   GemmSchedule s = {};
   s.units = tiles < max_units ? tiles : max_units;
   if (s.units < 1) s.units = 1;
   const int full_rounds = tiles / s.units;
   const int remainder = tiles % s.units;
-  if (allow_stream_k && full_rounds >= 1 && remainder > 0 && remainder * 100 <= s.units * 85 && num_kb >= 4) {
+  const long long saved_stages = static_cast<long long>(s.units - remainder) * num_kb / s.units;
+  if (allow_stream_k && full_rounds >= 1 && remainder > 0 && saved_stages >= kStreamKMinSavedStages) {
     s.dp_rounds = full_rounds - 1;
     s.sk_tiles = remainder + s.units;
     s.sk_first_tile = s.dp_rounds * s.units;
@@ -1059,6 +1343,10 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
     return cudaErrorInvalidValue;
   }
   kp.status = a.status;
+  if (a.b_is_e4m3 && (a.kind != kGemmF16 || kp.num_out > 1)) {
+    *why = "an e4m3 right operand widened in the kernel goes with half operands and one destination";
+    return cudaErrorInvalidValue;
+  }
 
   // A pair of CTAs per 256-row tile halves the B bytes each SM pulls from L2; it needs two row
   // blocks to share the B tile between. Narrow outputs use the narrower single-CTA tile so that
@@ -1084,6 +1372,11 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
       if (pair) return launch_one<kKindBF16, 256, 2>(a, kp, row_bytes, why);
       return narrow ? launch_one<kKindBF16, 128, 1>(a, kp, row_bytes, why) : launch_one<kKindBF16, 256, 1>(a, kp, row_bytes, why);
     default:
+      if (a.b_is_e4m3) {
+        if (pair) return launch_one<kKindF16, 256, 2, true>(a, kp, row_bytes, why);
+        return narrow ? launch_one<kKindF16, 128, 1, true>(a, kp, row_bytes, why)
+                      : launch_one<kKindF16, 256, 1, true>(a, kp, row_bytes, why);
+      }
       if (pair) return launch_one<kKindF16, 256, 2>(a, kp, row_bytes, why);
       return narrow ? launch_one<kKindF16, 128, 1>(a, kp, row_bytes, why) : launch_one<kKindF16, 256, 1>(a, kp, row_bytes, why);
   }

@@ -33,7 +33,8 @@ struct GemmArgs {
   int m, n, k;  // k counts elements
   // Operands in device memory, rows 16-byte aligned (pitch = k * element size, a multiple of 16).
   const void *a;  // (m, k)
-  const void *b;  // (n, k)
+  const void *b;  // (n, k); with b_is_e4m3 (kGemmF16 only), e4m3 bytes that the kernel widens to half, exactly
+  int b_is_e4m3;
   // NVFP4 only: scale factors in the 128-row x 4-factor tile layout the tensor cores read
   // (see pack_scale_factors()), and how many 4-factor tiles one row group holds along k.
   const uint8_t *sfa;

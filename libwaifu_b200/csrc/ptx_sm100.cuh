@@ -95,6 +95,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   return done != 0;
 }
 
+// The same test with cluster scope: for a barrier whose arrivals come from the other CTA of a pair
+// and guard shared memory that CTA wrote.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
 // Upper bound on try_wait polls before a wait gives up. One poll blocks for a hardware-chosen
 // slice (well under a millisecond), so the bound is reached only when the awaited event never
 // comes; legitimate waits in these kernels last microseconds.
@@ -113,6 +129,26 @@ __device__ __forceinline__ bool mbar_wait_limited(uint64_t *bar, uint32_t parity
 
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag) {
   return mbar_wait_limited(bar, parity, abort_flag, kWaitPollLimit);
+}
+
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag) {
+  for (uint32_t polls = 0; polls < kWaitPollLimit; ++polls) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((polls & 0x3ff) == 0x3ff && *abort_flag != 0) return false;
+  }
+  return false;
+}
+
+// Four e4m3 codes (one 32-bit word, lowest byte first) as four halves in two 32-bit words; exact.
+__device__ __forceinline__ void e4m3x4_to_f16x4(uint32_t codes, uint32_t *lo, uint32_t *hi) {
+  asm("{\n\t"
+      ".reg .b16 a, b;\n\t"
+      "mov.b32 {a, b}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, a;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, b;\n\t"
+      "}"
+      : "=r"(*lo), "=r"(*hi)
+      : "r"(codes));
 }
 
 // ---- TMA ---------------------------------------------------------------------------------
@@ -141,6 +177,27 @@ __device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorM
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr), "r"(x), "r"(y)
       : "memory");
 }
+
+// 2-D tiled store of this CTA's shared memory -> global (this GPU's own memory), in the calling
+// thread's bulk async-group. Rows and columns of the box that lie outside the tensor are not written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *desc, const void *smem_src, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(desc)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until the calling thread's bulk stores have read their shared memory (it may be overwritten) ...
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... and until they have completed altogether.
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// 16 bytes global -> shared without passing through registers (`src_bytes` 16, or 0 for zeros),
+// and the wait for every such copy the calling thread has issued.
+__device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // 1-D bulk copy global -> shared (16-byte aligned on both sides, size a multiple of 16).
 __device__ __forceinline__ void bulk_load_1d(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar) {

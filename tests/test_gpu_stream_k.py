@@ -55,8 +55,9 @@ def compare(oracle, runs, want, is_bf16, what):
 
 
 # (m, n, k, act): pair tiles 256 x 256 (81 tiles on 74 pairs), single-CTA 128-wide tiles (160 on 148),
-# and a ragged case whose edge tiles are partly outside the matrix
-@pytest.mark.parametrize("m,n,k,act", [(2304, 2304, 1024, 1), (20480, 128, 512, 0), (2250, 2312, 656, 0)])
+# and a ragged case whose edge tiles are partly outside the matrix; K long enough (48 stages) that
+# the schedule takes its stream-K form
+@pytest.mark.parametrize("m,n,k,act", [(2304, 2304, 6144, 1), (20480, 128, 6144, 0), (2250, 2056, 6160, 0)])
 def test_fp8_linear_under_both_schedules(flint, oracle, m, n, k, act):
     F = flint
     p = plan(F, 2, m, n, k)
@@ -79,7 +80,7 @@ def test_fp8_linear_under_both_schedules(flint, oracle, m, n, k, act):
 
 def test_nvfp4_linear_under_both_schedules(flint, oracle):
     F = flint
-    m, n, k = 2304, 1728, 1024  # 9 x 9 pair tiles of 256 x 192
+    m, n, k = 2304, 1728, 12288  # 9 x 9 pair tiles of 256 x 192, 48 K stages
     p = plan(F, 3, m, n, k)
     if p[6] == 0:
         pytest.skip(f"this card's SM count gives the shape no stream-K part (plan {p})")
@@ -98,7 +99,7 @@ def test_nvfp4_linear_under_both_schedules(flint, oracle):
 @pytest.mark.parametrize("is_bf16", [True, False])
 def test_16_bit_matmul_under_both_schedules(flint, oracle, is_bf16):
     F = flint
-    m, n, k = 2304, 2304, 512
+    m, n, k = 2304, 2304, 3072
     p = plan(F, 1 if is_bf16 else 0, m, n, k)
     if p[6] == 0:
         pytest.skip(f"this card's SM count gives the shape no stream-K part (plan {p})")
@@ -123,7 +124,7 @@ def test_counters_are_left_zero_between_launches(flint, oracle):
     rng = np.random.default_rng(79)
     bf = F.DType.BFLOAT16
     outs, wants = [], []
-    for (m, n, k) in [(2304, 2304, 512), (2560, 2304, 768), (2304, 2304, 512), (20480, 128, 512)]:
+    for (m, n, k) in [(2304, 2304, 6144), (2560, 2304, 6400), (2304, 2304, 6144), (20480, 128, 6144)]:
         x = oracle.narrow(randn(rng, (m, k)), True)
         codes, scales = oracle.quantize_fp8_rows(randn(rng, (n, k), 0.02))
         outs.append(F.fp8_linear(dev(F, x, bf), dev(F, codes, F.DType.FP8E4M3), dev(F, scales, F.DType.FLOAT)))
