@@ -2,9 +2,9 @@
 // mma.sync kernel of flint/cuda/gemm_fp8_cutlass.cu:94-197,267-305).
 //
 // One persistent CTA per SM (or one pair of CTAs per two SMs), twelve warps:
-//   warps 0-7  epilogue: tensor memory -> registers -> scale/bias/GELU/residual -> 16-bit stores.
-//              Warp w reads the 32 accumulator rows of lane quarter (w & 3) and the column half
-//              (w >> 2) of the tile.
+//   warps 0-7  epilogue: tensor memory -> registers -> scale/bias/GELU/residual -> 16-bit results,
+//              which leave through a per-warp shared-memory buffer and TMA stores. Warp w reads
+//              the 32 accumulator rows of lane quarter (w & 3) and the column half (w >> 2) of the tile.
 //   warp  8    producer: TMA tile loads of A and B (and the NVFP4 scale-factor tiles) into a
 //              ring of shared-memory stages, signalled through mbarriers
 //   warp  9    MMA: one thread issues tcgen05.mma on the staged tiles, accumulating in tensor
@@ -13,11 +13,13 @@
 //   warps 10-11 pushers, only at work in the scatter form (a product gathered on several GPUs):
 //              once the epilogue has written a tile into this GPU's matrix they copy its rows to
 //              the peers' matrices, 512 contiguous bytes per store instruction, over NVLink.
-//              In the mixed form (a 16-bit activation against an e4m3 weight that is NOT narrowed,
-//              flint's fl_fp8_matmul) they are the converters instead: the weight tile arrives
-//              as e4m3 bytes, they widen it exactly to half into the swizzled 16-bit tile the
-//              UMMA reads, so the weight crosses HBM and L2 once, as bytes (the reference widens
-//              in registers inside its main loop, flint/cuda/gemm_fp8_cutlass.cu:142-149)
+// The mixed form (a half activation against an e4m3 weight that is NOT narrowed, flint's
+// fl_fp8_matmul) divides the twelve differently: warps 0-3 epilogue (a warp takes its 32 rows of
+// all the tile's columns), warp 4 producer, warp 5 MMA, warps 6-11 converters. The weight tile
+// arrives as e4m3 bytes and the converters widen it exactly to half into the swizzled 16-bit tile
+// the UMMA reads, so the weight crosses HBM and L2 once, as bytes (the reference widens in
+// registers inside its main loop, flint/cuda/gemm_fp8_cutlass.cu:142-149). Six warps because the
+// conversion instruction's units are per scheduler and two warps could not keep up with the UMMAs.
 // The accumulator is double-buffered in tensor memory so the epilogue of tile i overlaps the
 // main loop of tile i+1.
 //
@@ -57,12 +59,23 @@ constexpr int kRowBytes = 128;          // bytes of K per operand row per stage
 constexpr int kMmaKBytes = 32;          // bytes of K one tcgen05.mma consumes per row
 constexpr int kMmasPerStage = kRowBytes / kMmaKBytes;
 constexpr int kSfTileBytes = 512;       // 128 rows x 4 scale factors
-constexpr int kEpilogueWarps = 8;
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
-constexpr int kPusherWarp0 = 10;
+constexpr int kNumWarps = 12;
+constexpr int kNumThreads = kNumWarps * 32;
+constexpr int kMaxEpilogueWarps = 8;
 constexpr int kPusherWarps = 2;
-constexpr int kNumThreads = 384;
+// Who does what among the twelve warps. Tensor memory lets a warp read the 32 lanes of its index
+// modulo 4 only, so epilogue warps come in fours, each four covering a tile's 128 rows and one
+// share of its columns. The mixed form gives up one of the two fours to have six converter warps:
+// widening is conversion-instruction bound, and those units are per scheduler.
+template <bool B8>
+struct Roles {
+  static constexpr int kEpilogueWarps = B8 ? 4 : 8;
+  static constexpr int kColumnShares = kEpilogueWarps / 4;
+  static constexpr int kProducerWarp = kEpilogueWarps;
+  static constexpr int kMmaWarp = kEpilogueWarps + 1;
+  static constexpr int kAuxWarp0 = kEpilogueWarps + 2;       // pushers / scale-factor copier, or converters
+  static constexpr int kAuxWarps = kNumWarps - kAuxWarp0;    // 2, or 6
+};
 // Tiles are walked in bands of tile columns, columns fastest inside a band, so that the tiles in
 // flight at one time share a compact set of A and B rows in L2. A matrix up to kBandMax tile
 // columns wide is one band (every A row block is then fetched from HBM once); wider ones are cut
@@ -177,9 +190,11 @@ struct WorkWalk {
 // CTAS == 2: a pair of CTAs (one cluster) shares a 256 x BLOCK_N tile through cta_group::2 UMMAs;
 // each CTA stages its own 128 rows of A and its own half of the BLOCK_N rows of B.
 template <int BLOCK_N, bool NVF4, int CTAS = 1, bool B8 = false>
-struct Config {
+struct Config : Roles<B8> {
+  using Roles<B8>::kEpilogueWarps;
+  using Roles<B8>::kColumnShares;
   static_assert(!(NVF4 && B8), "the mixed form is a 16-bit kind");
-  static_assert(BLOCK_N % 64 == 0, "each epilogue warp takes whole 32-column chunks of half a tile");
+  static_assert(BLOCK_N % 64 == 0, "each epilogue warp takes whole 32-column chunks of its share of a tile");
   static constexpr int kABytes = kBlockM * kRowBytes;
   static constexpr int kBRows = BLOCK_N / CTAS;
   static constexpr int kBBytes = kBRows * kRowBytes;
@@ -194,7 +209,7 @@ struct Config {
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes + kRawBytes;
   // Each epilogue warp keeps its own copy of its columns' scale and bias as fp32 (a private copy
   // needs no barrier between warps, so no wait in the epilogue is unbounded).
-  static constexpr int kHalfN = BLOCK_N / 2;
+  static constexpr int kHalfN = BLOCK_N / kColumnShares;  // columns of a tile one epilogue warp handles
   static constexpr int kColParamBytes = kEpilogueWarps * 2 * kHalfN * 4;
   // Each epilogue warp also has 32 rows x 64 bytes of its own (one 32-column chunk of 16-bit
   // results in the 64-byte swizzle) through which results leave by TMA store and residual rows
@@ -273,6 +288,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   constexpr bool NVF4 = (KIND == kKindNvf4);
   using Cfg = Config<BLOCK_N, NVF4, CTAS, B8>;
   constexpr int STAGES = Cfg::kStages;
+  constexpr int kEpilogueWarps = Cfg::kEpilogueWarps;
+  constexpr int kProducerWarp = Cfg::kProducerWarp;
+  constexpr int kMmaWarp = Cfg::kMmaWarp;
+  constexpr int kPusherWarp0 = Cfg::kAuxWarp0;
+  constexpr int kConverterWarps = Cfg::kAuxWarps;
   // A work unit is one CTA, or one pair of CTAs; rank 0 of a pair is its leader: it owns the
   // barriers both producers signal and it alone issues the UMMAs.
   const uint32_t cta_rank = (CTAS == 2) ? cluster_cta_rank() : 0u;
@@ -303,7 +323,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     for (int s = 0; s < STAGES; ++s) {
       // Mixed form: a stage is full when the A bytes have landed (the producer's arrival with
       // its byte count) and every converter warp of the unit has written its share of B.
-      mbar_init(&full_bar[s], B8 ? 1 + kPusherWarps * CTAS : 1);
+      mbar_init(&full_bar[s], B8 ? 1 + kConverterWarps * CTAS : 1);
       mbar_init(&empty_bar[s], 1);
       if constexpr (B8) mbar_init(&raw_full_bar[s], 1);
     }
@@ -476,9 +496,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
         const int kb_first = item.kb0;  // the item's first UMMA overwrites the accumulator
         for (int kb = item.kb0; kb < item.kb1; ++kb) {
-          // (mixed form in a pair: the other CTA's converters wrote its half of B and arrived from there)
-          if (!((B8 && CTAS == 2) ? mbar_wait_cluster(&full_bar[stage], phase, &abort_flag)
-                                  : mbar_wait(&full_bar[stage], phase, &abort_flag))) {
+          if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) {
             ok = false;
             break;
           }
@@ -614,7 +632,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint8_t *raw = stage_raw(stage);
         uint8_t *b16 = stage_b(stage);
 #pragma unroll 4
-        for (int piece = cw * 32 + static_cast<int>(lane); piece < Cfg::kBRows * 4; piece += kPusherWarps * 32) {
+        for (int piece = cw * 32 + static_cast<int>(lane); piece < Cfg::kBRows * 4; piece += kConverterWarps * 32) {
           const uint32_t r = static_cast<uint32_t>(piece) >> 2, q = static_cast<uint32_t>(piece) & 3;
           const uint4 v = *reinterpret_cast<const uint4 *>(raw + piece * 16);
           uint4 lo, hi;
@@ -629,10 +647,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         fence_proxy_async_smem();  // the UMMA reads these bytes through the async proxy
         __syncwarp();
         if (lane == 0) {
-          if constexpr (CTAS == 2) {
-            mbar_arrive_cluster(map_to_cta(smem_u32(&full_bar[stage]), 0));
-          } else {
+          if (leader) {
             mbar_arrive(&full_bar[stage]);
+          } else {
+            mbar_arrive_remote(map_to_cta(smem_u32(&full_bar[stage]), 0));
           }
         }
         if (++stage == STAGES) {
@@ -645,7 +663,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       abort_flag = 1;
       atomicCAS(p.status, 0u, static_cast<uint32_t>(kStatusProducerTimeout));
     }
-  } else if (warp >= kPusherWarp0) {
+  } else if (!B8 && warp >= kPusherWarp0) {
     // ------------------------------------------------------------------ pushers (scatter form)
     if (scatter && p.out_vector) {
       bool ok = true;
@@ -710,7 +728,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     constexpr int HALF_N = Cfg::kHalfN;
     constexpr int HALF_CHUNKS = HALF_N / 32;
     const uint32_t quarter = warp & 3;  // which 32 lanes of tensor memory, i.e. which 32 rows of the tile
-    const uint32_t half = warp >> 2;    // which half of the tile's columns
+    const uint32_t half = warp >> 2;    // which share of the tile's columns (two halves; one whole in the mixed form)
     bool ok = true;
     int local = 0;
     const int is_bf16 = p.out_bf16;
@@ -1202,10 +1220,10 @@ cudaError_t launch_one(const GemmArgs &a, KernelParams kp, uint64_t row_bytes, c
     attr_set = true;
   }
   const int tiles = kp.tiles_m * kp.tiles_n;
-  const size_t part_floats_per_unit = static_cast<size_t>(2) * CTAS * kEpilogueWarps * (BLOCK_N / 2) * 32;
+  const size_t part_floats_per_unit = static_cast<size_t>(2) * CTAS * kBlockM * BLOCK_N;
   const bool may_stream_k = a.sk_partials && a.sk_counters && !a.no_stream_k && kp.num_out == 1 &&
                             part_floats_per_unit * (sm_count() / CTAS) <= a.sk_partial_floats &&
-                            static_cast<size_t>(2) * sm_count() * kEpilogueWarps <= a.sk_counter_words;
+                            static_cast<size_t>(2) * sm_count() * kMaxEpilogueWarps <= a.sk_counter_words;
   const GemmSchedule sch = gemm_schedule(tiles, sm_count() / CTAS, kp.num_kb, may_stream_k);
   const int units = sch.units;
   kp.dp_rounds = sch.dp_rounds;
@@ -1289,7 +1307,7 @@ void gemm_plan(GemmKind kind, int m, int n, int k, int sms, int allow_stream_k, 
 // Two parts per SM of 128 rows x 256 columns at most; a counter per epilogue warp of every tile of
 // the stream-K part, which has fewer than two rounds of tiles.
 size_t gemm_stream_k_partial_floats() { return static_cast<size_t>(sm_count()) * 2 * kBlockM * 256; }
-size_t gemm_stream_k_counter_words() { return static_cast<size_t>(sm_count()) * 2 * kEpilogueWarps; }
+size_t gemm_stream_k_counter_words() { return static_cast<size_t>(sm_count()) * 2 * kMaxEpilogueWarps; }
 
 cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
   *why = "";

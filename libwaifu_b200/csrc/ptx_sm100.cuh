@@ -81,6 +81,14 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
+// The same arrival with the default (CTA-scope release) semantics: for a writer that has already
+// made its shared-memory writes visible to the async proxy with a proxy fence and only needs the
+// count. A cluster-scope release costs the arriving thread the better part of a microsecond, which
+// is nothing once per tile and everything once per K stage.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
