@@ -132,12 +132,14 @@ FLAPI void fl_transfer_destroy(fl_transfer_t transfer);
 /* flint/capi.h:279. <float>, <float16> and <bfloat16> tensors here. */
 FLAPI int32_t fl_fill(fl_operators_t operators, fl_tensor_view_t tensor, float value);
 
-/* flint/capi.h:440-446 and 448-456, for the linear-layer case only: a <float16|bfloat16>(..., k)
- * contiguous, b (k, n) the transposed view (strides 1, k) of a contiguous (n, k) weight of the
- * same type -- what an unquantised Linear passes (waifu/src/layers.rs:230-246) -- out (..., n);
- * n and k multiples of 8. fl_matmul_add adds a bias (n) or a residual broadcast over out's leading
- * dimensions to the fp32 sum, one rounding (flint/capi.h:448-452). Float32 operands, batched or
- * row-major right operands are not implemented here and are refused with FL_ERROR_INVALID_ARG. */
+/* flint/capi.h:440-446 and 448-456. Matrix multiplication, batched over the leading dimensions:
+ * a (..., m, k), b (k, n) or (..., k, n) with leading dimensions that equal a's or are 1, out
+ * (..., m, n) contiguous; operands of one type, <float>, <float16> or <bfloat16>, out of that type or
+ * <float>; any strides. fl_matmul_add adds `addend`, of out's type, broadcast over out's leading
+ * dimensions (a bias (n), or a residual) to the float sum, one rounding (flint/capi.h:448-452).
+ * The linear-layer case -- 16-bit a contiguous, b the transposed view (strides 1, k) of a contiguous
+ * (n, k) weight (waifu/src/layers.rs:230-246), n and k multiples of 8 -- runs on the tensor cores;
+ * every other case on a general fp32-accumulating kernel. */
 FLAPI int32_t fl_matmul(fl_operators_t operators, fl_tensor_view_t a, fl_tensor_view_t b, fl_tensor_view_t out);
 FLAPI int32_t fl_matmul_add(fl_operators_t operators, fl_tensor_view_t a, fl_tensor_view_t b, fl_tensor_view_t addend,
                             fl_tensor_view_t out);
@@ -151,8 +153,8 @@ FLAPI int32_t fl_add(fl_operators_t operators, fl_tensor_view_t a, fl_tensor_vie
 typedef enum fl_mask_type_t {
   FL_MASK_NONE = 0,           /* every key; block_size 0 */
   FL_MASK_CAUSAL = 1,         /* keys 0..p; block_size 0; needs S >= L */
-  FL_MASK_BLOCK_CAUSAL = 2,   /* not implemented in this library: refused with the reason */
-  FL_MASK_BLOCK_DIAGONAL = 3, /* not implemented in this library: refused with the reason */
+  FL_MASK_BLOCK_CAUSAL = 2,   /* p's own block of block_size keys and every block before it; needs S >= L */
+  FL_MASK_BLOCK_DIAGONAL = 3, /* p's own block alone; needs S == L */
 } fl_mask_type_t;
 
 /* flint/capi.h:532-544. Scaled dot product attention: q (N, heads, L, D), k and v (N, kv_heads, S, D)
@@ -162,7 +164,9 @@ typedef enum fl_mask_type_t {
  * 64 or 128. Softmax in float over scores scaled by 1/sqrt(D); probabilities rounded to the
  * operands' type before the second product (flint/cuda/attention.cu:30-70). A mask that is not one
  * (a block size beside NONE or CAUSAL, none beside a block mask, keys too few) is
- * FL_ERROR_INVALID_ARG, and so is what this library has no kernel for, with the reason. Two
+ * FL_ERROR_INVALID_ARG, and so is what this library has no kernel for (float32 operands, other
+ * head sizes, broadcast q, k or out), with the reason. Blocks of 128 keys no query of a tile sees
+ * are skipped. Two
  * launches (a transposition of v into scratch, the attention kernel), no host synchronisation. */
 FLAPI int32_t fl_attention(fl_operators_t operators, fl_tensor_view_t q, fl_tensor_view_t k, fl_tensor_view_t v,
                            fl_mask_type_t mask_type, int32_t block_size, fl_tensor_view_t out);

@@ -97,7 +97,8 @@ struct KernelParams {
   int heads, group;  // group = heads / kv_heads
   int kv_heads;
   int q_len, kv_len;
-  int causal;
+  int mask_type;   // 0 none, 1 causal, 2 block causal, 3 block diagonal (flint/capi.h:118-133)
+  int block_size;
   float scale_log2;
   uint32_t *status;
 };
@@ -117,6 +118,16 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *d
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(desc)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
+}
+
+// The first and the last key a query at `position` may see (flint/cuda/attention.cu:165-179).
+__device__ __forceinline__ int first_key_of(const KernelParams &p, int position) {
+  return p.mask_type == 3 ? (position / p.block_size) * p.block_size : 0;
+}
+__device__ __forceinline__ int last_key_of(const KernelParams &p, int position) {
+  if (p.mask_type == 0) return p.kv_len - 1;
+  if (p.mask_type == 1) return min(p.kv_len - 1, position);
+  return min(p.kv_len - 1, (position / p.block_size) * p.block_size + p.block_size - 1);
 }
 
 // 2^x for x <= 2^kRescaleStep's exponent: the hardware approximation (relative error 2^-22), -inf -> 0.
@@ -185,13 +196,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int batch = blockIdx.z;
   const int kv_head = head / p.group;
   const int offset = p.kv_len - p.q_len;  // query i sits at key position i + offset
-  // Keys this CTA's queries can see: all of them, or up to its last query's position.
-  int kv_end = p.kv_len;
-  if (p.causal) {
-    const int last_q = min(q0 + kBlockQ, p.q_len) - 1;
-    kv_end = min(p.kv_len, last_q + offset + 1);
-  }
-  const int num_blocks = (kv_end + kBlockKv - 1) / kBlockKv;
+  // The keys this CTA's queries can see between them: both ends of a query's range grow with its
+  // position, so the range of the CTA runs from its first query's first key to its last query's
+  // last key. Blocks of 128 keys outside it are never loaded.
+  const int last_row = min(q0 + kBlockQ, p.q_len) - 1;
+  const int kv_begin = first_key_of(p, q0 + offset);
+  const int kv_end = last_key_of(p, last_row + offset) + 1;
+  const int block0 = kv_begin / kBlockKv;  // first block of keys this CTA walks
+  const int num_blocks = (kv_end + kBlockKv - 1) / kBlockKv - block0;
 
   if (threadIdx.x == 0) {
     t.abort_flag = 0;
@@ -246,7 +258,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         mbar_arrive_expect_tx(&t.k_full_bar[st], L::kKBytes);
 #pragma unroll
         for (int a = 0; a < L::kQAtoms; ++a) {
-          tma_load_4d(k_stage(st) + a * kBlockKv * kAtomBytes, &tmap_k, &t.k_full_bar[st], a * kAtomBytes, j * kBlockKv,
+          tma_load_4d(k_stage(st) + a * kBlockKv * kAtomBytes, &tmap_k, &t.k_full_bar[st], a * kAtomBytes, (block0 + j) * kBlockKv,
                       kv_head, batch);
         }
         return true;
@@ -258,7 +270,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
         for (int a = 0; a < L::kVAtoms; ++a) {
           tma_load_3d(v_stage(st) + a * L::kVAtomBytes, &tmap_vt, &t.v_full_bar[st],
-                      (j * kBlockKv + a * kAtomElems) * 2, 0, batch * p.kv_heads + kv_head);
+                      ((block0 + j) * kBlockKv + a * kAtomElems) * 2, 0, batch * p.kv_heads + kv_head);
         }
         return true;
       };
@@ -373,7 +385,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     constexpr int kMyKeys = kBlockKv / 2;  // = one swizzle atom of P
     static_assert(kMyKeys == kAtomElems, "a warp writes one atom of P");
     const int row = static_cast<int>(quarter) * 32 + static_cast<int>(lane);  // query within the CTA = lane of tensor memory
-    const int q_pos = q0 + row + offset;  // the last key this query sees under the causal mask
+    const int q_pos = q0 + row + offset;  // this query's position among the keys
+    const int key_first = first_key_of(p, q_pos), key_last = last_key_of(p, q_pos);  // what it sees
+    // What every query of the CTA sees: a block of keys inside this range needs no masking.
+    const int common_first = first_key_of(p, last_row + offset), common_last = last_key_of(p, q0 + offset);
     const uint32_t t_lane = tmem_base + ((quarter * 32u) << 16);
     // Where this row's 16-byte pieces go in an atom of P: piece c of row r sits at c ^ (r & 7).
     uint8_t *p_row = p_smem + half * L::kPAtomBytes + (row >> 3) * 1024 + (row & 7) * kAtomBytes;
@@ -435,10 +450,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
     fetch_scores(0);
     for (int j = 0; j < num_blocks && ok; ++j) {
-      const int key0 = j * kBlockKv + static_cast<int>(half) * kMyKeys;  // this thread's first key
+      const int block_key0 = (block0 + j) * kBlockKv;
+      const int key0 = block_key0 + static_cast<int>(half) * kMyKeys;  // this thread's first key
       // Does any key of this block need masking for any row of the CTA?
-      const bool edge = (j * kBlockKv + kBlockKv > p.kv_len) || (p.causal && j * kBlockKv + kBlockKv - 1 > q0 + offset);
-      const int key_limit = p.causal ? min(p.kv_len - 1, q_pos) : p.kv_len - 1;  // last key this row sees
+      const bool edge = block_key0 < common_first || block_key0 + kBlockKv - 1 > common_last;
       // Masked (edge blocks only), and the maximum over this thread's keys; the scale to log2
       // units is positive, so it is applied to the maximum here and to the scores inside the
       // exponent's multiply-add below.
@@ -448,7 +463,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         for (int c = 0; c < kMyKeys / 32; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            if (key0 + c * 32 + i > key_limit) sc[c][i] = __float_as_uint(-INFINITY);
+            const int key = key0 + c * 32 + i;
+            if (key > key_last || key < key_first) sc[c][i] = __float_as_uint(-INFINITY);
           }
         }
       }
@@ -640,7 +656,10 @@ bool attention_supported(const AttentionArgs &a, const char **why) {
   if (a.batch < 0 || a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads != 0) return fail("heads is not a multiple of kv_heads");
   if (a.batch > 65535 || a.heads > 65535) return fail("more than 65535 heads or batches");
   if (a.q_len < 0 || a.kv_len <= 0) return fail("no keys");
-  if (a.causal && a.kv_len < a.q_len) return fail("the causal mask needs at least as many keys as queries");
+  if (a.mask_type < 0 || a.mask_type > 3) return fail("unknown mask");
+  if ((a.mask_type == 1 || a.mask_type == 2) && a.kv_len < a.q_len) return fail("the causal masks need at least as many keys as queries");
+  if (a.mask_type == 3 && a.kv_len != a.q_len) return fail("the block diagonal mask is self-attention: as many keys as queries");
+  if ((a.mask_type >= 2) != (a.block_size > 0)) return fail("a block size goes with a block mask, and only with one");
   const void *ptrs[4] = {a.q, a.k, a.v, a.out};
   for (const void *ptr : ptrs) {
     if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail("an operand does not start on a 16-byte boundary");
@@ -731,7 +750,8 @@ cudaError_t attention(const AttentionArgs &a, const char **why) {
   kp.group = a.heads / a.kv_heads;
   kp.q_len = a.q_len;
   kp.kv_len = a.kv_len;
-  kp.causal = a.causal;
+  kp.mask_type = a.mask_type;
+  kp.block_size = a.block_size;
   kp.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(d));
   kp.status = a.status;
   if (d == 64) return launch<64>(a, tq, tk, tvt, kp, why);

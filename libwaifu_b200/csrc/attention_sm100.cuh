@@ -11,22 +11,24 @@ namespace flsm100 {
 // flint/operators.h:255-272): q (batch, heads, q_len, head_dim), k and v (batch, kv_heads, kv_len,
 // head_dim), out like q; heads a multiple of kv_heads. Every tensor's last dimension is contiguous;
 // the other strides are in elements and need not be those of a contiguous tensor (a model hands in
-// (batch, length, heads, head_dim) transposed). Under the causal mask query i sees keys
-// 0 .. i + kv_len - q_len.
+// (batch, length, heads, head_dim) transposed). Query i sits at position p = i + kv_len - q_len and
+// sees every key (mask 0), keys 0 .. p (1, causal), the keys of p's own block of `block_size` and of
+// every block before it (2, block causal) or of p's own block alone (3, block diagonal).
 struct AttentionArgs {
   const void *q, *k, *v;
   void *out;
   int is_bf16;  // else half
   int batch, heads, kv_heads, q_len, kv_len, head_dim;
   int64_t q_stride[3], k_stride[3], v_stride[3], out_stride[3];  // batch, head, position
-  int causal;
+  int mask_type;   // fl_mask_type_t
+  int block_size;  // of the block masks, else 0
   void *v_transposed;   // scratch of attention_scratch_bytes(): v as (batch * kv_heads, head_dim, padded kv_len)
   uint32_t *status;     // device word: the kernel records a wait that gave up (never a hang)
   cudaStream_t stream;
 };
 
 // head_dim 64 or 128; bases 16-byte aligned and strides multiples of 8 elements (TMA reads the
-// operands); causal needs kv_len >= q_len.
+// operands); the causal masks need kv_len >= q_len, the block diagonal one kv_len == q_len.
 bool attention_supported(const AttentionArgs &a, const char **why);
 size_t attention_scratch_bytes(int batch, int kv_heads, int kv_len, int head_dim);
 // Two launches: the transposition of v, and the attention kernel.

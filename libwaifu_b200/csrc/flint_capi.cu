@@ -21,6 +21,7 @@
 #include "attention_sm100.cuh"
 #include "elementwise_sm100.cuh"
 #include "selftest_sm100.cuh"
+#include "matmul_simt_sm100.cuh"
 
 using namespace flsm100;
 
@@ -356,6 +357,16 @@ constexpr int64_t kMaxStorageElements = int64_t(1) << 30;  // TensorData::MaxNum
 constexpr size_t kResidentWeightBytes = size_t(2) << 20;   // flint/cuda/common.h:167
 
 bool is_half_type(fl_dtype_t t) { return t == FL_DTYPE_FLOAT16 || t == FL_DTYPE_BFLOAT16; }
+
+bool elem_kind_of(fl_dtype_t t, ElemKind *kind) {
+  switch (t) {
+    case FL_DTYPE_FLOAT: *kind = kElemF32; return true;
+    case FL_DTYPE_FLOAT16: *kind = kElemF16; return true;
+    case FL_DTYPE_BFLOAT16: *kind = kElemBF16; return true;
+    default: return false;
+  }
+}
+
 
 void check_shape(const fl_tensor_view_impl_t &v, const std::vector<int32_t> &shape, const char *what) {
   if (v.shape != shape) {
@@ -1088,10 +1099,13 @@ int32_t fl_matmul(fl_operators_t operators, fl_tensor_view_t a, fl_tensor_view_t
   return fl_matmul_add(operators, a, b, nullptr, out);
 }
 
-// The linear-layer case of flint's matmul on 16-bit operands: `b` is the transposed view of a
-// weight stored (n, k) row-major, which is how an unquantised Linear hands its weight over
-// (waifu/src/layers.rs:230-246). Other operand layouts of the reference's matmul are not served by
-// this library and are refused as such.
+// flint/capi.h:440-456, flint/cuda/matmul.cc:96-146,315-343. The linear-layer case on 16-bit
+// operands -- `b` the transposed view of a weight stored (n, k) row-major, which is how an
+// unquantised Linear hands its weight over (waifu/src/layers.rs:230-246), n and k multiples of 8 --
+// runs on the tcgen05 tile kernel (at most 16 rows: the few-row kernel). Everything else the
+// reference's matmul takes -- float32 operands, a float32 result from half operands, batches on
+// either side, other layouts of `b`, odd extents -- runs on the general kernel of
+// matmul_simt_sm100.cu.
 int32_t fl_matmul_add(fl_operators_t operators, fl_tensor_view_t a_h, fl_tensor_view_t b_h, fl_tensor_view_t addend_h,
                       fl_tensor_view_t out_h) {
   return guard([&]() -> int32_t {
@@ -1099,86 +1113,147 @@ int32_t fl_matmul_add(fl_operators_t operators, fl_tensor_view_t a_h, fl_tensor_
     const fl_tensor_view_impl_t &a = deref(a_h);
     const fl_tensor_view_impl_t &b = deref(b_h);
     const fl_tensor_view_impl_t &out = deref(out_h);
-    if (numel_of(a) == 0) invalid("the left operand is empty");
-    if (numel_of(b) == 0) invalid("the right operand is empty");
     for (const fl_tensor_view_impl_t *v : {&a, &b, &out}) {
       if (device_of(*v) != FL_DEVICE_CUDA) invalid("an operand is not on the operators' device");
     }
-    if (!is_half_type(dtype_of(a)) || dtype_of(b) != dtype_of(a) || dtype_of(out) != dtype_of(a)) {
-      invalid("matmul: this library multiplies <float16> or <bfloat16> operands of one type");
+    ElemKind in_kind, out_kind;
+    if (!elem_kind_of(dtype_of(a), &in_kind) || dtype_of(b) != dtype_of(a) || !elem_kind_of(dtype_of(out), &out_kind) ||
+        !(out_kind == in_kind || out_kind == kElemF32)) {
+      invalid("matmul: operands of one type, <float>, <float16> or <bfloat16>, into a result of that type or <float>");
     }
-    if (a.shape.size() < 2 || !is_contiguous(a)) invalid("matmul: the left operand is not a contiguous (..., k)");
-    if (b.shape.size() != 2) invalid("matmul: this library takes a two-dimensional right operand");
-    const int k = b.shape[0], n = b.shape[1];
-    if (a.shape.back() != k) invalid("the two operands disagree about k");
-    // (k, n) with strides (1, k): the transpose of a contiguous (n, k) weight.
-    const bool k_major = (b.stride[0] == 1 || k == 1) && (b.stride[1] == k || n == 1);
-    if (!k_major) {
-      invalid("matmul: the right operand is not the transposed view of a contiguous (n, k) weight; "
-              "other layouts are not implemented in this library");
+    if (a.shape.size() < 2 || b.shape.size() < 2 || b.shape.size() > a.shape.size()) {
+      invalid("matmul: both operands have at least two dimensions, the right one no more than the left");
     }
+    const int ad = static_cast<int>(a.shape.size()), bd = static_cast<int>(b.shape.size());
+    const int m_inner = a.shape[ad - 2], k = a.shape[ad - 1], n = b.shape[bd - 1];
+    if (b.shape[bd - 2] != k) invalid("the two operands disagree about k");
     if (!is_contiguous(out)) invalid("out is not contiguous");
     std::vector<int32_t> shape = a.shape;
     shape.back() = n;
     check_shape(out, shape, "out");
-    if (n % 8 != 0 || k % 8 != 0) invalid("matmul: n and k are multiples of 8 in this library");
+    // the right operand's leading dimensions, aligned to the left one's from the right, equal or 1
+    for (int i = 0; i < bd - 2; ++i) {
+      const int32_t bs = b.shape[i], as = a.shape[ad - bd + i];
+      if (bs != as && bs != 1) invalid("matmul: the right operand's leading dimensions do not broadcast over the left one's");
+    }
     const fl_tensor_view_impl_t *addend = addend_h ? &deref(addend_h) : nullptr;
     if (addend) {
       if (device_of(*addend) != FL_DEVICE_CUDA || dtype_of(*addend) != dtype_of(out) ||
           addend->shape.size() > out.shape.size()) {
-        invalid("the addend is not of out's type on the device, of out's shape");
+        invalid("matmul: the addend must be of the output's type and fit its shape");
       }
     }
     require_kernels();
     check_earlier_kernel_status();
+    if (numel_of(out) == 0) return clear_error();
     const int64_t m64 = leading_rows(a);
     if (m64 > INT32_MAX) invalid("the left operand has more rows than the kernels can index");
-    const int m = static_cast<int>(m64);
     const int is_bf16 = dtype_of(a) == FL_DTYPE_BFLOAT16;
 
-    // A handful of rows (the reference keeps a GEMV for this, flint/cuda/matvec.cu): one
-    // bandwidth-shaped launch with the bias or residual in its epilogue, no scratch.
-    if (m <= 16) {
-      static const bool no_skinny = []() {
-        const char *v = std::getenv("FLINT_SM100_NO_SKINNY");
-        return v && v[0] == '1';
-      }();
-      AddendPlan quick;
-      std::vector<int32_t> bs;
-      std::vector<int64_t> bt;
-      if (addend) quick = plan_addend(*addend, out, &bs, &bt);
-      if (!no_skinny && !quick.needs_expand &&
-          skinny_w16_supported(m, n, k, raw_ptr(a), raw_ptr(b), raw_ptr(out), quick.residual != nullptr)) {
-        cuda_check(skinny_w16_matmul(raw_ptr(a), is_bf16, m, n, k, raw_ptr(b), quick.bias, quick.residual, quick.residual_rows,
-                                     quick.residual_ld, raw_ptr(out), status_word(), 0),
-                   "few-row matmul");
-        ++g_gemm_launches;
-        return clear_error();
+    // ---- the linear-layer case on 16-bit operands: tensor cores ----
+    // (k, n) with strides (1, k): the transpose of a contiguous (n, k) weight.
+    const bool k_major = bd == 2 && (b.stride[0] == 1 || k == 1) && (b.stride[1] == k || n == 1);
+    if (in_kind != kElemF32 && out_kind == in_kind && k_major && is_contiguous(a) && n % 8 == 0 && k % 8 == 0 && k > 0) {
+      const int m = static_cast<int>(m64);
+      // A handful of rows (the reference keeps a GEMV for this, flint/cuda/matvec.cu): one
+      // bandwidth-shaped launch with the bias or residual in its epilogue, no scratch.
+      if (m <= 16) {
+        static const bool no_skinny = []() {
+          const char *v = std::getenv("FLINT_SM100_NO_SKINNY");
+          return v && v[0] == '1';
+        }();
+        AddendPlan quick;
+        std::vector<int32_t> bs;
+        std::vector<int64_t> bt;
+        if (addend) quick = plan_addend(*addend, out, &bs, &bt);
+        if (!no_skinny && !quick.needs_expand &&
+            skinny_w16_supported(m, n, k, raw_ptr(a), raw_ptr(b), raw_ptr(out), quick.residual != nullptr)) {
+          cuda_check(skinny_w16_matmul(raw_ptr(a), is_bf16, m, n, k, raw_ptr(b), quick.bias, quick.residual, quick.residual_rows,
+                                       quick.residual_ld, raw_ptr(out), status_word(), 0),
+                     "few-row matmul");
+          ++g_gemm_launches;
+          return clear_error();
+        }
       }
+      Scratch scratch;
+      size_t a_off = 0, b_off = 0;
+      const bool a_misaligned = !aligned16(raw_ptr(a));
+      const bool b_misaligned = !aligned16(raw_ptr(b));
+      if (a_misaligned) a_off = scratch.reserve(static_cast<size_t>(m) * k * 2);
+      if (b_misaligned) b_off = scratch.reserve(static_cast<size_t>(n) * k * 2);
+      AddendResolver res;
+      res.prepare(addend, out, &scratch);
+      uint8_t *base = scratch.used ? scratch.commit() : nullptr;
+      const void *a_ptr = raw_ptr(a);
+      const void *b_ptr = raw_ptr(b);
+      if (a_misaligned) {
+        cuda_check(cudaMemcpyAsync(base + a_off, a_ptr, static_cast<size_t>(m) * k * 2, cudaMemcpyDeviceToDevice, 0), "staging");
+        a_ptr = base + a_off;
+      }
+      if (b_misaligned) {
+        cuda_check(cudaMemcpyAsync(base + b_off, b_ptr, static_cast<size_t>(n) * k * 2, cudaMemcpyDeviceToDevice, 0), "staging");
+        b_ptr = base + b_off;
+      }
+      Epilogue ep;
+      res.resolve(base, m, n, &ep);
+      run_gemm(is_bf16 ? kGemmBF16 : kGemmF16, m, n, k, a_ptr, b_ptr, nullptr, nullptr, ep, is_bf16, raw_ptr(out));
+      return clear_error();
     }
 
+    // ---- every other case: the general kernel ----
+    GeneralMatmulArgs g = {};
+    g.a = raw_ptr(a);
+    g.b = raw_ptr(b);
+    g.out = raw_ptr(out);
+    g.in_kind = in_kind;
+    g.out_kind = out_kind;
+    g.n = n;
+    g.k = k;
+    g.a_col = a.stride[ad - 1];
+    g.b_row = b.stride[bd - 2];
+    g.b_col = b.stride[bd - 1];
+    g.stream = 0;
+    if (bd == 2 && is_contiguous(a)) {
+      // one right operand for every row of a contiguous left one: the leading dimensions fold into m
+      g.m = static_cast<int>(m64);
+      g.a_row = k;
+      g.a_col = 1;
+      g.batch_dims = 0;
+    } else {
+      g.m = m_inner;
+      g.a_row = a.stride[ad - 2];
+      const int lead = ad - 2;
+      if (lead > kMaxMatmulBatchDims) {
+        invalid("matmul: more than " + std::to_string(kMaxMatmulBatchDims) + " leading dimensions on a batched product");
+      }
+      g.batch_dims = lead;
+      int64_t batches = 1;
+      for (int i = 0; i < lead; ++i) {
+        g.batch_shape[i] = a.shape[i];
+        g.a_batch[i] = a.shape[i] == 1 ? 0 : a.stride[i];
+        const int bi = i - (ad - bd);  // the right operand's dimension under this one, if it has it
+        g.b_batch[i] = (bi >= 0 && b.shape[bi] != 1) ? b.stride[bi] : 0;
+        batches *= a.shape[i];
+      }
+      if (batches > 65535) invalid("matmul: more than 65535 products in a batch");
+    }
     Scratch scratch;
-    size_t a_off = 0, b_off = 0;
-    const bool a_misaligned = !aligned16(raw_ptr(a));
-    const bool b_misaligned = !aligned16(raw_ptr(b));
-    if (a_misaligned) a_off = scratch.reserve(static_cast<size_t>(m) * k * 2);
-    if (b_misaligned) b_off = scratch.reserve(static_cast<size_t>(n) * k * 2);
     AddendResolver res;
     res.prepare(addend, out, &scratch);
-    uint8_t *base = scratch.used ? scratch.commit() : nullptr;
-    const void *a_ptr = raw_ptr(a);
-    const void *b_ptr = raw_ptr(b);
-    if (a_misaligned) {
-      cuda_check(cudaMemcpyAsync(base + a_off, a_ptr, static_cast<size_t>(m) * k * 2, cudaMemcpyDeviceToDevice, 0), "staging");
-      a_ptr = base + a_off;
-    }
-    if (b_misaligned) {
-      cuda_check(cudaMemcpyAsync(base + b_off, b_ptr, static_cast<size_t>(n) * k * 2, cudaMemcpyDeviceToDevice, 0), "staging");
-      b_ptr = base + b_off;
+    uint8_t *base = nullptr;
+    if (scratch.used) {
+      if (out_kind == kElemF32 && res.plan.needs_expand) {
+        invalid("matmul: a <float> addend has to be a bias or a residual laid out as rows of out");
+      }
+      base = scratch.commit();
     }
     Epilogue ep;
-    res.resolve(base, m, n, &ep);
-    run_gemm(is_bf16 ? kGemmBF16 : kGemmF16, m, n, k, a_ptr, b_ptr, nullptr, nullptr, ep, is_bf16, raw_ptr(out));
+    res.resolve(base, static_cast<int>(m64), n, &ep);
+    g.bias = ep.bias;
+    g.residual = ep.residual;
+    g.residual_rows = ep.residual_rows;
+    g.residual_ld = ep.residual_ld;
+    cuda_check(general_matmul(g), "matmul");
     return clear_error();
   });
 }
@@ -1186,15 +1261,6 @@ int32_t fl_matmul_add(fl_operators_t operators, fl_tensor_view_t a_h, fl_tensor_
 // ---- the elementwise operators around the path (flint/capi.h:246-249,279,483) -------------------
 
 namespace {
-
-bool elem_kind_of(fl_dtype_t t, ElemKind *kind) {
-  switch (t) {
-    case FL_DTYPE_FLOAT: *kind = kElemF32; return true;
-    case FL_DTYPE_FLOAT16: *kind = kElemF16; return true;
-    case FL_DTYPE_BFLOAT16: *kind = kElemBF16; return true;
-    default: return false;
-  }
-}
 
 ElemView elem_view(const fl_tensor_view_impl_t &v, const char *what) {
   if (v.shape.size() > static_cast<size_t>(kMaxElemDims)) {
@@ -1884,8 +1950,8 @@ int32_t fl_qk_norm_rope(fl_tensor_view_t qkv_h, fl_tensor_view_t q_weight_h, fl_
   });
 }
 
-// flint/capi.h:532-544 for the masks none and causal. The block masks have no kernel here and are
-// refused with the reason, as the reference's devices without one refuse them.
+// flint/capi.h:532-544, every mask of flint/capi.h:118-133; the checks are those of
+// flint/operators.cc:108-146.
 int32_t fl_attention(fl_operators_t operators, fl_tensor_view_t q_h, fl_tensor_view_t k_h, fl_tensor_view_t v_h,
                      fl_mask_type_t mask_type, int32_t block_size, fl_tensor_view_t out_h) {
   return guard([&]() -> int32_t {
@@ -1895,11 +1961,12 @@ int32_t fl_attention(fl_operators_t operators, fl_tensor_view_t q_h, fl_tensor_v
     const fl_tensor_view_impl_t &v = deref(v_h);
     const fl_tensor_view_impl_t &out = deref(out_h);
     if (mask_type < FL_MASK_NONE || mask_type > FL_MASK_BLOCK_DIAGONAL) invalid("attention: unknown mask type");
-    if (mask_type == FL_MASK_NONE || mask_type == FL_MASK_CAUSAL) {
-      if (block_size != 0) invalid("attention: a block size beside a mask that has no blocks");
-    } else {
-      if (block_size <= 0) invalid("attention: a block mask without a block size");
-      invalid("attention: the block masks are not implemented in this library");
+    const bool block_mask = mask_type == FL_MASK_BLOCK_CAUSAL || mask_type == FL_MASK_BLOCK_DIAGONAL;
+    if (!block_mask && block_size != 0) {
+      invalid("attention: a block size of " + std::to_string(block_size) + " without a block mask");
+    }
+    if (block_mask && block_size <= 0) {
+      invalid("attention: a block mask of " + std::to_string(block_size) + " keys a block");
     }
     for (const fl_tensor_view_impl_t *t : {&q, &k, &v, &out}) {
       if (t->shape.size() != 4) invalid("attention: q, k, v and out are four-dimensional");
@@ -1916,6 +1983,14 @@ int32_t fl_attention(fl_operators_t operators, fl_tensor_view_t q_h, fl_tensor_v
     if (kv_heads <= 0 || heads % kv_heads != 0) invalid("attention: the query heads are not a multiple of the key-value heads");
     if (kv_len <= 0) invalid("attention: no keys");
     if (mask_type == FL_MASK_CAUSAL && kv_len < q_len) invalid("attention: keys too few for the causal mask");
+    if (mask_type == FL_MASK_BLOCK_CAUSAL && kv_len < q_len) {
+      invalid("attention: a block causal mask over " + std::to_string(kv_len) + " keys and " + std::to_string(q_len) +
+              " queries, which leaves the first queries before every key");
+    }
+    if (mask_type == FL_MASK_BLOCK_DIAGONAL && kv_len != q_len) {
+      invalid("attention: a block diagonal mask is self-attention, and this is " + std::to_string(q_len) +
+              " queries over " + std::to_string(kv_len) + " keys");
+    }
     require_kernels();
     check_earlier_kernel_status();
     if (batch == 0 || q_len == 0) return clear_error();
@@ -1938,7 +2013,8 @@ int32_t fl_attention(fl_operators_t operators, fl_tensor_view_t q_h, fl_tensor_v
       a.v_stride[i] = v.stride[i];
       a.out_stride[i] = out.stride[i];
     }
-    a.causal = mask_type == FL_MASK_CAUSAL;
+    a.mask_type = static_cast<int>(mask_type);
+    a.block_size = block_size;
     a.status = status_word();
     a.stream = 0;
     const char *why = "";
@@ -2093,7 +2169,8 @@ int32_t fl_sm100_gemm_plan(int32_t kind, int32_t m, int32_t n, int32_t k, int32_
 }
 
 int64_t fl_sm100_launch_count(void) {
-  return g_gemm_launches.load() + g_block_launches.load() + helper_launch_count() + elementwise_launch_count();
+  return g_gemm_launches.load() + g_block_launches.load() + helper_launch_count() + elementwise_launch_count() +
+         general_matmul_launch_count();
 }
 
 

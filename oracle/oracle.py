@@ -265,13 +265,31 @@ def qk_norm_rope(qkv16: np.ndarray, cos: np.ndarray, sin: np.ndarray, heads: int
     return out
 
 
-def attention(q16: np.ndarray, k16: np.ndarray, v16: np.ndarray, causal: bool, is_bf16: bool) -> np.ndarray:
+def attention_keep(mask, block_size: int, L: int, S: int):
+    """Which keys each query may see (flint/capi.h:118-133, flint/cuda/attention.cu:165-179): query i
+    sits at position p = i + S - L; `mask` is False/0 (every key), True/1 (causal: keys 0..p), 2
+    (block causal: p's block of `block_size` keys and every block before it) or 3 (block diagonal:
+    p's block alone). Returns a boolean (L, S) array, or None for no mask."""
+    mask = int(mask)
+    if mask == 0:
+        return None
+    pos = (np.arange(L) + (S - L))[:, None]
+    key = np.arange(S)[None, :]
+    if mask == 1:
+        return key <= pos
+    first = (pos // block_size) * block_size if mask == 3 else 0
+    last = np.minimum(S - 1, (pos // block_size) * block_size + block_size - 1)
+    return (key >= first) & (key <= last)
+
+
+def attention(q16: np.ndarray, k16: np.ndarray, v16: np.ndarray, causal, is_bf16: bool, block_size: int = 0) -> np.ndarray:
     """Scaled dot product attention on 16-bit bit patterns, q (N, heads, L, D), k and v
     (N, kv_heads, S, D) with kv_heads dividing heads (query head h reads key-value head
     h // (heads / kv_heads), flint/operators.h:255-260): softmax(q k^T / sqrt(D)) v in float64,
-    under the causal mask query i seeing keys 0 .. i + S - L (flint/capi.h:118-126). Returns
-    float64; no intermediate is rounded, so a kernel that rounds its probabilities to 16 bits
-    (flint/cuda/attention.cu:30-70, flint/operators.cc:170-175) agrees to that rounding."""
+    under the mask `causal` names (a bool, or a mask number with its `block_size`: see
+    attention_keep). Returns float64; no intermediate is rounded, so a kernel that rounds its
+    probabilities to 16 bits (flint/cuda/attention.cu:30-70, flint/operators.cc:170-175) agrees to
+    that rounding."""
     q = widen(np.asarray(q16, np.uint16), is_bf16).astype(np.float64)
     k = widen(np.asarray(k16, np.uint16), is_bf16).astype(np.float64)
     v = widen(np.asarray(v16, np.uint16), is_bf16).astype(np.float64)
@@ -279,9 +297,7 @@ def attention(q16: np.ndarray, k16: np.ndarray, v16: np.ndarray, causal: bool, i
     kv_heads, S = k.shape[1], k.shape[2]
     group = heads // kv_heads
     out = np.empty((n, heads, L, d), np.float64)
-    keep = None
-    if causal:
-        keep = np.arange(S)[None, :] <= (np.arange(L)[:, None] + (S - L))
+    keep = attention_keep(causal, block_size, L, S)
     for b in range(n):
         for h in range(heads):
             s = q[b, h] @ k[b, h // group].T / np.sqrt(float(d))
@@ -407,9 +423,10 @@ class _Ref:
         """fl_swiglu (flint/capi.h:517-519)."""
         return self._unary(lambda vx, a, vo: self.L.fl_swiglu(self.ops, vx, vo), x, x.shape[1] // 2)
 
-    def attention(self, q: np.ndarray, k: np.ndarray, v: np.ndarray, causal: bool) -> np.ndarray:
+    def attention(self, q: np.ndarray, k: np.ndarray, v: np.ndarray, causal, block_size: int = 0) -> np.ndarray:
         """fl_attention on the CPU device with float32 operands (flint/capi.h:532-544): q
-        (N, heads, L, D), k and v (N, kv_heads, S, D), contiguous."""
+        (N, heads, L, D), k and v (N, kv_heads, S, D), contiguous; `causal` a bool or a mask
+        number (flint/capi.h:118-133) with its `block_size`."""
         arrs = [np.ascontiguousarray(t, dtype=np.float32) for t in (q, k, v)]
         out = np.empty(arrs[0].shape, dtype=np.float32)
         held = []
@@ -417,7 +434,7 @@ class _Ref:
             for t in arrs + [out]:
                 stride = [int(np.prod(t.shape[i + 1:])) for i in range(4)]
                 held.append(self._view(t, t.shape, stride))
-            self._check(self.L.fl_attention(self.ops, held[0][1], held[1][1], held[2][1], 1 if causal else 0, 0, held[3][1]))
+            self._check(self.L.fl_attention(self.ops, held[0][1], held[1][1], held[2][1], int(causal), int(block_size), held[3][1]))
         finally:
             for d, vw in held:
                 self.L.fl_tensor_view_destroy(vw)

@@ -25,10 +25,10 @@ def make(oracle, rng, n, h, hk, L, S, d, is_bf16, spread=1.0):
     return q, k, v
 
 
-def run(F, q, k, v, causal, is_bf16):
+def run(F, q, k, v, causal, is_bf16, block_size=0):
     dt = dtype_of(F, is_bf16)
     tq, tk, tv = (F.Tensor.from_numpy(t, dt, F.Device.CUDA) for t in (q, k, v))
-    out = F.attention(tq, tk, tv, F.MaskType.CAUSAL if causal else F.MaskType.NONE, 0)
+    out = F.attention(tq, tk, tv, int(causal), block_size)
     got = out.numpy()
     F.synchronize()
     return got
@@ -98,11 +98,11 @@ def test_transposed_operands(flint, oracle):
     check(oracle, got, oracle.attention(q, k, v, True, True), True, "transposed")
 
 
-@pytest.mark.parametrize("name", ["causal_gqa", "full_d128"])
+@pytest.mark.parametrize("name", ["causal_gqa", "full_d128", "block_causal", "block_diagonal"])
 def test_golden_vectors(flint, oracle, name):
     fx = np.load(GOLDEN)
-    causal, is_bf16 = (bool(x) for x in fx[name + "_flags"])
-    got = run(flint, fx[name + "_q"], fx[name + "_k"], fx[name + "_v"], causal, is_bf16)
+    mask, is_bf16, block = (int(x) for x in fx[name + "_flags"])
+    got = run(flint, fx[name + "_q"], fx[name + "_k"], fx[name + "_v"], mask, bool(is_bf16), block)
     check(oracle, got, fx[name + "_y"].astype(np.float64), is_bf16, name)
 
 
@@ -112,13 +112,14 @@ def test_what_is_not_a_mask_is_refused(flint, oracle):
     q, k, v = make(oracle, rng, 1, 2, 2, 16, 16, 64, True)
     tq, tk, tv = (F.Tensor.from_numpy(t, F.DType.BFLOAT16, F.Device.CUDA) for t in (q, k, v))
     for mask, block in [(F.MaskType.NONE, 4), (F.MaskType.CAUSAL, 4), (F.MaskType.BLOCK_CAUSAL, 0),
-                        (F.MaskType.BLOCK_CAUSAL, 4), (F.MaskType.BLOCK_DIAGONAL, 4), (7, 0)]:
+                        (F.MaskType.BLOCK_DIAGONAL, -1), (7, 0)]:
         with pytest.raises(F.FlintError):
             F.attention(tq, tk, tv, mask, block)
-    # Keys too few for the causal mask; a head_dim without a kernel.
+    # Keys too few for the causal masks, or not as many as queries for the diagonal one; a head_dim without a kernel.
     short = F.Tensor.from_numpy(k[:, :, :8].copy(), F.DType.BFLOAT16, F.Device.CUDA)
-    with pytest.raises(F.FlintError):
-        F.attention(tq, short, short, F.MaskType.CAUSAL, 0)
+    for mask, block in [(F.MaskType.CAUSAL, 0), (F.MaskType.BLOCK_CAUSAL, 4), (F.MaskType.BLOCK_DIAGONAL, 4)]:
+        with pytest.raises(F.FlintError):
+            F.attention(tq, short, short, mask, block)
     q96, k96, v96 = make(oracle, rng, 1, 1, 1, 8, 8, 96, True)
     t96 = [F.Tensor.from_numpy(t, F.DType.BFLOAT16, F.Device.CUDA) for t in (q96, k96, v96)]
     with pytest.raises(F.FlintError):
@@ -176,3 +177,27 @@ def test_broadcast_views_are_refused_or_read_correctly(flint, oracle):
     got1 = F.attention(q1, k1, v1, F.MaskType.NONE, 0).numpy()
     F.synchronize()
     check(oracle, got1, oracle.attention(q[:1], k[:1], v[:1], False, True), True, "batch of one, stride 0")
+
+
+BLOCK_CASES = [
+    # mask, block_size, n, heads, kv_heads, L, S, d
+    (2, 64, 1, 2, 2, 300, 300, 64),     # block causal, blocks half a tile
+    (2, 200, 1, 4, 2, 513, 700, 128),   # blocks that straddle tiles, more keys than queries, grouped heads
+    (2, 1, 1, 1, 1, 130, 130, 64),      # blocks of one key: the causal mask
+    (3, 128, 2, 2, 2, 512, 512, 128),   # block diagonal, blocks equal to tiles: every other block of keys is skipped
+    (3, 48, 1, 3, 1, 333, 333, 64),     # ragged blocks inside tiles
+    (3, 1000, 1, 2, 2, 260, 260, 128),  # one block covers everything: no mask
+]
+
+
+@pytest.mark.parametrize("mask,block,n,h,hk,L,S,d", BLOCK_CASES)
+@pytest.mark.parametrize("is_bf16", [True, False])
+def test_block_masks(flint, oracle, mask, block, n, h, hk, L, S, d, is_bf16):
+    rng = np.random.default_rng(300 + mask * 10 + block)
+    q, k, v = make(oracle, rng, n, h, hk, L, S, d, is_bf16)
+    got = run(flint, q, k, v, mask, is_bf16, block)
+    check(oracle, got, oracle.attention(q, k, v, mask, is_bf16, block), is_bf16, f"mask {mask} block {block}")
+    if block == 1 and mask == 2:
+        assert np.array_equal(got, run(flint, q, k, v, 1, is_bf16))      # the causal mask, bit for bit
+    if block >= S and mask == 3:
+        assert np.array_equal(got, run(flint, q, k, v, 0, is_bf16))      # no mask, bit for bit
