@@ -361,13 +361,19 @@ def run_ours(args, wl):
         operand_sets.append((wrap(x, bf), layers, bias))
     outs = [F.Tensor.empty((m, n), bf) for (n, _) in wl["gemms"]]
 
-    nsplit = args.parallel in ("nsplit", "nsplit_push")
-    push = args.parallel == "nsplit_push"
-    if nsplit:
-        # Strong scaling of one MLP: every rank holds a slice of each weight's output channels,
-        # multiplies the whole activation by it and all-gathers the slices (H, then Y) over NCCL.
-        if not (wl["kind"] == "fp8" and len(wl["gemms"]) == 2 and dist is not None):
-            raise SystemExit("--parallel nsplit needs the c2_mlp workload and more than one GPU")
+    nsplit = args.parallel in ("nsplit", "nsplit_push", "nsplit_fp8")
+
+    def build_split(mode):
+        """Strong scaling of one MLP: every rank holds a slice of each weight's output channels and
+        multiplies the whole activation by it. `mode` says how H and Y reach every rank:
+          nsplit       NCCL all-gathers of the 16-bit slices;
+          nsplit_push  the GEMMs' epilogues write their column blocks into every rank's full-width H
+                       and Y over NVLink (peer-mapped storage);
+          nsplit_fp8   H crosses as e4m3 codes: the up GEMM's epilogue leaves the rows' maxima, one
+                       all-reduce(MAX) of m floats makes them the whole rows', a quantise-and-scatter
+                       kernel writes the codes to every rank, the down GEMM reads codes and scatters Y.
+        A one-element all-reduce on the stream orders the ranks after each scatter. Returns the step
+        and the tensor the result lands in."""
         from libwaifu_b200 import sharding
         (n_up, k_up), (n_dn, k_dn) = wl["gemms"]
         up_a, up_b = sharding.column_shard(n_up, world, rank, 128)
@@ -375,48 +381,72 @@ def run_ours(args, wl):
         up_sizes = sharding.column_sizes(n_up, world, 128)
         dn_sizes = sharding.column_sizes(n_dn, world, 128)
         g2 = torch.Generator(device="cuda").manual_seed(77)
+        g3 = torch.Generator(device="cuda").manual_seed(4321 + rank)
         x_t = torch.randn(m, k_up, device="cuda", dtype=torch.bfloat16, generator=g2)
         x_cols_t = x_t[:, dn_a:dn_b].contiguous()
-        w_up = torch.randn(up_b - up_a, k_up, device="cuda", dtype=torch.float32, generator=gen) * 0.02
-        w_dn = torch.randn(dn_b - dn_a, k_dn, device="cuda", dtype=torch.float32, generator=gen) * 0.02
+        w_up = torch.randn(up_b - up_a, k_up, device="cuda", dtype=torch.float32, generator=g3) * 0.02
+        w_dn = torch.randn(dn_b - dn_a, k_dn, device="cuda", dtype=torch.float32, generator=g3) * 0.02
         up_q = F.quantize_fp8_rows(wrap(w_up, F.DType.FLOAT))
         dn_q = F.quantize_fp8_rows(wrap(w_dn, F.DType.FLOAT))
         F.synchronize()
         del w_up, w_dn
         h_loc_t = torch.empty(m, up_b - up_a, device="cuda", dtype=torch.bfloat16)
-        h_t = torch.empty(m, n_up, device="cuda", dtype=torch.bfloat16)
-        y_loc_t = torch.empty(m, dn_b - dn_a, device="cuda", dtype=torch.bfloat16)
-        y_t = torch.empty(m, n_dn, device="cuda", dtype=torch.bfloat16)
-        x_w, x_cols_w = wrap(x_t, bf), wrap(x_cols_t, bf)
-        h_loc_w, h_w, y_loc_w = wrap(h_loc_t, bf), wrap(h_t, bf), wrap(y_loc_t, bf)
+        x_w, x_cols_w, h_loc_w = wrap(x_t, bf), wrap(x_cols_t, bf), wrap(h_loc_t, bf)
+        if mode == "nsplit":
+            h_t = torch.empty(m, n_up, device="cuda", dtype=torch.bfloat16)
+            y_loc_t = torch.empty(m, dn_b - dn_a, device="cuda", dtype=torch.bfloat16)
+            y_t = torch.empty(m, n_dn, device="cuda", dtype=torch.bfloat16)
+            h_w, y_loc_w = wrap(h_t, bf), wrap(y_loc_t, bf)
 
-        def nsplit_step():
-            F.fp8_linear(x_w, up_q[0], up_q[1], None, None, F.ACT_GELU_TANH, h_loc_w)
-            sharding.all_gather_columns(dist, h_loc_t, up_sizes, h_t)
-            F.fp8_linear(h_w, dn_q[0], dn_q[1], None, x_cols_w, F.ACT_NONE, y_loc_w)
-            sharding.all_gather_columns(dist, y_loc_t, dn_sizes, y_t)
+            def split_step():
+                F.fp8_linear(x_w, up_q[0], up_q[1], None, None, F.ACT_GELU_TANH, h_loc_w)
+                sharding.all_gather_columns(dist, h_loc_t, up_sizes, h_t)
+                F.fp8_linear(h_w, dn_q[0], dn_q[1], None, x_cols_w, F.ACT_NONE, y_loc_w)
+                sharding.all_gather_columns(dist, y_loc_t, dn_sizes, y_t)
+            return split_step, wrap(y_t, bf), x_w, (h_t, y_t, y_loc_t)
 
-        if push:
-            # The all-gathers fused into the GEMMs: every rank's epilogue writes its column block
-            # into every rank's full-width H and Y over NVLink (peer-mapped storage), and a
-            # one-element all-reduce on the stream orders the ranks before the result is read.
-            h_own = F.Tensor.empty((m, n_up), bf, hint=F.AllocHint.WEIGHT)  # memory of its own: exportable
-            y_own = F.Tensor.empty((m, n_dn), bf, hint=F.AllocHint.WEIGHT)
-            handles = [None] * world
-            dist.all_gather_object(handles, (F.ipc_export(h_own), F.ipc_export(y_own)))
-            h_dests, y_dests = [h_own], [y_own]
-            for r in range(world):
-                if r != rank:
-                    h_dests.append(F.ipc_import(handles[r][0], (m, n_up), bf))
-                    y_dests.append(F.ipc_import(handles[r][1], (m, n_dn), bf))
-            flag = torch.zeros(1, device="cuda", dtype=torch.float32)
-
-            def nsplit_step():  # noqa: F811
+        # memory of its own (not the pool's): the only kind another process can map
+        h_dtype = F.DType.FP8E4M3 if mode == "nsplit_fp8" else bf
+        h_own = F.Tensor.empty((m, n_up), h_dtype, hint=F.AllocHint.WEIGHT)
+        y_own = F.Tensor.empty((m, n_dn), bf, hint=F.AllocHint.WEIGHT)
+        handles = [None] * world
+        dist.all_gather_object(handles, (F.ipc_export(h_own), F.ipc_export(y_own)))
+        h_dests, y_dests = [h_own], [y_own]
+        for r in range(world):
+            if r != rank:
+                h_dests.append(F.ipc_import(handles[r][0], (m, n_up), h_dtype))
+                y_dests.append(F.ipc_import(handles[r][1], (m, n_dn), bf))
+        flag = torch.zeros(1, device="cuda", dtype=torch.float32)
+        if mode == "nsplit_push":
+            def split_step():
                 F.fp8_linear_scatter(x_w, up_q[0], up_q[1], h_dests, up_a, None, None, F.ACT_GELU_TANH)
                 dist.all_reduce(flag)
                 F.fp8_linear_scatter(h_own, dn_q[0], dn_q[1], y_dests, dn_a, None, x_cols_w, F.ACT_NONE)
                 dist.all_reduce(flag)
-            y_result = y_own
+            return split_step, y_own, x_w, (h_dests, y_dests, flag)
+
+        amax_t = torch.zeros(m, device="cuda", dtype=torch.float32)
+        scales_t = torch.zeros(m, device="cuda", dtype=torch.float32)
+        amax_w, scales_w = wrap(amax_t, F.DType.FLOAT), wrap(scales_t, F.DType.FLOAT)
+
+        def split_step():
+            F.fp8_linear_amax(x_w, up_q[0], up_q[1], amax_w, None, None, F.ACT_GELU_TANH, h_loc_w)
+            dist.all_reduce(amax_t, op=dist.ReduceOp.MAX)
+            F.fp8_quantize_scatter(h_loc_w, amax_w, h_dests, up_a, scales_w)
+            dist.all_reduce(flag)
+            F.fp8_linear_quantized_scatter(h_own, scales_w, dn_q[0], dn_q[1], y_dests, dn_a, None, x_cols_w, F.ACT_NONE)
+            dist.all_reduce(flag)
+        return split_step, y_own, x_w, (h_dests, y_dests, flag, amax_t, scales_t, h_loc_t)
+
+    SPLIT_WORDS = {
+        "nsplit": "NCCL all-gather of H and Y in 16 bits",
+        "nsplit_push": "epilogues push H and Y (16 bits) to peers over NVLink",
+        "nsplit_fp8": "H crosses as e4m3 codes (row maxima all-reduced, quantise-and-scatter kernel), the down GEMM's epilogue pushes Y",
+    }
+    if nsplit:
+        if not (wl["kind"] == "fp8" and len(wl["gemms"]) == 2 and dist is not None):
+            raise SystemExit("--parallel nsplit* needs the c2_mlp workload and more than one GPU")
+        nsplit_step, split_result, x_w, split_keep = build_split(args.parallel)
 
     def step(i, x_override=None, alloc=False):
         """One step on operand set i. `alloc`: the outputs are allocated by the call, as the
@@ -546,7 +576,7 @@ def run_ours(args, wl):
     host_x = F.Tensor.empty((m, k0), bf, F.Device.CUDA_HOST)
     host_y = F.Tensor.empty((m, n_last), bf, F.Device.CUDA_HOST)
     os.sched_setaffinity(0, affinity)  # only the allocation (and its first touch) needed the binding
-    result = (y_own if push else wrap(y_t, bf)) if nsplit else None
+    result = split_result if nsplit else None
     import ctypes
     import numpy as np
     p = ctypes.c_void_p()
@@ -623,6 +653,25 @@ def run_ours(args, wl):
         cpu_baseline = {"value": flops_per_step(wl, rows) / best / 1e12, "unit": UNIT, "cores": cores, "kind": kind,
                         "sample": f"{rows} of {m} rows, whole step on the host, best of 3"}
 
+    # ---- the same MLP once more, split over the ranks by output channel (strong scaling) ----------
+    strong = None
+    if dist is not None and not nsplit and wl["kind"] == "fp8" and len(wl["gemms"]) == 2 and not args.no_strong_scaling:
+        del operand_sets[1:]
+        split_step, _, _, split_keep = build_split("nsplit_fp8")
+        for _ in range(max(3, args.warmup)):
+            split_step()
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            split_step()
+        e1.record()
+        barrier()
+        split_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+        strong = {"ms_per_step": split_ms, "one_gpu_ms_per_step": ms_step, "speedup_over_one_gpu": ms_step / split_ms,
+                  "value": flops_per_step(wl) / (split_ms * 1e-3) / 1e12, "unit": UNIT, "rows": m,
+                  "how": f"one MLP of {m} rows, weights split by output channel x{world}: {SPLIT_WORDS['nsplit_fp8']}; "
+                         "bit-identical to the unsplit MLP; one_gpu_ms_per_step is this run's own step (every rank the whole MLP)"}
+
     if rank == 0:
         touched = sets * (m * k0 * 2 + sum(n * k * (1 if wl["kind"] == "fp8" else 0.5625) for (n, k) in wl["gemms"]))
         line = {
@@ -631,8 +680,7 @@ def run_ours(args, wl):
             "vs_baseline": None,
             "dtype": "e4m3" if wl["kind"] == "fp8" else "e2m1", "data": "synthetic",
             "config": {"workload": args.workload, "what": wl["desc"], "m_per_gpu": m,
-                       "parallelism": ((f"weights split by output channel x{world}, epilogue pushes H and Y to peers over NVLink"
-                                        if push else f"weights split by output channel x{world}, NCCL all-gather of H and Y")
+                       "parallelism": (f"weights split by output channel x{world}, {SPLIT_WORDS[args.parallel]}"
                                        if nsplit else f"batch-sharded x{world}, weights replicated, no collective"),
                        "l2": f"{sets} rotating operand sets ({touched / 1e6:.0f} MB of inputs) > 126 MB L2",
                        "accumulate": "fp32", "out": "bf16"},
@@ -642,6 +690,7 @@ def run_ours(args, wl):
                            "fl_transfer_wait, downloads on a second copy stream; outputs allocated per call; one host wait per step",
                     "host_memory": bind_note},
             "per_call_alloc": alloc_check,
+            "strong_scaling": strong,
             "gpu_launches": launches,
             "clocks": sampler.summary(),
             "roofline": roofline,
@@ -1323,9 +1372,11 @@ def main():
     ap.add_argument("--e2e-chunks", type=int, default=4, help="row chunks the end-to-end step is pipelined in")
     ap.add_argument("--sustained-seconds", type=float, default=1.0,
                     help="length of the extra back-to-back loop behind roofline.sustained (0: skip it)")
-    ap.add_argument("--parallel", default="batch", choices=["batch", "nsplit", "nsplit_push"],
-                    help="batch: rows sharded, no collective (weak scaling); nsplit: one MLP with its weights "
-                         "split by output channel and NCCL all-gathers (strong scaling)")
+    ap.add_argument("--parallel", default="batch", choices=["batch", "nsplit", "nsplit_push", "nsplit_fp8"],
+                    help="batch: rows sharded, no collective (weak scaling; at N > 1 the line also carries a "
+                         "strong_scaling object from the nsplit_fp8 form); nsplit*: one MLP with its weights split by "
+                         "output channel (strong scaling): NCCL all-gathers / epilogue pushes in 16 bits / H gathered as e4m3 codes")
+    ap.add_argument("--no-strong-scaling", action="store_true", help="leave the strong_scaling object out of a batch run at N > 1")
     ap.add_argument("--blocks", type=int, default=None, help="c4_mmdit_step: run this many blocks instead of 60")
     ap.add_argument("--attention", default="flint", choices=["sdpa", "flint"],
                     help="c4_mmdit_step: this library's fl_attention (the reported number), or torch's attention; "

@@ -258,6 +258,34 @@ FLAPI int32_t fl_fp8_linear_scatter(fl_tensor_view_t a, fl_tensor_view_t data, f
                                     fl_tensor_view_t bias, fl_tensor_view_t residual, int32_t act,
                                     const fl_tensor_view_t *dests, int32_t n_dest, int32_t col0);
 
+/* The two halves of a narrow gather, for a matrix H = act(a W^T) split over the GPUs by output
+ * channel whose next use is another fl_fp8_linear: moving H as e4m3 codes costs half the bytes of
+ * moving it in 16 bits, but a row's codes need the row's scale, the maximum over ALL its columns.
+ *   fl_fp8_linear_amax: fl_fp8_linear into `out` (this rank's column block, local) that also leaves
+ *     in row_amax <float>(rows of a) the largest magnitude of each row of `out` as rounded (the call
+ *     clears row_amax first; the epilogue merges with atomicMax).
+ *   -- the caller takes the maximum of row_amax over the ranks (one all-reduce of m floats) --
+ *   fl_fp8_quantize_scatter: x <float16|bfloat16>(..., k) (the block), quantised per row exactly as
+ *     fl_quantize_fp8_activation would quantise the whole row (scale = row_amax / 448), the codes
+ *     written into columns [col0, col0 + k) of each of `n_dest` (1..8) <fp8e4m3>(..., ld) matrices:
+ *     this GPU's and, through fl_sm100_ipc_import(), its peers', with plain 16-byte stores. Leaves the
+ *     rows' scales in row_scales <float>(rows) if that is not NULL. k, ld, col0 multiples of 16.
+ * The gathered codes and scales then go to fl_fp8_linear_quantized(), and the result equals the
+ * unsplit fl_fp8_linear chain bit for bit. The caller orders the ranks (a barrier or any collective
+ * on the stream) between the scatter and the first read. No counterpart in the reference. */
+FLAPI int32_t fl_fp8_linear_amax(fl_tensor_view_t a, fl_tensor_view_t data, fl_tensor_view_t scales, fl_tensor_view_t bias,
+                                 fl_tensor_view_t residual, int32_t act, fl_tensor_view_t out, fl_tensor_view_t row_amax);
+FLAPI int32_t fl_fp8_quantize_scatter(fl_tensor_view_t x, fl_tensor_view_t row_amax, const fl_tensor_view_t *dests,
+                                      int32_t n_dest, int32_t col0, fl_tensor_view_t row_scales);
+
+/* fl_fp8_linear_quantized() with fl_fp8_linear_scatter()'s way out: codes <fp8e4m3>(..., k) and their
+ * rows' scales times the weight, the product written into columns [col0, col0 + rows) of each of
+ * `n_dest` (1..8) <float16|bfloat16>(..., ld) matrices, whose type is the product's. The second GEMM
+ * of a column-split MLP whose hidden activation was gathered as codes. */
+FLAPI int32_t fl_fp8_linear_quantized_scatter(fl_tensor_view_t codes, fl_tensor_view_t row_scales, fl_tensor_view_t data,
+                                              fl_tensor_view_t scales, fl_tensor_view_t bias, fl_tensor_view_t residual,
+                                              int32_t act, const fl_tensor_view_t *dests, int32_t n_dest, int32_t col0);
+
 /* Device storage shared between the processes of one box (one process per GPU): export writes
  * the 64-byte handle of storage made by fl_tensor_data_create(FL_DEVICE_CUDA, ..., FL_ALLOC_WEIGHT, ...)
  * of 2 MiB or more (memory of its own; blocks of the stream-ordered pool have no handle); import maps

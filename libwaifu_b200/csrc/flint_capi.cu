@@ -516,6 +516,7 @@ struct Epilogue {
   int residual_rows = 0;
   int64_t residual_ld = 0;
   int act = 0;
+  float *row_amax = nullptr;
 };
 
 // The stream-K workspace, from the pool in stream 0's order the first time a GEMM runs (38 MB on a
@@ -565,6 +566,7 @@ void run_gemm(GemmKind kind, int m, int n, int k, const void *a, const void *b, 
   g.residual_rows = ep.residual_rows;
   g.residual_ld = ep.residual_ld;
   g.act = ep.act;
+  g.row_amax = ep.row_amax;
   g.out_bf16 = out_bf16;
   g.out = out;
   for (int i = 0; i < 7; ++i) g.extra_out[i] = ep.extra_out[i];
@@ -1360,8 +1362,10 @@ int32_t fl_add(fl_operators_t operators, fl_tensor_view_t a_h, fl_tensor_view_t 
 
 // ============================ Part 2 ==========================================================
 
-int32_t fl_fp8_linear(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_view_t scales_h,
-                      fl_tensor_view_t bias_h, fl_tensor_view_t residual_h, int32_t act, fl_tensor_view_t out_h) {
+namespace {
+int32_t fp8_linear_impl(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_view_t scales_h,
+                        fl_tensor_view_t bias_h, fl_tensor_view_t residual_h, int32_t act, fl_tensor_view_t out_h,
+                        fl_tensor_view_t row_amax_h, bool want_amax) {
   return guard([&]() -> int32_t {
     const fl_tensor_view_impl_t &weight = deref(data_h);
     const fl_tensor_view_impl_t &scales = deref(scales_h);
@@ -1407,7 +1411,17 @@ int32_t fl_fp8_linear(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_v
       const char *v = std::getenv("FLINT_SM100_NO_SKINNY");
       return v && v[0] == '1';
     }();
-    if (!no_skinny && m <= 4 && skinny_fp8_supported(m, rows, k, raw_ptr(a), raw_ptr(weight), raw_ptr(out), residual != nullptr)) {
+    float *row_amax = nullptr;
+    if (want_amax) {
+      const fl_tensor_view_impl_t &am = deref(row_amax_h);
+      if (dtype_of(am) != FL_DTYPE_FLOAT || numel_of(am) != m64 || !is_contiguous(am) || device_of(am) != device) {
+        invalid("row_amax is not a contiguous <float> tensor of one value per row on the weight's device");
+      }
+      row_amax = reinterpret_cast<float *>(raw_ptr(am));
+      cuda_check(cudaMemsetAsync(row_amax, 0, static_cast<size_t>(m) * sizeof(float), 0), "clearing the row maxima");
+    }
+    if (!want_amax && !no_skinny && m <= 4 &&
+        skinny_fp8_supported(m, rows, k, raw_ptr(a), raw_ptr(weight), raw_ptr(out), residual != nullptr)) {
       cuda_check(skinny_fp8_linear(raw_ptr(a), is_bf16, m, rows, k, raw_ptr(weight),
                                    reinterpret_cast<const float *>(raw_ptr(scales)), numel_of(scales) == 1 ? 1 : 0,
                                    bias ? raw_ptr(*bias) : nullptr, residual ? raw_ptr(*residual) : nullptr, act,
@@ -1445,10 +1459,118 @@ int32_t fl_fp8_linear(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_v
       ep.residual_ld = rows;
     }
     ep.act = act;
+    ep.row_amax = row_amax;
     run_gemm(kGemmE4M3, m, rows, k, codes, w_ptr, nullptr, nullptr, ep, is_bf16, raw_ptr(out));
     return clear_error();
   });
 }
+}  // namespace
+
+int32_t fl_fp8_linear(fl_tensor_view_t a, fl_tensor_view_t data, fl_tensor_view_t scales, fl_tensor_view_t bias,
+                      fl_tensor_view_t residual, int32_t act, fl_tensor_view_t out) {
+  return fp8_linear_impl(a, data, scales, bias, residual, act, out, nullptr, false);
+}
+
+int32_t fl_fp8_linear_amax(fl_tensor_view_t a, fl_tensor_view_t data, fl_tensor_view_t scales, fl_tensor_view_t bias,
+                           fl_tensor_view_t residual, int32_t act, fl_tensor_view_t out, fl_tensor_view_t row_amax) {
+  return fp8_linear_impl(a, data, scales, bias, residual, act, out, row_amax, true);
+}
+
+// The second half of a narrow gather: this rank's column block of a 16-bit matrix, quantised per
+// row with the rows' maxima over the whole matrix (fl_fp8_linear_amax's output after a maximum
+// over the ranks), written as e4m3 codes into the same columns of every rank's full-width matrix.
+int32_t fl_fp8_quantize_scatter(fl_tensor_view_t x_h, fl_tensor_view_t row_amax_h, const fl_tensor_view_t *dests,
+                                int32_t n_dest, int32_t col0, fl_tensor_view_t row_scales_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &x = deref(x_h);
+    const fl_tensor_view_impl_t &am = deref(row_amax_h);
+    if (!is_half_type(dtype_of(x)) || x.shape.size() < 2 || !is_contiguous(x) || device_of(x) != FL_DEVICE_CUDA) {
+      invalid("x is not a contiguous <float16> or <bfloat16> tensor of at least two dimensions on cuda");
+    }
+    const int64_t m64 = leading_rows(x);
+    const int k = x.shape.back();
+    if (dtype_of(am) != FL_DTYPE_FLOAT || numel_of(am) != m64 || !is_contiguous(am) || device_of(am) != FL_DEVICE_CUDA) {
+      invalid("row_amax is not a contiguous <float> tensor of one value per row of x on cuda");
+    }
+    if (!dests || n_dest < 1 || n_dest > kMaxGemmOutputs) {
+      invalid("scatter: between 1 and " + std::to_string(kMaxGemmOutputs) + " destinations are needed");
+    }
+    const fl_tensor_view_impl_t &first = deref(dests[0]);
+    if (first.shape.size() != x.shape.size()) invalid("scatter: a destination has not x's rank");
+    const int64_t ld = first.shape.back();
+    if (col0 < 0 || col0 + static_cast<int64_t>(k) > ld) invalid("scatter: the column block does not fit the destination");
+    if (k % 16 != 0 || ld % 16 != 0 || col0 % 16 != 0) invalid("scatter: x's width, the destination's width and the column offset are multiples of 16");
+    uint8_t *ptrs[kMaxGemmOutputs];
+    for (int i = 0; i < n_dest; ++i) {
+      const fl_tensor_view_impl_t &d = deref(dests[i]);
+      if (device_of(d) != FL_DEVICE_CUDA || dtype_of(d) != FL_DTYPE_FP8E4M3 || !is_contiguous(d) || d.shape != first.shape) {
+        invalid("scatter: the destinations are not contiguous <fp8e4m3> matrices of one shape on cuda");
+      }
+      for (size_t j = 0; j + 1 < x.shape.size(); ++j) {
+        if (d.shape[j] != x.shape[j]) invalid("scatter: a destination has not x's leading dimensions");
+      }
+      if (!aligned16(raw_ptr(d))) invalid("scatter: a destination's first element is not 16-byte aligned");
+      ptrs[i] = raw_ptr(d);
+    }
+    if (!aligned16(raw_ptr(x))) invalid("scatter: x's first element is not 16-byte aligned");
+    float *scales_out = nullptr;
+    if (row_scales_h) {
+      const fl_tensor_view_impl_t &rs = deref(row_scales_h);
+      if (dtype_of(rs) != FL_DTYPE_FLOAT || numel_of(rs) != m64 || !is_contiguous(rs) || device_of(rs) != FL_DEVICE_CUDA) {
+        invalid("row_scales is not a contiguous <float> tensor of one value per row of x on cuda");
+      }
+      scales_out = reinterpret_cast<float *>(raw_ptr(rs));
+    }
+    require_kernels();
+    check_earlier_kernel_status();
+    if (m64 == 0) return clear_error();
+    if (m64 > INT32_MAX) invalid("x has more rows than the kernel can index");
+    cuda_check(quantize_fp8_scatter(raw_ptr(x), dtype_of(x) == FL_DTYPE_BFLOAT16, static_cast<int>(m64), k,
+                                    reinterpret_cast<const float *>(raw_ptr(am)), ptrs, n_dest, ld, col0, scales_out, 0),
+               "quantising and scattering");
+    return clear_error();
+  });
+}
+
+namespace {
+
+// The destinations of a scattering epilogue: contiguous (..., ld) matrices of one shape with the left
+// operand's leading dimensions, of the product's type, on the device; the product lands in columns
+// [col0, col0 + rows) of each.
+struct ScatterDests {
+  void *first = nullptr;
+  void *extra[kMaxGemmOutputs] = {};
+  int num_extra = 0;
+  int64_t ld = 0;
+};
+
+ScatterDests check_scatter_dests(const fl_tensor_view_t *dests, int32_t n_dest, int32_t col0, int rows,
+                                 const std::vector<int32_t> &left_shape, fl_dtype_t dtype, fl_device_type_t device) {
+  if (!dests || n_dest < 1 || n_dest > kMaxGemmOutputs) {
+    invalid("scatter: between 1 and " + std::to_string(kMaxGemmOutputs) + " destinations are needed");
+  }
+  const fl_tensor_view_impl_t &first = deref(dests[0]);
+  if (first.shape.size() != left_shape.size()) invalid("scatter: a destination has not the left operand's rank");
+  ScatterDests out;
+  out.ld = first.shape.back();
+  if (col0 < 0 || col0 + static_cast<int64_t>(rows) > out.ld) invalid("scatter: the column block does not fit the destination");
+  if (out.ld % 8 != 0 || col0 % 8 != 0) invalid("scatter: the destination's width and the column offset are multiples of 8");
+  for (int i = 0; i < n_dest; ++i) {
+    const fl_tensor_view_impl_t &d = deref(dests[i]);
+    if (device_of(d) != device || dtype_of(d) != dtype || !is_contiguous(d) || d.shape != first.shape) {
+      invalid("scatter: the destinations are not contiguous matrices of one shape, of the product's type, on the device");
+    }
+    for (size_t j = 0; j + 1 < left_shape.size(); ++j) {
+      if (d.shape[j] != left_shape[j]) invalid("scatter: a destination has not the left operand's leading dimensions");
+    }
+    if (!aligned16(raw_ptr(d))) invalid("scatter: a destination's first element is not 16-byte aligned");
+    if (i == 0) out.first = raw_ptr(d);
+    else out.extra[out.num_extra++] = raw_ptr(d);
+  }
+  return out;
+}
+
+}  // namespace
 
 int32_t fl_fp8_linear_scatter(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_view_t scales_h,
                               fl_tensor_view_t bias_h, fl_tensor_view_t residual_h, int32_t act,
@@ -1464,26 +1586,7 @@ int32_t fl_fp8_linear_scatter(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_
     check_activation(a, device, "the left operand");
     if (a.shape.back() != k) invalid("the two operands disagree about k");
     if (act != FL_ACT_NONE && act != FL_ACT_GELU_TANH) invalid("unknown activation");
-    if (!dests || n_dest < 1 || n_dest > kMaxGemmOutputs) {
-      invalid("scatter: between 1 and " + std::to_string(kMaxGemmOutputs) + " destinations are needed");
-    }
-    // Every destination is a contiguous (..., ld) matrix with the left operand's leading
-    // dimensions, of its type, on the device; the product lands in columns [col0, col0 + rows).
-    const fl_tensor_view_impl_t &first = deref(dests[0]);
-    if (first.shape.size() != a.shape.size()) invalid("scatter: a destination has not the left operand's rank");
-    const int64_t ld = first.shape.back();
-    if (col0 < 0 || col0 + static_cast<int64_t>(rows) > ld) invalid("scatter: the column block does not fit the destination");
-    if (ld % 8 != 0 || col0 % 8 != 0) invalid("scatter: the destination's width and the column offset are multiples of 8");
-    for (int i = 0; i < n_dest; ++i) {
-      const fl_tensor_view_impl_t &d = deref(dests[i]);
-      if (device_of(d) != device || dtype_of(d) != dtype_of(a) || !is_contiguous(d) || d.shape != first.shape) {
-        invalid("scatter: the destinations are not contiguous matrices of one shape, of the left operand's type, on the device");
-      }
-      for (size_t j = 0; j + 1 < a.shape.size(); ++j) {
-        if (d.shape[j] != a.shape[j]) invalid("scatter: a destination has not the left operand's leading dimensions");
-      }
-      if (!aligned16(raw_ptr(d))) invalid("scatter: a destination's first element is not 16-byte aligned");
-    }
+    const ScatterDests sd = check_scatter_dests(dests, n_dest, col0, rows, a.shape, dtype_of(a), device);
     const fl_tensor_view_impl_t *bias = bias_h ? &deref(bias_h) : nullptr;
     const fl_tensor_view_impl_t *residual = residual_h ? &deref(residual_h) : nullptr;
     if (bias) {
@@ -1537,10 +1640,10 @@ int32_t fl_fp8_linear_scatter(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_
       ep.residual_ld = rows;
     }
     ep.act = act;
-    ep.out_ld = ld;
+    ep.out_ld = sd.ld;
     ep.out_col0 = col0;
-    for (int i = 1; i < n_dest; ++i) ep.extra_out[ep.num_extra_out++] = raw_ptr(deref(dests[i]));
-    run_gemm(kGemmE4M3, m, rows, k, codes, w_ptr, nullptr, nullptr, ep, is_bf16, raw_ptr(first));
+    for (int i = 0; i < sd.num_extra; ++i) ep.extra_out[ep.num_extra_out++] = sd.extra[i];
+    run_gemm(kGemmE4M3, m, rows, k, codes, w_ptr, nullptr, nullptr, ep, is_bf16, sd.first);
     return clear_error();
   });
 }
@@ -1778,9 +1881,13 @@ int32_t fl_fp8_layernorm_quantize(fl_tensor_view_t x_h, fl_tensor_view_t scale_h
   });
 }
 
-int32_t fl_fp8_linear_quantized(fl_tensor_view_t codes_h, fl_tensor_view_t row_scales_h, fl_tensor_view_t data_h,
-                                fl_tensor_view_t scales_h, fl_tensor_view_t bias_h, fl_tensor_view_t residual_h,
-                                int32_t act, fl_tensor_view_t out_h) {
+namespace {
+
+// fl_fp8_linear_quantized (out_h) and fl_fp8_linear_quantized_scatter (dests): one of the two is given.
+int32_t fp8_linear_quantized_impl(fl_tensor_view_t codes_h, fl_tensor_view_t row_scales_h, fl_tensor_view_t data_h,
+                                  fl_tensor_view_t scales_h, fl_tensor_view_t bias_h, fl_tensor_view_t residual_h,
+                                  int32_t act, fl_tensor_view_t out_h, const fl_tensor_view_t *dests, int32_t n_dest,
+                                  int32_t col0) {
   return guard([&]() -> int32_t {
     const fl_tensor_view_impl_t &weight = deref(data_h);
     const fl_tensor_view_impl_t &scales = deref(scales_h);
@@ -1799,29 +1906,38 @@ int32_t fl_fp8_linear_quantized(fl_tensor_view_t codes_h, fl_tensor_view_t row_s
         device_of(row_scales) != device) {
       invalid("row_scales is not a contiguous <float> tensor of one value per row on the weight's device");
     }
-    const fl_tensor_view_impl_t &out = deref(out_h);
-    if (!is_half_type(dtype_of(out)) || device_of(out) != device || !is_contiguous(out)) {
-      invalid("out is not a contiguous <float16> or <bfloat16> tensor on the weight's device");
-    }
-    {
-      std::vector<int32_t> want(a.shape.begin(), a.shape.end());
-      want.back() = rows;
-      check_shape(out, want, "out");
+    std::vector<int32_t> out_shape(a.shape.begin(), a.shape.end());
+    out_shape.back() = rows;
+    ScatterDests sd;
+    fl_dtype_t out_dtype;
+    if (out_h) {
+      const fl_tensor_view_impl_t &out = deref(out_h);
+      if (!is_half_type(dtype_of(out)) || device_of(out) != device || !is_contiguous(out)) {
+        invalid("out is not a contiguous <float16> or <bfloat16> tensor on the weight's device");
+      }
+      check_shape(out, out_shape, "out");
+      out_dtype = dtype_of(out);
+      sd.first = raw_ptr(out);
+    } else {
+      if (!dests || n_dest < 1) invalid("scatter: between 1 and " + std::to_string(kMaxGemmOutputs) + " destinations are needed");
+      out_dtype = dtype_of(deref(dests[0]));
+      if (!is_half_type(out_dtype)) invalid("scatter: the destinations are not <float16> or <bfloat16>");
+      sd = check_scatter_dests(dests, n_dest, col0, rows, a.shape, out_dtype, device);
     }
     if (act != FL_ACT_NONE && act != FL_ACT_GELU_TANH) invalid("unknown activation");
     const fl_tensor_view_impl_t *bias = bias_h ? &deref(bias_h) : nullptr;
     const fl_tensor_view_impl_t *residual = residual_h ? &deref(residual_h) : nullptr;
     if (bias) {
-      if (device_of(*bias) != device || dtype_of(*bias) != dtype_of(out) || numel_of(*bias) != rows ||
+      if (device_of(*bias) != device || dtype_of(*bias) != out_dtype || numel_of(*bias) != rows ||
           !is_contiguous(*bias)) {
         invalid("the bias is not a contiguous (rows) vector of out's type on the weight's device");
       }
     }
     if (residual) {
-      if (device_of(*residual) != device || dtype_of(*residual) != dtype_of(out) || !is_contiguous(*residual)) {
+      if (device_of(*residual) != device || dtype_of(*residual) != out_dtype || !is_contiguous(*residual)) {
         invalid("the residual is not contiguous, of out's type, on the weight's device");
       }
-      check_shape(*residual, out.shape, "the residual");
+      check_shape(*residual, out_shape, "the residual");
     }
     if (device != FL_DEVICE_CUDA) invalid("the fp8 operand is on a device with no FP8 kernels");
     check_tiles(rows, k, 16);
@@ -1864,9 +1980,29 @@ int32_t fl_fp8_linear_quantized(fl_tensor_view_t codes_h, fl_tensor_view_t row_s
       ep.residual_ld = rows;
     }
     ep.act = act;
-    run_gemm(kGemmE4M3, m, rows, k, a_ptr, w_ptr, nullptr, nullptr, ep, dtype_of(out) == FL_DTYPE_BFLOAT16, raw_ptr(out));
+    if (!out_h) {
+      ep.out_ld = sd.ld;
+      ep.out_col0 = col0;
+      for (int i = 0; i < sd.num_extra; ++i) ep.extra_out[ep.num_extra_out++] = sd.extra[i];
+    }
+    run_gemm(kGemmE4M3, m, rows, k, a_ptr, w_ptr, nullptr, nullptr, ep, out_dtype == FL_DTYPE_BFLOAT16, sd.first);
     return clear_error();
   });
+}
+
+}  // namespace
+
+int32_t fl_fp8_linear_quantized(fl_tensor_view_t codes_h, fl_tensor_view_t row_scales_h, fl_tensor_view_t data_h,
+                                fl_tensor_view_t scales_h, fl_tensor_view_t bias_h, fl_tensor_view_t residual_h,
+                                int32_t act, fl_tensor_view_t out_h) {
+  if (!out_h) return guard([&]() -> int32_t { invalid("out is null"); });
+  return fp8_linear_quantized_impl(codes_h, row_scales_h, data_h, scales_h, bias_h, residual_h, act, out_h, nullptr, 0, 0);
+}
+
+int32_t fl_fp8_linear_quantized_scatter(fl_tensor_view_t codes_h, fl_tensor_view_t row_scales_h, fl_tensor_view_t data_h,
+                                        fl_tensor_view_t scales_h, fl_tensor_view_t bias_h, fl_tensor_view_t residual_h,
+                                        int32_t act, const fl_tensor_view_t *dests, int32_t n_dest, int32_t col0) {
+  return fp8_linear_quantized_impl(codes_h, row_scales_h, data_h, scales_h, bias_h, residual_h, act, nullptr, dests, n_dest, col0);
 }
 
 int32_t fl_fp8_swiglu_quantize(fl_tensor_view_t x_h, fl_tensor_view_t codes_h, fl_tensor_view_t row_scales_h) {

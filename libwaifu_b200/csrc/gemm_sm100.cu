@@ -100,6 +100,7 @@ struct KernelParams {
   int residual_rows;
   long long residual_ld;
   int act;
+  float *row_amax;  // (m) or null: per-row maximum of the rounded results' magnitudes, by atomicMax on the float's bits
   int out_bf16;
   void *out[kMaxGemmOutputs];  // destinations of every tile: one, or this GPU's and its peers' copies
   int num_out;
@@ -789,6 +790,18 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       chunks = chunks < 0 ? 0 : (chunks > HALF_CHUNKS ? HALF_CHUNKS : chunks);
       const uint32_t tacc = tmem_base + ((quarter * 32) << 16) + acc * BLOCK_N + half * HALF_N;
 
+      // The largest magnitude among a chunk's 32 rounded results of this lane's row, merged into the
+      // row's maximum in global memory. Magnitudes of one 16-bit format order like their bit
+      // patterns, and non-negative floats like theirs, so both maxima are integer ones.
+      auto note_row_amax = [&](const uint32_t (&packed)[16], int nc) {
+        uint32_t top = 0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (nc + 2 * j < p.n) top = max(top, max(packed[j] & 0x7fffu, (packed[j] >> 16) & 0x7fffu));
+        }
+        const float as_float = is_bf16 ? __uint_as_float(top << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(top)));
+        atomicMax(reinterpret_cast<unsigned int *>(p.row_amax) + row, __float_as_uint(as_float));
+      };
       // One 32-column chunk: scale, bias, activation, residual in fp32; one rounding; store.
       auto finish_chunk = [&](int c, uint32_t (&v)[32]) {
         const int nc = n0 + c * 32;
@@ -866,11 +879,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
             // (a lane's row is read by that lane only, so it may be overwritten without another barrier)
           }
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) packed[j] = pack16(x[2 * j], x[2 * j + 1], is_bf16);
+          if (p.row_amax != nullptr && row_ok) note_row_amax(packed, nc);
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             *reinterpret_cast<uint4 *>(obuf + own_row_off + ((g ^ own_swz) << 4)) =
-                make_uint4(pack16(x[8 * g], x[8 * g + 1], is_bf16), pack16(x[8 * g + 2], x[8 * g + 3], is_bf16),
-                           pack16(x[8 * g + 4], x[8 * g + 5], is_bf16), pack16(x[8 * g + 6], x[8 * g + 7], is_bf16));
+                make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
           }
           fence_proxy_async_smem();
           __syncwarp();
@@ -913,6 +929,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
         for (int j = 0; j < 16; ++j) packed[j] = pack16(x[2 * j], x[2 * j + 1], is_bf16);
         if (!row_ok) return;
+        if (p.row_amax != nullptr) note_row_amax(packed, nc);
         // (In the scatter form the peers' copies are made by the pusher warps from this one.)
         {
           uint16_t *out_row = reinterpret_cast<uint16_t *>(p.out[0]) + out_off;
@@ -1343,6 +1360,7 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
   kp.residual_rows = a.residual_rows > 0 ? a.residual_rows : a.m;
   kp.residual_ld = a.residual_ld;
   kp.act = a.act;
+  kp.row_amax = a.row_amax;
   kp.out_bf16 = a.out_bf16;
   kp.num_out = 0;
   kp.out[kp.num_out++] = a.out;

@@ -52,6 +52,9 @@ struct GemmArgs {
   int residual_rows;           // period of the residual's rows over m (m itself for a full one)
   int64_t residual_ld;
   int act;
+  // (m) or NULL: the epilogue takes the maximum of |result| over each row, of the values as rounded to
+  // the output type, into this array with atomicMax on the float's bits; the caller zeroes it.
+  float *row_amax;
   int out_bf16;                // 1 bf16, 0 fp16
   void *out;                   // (m, n), pitch n -- or, with out_ld != 0, columns [out_col0, out_col0 + n)
                                // of a row-major matrix of pitch out_ld

@@ -148,6 +148,36 @@ __global__ void __launch_bounds__(256) quantize_fp8_act_reg_kernel(const uint16_
   }
 }
 
+// Per-row e4m3 of x (m, k) with the rows' maxima given (taken over a wider row than x: x is one
+// rank's column block of a matrix split by output channel, `amax` the maximum over all ranks'
+// blocks), written into columns [col0, col0 + k) of up to eight (m, ld) matrices of codes: this
+// GPU's own and its peers'. The arithmetic is quantize_fp8_act's, so the gathered codes equal what
+// that kernel makes of the whole row. A CTA takes a row; a lane's 16 bytes of codes go out as one
+// store per destination, 512 contiguous bytes per warp, which is what NVLink wants.
+struct ScatterDests {
+  uint8_t *ptr[8];
+  int count;
+};
+
+__global__ void __launch_bounds__(128) quantize_fp8_scatter_kernel(const uint16_t *__restrict__ x, int is_bf16, int k,
+                                                                 const float *__restrict__ amax, ScatterDests dests,
+                                                                 long long ld, int col0, float *__restrict__ scales) {
+  griddep_wait();
+  const long long row = blockIdx.x;
+  const float scale = __fdiv_rn(amax[row], 448.0f);
+  const float inv = __frcp_rn(scale > 0.0f ? scale : 1.0f);
+  if (threadIdx.x == 0 && scales) scales[row] = scale;
+  const uint4 *xv = reinterpret_cast<const uint4 *>(x + row * k);
+  for (int v = threadIdx.x; v < k / 16; v += blockDim.x) {
+    const uint2 lo = e4m3x8_of(xv[2 * v], is_bf16, inv);
+    const uint2 hi = e4m3x8_of(xv[2 * v + 1], is_bf16, inv);
+    const uint4 codes = make_uint4(lo.x, lo.y, hi.x, hi.y);
+    const long long off = row * ld + col0 + static_cast<long long>(v) * 16;
+#pragma unroll 1
+    for (int d = 0; d < dests.count; ++d) *reinterpret_cast<uint4 *>(dests.ptr[d] + off) = codes;
+  }
+}
+
 // ---- layer norm -> modulate -> per-row e4m3, one pass ----------------------------------------
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -616,6 +646,21 @@ cudaError_t quantize_fp8_act(const void *x, int is_bf16, int m, int k, uint8_t *
   }
   ++g_helper_launches;
   return e;
+}
+
+cudaError_t quantize_fp8_scatter(const void *x, int is_bf16, int m, int k, const float *amax, uint8_t *const *dests,
+                                 int n_dest, int64_t ld, int col0, float *scales, cudaStream_t stream) {
+  if (n_dest < 1 || n_dest > 8 || k % 16 != 0 || ld % 16 != 0 || col0 % 16 != 0 || !aligned16(x)) return cudaErrorInvalidValue;
+  ScatterDests d = {};
+  d.count = n_dest;
+  for (int i = 0; i < n_dest; ++i) {
+    if (!aligned16(dests[i])) return cudaErrorInvalidValue;
+    d.ptr[i] = dests[i];
+  }
+  quantize_fp8_scatter_kernel<<<static_cast<unsigned>(m), 128, 0, stream>>>(static_cast<const uint16_t *>(x), is_bf16, k, amax, d,
+                                                                            ld, col0, scales);
+  ++g_helper_launches;
+  return cudaGetLastError();
 }
 
 cudaError_t ln_modulate_quantize_fp8(const void *x, int is_bf16, int m, int k, const void *scale, int64_t scale_pitch,

@@ -16,6 +16,13 @@ cudaError_t quantize_fp8_act(const void *x, int is_bf16, int m, int k, uint8_t *
 cudaError_t quantize_fp8_rows_f32(const float *w, int rows, int k, uint8_t *codes, float *scales,
                                   cudaStream_t stream);
 
+// quantize_fp8_act with the rows' maxima given instead of taken (`amax` (m): the maximum of |x| over
+// a row that may be wider than x), the codes written into columns [col0, col0 + k) of `n_dest`
+// (1..8) matrices of pitch `ld` bytes, and scales[r] = amax[r] / 448 (scales may be null). k, ld and
+// col0 multiples of 16, every base 16-byte aligned.
+cudaError_t quantize_fp8_scatter(const void *x, int is_bf16, int m, int k, const float *amax, uint8_t *const *dests,
+                                 int n_dest, int64_t ld, int col0, float *scales, cudaStream_t stream);
+
 // Layer norm over the last dimension (no affine; fp32 sums, mean = sum / k, variance =
 // sumsq / k - mean^2, eps inside the root: flint/cpu/normalizations.cc:98-140), then the adaLN modulation
 // h = round16(n * scale + n [+ shift]) with `scale`/`shift` (groups, k) 16-bit or null, a group's

@@ -117,6 +117,10 @@ def lib() -> ctypes.CDLL:
     L.fl_fp8_linear_static.restype = c_int32
     L.fl_fp8_linear_scatter.argtypes = [V, V, V, V, V, c_int32, POINTER(V), c_int32, c_int32]
     L.fl_fp8_linear_scatter.restype = c_int32
+    L.fl_fp8_linear_amax.argtypes = [V, V, V, V, V, c_int32, V, V]; L.fl_fp8_linear_amax.restype = c_int32
+    L.fl_fp8_quantize_scatter.argtypes = [V, V, POINTER(V), c_int32, c_int32, V]; L.fl_fp8_quantize_scatter.restype = c_int32
+    L.fl_fp8_linear_quantized_scatter.argtypes = [V, V, V, V, V, V, c_int32, POINTER(V), c_int32, c_int32]
+    L.fl_fp8_linear_quantized_scatter.restype = c_int32
     L.fl_sm100_ipc_export.argtypes = [V, V]; L.fl_sm100_ipc_export.restype = c_int32
     L.fl_sm100_ipc_import.argtypes = [V, c_int32, c_int64, POINTER(V)]; L.fl_sm100_ipc_import.restype = c_int32
     L.fl_quantize_fp8_rows.argtypes = [V, V, V]
@@ -513,6 +517,35 @@ def fp8_linear_scatter(a: Tensor, weight: Tensor, scales: Tensor, dests: Sequenc
     arr = (c_void_p * len(dests))(*[d.raw() for d in dests])
     check(lib().fl_fp8_linear_scatter(a.raw(), weight.raw(), scales.raw(), bias.raw() if bias else None,
                                       residual.raw() if residual else None, int(act), arr, len(dests), int(col0)))
+
+
+def fp8_linear_amax(a: Tensor, weight: Tensor, scales: Tensor, row_amax: Tensor, bias: Optional[Tensor] = None,
+                    residual: Optional[Tensor] = None, act: int = ACT_NONE, out: Optional[Tensor] = None) -> Tensor:
+    """fp8_linear that also leaves each output row's largest magnitude (as rounded) in `row_amax`."""
+    if out is None:
+        out = _fp8_result(a, weight.shape[0])
+    check(lib().fl_fp8_linear_amax(a.raw(), weight.raw(), scales.raw(), bias.raw() if bias else None,
+                                   residual.raw() if residual else None, int(act), out.raw(), row_amax.raw()))
+    return out
+
+
+def fp8_quantize_scatter(x: Tensor, row_amax: Tensor, dests: Sequence[Tensor], col0: int,
+                         row_scales: Optional[Tensor] = None) -> None:
+    """Per-row e4m3 of `x` with the rows' maxima given, the codes written into columns
+    [col0, col0 + k) of every matrix in `dests` (this GPU's and its peers')."""
+    arr = (c_void_p * len(dests))(*[d.raw() for d in dests])
+    check(lib().fl_fp8_quantize_scatter(x.raw(), row_amax.raw(), arr, len(dests), int(col0),
+                                        row_scales.raw() if row_scales else None))
+
+
+def fp8_linear_quantized_scatter(codes: Tensor, row_scales: Tensor, weight: Tensor, scales: Tensor, dests: Sequence[Tensor],
+                                 col0: int, bias: Optional[Tensor] = None, residual: Optional[Tensor] = None,
+                                 act: int = ACT_NONE) -> None:
+    """fp8_linear_quantized whose result lands in columns [col0, col0 + rows) of every matrix in `dests`."""
+    arr = (c_void_p * len(dests))(*[d.raw() for d in dests])
+    check(lib().fl_fp8_linear_quantized_scatter(codes.raw(), row_scales.raw(), weight.raw(), scales.raw(),
+                                                bias.raw() if bias else None, residual.raw() if residual else None,
+                                                int(act), arr, len(dests), int(col0)))
 
 
 def ipc_export(t: Tensor) -> bytes:

@@ -107,6 +107,46 @@ class ColumnSplitLinear:
         return all_gather_columns(self.dist, local, self.sizes, out)
 
 
+class NarrowGatherMlp:
+    """An MLP split by output channel whose hidden activation crosses the links as e4m3 codes.
+
+    The up projection's result H is only ever read by the down projection's activation quantiser,
+    which turns a row of H into e4m3 codes and one scale, the row's largest magnitude over ALL its
+    columns divided by 448. Gathering H in 16 bits and quantising afterwards moves twice the bytes
+    it has to. Here every rank
+      1. computes its column block of H and the largest magnitude of each row over that block
+         (``up``: fl_fp8_linear_amax),
+      2. takes the maximum of those over the ranks (one all-reduce of m floats),
+      3. quantises its block with the whole row's scale and writes the codes into every rank's
+         full-width matrix of codes (``scatter_codes``: fl_fp8_quantize_scatter over peer-mapped
+         storage; the CPU tests all-gather instead),
+      4. multiplies the gathered codes by its slice of the down weight (``down``:
+         fl_fp8_linear_quantized, whose epilogue writes Y into every rank's matrix in the scatter
+         form, or whose slices are all-gathered).
+    The codes and scales equal what the unsplit chain's quantiser makes of the whole row, and a
+    linear's output channels are independent, so the result equals the unsplit MLP's bit for bit.
+
+    `ops` supplies the four callables; `dist` the collective for step 2."""
+
+    def __init__(self, dist, n_up: int, n_down: int, multiple: int = 128):
+        self.dist = dist
+        self.world = dist.get_world_size()
+        self.rank = dist.get_rank()
+        self.up_range = column_shard(n_up, self.world, self.rank, multiple)
+        self.down_range = column_shard(n_down, self.world, self.rank, multiple)
+        self.up_sizes = column_sizes(n_up, self.world, multiple)
+        self.down_sizes = column_sizes(n_down, self.world, multiple)
+
+    def step(self, x, up, scatter_codes, down):
+        """`up(x) -> (h_block, row_amax tensor)`; `scatter_codes(h_block, row_amax, col0) -> (codes, scales)`
+        (the full-width codes as this rank will read them, and the rows' scales);
+        `down(codes, scales, col0) -> y`. Returns what `down` returns."""
+        h_block, amax = up(x)
+        self.dist.all_reduce(amax, op=self.dist.ReduceOp.MAX)
+        codes, scales = scatter_codes(h_block, amax, self.up_range[0])
+        return down(codes, scales, self.down_range[0])
+
+
 def gather_rows(dist, local, sizes: Sequence[int]):
     """Concatenates row shards (used to hand a whole batch back to one caller)."""
     import torch

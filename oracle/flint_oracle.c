@@ -186,6 +186,23 @@ void fo_quantize_fp8_act(const uint16_t *x, int is_bf16, int rows, int k, uint8_
   }
 }
 
+void fo_quantize_fp8_act_amax(const uint16_t *x, int is_bf16, int rows, int k, const float *amax,
+                              uint8_t *codes, float *scales) {
+  /* fo_quantize_fp8_act with the rows' maxima given (taken over a wider row than x). */
+  int r;
+#pragma omp parallel for schedule(static)
+  for (r = 0; r < rows; ++r) {
+    const uint16_t *row = x + (int64_t)r * k;
+    uint8_t *out = codes + (int64_t)r * k;
+    float s = amax[r] / 448.0f, divisor, inv;
+    int j;
+    divisor = s > 0.0f ? s : 1.0f;
+    inv = 1.0f / divisor;
+    for (j = 0; j < k; ++j) out[j] = fo_e4m3_encode(widen16(row[j], is_bf16) * inv);
+    scales[r] = s;
+  }
+}
+
 static void nvfp4_block(const float *v, float global, uint8_t *codes8, uint8_t *scale_code) {
   /* 16 values -> 8 bytes of e2m1 pairs + one unsigned e4m3 block scale. */
   float amax = 0.0f, sdec, denom, inv;

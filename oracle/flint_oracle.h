@@ -49,6 +49,10 @@ void fo_quantize_fp8_rows(const float *w, int rows, int k, uint8_t *codes, float
  * taken once per row in IEEE fp32; zero row -> scale 0, codes 0. */
 void fo_quantize_fp8_act(const uint16_t *x, int is_bf16, int rows, int k, uint8_t *codes,
                          float *scales);
+/* The same with the rows' maxima given: one rank's column block of a row whose maximum was taken
+ * over all ranks' blocks. codes (rows, k), scales[r] = amax[r] / 448. */
+void fo_quantize_fp8_act_amax(const uint16_t *x, int is_bf16, int rows, int k, const float *amax,
+                              uint8_t *codes, float *scales);
 /* NVFP4 weight: g = amax/(448*6); per 16 consecutive k: s = e4m3(amax_b/(6 g)) (unsigned),
  * code = e2m1(w * (1/(decode(s) g))), the reciprocal taken once per block in IEEE fp32; zero
  * block -> s = 0, codes 0. codes: two per byte, low nibble

@@ -65,6 +65,7 @@ def lib() -> ctypes.CDLL:
         L.fo_quantize_fp8_tensor.argtypes = [f32p, c_int64, u8p, f32p]
         L.fo_quantize_fp8_rows.argtypes = [f32p, c_int, c_int, u8p, f32p]
         L.fo_quantize_fp8_act.argtypes = [u16p, c_int, c_int, c_int, u8p, f32p]
+        L.fo_quantize_fp8_act_amax.argtypes = [u16p, c_int, c_int, c_int, f32p, u8p, f32p]
         L.fo_quantize_nvfp4_weight.argtypes = [f32p, c_int, c_int, u8p, u8p, f32p]
         L.fo_quantize_nvfp4_act.argtypes = [u16p, c_int, c_int, c_int, u8p, u8p]
         L.fo_decode_e4m3.argtypes = [u8p, c_int64, f32p]
@@ -157,6 +158,24 @@ def quantize_fp8_act(x16: np.ndarray, is_bf16: bool):
     scales = np.zeros(rows, dtype=np.float32)
     lib().fo_quantize_fp8_act(_p(x16, c_uint16), int(is_bf16), rows, k, _p(codes, c_uint8), _p(scales, c_float))
     return codes, scales
+
+
+def quantize_fp8_act_amax(x16: np.ndarray, amax: np.ndarray, is_bf16: bool):
+    """quantize_fp8_act with the rows' maxima given (a column block of rows whose maxima were taken
+    over the whole row): (codes, scales = amax / 448)."""
+    x16 = np.ascontiguousarray(x16, dtype=np.uint16)
+    amax = np.ascontiguousarray(amax, dtype=np.float32)
+    rows, k = x16.shape
+    codes = np.empty((rows, k), dtype=np.uint8)
+    scales = np.zeros(rows, dtype=np.float32)
+    lib().fo_quantize_fp8_act_amax(_p(x16, c_uint16), int(is_bf16), rows, k, _p(amax, c_float), _p(codes, c_uint8),
+                                   _p(scales, c_float))
+    return codes, scales
+
+
+def row_amax(x16: np.ndarray, is_bf16: bool) -> np.ndarray:
+    """The largest magnitude of each row of a 16-bit matrix, as float32."""
+    return np.abs(widen(np.ascontiguousarray(x16, dtype=np.uint16), is_bf16)).max(axis=-1).astype(np.float32)
 
 
 def quantize_nvfp4_weight(w: np.ndarray):
@@ -532,6 +551,14 @@ def fp8_linear(x16, codes, scales, bias=None, residual=None, act=ACT_NONE, is_bf
     res = None if residual is None else np.asarray(residual, dtype=np.uint16).reshape(m, n)
     out = epilogue(acc, xs, scales, 1.0, bias, res, act, is_bf16)
     return out.reshape(lead + (n,))
+
+
+def fp8_linear_quantized(xc, xs, codes, scales, bias=None, residual=None, act=ACT_NONE, is_bf16=True, engine="auto"):
+    """fp8_linear for an activation that is e4m3 codes (m, k) with per-row scales (m) already."""
+    acc = gemm_f32_nt(decode_e4m3(np.ascontiguousarray(xc, dtype=np.uint8)), decode_e4m3(codes), engine)
+    m, n = acc.shape
+    res = None if residual is None else np.asarray(residual, dtype=np.uint16).reshape(m, n)
+    return epilogue(acc, np.asarray(xs, dtype=np.float32), scales, 1.0, bias, res, act, is_bf16)
 
 
 def nvfp4_linear(x16, codes, block_scales, global_scale, bias=None, residual=None, act=ACT_NONE,

@@ -101,3 +101,146 @@ def test_fused_all_gather_across_gpus(flint, oracle):
     finally:
         os.environ.clear()
         os.environ.update(env)
+
+
+def _narrow_worker(rank, world, port):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch
+    import torch.distributed as dist
+    from libwaifu_b200 import flint as F
+    from libwaifu_b200 import sharding
+    from oracle import oracle as O
+    torch.cuda.set_device(rank)
+    F.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        rng = np.random.default_rng(6)  # the same on every rank
+        m, d, n_up = 520, 256, 512
+        x = O.narrow(rng.standard_normal((m, d)).astype(np.float32), True)
+        up_c, up_s = O.quantize_fp8_rows((rng.standard_normal((n_up, d)) * 0.02).astype(np.float32))
+        dn_c, dn_s = O.quantize_fp8_rows((rng.standard_normal((d, n_up)) * 0.02).astype(np.float32))
+        bf, f8, fl = F.DType.BFLOAT16, F.DType.FP8E4M3, F.DType.FLOAT
+        dev = lambda a, dt: F.Tensor.from_numpy(a, dt, F.Device.CUDA)
+        mlp = sharding.NarrowGatherMlp(dist, n_up, d, multiple=128)
+        (ua, ub), (da, db) = mlp.up_range, mlp.down_range
+        # the full-width matrix of codes every rank writes its block into: storage of its own
+        # allocation (2 MiB or more), the only kind another process can map
+        big_rows = 4104
+        codes_block = F.Tensor.empty((big_rows, n_up), f8, hint=F.AllocHint.WEIGHT)
+        y_block = F.Tensor.empty((big_rows, d), bf, hint=F.AllocHint.WEIGHT)
+        handles = [None] * world
+        dist.all_gather_object(handles, (F.ipc_export(codes_block), F.ipc_export(y_block)))
+        peers = [(F.ipc_import(handles[r][0], (big_rows, n_up), f8), F.ipc_import(handles[r][1], (big_rows, d), bf))
+                 for r in range(world) if r != rank]
+        codes_own = codes_block.view_as((m, n_up), (n_up, 1))
+        y_own = y_block.view_as((m, d), (d, 1))
+        codes_dests = [codes_own] + [p[0].view_as((m, n_up), (n_up, 1)) for p in peers]
+        y_dests = [y_own] + [p[1].view_as((m, d), (d, 1)) for p in peers]
+        xd = dev(x, bf)
+        w_up, s_up = dev(up_c[ua:ub], f8), dev(up_s[ua:ub], fl)
+        w_dn, s_dn = dev(dn_c[da:db], f8), dev(dn_s[da:db], fl)
+        x_cols = dev(np.ascontiguousarray(x[:, da:db]), bf)
+        amax_t = torch.zeros(m, device="cuda", dtype=torch.float32)
+        amax = F.Tensor.from_device_ptr(amax_t.data_ptr(), (m,), fl, keepalive=amax_t)
+        scales = F.Tensor.empty((m,), fl)
+        flag = torch.zeros(1, device="cuda")
+
+        def up_op(_):
+            h_block = F.fp8_linear_amax(xd, w_up, s_up, amax, None, None, F.ACT_GELU_TANH)
+            F.synchronize()  # the library's stream, then the collective's
+            return h_block, amax_t
+
+        def scatter_op(h_block, amax_tensor, col0):
+            F.fp8_quantize_scatter(h_block, amax, codes_dests, col0, scales)
+            F.synchronize()
+            dist.all_reduce(flag)  # every rank's block of codes has landed once this has completed
+            torch.cuda.synchronize()
+            return codes_own, scales
+
+        def down_op(codes, row_scales, col0):
+            F.fp8_linear_quantized_scatter(codes, row_scales, w_dn, s_dn, y_dests, col0, None, x_cols, F.ACT_NONE)
+            F.synchronize()
+            dist.all_reduce(flag)
+            torch.cuda.synchronize()
+            return y_own
+
+        mlp.step(xd, up_op, scatter_op, down_op)
+        F.synchronize()
+        got_codes = codes_own.numpy()
+        h_ref = O.fp8_linear(x, up_c, up_s, None, None, O.ACT_GELU_TANH)
+        want_codes, want_scales = O.quantize_fp8_act(h_ref, True)
+        # H is the GPU's and may differ from the oracle's in a last place here and there, which moves
+        # a code or, where it is the row's largest value, a scale: nearly all agree
+        same_scales = float(np.mean(scales.numpy().view(np.uint32) == want_scales.view(np.uint32)))
+        same = float(np.mean(got_codes == want_codes))
+        assert same_scales >= 0.9 and same >= 0.9, f"rank {rank}: {same_scales:.3f} of the scales, {same:.4f} of the codes equal the oracle's"
+        y_ref = O.fp8_linear(h_ref, dn_c, dn_s, None, x, O.ACT_NONE)
+        got_y = y_own.numpy()
+        check_parity_local(O, got_y, y_ref, f"rank {rank}: the whole MLP, codes gathered and Y scattered")
+        # the gathered codes and scales are the same bytes on every rank
+        digest = torch.tensor([float(got_codes.astype(np.uint64).sum()), float(scales.numpy().astype(np.float64).sum()),
+                               float(got_y.astype(np.uint64).sum())],
+                              device="cuda", dtype=torch.float64)
+        both = [torch.zeros_like(digest) for _ in range(world)]
+        dist.all_gather(both, digest)
+        assert all(torch.equal(b, both[0]) for b in both), "the ranks hold different codes, scales or results"
+        dist.barrier()
+        del codes_dests, y_dests, peers
+    finally:
+        dist.destroy_process_group()
+
+
+def check_parity_local(O, got16, want16, what):
+    from helpers import check_parity as check
+    check(O, got16, want16, True, what=what)
+
+
+def test_narrow_gather_across_gpus(flint, oracle):
+    """The hidden activation of a column-split MLP gathered as e4m3 codes over peer-mapped storage
+    (fl_fp8_linear_amax, a maximum over the ranks, fl_fp8_quantize_scatter), on two GPUs."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs on one box")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    try:
+        mp.spawn(_narrow_worker, args=(2, port), nprocs=2, join=True)
+    finally:
+        os.environ.clear()
+        os.environ.update(env)
+
+
+def test_row_maxima_and_quantise_scatter_on_one_gpu(flint, oracle):
+    """fl_fp8_linear_amax leaves the rows' largest rounded magnitudes; fl_fp8_quantize_scatter with
+    those maxima writes, block by block, exactly the codes and scales fl_quantize_fp8_activation makes
+    of the whole matrix."""
+    F = flint
+    rng = np.random.default_rng(72)
+    m, n, k = 300, 384, 192
+    x = oracle.narrow(randn(rng, (m, k)), True)
+    codes, scales = oracle.quantize_fp8_rows(randn(rng, (n, k), 0.02))
+    bias = oracle.narrow(randn(rng, (n,), 0.01), True)
+    bf, f8, fl = F.DType.BFLOAT16, F.DType.FP8E4M3, F.DType.FLOAT
+    amax = F.Tensor.empty((m,), fl)
+    h = F.fp8_linear_amax(dev(F, x, bf), dev(F, codes, f8), dev(F, scales, fl), amax, dev(F, bias, bf), None, F.ACT_GELU_TANH)
+    h_np = h.numpy()
+    assert np.array_equal(amax.numpy(), oracle.row_amax(h_np, True))
+    check_parity(oracle, h_np, oracle.fp8_linear(x, codes, scales, bias, None, oracle.ACT_GELU_TANH), True, what="with row maxima")
+    # two column blocks of h scattered into two full-width matrices of codes
+    d0 = dev(F, np.full((m, n), 0x7F, np.uint8), f8)
+    d1 = dev(F, np.full((m, n), 0x7F, np.uint8), f8)
+    row_scales = F.Tensor.empty((m,), fl)
+    for (a, b) in [(0, 256), (256, 384)]:
+        block = dev(F, np.ascontiguousarray(h_np[:, a:b]), bf)
+        F.fp8_quantize_scatter(block, amax, [d0, d1], a, row_scales)
+    want_codes, want_scales = oracle.quantize_fp8_act(h_np, True)
+    assert np.array_equal(d0.numpy(), want_codes) and np.array_equal(d1.numpy(), want_codes)
+    assert np.array_equal(row_scales.numpy().view(np.uint32), want_scales.view(np.uint32))
+    with pytest.raises(F.FlintError):
+        F.fp8_quantize_scatter(dev(F, np.ascontiguousarray(h_np[:, :256]), bf), amax, [d0], 136)   # does not fit / not a multiple of 16

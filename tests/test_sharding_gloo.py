@@ -66,6 +66,28 @@ def _worker(rank, world, port, ragged):
         xt = _as_t(x)
         y = down.forward(h, down.slice_of(dn_c), down.slice_of(dn_s), None, down.columns_of(xt).contiguous(), O.ACT_NONE)
         assert np.array_equal(_as_np(y), y_ref), "column-split down projection differs"
+
+        # ---- output channels with the hidden activation gathered as e4m3 codes
+        mlp = sharding.NarrowGatherMlp(dist, n_up, k, multiple=8)
+        assert (mlp.up_range, mlp.down_range) == ((up.start, up.stop), (down.start, down.stop))
+
+        def up_op(x16):
+            a0, b0 = mlp.up_range
+            h_block = O.fp8_linear(x16, up_c[a0:b0], up_s[a0:b0], bias[a0:b0], None, O.ACT_GELU_TANH)
+            return h_block, torch.from_numpy(O.row_amax(h_block, True).copy())
+
+        def scatter_op(h_block, amax_t, col0):
+            codes_block, scales = O.quantize_fp8_act_amax(h_block, amax_t.numpy(), True)
+            gathered = sharding.all_gather_columns(dist, torch.from_numpy(codes_block.astype(np.int32)), mlp.up_sizes)
+            return gathered.numpy().astype(np.uint8), scales
+
+        def down_op(codes, scales, col0):
+            a0, b0 = mlp.down_range
+            y_block = O.fp8_linear_quantized(codes, scales, dn_c[a0:b0], dn_s[a0:b0], None, x[:, a0:b0], O.ACT_NONE)
+            return _as_np(sharding.all_gather_columns(dist, _as_t(y_block), mlp.down_sizes))
+
+        y_narrow = mlp.step(x, up_op, scatter_op, down_op)
+        assert np.array_equal(y_narrow, y_ref), "the MLP with e4m3-gathered hidden activation differs from the unsharded one"
     finally:
         dist.destroy_process_group()
 
