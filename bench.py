@@ -361,7 +361,7 @@ def run_ours(args, wl):
         operand_sets.append((wrap(x, bf), layers, bias))
     outs = [F.Tensor.empty((m, n), bf) for (n, _) in wl["gemms"]]
 
-    nsplit = args.parallel in ("nsplit", "nsplit_push", "nsplit_fp8")
+    nsplit = args.parallel in ("nsplit", "nsplit_push", "nsplit_fp8", "nsplit_fp8_nccl")
 
     def build_split(mode):
         """Strong scaling of one MLP: every rank holds a slice of each weight's output channels and
@@ -369,11 +369,14 @@ def run_ours(args, wl):
           nsplit       NCCL all-gathers of the 16-bit slices;
           nsplit_push  the GEMMs' epilogues write their column blocks into every rank's full-width H
                        and Y over NVLink (peer-mapped storage);
-          nsplit_fp8   H crosses as e4m3 codes: the up GEMM's epilogue leaves the rows' maxima, one
-                       all-reduce(MAX) of m floats makes them the whole rows', a quantise-and-scatter
-                       kernel writes the codes to every rank, the down GEMM reads codes and scatters Y.
-        A one-element all-reduce on the stream orders the ranks after each scatter. Returns the step
-        and the tensor the result lands in."""
+          nsplit_fp8   H crosses as e4m3 codes: the up GEMM's epilogue leaves the rows' maxima, the
+                       library's exchange kernel makes them the whole rows' over peer-mapped
+                       mailboxes, a quantise-and-scatter kernel writes the codes to every rank, the
+                       down GEMM reads codes and scatters Y; the same exchange kernel is the barrier
+                       after each scatter (no library collective inside the step);
+          nsplit_fp8_nccl  the same with NCCL all-reduces in place of the exchange kernel.
+        The 16-bit push orders the ranks with a one-element all-reduce on the stream after each
+        scatter. Returns the step and the tensor the result lands in."""
         from libwaifu_b200 import sharding
         (n_up, k_up), (n_dn, k_dn) = wl["gemms"]
         up_a, up_b = sharding.column_shard(n_up, world, rank, 128)
@@ -406,7 +409,7 @@ def run_ours(args, wl):
             return split_step, wrap(y_t, bf), x_w, (h_t, y_t, y_loc_t)
 
         # memory of its own (not the pool's): the only kind another process can map
-        h_dtype = F.DType.FP8E4M3 if mode == "nsplit_fp8" else bf
+        h_dtype = F.DType.FP8E4M3 if mode.startswith("nsplit_fp8") else bf
         h_own = F.Tensor.empty((m, n_up), h_dtype, hint=F.AllocHint.WEIGHT)
         y_own = F.Tensor.empty((m, n_dn), bf, hint=F.AllocHint.WEIGHT)
         handles = [None] * world
@@ -429,19 +432,37 @@ def run_ours(args, wl):
         scales_t = torch.zeros(m, device="cuda", dtype=torch.float32)
         amax_w, scales_w = wrap(amax_t, F.DType.FLOAT), wrap(scales_t, F.DType.FLOAT)
 
-        def split_step():
-            F.fp8_linear_amax(x_w, up_q[0], up_q[1], amax_w, None, None, F.ACT_GELU_TANH, h_loc_w)
-            dist.all_reduce(amax_t, op=dist.ReduceOp.MAX)
-            F.fp8_quantize_scatter(h_loc_w, amax_w, h_dests, up_a, scales_w)
-            dist.all_reduce(flag)
-            F.fp8_linear_quantized_scatter(h_own, scales_w, dn_q[0], dn_q[1], y_dests, dn_a, None, x_cols_w, F.ACT_NONE)
-            dist.all_reduce(flag)
-        return split_step, y_own, x_w, (h_dests, y_dests, flag, amax_t, scales_t, h_loc_t)
+        def all_gather_handles(mine):
+            every = [None] * world
+            dist.all_gather_object(every, mine)
+            return every
+
+        group = F.PeerGroup(rank, world, m, all_gather_handles)
+        if mode == "nsplit_fp8_nccl":
+            def split_step():
+                F.fp8_linear_amax(x_w, up_q[0], up_q[1], amax_w, None, None, F.ACT_GELU_TANH, h_loc_w)
+                dist.all_reduce(amax_t, op=dist.ReduceOp.MAX)
+                F.fp8_quantize_scatter(h_loc_w, amax_w, h_dests, up_a, scales_w)
+                dist.all_reduce(flag)
+                F.fp8_linear_quantized_scatter(h_own, scales_w, dn_q[0], dn_q[1], y_dests, dn_a, None, x_cols_w, F.ACT_NONE)
+                dist.all_reduce(flag)
+        else:
+            def split_step():
+                F.fp8_linear_amax(x_w, up_q[0], up_q[1], amax_w, None, None, F.ACT_GELU_TANH, h_loc_w)
+                group.exchange(amax_w)       # the rows' maxima over all ranks
+                F.fp8_quantize_scatter(h_loc_w, amax_w, h_dests, up_a, scales_w)
+                group.exchange()             # every rank's codes have landed
+                F.fp8_linear_quantized_scatter(h_own, scales_w, dn_q[0], dn_q[1], y_dests, dn_a, None, x_cols_w, F.ACT_NONE)
+                group.exchange()             # every rank's block of Y has landed
+        return split_step, y_own, x_w, (h_dests, y_dests, flag, amax_t, scales_t, h_loc_t, group)
 
     SPLIT_WORDS = {
         "nsplit": "NCCL all-gather of H and Y in 16 bits",
         "nsplit_push": "epilogues push H and Y (16 bits) to peers over NVLink",
-        "nsplit_fp8": "H crosses as e4m3 codes (row maxima all-reduced, quantise-and-scatter kernel), the down GEMM's epilogue pushes Y",
+        "nsplit_fp8": "H crosses as e4m3 codes (row maxima and barriers by the library's exchange kernel over peer mailboxes, "
+                      "quantise-and-scatter kernel), the down GEMM's epilogue pushes Y",
+        "nsplit_fp8_nccl": "H crosses as e4m3 codes (row maxima and barriers by NCCL all-reduces, quantise-and-scatter kernel), "
+                           "the down GEMM's epilogue pushes Y",
     }
     if nsplit:
         if not (wl["kind"] == "fp8" and len(wl["gemms"]) == 2 and dist is not None):
@@ -1372,7 +1393,7 @@ def main():
     ap.add_argument("--e2e-chunks", type=int, default=4, help="row chunks the end-to-end step is pipelined in")
     ap.add_argument("--sustained-seconds", type=float, default=1.0,
                     help="length of the extra back-to-back loop behind roofline.sustained (0: skip it)")
-    ap.add_argument("--parallel", default="batch", choices=["batch", "nsplit", "nsplit_push", "nsplit_fp8"],
+    ap.add_argument("--parallel", default="batch", choices=["batch", "nsplit", "nsplit_push", "nsplit_fp8", "nsplit_fp8_nccl"],
                     help="batch: rows sharded, no collective (weak scaling; at N > 1 the line also carries a "
                          "strong_scaling object from the nsplit_fp8 form); nsplit*: one MLP with its weights split by "
                          "output channel (strong scaling): NCCL all-gathers / epilogue pushes in 16 bits / H gathered as e4m3 codes")

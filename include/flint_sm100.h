@@ -286,6 +286,26 @@ FLAPI int32_t fl_fp8_linear_quantized_scatter(fl_tensor_view_t codes, fl_tensor_
                                               fl_tensor_view_t scales, fl_tensor_view_t bias, fl_tensor_view_t residual,
                                               int32_t act, const fl_tensor_view_t *dests, int32_t n_dest, int32_t col0);
 
+/* A barrier among the GPUs of one box (one process each), in one small kernel on the stream, that can
+ * carry a maximum per row: what stands between the kernels of a split linear in place of a library
+ * collective. mailboxes[i] is rank i's <int32>(n_ranks, FL_SM100_PEER_HEADER + capacity) matrix, zeroed
+ * when made: mailboxes[rank] this GPU's own (FL_ALLOC_WEIGHT storage of 2 MiB or more, exported), the
+ * others imported with fl_sm100_ipc_import(). Every rank makes the same calls in the same order with
+ * the same `epoch`, 1 at the first call and larger at every later one. The kernel
+ *   - if row_amax <float>(rows <= capacity) is not NULL, writes it into every rank's mailbox;
+ *   - makes everything this GPU wrote before it (earlier kernels of the stream included: scattered
+ *     codes, a product's column block) visible ahead of its flag, and sets the flag in every mailbox;
+ *   - waits until every rank's flag in its own mailbox has reached `epoch`: what those ranks wrote
+ *     before their call is visible to the kernels that follow on this stream;
+ *   - if row_amax, leaves in it the largest of the ranks' values per row.
+ * The wait is bounded: after max_polls polls (0: a default of about two seconds) the kernel records
+ * a status the next call and fl_sm100_synchronize() report as FL_ERROR_ABORTED, and returns with
+ * row_amax as it was. A rank may not reuse what a peer reads (the scattered buffers) before a later
+ * exchange has completed. No counterpart in the reference. */
+#define FL_SM100_PEER_HEADER 64
+FLAPI int32_t fl_sm100_peer_exchange(const fl_tensor_view_t *mailboxes, int32_t n_ranks, int32_t rank, int32_t epoch,
+                                     fl_tensor_view_t row_amax, int32_t max_polls);
+
 /* Device storage shared between the processes of one box (one process per GPU): export writes
  * the 64-byte handle of storage made by fl_tensor_data_create(FL_DEVICE_CUDA, ..., FL_ALLOC_WEIGHT, ...)
  * of 2 MiB or more (memory of its own; blocks of the stream-ordered pool have no handle); import maps

@@ -20,6 +20,7 @@
 #include "skinny_sm100.cuh"
 #include "attention_sm100.cuh"
 #include "elementwise_sm100.cuh"
+#include "peer_sm100.cuh"
 #include "selftest_sm100.cuh"
 #include "matmul_simt_sm100.cuh"
 
@@ -1644,6 +1645,50 @@ int32_t fl_fp8_linear_scatter(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_
     ep.out_col0 = col0;
     for (int i = 0; i < sd.num_extra; ++i) ep.extra_out[ep.num_extra_out++] = sd.extra[i];
     run_gemm(kGemmE4M3, m, rows, k, codes, w_ptr, nullptr, nullptr, ep, is_bf16, sd.first);
+    return clear_error();
+  });
+}
+
+int32_t fl_sm100_peer_exchange(const fl_tensor_view_t *mailboxes, int32_t n_ranks, int32_t rank, int32_t epoch,
+                               fl_tensor_view_t row_amax_h, int32_t max_polls) {
+  return guard([&]() -> int32_t {
+    if (!mailboxes || n_ranks < 1 || n_ranks > kPeerMaxRanks) invalid("between 1 and " + std::to_string(kPeerMaxRanks) + " mailboxes are needed");
+    if (rank < 0 || rank >= n_ranks) invalid("rank is not one of the mailboxes");
+    if (epoch < 1) invalid("epochs start at 1 and grow");
+    if (max_polls < 0) invalid("max_polls is not negative (0: the default limit)");
+    PeerExchangeArgs args{};
+    const fl_tensor_view_impl_t &first = deref(mailboxes[0]);
+    if (first.shape.size() != 2 || first.shape[0] < n_ranks || first.shape[1] < kPeerHeaderWords) {
+      invalid("a mailbox is an <int32>(n_ranks or more, " + std::to_string(kPeerHeaderWords) + " + rows) matrix");
+    }
+    for (int i = 0; i < n_ranks; ++i) {
+      const fl_tensor_view_impl_t &b = deref(mailboxes[i]);
+      if (dtype_of(b) != FL_DTYPE_INT32 || device_of(b) != FL_DEVICE_CUDA || !is_contiguous(b) || b.shape != first.shape) {
+        invalid("the mailboxes are not contiguous <int32> matrices of one shape on cuda");
+      }
+      if (!aligned16(raw_ptr(b))) invalid("a mailbox's first element is not 16-byte aligned");
+      args.mailbox[i] = reinterpret_cast<int32_t *>(raw_ptr(b));
+    }
+    args.n_ranks = n_ranks;
+    args.rank = rank;
+    args.ld = first.shape[1];
+    args.epoch = epoch;
+    if (row_amax_h) {
+      const fl_tensor_view_impl_t &am = deref(row_amax_h);
+      if (dtype_of(am) != FL_DTYPE_FLOAT || device_of(am) != FL_DEVICE_CUDA || !is_contiguous(am)) {
+        invalid("row_amax is not a contiguous <float> tensor on cuda");
+      }
+      if (numel_of(am) > first.shape[1] - kPeerHeaderWords) invalid("row_amax has more values than a mailbox row holds");
+      args.row_amax = reinterpret_cast<float *>(raw_ptr(am));
+      args.rows = static_cast<int>(numel_of(am));
+    }
+    args.max_polls = static_cast<uint32_t>(max_polls);
+    require_kernels();
+    check_earlier_kernel_status();
+    args.status = status_word();
+    args.stream = 0;
+    cuda_check(peer_exchange(args), "launching the peer exchange");
+    ++g_block_launches;
     return clear_error();
   });
 }

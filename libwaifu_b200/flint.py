@@ -121,6 +121,7 @@ def lib() -> ctypes.CDLL:
     L.fl_fp8_quantize_scatter.argtypes = [V, V, POINTER(V), c_int32, c_int32, V]; L.fl_fp8_quantize_scatter.restype = c_int32
     L.fl_fp8_linear_quantized_scatter.argtypes = [V, V, V, V, V, V, c_int32, POINTER(V), c_int32, c_int32]
     L.fl_fp8_linear_quantized_scatter.restype = c_int32
+    L.fl_sm100_peer_exchange.argtypes = [POINTER(V), c_int32, c_int32, c_int32, V, c_int32]; L.fl_sm100_peer_exchange.restype = c_int32
     L.fl_sm100_ipc_export.argtypes = [V, V]; L.fl_sm100_ipc_export.restype = c_int32
     L.fl_sm100_ipc_import.argtypes = [V, c_int32, c_int64, POINTER(V)]; L.fl_sm100_ipc_import.restype = c_int32
     L.fl_quantize_fp8_rows.argtypes = [V, V, V]
@@ -546,6 +547,35 @@ def fp8_linear_quantized_scatter(codes: Tensor, row_scales: Tensor, weight: Tens
     check(lib().fl_fp8_linear_quantized_scatter(codes.raw(), row_scales.raw(), weight.raw(), scales.raw(),
                                                 bias.raw() if bias else None, residual.raw() if residual else None,
                                                 int(act), arr, len(dests), int(col0)))
+
+
+PEER_HEADER = 64
+
+
+class PeerGroup:
+    """The mailboxes of fl_sm100_peer_exchange for the ranks of one box and the epoch they count.
+
+    `exchange_handles(handle) -> list of every rank's handle` is the caller's way of passing 64-byte
+    handles between the processes (an all_gather_object, a file, a pipe)."""
+
+    def __init__(self, rank: int, world: int, capacity: int, exchange_handles):
+        self.rank, self.world = rank, world
+        width = PEER_HEADER + max(int(capacity), 0)
+        rows = max(world, -(-(2 << 20) // (4 * width)))  # storage of its own starts at 2 MiB
+        self._own = Tensor.empty((rows, width), DType.INT32, hint=AllocHint.WEIGHT)
+        copy(Tensor.from_numpy(np.zeros((rows, width), np.int32), DType.INT32), self._own)
+        synchronize()
+        handles = exchange_handles(ipc_export(self._own))
+        self._peers = {r: ipc_import(handles[r], (rows, width), DType.INT32) for r in range(world) if r != rank}
+        self._boxes = [(self._own if r == rank else self._peers[r]).view_as((world, width), (width, 1)) for r in range(world)]
+        self._arr = (c_void_p * world)(*[b.raw() for b in self._boxes])
+        self.epoch = 0
+
+    def exchange(self, row_amax: Optional[Tensor] = None, max_polls: int = 0) -> None:
+        """A barrier on the stream among the ranks; with `row_amax`, also its maximum over the ranks."""
+        self.epoch += 1
+        check(lib().fl_sm100_peer_exchange(self._arr, self.world, self.rank, self.epoch,
+                                           row_amax.raw() if row_amax else None, int(max_polls)))
 
 
 def ipc_export(t: Tensor) -> bytes:

@@ -2,6 +2,7 @@
 full-width matrices. On one GPU the destinations are two local matrices; with two or more GPUs a
 second test maps a peer process's matrix through the IPC handle and checks the fused all-gather of
 an output-channel split against the unsplit oracle."""
+import ctypes
 import os
 import socket
 import sys
@@ -145,28 +146,42 @@ def _narrow_worker(rank, world, port):
         amax_t = torch.zeros(m, device="cuda", dtype=torch.float32)
         amax = F.Tensor.from_device_ptr(amax_t.data_ptr(), (m,), fl, keepalive=amax_t)
         scales = F.Tensor.empty((m,), fl)
-        flag = torch.zeros(1, device="cuda")
+
+        def all_gather_handles(mine):
+            every = [None] * world
+            dist.all_gather_object(every, mine)
+            return every
+
+        group = F.PeerGroup(rank, world, m, all_gather_handles)
+
+        class InKernelMax:
+            """What NarrowGatherMlp asks of `dist`: the maximum over the ranks, here by the library's own
+            exchange kernel on the stream (no library collective between the GEMMs)."""
+            ReduceOp = dist.ReduceOp
+            get_world_size, get_rank = staticmethod(dist.get_world_size), staticmethod(dist.get_rank)
+
+            @staticmethod
+            def all_reduce(t, op=None):
+                assert t is amax_t and op == dist.ReduceOp.MAX
+                group.exchange(amax)
+
+        mlp.dist = InKernelMax
 
         def up_op(_):
-            h_block = F.fp8_linear_amax(xd, w_up, s_up, amax, None, None, F.ACT_GELU_TANH)
-            F.synchronize()  # the library's stream, then the collective's
-            return h_block, amax_t
+            return F.fp8_linear_amax(xd, w_up, s_up, amax, None, None, F.ACT_GELU_TANH), amax_t
 
         def scatter_op(h_block, amax_tensor, col0):
             F.fp8_quantize_scatter(h_block, amax, codes_dests, col0, scales)
-            F.synchronize()
-            dist.all_reduce(flag)  # every rank's block of codes has landed once this has completed
-            torch.cuda.synchronize()
+            group.exchange()  # every rank's block of codes has landed once this has completed
             return codes_own, scales
 
         def down_op(codes, row_scales, col0):
             F.fp8_linear_quantized_scatter(codes, row_scales, w_dn, s_dn, y_dests, col0, None, x_cols, F.ACT_NONE)
-            F.synchronize()
-            dist.all_reduce(flag)
-            torch.cuda.synchronize()
+            group.exchange()
             return y_own
 
-        mlp.step(xd, up_op, scatter_op, down_op)
+        for _ in range(3):  # the buffers and mailboxes are reused step after step
+            mlp.step(xd, up_op, scatter_op, down_op)
         F.synchronize()
         got_codes = codes_own.numpy()
         h_ref = O.fp8_linear(x, up_c, up_s, None, None, O.ACT_GELU_TANH)
@@ -187,7 +202,7 @@ def _narrow_worker(rank, world, port):
         dist.all_gather(both, digest)
         assert all(torch.equal(b, both[0]) for b in both), "the ranks hold different codes, scales or results"
         dist.barrier()
-        del codes_dests, y_dests, peers
+        del codes_dests, y_dests, peers, group
     finally:
         dist.destroy_process_group()
 
@@ -244,3 +259,50 @@ def test_row_maxima_and_quantise_scatter_on_one_gpu(flint, oracle):
     assert np.array_equal(row_scales.numpy().view(np.uint32), want_scales.view(np.uint32))
     with pytest.raises(F.FlintError):
         F.fp8_quantize_scatter(dev(F, np.ascontiguousarray(h_np[:, :256]), bf), amax, [d0], 136)   # does not fit / not a multiple of 16
+
+
+def test_peer_exchange_with_a_peer_written_by_the_host(flint, oracle):
+    """One GPU, two mailboxes: this rank's and a stand-in for a peer's. The peer's flag and payload
+    are put into this rank's mailbox by a copy before the kernel runs (no second kernel waits on this
+    one), so the kernel finds its peer arrived, and leaves the larger of the two maxima per row."""
+    F = flint
+    rows, world, width = 300, 2, F.PEER_HEADER + 320
+    rng = np.random.default_rng(8)
+    mine = np.abs(rng.standard_normal(rows)).astype(np.float32)
+    theirs = np.abs(rng.standard_normal(rows)).astype(np.float32)
+    box0 = np.zeros((world, width), np.int32)
+    box0[1, 0] = 7                                   # the peer's flag, already at this epoch
+    box0[1, F.PEER_HEADER:F.PEER_HEADER + rows] = theirs.view(np.int32)
+    own = F.Tensor.from_numpy(box0, F.DType.INT32)
+    peer = F.Tensor.from_numpy(np.zeros((world, width), np.int32), F.DType.INT32)
+    amax = F.Tensor.from_numpy(mine, F.DType.FLOAT)
+    arr = (ctypes.c_void_p * 2)(own.raw(), peer.raw())
+    F.check(F.lib().fl_sm100_peer_exchange(arr, 2, 0, 7, amax.raw(), 0))
+    F.synchronize()
+    assert np.array_equal(amax.numpy(), np.maximum(mine, theirs))
+    got_peer = peer.numpy()
+    assert got_peer[0, 0] == 7 and np.array_equal(got_peer[0, F.PEER_HEADER:F.PEER_HEADER + rows].view(np.float32), mine)
+    assert own.numpy()[0, 0] == 7
+    # a later epoch passes too when the flag is already ahead of it; an earlier argument is refused
+    F.check(F.lib().fl_sm100_peer_exchange(arr, 1, 0, 8, None, 0))
+    F.synchronize()
+    for bad in [(arr, 0, 0, 1), (arr, 2, 2, 1), (arr, 2, 0, 0)]:
+        assert F.lib().fl_sm100_peer_exchange(bad[0], bad[1], bad[2], bad[3], None, 0) == F.FL_ERROR_INVALID_ARG
+
+
+def test_peer_exchange_gives_up_on_a_peer_that_never_arrives(flint):
+    """The wait is bounded: a peer whose flag nothing sets makes the kernel record its status and
+    return; the next synchronisation reports it and the library carries on."""
+    F, L = flint, flint.lib()
+    world, width = 2, F.PEER_HEADER + 16
+    own = F.Tensor.from_numpy(np.zeros((world, width), np.int32), F.DType.INT32)
+    peer = F.Tensor.from_numpy(np.zeros((world, width), np.int32), F.DType.INT32)
+    keep = np.arange(16, dtype=np.float32)
+    amax = F.Tensor.from_numpy(keep, F.DType.FLOAT)
+    arr = (ctypes.c_void_p * 2)(own.raw(), peer.raw())
+    F.synchronize()
+    F.check(L.fl_sm100_peer_exchange(arr, 2, 0, 1, amax.raw(), 64))
+    status = ctypes.c_int32(0)
+    assert L.fl_sm100_synchronize(ctypes.byref(status)) == F.FL_ERROR_ABORTED and status.value == 0x61
+    assert L.fl_sm100_synchronize(ctypes.byref(status)) == F.FL_OK and status.value == 0
+    assert np.array_equal(amax.numpy(), keep)
