@@ -84,6 +84,11 @@ constexpr int kStreamKMinSavedStages = 40;
 constexpr int kBandTiles = 8;
 constexpr int kBandMax = 16;
 
+// One map per destination of the staged epilogue.
+struct OutMaps {
+  CUtensorMap at[kMaxGemmOutputs];
+};
+
 struct KernelParams {
   int m, n;
   int num_kb;  // stages of K per tile
@@ -285,7 +290,7 @@ template <int KIND, int BLOCK_N, int CTAS, bool B8>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-               const __grid_constant__ CUtensorMap tmap_out, const KernelParams p) {
+               const __grid_constant__ OutMaps tmaps_out, const KernelParams p) {
   constexpr bool NVF4 = (KIND == kKindNvf4);
   using Cfg = Config<BLOCK_N, NVF4, CTAS, B8>;
   constexpr int STAGES = Cfg::kStages;
@@ -317,7 +322,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
-  const bool scatter = p.num_out > 1;
+  // Several destinations (a product gathered on several GPUs): in the staged form every chunk leaves
+  // shared memory once per destination by TMA; otherwise the pusher warps copy this GPU's finished
+  // tile to the others.
+  const bool scatter = p.num_out > 1 && !p.out_staged;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -342,7 +350,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == kProducerWarp && lane == 0) {
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
-    if (p.out_staged) tma_prefetch_desc(&tmap_out);
+    if (p.out_staged) {
+      for (int d = 0; d < p.num_out; ++d) tma_prefetch_desc(&tmaps_out.at[d]);
+    }
   }
   if (warp == kMmaWarp) {
     tmem_alloc<CTAS>(&tmem_base_slot, Cfg::kTmemCols);
@@ -892,7 +902,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           __syncwarp();
           // Rows past m and columns past n are not written: the tensor map ends there.
           if (lane == 0) {
-            tma_store_2d(&tmap_out, obuf, nc, row - static_cast<int>(lane));
+            for (int d = 0; d < p.num_out; ++d) tma_store_2d(&tmaps_out.at[d], obuf, nc, row - static_cast<int>(lane));
             bulk_commit_group();
           }
           return;
@@ -1218,13 +1228,16 @@ cudaError_t launch_one(const GemmArgs &a, KernelParams kp, uint64_t row_bytes, c
   // be described by a tensor map (one 16-byte aligned matrix, pitch a multiple of 8 elements) and
   // the residual, if any, is a plain 16-byte aligned matrix of out's rows; otherwise every lane
   // stores (and loads the residual of) its own row.
-  CUtensorMap tout = ta;
+  OutMaps tout;
+  for (int d = 0; d < kMaxGemmOutputs; ++d) tout.at[d] = ta;
   kp.out_staged = 0;
-  if (kp.out_vector && kp.num_out == 1 &&
-      (!kp.residual || (kp.residual_rows == a.m && (reinterpret_cast<uintptr_t>(kp.residual) & 15) == 0 &&
-                        kp.residual_ld % 8 == 0))) {
-    void *base = reinterpret_cast<uint16_t *>(kp.out[0]) + kp.out_col0;
-    if (make_tmap_out(&tout, base, a.m, a.n, kp.out_ld)) kp.out_staged = 1;
+  if (kp.out_vector && (!kp.residual || (kp.residual_rows == a.m && (reinterpret_cast<uintptr_t>(kp.residual) & 15) == 0 &&
+                                         kp.residual_ld % 8 == 0))) {
+    kp.out_staged = 1;
+    for (int d = 0; d < kp.num_out && kp.out_staged; ++d) {
+      void *base = reinterpret_cast<uint16_t *>(kp.out[d]) + kp.out_col0;
+      if (!make_tmap_out(&tout.at[d], base, a.m, a.n, kp.out_ld)) kp.out_staged = 0;
+    }
   }
   auto kernel = gemm_tn_kernel<KIND, BLOCK_N, CTAS, B8>;
   static bool attr_set = false;  // per instantiation
@@ -1238,7 +1251,7 @@ cudaError_t launch_one(const GemmArgs &a, KernelParams kp, uint64_t row_bytes, c
   }
   const int tiles = kp.tiles_m * kp.tiles_n;
   const size_t part_floats_per_unit = static_cast<size_t>(2) * CTAS * kBlockM * BLOCK_N;
-  const bool may_stream_k = a.sk_partials && a.sk_counters && !a.no_stream_k && kp.num_out == 1 &&
+  const bool may_stream_k = a.sk_partials && a.sk_counters && !a.no_stream_k && (kp.num_out == 1 || kp.out_staged) &&
                             part_floats_per_unit * (sm_count() / CTAS) <= a.sk_partial_floats &&
                             static_cast<size_t>(2) * sm_count() * kMaxEpilogueWarps <= a.sk_counter_words;
   const GemmSchedule sch = gemm_schedule(tiles, sm_count() / CTAS, kp.num_kb, may_stream_k);
