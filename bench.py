@@ -177,6 +177,29 @@ class ClockSampler(threading.Thread):
                 "reasons": reasons, "samples": len(self.samples), "power_w_max": max(watts)}
 
 
+def bind_by_nvml_affinity(bus):
+    """Where sysfs names no NUMA node for the GPU (a virtual machine), the driver may still know the
+    CPUs nearest to it: NVML's ideal CPU set for the device, read only, intersected with the CPUs
+    this process may use."""
+    allowed_now = set(os.sched_getaffinity(0))
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            words = pynvml.nvmlDeviceGetCpuAffinity(handle, (max(allowed_now) // 64) + 1)
+        finally:
+            pynvml.nvmlShutdown()
+        cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        allowed = cpus & allowed_now
+        if not allowed or allowed == allowed_now:
+            return f"the GPU reports no NUMA node and the driver's ideal CPU set does not narrow this process's {len(allowed_now)} CPUs; not bound"
+        os.sched_setaffinity(0, allowed)
+        return f"pinned buffers allocated from the driver's ideal CPU set for the GPU ({len(allowed)} of {len(allowed_now)} CPUs)"
+    except Exception as e:
+        return f"the GPU reports no NUMA node; not bound ({len(allowed_now)} CPUs, NVML: {type(e).__name__})"
+
+
 def bind_to_gpu_numa_node(local_index):
     """Best effort: runs this process on the CPUs of the NUMA node its GPU hangs off, so that the
     page-locked buffers allocated afterwards are local to the GPU's PCIe root (eight ranks copying
@@ -188,7 +211,7 @@ def bind_to_gpu_numa_node(local_index):
         with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
             node = int(f.read().strip())
         if node < 0:
-            return "the GPU reports no NUMA node; not bound"
+            return bind_by_nvml_affinity(bus)
         with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
             text = f.read().strip()
         cpus = set()
@@ -594,54 +617,85 @@ def run_ours(args, wl):
     n_last = wl["gemms"][-1][0]
     affinity = os.sched_getaffinity(0)
     bind_note = bind_to_gpu_numa_node(local)
-    host_x = F.Tensor.empty((m, k0), bf, F.Device.CUDA_HOST)
-    host_y = F.Tensor.empty((m, n_last), bf, F.Device.CUDA_HOST)
+    depth = 1 if nsplit else 2   # steps in flight: page-locked buffers each way
+    host_xs = [F.Tensor.empty((m, k0), bf, F.Device.CUDA_HOST) for _ in range(depth)]
+    host_ys = [F.Tensor.empty((m, n_last), bf, F.Device.CUDA_HOST) for _ in range(depth)]
     os.sched_setaffinity(0, affinity)  # only the allocation (and its first touch) needed the binding
     result = split_result if nsplit else None
     import ctypes
     import numpy as np
-    p = ctypes.c_void_p()
-    F.check(F.lib().fl_tensor_data_get_host_ptr(host_x._data, ctypes.byref(p)))
-    hx = np.ctypeslib.as_array(ctypes.cast(p.value, ctypes.POINTER(ctypes.c_uint16)), shape=(m * k0,))
-    hx[:] = (np.random.default_rng(7 + rank).standard_normal(m * k0).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    for j, hx_t in enumerate(host_xs):
+        p = ctypes.c_void_p()
+        F.check(F.lib().fl_tensor_data_get_host_ptr(hx_t._data, ctypes.byref(p)))
+        hx = np.ctypeslib.as_array(ctypes.cast(p.value, ctypes.POINTER(ctypes.c_uint16)), shape=(m * k0,))
+        hx[:] = (np.random.default_rng(7 + rank + 100 * j).standard_normal(m * k0).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
     ops = F.operators()
     chunks = 1 if nsplit else max(1, min(args.e2e_chunks, m // 128))
     bounds = [min(m, ((m * c // chunks) + 255) // 256 * 256) for c in range(chunks)] + [m]  # whole 256-row tiles
     bounds[0] = 0
     bounds = sorted(set(bounds))
     chunks = len(bounds) - 1
-    x_chunks = [host_x.view_as((bounds[c + 1] - bounds[c], k0), (k0, 1), bounds[c] * k0) for c in range(chunks)]
-    y_chunks = [host_y.view_as((bounds[c + 1] - bounds[c], n_last), (n_last, 1), bounds[c] * n_last) for c in range(chunks)]
+    x_chunks = [[hx_t.view_as((bounds[c + 1] - bounds[c], k0), (k0, 1), bounds[c] * k0) for c in range(chunks)] for hx_t in host_xs]
+    y_chunks = [[hy_t.view_as((bounds[c + 1] - bounds[c], n_last), (n_last, 1), bounds[c] * n_last) for c in range(chunks)]
+                for hy_t in host_ys]
 
-    def e2e_step(i):
+    def e2e_issue(i):
+        """Starts step i: every chunk's upload at once, chunk j's linears behind chunk j's upload
+        only, its result handed to the download stream. Returns what the step's end waits for."""
         if nsplit:
-            F.check(F.lib().fl_transfer(ops, host_x.raw(), x_w.raw()))
+            F.check(F.lib().fl_transfer(ops, host_xs[0].raw(), x_w.raw()))
             step(i)
-            F.check(F.lib().fl_transfer(ops, result.raw(), host_y.raw()))  # synchronises
-            return
-        uploads = [F.transfer_async(xc) for xc in x_chunks]
+            F.check(F.lib().fl_transfer(ops, result.raw(), host_ys[0].raw()))  # synchronises
+            return None
+        uploads = [F.transfer_async(xc) for xc in x_chunks[i % depth]]
         downloads, alive = [], []
         for c in range(chunks):
             xd, pending = uploads[c]
             pending.wait()
             y = step(i, x_override=xd, alloc=True)
-            downloads.append(F.transfer_to_host_async(y, y_chunks[c]))
-            alive.append(y)
-        downloads[-1].wait_sync()   # downloads complete in order on their stream
-        for d in downloads[:-1]:
-            d.wait_sync()
+            downloads.append(F.transfer_to_host_async(y, y_chunks[i % depth][c]))
+            alive.append((xd, y))
+        return downloads, alive
 
-    e2e_steps = max(3, min(args.steps, 20))
-    for i in range(3):
-        e2e_step(i)
+    def e2e_finish(token):
+        """The host has step i's result: its downloads are complete (in order on their stream)."""
+        if token is not None:
+            for d in reversed(token[0]):
+                d.wait_sync()
+
+    def e2e_run(n_steps):
+        # Two steps in flight: step i + 1 is started (its uploads cross while step i computes and
+        # step i - 1's result goes back) before the host waits for step i's result, as a caller with
+        # a queue of requests would; each step's copies, both ways, are inside the timed region.
+        in_flight = []
+        for i in range(n_steps):
+            in_flight.append(e2e_issue(i))
+            if len(in_flight) >= depth:
+                e2e_finish(in_flight.pop(0))
+        while in_flight:
+            e2e_finish(in_flight.pop(0))
+
+    e2e_steps = max(4, min(args.steps, 20))
+    e2e_run(3)
     barrier()
     e0.record()
-    for i in range(e2e_steps):
-        e2e_step(i)
+    e2e_run(e2e_steps)
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
     e2e_value = work_units * flops_per_step(wl) / (e2e_ms * 1e-3) / 1e12
+    # the same with one step at a time (the host waits for a step's result before it starts the next)
+    e2e_serial_ms = None
+    if not nsplit:
+        depth_keep, depth = depth, 1
+        e2e_run(2)
+        barrier()
+        e0.record()
+        e2e_run(e2e_steps)
+        e1.record()
+        barrier()
+        e2e_serial_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
+        depth = depth_keep
 
     # ---- roofline of the dominant kernel (the tcgen05 GEMM), from its own events ---------------
     clocks = sampler.summary()
@@ -707,8 +761,11 @@ def run_ours(args, wl):
                        "accumulate": "fp32", "out": "bf16"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": m * k0 * 2,
                     "d2h_bytes_per_step": m * n_last * 2, "steps": e2e_steps, "chunks": chunks,
+                    "steps_in_flight": depth, "one_step_at_a_time_ms": e2e_serial_ms,
                     "how": "rows in chunks: uploads on a copy stream (fl_transfer_async), linears per chunk behind "
-                           "fl_transfer_wait, downloads on a second copy stream; outputs allocated per call; one host wait per step",
+                           "fl_transfer_wait, downloads on a second copy stream; outputs allocated per call; step i + 1 is "
+                           "started before the host waits for step i's result (two page-locked buffers each way); "
+                           "one_step_at_a_time_ms is the same with one step in flight",
                     "host_memory": bind_note},
             "per_call_alloc": alloc_check,
             "strong_scaling": strong,

@@ -277,6 +277,10 @@ FLAPI int32_t fl_fp8_linear_amax(fl_tensor_view_t a, fl_tensor_view_t data, fl_t
                                  fl_tensor_view_t residual, int32_t act, fl_tensor_view_t out, fl_tensor_view_t row_amax);
 FLAPI int32_t fl_fp8_quantize_scatter(fl_tensor_view_t x, fl_tensor_view_t row_amax, const fl_tensor_view_t *dests,
                                       int32_t n_dest, int32_t col0, fl_tensor_view_t row_scales);
+/* The rows' maxima of a block that no GEMM of this library produced (this rank's heads of an
+ * attention result, say): row_amax[r] = max |x[r, :]| of x <float16|bfloat16>(rows, k), whose rows
+ * may lie further apart than k (a column block of a wider matrix). */
+FLAPI int32_t fl_fp8_row_amax(fl_tensor_view_t x, fl_tensor_view_t row_amax);
 
 /* fl_fp8_linear_quantized() with fl_fp8_linear_scatter()'s way out: codes <fp8e4m3>(..., k) and their
  * rows' scales times the weight, the product written into columns [col0, col0 + rows) of each of

@@ -1573,6 +1573,26 @@ ScatterDests check_scatter_dests(const fl_tensor_view_t *dests, int32_t n_dest, 
 
 }  // namespace
 
+int32_t fl_fp8_row_amax(fl_tensor_view_t x_h, fl_tensor_view_t row_amax_h) {
+  return guard([&]() -> int32_t {
+    const fl_tensor_view_impl_t &x = deref(x_h);
+    const fl_tensor_view_impl_t &am = deref(row_amax_h);
+    if (!is_half_type(dtype_of(x)) || x.shape.size() != 2 || x.stride[1] != 1 || device_of(x) != FL_DEVICE_CUDA) {
+      invalid("x is not a <float16> or <bfloat16> matrix with contiguous rows on cuda");
+    }
+    if (dtype_of(am) != FL_DTYPE_FLOAT || numel_of(am) != x.shape[0] || !is_contiguous(am) || device_of(am) != FL_DEVICE_CUDA) {
+      invalid("row_amax is not a contiguous <float> tensor of one value per row of x on cuda");
+    }
+    require_kernels();
+    check_earlier_kernel_status();
+    if (x.shape[0] == 0) return clear_error();
+    cuda_check(row_amax_16(raw_ptr(x), dtype_of(x) == FL_DTYPE_BFLOAT16, x.shape[0], x.shape[1], x.stride[0],
+                           reinterpret_cast<float *>(raw_ptr(am)), 0),
+               "taking the rows' maxima");
+    return clear_error();
+  });
+}
+
 int32_t fl_fp8_linear_scatter(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_view_t scales_h,
                               fl_tensor_view_t bias_h, fl_tensor_view_t residual_h, int32_t act,
                               const fl_tensor_view_t *dests, int32_t n_dest, int32_t col0) {

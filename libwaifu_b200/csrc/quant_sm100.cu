@@ -178,6 +178,28 @@ __global__ void __launch_bounds__(128) quantize_fp8_scatter_kernel(const uint16_
   }
 }
 
+// The largest magnitude of each row of a 16-bit matrix whose rows lie `pitch` elements apart.
+__global__ void __launch_bounds__(128) row_amax_kernel(const uint16_t *__restrict__ x, int is_bf16, int k, long long pitch,
+                                                     float *__restrict__ amax) {
+  __shared__ float red[4];
+  const uint16_t *xr = x + blockIdx.x * pitch;
+  uint32_t top = 0;  // magnitudes of one 16-bit format order like their bit patterns
+  if ((reinterpret_cast<uintptr_t>(xr) & 15) == 0 && k % 8 == 0) {
+    const uint4 *xv = reinterpret_cast<const uint4 *>(xr);
+    for (int v = threadIdx.x; v < k / 8; v += blockDim.x) {
+      const uint4 q = xv[v];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) top = max(top, max(w[j] & 0x7fffu, (w[j] >> 16) & 0x7fffu));
+    }
+  } else {
+    for (int i = threadIdx.x; i < k; i += blockDim.x) top = max(top, static_cast<uint32_t>(xr[i]) & 0x7fffu);
+  }
+  const float mine = widen(static_cast<uint16_t>(top), is_bf16);
+  const float all = block_max(mine, red);
+  if (threadIdx.x == 0) amax[blockIdx.x] = all;
+}
+
 // ---- layer norm -> modulate -> per-row e4m3, one pass ----------------------------------------
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -659,6 +681,12 @@ cudaError_t quantize_fp8_scatter(const void *x, int is_bf16, int m, int k, const
   }
   quantize_fp8_scatter_kernel<<<static_cast<unsigned>(m), 128, 0, stream>>>(static_cast<const uint16_t *>(x), is_bf16, k, amax, d,
                                                                             ld, col0, scales);
+  ++g_helper_launches;
+  return cudaGetLastError();
+}
+
+cudaError_t row_amax_16(const void *x, int is_bf16, int m, int k, int64_t pitch, float *amax, cudaStream_t stream) {
+  row_amax_kernel<<<static_cast<unsigned>(m), 128, 0, stream>>>(static_cast<const uint16_t *>(x), is_bf16, k, pitch, amax);
   ++g_helper_launches;
   return cudaGetLastError();
 }

@@ -23,6 +23,10 @@ cudaError_t quantize_fp8_rows_f32(const float *w, int rows, int k, uint8_t *code
 cudaError_t quantize_fp8_scatter(const void *x, int is_bf16, int m, int k, const float *amax, uint8_t *const *dests,
                                  int n_dest, int64_t ld, int col0, float *scales, cudaStream_t stream);
 
+// amax[r] = the largest |x[r, :]| of an (m, k) 16-bit matrix whose rows lie `pitch` elements apart
+// (NaNs order above every number, as in the epilogue's row maxima).
+cudaError_t row_amax_16(const void *x, int is_bf16, int m, int k, int64_t pitch, float *amax, cudaStream_t stream);
+
 // Layer norm over the last dimension (no affine; fp32 sums, mean = sum / k, variance =
 // sumsq / k - mean^2, eps inside the root: flint/cpu/normalizations.cc:98-140), then the adaLN modulation
 // h = round16(n * scale + n [+ shift]) with `scale`/`shift` (groups, k) 16-bit or null, a group's

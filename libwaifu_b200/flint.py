@@ -121,6 +121,7 @@ def lib() -> ctypes.CDLL:
     L.fl_fp8_quantize_scatter.argtypes = [V, V, POINTER(V), c_int32, c_int32, V]; L.fl_fp8_quantize_scatter.restype = c_int32
     L.fl_fp8_linear_quantized_scatter.argtypes = [V, V, V, V, V, V, c_int32, POINTER(V), c_int32, c_int32]
     L.fl_fp8_linear_quantized_scatter.restype = c_int32
+    L.fl_fp8_row_amax.argtypes = [V, V]; L.fl_fp8_row_amax.restype = c_int32
     L.fl_sm100_peer_exchange.argtypes = [POINTER(V), c_int32, c_int32, c_int32, V, c_int32]; L.fl_sm100_peer_exchange.restype = c_int32
     L.fl_sm100_ipc_export.argtypes = [V, V]; L.fl_sm100_ipc_export.restype = c_int32
     L.fl_sm100_ipc_import.argtypes = [V, c_int32, c_int64, POINTER(V)]; L.fl_sm100_ipc_import.restype = c_int32
@@ -528,6 +529,14 @@ def fp8_linear_amax(a: Tensor, weight: Tensor, scales: Tensor, row_amax: Tensor,
     check(lib().fl_fp8_linear_amax(a.raw(), weight.raw(), scales.raw(), bias.raw() if bias else None,
                                    residual.raw() if residual else None, int(act), out.raw(), row_amax.raw()))
     return out
+
+
+def fp8_row_amax(x: Tensor, row_amax: Optional[Tensor] = None) -> Tensor:
+    """The largest magnitude of each row of a 16-bit matrix (its rows may be a wider matrix's)."""
+    if row_amax is None:
+        row_amax = Tensor.empty((x.shape[0],), DType.FLOAT)
+    check(lib().fl_fp8_row_amax(x.raw(), row_amax.raw()))
+    return row_amax
 
 
 def fp8_quantize_scatter(x: Tensor, row_amax: Tensor, dests: Sequence[Tensor], col0: int,

@@ -147,6 +147,51 @@ class NarrowGatherMlp:
         return down(codes, scales, self.down_range[0])
 
 
+def qkv_head_rows(heads: int, head_dim: int, world: int, rank: int) -> List[Tuple[int, int]]:
+    """The rows of a fused (3 * heads * head_dim, k) QKV weight, laid out [q heads | k heads | v heads]
+    (waifu/src/qwen_image/dit.rs:239-263), that rank `rank` owns when the projection is split on head
+    boundaries: the same heads [h0, h1) of each of q, k and v, so that the rank can normalise, rotate
+    and attend over its heads without any exchange. Three [start, stop) ranges."""
+    h0, h1 = row_shard(heads, world, rank)
+    return [(part * heads * head_dim + h0 * head_dim, part * heads * head_dim + h1 * head_dim) for part in range(3)]
+
+
+class HeadSplitAttentionBlock:
+    """QKV projection, attention and out projection of one stream, split over the ranks by head.
+
+    Every rank projects the whole activation onto its heads of q, k and v (``qkv_head_rows``),
+    normalises, rotates and attends over those heads alone, and holds a column block of the
+    attention result (its heads' columns). The out projection reads whole rows, quantised per row:
+    the block crosses the links as e4m3 codes exactly as the hidden activation of
+    ``NarrowGatherMlp`` does (rows' maxima over the block, maximum over the ranks, codes written into
+    every rank's full-width matrix), and every rank multiplies the gathered codes by its slice of the
+    out projection's output channels. Heads, rows of a quantiser and output channels are all
+    independent, so the result equals the unsplit chain bit for bit."""
+
+    def __init__(self, dist, heads: int, head_dim: int, n_out: int, multiple: int = 128):
+        self.dist = dist
+        self.world = dist.get_world_size()
+        self.rank = dist.get_rank()
+        self.heads = row_shard(heads, self.world, self.rank)
+        self.qkv_rows = qkv_head_rows(heads, head_dim, self.world, self.rank)
+        self.head_dim = head_dim
+        self.col_range = (self.heads[0] * head_dim, self.heads[1] * head_dim)
+        self.col_sizes = [(row_shard(heads, self.world, r)[1] - row_shard(heads, self.world, r)[0]) * head_dim
+                          for r in range(self.world)]
+        self.out_range = column_shard(n_out, self.world, self.rank, multiple)
+        self.out_sizes = column_sizes(n_out, self.world, multiple)
+
+    def step(self, x, qkv, attend, row_amax, scatter_codes, out_proj):
+        """`qkv(x) -> this rank's (m, 3, heads_r, head_dim)`; `attend(qkv_r) -> (m, heads_r * head_dim)`;
+        `row_amax(a_r) -> tensor of m maxima`; `scatter_codes(a_r, amax, col0) -> (codes, scales)`;
+        `out_proj(codes, scales, col0) -> y`. Returns what `out_proj` returns."""
+        a_block = attend(qkv(x))
+        amax = row_amax(a_block)
+        self.dist.all_reduce(amax, op=self.dist.ReduceOp.MAX)
+        codes, scales = scatter_codes(a_block, amax, self.col_range[0])
+        return out_proj(codes, scales, self.out_range[0])
+
+
 def gather_rows(dist, local, sizes: Sequence[int]):
     """Concatenates row shards (used to hand a whole batch back to one caller)."""
     import torch

@@ -306,3 +306,17 @@ def test_peer_exchange_gives_up_on_a_peer_that_never_arrives(flint):
     assert L.fl_sm100_synchronize(ctypes.byref(status)) == F.FL_ERROR_ABORTED and status.value == 0x61
     assert L.fl_sm100_synchronize(ctypes.byref(status)) == F.FL_OK and status.value == 0
     assert np.array_equal(amax.numpy(), keep)
+
+
+def test_row_maxima_of_a_column_block(flint, oracle):
+    """fl_fp8_row_amax over a column block of a wider matrix (this rank's heads of an attention
+    result) equals the oracle's maxima of the same block, for both 16-bit types."""
+    F = flint
+    rng = np.random.default_rng(73)
+    for is_bf16, dt in ((True, F.DType.BFLOAT16), (False, F.DType.FLOAT16)):
+        full = oracle.narrow(randn(rng, (70, 384), 3.0), is_bf16)
+        d = dev(F, full, dt)
+        for (a, b) in [(0, 384), (128, 256), (250, 381)]:   # the last neither aligned nor a multiple of 8
+            block = d.view_as((70, b - a), (384, 1), a)
+            got = F.fp8_row_amax(block).numpy()
+            assert np.array_equal(got, oracle.row_amax(np.ascontiguousarray(full[:, a:b]), is_bf16)), (is_bf16, a, b)

@@ -88,6 +88,53 @@ def _worker(rank, world, port, ragged):
 
         y_narrow = mlp.step(x, up_op, scatter_op, down_op)
         assert np.array_equal(y_narrow, y_ref), "the MLP with e4m3-gathered hidden activation differs from the unsharded one"
+
+        # ---- QKV split on head boundaries, attention on a rank's own heads, the out projection on
+        # ---- the attention result gathered as e4m3 codes
+        heads, hd, tokens, batch = 4, 32, 24, 2
+        hidden, rows = heads * hd, batch * tokens
+        xa = O.narrow(rng.standard_normal((rows, hidden)).astype(np.float32), True)
+        qkv_c, qkv_s = O.quantize_fp8_rows((rng.standard_normal((3 * hidden, hidden)) * 0.05).astype(np.float32))
+        out_c, out_s = O.quantize_fp8_rows((rng.standard_normal((hidden, hidden)) * 0.05).astype(np.float32))
+        ang = np.outer(np.arange(tokens), 1.0 / (10000.0 ** (np.arange(hd // 2) / (hd // 2)))).astype(np.float32)
+        cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+
+        def attend(qkv16, n_heads):
+            """(rows, 3 * n_heads * hd) -> (rows, n_heads * hd): norm and rotation, then attention per image."""
+            r = O.qk_norm_rope(qkv16, cos, sin, n_heads, 1e-6, True)
+            five = r.reshape(batch, tokens, 3, n_heads, hd)
+            q, kk, v = (np.ascontiguousarray(five[:, :, i].transpose(0, 2, 1, 3)) for i in range(3))
+            a = O.narrow(O.attention(q, kk, v, False, True).astype(np.float32), True)       # (batch, heads, tokens, hd)
+            return np.ascontiguousarray(a.transpose(0, 2, 1, 3)).reshape(rows, n_heads * hd)
+
+        a_ref = attend(O.fp8_linear(xa, qkv_c, qkv_s, None, None, O.ACT_NONE), heads)
+        y_attn_ref = O.fp8_linear(a_ref, out_c, out_s, None, xa, O.ACT_NONE)
+        blk = sharding.HeadSplitAttentionBlock(dist, heads, hd, hidden, multiple=8)
+        mine = np.concatenate([np.arange(a0, b0) for a0, b0 in blk.qkv_rows])
+        assert len(mine) == 3 * (blk.heads[1] - blk.heads[0]) * hd
+
+        def qkv_op(x16):
+            return O.fp8_linear(x16, qkv_c[mine], qkv_s[mine], None, None, O.ACT_NONE)
+
+        def attend_op(qkv_block):
+            return attend(qkv_block, blk.heads[1] - blk.heads[0])
+
+        def amax_op(a_block):
+            return torch.from_numpy(O.row_amax(a_block, True).copy())
+
+        def scatter_attn(a_block, amax_t, col0):
+            assert col0 == blk.col_range[0]
+            codes_block, scales = O.quantize_fp8_act_amax(a_block, amax_t.numpy(), True)
+            gathered = sharding.all_gather_columns(dist, torch.from_numpy(codes_block.astype(np.int32)), blk.col_sizes)
+            return gathered.numpy().astype(np.uint8), scales
+
+        def out_op(codes, scales, col0):
+            a0, b0 = blk.out_range
+            y_block = O.fp8_linear_quantized(codes, scales, out_c[a0:b0], out_s[a0:b0], None, xa[:, a0:b0], O.ACT_NONE)
+            return _as_np(sharding.all_gather_columns(dist, _as_t(y_block), blk.out_sizes))
+
+        y_attn = blk.step(xa, qkv_op, attend_op, amax_op, scatter_attn, out_op)
+        assert np.array_equal(y_attn, y_attn_ref), "the head-split attention block differs from the unsplit one"
     finally:
         dist.destroy_process_group()
 
@@ -109,3 +156,13 @@ def test_shard_ranges_cover_and_align():
         assert max(b - a for a, b in spans) - min(b - a for a, b in spans) <= g
     with pytest.raises(ValueError):
         sharding.column_shard(100, 4, 0, multiple=8)
+    # a fused QKV weight split on head boundaries: every rank the same heads of q, k and v, all rows taken once
+    heads, hd = 24, 128
+    seen = np.zeros(3 * heads * hd, np.int32)
+    for r in range(8):
+        spans = sharding.qkv_head_rows(heads, hd, 8, r)
+        assert len(spans) == 3 and len({b - a for a, b in spans}) == 1 and all(a % hd == 0 and b % hd == 0 for a, b in spans)
+        assert spans[1][0] - spans[0][0] == heads * hd and spans[2][0] - spans[1][0] == heads * hd
+        for a, b in spans:
+            seen[a:b] += 1
+    assert (seen == 1).all()
