@@ -617,7 +617,7 @@ def run_ours(args, wl):
     n_last = wl["gemms"][-1][0]
     affinity = os.sched_getaffinity(0)
     bind_note = bind_to_gpu_numa_node(local)
-    depth = 1 if nsplit else 2   # steps in flight: page-locked buffers each way
+    depth = 1 if nsplit else max(1, args.e2e_depth)   # steps in flight: page-locked buffers each way
     host_xs = [F.Tensor.empty((m, k0), bf, F.Device.CUDA_HOST) for _ in range(depth)]
     host_ys = [F.Tensor.empty((m, n_last), bf, F.Device.CUDA_HOST) for _ in range(depth)]
     os.sched_setaffinity(0, affinity)  # only the allocation (and its first touch) needed the binding
@@ -763,8 +763,8 @@ def run_ours(args, wl):
                     "d2h_bytes_per_step": m * n_last * 2, "steps": e2e_steps, "chunks": chunks,
                     "steps_in_flight": depth, "one_step_at_a_time_ms": e2e_serial_ms,
                     "how": "rows in chunks: uploads on a copy stream (fl_transfer_async), linears per chunk behind "
-                           "fl_transfer_wait, downloads on a second copy stream; outputs allocated per call; step i + 1 is "
-                           "started before the host waits for step i's result (two page-locked buffers each way); "
+                           "fl_transfer_wait, downloads on a second copy stream; outputs allocated per call; the next step is "
+                           "started before the host waits for a step's result (steps_in_flight page-locked buffers each way); "
                            "one_step_at_a_time_ms is the same with one step in flight",
                     "host_memory": bind_note},
             "per_call_alloc": alloc_check,
@@ -1454,6 +1454,7 @@ def main():
                     help="batch: rows sharded, no collective (weak scaling; at N > 1 the line also carries a "
                          "strong_scaling object from the nsplit_fp8 form); nsplit*: one MLP with its weights split by "
                          "output channel (strong scaling): NCCL all-gathers / epilogue pushes in 16 bits / H gathered as e4m3 codes")
+    ap.add_argument("--e2e-depth", type=int, default=2, help="end-to-end leg: steps in flight (page-locked buffers each way)")
     ap.add_argument("--no-strong-scaling", action="store_true", help="leave the strong_scaling object out of a batch run at N > 1")
     ap.add_argument("--blocks", type=int, default=None, help="c4_mmdit_step: run this many blocks instead of 60")
     ap.add_argument("--attention", default="flint", choices=["sdpa", "flint"],
