@@ -67,6 +67,7 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # so (`traffic_source`). None until a capture of that workload exists.
 NCU_TRAFFIC_SOURCE = {
     "c2_mlp": "profiles/gemm_tn_kernel_fp8_c2_mlp.md",
+    "legacy_fp8_matmul": "profiles/gemm_tn_kernel_mixed_legacy_fp8_matmul.md",
     "c1_linear": "profiles/gemm_tn_kernel_fp8_c2_mlp.md",
     "c3_nvfp4_qkv": "profiles/gemm_tn_kernel_nvfp4_c3_qkv.md",
     "skinny_decode": "profiles/skinny_fp8_kernel_decode_1x16384x3072.md",
@@ -81,7 +82,7 @@ def traffic_fields(workload):
 
 
 NCU_TRAFFIC_BYTES = {
-    "c2_mlp": (51.7e6 + 55.0e6 + 164.1e6 + 12.0e6) / 2,  # mean of the up and the down launch
+    "c2_mlp": (51.9e6 + 64.5e6 + 169.5e6 + 14.9e6) / 2,  # mean of the up and the down launch
     "c1_linear": 22.1e6,                                 # the bf16 output stays dirty in L2
     "c3_nvfp4_qkv": 24.0e6 + 25.5e6,
     "skinny_decode": 50.38e6 + 7.0e6,                    # the weight once; the writes are older dirty lines leaving L2
