@@ -587,6 +587,8 @@ void run_gemm(GemmKind kind, int m, int n, int k, const void *a, const void *b, 
   const char *no_sk = std::getenv("FLINT_SM100_NO_STREAM_K");
   g.no_stream_k = (no_sk && no_sk[0] == '1') ? 1 : 0;
   if (!g.no_stream_k) stream_k_workspace(&g);
+  const char *no_st = std::getenv("FLINT_SM100_NO_STAGED_EPILOGUE");
+  g.no_staged_out = (no_st && no_st[0] == '1') ? 1 : 0;
   const char *why = "";
   std::pair<cudaEvent_t, cudaEvent_t> ev{nullptr, nullptr};
   if (g_timing.enabled) {

@@ -1231,7 +1231,7 @@ cudaError_t launch_one(const GemmArgs &a, KernelParams kp, uint64_t row_bytes, c
   OutMaps tout;
   for (int d = 0; d < kMaxGemmOutputs; ++d) tout.at[d] = ta;
   kp.out_staged = 0;
-  if (kp.out_vector && (!kp.residual || (kp.residual_rows == a.m && (reinterpret_cast<uintptr_t>(kp.residual) & 15) == 0 &&
+  if (kp.out_vector && !a.no_staged_out && (!kp.residual || (kp.residual_rows == a.m && (reinterpret_cast<uintptr_t>(kp.residual) & 15) == 0 &&
                                          kp.residual_ld % 8 == 0))) {
     kp.out_staged = 1;
     for (int d = 0; d < kp.num_out && kp.out_staged; ++d) {

@@ -76,6 +76,7 @@ struct GemmArgs {
   uint32_t *sk_counters;
   size_t sk_counter_words;
   int no_stream_k;             // 1: never use the workspace (for tests that compare the two schedules)
+  int no_staged_out;           // 1: results leave by per-lane stores (for measurements that compare the two epilogues)
   cudaStream_t stream;
 };
 
