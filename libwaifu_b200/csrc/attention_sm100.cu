@@ -27,6 +27,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <type_traits>
 
 #include "ptx_sm100.cuh"
@@ -135,6 +136,49 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// Two floats in one 64-bit register, for the two-wide float instructions of sm_100.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float *lo, float *hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(*lo), "=f"(*hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+// 2^x for a pair of exponents x <= 2^kRescaleStep's, without the special-function unit: that unit
+// delivers 16 results a cycle and SM, so the 128 x 128 exponentials of a block would hold it for
+// 1024 cycles; every other pair of a row goes through here instead, on the multiply-add pipes.
+// x = n + f with n = round(x) (the low mantissa bits of x + 1.5 * 2^23) and f in [-0.5, 0.5]; 2^f
+// by a cubic (relative error 7.5e-5, below the 16-bit rounding the probabilities get); n added
+// into the exponent field. Exponents below -126 (masked keys are -inf) give 2^-126 or 0.
+__device__ __forceinline__ void exp2_pair_poly(uint64_t x, float *e0, float *e1) {
+  float x0, x1;
+  f2_unpack(x, &x0, &x1);
+  x = f2_pack(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+  const uint64_t t = f2_add(x, f2_pack(12582912.0f, 12582912.0f));
+  const uint64_t n = f2_add(t, f2_pack(-12582912.0f, -12582912.0f));
+  const uint64_t f = f2_fma(n, f2_pack(-1.0f, -1.0f), x);
+  uint64_t q = f2_fma(f, f2_pack(0.05517162f, 0.05517162f), f2_pack(0.24261113f, 0.24261113f));
+  q = f2_fma(q, f, f2_pack(0.69326097f, 0.69326097f));
+  q = f2_fma(q, f, f2_pack(0.99992806f, 0.99992806f));
+  float q0, q1, t0, t1;
+  f2_unpack(q, &q0, &q1);
+  f2_unpack(t, &t0, &t1);
+  *e0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+  *e1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
 }
 
 // max(a, b, c) in one instruction.
@@ -588,6 +632,390 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   }
 }
 
+// ---- two query tiles per CTA, probabilities in tensor memory -----------------------------------
+//
+// The kernel above reads both operands of both products from shared memory: 8 KB per instruction
+// of 64 cycles is all the bandwidth shared memory has, and the probabilities written there and the
+// K and V blocks arriving there take their share of it. Here a CTA owns two tiles of 128 queries of
+// one head that walk the same keys, and a tile's probabilities never leave tensor memory: the
+// softmax writes them (16-bit pairs, one row per lane) over the first half of the tile's own score
+// buffer, and O += P V takes its A operand from there. Eight softmax warps (four per tile: a thread
+// owns a whole row of a block's scores, so no two threads have to agree on a maximum), one producer
+// warp, one issuing warp. The tiles share the K and V blocks (one ring of equal slots: K0 V0 K1 V1
+// ...); tensor memory holds 2 x (128 + head_dim) <= 512 columns. Per tile the chain is serial
+// (scores -> softmax -> P -> product -> the next scores, which overwrite P); the other tile's
+// chain runs in its gaps.
+constexpr int kTiles = 2;
+constexpr int kTileWarps = 4;
+constexpr int kSoftmaxWarps2 = kTiles * kTileWarps;
+constexpr int kProducerWarp2 = kSoftmaxWarps2;
+constexpr int kMmaWarp2 = kSoftmaxWarps2 + 1;
+constexpr int kThreads2 = (kSoftmaxWarps2 + 2) * 32;
+constexpr int kMaxSlots = 6;
+
+struct Tail2 {
+  uint64_t q_full_bar[kTiles];
+  uint64_t slot_full_bar[kMaxSlots], slot_empty_bar[kMaxSlots];
+  uint64_t s_full_bar[kTiles];   // MMA -> softmax: the tile's scores are in tensor memory
+  uint64_t p_full_bar[kTiles];   // softmax -> MMA: the tile's probabilities are in tensor memory
+  uint64_t pv_done_bar[kTiles];  // MMA -> softmax: the block is in the tile's output
+  uint32_t tmem_base_slot;
+  uint32_t abort_flag;
+};
+
+template <int D>
+struct Layout2 {
+  static constexpr int kQAtoms = D / kAtomElems;
+  static constexpr int kQBytes = kQAtoms * kBlockQ * kAtomBytes;  // one tile's queries
+  static constexpr int kSlotBytes = kQAtoms * kBlockKv * kAtomBytes;  // a block of K: 128 keys x head_dim
+  static constexpr int kVAtoms = kBlockKv / kAtomElems;
+  static constexpr int kVAtomBytes = D * kAtomBytes;
+  static_assert(kVAtoms * kVAtomBytes == kSlotBytes, "a block of V^T fills a slot exactly as a block of K does");
+  static constexpr int kRoom = (227 * 1024 - kTiles * kQBytes - static_cast<int>(sizeof(Tail2))) / kSlotBytes;
+  static constexpr int kSlots = kRoom < kMaxSlots ? kRoom : kMaxSlots;
+  static_assert(kSlots >= 3, "K of the next block, V of this one and a load in flight");
+  static constexpr int kQOff = 0;
+  static constexpr int kSlotOff = kQOff + kTiles * kQBytes;
+  static constexpr int kTailOff = kSlotOff + kSlots * kSlotBytes;
+  static constexpr int kSmemBytes = kTailOff + static_cast<int>(sizeof(Tail2));
+  static constexpr int kSCols = kBlockKv;           // tile t's scores at column t * kSCols, its P over their first half
+  static constexpr int kOCol = kTiles * kSCols;     // tile t's output at kOCol + t * D
+  static constexpr int kTmemCols = 512;
+  static_assert(kOCol + kTiles * D <= kTmemCols, "tensor memory holds 512 columns");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory");
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads2, 1)
+attention2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                  const __grid_constant__ CUtensorMap tmap_vt, const KernelParams p) {
+  using L = Layout2<D>;
+  constexpr int S = L::kSlots;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  Tail2 &t = *reinterpret_cast<Tail2 *>(smem + L::kTailOff);
+  volatile uint32_t &abort_flag = *reinterpret_cast<volatile uint32_t *>(&t.abort_flag);
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0u, kStatusAttentionLayout);
+    return;
+  }
+  const int q0 = blockIdx.x * (kTiles * kBlockQ);
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int kv_head = head / p.group;
+  const int offset = p.kv_len - p.q_len;
+  // Both tiles walk the blocks of keys that some query of the CTA sees; a block none of a tile's
+  // queries sees costs that tile a block of zero probabilities.
+  const int last_row = min(q0 + kTiles * kBlockQ, p.q_len) - 1;
+  const int kv_begin = first_key_of(p, q0 + offset);
+  const int kv_end = last_key_of(p, last_row + offset) + 1;
+  const int block0 = kv_begin / kBlockKv;
+  const int num_blocks = (kv_end + kBlockKv - 1) / kBlockKv - block0;
+
+  if (threadIdx.x == 0) {
+    t.abort_flag = 0;
+    for (int i = 0; i < S; ++i) {
+      mbar_init(&t.slot_full_bar[i], 1);
+      mbar_init(&t.slot_empty_bar[i], 1);
+    }
+    for (int i = 0; i < kTiles; ++i) {
+      mbar_init(&t.q_full_bar[i], 1);
+      mbar_init(&t.s_full_bar[i], 1);
+      mbar_init(&t.p_full_bar[i], kTileWarps);
+      mbar_init(&t.pv_done_bar[i], 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == kProducerWarp2 && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_vt);
+  }
+  if (warp == kMmaWarp2) {
+    tmem_alloc<1>(&t.tmem_base_slot, L::kTmemCols);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = t.tmem_base_slot;
+
+  auto q_tile = [&](int i) { return smem + L::kQOff + i * L::kQBytes; };
+  auto slot = [&](int i) { return smem + L::kSlotOff + i * L::kSlotBytes; };
+
+  // Load n of the ring (K of block n / 2 when n is even, V of it when odd) goes to slot n % S.
+  if (warp == kProducerWarp2) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      bool ok = true;
+      for (int i = 0; i < kTiles; ++i) {
+        mbar_arrive_expect_tx(&t.q_full_bar[i], L::kQBytes);
+#pragma unroll
+        for (int a = 0; a < L::kQAtoms; ++a) {
+          tma_load_4d(q_tile(i) + a * kBlockQ * kAtomBytes, &tmap_q, &t.q_full_bar[i], a * kAtomBytes, q0 + i * kBlockQ, head,
+                      batch);
+        }
+      }
+      for (int n = 0; n < 2 * num_blocks && ok; ++n) {
+        const int st = n % S, j = n >> 1;
+        if (!mbar_wait(&t.slot_empty_bar[st], ((n / S) & 1) ^ 1, &abort_flag)) {
+          ok = false;
+          break;
+        }
+        mbar_arrive_expect_tx(&t.slot_full_bar[st], L::kSlotBytes);
+        if ((n & 1) == 0) {
+#pragma unroll
+          for (int a = 0; a < L::kQAtoms; ++a) {
+            tma_load_4d(slot(st) + a * kBlockKv * kAtomBytes, &tmap_k, &t.slot_full_bar[st], a * kAtomBytes,
+                        (block0 + j) * kBlockKv, kv_head, batch);
+          }
+        } else {
+#pragma unroll
+          for (int a = 0; a < L::kVAtoms; ++a) {
+            tma_load_3d(slot(st) + a * L::kVAtomBytes, &tmap_vt, &t.slot_full_bar[st],
+                        ((block0 + j) * kBlockKv + a * kAtomElems) * 2, 0, batch * p.kv_heads + kv_head);
+          }
+        }
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(p.status, 0u, kStatusAttentionTimeout);
+      }
+    }
+  } else if (warp == kMmaWarp2) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t fmt = p.is_bf16 ? 1u : 0u;
+      const uint32_t idesc_s = umma_idesc(kBlockQ, kBlockKv, fmt, fmt);
+      const uint32_t idesc_o = umma_idesc(kBlockQ, D, fmt, fmt);
+      constexpr uint64_t kMmaStep = kMmaKBytes >> 4;
+      constexpr int kMmasPerAtom = kAtomBytes / kMmaKBytes;
+      constexpr int kScoreMmas = L::kQAtoms * kMmasPerAtom;
+      constexpr int kOutMmas = L::kVAtoms * kMmasPerAtom;  // one per 16 keys: 8 columns of P each
+      const uint64_t qdesc0 = umma_desc_sw128(smem_u32(q_tile(0)));
+      const uint64_t sdesc0 = umma_desc_sw128(smem_u32(slot(0)));
+      bool ok = true;
+      auto scores = [&](int i, uint64_t kd) {  // S_i = Q_i K^T
+        const uint32_t s_tmem = tmem_base + i * L::kSCols;
+        const uint64_t qd = qdesc0 + static_cast<uint64_t>(i * (L::kQBytes >> 4));
+#pragma unroll
+        for (int m = 0; m < kScoreMmas; ++m) {
+          const int a = m / kMmasPerAtom, s = m % kMmasPerAtom;
+          umma_ss<kKindF16>(s_tmem, qd + (((a * kBlockQ * kAtomBytes) >> 4) + s * kMmaStep),
+                            kd + (((a * kBlockKv * kAtomBytes) >> 4) + s * kMmaStep), idesc_s, m != 0 ? 1u : 0u);
+        }
+      };
+      auto product = [&](int i, uint64_t vd, uint32_t first_block) {  // O_i += P_i V
+        const uint32_t o_tmem = tmem_base + L::kOCol + i * D;
+        const uint32_t p_tmem = tmem_base + i * L::kSCols;
+#pragma unroll
+        for (int m = 0; m < kOutMmas; ++m) {
+          const int a = m / kMmasPerAtom, s = m % kMmasPerAtom;
+          umma_ts_f16(o_tmem, p_tmem + m * 8, vd + (((a * L::kVAtomBytes) >> 4) + s * kMmaStep), idesc_o,
+                      m != 0 ? 1u : (first_block ^ 1u));
+        }
+      };
+      auto wait_full = [&](int n) -> bool { return mbar_wait(&t.slot_full_bar[n % S], (n / S) & 1, &abort_flag); };
+      auto desc_of = [&](int n) -> uint64_t { return sdesc0 + static_cast<uint64_t>((n % S) * (L::kSlotBytes >> 4)); };
+      for (int i = 0; i < kTiles && ok; ++i) ok = mbar_wait(&t.q_full_bar[i], 0, &abort_flag);
+      if (ok && num_blocks > 0) ok = wait_full(0);
+      if (ok && num_blocks > 0) {
+        tc_fence_after_sync();
+        for (int i = 0; i < kTiles; ++i) {
+          scores(i, desc_of(0));
+          umma_commit(&t.s_full_bar[i]);
+        }
+        umma_commit(&t.slot_empty_bar[0]);
+      }
+      for (int j = 0; j < num_blocks && ok; ++j) {
+        const bool more = j + 1 < num_blocks;
+        const int nv = 2 * j + 1, nk = 2 * j + 2;
+        const uint32_t first_block = j == 0 ? 1u : 0u;
+        for (int i = 0; i < kTiles && ok; ++i) {
+          if (!mbar_wait(&t.p_full_bar[i], j & 1, &abort_flag) || !wait_full(nv) || (more && !wait_full(nk))) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          // The product reads P from the columns the next scores overwrite: the instructions of one
+          // thread run in the order they were issued.
+          product(i, desc_of(nv), first_block);
+          umma_commit(&t.pv_done_bar[i]);
+          if (more) {
+            scores(i, desc_of(nk));
+            umma_commit(&t.s_full_bar[i]);
+          }
+          if (i == kTiles - 1) {  // both tiles have read the two slots
+            umma_commit(&t.slot_empty_bar[nv % S]);
+            if (more) umma_commit(&t.slot_empty_bar[nk % S]);
+          }
+        }
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(p.status, 0u, kStatusAttentionTimeout);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax and output
+    const int tile = static_cast<int>(warp >> 2);
+    const uint32_t quarter = warp & 3;
+    const int tq0 = q0 + tile * kBlockQ;  // the tile's first query
+    const int row = static_cast<int>(quarter) * 32 + static_cast<int>(lane);
+    const int q_pos = tq0 + row + offset;
+    const int key_first = first_key_of(p, q_pos), key_last = last_key_of(p, q_pos);
+    const int tile_last_row = min(tq0 + kBlockQ, p.q_len) - 1;
+    // What every query of the tile sees (an empty range for a tile past the last query: every block
+    // is then an edge block, and nothing of it is stored).
+    const int common_first = first_key_of(p, tile_last_row + offset), common_last = last_key_of(p, tq0 + offset);
+    const uint32_t t_lane = tmem_base + ((quarter * 32u) << 16);
+    const uint32_t t_scores = t_lane + tile * L::kSCols;  // the row's 128 scores, then its 128 probabilities in 64 columns
+    const uint32_t t_out = t_lane + L::kOCol + tile * D;
+    constexpr int kChunks = kBlockKv / 32;
+    static_assert(kChunks == 4, "four chunks of scores pack into the first two");
+    constexpr float kRescaleStep = 8.0f;
+    float m_used = -INFINITY;
+    float l_run = 0.0f;
+    bool ok = true;
+    uint32_t sc[kChunks][32];
+
+    for (int j = 0; j < num_blocks && ok; ++j) {
+      // The row's scores of the block into registers in one round trip. (Scores of block j are
+      // issued behind the product of block j - 1: once they are here the tile's output is complete
+      // up to that block.)
+      ok = __all_sync(0xffffffffu, mbar_wait(&t.s_full_bar[tile], j & 1, &abort_flag));
+      if (!ok) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) tmem_ld_32x32(t_scores + c * 32, sc[c]);
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) tmem_ld_wait(sc[c]);
+      const int block_key0 = (block0 + j) * kBlockKv;
+      const bool edge = block_key0 < common_first || block_key0 + kBlockKv - 1 > common_last;
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (edge) {
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = block_key0 + c * 32 + i;
+            if (key > key_last || key < key_first) sc[c][i] = __float_as_uint(-INFINITY);
+          }
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], __uint_as_float(sc[c][i]), __uint_as_float(sc[c][i + 1]));
+        }
+      }
+      const float m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
+      if (__any_sync(0xffffffffu, m_blk > m_used + kRescaleStep)) {
+        const float m_new = fmaxf(m_used, m_blk);
+        const float alpha = exp2f(m_used - ((m_new == -INFINITY) ? 0.0f : m_new));
+        l_run *= alpha;
+        if (j > 0) {
+#pragma unroll 1
+          for (int c = 0; c < D / 16; ++c) {  // sixteen columns at a time: the block's scores stay in registers
+            uint32_t v[16];
+            tmem_ld_32x16(t_out + c * 16, v);
+            tmem_ld_wait(v);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x16(t_out + c * 16, v);
+          }
+        }
+        m_used = m_new;
+      }
+      const float m_sub = (m_used == -INFINITY) ? 0.0f : m_used;
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      // The probabilities, packed in place: pair i of the row's keys becomes column i of its P
+      // (a slot whose scores have been used by then).
+      const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), neg_m2 = f2_pack(-m_sub, -m_sub);
+      auto emit = [&](auto bf16_tag) {
+        constexpr int kBf16 = decltype(bf16_tag)::value ? 1 : 0;
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const uint64_t x = f2_fma(f2_pack(__uint_as_float(sc[c][i]), __uint_as_float(sc[c][i + 1])), scale2, neg_m2);
+            float e0, e1;
+            if ((i & 2) == 0) {  // pairs take turns between the special-function unit and the cubic
+              float x0, x1;
+              f2_unpack(x, &x0, &x1);
+              e0 = fast_exp2(x0);
+              e1 = fast_exp2(x1);
+            } else {
+              exp2_pair_poly(x, &e0, &e1);
+            }
+            sum4[(i >> 1) & 3] += e0 + e1;
+            sc[c >> 1][(c & 1) * 16 + (i >> 1)] = pack16(e0, e1, kBf16);
+          }
+        }
+      };
+      if (p.is_bf16) {
+        emit(std::true_type{});
+      } else {
+        emit(std::false_type{});
+      }
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      tmem_st_32x32(t_scores, sc[0]);
+      tmem_st_32x32(t_scores + 32, sc[1]);
+      tmem_st_wait();          // the probabilities and a rescaled output are in tensor memory
+      tc_fence_before_sync();  // before the MMAs that the hand-over starts
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&t.p_full_bar[tile]);
+    }
+    // The last product.
+    if (ok && num_blocks > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&t.pv_done_bar[tile], (num_blocks - 1) & 1, &abort_flag));
+      tc_fence_after_sync();
+    }
+    if (ok) {
+      const bool live = tq0 + row < p.q_len;
+      const float inv = 1.0f / l_run;
+      uint16_t *dst = reinterpret_cast<uint16_t *>(p.out) + batch * p.out_stride[0] + head * p.out_stride[1] +
+                      static_cast<int64_t>(tq0 + row) * p.out_stride[2];
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_out + c * 32, v);
+        tmem_ld_wait(v);
+        if (live) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = pack16(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv, p.is_bf16);
+            w.y = pack16(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv, p.is_bf16);
+            w.z = pack16(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv, p.is_bf16);
+            w.w = pack16(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv, p.is_bf16);
+            *reinterpret_cast<uint4 *>(dst + c * 32 + g * 8) = w;
+          }
+        }
+      }
+    }
+    if (!ok && lane == 0) {
+      abort_flag = 1;
+      atomicCAS(p.status, 0u, kStatusAttentionTimeout);
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (abort_flag != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    __syncthreads();
+  }
+  if (warp == kMmaWarp2) {
+    tc_fence_after_sync();
+    tmem_dealloc<1>(tmem_base, L::kTmemCols);
+  }
+}
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -642,6 +1070,27 @@ cudaError_t launch(const AttentionArgs &a, const CUtensorMap &tq, const CUtensor
   const dim3 grid(static_cast<unsigned>((a.q_len + kBlockQ - 1) / kBlockQ), static_cast<unsigned>(a.heads),
                   static_cast<unsigned>(a.batch));
   kernel<<<grid, kThreads, L::kSmemBytes, a.stream>>>(tq, tk, tvt, kp);
+  return cudaGetLastError();
+}
+
+template <int D>
+cudaError_t launch2(const AttentionArgs &a, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tvt,
+                    const KernelParams &kp, const char **why) {
+  using L = Layout2<D>;
+  auto kernel = attention2_kernel<D>;
+  static bool attr_set = false;  // per instantiation
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes);
+    if (e != cudaSuccess) {
+      *why = "cudaFuncSetAttribute(max dynamic shared memory) failed";
+      return e;
+    }
+    attr_set = true;
+  }
+  const int per_cta = kTiles * kBlockQ;
+  const dim3 grid(static_cast<unsigned>((a.q_len + per_cta - 1) / per_cta), static_cast<unsigned>(a.heads),
+                  static_cast<unsigned>(a.batch));
+  kernel<<<grid, kThreads2, L::kSmemBytes, a.stream>>>(tq, tk, tvt, kp);
   return cudaGetLastError();
 }
 
@@ -752,8 +1201,20 @@ cudaError_t attention(const AttentionArgs &a, const char **why) {
   kp.kv_len = a.kv_len;
   kp.mask_type = a.mask_type;
   kp.block_size = a.block_size;
+  if (a.mask_type >= 2 && a.block_size >= a.kv_len) {  // one block holds every key: no mask at all
+    kp.mask_type = 0;
+    kp.block_size = 0;
+  }
   kp.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(d));
   kp.status = a.status;
+  // Two tiles of queries per CTA where a head has more than one tile of them; the block diagonal
+  // mask, whose tiles see different keys, and short query runs keep one tile per CTA.
+  static const bool one_tile_only = [] {
+    const char *e = std::getenv("FLINT_SM100_ATTENTION_ONE_TILE");
+    return e && e[0] == '1';
+  }();
+  const bool two_tiles = a.q_len > kBlockQ && kp.mask_type != 3 && !one_tile_only;
+  if (two_tiles) return d == 64 ? launch2<64>(a, tq, tk, tvt, kp, why) : launch2<128>(a, tq, tk, tvt, kp, why);
   if (d == 64) return launch<64>(a, tq, tk, tvt, kp, why);
   return launch<128>(a, tq, tk, tvt, kp, why);
 }
