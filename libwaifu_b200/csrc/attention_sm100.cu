@@ -101,6 +101,7 @@ struct KernelParams {
   int mask_type;   // 0 none, 1 causal, 2 block causal, 3 block diagonal (flint/capi.h:118-133)
   int block_size;
   float scale_log2;
+  int v_direct;  // two-tile kernel: v is read as it lies (an MN-major operand), not through its transposition
   uint32_t *status;
 };
 
@@ -771,6 +772,12 @@ attention2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             tma_load_4d(slot(st) + a * kBlockKv * kAtomBytes, &tmap_k, &t.slot_full_bar[st], a * kAtomBytes,
                         (block0 + j) * kBlockKv, kv_head, batch);
           }
+        } else if (p.v_direct) {  // v like k: 128 keys x 64 elements of head_dim per atom
+#pragma unroll
+          for (int a = 0; a < L::kQAtoms; ++a) {
+            tma_load_4d(slot(st) + a * kBlockKv * kAtomBytes, &tmap_vt, &t.slot_full_bar[st], a * kAtomBytes,
+                        (block0 + j) * kBlockKv, kv_head, batch);
+          }
         } else {
 #pragma unroll
           for (int a = 0; a < L::kVAtoms; ++a) {
@@ -807,14 +814,27 @@ attention2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
                             kd + (((a * kBlockKv * kAtomBytes) >> 4) + s * kMmaStep), idesc_s, m != 0 ? 1u : 0u);
         }
       };
+      // With v as it lies, a slot's rows are keys: an instruction's 16 keys are 16 rows of 128 bytes
+      // on, the operand is MN-major (bit 16 of the instruction descriptor) and its runs of 64
+      // head_dim positions lie a 128-key atom apart.
+      const uint32_t idesc_o_mn = idesc_o | (1u << 16);
+      const uint64_t mn_fields = umma_desc_sw128_mn(0, kBlockKv * kAtomBytes) ^ umma_desc_sw128(0);
       auto product = [&](int i, uint64_t vd, uint32_t first_block) {  // O_i += P_i V
         const uint32_t o_tmem = tmem_base + L::kOCol + i * D;
         const uint32_t p_tmem = tmem_base + i * L::kSCols;
+        if (p.v_direct) {
 #pragma unroll
-        for (int m = 0; m < kOutMmas; ++m) {
-          const int a = m / kMmasPerAtom, s = m % kMmasPerAtom;
-          umma_ts_f16(o_tmem, p_tmem + m * 8, vd + (((a * L::kVAtomBytes) >> 4) + s * kMmaStep), idesc_o,
-                      m != 0 ? 1u : (first_block ^ 1u));
+          for (int m = 0; m < kOutMmas; ++m) {
+            umma_ts_f16(o_tmem, p_tmem + m * 8, (vd ^ mn_fields) + static_cast<uint64_t>(m * ((16 * kAtomBytes) >> 4)), idesc_o_mn,
+                        m != 0 ? 1u : (first_block ^ 1u));
+          }
+        } else {
+#pragma unroll
+          for (int m = 0; m < kOutMmas; ++m) {
+            const int a = m / kMmasPerAtom, s = m % kMmasPerAtom;
+            umma_ts_f16(o_tmem, p_tmem + m * 8, vd + (((a * L::kVAtomBytes) >> 4) + s * kMmaStep), idesc_o,
+                        m != 0 ? 1u : (first_block ^ 1u));
+          }
         }
       };
       auto wait_full = [&](int n) -> bool { return mbar_wait(&t.slot_full_bar[n % S], (n / S) & 1, &abort_flag); };
@@ -1144,19 +1164,56 @@ cudaError_t attention(const AttentionArgs &a, const char **why) {
   const int d = a.head_dim;
   const int kv_pad = round_up(a.kv_len, kPadKv);
 
-  const dim3 tgrid(static_cast<unsigned>(kv_pad / 64), static_cast<unsigned>(d / 64),
-                   static_cast<unsigned>(a.batch * a.kv_heads));
-  transpose_v_kernel<<<tgrid, 256, 0, a.stream>>>(reinterpret_cast<const uint16_t *>(a.v), a.v_stride[0], a.v_stride[1],
-                                                  a.v_stride[2], a.kv_heads, a.kv_len, kv_pad, d,
-                                                  reinterpret_cast<uint16_t *>(a.v_transposed));
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) {
-    *why = "launching the transposition of v";
-    return e;
+  KernelParams kp = {};
+  kp.out = a.out;
+  for (int i = 0; i < 3; ++i) kp.out_stride[i] = a.out_stride[i];
+  kp.is_bf16 = a.is_bf16;
+  kp.heads = a.heads;
+  kp.kv_heads = a.kv_heads;
+  kp.group = a.heads / a.kv_heads;
+  kp.q_len = a.q_len;
+  kp.kv_len = a.kv_len;
+  kp.mask_type = a.mask_type;
+  kp.block_size = a.block_size;
+  if (a.mask_type >= 2 && a.block_size >= a.kv_len) {  // one block holds every key: no mask at all
+    kp.mask_type = 0;
+    kp.block_size = 0;
+  }
+  kp.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(d));
+  kp.status = a.status;
+  // Two tiles of queries per CTA where a head has more than one tile of them; the block diagonal
+  // mask, whose tiles see different keys, and short query runs keep one tile per CTA.
+  static const bool one_tile_only = [] {
+    const char *e = std::getenv("FLINT_SM100_ATTENTION_ONE_TILE");
+    return e && e[0] == '1';
+  }();
+  static const bool transposed_v_only = [] {
+    const char *e = std::getenv("FLINT_SM100_ATTENTION_TRANSPOSED_V");
+    return e && e[0] == '1';
+  }();
+  const bool two_tiles = a.q_len > kBlockQ && kp.mask_type != 3 && !one_tile_only;
+  // The two-tile kernel reads v as it lies (a tensor map like k's, the operand MN-major) unless v
+  // repeats a dimension through a stride of 0, which only the transposing kernel can follow.
+  const int v_extent[3] = {a.batch, a.kv_heads, a.kv_len};
+  bool v_plain = true;
+  for (int i = 0; i < 3; ++i) v_plain = v_plain && !(v_extent[i] > 1 && a.v_stride[i] == 0);
+  kp.v_direct = (two_tiles && v_plain && !transposed_v_only) ? 1 : 0;
+
+  if (!kp.v_direct) {
+    const dim3 tgrid(static_cast<unsigned>(kv_pad / 64), static_cast<unsigned>(d / 64),
+                     static_cast<unsigned>(a.batch * a.kv_heads));
+    transpose_v_kernel<<<tgrid, 256, 0, a.stream>>>(reinterpret_cast<const uint16_t *>(a.v), a.v_stride[0], a.v_stride[1],
+                                                    a.v_stride[2], a.kv_heads, a.kv_len, kv_pad, d,
+                                                    reinterpret_cast<uint16_t *>(a.v_transposed));
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      *why = "launching the transposition of v";
+      return e;
+    }
   }
 
-  // q and k as (head_dim bytes, positions, heads, batch); a size-1 dimension's stride is never used
-  // but has to pass the encoder's checks.
+  // q, k (and v as it lies) as (head_dim bytes, positions, heads, batch); a size-1 dimension's
+  // stride is never used but has to pass the encoder's checks.
   auto dims4 = [&](int len, int heads, uint64_t *dims) {
     dims[0] = static_cast<uint64_t>(d) * 2;
     dims[1] = static_cast<uint64_t>(len);
@@ -1182,38 +1239,21 @@ cudaError_t attention(const AttentionArgs &a, const char **why) {
     *why = "cuTensorMapEncodeTiled refused k";
     return cudaErrorInvalidValue;
   }
-  uint64_t vdims[3] = {static_cast<uint64_t>(kv_pad) * 2, static_cast<uint64_t>(d),
-                       static_cast<uint64_t>(a.batch) * a.kv_heads};
-  uint64_t vstrides[2] = {static_cast<uint64_t>(kv_pad) * 2, static_cast<uint64_t>(d) * kv_pad * 2};
-  if (!make_tmap(&tvt, a.v_transposed, 3, vdims, vstrides, static_cast<uint32_t>(d))) {
-    *why = "cuTensorMapEncodeTiled refused the transposed v";
-    return cudaErrorInvalidValue;
+  if (kp.v_direct) {
+    strides4(a.v_stride, strides);
+    if (!make_tmap(&tvt, a.v, 4, dims, strides, kBlockKv)) {
+      *why = "cuTensorMapEncodeTiled refused v";
+      return cudaErrorInvalidValue;
+    }
+  } else {
+    uint64_t vdims[3] = {static_cast<uint64_t>(kv_pad) * 2, static_cast<uint64_t>(d),
+                         static_cast<uint64_t>(a.batch) * a.kv_heads};
+    uint64_t vstrides[2] = {static_cast<uint64_t>(kv_pad) * 2, static_cast<uint64_t>(d) * kv_pad * 2};
+    if (!make_tmap(&tvt, a.v_transposed, 3, vdims, vstrides, static_cast<uint32_t>(d))) {
+      *why = "cuTensorMapEncodeTiled refused the transposed v";
+      return cudaErrorInvalidValue;
+    }
   }
-
-  KernelParams kp = {};
-  kp.out = a.out;
-  for (int i = 0; i < 3; ++i) kp.out_stride[i] = a.out_stride[i];
-  kp.is_bf16 = a.is_bf16;
-  kp.heads = a.heads;
-  kp.kv_heads = a.kv_heads;
-  kp.group = a.heads / a.kv_heads;
-  kp.q_len = a.q_len;
-  kp.kv_len = a.kv_len;
-  kp.mask_type = a.mask_type;
-  kp.block_size = a.block_size;
-  if (a.mask_type >= 2 && a.block_size >= a.kv_len) {  // one block holds every key: no mask at all
-    kp.mask_type = 0;
-    kp.block_size = 0;
-  }
-  kp.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(d));
-  kp.status = a.status;
-  // Two tiles of queries per CTA where a head has more than one tile of them; the block diagonal
-  // mask, whose tiles see different keys, and short query runs keep one tile per CTA.
-  static const bool one_tile_only = [] {
-    const char *e = std::getenv("FLINT_SM100_ATTENTION_ONE_TILE");
-    return e && e[0] == '1';
-  }();
-  const bool two_tiles = a.q_len > kBlockQ && kp.mask_type != 3 && !one_tile_only;
   if (two_tiles) return d == 64 ? launch2<64>(a, tq, tk, tvt, kp, why) : launch2<128>(a, tq, tk, tvt, kp, why);
   if (d == 64) return launch<64>(a, tq, tk, tvt, kp, why);
   return launch<128>(a, tq, tk, tvt, kp, why);

@@ -271,6 +271,19 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// The same tile read as an MN-major operand: its rows are K positions and a row's 128 bytes are 64
+// consecutive M or N positions; `atom_stride` bytes lie between one such run of 64 and the next.
+// (The instruction descriptor says which operand is read that way: bit 15 for A, bit 16 for B.)
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr, uint32_t atom_stride) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
+  d |= static_cast<uint64_t>((atom_stride >> 4) & 0x3fff) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
 // Descriptor of an unswizzled run of 32 rows x 16 bytes (8-row groups 128 bytes apart): the
 // source of the scale-factor copy into tensor memory.
 __device__ __forceinline__ uint64_t umma_desc_sf(uint32_t smem_addr) {
