@@ -161,7 +161,9 @@ __device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
 
 // 2^x for a pair of exponents x <= 2^kRescaleStep's, without the special-function unit: that unit
 // delivers 16 results a cycle and SM, so the 128 x 128 exponentials of a block would hold it for
-// 1024 cycles; every other pair of a row goes through here instead, on the multiply-add pipes.
+// 1024 cycles; one pair in four of a row goes through here instead, on the multiply-add pipes
+// (with one softmax warp per scheduler at work at a time, more than that costs more issue slots
+// than it frees special-function cycles).
 // x = n + f with n = round(x) (the low mantissa bits of x + 1.5 * 2^23) and f in [-0.5, 0.5]; 2^f
 // by a cubic (relative error 7.5e-5, below the 16-bit rounding the probabilities get); n added
 // into the exponent field. Exponents below -126 (masked keys are -inf) give 2^-126 or 0.
@@ -854,7 +856,8 @@ attention2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         const int nv = 2 * j + 1, nk = 2 * j + 2;
         const uint32_t first_block = j == 0 ? 1u : 0u;
         for (int i = 0; i < kTiles && ok; ++i) {
-          if (!mbar_wait(&t.p_full_bar[i], j & 1, &abort_flag) || !wait_full(nv) || (more && !wait_full(nk))) {
+          // (The second tile reads the slots the first one has just been seen to wait for.)
+          if (!mbar_wait(&t.p_full_bar[i], j & 1, &abort_flag) || (i == 0 && (!wait_full(nv) || (more && !wait_full(nk))))) {
             ok = false;
             break;
           }
@@ -862,7 +865,7 @@ attention2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           // The product reads P from the columns the next scores overwrite: the instructions of one
           // thread run in the order they were issued.
           product(i, desc_of(nv), first_block);
-          umma_commit(&t.pv_done_bar[i]);
+          if (!more) umma_commit(&t.pv_done_bar[i]);  // (a block's scores, which the softmax waits for, follow its product)
           if (more) {
             scores(i, desc_of(nk));
             umma_commit(&t.s_full_bar[i]);
@@ -963,7 +966,7 @@ attention2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           for (int i = 0; i < 32; i += 2) {
             const uint64_t x = f2_fma(f2_pack(__uint_as_float(sc[c][i]), __uint_as_float(sc[c][i + 1])), scale2, neg_m2);
             float e0, e1;
-            if ((i & 2) == 0) {  // pairs take turns between the special-function unit and the cubic
+            if ((i & 6) != 6) {  // one pair in four goes through the cubic, the others through the special-function unit
               float x0, x1;
               f2_unpack(x, &x0, &x1);
               e0 = fast_exp2(x0);
@@ -991,7 +994,7 @@ attention2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     }
     // The last product.
     if (ok && num_blocks > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(&t.pv_done_bar[tile], (num_blocks - 1) & 1, &abort_flag));
+      ok = __all_sync(0xffffffffu, mbar_wait(&t.pv_done_bar[tile], 0, &abort_flag));
       tc_fence_after_sync();
     }
     if (ok) {
