@@ -39,6 +39,10 @@ struct fl_tensor_data_impl_t {
   bool pooled = false;
   bool resident = false;
   cudaStream_t stream = nullptr;
+  // The stream a pooled block was taken on when that is not the compute stream (an upload's
+  // destination is taken on the copy stream): it goes back in that stream's order, behind the
+  // compute stream's last use, so that the next upload finds it free without the pool growing.
+  cudaStream_t home = nullptr;
 };
 
 // flint/capi.cc:530-535: the event that marks the end of a copy, and the storage it fills.
@@ -162,10 +166,37 @@ struct DeviceState {
   // (zero between launches). Made once, on the first GEMM, and kept.
   float *sk_partials = nullptr;
   uint32_t *sk_counters = nullptr;
+  // Upload destinations on their way back to the pool: a block taken on the copy stream goes back
+  // in that stream's order (so that the next upload reuses it at once), but only after the compute
+  // stream's last use of it has completed, which `used` marks; nothing waits, the list is swept
+  // at the next upload or release.
+  struct Returning {
+    void *ptr;
+    cudaEvent_t used;
+    cudaStream_t home;
+  };
+  std::vector<Returning> returning;
 };
 
 std::mutex g_mutex;
 DeviceState g_dev;
+
+// Gives back every block of the list whose last use has completed (all of them when `all`: the
+// caller has synchronised the compute stream). Called with g_mutex held.
+void sweep_returning_locked(bool all) {
+  size_t kept = 0;
+  for (size_t i = 0; i < g_dev.returning.size(); ++i) {
+    DeviceState::Returning r = g_dev.returning[i];
+    if (all || cudaEventQuery(r.used) == cudaSuccess) {
+      cudaEventDestroy(r.used);
+      cudaFreeAsync(r.ptr, r.home);
+    } else {
+      g_dev.returning[kept++] = r;
+    }
+  }
+  cudaGetLastError();  // cudaErrorNotReady from a query is not an error of ours
+  g_dev.returning.resize(kept);
+}
 std::atomic<int64_t> g_gemm_launches{0};
 std::atomic<int64_t> g_block_launches{0};  // kernels of block_sm100.cu
 
@@ -227,6 +258,20 @@ void ensure_pool() {
   uint64_t threshold = UINT64_MAX;
   cuda_check(cudaDeviceGetDefaultMemPool(&pool, dev), "cudaDeviceGetDefaultMemPool");
   cuda_check(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold), "cudaMemPoolSetAttribute");
+  // One contiguous reserve to start from (FLINT_SM100_POOL_RESERVE_MB, default 1024, 0 for none):
+  // a pool that has grown piece by piece serves a 30 MB block by mapping more memory even when it
+  // holds enough in pieces, which costs tens of microseconds a call and, now and then, tens of
+  // milliseconds; taken and given back once, the reserve stays with the pool.
+  size_t reserve_mb = 1024;
+  if (const char *e = std::getenv("FLINT_SM100_POOL_RESERVE_MB")) reserve_mb = static_cast<size_t>(std::strtoull(e, nullptr, 10));
+  if (reserve_mb > 0) {
+    void *p = nullptr;
+    if (cudaMallocAsync(&p, reserve_mb << 20, 0) == cudaSuccess) {
+      cudaFreeAsync(p, 0);
+    } else {
+      cudaGetLastError();  // a card too full for the reserve runs without it
+    }
+  }
   g_dev.pool_ready = true;
 }
 
@@ -781,7 +826,20 @@ void fl_tensor_data_destroy(fl_tensor_data_t data) {
         // In the order of the stream that last owned the bytes, so nothing waits; a weight's own
         // memory goes back with cudaFree, which waits for the device (flint/cuda/cuda_tensor_data.cc:62-77).
         if (data->pooled) {
-          cudaFreeAsync(data->ptr, data->stream);
+          if (data->home && data->home != data->stream) {
+            cudaEvent_t used = nullptr;
+            if (cudaEventCreateWithFlags(&used, cudaEventDisableTiming) == cudaSuccess &&
+                cudaEventRecord(used, data->stream) == cudaSuccess) {
+              std::lock_guard<std::mutex> lock(g_mutex);
+              g_dev.returning.push_back({data->ptr, used, data->home});
+              sweep_returning_locked(false);
+            } else {
+              if (used) cudaEventDestroy(used);
+              cudaFreeAsync(data->ptr, data->stream);
+            }
+          } else {
+            cudaFreeAsync(data->ptr, data->stream);
+          }
         } else {
           cudaFree(data->ptr);
         }
@@ -885,6 +943,10 @@ int32_t fl_transfer_async(fl_tensor_view_t src_h, fl_device_type_t device, fl_te
     cudaStream_t stream = copy_stream(/*upload=*/true);
     const int64_t numel = numel_of(src);
     const size_t bytes = static_cast<size_t>(numel * dtype_size(dtype_of(src)));
+    {
+      std::lock_guard<std::mutex> lock(g_mutex);
+      sweep_returning_locked(false);
+    }
     void *p = nullptr;
     cuda_check(cudaMallocAsync(&p, bytes ? bytes : 1, stream), "cudaMallocAsync");
     auto *d = new fl_tensor_data_impl_t();
@@ -895,6 +957,7 @@ int32_t fl_transfer_async(fl_tensor_view_t src_h, fl_device_type_t device, fl_te
     d->owned = true;
     d->pooled = true;
     d->stream = stream;  // until the transfer is waited on, the copy stream owns the bytes
+    d->home = stream;
     auto *t = new fl_transfer_impl_t();
     t->dest = d;
     cudaError_t e = bytes ? cudaMemcpyAsync(p, raw_ptr(src), bytes, cudaMemcpyHostToDevice, stream) : cudaSuccess;
@@ -2307,6 +2370,7 @@ int32_t fl_sm100_synchronize(int32_t *kernel_status) {
     uint32_t code = 0;
     {
       std::lock_guard<std::mutex> lock(g_mutex);
+      sweep_returning_locked(true);
       if (g_dev.status_host) {
         code = *reinterpret_cast<volatile uint32_t *>(g_dev.status_host);
         *reinterpret_cast<volatile uint32_t *>(g_dev.status_host) = 0;
