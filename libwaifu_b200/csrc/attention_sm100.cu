@@ -238,7 +238,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (threadIdx.x == 0) atomicCAS(p.status, 0u, kStatusAttentionLayout);
     return;
   }
-  const int q0 = blockIdx.x * kBlockQ;
+  const int q0 = static_cast<int>(p.mask_type != 0 ? gridDim.x - 1 - blockIdx.x : blockIdx.x) * kBlockQ;  // longest walks first
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
   const int kv_head = head / p.group;
@@ -704,7 +704,9 @@ attention2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     if (threadIdx.x == 0) atomicCAS(p.status, 0u, kStatusAttentionLayout);
     return;
   }
-  const int q0 = blockIdx.x * (kTiles * kBlockQ);
+  // Under a causal mask the later queries have more keys to walk: those CTAs go first, so that the
+  // grid's last round is made of short ones.
+  const int q0 = static_cast<int>(p.mask_type != 0 ? gridDim.x - 1 - blockIdx.x : blockIdx.x) * (kTiles * kBlockQ);
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
   const int kv_head = head / p.group;
