@@ -150,8 +150,9 @@ struct DeviceState {
   // Kernel status word in mapped host memory: kernels write it, the host reads it without a copy.
   uint32_t *status_host = nullptr;
   uint32_t *status_dev = nullptr;
-  // Grow-only scratch for quantised activations, re-tiled scale factors and widened weights.
-  // All work is ordered on the legacy default stream, so one arena can be reused call after call.
+  // Grow-only scratch for quantised activations, re-tiled scale factors and widened weights: one
+  // block of the stream-ordered pool. All work is ordered on the legacy default stream, so it can be
+  // reused call after call.
   uint8_t *scratch = nullptr;
   size_t scratch_cap = 0;
   // Set by the first call that touches the GPU: from then on this process belongs to that device
