@@ -1,4 +1,6 @@
-// Scaled dot product attention on sm_100a.
+// Scaled dot product attention on sm_100a. Two kernels: the one described first, one tile of
+// queries per CTA, serves runs of at most 128 queries and the block diagonal mask; the two-tile
+// kernel further down (probabilities in tensor memory, v read as it lies) serves the rest.
 //
 // A CTA owns 128 queries of one head and walks that head's keys 128 at a time. Per block of keys:
 //   S = Q K^T      tcgen05.mma kind::f16, 128 x 128 x head_dim, into one of two score buffers in

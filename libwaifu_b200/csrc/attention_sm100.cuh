@@ -1,5 +1,6 @@
 // Scaled dot product attention for sm_100a: one pass over the keys with the online softmax, both
-// products on tcgen05 tensor cores with the scores and the block's output in tensor memory.
+// products on tcgen05 tensor cores with the scores, the probabilities (two-tile kernel) and the
+// block's output in tensor memory.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -31,7 +32,9 @@ struct AttentionArgs {
 // operands); the causal masks need kv_len >= q_len, the block diagonal one kv_len == q_len.
 bool attention_supported(const AttentionArgs &a, const char **why);
 size_t attention_scratch_bytes(int batch, int kv_heads, int kv_len, int head_dim);
-// Two launches: the transposition of v, and the attention kernel.
+// One launch where two tiles of queries share a CTA (more than 128 queries, any mask but the block
+// diagonal one, a v without repeated dimensions): v is read as it lies. Otherwise two: the
+// transposition of v into the scratch, and the one-tile kernel.
 cudaError_t attention(const AttentionArgs &a, const char **why);
 
 constexpr uint32_t kStatusAttentionTimeout = 0x41;

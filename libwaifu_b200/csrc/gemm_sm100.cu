@@ -10,9 +10,12 @@
 //   warp  9    MMA: one thread issues tcgen05.mma on the staged tiles, accumulating in tensor
 //              memory; tcgen05.commit hands stages back to the producer and finished
 //              accumulators to the epilogue
-//   warps 10-11 pushers, only at work in the scatter form (a product gathered on several GPUs):
-//              once the epilogue has written a tile into this GPU's matrix they copy its rows to
-//              the peers' matrices, 512 contiguous bytes per store instruction, over NVLink.
+//   warps 10-11 in the NVFP4 kind one thread of them copies scale factors into tensor memory; in
+//              the scatter form (a product gathered on several GPUs) the epilogue's TMA stores go
+//              to every destination matrix, this GPU's and its peers', and these warps are idle;
+//              only where a destination cannot be described by a tensor map do they push: once the
+//              epilogue has written a tile into this GPU's matrix they copy its rows to the peers'
+//              matrices, 512 contiguous bytes per store instruction, over NVLink.
 // The mixed form (a half activation against an e4m3 weight that is NOT narrowed, flint's
 // fl_fp8_matmul) divides the twelve differently: warps 0-3 epilogue (a warp takes its 32 rows of
 // all the tile's columns), warp 4 producer, warp 5 MMA, warps 6-11 converters. The weight tile
