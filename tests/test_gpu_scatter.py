@@ -320,3 +320,33 @@ def test_row_maxima_of_a_column_block(flint, oracle):
             block = d.view_as((70, b - a), (384, 1), a)
             got = F.fp8_row_amax(block).numpy()
             assert np.array_equal(got, oracle.row_amax(np.ascontiguousarray(full[:, a:b]), is_bf16)), (is_bf16, a, b)
+
+
+def test_quantized_product_lands_in_every_destination(flint, oracle):
+    """fl_fp8_linear_quantized_scatter on one GPU: codes and row scales in, the product (bias,
+    residual, one rounding) in a column block of two full-width matrices, the rest of them untouched;
+    the same bits as fl_fp8_linear_quantized gives on its own."""
+    F = flint
+    rng = np.random.default_rng(74)
+    m, n, k, ld, col0 = 300, 136, 192, 400, 64
+    x = oracle.narrow(randn(rng, (m, k)), True)
+    a_codes, a_scales = oracle.quantize_fp8_act(x, True)
+    codes, scales = oracle.quantize_fp8_rows(randn(rng, (n, k), 0.02))
+    bias = oracle.narrow(randn(rng, (n,), 0.01), True)
+    res = oracle.narrow(randn(rng, (m, n)), True)
+    bf, f8, fl = F.DType.BFLOAT16, F.DType.FP8E4M3, F.DType.FLOAT
+    fill = np.full((m, ld), 0x7FC0, np.uint16)
+    d0, d1 = dev(F, fill, bf), dev(F, fill, bf)
+    ops = (dev(F, a_codes, f8), dev(F, a_scales, fl), dev(F, codes, f8), dev(F, scales, fl))
+    F.fp8_linear_quantized_scatter(*ops, [d0, d1], col0, dev(F, bias, bf), dev(F, res, bf), F.ACT_GELU_TANH)
+    alone = F.Tensor.empty((m, n), bf)
+    F.fp8_linear_quantized(*ops, dev(F, bias, bf), dev(F, res, bf), F.ACT_GELU_TANH, alone)
+    F.synchronize()
+    want = oracle.fp8_linear_quantized(a_codes, a_scales, codes, scales, bias, res, oracle.ACT_GELU_TANH)
+    for d in (d0, d1):
+        got = d.numpy()
+        assert np.array_equal(got[:, col0:col0 + n], alone.numpy())
+        check_parity(oracle, got[:, col0:col0 + n], want, True, what="quantized scatter")
+        assert (got[:, :col0] == 0x7FC0).all() and (got[:, col0 + n:] == 0x7FC0).all()
+    with pytest.raises(F.FlintError):
+        F.fp8_linear_quantized_scatter(*ops, [d0], ld - n + 8, None, None, F.ACT_NONE)   # does not fit
