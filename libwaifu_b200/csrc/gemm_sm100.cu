@@ -1305,7 +1305,9 @@ int sm_count() {
 // about ten microseconds of a launch (two more epilogue-side passes per unit, the second of them
 // exposed at the end), that is some thirty K stages. It is used where the saving is forty stages
 // or more: long-K products whose last round is poorly filled (8704 x 3072 x 12288: 408 tiles on 74
-// pairs, 248 -> 232 us); with 3072-deep tiles it never is.
+// pairs, 248 -> 232 us); with 3072-deep tiles it never is. A product with fewer tiles than half
+// the units and a long K has every tile cut into two halves on twice as many units (the same two
+// holders per tile, the same workspace slots and counters).
 GemmSchedule gemm_schedule(int tiles, int max_units, int num_kb, bool allow_stream_k) {
   GemmSchedule s = {};
   s.units = tiles < max_units ? tiles : max_units;
@@ -1313,7 +1315,14 @@ GemmSchedule gemm_schedule(int tiles, int max_units, int num_kb, bool allow_stre
   const int full_rounds = tiles / s.units;
   const int remainder = tiles % s.units;
   const long long saved_stages = static_cast<long long>(s.units - remainder) * num_kb / s.units;
-  if (allow_stream_k && full_rounds >= 1 && remainder > 0 && saved_stages >= kStreamKMinSavedStages) {
+  if (allow_stream_k && 2 * tiles <= max_units && num_kb / 2 >= kStreamKMinSavedStages) {
+    // Fewer tiles than half the units and a long K: every tile is cut in two halves of its K
+    // stages, held by two neighbouring units (4352 x 384 x 12288: 34 tiles on 68 of 74 pairs).
+    s.units = 2 * tiles;
+    s.dp_rounds = 0;
+    s.sk_tiles = tiles;
+    s.sk_first_tile = 0;
+  } else if (allow_stream_k && full_rounds >= 1 && remainder > 0 && saved_stages >= kStreamKMinSavedStages) {
     s.dp_rounds = full_rounds - 1;
     s.sk_tiles = remainder + s.units;
     s.sk_first_tile = s.dp_rounds * s.units;

@@ -52,15 +52,20 @@ SHAPES = [("e4m3", 4352, 12288, 3072), ("e4m3", 4352, 3072, 12288), ("e4m3", 409
           ("e4m3", 8192, 3072, 64), ("e4m3", 300, 200, 256), ("half", 513, 64, 64), ("e4m3", 19200, 256, 512),
           ("e4m3", 2, 18432, 3072), ("e4m3", 77 * 256, 256, 8192), ("e4m3", 149 * 128, 128, 8192),
           ("e4m3", 2304, 2304, 6144), ("e4m3", 20480, 128, 6144), ("e4m3", 2250, 2312, 6160), ("nvfp4", 2304, 1728, 12288),
-          ("bf16", 2304, 2304, 3072), ("e4m3", 5000, 5000, 16384)]
+          ("bf16", 2304, 2304, 3072), ("e4m3", 5000, 5000, 16384),
+          ("e4m3", 4352, 384, 12288), ("e4m3", 1024, 384, 12288), ("bf16", 512, 256, 8192), ("e4m3", 300, 200, 10368)]
 
 
 @pytest.mark.parametrize("sms", [148, 132, 16, 2])
 @pytest.mark.parametrize("kind,m,n,k", SHAPES)
 def test_every_stage_of_every_tile_is_computed_once(kind, m, n, k, sms):
     p = plan(kind, m, n, k, sms)
-    assert p["units"] == min(p["tiles"], sms // p["ctas"])
-    assert p["sk_tiles"] == 0 or p["sk_tiles"] >= p["units"]
+    halves = p["sk_tiles"] > 0 and p["units"] == 2 * p["tiles"]  # few tiles, long K: every tile in two halves
+    if halves:
+        assert p["units"] <= sms // p["ctas"] and (p["dp_rounds"], p["sk_tiles"], p["sk_first_tile"]) == (0, p["tiles"], 0)
+    else:
+        assert p["units"] == min(p["tiles"], sms // p["ctas"])
+        assert p["sk_tiles"] == 0 or p["sk_tiles"] >= p["units"]
     assert p["dp_rounds"] * p["units"] == p["sk_first_tile"] or p["sk_tiles"] == 0
     covered = {}
     holders = {}
@@ -105,3 +110,7 @@ def test_stream_k_is_taken_where_it_saves_forty_stages_or_more():
     assert plan("e4m3", 8704, 3072, 12288, 148, allow=0)["sk_tiles"] == 0
     assert plan("e4m3", 520, 328, 8192, 148)["sk_tiles"] == 0          # fewer tiles than units
     assert plan("e4m3", 2304, 2304, 6144, 148)["sk_tiles"] == 81        # what the GPU tests run
+    # few tiles and a long K: every tile in two halves on twice as many units
+    few = plan("e4m3", 4352, 384, 12288, 148)
+    assert (few["tiles"], few["units"], few["dp_rounds"], few["sk_tiles"]) == (34, 68, 0, 34)
+    assert plan("e4m3", 4352, 768, 12288, 148)["sk_tiles"] == 0          # 51 tiles: twice that does not fit 74 pairs

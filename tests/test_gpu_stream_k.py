@@ -57,7 +57,9 @@ def compare(oracle, runs, want, is_bf16, what):
 # (m, n, k, act): pair tiles 256 x 256 (81 tiles on 74 pairs), single-CTA 128-wide tiles (160 on 148),
 # and a ragged case whose edge tiles are partly outside the matrix; K long enough (48 stages) that
 # the schedule takes its stream-K form
-@pytest.mark.parametrize("m,n,k,act", [(2304, 2304, 6144, 1), (20480, 128, 6144, 0), (2250, 2056, 6160, 0)])
+# ... and few tiles with a long K, every tile cut in two halves (8 pair tiles on 16 of the pairs; a ragged one)
+@pytest.mark.parametrize("m,n,k,act", [(2304, 2304, 6144, 1), (20480, 128, 6144, 0), (2250, 2056, 6160, 0),
+                                       (1024, 384, 12288, 1), (700, 392, 10368, 0)])
 def test_fp8_linear_under_both_schedules(flint, oracle, m, n, k, act):
     F = flint
     p = plan(F, 2, m, n, k)
