@@ -1164,6 +1164,30 @@ size_t attention_scratch_bytes(int batch, int kv_heads, int kv_len, int head_dim
   return static_cast<size_t>(batch) * kv_heads * head_dim * round_up(kv_len, kPadKv) * 2;
 }
 
+AttentionPlan attention_plan(const AttentionArgs &a) {
+  // Two tiles of queries per CTA where a head has more than one tile of them; the block diagonal
+  // mask, whose tiles see different keys, and short query runs keep one tile per CTA.
+  static const bool one_tile_only = [] {
+    const char *e = std::getenv("FLINT_SM100_ATTENTION_ONE_TILE");
+    return e && e[0] == '1';
+  }();
+  static const bool transposed_v_only = [] {
+    const char *e = std::getenv("FLINT_SM100_ATTENTION_TRANSPOSED_V");
+    return e && e[0] == '1';
+  }();
+  const bool block_diagonal = a.mask_type == 3 && a.block_size < a.kv_len;  // (one block over every key is no mask)
+  AttentionPlan plan;
+  plan.two_tiles = a.q_len > kBlockQ && !block_diagonal && !one_tile_only;
+  // The two-tile kernel reads v as it lies (a tensor map like k's, the operand MN-major) unless v
+  // repeats a dimension through a stride of 0, which only the transposing kernel can follow.
+  const int v_extent[3] = {a.batch, a.kv_heads, a.kv_len};
+  bool v_plain = true;
+  for (int i = 0; i < 3; ++i) v_plain = v_plain && !(v_extent[i] > 1 && a.v_stride[i] == 0);
+  plan.v_direct = plan.two_tiles && v_plain && !transposed_v_only;
+  plan.launches = plan.v_direct ? 1 : 2;
+  return plan;
+}
+
 cudaError_t attention(const AttentionArgs &a, const char **why) {
   *why = "";
   if (!attention_supported(a, why)) return cudaErrorInvalidValue;
@@ -1188,23 +1212,9 @@ cudaError_t attention(const AttentionArgs &a, const char **why) {
   }
   kp.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(d));
   kp.status = a.status;
-  // Two tiles of queries per CTA where a head has more than one tile of them; the block diagonal
-  // mask, whose tiles see different keys, and short query runs keep one tile per CTA.
-  static const bool one_tile_only = [] {
-    const char *e = std::getenv("FLINT_SM100_ATTENTION_ONE_TILE");
-    return e && e[0] == '1';
-  }();
-  static const bool transposed_v_only = [] {
-    const char *e = std::getenv("FLINT_SM100_ATTENTION_TRANSPOSED_V");
-    return e && e[0] == '1';
-  }();
-  const bool two_tiles = a.q_len > kBlockQ && kp.mask_type != 3 && !one_tile_only;
-  // The two-tile kernel reads v as it lies (a tensor map like k's, the operand MN-major) unless v
-  // repeats a dimension through a stride of 0, which only the transposing kernel can follow.
-  const int v_extent[3] = {a.batch, a.kv_heads, a.kv_len};
-  bool v_plain = true;
-  for (int i = 0; i < 3; ++i) v_plain = v_plain && !(v_extent[i] > 1 && a.v_stride[i] == 0);
-  kp.v_direct = (two_tiles && v_plain && !transposed_v_only) ? 1 : 0;
+  const AttentionPlan plan = attention_plan(a);
+  const bool two_tiles = plan.two_tiles;
+  kp.v_direct = plan.v_direct ? 1 : 0;
 
   if (!kp.v_direct) {
     const dim3 tgrid(static_cast<unsigned>(kv_pad / 64), static_cast<unsigned>(d / 64),

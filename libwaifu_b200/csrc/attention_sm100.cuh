@@ -32,6 +32,14 @@ struct AttentionArgs {
 // operands); the causal masks need kv_len >= q_len, the block diagonal one kv_len == q_len.
 bool attention_supported(const AttentionArgs &a, const char **why);
 size_t attention_scratch_bytes(int batch, int kv_heads, int kv_len, int head_dim);
+// Which kernel a call runs on: two tiles of queries per CTA or one, and whether v is read as it
+// lies (then no scratch is needed and the call is one launch) or through its transposition.
+struct AttentionPlan {
+  bool two_tiles;
+  bool v_direct;
+  int launches;
+};
+AttentionPlan attention_plan(const AttentionArgs &a);
 // One launch where two tiles of queries share a CTA (more than 128 queries, any mask but the block
 // diagonal one, a v without repeated dimensions): v is read as it lies. Otherwise two: the
 // transposition of v into the scratch, and the one-tile kernel.

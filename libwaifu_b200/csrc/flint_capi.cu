@@ -2286,12 +2286,15 @@ int32_t fl_attention(fl_operators_t operators, fl_tensor_view_t q_h, fl_tensor_v
     a.stream = 0;
     const char *why = "";
     if (!attention_supported(a, &why)) invalid(std::string("attention: ") + why + " (not implemented in this library)");
+    const AttentionPlan plan = attention_plan(a);
     Scratch scratch;
-    const size_t vt_off = scratch.reserve(attention_scratch_bytes(batch, kv_heads, kv_len, d));
-    a.v_transposed = scratch.commit() + vt_off;
+    if (!plan.v_direct) {  // v goes through its transposition
+      const size_t vt_off = scratch.reserve(attention_scratch_bytes(batch, kv_heads, kv_len, d));
+      a.v_transposed = scratch.commit() + vt_off;
+    }
     cudaError_t e = attention(a, &why);
     if (e != cudaSuccess) cuda_check(e, (std::string("attention: ") + why).c_str());
-    g_block_launches += 2;
+    g_block_launches += plan.launches;
     return clear_error();
   });
 }
