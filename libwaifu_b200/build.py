@@ -11,9 +11,9 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libflint_sm100.so")
 SOURCES = ["gemm_sm100.cu", "quant_sm100.cu", "skinny_sm100.cu", "block_sm100.cu", "attention_sm100.cu", "elementwise_sm100.cu",
-           "selftest_sm100.cu", "matmul_simt_sm100.cu", "peer_sm100.cu", "flint_capi.cu"]
+           "selftest_sm100.cu", "matmul_simt_sm100.cu", "peer_sm100.cu", "fewrow_tc_sm100.cu", "flint_capi.cu"]
 HEADERS = ["gemm_sm100.cuh", "quant_sm100.cuh", "skinny_sm100.cuh", "block_sm100.cuh", "attention_sm100.cuh", "elementwise_sm100.cuh",
-           "selftest_sm100.cuh", "matmul_simt_sm100.cuh", "peer_sm100.cuh", "ptx_sm100.cuh", os.path.join("..", "..", "include", "flint_sm100.h")]
+           "selftest_sm100.cuh", "matmul_simt_sm100.cuh", "peer_sm100.cuh", "fewrow_tc_sm100.cuh", "ptx_sm100.cuh", os.path.join("..", "..", "include", "flint_sm100.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -1,0 +1,23 @@
+// The reference-compatible product for at most 16 half rows on tensor cores: the weight on the M
+// side of tcgen05.mma, the rows as N = 16 (see fewrow_tc_sm100.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace flsm100 {
+
+constexpr uint32_t kStatusFewRowTcTimeout = 0x71;
+
+// 1..16 half rows (not bfloat16: the widened weight and the rows have to be one type), k a
+// multiple of 64, n a multiple of 8, x and w 16-byte aligned.
+bool fewrow_tc_supported(int m, int n, int k, int is_bf16, const void *x, const void *w, const void *out);
+
+// out (m, n) = round16( (x . widen(w)^T) * scale + bias (n) + residual rows (period residual_rows over
+// m, pitch residual_ld) ), x (m, k) half, w (n, k) e4m3, one <float> scale, fp32 accumulation
+// (flint/cuda/gemm_fp8_cutlass.cu:107-125). One launch, no scratch.
+cudaError_t fewrow_tc_matmul(const void *x, int m, int n, int k, const uint8_t *w, const float *scale, const void *bias,
+                             const void *residual, int residual_rows, int64_t residual_ld, void *out, uint32_t *status,
+                             cudaStream_t stream, const char **why);
+
+}  // namespace flsm100

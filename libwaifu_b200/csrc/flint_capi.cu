@@ -20,6 +20,7 @@
 #include "skinny_sm100.cuh"
 #include "attention_sm100.cuh"
 #include "elementwise_sm100.cuh"
+#include "fewrow_tc_sm100.cuh"
 #include "peer_sm100.cuh"
 #include "selftest_sm100.cuh"
 #include "matmul_simt_sm100.cuh"
@@ -1102,6 +1103,26 @@ int32_t fl_fp8_matmul_add(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tens
       std::vector<int32_t> bs;
       std::vector<int64_t> bt;
       if (addend) quick = plan_addend(*addend, out, &bs, &bt);
+      // Four to sixteen half rows against many channels: the weight on the M side of the tensor-core
+      // instruction (fewrow_tc_sm100.cu), whose time does not grow with the rows. With fewer rows the
+      // kernel underneath is as fast, and below kFewRowTcMinChannels this one's CTAs, one per 128
+      // channels, are too few to pull on HBM.
+      static const bool no_fewrow_tc = [] {
+        const char *e = std::getenv("FLINT_SM100_NO_FEWROW_TC");
+        return e && e[0] == '1';
+      }();
+      constexpr int kFewRowTcMinChannels = 12288, kFewRowTcMinRows = 4;
+      if (!no_skinny && !no_fewrow_tc && !quick.needs_expand && rows >= kFewRowTcMinChannels && m >= kFewRowTcMinRows &&
+          fewrow_tc_supported(m, rows, k, is_bf16, raw_ptr(a), raw_ptr(weight), raw_ptr(out)) &&
+          (!quick.residual || quick.residual_rows > 0)) {
+        const char *why = "";
+        cudaError_t e = fewrow_tc_matmul(raw_ptr(a), m, rows, k, reinterpret_cast<const uint8_t *>(raw_ptr(weight)),
+                                         reinterpret_cast<const float *>(raw_ptr(scale)), quick.bias, quick.residual,
+                                         quick.residual_rows, quick.residual_ld, raw_ptr(out), status_word(), 0, &why);
+        if (e != cudaSuccess) cuda_check(e, (std::string("few-row FP8 matmul: ") + why).c_str());
+        ++g_gemm_launches;
+        return clear_error();
+      }
       if (!no_skinny && !quick.needs_expand &&
           skinny_upcast_supported(m, rows, k, raw_ptr(a), raw_ptr(weight), raw_ptr(out), quick.residual != nullptr)) {
         cuda_check(skinny_upcast_matmul(raw_ptr(a), is_bf16, m, rows, k, raw_ptr(weight),
