@@ -992,7 +992,10 @@ def run_skinny(args):
     import numpy as np
     import torch
     from libwaifu_b200 import flint as F
-    wl = WORKLOADS["skinny_decode"]
+    wl = dict(WORKLOADS["skinny_decode"])
+    if args.rows:  # (--rows 4 .. 16: the tensor-core few-row kernel's share of the path)
+        wl["m"] = args.rows
+        wl["desc"] = wl["desc"] + f" [{args.rows} rows]"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -1089,7 +1092,7 @@ def run_skinny(args):
     _, hbm_peak, peak_kind = measured_peaks()
     alg_bytes = n * k + m * k * 2 + m * n * 2 + 4
     achieved = alg_bytes / (ms_step * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "skinny_fp8_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+    roofline = {"bound": "hbm", "kernel": "fewrow_tc_kernel" if 4 <= m <= 16 else "skinny_fp8_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                 "frac": achieved / hbm_peak, "peak_source": f"stream copy, of {peak_kind}", "launches": launches,
                 "avg_launch_ms": ms_step, **traffic_fields("skinny_decode"),
                 "algorithmic_bytes_per_step": alg_bytes,
