@@ -70,7 +70,7 @@ NCU_TRAFFIC_SOURCE = {
     "legacy_fp8_matmul": "profiles/gemm_tn_kernel_mixed_legacy_fp8_matmul.md",
     "c1_linear": "profiles/gemm_tn_kernel_fp8_c2_mlp.md",
     "c3_nvfp4_qkv": "profiles/gemm_tn_kernel_nvfp4_c3_qkv.md",
-    "skinny_decode": "profiles/skinny_fp8_kernel_decode_1x16384x3072.md",
+    "skinny_decode": "profiles/fewrow_tc_kernel_decode_16x16384x3072.md",
     "attention_step": "profiles/attention_kernel_denoise_step.md",
 }
 
@@ -85,7 +85,7 @@ NCU_TRAFFIC_BYTES = {
     "c2_mlp": (51.9e6 + 64.5e6 + 169.5e6 + 14.9e6) / 2,  # mean of the up and the down launch
     "c1_linear": 22.1e6,                                 # the bf16 output stays dirty in L2
     "c3_nvfp4_qkv": 24.0e6 + 25.5e6,
-    "skinny_decode": 50.38e6 + 7.0e6,                    # the weight once; the writes are older dirty lines leaving L2
+    "skinny_decode": 50.46e6 + 0.01e6,                   # the weight once; the result stays in L2
     "attention_step": 160.5e6 + 32.7e6,                  # q, k, v once (K and V re-reads hit L2); the output partly stays in L2
 }
 
@@ -993,7 +993,7 @@ def run_skinny(args):
     import torch
     from libwaifu_b200 import flint as F
     wl = dict(WORKLOADS["skinny_decode"])
-    if args.rows:  # (--rows 4 .. 16: the tensor-core few-row kernel's share of the path)
+    if args.rows:  # (up to 16 rows)
         wl["m"] = args.rows
         wl["desc"] = wl["desc"] + f" [{args.rows} rows]"
     rank = int(os.environ.get("RANK", "0"))
@@ -1092,7 +1092,7 @@ def run_skinny(args):
     _, hbm_peak, peak_kind = measured_peaks()
     alg_bytes = n * k + m * k * 2 + m * n * 2 + 4
     achieved = alg_bytes / (ms_step * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "fewrow_tc_kernel" if 4 <= m <= 16 else "skinny_fp8_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+    roofline = {"bound": "hbm", "kernel": "fewrow_tc_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                 "frac": achieved / hbm_peak, "peak_source": f"stream copy, of {peak_kind}", "launches": launches,
                 "avg_launch_ms": ms_step, **traffic_fields("skinny_decode"),
                 "algorithmic_bytes_per_step": alg_bytes,

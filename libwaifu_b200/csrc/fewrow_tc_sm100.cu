@@ -3,12 +3,14 @@
 // once. Here the weight sits on the M side of tcgen05.mma and the rows are its N = 16, so that no
 // instruction of a CUDA core multiplies anything and the time does not depend on the row count
 // (the kernel in skinny_sm100.cu, which multiplies on mma.sync, takes 20 us for one row against
-// 16384 x 3072 and 36 us for sixteen; this one 21 us for either):
+// 16384 x 3072 and 36 us for sixteen; this one 17.4 us for either):
 //   warp 4     producer: per stage of 256 K positions one TMA copy of 128 weight rows x 256 e4m3
-//              bytes (as they lie) and four of the 16 rows x 128 bytes of x (128-byte swizzle), into
-//              a ring of two stages; the weight is read exactly once;
+//              bytes (as they lie) into a ring of two raw stages, and four copies of the 16 rows x
+//              128 bytes of x (128-byte swizzle) into a ring of four; the weight is read exactly once;
 //   warps 6-11 converters: widen a stage's weight bytes to half (cvt.rn.f16x2.e4m3x2, exact) into
-//              four 128-row x 128-byte tiles in the 128-byte swizzle (two such sets);
+//              four 128-row x 128-byte tiles in the 128-byte swizzle (two such sets), and hand the
+//              raw stage back at once, so that its next load is on its way while the instructions
+//              run (with the raw stage held until those were done the kernel took 21 us);
 //   warp 5     one thread issues sixteen tcgen05.mma kind::f16 (M = 128 channels, N = 16 rows,
 //              K = 16) per stage into four accumulators in turn (4 x 128 x 16 floats in tensor
 //              memory); it waits and commits once per stage: every tcgen05 issue and every wait,
@@ -16,9 +18,9 @@
 //              hand-overs per 64 K positions the kernel took 25 us;
 //   warps 0-3  epilogue: a lane owns a channel, reads its 4 x 16 partial sums and adds them; scale,
 //              bias, residual, one rounding; for every row the warp stores 32 consecutive channels.
-// A CTA owns 128 output channels, so the kernel wants 12288 channels or more to put enough SMs on
-// the weight; what paces it is the issuing thread (sixteen instructions per 32 KB of weight).
-// Every wait is bounded (status word, as everywhere else).
+// A CTA owns 128 output channels and is paced by its own chain (load, widen, multiply) over the
+// k / 256 stages, two of them in flight: 17 us at k = 3072 for any channel count, so the kernel is
+// for wide weights. Every wait is bounded (status word, as everywhere else).
 #include "fewrow_tc_sm100.cuh"
 
 #include <cuda.h>
@@ -38,8 +40,8 @@ constexpr int kStageK = kBlocksPerStage * kBlockK;     // K positions per ring s
 constexpr int kRawWBytes = kChannels * kStageK;        // 32 KB
 constexpr int kXAtomBytes = kTokens * kBlockK * 2;     // 2 KB: a block's 16 rows x 128 bytes
 constexpr int kXBytes = kBlocksPerStage * kXAtomBytes; // 8 KB
-constexpr int kStageBytes = kRawWBytes + kXBytes;      // 40 KB
-constexpr int kStages = 2;
+constexpr int kStages = 2;                             // of raw weight bytes: given back as soon as they are widened
+constexpr int kXStages = 4;                            // of x: given back when the instructions that read them are done
 constexpr int kWideBytes = kChannels * kBlockK * 2;    // 16 KB
 constexpr int kWideUnits = 2;                 // a unit: the four widened tiles of one stage
 constexpr int kWide = kWideUnits * kBlocksPerStage;
@@ -51,9 +53,10 @@ constexpr int kConverterWarp0 = 6;
 constexpr int kConverterWarps = 6;
 constexpr int kThreads = (kConverterWarp0 + kConverterWarps) * 32;
 constexpr int kWideOff = 0;                               // 1024-byte aligned tiles first
-constexpr int kRingOff = kWideOff + kWide * kWideBytes;   // stage: x (2 KB, swizzled: 1024-aligned) then raw w
-constexpr int kSmemBytes = kRingOff + kStages * kStageBytes + 1024;
-static_assert(kStageBytes % 1024 == 0 && kWideBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
+constexpr int kXOff = kWideOff + kWide * kWideBytes;      // then x's swizzled tiles
+constexpr int kRingOff = kXOff + kXStages * kXBytes;      // then the raw weight stages
+constexpr int kSmemBytes = kRingOff + kStages * kRawWBytes + 1024;
+static_assert(kXBytes % 1024 == 0 && kWideBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory");
 
 struct Params {
@@ -72,6 +75,7 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ __align__(8) uint64_t raw_full_bar[kStages], raw_empty_bar[kStages];
+  __shared__ __align__(8) uint64_t x_full_bar[kXStages], x_empty_bar[kXStages];
   __shared__ __align__(8) uint64_t wide_full_bar[kWideUnits], wide_empty_bar[kWideUnits];
   __shared__ __align__(8) uint64_t acc_full_bar;
   __shared__ uint32_t tmem_base_slot;
@@ -87,7 +91,11 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&raw_full_bar[s], 1);
-      mbar_init(&raw_empty_bar[s], 1);
+      mbar_init(&raw_empty_bar[s], kConverterWarps);
+    }
+    for (int s = 0; s < kXStages; ++s) {
+      mbar_init(&x_full_bar[s], 1);
+      mbar_init(&x_empty_bar[s], 1);
     }
     for (int w = 0; w < kWideUnits; ++w) {
       mbar_init(&wide_full_bar[w], kConverterWarps);
@@ -111,24 +119,26 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
   griddep_wait();
   griddep_launch_dependents();
 
-  auto stage_x = [&](int s) { return smem + kRingOff + s * kStageBytes; };
-  auto stage_w = [&](int s) { return smem + kRingOff + s * kStageBytes + kXBytes; };
+  auto stage_x = [&](int s) { return smem + kXOff + s * kXBytes; };
+  auto stage_w = [&](int s) { return smem + kRingOff + s * kRawWBytes; };
   auto wide = [&](int w) { return smem + kWideOff + w * kWideBytes; };
 
   if (warp == kProducerWarp) {
     if (lane == 0) {
       bool ok = true;
       for (int st = 0; st < num_stages && ok; ++st) {
-        const int s = st % kStages;
-        if (!mbar_wait(&raw_empty_bar[s], ((st / kStages) & 1) ^ 1, &abort_flag)) {
+        const int s = st % kStages, xs = st % kXStages;
+        if (!mbar_wait(&raw_empty_bar[s], ((st / kStages) & 1) ^ 1, &abort_flag) ||
+            !mbar_wait(&x_empty_bar[xs], ((st / kXStages) & 1) ^ 1, &abort_flag)) {
           ok = false;
           break;
         }
-        mbar_arrive_expect_tx(&raw_full_bar[s], kStageBytes);  // (bytes past the end of a row arrive as zeros)
+        mbar_arrive_expect_tx(&raw_full_bar[s], kRawWBytes);  // (bytes past the end of a row arrive as zeros)
         tma_load_2d(stage_w(s), &tmap_w, &raw_full_bar[s], st * kStageK, n0);
+        mbar_arrive_expect_tx(&x_full_bar[xs], kXBytes);
 #pragma unroll
         for (int j = 0; j < kBlocksPerStage; ++j) {
-          tma_load_2d(stage_x(s) + j * kXAtomBytes, &tmap_x, &raw_full_bar[s], (st * kStageK + j * kBlockK) * 2, 0);
+          tma_load_2d(stage_x(xs) + j * kXAtomBytes, &tmap_x, &x_full_bar[xs], (st * kStageK + j * kBlockK) * 2, 0);
         }
       }
       if (!ok) {
@@ -146,9 +156,9 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       // tcgen05 issue, each wait on a completed barrier is some 80 cycles) are what a few-row
       // product has to keep off the path of the bytes.
       for (int st = 0; st < num_stages && ok; ++st) {
-        const int s = st % kStages, u = st % kWideUnits;
+        const int xs = st % kXStages, u = st % kWideUnits;
         if (!mbar_wait(&wide_full_bar[u], (st / kWideUnits) & 1, &abort_flag) ||
-            !mbar_wait(&raw_full_bar[s], (st / kStages) & 1, &abort_flag)) {  // (x's bytes came under this one)
+            !mbar_wait(&x_full_bar[xs], (st / kXStages) & 1, &abort_flag)) {
           ok = false;
           break;
         }
@@ -156,14 +166,14 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const int blocks = min(kBlocksPerStage, num_kb - st * kBlocksPerStage);
         for (int j = 0; j < blocks; ++j) {
           const uint64_t wd = wdesc0 + static_cast<uint64_t>((u * kBlocksPerStage + j) * (kWideBytes >> 4));
-          const uint64_t xd = xdesc0 + static_cast<uint64_t>((s * kStageBytes + j * kXAtomBytes) >> 4);
+          const uint64_t xd = xdesc0 + static_cast<uint64_t>((xs * kXBytes + j * kXAtomBytes) >> 4);
 #pragma unroll
           for (int i = 0; i < kChains; ++i) {  // 16 K positions = 32 bytes of a row each
             umma_ss<kKindF16>(tmem_base + i * kTokens, wd + i * 2, xd + i * 2, idesc, (st > 0 || j > 0) ? 1u : 0u);
           }
         }
         umma_commit(&wide_empty_bar[u]);
-        umma_commit(&raw_empty_bar[s]);
+        umma_commit(&x_empty_bar[xs]);
       }
       if (ok) umma_commit(&acc_full_bar);
       if (!ok) {
@@ -201,7 +211,10 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       }
       fence_proxy_async_smem();  // the UMMA reads these bytes through the async proxy
       __syncwarp();
-      if (lane == 0) mbar_arrive(&wide_full_bar[u]);
+      if (lane == 0) {
+        mbar_arrive(&raw_empty_bar[s]);  // the raw bytes have been read: the stage may be refilled at once
+        mbar_arrive(&wide_full_bar[u]);
+      }
     }
     if (!ok && lane == 0) {
       abort_flag = 1;

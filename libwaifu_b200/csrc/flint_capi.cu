@@ -1103,16 +1103,17 @@ int32_t fl_fp8_matmul_add(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tens
       std::vector<int32_t> bs;
       std::vector<int64_t> bt;
       if (addend) quick = plan_addend(*addend, out, &bs, &bt);
-      // Four to sixteen half rows against many channels: the weight on the M side of the tensor-core
-      // instruction (fewrow_tc_sm100.cu), whose time does not grow with the rows. With fewer rows the
-      // kernel underneath is as fast, and below kFewRowTcMinChannels this one's CTAs, one per 128
-      // channels, are too few to pull on HBM.
+      // Half rows against many channels: the weight on the M side of the tensor-core instruction
+      // (fewrow_tc_sm100.cu). Its time, 17 us at 3072-deep rows, depends neither on the row count
+      // nor much on the channel count (a CTA per 128 channels, paced by its own chain of stages),
+      // so it takes the products the kernel underneath is slower on, as measured: any row count
+      // from 16384 channels, four rows or more from 12288, eight or more from 8192.
       static const bool no_fewrow_tc = [] {
         const char *e = std::getenv("FLINT_SM100_NO_FEWROW_TC");
         return e && e[0] == '1';
       }();
-      constexpr int kFewRowTcMinChannels = 12288, kFewRowTcMinRows = 4;
-      if (!no_skinny && !no_fewrow_tc && !quick.needs_expand && rows >= kFewRowTcMinChannels && m >= kFewRowTcMinRows &&
+      const bool fewrow_tc_wins = rows >= 16384 || (rows >= 12288 && m >= 4) || (rows >= 8192 && m >= 8);
+      if (!no_skinny && !no_fewrow_tc && !quick.needs_expand && fewrow_tc_wins &&
           fewrow_tc_supported(m, rows, k, is_bf16, raw_ptr(a), raw_ptr(weight), raw_ptr(out)) &&
           (!quick.residual || quick.residual_rows > 0)) {
         const char *why = "";
