@@ -85,7 +85,7 @@ NCU_TRAFFIC_BYTES = {
     "c2_mlp": (51.9e6 + 64.5e6 + 169.5e6 + 14.9e6) / 2,  # mean of the up and the down launch
     "c1_linear": 22.1e6,                                 # the bf16 output stays dirty in L2
     "c3_nvfp4_qkv": 24.0e6 + 25.5e6,
-    "skinny_decode": 50.46e6 + 0.01e6,                   # the weight once; the result stays in L2
+    "skinny_decode": 50.47e6 + 0.01e6,                   # the weight once; the result stays in L2
     "attention_step": 160.5e6 + 32.7e6,                  # q, k, v once (K and V re-reads hit L2); the output partly stays in L2
 }
 

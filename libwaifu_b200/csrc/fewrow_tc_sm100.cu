@@ -3,24 +3,30 @@
 // once. Here the weight sits on the M side of tcgen05.mma and the rows are its N = 16, so that no
 // instruction of a CUDA core multiplies anything and the time does not depend on the row count
 // (the kernel in skinny_sm100.cu, which multiplies on mma.sync, takes 20 us for one row against
-// 16384 x 3072 and 36 us for sixteen; this one 17.4 us for either):
-//   warp 4     producer: per stage of 256 K positions one TMA copy of 128 weight rows x 256 e4m3
-//              bytes (as they lie) into a ring of two raw stages, and four copies of the 16 rows x
-//              128 bytes of x (128-byte swizzle) into a ring of four; the weight is read exactly once;
-//   warps 6-11 converters: widen a stage's weight bytes to half (cvt.rn.f16x2.e4m3x2, exact) into
-//              four 128-row x 128-byte tiles in the 128-byte swizzle (two such sets), and hand the
-//              raw stage back at once, so that its next load is on its way while the instructions
-//              run (with the raw stage held until those were done the kernel took 21 us);
-//   warp 5     one thread issues sixteen tcgen05.mma kind::f16 (M = 128 channels, N = 16 rows,
-//              K = 16) per stage into four accumulators in turn (4 x 128 x 16 floats in tensor
-//              memory); it waits and commits once per stage: every tcgen05 issue and every wait,
-//              even on a completed barrier, costs the thread some 80 cycles or more, and with
-//              hand-overs per 64 K positions the kernel took 25 us;
-//   warps 0-3  epilogue: a lane owns a channel, reads its 4 x 16 partial sums and adds them; scale,
-//              bias, residual, one rounding; for every row the warp stores 32 consecutive channels.
+// 16384 x 3072 and 36 us for sixteen; this one 12.7 us for either). The widened weight never
+// touches shared memory: the A operand of tcgen05.mma may lie in tensor memory (row i of the tile
+// in lane i, the sixteen halves of an instruction packed into eight columns), so shared memory
+// holds nothing but bytes as they came from HBM, six stages of 32 KB in flight per CTA.
+//   warp 8     producer: per stage of 256 K positions two TMA copies of 128 weight rows x 128 e4m3
+//              bytes (128-byte swizzle) into a ring of six raw stages, and four copies of the 16 rows
+//              x 128 bytes of x (128-byte swizzle) into a ring of four; the weight is read exactly once;
+//   warps 0-7  converters: a thread owns one of the 128 channels (warp % 4 is the quarter of tensor
+//              memory's lanes the warp may write, warp / 4 the half of the stage), reads 128 e4m3
+//              bytes of its row from the raw tile (the swizzle puts the 32 rows a warp reads in one
+//              instruction into different banks), widens them in registers (cvt.rn.f16x2.e4m3x2,
+//              exact), writes them with tcgen05.st into one of three units of 128 columns, and hands
+//              the raw stage back;
+//   warps 9-12 four threads issue the sixteen tcgen05.mma kind::f16 (M = 128 channels, N = 16 rows,
+//              K = 16) of a stage, four each, into two accumulators each in turn. Every tcgen05
+//              issue costs the issuing thread some 60 cycles: with one thread issuing all sixteen
+//              the kernel took 16.9 us, with two 14.0 us, with four 12.7 us;
+//   warps 0-3  then the epilogue: a lane owns a channel, reads its 8 x 16 partial sums and adds them;
+//              scale, bias, residual, one rounding; for every row the warp stores 32 consecutive
+//              channels.
 // A CTA owns 128 output channels and is paced by its own chain (load, widen, multiply) over the
-// k / 256 stages, two of them in flight: 17 us at k = 3072 for any channel count, so the kernel is
-// for wide weights. Every wait is bounded (status word, as everywhere else).
+// k / 256 stages, some 0.65 us each after 5 us of launch, first load and epilogue: 11 to 12.5 us at
+// k = 3072 for any channel count up to 148 x 128. Sixteen converter warps, on alternate stages or
+// on quarters of every stage, were no faster. Every wait is bounded (status word, as everywhere else).
 #include "fewrow_tc_sm100.cuh"
 
 #include <cuda.h>
@@ -34,30 +40,35 @@ namespace {
 
 constexpr int kChannels = 128;   // per CTA: the M of the instruction
 constexpr int kTokens = 16;      // its N
-constexpr int kBlockK = 64;      // K positions per block: 64 e4m3 bytes, 128 bytes of half, four instructions
+constexpr int kBlockK = 64;      // K positions per block: 128 bytes of an x row, four instructions
 constexpr int kBlocksPerStage = 4;
 constexpr int kStageK = kBlocksPerStage * kBlockK;     // K positions per ring stage
 constexpr int kRawWBytes = kChannels * kStageK;        // 32 KB
+constexpr int kAtomBytes = kChannels * 128;            // 128 rows x 128 e4m3 bytes, 128-byte swizzle
+constexpr int kAtoms = kStageK / 128;                  // 2 per stage
 constexpr int kXAtomBytes = kTokens * kBlockK * 2;     // 2 KB: a block's 16 rows x 128 bytes
 constexpr int kXBytes = kBlocksPerStage * kXAtomBytes; // 8 KB
-constexpr int kStages = 2;                             // of raw weight bytes: given back as soon as they are widened
+constexpr int kRawStages = 6;                          // of raw weight bytes: given back as soon as they are widened
 constexpr int kXStages = 4;                            // of x: given back when the instructions that read them are done
-constexpr int kWideBytes = kChannels * kBlockK * 2;    // 16 KB
-constexpr int kWideUnits = 2;                 // a unit: the four widened tiles of one stage
-constexpr int kWide = kWideUnits * kBlocksPerStage;
-constexpr int kChains = 4;                  // one accumulator per instruction of a block
-constexpr int kAccCols = kChains * kTokens;  // 64 columns of tensor memory
-constexpr int kProducerWarp = 4;
-constexpr int kMmaWarp = 5;
-constexpr int kConverterWarp0 = 6;
-constexpr int kConverterWarps = 6;
-constexpr int kThreads = (kConverterWarp0 + kConverterWarps) * 32;
-constexpr int kWideOff = 0;                               // 1024-byte aligned tiles first
-constexpr int kXOff = kWideOff + kWide * kWideBytes;      // then x's swizzled tiles
-constexpr int kRingOff = kXOff + kXStages * kXBytes;      // then the raw weight stages
-constexpr int kSmemBytes = kRingOff + kStages * kRawWBytes + 1024;
-static_assert(kXBytes % 1024 == 0 && kWideBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
-static_assert(kSmemBytes <= 227 * 1024, "shared memory");
+constexpr int kUnits = 3;                              // widened stages in tensor memory
+constexpr int kUnitCols = kStageK / 2;                 // 128 columns: 256 halves of a row, two to a column
+constexpr int kMmaWarps = 4;                           // W: threads that issue, one block of a stage each
+constexpr int kChains = 2;                             // C: accumulators per issuing thread, used in turn
+constexpr int kAccCols = kMmaWarps * kChains * kTokens;  // 128 columns
+constexpr int kUnitCol0 = kAccCols;
+constexpr int kTmemCols = 512;                         // 128 + 3 x 128; allocations are powers of two
+constexpr int kConvGroups = kAtoms;                    // warps 0..7 in groups of four
+constexpr int kConvWarps = 4 * kConvGroups;
+constexpr int kProducer = kConvWarps;
+constexpr int kMma = kProducer + 1;
+constexpr int kThreads = (kMma + kMmaWarps) * 32;
+constexpr int kRawOff = 0;
+constexpr int kXOff = kRawOff + kRawStages * kRawWBytes;
+constexpr int kSmemBytes = kXOff + kXStages * kXBytes + 1024;
+static_assert(kBlocksPerStage % kMmaWarps == 0, "the blocks of a stage are dealt evenly");
+static_assert(kUnitCol0 + kUnits * kUnitCols <= kTmemCols, "tensor memory");
+static_assert(kXBytes % 1024 == 0 && kAtomBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
+static_assert(kSmemBytes <= 227 * 1024 - 512, "shared memory");
 
 struct Params {
   const float *scale;
@@ -74,9 +85,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ __align__(8) uint64_t raw_full_bar[kStages], raw_empty_bar[kStages];
+  __shared__ __align__(8) uint64_t raw_full_bar[kRawStages], raw_empty_bar[kRawStages];
   __shared__ __align__(8) uint64_t x_full_bar[kXStages], x_empty_bar[kXStages];
-  __shared__ __align__(8) uint64_t wide_full_bar[kWideUnits], wide_empty_bar[kWideUnits];
+  __shared__ __align__(8) uint64_t unit_full_bar[kUnits], unit_empty_bar[kUnits];
   __shared__ __align__(8) uint64_t acc_full_bar;
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile uint32_t abort_flag;
@@ -84,32 +95,32 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * kChannels;
-  const int num_kb = p.k / kBlockK;                                  // blocks
-  const int num_stages = (num_kb + kBlocksPerStage - 1) / kBlocksPerStage;  // ring stages (the last may be part zeros)
+  const int num_kb = p.k / kBlockK;
+  const int num_stages = (num_kb + kBlocksPerStage - 1) / kBlocksPerStage;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kRawStages; ++s) {
       mbar_init(&raw_full_bar[s], 1);
-      mbar_init(&raw_empty_bar[s], kConverterWarps);
+      mbar_init(&raw_empty_bar[s], kConvWarps);
     }
     for (int s = 0; s < kXStages; ++s) {
       mbar_init(&x_full_bar[s], 1);
-      mbar_init(&x_empty_bar[s], 1);
+      mbar_init(&x_empty_bar[s], kMmaWarps);
     }
-    for (int w = 0; w < kWideUnits; ++w) {
-      mbar_init(&wide_full_bar[w], kConverterWarps);
-      mbar_init(&wide_empty_bar[w], 1);
+    for (int u = 0; u < kUnits; ++u) {
+      mbar_init(&unit_full_bar[u], kConvWarps);
+      mbar_init(&unit_empty_bar[u], kMmaWarps);
     }
-    mbar_init(&acc_full_bar, 1);
+    mbar_init(&acc_full_bar, kMmaWarps);
     fence_barrier_init();
   }
-  if (warp == kProducerWarp && lane == 0) {
+  if (warp == kProducer && lane == 0) {
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_x);
   }
-  if (warp == kMmaWarp) {
-    tmem_alloc<1>(&tmem_base_slot, kAccCols);
+  if (warp == kMma) {
+    tmem_alloc<1>(&tmem_base_slot, kTmemCols);
     tmem_relinquish<1>();
   }
   tc_fence_before_sync();
@@ -120,21 +131,23 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
   griddep_launch_dependents();
 
   auto stage_x = [&](int s) { return smem + kXOff + s * kXBytes; };
-  auto stage_w = [&](int s) { return smem + kRingOff + s * kRawWBytes; };
-  auto wide = [&](int w) { return smem + kWideOff + w * kWideBytes; };
+  auto stage_w = [&](int s) { return smem + kRawOff + s * kRawWBytes; };
 
-  if (warp == kProducerWarp) {
+  if (warp == kProducer) {
     if (lane == 0) {
       bool ok = true;
       for (int st = 0; st < num_stages && ok; ++st) {
-        const int s = st % kStages, xs = st % kXStages;
-        if (!mbar_wait(&raw_empty_bar[s], ((st / kStages) & 1) ^ 1, &abort_flag) ||
+        const int s = st % kRawStages, xs = st % kXStages;
+        if (!mbar_wait(&raw_empty_bar[s], ((st / kRawStages) & 1) ^ 1, &abort_flag) ||
             !mbar_wait(&x_empty_bar[xs], ((st / kXStages) & 1) ^ 1, &abort_flag)) {
           ok = false;
           break;
         }
         mbar_arrive_expect_tx(&raw_full_bar[s], kRawWBytes);  // (bytes past the end of a row arrive as zeros)
-        tma_load_2d(stage_w(s), &tmap_w, &raw_full_bar[s], st * kStageK, n0);
+#pragma unroll
+        for (int a = 0; a < kAtoms; ++a) {
+          tma_load_2d(stage_w(s) + a * kAtomBytes, &tmap_w, &raw_full_bar[s], st * kStageK + a * 128, n0);
+        }
         mbar_arrive_expect_tx(&x_full_bar[xs], kXBytes);
 #pragma unroll
         for (int j = 0; j < kBlocksPerStage; ++j) {
@@ -146,33 +159,35 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         atomicCAS(p.status, 0u, kStatusFewRowTcTimeout);
       }
     }
-  } else if (warp == kMmaWarp) {
+  } else if (warp >= kMma && warp < kMma + kMmaWarps) {
     if (lane == 0) {
+      // Every tcgen05 issue costs the issuing thread some 90 cycles, sixteen of them per stage more
+      // than the stage's bytes take to arrive: the blocks of a stage are dealt to four threads.
+      const int mw = static_cast<int>(warp) - kMma;
       const uint32_t idesc = umma_idesc(kChannels, kTokens, 0u, 0u);
-      const uint64_t wdesc0 = umma_desc_sw128(smem_u32(wide(0)));
       const uint64_t xdesc0 = umma_desc_sw128(smem_u32(stage_x(0)));
+      const uint32_t acc0 = tmem_base + mw * kChains * kTokens;
+      uint32_t issued = 0;
       bool ok = true;
-      // One wait and two commits per stage of four blocks: the thread's own instructions (each
-      // tcgen05 issue, each wait on a completed barrier is some 80 cycles) are what a few-row
-      // product has to keep off the path of the bytes.
       for (int st = 0; st < num_stages && ok; ++st) {
-        const int xs = st % kXStages, u = st % kWideUnits;
-        if (!mbar_wait(&wide_full_bar[u], (st / kWideUnits) & 1, &abort_flag) ||
+        const int xs = st % kXStages, u = st % kUnits;
+        if (!mbar_wait(&unit_full_bar[u], (st / kUnits) & 1, &abort_flag) ||
             !mbar_wait(&x_full_bar[xs], (st / kXStages) & 1, &abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
         const int blocks = min(kBlocksPerStage, num_kb - st * kBlocksPerStage);
-        for (int j = 0; j < blocks; ++j) {
-          const uint64_t wd = wdesc0 + static_cast<uint64_t>((u * kBlocksPerStage + j) * (kWideBytes >> 4));
+        const uint32_t a_tmem = tmem_base + kUnitCol0 + u * kUnitCols;
+        for (int j = mw; j < blocks; j += kMmaWarps) {
           const uint64_t xd = xdesc0 + static_cast<uint64_t>((xs * kXBytes + j * kXAtomBytes) >> 4);
 #pragma unroll
-          for (int i = 0; i < kChains; ++i) {  // 16 K positions = 32 bytes of a row each
-            umma_ss<kKindF16>(tmem_base + i * kTokens, wd + i * 2, xd + i * 2, idesc, (st > 0 || j > 0) ? 1u : 0u);
+          for (int i = 0; i < 4; ++i) {  // 16 K positions: eight columns of the unit, 32 bytes of an x row
+            umma_ts_f16(acc0 + (issued % kChains) * kTokens, a_tmem + (j * 4 + i) * 8, xd + i * 2, idesc, issued >= kChains ? 1u : 0u);
+            ++issued;
           }
         }
-        umma_commit(&wide_empty_bar[u]);
+        umma_commit(&unit_empty_bar[u]);
         umma_commit(&x_empty_bar[xs]);
       }
       if (ok) umma_commit(&acc_full_bar);
@@ -181,79 +196,87 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         atomicCAS(p.status, 0u, kStatusFewRowTcTimeout);
       }
     }
-  } else if (warp >= kConverterWarp0) {
-    // 16 e4m3 bytes of a row -> 16 halves = two 16-byte pieces of the row's 128 bytes in the
-    // 128-byte swizzle (piece index xor row % 8).
-    const int cw = static_cast<int>(warp) - kConverterWarp0;
+  } else if (warp < kProducer) {
+    const uint32_t quarter = warp & 3;                       // the lanes of tensor memory this warp may touch
+    const uint32_t group = warp >> 2;
+    const uint32_t atom = group;                             // which 128 K positions of the stage
+    const uint32_t row = quarter * 32 + lane;                // the channel this thread widens
+    const uint32_t row_off = atom * kAtomBytes + row * 128, sw = row & 7;
+    const uint32_t t_row = tmem_base + ((quarter * 32u) << 16) + kUnitCol0 + atom * (kUnitCols / kAtoms);
     bool ok = true;
     for (int st = 0; st < num_stages && ok; ++st) {
-      const int s = st % kStages, u = st % kWideUnits;
-      if (!mbar_wait(&raw_full_bar[s], (st / kStages) & 1, &abort_flag) ||
-          !mbar_wait(&wide_empty_bar[u], ((st / kWideUnits) & 1) ^ 1, &abort_flag)) {
+      const int s = st % kRawStages, u = st % kUnits;
+      if (!mbar_wait(&raw_full_bar[s], (st / kRawStages) & 1, &abort_flag) ||
+          !mbar_wait(&unit_empty_bar[u], ((st / kUnits) & 1) ^ 1, &abort_flag)) {
         ok = false;
         break;
       }
-      const uint8_t *raw = stage_w(s);
-      // a stage: 128 rows x 16 pieces of 16 e4m3 bytes; piece (r, c) belongs to block c / 4
-#pragma unroll 4
-      for (int piece = cw * 32 + static_cast<int>(lane); piece < kChannels * 16; piece += kConverterWarps * 32) {
-        const uint32_t r = static_cast<uint32_t>(piece) >> 4, c = static_cast<uint32_t>(piece) & 15;
-        const uint32_t j = c >> 2, q = c & 3;
-        const uint4 v = *reinterpret_cast<const uint4 *>(raw + piece * 16);
-        uint4 lo, hi;
-        e4m3x4_to_f16x4(v.x, &lo.x, &lo.y);
-        e4m3x4_to_f16x4(v.y, &lo.z, &lo.w);
-        e4m3x4_to_f16x4(v.z, &hi.x, &hi.y);
-        e4m3x4_to_f16x4(v.w, &hi.z, &hi.w);
-        uint8_t *row_base = wide(u * kBlocksPerStage + j) + r * 128;
-        *reinterpret_cast<uint4 *>(row_base + (((2 * q) ^ (r & 7)) << 4)) = lo;
-        *reinterpret_cast<uint4 *>(row_base + (((2 * q + 1) ^ (r & 7)) << 4)) = hi;
+      tc_fence_after_sync();  // the instructions that read this unit last are done
+      const uint8_t *raw = stage_w(s) + row_off;
+#pragma unroll
+      for (uint32_t pp = 0; pp < 4; ++pp) {  // two 16-byte pieces -> 32 halves -> 16 columns
+        const uint4 v0 = *reinterpret_cast<const uint4 *>(raw + (((2 * pp) ^ sw) << 4));
+        const uint4 v1 = *reinterpret_cast<const uint4 *>(raw + (((2 * pp + 1) ^ sw) << 4));
+        uint32_t w[16];
+        e4m3x4_to_f16x4(v0.x, &w[0], &w[1]);
+        e4m3x4_to_f16x4(v0.y, &w[2], &w[3]);
+        e4m3x4_to_f16x4(v0.z, &w[4], &w[5]);
+        e4m3x4_to_f16x4(v0.w, &w[6], &w[7]);
+        e4m3x4_to_f16x4(v1.x, &w[8], &w[9]);
+        e4m3x4_to_f16x4(v1.y, &w[10], &w[11]);
+        e4m3x4_to_f16x4(v1.z, &w[12], &w[13]);
+        e4m3x4_to_f16x4(v1.w, &w[14], &w[15]);
+        tmem_st_32x16(t_row + u * kUnitCols + pp * 16, w);
       }
-      fence_proxy_async_smem();  // the UMMA reads these bytes through the async proxy
+      tmem_st_wait();
+      tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&raw_empty_bar[s]);  // the raw bytes have been read: the stage may be refilled at once
-        mbar_arrive(&wide_full_bar[u]);
+        mbar_arrive(&raw_empty_bar[s]);
+        mbar_arrive(&unit_full_bar[u]);
       }
     }
     if (!ok && lane == 0) {
       abort_flag = 1;
       atomicCAS(p.status, 0u, kStatusFewRowTcTimeout);
     }
-  } else {
-    // ------------------------------------------------------------------ epilogue
-    const bool ok = mbar_wait(&acc_full_bar, 0, &abort_flag);
-    if (__all_sync(0xffffffffu, ok)) {
-      tc_fence_after_sync();
-      uint32_t v[16];
-      tmem_ld_32x16(tmem_base + ((warp * 32u) << 16), v);
-      tmem_ld_wait(v);
-#pragma unroll
-      for (int c = 1; c < kChains; ++c) {
-        uint32_t u[16];
-        tmem_ld_32x16(tmem_base + ((warp * 32u) << 16) + c * kTokens, u);
-        tmem_ld_wait(u);
-#pragma unroll
-        for (int t = 0; t < kTokens; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) + __uint_as_float(u[t]));
-      }
-      const int channel = n0 + static_cast<int>(warp) * 32 + static_cast<int>(lane);
-      if (channel < p.n) {
-        const float scale = __ldg(p.scale);
-        const float bias = p.bias ? __half2float(reinterpret_cast<const __half *>(p.bias)[channel]) : 0.0f;
-        const __half *res = reinterpret_cast<const __half *>(p.residual);
-        __half *out = reinterpret_cast<__half *>(p.out);
-#pragma unroll
-        for (int t = 0; t < kTokens; ++t) {
-          if (t < p.m) {
-            float y = __uint_as_float(v[t]) * scale + bias;
-            if (res) y += __half2float(res[static_cast<long long>(t % p.residual_rows) * p.residual_ld + channel]);
-            out[static_cast<long long>(t) * p.n + channel] = __float2half_rn(y);
+    // -------------------------------------------------------------- epilogue: the first four warps
+    if (warp < 4 && __all_sync(0xffffffffu, ok)) {
+      ok = mbar_wait(&acc_full_bar, 0, &abort_flag);
+      if (__all_sync(0xffffffffu, ok)) {
+        tc_fence_after_sync();
+        uint32_t v[16];
+        tmem_ld_32x16(tmem_base + ((warp * 32u) << 16), v);
+        tmem_ld_wait(v);
+  #pragma unroll
+        for (int c = 1; c < kMmaWarps * kChains; ++c) {
+          uint32_t u[16];
+          tmem_ld_32x16(tmem_base + ((warp * 32u) << 16) + c * kTokens, u);
+          tmem_ld_wait(u);
+          if (c / kChains < num_kb) {  // (an issuing warp beyond the last block of a short product wrote nothing)
+  #pragma unroll
+            for (int t = 0; t < kTokens; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) + __uint_as_float(u[t]));
           }
         }
+        const int channel = n0 + static_cast<int>(warp) * 32 + static_cast<int>(lane);
+        if (channel < p.n) {
+          const float scale = __ldg(p.scale);
+          const float bias = p.bias ? __half2float(reinterpret_cast<const __half *>(p.bias)[channel]) : 0.0f;
+          const __half *res = reinterpret_cast<const __half *>(p.residual);
+          __half *out = reinterpret_cast<__half *>(p.out);
+  #pragma unroll
+          for (int t = 0; t < kTokens; ++t) {
+            if (t < p.m) {
+              float y = __uint_as_float(v[t]) * scale + bias;
+              if (res) y += __half2float(res[static_cast<long long>(t % p.residual_rows) * p.residual_ld + channel]);
+              out[static_cast<long long>(t) * p.n + channel] = __float2half_rn(y);
+            }
+          }
+        }
+      } else if (lane == 0) {
+        abort_flag = 1;
+        atomicCAS(p.status, 0u, kStatusFewRowTcTimeout);
       }
-    } else if (lane == 0) {
-      abort_flag = 1;
-      atomicCAS(p.status, 0u, kStatusFewRowTcTimeout);
     }
   }
 
@@ -263,9 +286,9 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     for (int i = 0; i < 64; ++i) __nanosleep(2000);  // copies that may still be in flight
     __syncthreads();
   }
-  if (warp == kMmaWarp) {
+  if (warp == kMma) {
     tc_fence_after_sync();
-    tmem_dealloc<1>(tmem_base, kAccCols);
+    tmem_dealloc<1>(tmem_base, kTmemCols);
   }
 }
 
@@ -315,7 +338,8 @@ cudaError_t fewrow_tc_matmul(const void *x, int m, int n, int k, const uint8_t *
                              cudaStream_t stream, const char **why) {
   *why = "";
   CUtensorMap tw, tx;
-  if (!make_map(&tw, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), kStageK, kChannels, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+  const bool w_ok = make_map(&tw, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 128, kChannels, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!w_ok ||
       !make_map(&tx, x, static_cast<uint64_t>(m), static_cast<uint64_t>(k) * 2, kBlockK * 2, kTokens,
                 CU_TENSOR_MAP_SWIZZLE_128B)) {
     *why = "cuTensorMapEncodeTiled refused an operand";

@@ -1,5 +1,6 @@
 // The reference-compatible product for at most 16 half rows on tensor cores: the weight on the M
-// side of tcgen05.mma, the rows as N = 16 (see fewrow_tc_sm100.cu).
+// side of tcgen05.mma, widened from shared memory into tensor memory, the rows as N = 16 (see
+// fewrow_tc_sm100.cu).
 #pragma once
 
 #include <cuda_runtime.h>

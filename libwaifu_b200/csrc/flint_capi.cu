@@ -1104,15 +1104,18 @@ int32_t fl_fp8_matmul_add(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tens
       std::vector<int64_t> bt;
       if (addend) quick = plan_addend(*addend, out, &bs, &bt);
       // Half rows against many channels: the weight on the M side of the tensor-core instruction
-      // (fewrow_tc_sm100.cu). Its time, 17 us at 3072-deep rows, depends neither on the row count
-      // nor much on the channel count (a CTA per 128 channels, paced by its own chain of stages),
-      // so it takes the products the kernel underneath is slower on, as measured: any row count
-      // from 16384 channels, four rows or more from 12288, eight or more from 8192.
+      // (fewrow_tc_sm100.cu). Its time, 5 us and 0.65 us per 256 K positions, depends neither on
+      // the row count nor on the channel count up to 148 x 128 (a CTA per 128 channels, paced by
+      // its own chain of stages), so it takes the products the kernel underneath is slower on, as
+      // measured at 3072- and 12288-deep rows: any row count from 8192 channels, two rows or more
+      // from 6144, eight or more from 3072; on shallower rows, where its fixed part weighs more,
+      // only what was measured there.
       static const bool no_fewrow_tc = [] {
         const char *e = std::getenv("FLINT_SM100_NO_FEWROW_TC");
         return e && e[0] == '1';
       }();
-      const bool fewrow_tc_wins = rows >= 16384 || (rows >= 12288 && m >= 4) || (rows >= 8192 && m >= 8);
+      const bool fewrow_tc_wins = k >= 2048 ? rows >= 8192 || (rows >= 6144 && m >= 2) || (rows >= 3072 && m >= 8)
+                                            : rows >= 16384 || (rows >= 12288 && m >= 4) || (rows >= 8192 && m >= 8);
       if (!no_skinny && !no_fewrow_tc && !quick.needs_expand && fewrow_tc_wins &&
           fewrow_tc_supported(m, rows, k, is_bf16, raw_ptr(a), raw_ptr(weight), raw_ptr(out)) &&
           (!quick.residual || quick.residual_rows > 0)) {

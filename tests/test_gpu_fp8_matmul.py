@@ -220,11 +220,12 @@ def test_bf16_variant(flint, oracle):
 
 
 # (half rows against wide weights, k a multiple of 64, run with the weight on the tensor cores' M
-# side: the first shape and the last four, one of them with a ragged last tile of channels and a
-# last stage that is part zeros)
+# side: the first shape and the last eight, among them ragged last tiles of channels, last stages
+# with one, two and three of their four blocks, and more CTAs than the GPU has SMs)
 @pytest.mark.parametrize("m,n,k,bf16", [(1, 16384, 3072, False), (16, 264, 3072, True), (9, 72, 12288, False),
                                         (5, 4096, 80, True), (2, 64, 4112, False), (7, 72, 6160, True), (3, 136, 1040, False),
-                                        (16, 12288, 64, False), (11, 12296, 4160, False), (4, 18432, 3072, False), (8, 8200, 320, False)])
+                                        (16, 12288, 64, False), (11, 12296, 4160, False), (4, 18432, 3072, False), (8, 8200, 320, False),
+                                        (1, 8192, 2240, False), (2, 6144, 2112, False), (8, 3080, 2176, False), (16, 24576, 2048, False)])
 def test_few_rows(flint, oracle, m, n, k, bf16):
     """At most 16 rows take the one-launch path that widens the weight in registers; the first
     shape is the reference's decode benchmark (docs/fp8.md:225-244)."""
