@@ -30,6 +30,7 @@
 #include "fewrow_tc_sm100.cuh"
 
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "ptx_sm100.cuh"
@@ -292,6 +293,214 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
   }
 }
 
+// ---- e4m3 rows against an e4m3 weight (fl_fp8_linear's product after its quantiser) ------------
+//
+// Both operands are what tcgen05.mma kind::f8f6f4 multiplies, so nothing touches the weight
+// between shared memory and the tensor core: the weight on the M side again (128 channels per
+// CTA), up to 64 rows as N, K = 32 per instruction. A stage is 256 K positions: two 128-byte
+// swizzle atoms of the weight (32 KB) and two of the rows (N x 128 bytes each); as many stages
+// as fit (six for 16 rows, four for 64). Four threads issue two of a stage's eight instructions
+// each into two accumulators each in turn; warps 0-3 are the epilogue (a lane per channel): the
+// eight partial sums, then the tile kernel's arithmetic in its order: acc * (row scale * channel
+// scale), + bias, GELU, + residual, one rounding.
+namespace q8 {
+
+constexpr int kMaxTokens = 64;
+constexpr int kMaxStages = 6;
+constexpr int kIssuers = 4;
+constexpr int kQChains = 2;
+constexpr int kQProducer = 4;
+constexpr int kQMma = 5;
+constexpr int kQThreads = (kQMma + kIssuers) * 32;
+constexpr int kSmemLimit = 227 * 1024 - 1024;  // (static shared memory beside it)
+
+struct QParams {
+  const float *row_scale;
+  const float *col_scale;
+  int col_scale_scalar;
+  const void *bias;
+  const void *residual;
+  int residual_rows;
+  long long residual_ld;
+  int act, is_bf16;
+  void *out;
+  int m, n, k;
+  int ntok;    // N of the instruction: the rows rounded up to a multiple of 16
+  int stages;
+  uint32_t tmem_cols;
+  uint32_t *status;
+};
+
+__device__ __forceinline__ float gelu_tanh_q(float x) {
+  // x / (1 + 2^z), z = x (c0 + c1 x^2): the tile kernel's form of the tanh GELU, bit for bit.
+  constexpr float kC0 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;
+  constexpr float kC1 = kC0 * 0.044715f;
+  const float z = x * fmaf(x * x, kC1, kC0);
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+  return x * r;
+}
+
+__global__ void __launch_bounds__(kQThreads, 1)
+fewrow_q8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const QParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t acc_full_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ volatile uint32_t abort_flag;
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * kChannels;
+  const int num_stages = (p.k + kStageK - 1) / kStageK;  // (the last may be part zeros)
+  const int x_atom = p.ntok * 128;
+  const int stage_bytes = kRawWBytes + kAtoms * x_atom;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kIssuers);
+    }
+    mbar_init(&acc_full_bar, kIssuers);
+    fence_barrier_init();
+  }
+  if (warp == kQProducer && lane == 0) {
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == kQMma) {
+    tmem_alloc<1>(&tmem_base_slot, p.tmem_cols);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+  griddep_wait();
+  griddep_launch_dependents();
+
+  if (warp == kQProducer) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int st = 0; st < num_stages && ok; ++st) {
+        const int s = st % p.stages;
+        if (!mbar_wait(&empty_bar[s], ((st / p.stages) & 1) ^ 1, &abort_flag)) {
+          ok = false;
+          break;
+        }
+        uint8_t *base = smem + s * stage_bytes;
+        mbar_arrive_expect_tx(&full_bar[s], static_cast<uint32_t>(stage_bytes));  // (bytes outside arrive as zeros)
+#pragma unroll
+        for (int a = 0; a < kAtoms; ++a) {
+          tma_load_2d(base + a * kAtomBytes, &tmap_w, &full_bar[s], st * kStageK + a * 128, n0);
+          tma_load_2d(base + kRawWBytes + a * x_atom, &tmap_x, &full_bar[s], st * kStageK + a * 128, 0);
+        }
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(p.status, 0u, kStatusFewRowTcTimeout);
+      }
+    }
+  } else if (warp >= kQMma) {
+    if (lane == 0) {
+      const int mw = static_cast<int>(warp) - kQMma;
+      const uint32_t idesc = umma_idesc(kChannels, static_cast<uint32_t>(p.ntok), 0u, 0u);
+      const uint32_t acc0 = tmem_base + mw * kQChains * p.ntok;
+      // this thread's two instructions of a stage: 32-byte steps 2 mw and 2 mw + 1 of the eight
+      const uint32_t atom = mw >> 1, step0 = (mw & 1) * 2;
+      bool ok = true;
+      for (int st = 0; st < num_stages && ok; ++st) {
+        const int s = st % p.stages;
+        if (!mbar_wait(&full_bar[s], (st / p.stages) & 1, &abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t base = smem_u32(smem + s * stage_bytes);
+        const uint64_t wd = umma_desc_sw128(base + atom * kAtomBytes) + step0 * 2;
+        const uint64_t xd = umma_desc_sw128(base + kRawWBytes + atom * x_atom) + step0 * 2;
+#pragma unroll
+        for (int i = 0; i < kQChains; ++i) {
+          umma_ss<kKindF8>(acc0 + i * p.ntok, wd + i * 2, xd + i * 2, idesc, st > 0 ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      if (ok) umma_commit(&acc_full_bar);
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(p.status, 0u, kStatusFewRowTcTimeout);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 0-3)
+    const bool ok = mbar_wait(&acc_full_bar, 0, &abort_flag);
+    if (__all_sync(0xffffffffu, ok)) {
+      tc_fence_after_sync();
+      const int channel = n0 + static_cast<int>(warp) * 32 + static_cast<int>(lane);
+      const bool live = channel < p.n;
+      const float cs = p.col_scale ? __ldg(p.col_scale + (p.col_scale_scalar || !live ? 0 : channel)) : 1.0f;
+      const uint16_t *bias16 = reinterpret_cast<const uint16_t *>(p.bias);
+      float bias = 0.0f;
+      if (bias16 && live) {
+        const uint16_t b = bias16[channel];
+        bias = p.is_bf16 ? __uint_as_float(static_cast<uint32_t>(b) << 16) : __half2float(__ushort_as_half(b));
+      }
+      const uint16_t *res = reinterpret_cast<const uint16_t *>(p.residual);
+      uint16_t *out = reinterpret_cast<uint16_t *>(p.out);
+      for (int t0 = 0; t0 < p.m; t0 += 16) {
+        uint32_t v[16];
+        tmem_ld_32x16(tmem_base + ((warp * 32u) << 16) + t0, v);
+        tmem_ld_wait(v);
+#pragma unroll
+        for (int c = 1; c < kIssuers * kQChains; ++c) {
+          uint32_t u[16];
+          tmem_ld_32x16(tmem_base + ((warp * 32u) << 16) + c * p.ntok + t0, u);
+          tmem_ld_wait(u);
+#pragma unroll
+          for (int t = 0; t < 16; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) + __uint_as_float(u[t]));
+        }
+        if (live) {
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            const int row = t0 + t;
+            if (row < p.m) {
+              const float rs = p.row_scale ? __ldg(p.row_scale + row) : 1.0f;
+              float y = __uint_as_float(v[t]) * (rs * cs);
+              if (bias16) y += bias;
+              if (p.act == 1) y = gelu_tanh_q(y);
+              if (res) {
+                const uint16_t r16 = res[static_cast<long long>(row % p.residual_rows) * p.residual_ld + channel];
+                y += p.is_bf16 ? __uint_as_float(static_cast<uint32_t>(r16) << 16) : __half2float(__ushort_as_half(r16));
+              }
+              out[static_cast<long long>(row) * p.n + channel] =
+                  p.is_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(y)) : __half_as_ushort(__float2half_rn(y));
+            }
+          }
+        }
+      }
+    } else if (lane == 0) {
+      abort_flag = 1;
+      atomicCAS(p.status, 0u, kStatusFewRowTcTimeout);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (abort_flag != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);  // copies that may still be in flight
+    __syncthreads();
+  }
+  if (warp == kQMma) {
+    tc_fence_after_sync();
+    tmem_dealloc<1>(tmem_base, p.tmem_cols);
+  }
+}
+
+}  // namespace q8
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -376,6 +585,74 @@ cudaError_t fewrow_tc_matmul(const void *x, int m, int n, int k, const uint8_t *
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, fewrow_tc_kernel, tw, tx, p);
+  if (e != cudaSuccess) *why = "kernel launch failed";
+  return e;
+}
+
+bool fewrow_q8_supported(int m, int n, int k, const void *codes, const void *w, const void *out) {
+  if (m < 1 || m > q8::kMaxTokens || n < 8 || n % 8 != 0 || k < 16 || k % 16 != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(codes) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(out) & 1)) {
+    return false;
+  }
+  return encode_fn() != nullptr;
+}
+
+cudaError_t fewrow_q8_linear(const uint8_t *codes, const float *row_scale, int m, int n, int k, const uint8_t *w,
+                             const float *col_scale, int col_scale_scalar, const void *bias, const void *residual,
+                             int residual_rows, int64_t residual_ld, int act, int is_bf16, void *out, uint32_t *status,
+                             cudaStream_t stream, const char **why) {
+  *why = "";
+  const int ntok = (m + 15) / 16 * 16;
+  CUtensorMap tw, tx;
+  if (!make_map(&tw, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 128, kChannels, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_map(&tx, codes, static_cast<uint64_t>(m), static_cast<uint64_t>(k), 128, static_cast<uint32_t>(ntok),
+                CU_TENSOR_MAP_SWIZZLE_128B)) {
+    *why = "cuTensorMapEncodeTiled refused an operand";
+    return cudaErrorInvalidValue;
+  }
+  const int stage_bytes = kRawWBytes + kAtoms * ntok * 128;
+  int stages = q8::kSmemLimit / stage_bytes;
+  if (stages > q8::kMaxStages) stages = q8::kMaxStages;
+  const int smem_bytes = stages * stage_bytes + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(q8::fewrow_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, q8::kSmemLimit);
+    if (e != cudaSuccess) {
+      *why = "cudaFuncSetAttribute(max dynamic shared memory) failed";
+      return e;
+    }
+    attr_set = true;
+  }
+  q8::QParams p = {};
+  p.row_scale = row_scale;
+  p.col_scale = col_scale;
+  p.col_scale_scalar = col_scale_scalar;
+  p.bias = bias;
+  p.residual = residual;
+  p.residual_rows = residual_rows > 0 ? residual_rows : 1;
+  p.residual_ld = residual_ld;
+  p.act = act;
+  p.is_bf16 = is_bf16;
+  p.out = out;
+  p.m = m;
+  p.n = n;
+  p.k = k;
+  p.ntok = ntok;
+  p.stages = stages;
+  const int acc_cols = q8::kIssuers * q8::kQChains * ntok;
+  p.tmem_cols = acc_cols <= 128 ? 128u : acc_cols <= 256 ? 256u : 512u;
+  p.status = status;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>((n + kChannels - 1) / kChannels), 1, 1);
+  cfg.blockDim = dim3(q8::kQThreads, 1, 1);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, q8::fewrow_q8_kernel, tw, tx, p);
   if (e != cudaSuccess) *why = "kernel launch failed";
   return e;
 }

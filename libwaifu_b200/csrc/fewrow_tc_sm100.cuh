@@ -21,4 +21,15 @@ cudaError_t fewrow_tc_matmul(const void *x, int m, int n, int k, const uint8_t *
                              const void *residual, int residual_rows, int64_t residual_ld, void *out, uint32_t *status,
                              cudaStream_t stream, const char **why);
 
+// e4m3 rows (a quantiser's codes, one <float> scale per row) against an e4m3 weight, for at most
+// 64 rows: k a multiple of 16, n a multiple of 8, codes and w 16-byte aligned.
+bool fewrow_q8_supported(int m, int n, int k, const void *codes, const void *w, const void *out);
+
+// out (m, n) = round16( act( (codes . w^T) * (row_scale[row] * col_scale[channel or 0]) + bias ) + residual ),
+// the arithmetic of fl_fp8_linear's epilogue in its order (fp32 accumulation). One launch, no scratch.
+cudaError_t fewrow_q8_linear(const uint8_t *codes, const float *row_scale, int m, int n, int k, const uint8_t *w,
+                             const float *col_scale, int col_scale_scalar, const void *bias, const void *residual,
+                             int residual_rows, int64_t residual_ld, int act, int is_bf16, void *out, uint32_t *status,
+                             cudaStream_t stream, const char **why);
+
 }  // namespace flsm100

@@ -1455,6 +1455,36 @@ int32_t fl_add(fl_operators_t operators, fl_tensor_view_t a_h, fl_tensor_view_t 
 // ============================ Part 2 ==========================================================
 
 namespace {
+// At most 32 quantised rows against a wide weight: the weight on the M side of the tensor-core
+// instruction (fewrow_tc_sm100.cu, fewrow_q8_kernel), where the tile kernel would stream it through
+// the few SMs its tiles land on. `fewrow_q8_wins` is where it measured faster, quantiser launch
+// included, than the tile kernel and (at most four rows) the one-launch kernel of skinny_sm100.cu,
+// over 1-128 rows, 3072-18432 channels, k = 3072 and 12288: e.g. 16 x 16384 x 3072 14.5 us against
+// 20.5, 1 x 16384 x 12288 35.4 against 63.0 (5.7 TB/s of weight); from 64 rows on the tile kernel
+// is level or ahead.
+bool fewrow_q8_wins(int m, int rows, int k) {
+  static const bool off = [] {
+    const char *a = std::getenv("FLINT_SM100_NO_SKINNY"), *b = std::getenv("FLINT_SM100_NO_FEWROW_TC");
+    return (a && a[0] == '1') || (b && b[0] == '1');
+  }();
+  if (off || m > 32 || k < 2048) return false;
+  return m >= 4 ? rows >= 3072 : rows >= 8192;
+}
+
+// Runs it if it wins and can take the operands; false when the tile kernel should run.
+bool try_fewrow_q8(const uint8_t *codes, const float *row_scales, int m, int rows, int k, const void *w,
+                   const Epilogue &ep, int is_bf16, void *out, uint32_t *status) {
+  if (ep.row_amax != nullptr || ep.num_extra_out != 0 || ep.out_ld != 0) return false;
+  if (!fewrow_q8_wins(m, rows, k) || !fewrow_q8_supported(m, rows, k, codes, w, out)) return false;
+  const char *why = "";
+  cudaError_t e = fewrow_q8_linear(codes, row_scales, m, rows, k, reinterpret_cast<const uint8_t *>(w), ep.col_scale,
+                                   ep.col_scale_scalar, ep.bias, ep.residual, ep.residual_rows, ep.residual_ld, ep.act,
+                                   is_bf16, out, status, 0, &why);
+  if (e != cudaSuccess) cuda_check(e, (std::string("few-row FP8 linear: ") + why).c_str());
+  ++g_gemm_launches;
+  return true;
+}
+
 int32_t fp8_linear_impl(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor_view_t scales_h,
                         fl_tensor_view_t bias_h, fl_tensor_view_t residual_h, int32_t act, fl_tensor_view_t out_h,
                         fl_tensor_view_t row_amax_h, bool want_amax) {
@@ -1512,7 +1542,7 @@ int32_t fp8_linear_impl(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor
       row_amax = reinterpret_cast<float *>(raw_ptr(am));
       cuda_check(cudaMemsetAsync(row_amax, 0, static_cast<size_t>(m) * sizeof(float), 0), "clearing the row maxima");
     }
-    if (!want_amax && !no_skinny && m <= 4 &&
+    if (!want_amax && !no_skinny && m <= 4 && !(aligned16(raw_ptr(weight)) && fewrow_q8_wins(m, rows, k)) &&
         skinny_fp8_supported(m, rows, k, raw_ptr(a), raw_ptr(weight), raw_ptr(out), residual != nullptr)) {
       cuda_check(skinny_fp8_linear(raw_ptr(a), is_bf16, m, rows, k, raw_ptr(weight),
                                    reinterpret_cast<const float *>(raw_ptr(scales)), numel_of(scales) == 1 ? 1 : 0,
@@ -1552,6 +1582,7 @@ int32_t fp8_linear_impl(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tensor
     }
     ep.act = act;
     ep.row_amax = row_amax;
+    if (try_fewrow_q8(codes, row_scales, m, rows, k, w_ptr, ep, is_bf16, raw_ptr(out), status_word())) return clear_error();
     run_gemm(kGemmE4M3, m, rows, k, codes, w_ptr, nullptr, nullptr, ep, is_bf16, raw_ptr(out));
     return clear_error();
   });
@@ -2141,6 +2172,10 @@ int32_t fp8_linear_quantized_impl(fl_tensor_view_t codes_h, fl_tensor_view_t row
       ep.out_col0 = col0;
       for (int i = 0; i < sd.num_extra; ++i) ep.extra_out[ep.num_extra_out++] = sd.extra[i];
     }
+    if (out_h && try_fewrow_q8(reinterpret_cast<const uint8_t *>(a_ptr), ep.row_scale, m, rows, k, w_ptr, ep,
+                               out_dtype == FL_DTYPE_BFLOAT16, sd.first, status_word())) {
+      return clear_error();
+    }
     run_gemm(kGemmE4M3, m, rows, k, a_ptr, w_ptr, nullptr, nullptr, ep, out_dtype == FL_DTYPE_BFLOAT16, sd.first);
     return clear_error();
   });
@@ -2628,6 +2663,20 @@ int32_t fl_fp8_linear_static(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_t
     }
 
     cuda_check(quantize_fp8_act(raw_ptr(a), is_bf16, m, k, codes, row_scales, 0), "quantising the activation");
+
+    {
+      Epilogue ep;
+      ep.col_scale = reinterpret_cast<const float *>(raw_ptr(scales));
+      ep.col_scale_scalar = numel_of(scales) == 1 ? 1 : 0;
+      ep.bias = bias ? raw_ptr(*bias) : nullptr;
+      if (residual) {
+        ep.residual = raw_ptr(*residual);
+        ep.residual_rows = m;
+        ep.residual_ld = rows;
+      }
+      ep.act = act;
+      if (try_fewrow_q8(codes, row_scales, m, rows, k, raw_ptr(weight), ep, is_bf16, raw_ptr(out), status)) return clear_error();
+    }
 
     GemmArgs g{};
     g.kind = kGemmE4M3;

@@ -102,6 +102,51 @@ def test_few_rows(flint, oracle, m, n, k, is_bf16):
         check_parity(oracle, got, want, is_bf16, what=f"few rows {m}x{n}x{k} act={act} bias={bias} res={residual}")
 
 
+@pytest.mark.parametrize("m,n,k", [(5, 3080, 2064), (32, 3072, 2048), (17, 4104, 4096), (4, 3072, 2304), (2, 8200, 2048),
+                                   (16, 18944, 3072), (9, 3072, 12288)])
+@pytest.mark.parametrize("is_bf16", [True, False])
+def test_few_rows_on_the_tensor_cores(flint, oracle, m, n, k, is_bf16):
+    """At most 32 rows against a wide, deep weight: the quantiser's codes go to the kernel that puts
+    the weight on the instruction's M side. Every epilogue form, a ragged last block of channels, k
+    that ends inside a 32-byte step and inside a stage, a zero row, more CTAs than SMs."""
+    rng = np.random.default_rng(61 + m + n + k)
+    for act, bias, residual, per_tensor in [(0, False, False, False), (1, True, False, False), (0, True, True, True),
+                                            (1, False, True, False)]:
+        x, codes, scales, b, r = make_case(oracle, rng, m, n, k, is_bf16, bias, residual, per_tensor)
+        if m > 1:
+            x[m - 1] = 0
+        got = run(flint, x, codes, scales, b, r, act, is_bf16)
+        want = oracle.fp8_linear(x, codes, scales, b, r, act, is_bf16)
+        check_parity(oracle, got, want, is_bf16, what=f"few rows {m}x{n}x{k} act={act} bias={bias} res={residual}")
+
+
+def test_few_rows_on_the_tensor_cores_match_the_tile_kernel(flint, oracle):
+    """The same rows alone (the few-row kernel) and inside 64 rows (the tile kernel), with a weight
+    of +-1 so that every partial sum is exact: the two epilogues agree to the last bit, through
+    fl_fp8_linear, fl_fp8_linear_static and fl_fp8_linear_quantized."""
+    rng = np.random.default_rng(62)
+    F = flint
+    n, k = 3080, 2064
+    x = oracle.narrow(randn(rng, (64, k)), True)
+    codes = np.where(rng.random((n, k)) < 0.5, 0x38, 0xb8).astype(np.uint8)
+    scales = (0.25 + rng.random(n)).astype(np.float32)
+    bias = oracle.narrow(randn(rng, (n,)), True)
+    res = oracle.narrow(randn(rng, (64, n)), True)
+    few = run(F, x[:8], codes, scales, bias, res[:8], 1)
+    many = run(F, x, codes, scales, bias, res, 1)
+    assert np.array_equal(few, many[:8])
+    bf = F.DType.BFLOAT16
+    cd, sd = dev(F, codes, F.DType.FP8E4M3), dev(F, scales, F.DType.FLOAT)
+    out = F.Tensor.empty((8, n), bf)
+    F.fp8_linear_static(dev(F, x[:8], bf), cd, sd, dev(F, bias, bf), dev(F, res[:8], bf), 1, out)
+    assert np.array_equal(out.numpy(), few)
+    a_codes, a_scales = oracle.quantize_fp8_act(x[:8], True)
+    out2 = F.Tensor.empty((8, n), bf)
+    F.fp8_linear_quantized(dev(F, a_codes, F.DType.FP8E4M3), dev(F, a_scales, F.DType.FLOAT), cd, sd, dev(F, bias, bf),
+                           dev(F, res[:8], bf), 1, out2)
+    assert np.array_equal(out2.numpy(), few)
+
+
 def test_few_rows_match_the_tile_path_quantiser(flint, oracle):
     """The in-kernel quantiser of the few-row kernel is the activation quantiser's arithmetic: with
     a weight of exact small integers the two paths (m = 4 and the same rows inside m = 64) agree
