@@ -71,6 +71,7 @@ NCU_TRAFFIC_SOURCE = {
     "c1_linear": "profiles/gemm_tn_kernel_fp8_c2_mlp.md",
     "c3_nvfp4_qkv": "profiles/gemm_tn_kernel_nvfp4_c3_qkv.md",
     "skinny_decode": "profiles/fewrow_tc_kernel_decode_16x16384x3072.md",
+    "skinny_decode_linear": "profiles/fewrow_q8_kernel_decode_16x16384x3072.md",
     "attention_step": "profiles/attention_kernel_denoise_step.md",
 }
 
@@ -86,6 +87,7 @@ NCU_TRAFFIC_BYTES = {
     "c1_linear": 22.1e6,                                 # the bf16 output stays dirty in L2
     "c3_nvfp4_qkv": 24.0e6 + 25.5e6,
     "skinny_decode": 50.47e6 + 0.01e6,                   # the weight once; the result stays in L2
+    "skinny_decode_linear": 50.48e6,                     # the same through fl_fp8_linear (the product's launch)
     "attention_step": 160.5e6 + 32.7e6,                  # q, k, v once (K and V re-reads hit L2); the output partly stays in L2
 }
 
@@ -993,9 +995,14 @@ def run_skinny(args):
     import torch
     from libwaifu_b200 import flint as F
     wl = dict(WORKLOADS["skinny_decode"])
-    if args.rows:  # (up to 16 rows)
+    if args.rows:  # (up to 16 rows; up to 32 through fl_fp8_linear)
         wl["m"] = args.rows
         wl["desc"] = wl["desc"] + f" [{args.rows} rows]"
+    linear = args.decode_entry == "fp8_linear"
+    if linear:
+        wl["kind"] = "fp8"
+        wl["desc"] = wl["desc"].replace("fl_fp8_matmul", "fl_fp8_linear").replace(
+            "fp16 activation x e4m3 weight, one scale", "bf16 activation quantised per token x e4m3 weight, channel scales")
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -1014,7 +1021,8 @@ def run_skinny(args):
     def wrap(t, dt):
         return F.Tensor.from_device_ptr(t.data_ptr(), tuple(t.shape), dt, keepalive=t)
 
-    xs = [torch.randn(m, k, device="cuda", dtype=torch.float16, generator=gen) for _ in range(sets)]
+    act_torch, act_dt = (torch.bfloat16, F.DType.BFLOAT16) if linear else (torch.float16, F.DType.FLOAT16)
+    xs = [torch.randn(m, k, device="cuda", dtype=act_torch, generator=gen) for _ in range(sets)]
     ws = []
     for _ in range(sets):
         w = torch.randn(n, k, device="cuda", dtype=torch.float32, generator=gen) * 0.02
@@ -1023,13 +1031,17 @@ def run_skinny(args):
         del w
     F.synchronize()
     scale = wrap(torch.full((1,), 0.02 / 448.0 * 4.0, device="cuda", dtype=torch.float32), F.DType.FLOAT)
-    out = F.Tensor.empty((m, n), F.DType.FLOAT16)
-    x_w = [wrap(x, F.DType.FLOAT16) for x in xs]
+    channel_scales = wrap(torch.full((n,), 0.02 / 448.0 * 4.0, device="cuda", dtype=torch.float32), F.DType.FLOAT)
+    out = F.Tensor.empty((m, n), act_dt)
+    x_w = [wrap(x, act_dt) for x in xs]
     L = F.lib()
 
     def step(i, x_override=None):
         x = x_override if x_override is not None else x_w[i % sets]
-        F.check(L.fl_fp8_matmul(x.raw(), ws[i % sets].raw(), scale.raw(), out.raw()))
+        if linear:
+            F.check(L.fl_fp8_linear(x.raw(), ws[i % sets].raw(), channel_scales.raw(), None, None, 0, out.raw()))
+        else:
+            F.check(L.fl_fp8_matmul(x.raw(), ws[i % sets].raw(), scale.raw(), out.raw()))
 
     def barrier():
         if dist is not None:
@@ -1064,13 +1076,15 @@ def run_skinny(args):
     value = world * flops_per_step(wl) / (ms_step * 1e-3) / 1e12
 
     # end to end: the row from pinned host memory, the result row back to the host
-    host_x = F.Tensor.empty((m, k), F.DType.FLOAT16, F.Device.CUDA_HOST)
-    host_y = F.Tensor.empty((m, n), F.DType.FLOAT16, F.Device.CUDA_HOST)
-    dev_x = F.Tensor.empty((m, k), F.DType.FLOAT16)
+    host_x = F.Tensor.empty((m, k), act_dt, F.Device.CUDA_HOST)
+    host_y = F.Tensor.empty((m, n), act_dt, F.Device.CUDA_HOST)
+    dev_x = F.Tensor.empty((m, k), act_dt)
     p = ctypes.c_void_p()
     F.check(L.fl_tensor_data_get_host_ptr(host_x._data, ctypes.byref(p)))
     hx = np.ctypeslib.as_array(ctypes.cast(p.value, ctypes.POINTER(ctypes.c_uint16)), shape=(m * k,))
     hx[:] = np.random.default_rng(7 + rank).standard_normal(m * k).astype(np.float16).view(np.uint16)
+    if linear:  # (the same bits read as bfloat16 are finite values as well)
+        hx[:] &= 0xbfff
     ops = F.operators()
 
     def e2e_step(i):
@@ -1090,13 +1104,19 @@ def run_skinny(args):
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
 
     _, hbm_peak, peak_kind = measured_peaks()
-    alg_bytes = n * k + m * k * 2 + m * n * 2 + 4
+    alg_bytes = n * k + m * k * 2 + m * n * 2 + (n * 4 if linear else 4)
     achieved = alg_bytes / (ms_step * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "fewrow_tc_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+    traffic = traffic_fields("skinny_decode")
+    if linear:
+        traffic = traffic_fields("skinny_decode_linear")
+    roofline = {"bound": "hbm", "kernel": "fewrow_q8_kernel" if linear else "fewrow_tc_kernel", "achieved": achieved,
+                "peak": hbm_peak, "unit": "GB/s",
                 "frac": achieved / hbm_peak, "peak_source": f"stream copy, of {peak_kind}", "launches": launches,
-                "avg_launch_ms": ms_step, **traffic_fields("skinny_decode"),
+                "avg_launch_ms": ms_step, **traffic,
                 "algorithmic_bytes_per_step": alg_bytes,
-                "note": "one launch per step; the launch time is the step time of the back-to-back timed region"}
+                "note": ("two launches per step (the rows' quantiser, then the product); the time is the step time of the "
+                         "back-to-back timed region" if linear else
+                         "one launch per step; the launch time is the step time of the back-to-back timed region")}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -1115,7 +1135,7 @@ def run_skinny(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f16 x e4m3 -> f32 accumulate", "data": "synthetic",
+            "dtype": "e4m3 x e4m3 -> f32 accumulate" if linear else "f16 x e4m3 -> f32 accumulate", "data": "synthetic",
             "config": {"workload": "skinny_decode", "what": wl["desc"], "parallelism": f"replicas{world}",
                        "l2": f"{sets} rotating weights of {n * k / 1e6:.0f} MB, larger than L2 together",
                        "published": "the reference reports 130.6 us for this shape on an RTX 5060 Ti (docs/fp8.md), other hardware"},
@@ -1451,6 +1471,8 @@ def main():
     ap.add_argument("--workload", default="c2_mlp", choices=sorted(WORKLOADS))
     ap.add_argument("--rotate", type=int, default=3, help="operand sets rotated through to defeat L2 reuse")
     ap.add_argument("--rows", type=int, default=None, help="override the workload's row count (for small profile captures)")
+    ap.add_argument("--decode-entry", default="fp8_matmul", choices=["fp8_matmul", "fp8_linear"],
+                    help="skinny_decode: the reference's fl_fp8_matmul (16-bit rows) or fl_fp8_linear (rows quantised per token)")
     ap.add_argument("--reference-rows", type=int, default=1088, help="rows of the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-chunks", type=int, default=4, help="row chunks the end-to-end step is pipelined in")
