@@ -79,6 +79,7 @@ struct Params {
   long long residual_ld;
   void *out;
   int m, n, k;
+  int cpc;  // channels per CTA: at most 128, a multiple of 8
   uint32_t *status;
 };
 
@@ -95,7 +96,7 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * kChannels;
+  const int n0 = blockIdx.x * p.cpc;
   const int num_kb = p.k / kBlockK;
   const int num_stages = (num_kb + kBlocksPerStage - 1) / kBlocksPerStage;
 
@@ -144,7 +145,7 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
           ok = false;
           break;
         }
-        mbar_arrive_expect_tx(&raw_full_bar[s], kRawWBytes);  // (bytes past the end of a row arrive as zeros)
+        mbar_arrive_expect_tx(&raw_full_bar[s], static_cast<uint32_t>(p.cpc) * kStageK);  // (bytes past the end of a row arrive as zeros)
 #pragma unroll
         for (int a = 0; a < kAtoms; ++a) {
           tma_load_2d(stage_w(s) + a * kAtomBytes, &tmap_w, &raw_full_bar[s], st * kStageK + a * 128, n0);
@@ -259,8 +260,9 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             for (int t = 0; t < kTokens; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) + __uint_as_float(u[t]));
           }
         }
-        const int channel = n0 + static_cast<int>(warp) * 32 + static_cast<int>(lane);
-        if (channel < p.n) {
+        const int local = static_cast<int>(warp) * 32 + static_cast<int>(lane);
+        const int channel = n0 + local;
+        if (local < p.cpc && channel < p.n) {
           const float scale = __ldg(p.scale);
           const float bias = p.bias ? __half2float(reinterpret_cast<const __half *>(p.bias)[channel]) : 0.0f;
           const __half *res = reinterpret_cast<const __half *>(p.residual);
@@ -326,6 +328,7 @@ struct QParams {
   void *out;
   int m, n, k;
   int ntok;    // N of the instruction: the rows rounded up to a multiple of 16
+  int cpc;     // channels per CTA: at most 128, a multiple of 8
   int stages;
   uint32_t tmem_cols;
   uint32_t *status;
@@ -353,7 +356,7 @@ fewrow_q8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * kChannels;
+  const int n0 = blockIdx.x * p.cpc;
   const int num_stages = (p.k + kStageK - 1) / kStageK;  // (the last may be part zeros)
   const int x_atom = p.ntok * 128;
   const int stage_bytes = kRawWBytes + kAtoms * x_atom;
@@ -392,7 +395,7 @@ fewrow_q8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
           break;
         }
         uint8_t *base = smem + s * stage_bytes;
-        mbar_arrive_expect_tx(&full_bar[s], static_cast<uint32_t>(stage_bytes));  // (bytes outside arrive as zeros)
+        mbar_arrive_expect_tx(&full_bar[s], static_cast<uint32_t>(p.cpc * kStageK + kAtoms * x_atom));  // (bytes outside arrive as zeros)
 #pragma unroll
         for (int a = 0; a < kAtoms; ++a) {
           tma_load_2d(base + a * kAtomBytes, &tmap_w, &full_bar[s], st * kStageK + a * 128, n0);
@@ -439,8 +442,9 @@ fewrow_q8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const bool ok = mbar_wait(&acc_full_bar, 0, &abort_flag);
     if (__all_sync(0xffffffffu, ok)) {
       tc_fence_after_sync();
-      const int channel = n0 + static_cast<int>(warp) * 32 + static_cast<int>(lane);
-      const bool live = channel < p.n;
+      const int local = static_cast<int>(warp) * 32 + static_cast<int>(lane);
+      const int channel = n0 + local;
+      const bool live = local < p.cpc && channel < p.n;
       const float cs = p.col_scale ? __ldg(p.col_scale + (p.col_scale_scalar || !live ? 0 : channel)) : 1.0f;
       const uint16_t *bias16 = reinterpret_cast<const uint16_t *>(p.bias);
       float bias = 0.0f;
@@ -501,6 +505,23 @@ fewrow_q8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
 }  // namespace q8
 
+// Channels per CTA. A CTA's time is its own chain over the k / 256 stages whatever the bytes a
+// stage brings (112 channels on 147 CTAs measured the same as 128 on 128), so 128 unless that
+// takes more than one round of the SMs: then the channels are dealt evenly over whole rounds
+// (24576 x 12288: 65.2 us on 280 CTAs of 88 channels against 68.7 on 192 of 128).
+int channels_per_cta(int n) {
+  static const int sms = [] {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v < 1) v = 148;
+    return v;
+  }();
+  const int ctas128 = (n + kChannels - 1) / kChannels;
+  if (ctas128 <= sms) return kChannels;
+  const int target = (ctas128 + sms - 1) / sms * sms;
+  const int cpc = ((n + target - 1) / target + 7) / 8 * 8;
+  return cpc > kChannels ? kChannels : cpc;
+}
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -547,7 +568,8 @@ cudaError_t fewrow_tc_matmul(const void *x, int m, int n, int k, const uint8_t *
                              cudaStream_t stream, const char **why) {
   *why = "";
   CUtensorMap tw, tx;
-  const bool w_ok = make_map(&tw, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 128, kChannels, CU_TENSOR_MAP_SWIZZLE_128B);
+  const int cpc = channels_per_cta(n);
+  const bool w_ok = make_map(&tw, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 128, static_cast<uint32_t>(cpc), CU_TENSOR_MAP_SWIZZLE_128B);
   if (!w_ok ||
       !make_map(&tx, x, static_cast<uint64_t>(m), static_cast<uint64_t>(k) * 2, kBlockK * 2, kTokens,
                 CU_TENSOR_MAP_SWIZZLE_128B)) {
@@ -573,9 +595,10 @@ cudaError_t fewrow_tc_matmul(const void *x, int m, int n, int k, const uint8_t *
   p.m = m;
   p.n = n;
   p.k = k;
+  p.cpc = cpc;
   p.status = status;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>((n + kChannels - 1) / kChannels), 1, 1);
+  cfg.gridDim = dim3(static_cast<unsigned>((n + cpc - 1) / cpc), 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
@@ -604,7 +627,8 @@ cudaError_t fewrow_q8_linear(const uint8_t *codes, const float *row_scale, int m
   *why = "";
   const int ntok = (m + 15) / 16 * 16;
   CUtensorMap tw, tx;
-  if (!make_map(&tw, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 128, kChannels, CU_TENSOR_MAP_SWIZZLE_128B) ||
+  const int cpc = channels_per_cta(n);
+  if (!make_map(&tw, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 128, static_cast<uint32_t>(cpc), CU_TENSOR_MAP_SWIZZLE_128B) ||
       !make_map(&tx, codes, static_cast<uint64_t>(m), static_cast<uint64_t>(k), 128, static_cast<uint32_t>(ntok),
                 CU_TENSOR_MAP_SWIZZLE_128B)) {
     *why = "cuTensorMapEncodeTiled refused an operand";
@@ -638,12 +662,13 @@ cudaError_t fewrow_q8_linear(const uint8_t *codes, const float *row_scale, int m
   p.n = n;
   p.k = k;
   p.ntok = ntok;
+  p.cpc = cpc;
   p.stages = stages;
   const int acc_cols = q8::kIssuers * q8::kQChains * ntok;
   p.tmem_cols = acc_cols <= 128 ? 128u : acc_cols <= 256 ? 256u : 512u;
   p.status = status;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>((n + kChannels - 1) / kChannels), 1, 1);
+  cfg.gridDim = dim3(static_cast<unsigned>((n + cpc - 1) / cpc), 1, 1);
   cfg.blockDim = dim3(q8::kQThreads, 1, 1);
   cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
   cfg.stream = stream;
