@@ -3,7 +3,7 @@
 // once. Here the weight sits on the M side of tcgen05.mma and the rows are its N = 16, so that no
 // instruction of a CUDA core multiplies anything and the time does not depend on the row count
 // (the kernel in skinny_sm100.cu, which multiplies on mma.sync, takes 20 us for one row against
-// 16384 x 3072 and 36 us for sixteen; this one 12.7 us for either). The widened weight never
+// 16384 x 3072 and 36 us for sixteen; this one 12.0 to 12.5 us). The widened weight never
 // touches shared memory: the A operand of tcgen05.mma may lie in tensor memory (row i of the tile
 // in lane i, the sixteen halves of an instruction packed into eight columns), so shared memory
 // holds nothing but bytes as they came from HBM, six stages of 32 KB in flight per CTA.
@@ -17,14 +17,14 @@
 //              exact), writes them with tcgen05.st into one of three units of 128 columns, and hands
 //              the raw stage back;
 //   warps 9-12 four threads issue the sixteen tcgen05.mma kind::f16 (M = 128 channels, N = 16 rows,
-//              K = 16) of a stage, four each, into two accumulators each in turn. Every tcgen05
+//              K = 16) of a stage, four each, into an accumulator each. Every tcgen05
 //              issue costs the issuing thread some 60 cycles: with one thread issuing all sixteen
 //              the kernel took 16.9 us, with two 14.0 us, with four 12.7 us;
-//   warps 0-3  then the epilogue: a lane owns a channel, reads its 8 x 16 partial sums and adds them;
+//   warps 0-3  then the epilogue: a lane owns a channel, reads its 4 x 16 partial sums and adds them;
 //              scale, bias, residual, one rounding; for every row the warp stores 32 consecutive
 //              channels.
 // A CTA owns 128 output channels and is paced by its own chain (load, widen, multiply) over the
-// k / 256 stages, some 0.65 us each after 5 us of launch, first load and epilogue: 11 to 12.5 us at
+// k / 256 stages, some 0.65 us each after 4.5 us of launch, first load and epilogue: 11 to 12.5 us at
 // k = 3072 for any channel count up to 148 x 128. Sixteen converter warps, on alternate stages or
 // on quarters of every stage, were no faster. Every wait is bounded (status word, as everywhere else).
 #include "fewrow_tc_sm100.cuh"
@@ -54,10 +54,10 @@ constexpr int kXStages = 4;                            // of x: given back when 
 constexpr int kUnits = 3;                              // widened stages in tensor memory
 constexpr int kUnitCols = kStageK / 2;                 // 128 columns: 256 halves of a row, two to a column
 constexpr int kMmaWarps = 4;                           // W: threads that issue, one block of a stage each
-constexpr int kChains = 2;                             // C: accumulators per issuing thread, used in turn
-constexpr int kAccCols = kMmaWarps * kChains * kTokens;  // 128 columns
+constexpr int kChains = 1;                             // C: accumulators per issuing thread (two in turn measured the same)
+constexpr int kAccCols = kMmaWarps * kChains * kTokens;  // 64 columns
 constexpr int kUnitCol0 = kAccCols;
-constexpr int kTmemCols = 512;                         // 128 + 3 x 128; allocations are powers of two
+constexpr int kTmemCols = 512;                         // 64 + 3 x 128; allocations are powers of two
 constexpr int kConvGroups = kAtoms;                    // warps 0..7 in groups of four
 constexpr int kConvWarps = 4 * kConvGroups;
 constexpr int kProducer = kConvWarps;
@@ -100,26 +100,36 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
   const int num_kb = p.k / kBlockK;
   const int num_stages = (num_kb + kBlocksPerStage - 1) / kBlocksPerStage;
 
-  if (threadIdx.x == 0) {
-    abort_flag = 0;
-    for (int s = 0; s < kRawStages; ++s) {
-      mbar_init(&raw_full_bar[s], 1);
-      mbar_init(&raw_empty_bar[s], kConvWarps);
+  if (warp == 0) {  // (a lane per ring slot: 27 barriers set up one after the other were half a microsecond)
+    if (lane < kRawStages) {
+      mbar_init(&raw_full_bar[lane], 1);
+      mbar_init(&raw_empty_bar[lane], kConvWarps);
     }
-    for (int s = 0; s < kXStages; ++s) {
-      mbar_init(&x_full_bar[s], 1);
-      mbar_init(&x_empty_bar[s], kMmaWarps);
+    if (lane < kXStages) {
+      mbar_init(&x_full_bar[lane], 1);
+      mbar_init(&x_empty_bar[lane], kMmaWarps);
     }
-    for (int u = 0; u < kUnits; ++u) {
-      mbar_init(&unit_full_bar[u], kConvWarps);
-      mbar_init(&unit_empty_bar[u], kMmaWarps);
+    if (lane < kUnits) {
+      mbar_init(&unit_full_bar[lane], kConvWarps);
+      mbar_init(&unit_empty_bar[lane], kMmaWarps);
     }
-    mbar_init(&acc_full_bar, kMmaWarps);
+    if (lane == 0) {
+      abort_flag = 0;
+      mbar_init(&acc_full_bar, kMmaWarps);
+    }
     fence_barrier_init();
   }
   if (warp == kProducer && lane == 0) {
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_x);
+    // The first stages of the weight are asked into L2 before the kernel ahead in the stream is
+    // known to be done: a prefetch writes nothing, and if that kernel does write these bytes its
+    // stores land in the same L2, so the loads below read what they would have read anyway. The
+    // CTA's first loads then meet the bytes half way instead of starting HBM's latency from zero.
+    for (int st = 0; st < num_stages && st < kRawStages; ++st) {
+#pragma unroll
+      for (int a = 0; a < kAtoms; ++a) tma_prefetch_l2_2d(&tmap_w, st * kStageK + a * 128, n0);
+    }
   }
   if (warp == kMma) {
     tmem_alloc<1>(&tmem_base_slot, kTmemCols);
@@ -247,17 +257,18 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       ok = mbar_wait(&acc_full_bar, 0, &abort_flag);
       if (__all_sync(0xffffffffu, ok)) {
         tc_fence_after_sync();
-        uint32_t v[16];
+        // the four partial sums: all four loads, then one wait
+        uint32_t v[16], u[kMmaWarps * kChains - 1][16];
         tmem_ld_32x16(tmem_base + ((warp * 32u) << 16), v);
+#pragma unroll
+        for (int c = 1; c < kMmaWarps * kChains; ++c) tmem_ld_32x16(tmem_base + ((warp * 32u) << 16) + c * kTokens, u[c - 1]);
         tmem_ld_wait(v);
-  #pragma unroll
+#pragma unroll
         for (int c = 1; c < kMmaWarps * kChains; ++c) {
-          uint32_t u[16];
-          tmem_ld_32x16(tmem_base + ((warp * 32u) << 16) + c * kTokens, u);
-          tmem_ld_wait(u);
+          tmem_ld_wait(u[c - 1]);
           if (c / kChains < num_kb) {  // (an issuing warp beyond the last block of a short product wrote nothing)
-  #pragma unroll
-            for (int t = 0; t < kTokens; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) + __uint_as_float(u[t]));
+#pragma unroll
+            for (int t = 0; t < kTokens; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) + __uint_as_float(u[c - 1][t]));
           }
         }
         const int local = static_cast<int>(warp) * 32 + static_cast<int>(lane);
@@ -267,7 +278,7 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
           const float bias = p.bias ? __half2float(reinterpret_cast<const __half *>(p.bias)[channel]) : 0.0f;
           const __half *res = reinterpret_cast<const __half *>(p.residual);
           __half *out = reinterpret_cast<__half *>(p.out);
-  #pragma unroll
+#pragma unroll
           for (int t = 0; t < kTokens; ++t) {
             if (t < p.m) {
               float y = __uint_as_float(v[t]) * scale + bias;
@@ -302,15 +313,15 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 // CTA), up to 64 rows as N, K = 32 per instruction. A stage is 256 K positions: two 128-byte
 // swizzle atoms of the weight (32 KB) and two of the rows (N x 128 bytes each); as many stages
 // as fit (six for 16 rows, four for 64). Four threads issue two of a stage's eight instructions
-// each into two accumulators each in turn; warps 0-3 are the epilogue (a lane per channel): the
-// eight partial sums, then the tile kernel's arithmetic in its order: acc * (row scale * channel
+// each into an accumulator of its own; warps 0-3 are the epilogue (a lane per channel): the
+// four partial sums, then the tile kernel's arithmetic in its order: acc * (row scale * channel
 // scale), + bias, GELU, + residual, one rounding.
 namespace q8 {
 
 constexpr int kMaxTokens = 64;
 constexpr int kMaxStages = 6;
 constexpr int kIssuers = 4;
-constexpr int kQChains = 2;
+constexpr int kQChains = 1;
 constexpr int kQProducer = 4;
 constexpr int kQMma = 5;
 constexpr int kQThreads = (kQMma + kIssuers) * 32;
@@ -361,18 +372,25 @@ fewrow_q8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
   const int x_atom = p.ntok * 128;
   const int stage_bytes = kRawWBytes + kAtoms * x_atom;
 
-  if (threadIdx.x == 0) {
-    abort_flag = 0;
-    for (int s = 0; s < p.stages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], kIssuers);
+  if (warp == 0) {
+    if (static_cast<int>(lane) < p.stages) {
+      mbar_init(&full_bar[lane], 1);
+      mbar_init(&empty_bar[lane], kIssuers);
     }
-    mbar_init(&acc_full_bar, kIssuers);
+    if (lane == 0) {
+      abort_flag = 0;
+      mbar_init(&acc_full_bar, kIssuers);
+    }
     fence_barrier_init();
   }
   if (warp == kQProducer && lane == 0) {
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_x);
+    // (the first stages of the weight into L2 ahead of the wait on the kernel before, as above)
+    for (int st = 0; st < num_stages && st < p.stages; ++st) {
+#pragma unroll
+      for (int a = 0; a < kAtoms; ++a) tma_prefetch_l2_2d(&tmap_w, st * kStageK + a * 128, n0);
+    }
   }
   if (warp == kQMma) {
     tmem_alloc<1>(&tmem_base_slot, p.tmem_cols);
@@ -426,8 +444,8 @@ fewrow_q8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const uint64_t wd = umma_desc_sw128(base + atom * kAtomBytes) + step0 * 2;
         const uint64_t xd = umma_desc_sw128(base + kRawWBytes + atom * x_atom) + step0 * 2;
 #pragma unroll
-        for (int i = 0; i < kQChains; ++i) {
-          umma_ss<kKindF8>(acc0 + i * p.ntok, wd + i * 2, xd + i * 2, idesc, st > 0 ? 1u : 0u);
+        for (int i = 0; i < 2; ++i) {  // this thread's two 32-byte steps of the stage
+          umma_ss<kKindF8>(acc0 + (i % kQChains) * p.ntok, wd + i * 2, xd + i * 2, idesc, (st > 0 || i >= kQChains) ? 1u : 0u);
         }
         umma_commit(&empty_bar[s]);
       }
@@ -455,16 +473,16 @@ fewrow_q8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       const uint16_t *res = reinterpret_cast<const uint16_t *>(p.residual);
       uint16_t *out = reinterpret_cast<uint16_t *>(p.out);
       for (int t0 = 0; t0 < p.m; t0 += 16) {
-        uint32_t v[16];
+        uint32_t v[16], u[kIssuers * kQChains - 1][16];
         tmem_ld_32x16(tmem_base + ((warp * 32u) << 16) + t0, v);
+#pragma unroll
+        for (int c = 1; c < kIssuers * kQChains; ++c) tmem_ld_32x16(tmem_base + ((warp * 32u) << 16) + c * p.ntok + t0, u[c - 1]);
         tmem_ld_wait(v);
 #pragma unroll
         for (int c = 1; c < kIssuers * kQChains; ++c) {
-          uint32_t u[16];
-          tmem_ld_32x16(tmem_base + ((warp * 32u) << 16) + c * p.ntok + t0, u);
-          tmem_ld_wait(u);
+          tmem_ld_wait(u[c - 1]);
 #pragma unroll
-          for (int t = 0; t < 16; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) + __uint_as_float(u[t]));
+          for (int t = 0; t < 16; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) + __uint_as_float(u[c - 1][t]));
         }
         if (live) {
 #pragma unroll

@@ -167,6 +167,13 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *desc) {
 
 // 2-D tiled load global -> this CTA's shared memory, completion counted in bytes on `bar`.
 // x is the innermost (contiguous) coordinate in elements, y the row.
+// Asks for a tile to be brought into L2; nothing waits for it and nothing is written anywhere else.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *desc, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+               ::"l"(reinterpret_cast<uint64_t>(desc)), "r"(x), "r"(y)
+               : "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *desc, uint64_t *bar, int32_t x,
                                             int32_t y) {
   asm volatile(
