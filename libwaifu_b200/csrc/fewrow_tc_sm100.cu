@@ -218,35 +218,40 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     bool ok = true;
     for (int st = 0; st < num_stages && ok; ++st) {
       const int s = st % kRawStages, u = st % kUnits;
-      if (!mbar_wait(&raw_full_bar[s], (st / kRawStages) & 1, &abort_flag) ||
-          !mbar_wait(&unit_empty_bar[u], ((st / kUnits) & 1) ^ 1, &abort_flag)) {
+      if (!mbar_wait(&raw_full_bar[s], (st / kRawStages) & 1, &abort_flag)) {
         ok = false;
         break;
       }
-      tc_fence_after_sync();  // the instructions that read this unit last are done
+      // Read and widen into registers first, hand the raw stage back, and only then wait for the
+      // unit (12.5 -> 12.2 us at sixteen rows).
       const uint8_t *raw = stage_w(s) + row_off;
+      uint32_t w[4][16];
 #pragma unroll
       for (uint32_t pp = 0; pp < 4; ++pp) {  // two 16-byte pieces -> 32 halves -> 16 columns
         const uint4 v0 = *reinterpret_cast<const uint4 *>(raw + (((2 * pp) ^ sw) << 4));
         const uint4 v1 = *reinterpret_cast<const uint4 *>(raw + (((2 * pp + 1) ^ sw) << 4));
-        uint32_t w[16];
-        e4m3x4_to_f16x4(v0.x, &w[0], &w[1]);
-        e4m3x4_to_f16x4(v0.y, &w[2], &w[3]);
-        e4m3x4_to_f16x4(v0.z, &w[4], &w[5]);
-        e4m3x4_to_f16x4(v0.w, &w[6], &w[7]);
-        e4m3x4_to_f16x4(v1.x, &w[8], &w[9]);
-        e4m3x4_to_f16x4(v1.y, &w[10], &w[11]);
-        e4m3x4_to_f16x4(v1.z, &w[12], &w[13]);
-        e4m3x4_to_f16x4(v1.w, &w[14], &w[15]);
-        tmem_st_32x16(t_row + u * kUnitCols + pp * 16, w);
+        e4m3x4_to_f16x4(v0.x, &w[pp][0], &w[pp][1]);
+        e4m3x4_to_f16x4(v0.y, &w[pp][2], &w[pp][3]);
+        e4m3x4_to_f16x4(v0.z, &w[pp][4], &w[pp][5]);
+        e4m3x4_to_f16x4(v0.w, &w[pp][6], &w[pp][7]);
+        e4m3x4_to_f16x4(v1.x, &w[pp][8], &w[pp][9]);
+        e4m3x4_to_f16x4(v1.y, &w[pp][10], &w[pp][11]);
+        e4m3x4_to_f16x4(v1.z, &w[pp][12], &w[pp][13]);
+        e4m3x4_to_f16x4(v1.w, &w[pp][14], &w[pp][15]);
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&raw_empty_bar[s]);  // the raw bytes are in registers: the stage may be refilled
+      if (!mbar_wait(&unit_empty_bar[u], ((st / kUnits) & 1) ^ 1, &abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();  // the instructions that read this unit last are done
+#pragma unroll
+      for (uint32_t pp = 0; pp < 4; ++pp) tmem_st_32x16(t_row + u * kUnitCols + pp * 16, w[pp]);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&raw_empty_bar[s]);
-        mbar_arrive(&unit_full_bar[u]);
-      }
+      if (lane == 0) mbar_arrive(&unit_full_bar[u]);
     }
     if (!ok && lane == 0) {
       abort_flag = 1;
