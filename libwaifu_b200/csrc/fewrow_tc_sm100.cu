@@ -40,36 +40,43 @@ namespace flsm100 {
 namespace {
 
 constexpr int kChannels = 128;   // per CTA: the M of the instruction
-constexpr int kTokens = 16;      // its N
+constexpr int kTokens = 16;      // its N, or twice that (the template parameter of the kernels below)
 constexpr int kBlockK = 64;      // K positions per block: 128 bytes of an x row, four instructions
 constexpr int kBlocksPerStage = 4;
 constexpr int kStageK = kBlocksPerStage * kBlockK;     // K positions per ring stage
 constexpr int kRawWBytes = kChannels * kStageK;        // 32 KB
 constexpr int kAtomBytes = kChannels * 128;            // 128 rows x 128 e4m3 bytes, 128-byte swizzle
 constexpr int kAtoms = kStageK / 128;                  // 2 per stage
-constexpr int kXAtomBytes = kTokens * kBlockK * 2;     // 2 KB: a block's 16 rows x 128 bytes
-constexpr int kXBytes = kBlocksPerStage * kXAtomBytes; // 8 KB
-constexpr int kRawStages = 6;                          // of raw weight bytes: given back as soon as they are widened
-constexpr int kXStages = 4;                            // of x: given back when the instructions that read them are done
-constexpr int kUnits = 3;                              // widened stages in tensor memory
 constexpr int kUnitCols = kStageK / 2;                 // 128 columns: 256 halves of a row, two to a column
 constexpr int kMmaWarps = 4;                           // W: threads that issue, one block of a stage each
 constexpr int kChains = 1;                             // C: accumulators per issuing thread (two in turn measured the same)
-constexpr int kAccCols = kMmaWarps * kChains * kTokens;  // 64 columns
-constexpr int kUnitCol0 = kAccCols;
-constexpr int kTmemCols = 512;                         // 64 + 3 x 128; allocations are powers of two
+constexpr int kTmemCols = 512;                         // 64 or 128 + 3 x 128; allocations are powers of two
 constexpr int kConvGroups = kAtoms;                    // warps 0..7 in groups of four
 constexpr int kConvWarps = 4 * kConvGroups;
 constexpr int kProducer = kConvWarps;
 constexpr int kMma = kProducer + 1;
 constexpr int kThreads = (kMma + kMmaWarps) * 32;
 constexpr int kRawOff = 0;
-constexpr int kXOff = kRawOff + kRawStages * kRawWBytes;
-constexpr int kSmemBytes = kXOff + kXStages * kXBytes + 1024;
 static_assert(kBlocksPerStage % kMmaWarps == 0, "the blocks of a stage are dealt evenly");
-static_assert(kUnitCol0 + kUnits * kUnitCols <= kTmemCols, "tensor memory");
-static_assert(kXBytes % 1024 == 0 && kAtomBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
-static_assert(kSmemBytes <= 227 * 1024 - 512, "shared memory");
+
+// What depends on the rows an instruction takes (NTOK = 16, 32 or 64): the instruction's time does
+// not, so 32 rows cost what one costs. Shared memory (227 KB) and tensor memory (512 columns) are
+// dealt accordingly.
+template <int NTOK>
+struct TcCfg {
+  static constexpr int kXAtomBytes = NTOK * kBlockK * 2;             // 2, 4 or 8 KB: a block's rows x 128 bytes
+  static constexpr int kXBytes = kBlocksPerStage * kXAtomBytes;      // 8, 16 or 32 KB
+  static constexpr int kRawStages = NTOK == 16 ? 6 : 5;              // of raw weight bytes: given back as soon as they are widened
+  static constexpr int kXStages = NTOK == 64 ? 2 : 4;                // of x: given back when the instructions that read them are done
+  static constexpr int kUnits = NTOK == 64 ? 2 : 3;                  // widened stages in tensor memory (two measured the same as three)
+  static constexpr int kAccCols = kMmaWarps * kChains * NTOK;        // 64, 128 or 256 columns
+  static constexpr int kUnitCol0 = kAccCols;
+  static constexpr int kXOff = kRawOff + kRawStages * kRawWBytes;
+  static constexpr int kSmemBytes = kXOff + kXStages * kXBytes + 1024;
+  static_assert(kUnitCol0 + kUnits * kUnitCols <= kTmemCols, "tensor memory");
+  static_assert(kXBytes % 1024 == 0 && kAtomBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
+  static_assert(kSmemBytes <= 227 * 1024 - 512, "shared memory");
+};
 
 struct Params {
   const float *scale;
@@ -83,8 +90,12 @@ struct Params {
   uint32_t *status;
 };
 
+template <int NTOK>
 __global__ void __launch_bounds__(kThreads, 1)
 fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const Params p) {
+  using C = TcCfg<NTOK>;
+  constexpr int kRawStages = C::kRawStages, kXBytes = C::kXBytes, kXAtomBytes = C::kXAtomBytes, kXOff = C::kXOff;
+  constexpr int kUnitCol0 = C::kUnitCol0, kXStages = C::kXStages, kUnits = C::kUnits;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ __align__(8) uint64_t raw_full_bar[kRawStages], raw_empty_bar[kRawStages];
@@ -176,9 +187,9 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       // Every tcgen05 issue costs the issuing thread some 90 cycles, sixteen of them per stage more
       // than the stage's bytes take to arrive: the blocks of a stage are dealt to four threads.
       const int mw = static_cast<int>(warp) - kMma;
-      const uint32_t idesc = umma_idesc(kChannels, kTokens, 0u, 0u);
+      const uint32_t idesc = umma_idesc(kChannels, NTOK, 0u, 0u);
       const uint64_t xdesc0 = umma_desc_sw128(smem_u32(stage_x(0)));
-      const uint32_t acc0 = tmem_base + mw * kChains * kTokens;
+      const uint32_t acc0 = tmem_base + mw * kChains * NTOK;
       uint32_t issued = 0;
       bool ok = true;
       for (int st = 0; st < num_stages && ok; ++st) {
@@ -195,7 +206,7 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
           const uint64_t xd = xdesc0 + static_cast<uint64_t>((xs * kXBytes + j * kXAtomBytes) >> 4);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {  // 16 K positions: eight columns of the unit, 32 bytes of an x row
-            umma_ts_f16(acc0 + (issued % kChains) * kTokens, a_tmem + (j * 4 + i) * 8, xd + i * 2, idesc, issued >= kChains ? 1u : 0u);
+            umma_ts_f16(acc0 + (issued % kChains) * NTOK, a_tmem + (j * 4 + i) * 8, xd + i * 2, idesc, issued >= kChains ? 1u : 0u);
             ++issued;
           }
         }
@@ -262,33 +273,37 @@ fewrow_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       ok = mbar_wait(&acc_full_bar, 0, &abort_flag);
       if (__all_sync(0xffffffffu, ok)) {
         tc_fence_after_sync();
-        // the four partial sums: all four loads, then one wait
-        uint32_t v[16], u[kMmaWarps * kChains - 1][16];
-        tmem_ld_32x16(tmem_base + ((warp * 32u) << 16), v);
-#pragma unroll
-        for (int c = 1; c < kMmaWarps * kChains; ++c) tmem_ld_32x16(tmem_base + ((warp * 32u) << 16) + c * kTokens, u[c - 1]);
-        tmem_ld_wait(v);
-#pragma unroll
-        for (int c = 1; c < kMmaWarps * kChains; ++c) {
-          tmem_ld_wait(u[c - 1]);
-          if (c / kChains < num_kb) {  // (an issuing warp beyond the last block of a short product wrote nothing)
-#pragma unroll
-            for (int t = 0; t < kTokens; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) + __uint_as_float(u[c - 1][t]));
-          }
-        }
         const int local = static_cast<int>(warp) * 32 + static_cast<int>(lane);
         const int channel = n0 + local;
-        if (local < p.cpc && channel < p.n) {
-          const float scale = __ldg(p.scale);
-          const float bias = p.bias ? __half2float(reinterpret_cast<const __half *>(p.bias)[channel]) : 0.0f;
-          const __half *res = reinterpret_cast<const __half *>(p.residual);
-          __half *out = reinterpret_cast<__half *>(p.out);
+        const bool live = local < p.cpc && channel < p.n;
+        const float scale = __ldg(p.scale);
+        const float bias = (p.bias && live) ? __half2float(reinterpret_cast<const __half *>(p.bias)[channel]) : 0.0f;
+        const __half *res = reinterpret_cast<const __half *>(p.residual);
+        __half *out = reinterpret_cast<__half *>(p.out);
+        for (int t0 = 0; t0 < NTOK && t0 < p.m; t0 += 16) {
+          // the four partial sums of sixteen rows: all four loads, then one wait
+          uint32_t v[16], u[kMmaWarps * kChains - 1][16];
+          tmem_ld_32x16(tmem_base + ((warp * 32u) << 16) + t0, v);
 #pragma unroll
-          for (int t = 0; t < kTokens; ++t) {
-            if (t < p.m) {
-              float y = __uint_as_float(v[t]) * scale + bias;
-              if (res) y += __half2float(res[static_cast<long long>(t % p.residual_rows) * p.residual_ld + channel]);
-              out[static_cast<long long>(t) * p.n + channel] = __float2half_rn(y);
+          for (int c = 1; c < kMmaWarps * kChains; ++c) tmem_ld_32x16(tmem_base + ((warp * 32u) << 16) + c * NTOK + t0, u[c - 1]);
+          tmem_ld_wait(v);
+#pragma unroll
+          for (int c = 1; c < kMmaWarps * kChains; ++c) {
+            tmem_ld_wait(u[c - 1]);
+            if (c / kChains < num_kb) {  // (an issuing warp beyond the last block of a short product wrote nothing)
+#pragma unroll
+              for (int t = 0; t < 16; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) + __uint_as_float(u[c - 1][t]));
+            }
+          }
+          if (live) {
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {
+              const int row = t0 + t;
+              if (row < p.m) {
+                float y = __uint_as_float(v[t]) * scale + bias;
+                if (res) y += __half2float(res[static_cast<long long>(row % p.residual_rows) * p.residual_ld + channel]);
+                out[static_cast<long long>(row) * p.n + channel] = __float2half_rn(y);
+              }
             }
           }
         }
@@ -579,7 +594,7 @@ bool make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_by
 }  // namespace
 
 bool fewrow_tc_supported(int m, int n, int k, int is_bf16, const void *x, const void *w, const void *out) {
-  if (is_bf16 || m < 1 || m > kTokens || n < 8 || n % 8 != 0 || k < kBlockK || k % kBlockK != 0) return false;
+  if (is_bf16 || m < 1 || m > 4 * kTokens || n < 8 || n % 8 != 0 || k < kBlockK || k % kBlockK != 0) return false;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(out) & 1)) {
     return false;
   }
@@ -591,17 +606,27 @@ cudaError_t fewrow_tc_matmul(const void *x, int m, int n, int k, const uint8_t *
                              cudaStream_t stream, const char **why) {
   *why = "";
   CUtensorMap tw, tx;
+  const int ntok = m <= kTokens ? kTokens : m <= 2 * kTokens ? 2 * kTokens : 4 * kTokens;  // the instruction's N
   const int cpc = channels_per_cta(n);
   const bool w_ok = make_map(&tw, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 128, static_cast<uint32_t>(cpc), CU_TENSOR_MAP_SWIZZLE_128B);
   if (!w_ok ||
-      !make_map(&tx, x, static_cast<uint64_t>(m), static_cast<uint64_t>(k) * 2, kBlockK * 2, kTokens,
+      !make_map(&tx, x, static_cast<uint64_t>(m), static_cast<uint64_t>(k) * 2, kBlockK * 2, static_cast<uint32_t>(ntok),
                 CU_TENSOR_MAP_SWIZZLE_128B)) {
     *why = "cuTensorMapEncodeTiled refused an operand";
     return cudaErrorInvalidValue;
   }
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(fewrow_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(fewrow_tc_kernel<kTokens>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         TcCfg<kTokens>::kSmemBytes);
+    if (e == cudaSuccess) {
+      e = cudaFuncSetAttribute(fewrow_tc_kernel<2 * kTokens>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               TcCfg<2 * kTokens>::kSmemBytes);
+    }
+    if (e == cudaSuccess) {
+      e = cudaFuncSetAttribute(fewrow_tc_kernel<4 * kTokens>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               TcCfg<4 * kTokens>::kSmemBytes);
+    }
     if (e != cudaSuccess) {
       *why = "cudaFuncSetAttribute(max dynamic shared memory) failed";
       return e;
@@ -623,14 +648,18 @@ cudaError_t fewrow_tc_matmul(const void *x, int m, int n, int k, const uint8_t *
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>((n + cpc - 1) / cpc), 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.dynamicSmemBytes = ntok == kTokens       ? TcCfg<kTokens>::kSmemBytes
+                         : ntok == 2 * kTokens ? TcCfg<2 * kTokens>::kSmemBytes
+                                               : TcCfg<4 * kTokens>::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, fewrow_tc_kernel, tw, tx, p);
+  cudaError_t e = ntok == kTokens       ? cudaLaunchKernelEx(&cfg, fewrow_tc_kernel<kTokens>, tw, tx, p)
+                  : ntok == 2 * kTokens ? cudaLaunchKernelEx(&cfg, fewrow_tc_kernel<2 * kTokens>, tw, tx, p)
+                                        : cudaLaunchKernelEx(&cfg, fewrow_tc_kernel<4 * kTokens>, tw, tx, p);
   if (e != cudaSuccess) *why = "kernel launch failed";
   return e;
 }

@@ -10,7 +10,7 @@ namespace flsm100 {
 
 constexpr uint32_t kStatusFewRowTcTimeout = 0x71;
 
-// 1..16 half rows (not bfloat16: the widened weight and the rows have to be one type), k a
+// 1..64 half rows (not bfloat16: the widened weight and the rows have to be one type), k a
 // multiple of 64, n a multiple of 8, x and w 16-byte aligned.
 bool fewrow_tc_supported(int m, int n, int k, int is_bf16, const void *x, const void *w, const void *out);
 

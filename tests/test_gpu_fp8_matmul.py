@@ -220,15 +220,19 @@ def test_bf16_variant(flint, oracle):
 
 
 # (half rows against wide weights, k a multiple of 64, run with the weight on the tensor cores' M
-# side: the first shape and the last eight, among them ragged last tiles of channels, last stages
-# with one, two and three of their four blocks, and more CTAs than the GPU has SMs)
+# side: the first shape and the last fourteen, among them ragged last tiles of channels, last stages
+# with one, two and three of their four blocks, more CTAs than the GPU has SMs, and 17 to 64 rows,
+# which the instruction takes as N = 32 or 64)
 @pytest.mark.parametrize("m,n,k,bf16", [(1, 16384, 3072, False), (16, 264, 3072, True), (9, 72, 12288, False),
                                         (5, 4096, 80, True), (2, 64, 4112, False), (7, 72, 6160, True), (3, 136, 1040, False),
                                         (16, 12288, 64, False), (11, 12296, 4160, False), (4, 18432, 3072, False), (8, 8200, 320, False),
-                                        (1, 8192, 2240, False), (2, 6144, 2112, False), (8, 3080, 2176, False), (16, 24576, 2048, False)])
+                                        (1, 8192, 2240, False), (2, 6144, 2112, False), (8, 3080, 2176, False), (16, 24576, 2048, False),
+                                        (17, 8200, 2112, False), (32, 3072, 4096, False), (25, 24576, 2048, False),
+                                        (33, 3080, 2112, False), (64, 8192, 2048, False), (48, 24576, 2048, False)])
 def test_few_rows(flint, oracle, m, n, k, bf16):
-    """At most 16 rows take the one-launch path that widens the weight in registers; the first
-    shape is the reference's decode benchmark (docs/fp8.md:225-244)."""
+    """Few rows take one-launch paths that widen the weight in registers (against wide weights:
+    into tensor memory, up to 64 rows); the first shape is the reference's decode benchmark
+    (docs/fp8.md:225-244)."""
     rng = np.random.default_rng(16 + m + n + k)
     a = oracle.narrow(rng.standard_normal((m, k)).astype(np.float32), bf16)
     codes = random_codes(rng, n, k)
