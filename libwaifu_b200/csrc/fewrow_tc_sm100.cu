@@ -358,6 +358,7 @@ struct QParams {
   int act, is_bf16;
   void *out;
   int m, n, k;
+  int kbytes;  // bytes of a row of either operand: k, or 2 k for 16-bit operands
   int ntok;    // N of the instruction: the rows rounded up to a multiple of 16
   int cpc;     // channels per CTA: at most 128, a multiple of 8
   int stages;
@@ -376,6 +377,10 @@ __device__ __forceinline__ float gelu_tanh_q(float x) {
   return x * r;
 }
 
+// KIND: kKindF8 (e4m3 codes on both sides), or kKindF16 / kKindBF16 for a 16-bit weight and 16-bit
+// rows (fl_matmul's linear-layer case): the same bytes per stage, half the K positions, and
+// nothing to scale.
+template <int KIND>
 __global__ void __launch_bounds__(kQThreads, 1)
 fewrow_q8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const QParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -388,7 +393,7 @@ fewrow_q8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * p.cpc;
-  const int num_stages = (p.k + kStageK - 1) / kStageK;  // (the last may be part zeros)
+  const int num_stages = (p.kbytes + kStageK - 1) / kStageK;  // a stage: 256 bytes of every row (the last may be part zeros)
   const int x_atom = p.ntok * 128;
   const int stage_bytes = kRawWBytes + kAtoms * x_atom;
 
@@ -448,7 +453,8 @@ fewrow_q8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
   } else if (warp >= kQMma) {
     if (lane == 0) {
       const int mw = static_cast<int>(warp) - kQMma;
-      const uint32_t idesc = umma_idesc(kChannels, static_cast<uint32_t>(p.ntok), 0u, 0u);
+      constexpr uint32_t kFmt = KIND == kKindBF16 ? 1u : 0u;
+      const uint32_t idesc = umma_idesc(kChannels, static_cast<uint32_t>(p.ntok), kFmt, kFmt);
       const uint32_t acc0 = tmem_base + mw * kQChains * p.ntok;
       // this thread's two instructions of a stage: 32-byte steps 2 mw and 2 mw + 1 of the eight
       const uint32_t atom = mw >> 1, step0 = (mw & 1) * 2;
@@ -465,7 +471,7 @@ fewrow_q8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const uint64_t xd = umma_desc_sw128(base + kRawWBytes + atom * x_atom) + step0 * 2;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {  // this thread's two 32-byte steps of the stage
-          umma_ss<kKindF8>(acc0 + (i % kQChains) * p.ntok, wd + i * 2, xd + i * 2, idesc, (st > 0 || i >= kQChains) ? 1u : 0u);
+          umma_ss<KIND>(acc0 + (i % kQChains) * p.ntok, wd + i * 2, xd + i * 2, idesc, (st > 0 || i >= kQChains) ? 1u : 0u);
         }
         umma_commit(&empty_bar[s]);
       }
@@ -672,17 +678,20 @@ bool fewrow_q8_supported(int m, int n, int k, const void *codes, const void *w, 
   return encode_fn() != nullptr;
 }
 
-cudaError_t fewrow_q8_linear(const uint8_t *codes, const float *row_scale, int m, int n, int k, const uint8_t *w,
-                             const float *col_scale, int col_scale_scalar, const void *bias, const void *residual,
-                             int residual_rows, int64_t residual_ld, int act, int is_bf16, void *out, uint32_t *status,
-                             cudaStream_t stream, const char **why) {
+namespace {
+
+// elem: bytes per element of both operands (1: e4m3 codes, 2: half or bfloat16 as `is_bf16` says).
+cudaError_t launch_q8(int elem, const void *rows, const float *row_scale, int m, int n, int k, const void *w,
+                      const float *col_scale, int col_scale_scalar, const void *bias, const void *residual,
+                      int residual_rows, int64_t residual_ld, int act, int is_bf16, void *out, uint32_t *status,
+                      cudaStream_t stream, const char **why) {
   *why = "";
   const int ntok = (m + 15) / 16 * 16;
+  const uint64_t kbytes = static_cast<uint64_t>(k) * elem;
   CUtensorMap tw, tx;
   const int cpc = channels_per_cta(n);
-  if (!make_map(&tw, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 128, static_cast<uint32_t>(cpc), CU_TENSOR_MAP_SWIZZLE_128B) ||
-      !make_map(&tx, codes, static_cast<uint64_t>(m), static_cast<uint64_t>(k), 128, static_cast<uint32_t>(ntok),
-                CU_TENSOR_MAP_SWIZZLE_128B)) {
+  if (!make_map(&tw, w, static_cast<uint64_t>(n), kbytes, 128, static_cast<uint32_t>(cpc), CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_map(&tx, rows, static_cast<uint64_t>(m), kbytes, 128, static_cast<uint32_t>(ntok), CU_TENSOR_MAP_SWIZZLE_128B)) {
     *why = "cuTensorMapEncodeTiled refused an operand";
     return cudaErrorInvalidValue;
   }
@@ -692,7 +701,13 @@ cudaError_t fewrow_q8_linear(const uint8_t *codes, const float *row_scale, int m
   const int smem_bytes = stages * stage_bytes + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(q8::fewrow_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, q8::kSmemLimit);
+    cudaError_t e = cudaFuncSetAttribute(q8::fewrow_q8_kernel<kKindF8>, cudaFuncAttributeMaxDynamicSharedMemorySize, q8::kSmemLimit);
+    if (e == cudaSuccess) {
+      e = cudaFuncSetAttribute(q8::fewrow_q8_kernel<kKindF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, q8::kSmemLimit);
+    }
+    if (e == cudaSuccess) {
+      e = cudaFuncSetAttribute(q8::fewrow_q8_kernel<kKindBF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, q8::kSmemLimit);
+    }
     if (e != cudaSuccess) {
       *why = "cudaFuncSetAttribute(max dynamic shared memory) failed";
       return e;
@@ -713,11 +728,12 @@ cudaError_t fewrow_q8_linear(const uint8_t *codes, const float *row_scale, int m
   p.m = m;
   p.n = n;
   p.k = k;
+  p.kbytes = static_cast<int>(kbytes);
   p.ntok = ntok;
   p.cpc = cpc;
   p.stages = stages;
   const int acc_cols = q8::kIssuers * q8::kQChains * ntok;
-  p.tmem_cols = acc_cols <= 128 ? 128u : acc_cols <= 256 ? 256u : 512u;
+  p.tmem_cols = acc_cols <= 64 ? 64u : acc_cols <= 128 ? 128u : acc_cols <= 256 ? 256u : 512u;
   p.status = status;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>((n + cpc - 1) / cpc), 1, 1);
@@ -729,9 +745,36 @@ cudaError_t fewrow_q8_linear(const uint8_t *codes, const float *row_scale, int m
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, q8::fewrow_q8_kernel, tw, tx, p);
+  cudaError_t e = elem == 1   ? cudaLaunchKernelEx(&cfg, q8::fewrow_q8_kernel<kKindF8>, tw, tx, p)
+                  : is_bf16   ? cudaLaunchKernelEx(&cfg, q8::fewrow_q8_kernel<kKindBF16>, tw, tx, p)
+                              : cudaLaunchKernelEx(&cfg, q8::fewrow_q8_kernel<kKindF16>, tw, tx, p);
   if (e != cudaSuccess) *why = "kernel launch failed";
   return e;
+}
+
+}  // namespace
+
+cudaError_t fewrow_q8_linear(const uint8_t *codes, const float *row_scale, int m, int n, int k, const uint8_t *w,
+                             const float *col_scale, int col_scale_scalar, const void *bias, const void *residual,
+                             int residual_rows, int64_t residual_ld, int act, int is_bf16, void *out, uint32_t *status,
+                             cudaStream_t stream, const char **why) {
+  return launch_q8(1, codes, row_scale, m, n, k, w, col_scale, col_scale_scalar, bias, residual, residual_rows, residual_ld,
+                   act, is_bf16, out, status, stream, why);
+}
+
+bool fewrow_w16_supported(int m, int n, int k, const void *x, const void *w, const void *out) {
+  if (m < 1 || m > q8::kMaxTokens || n < 8 || n % 8 != 0 || k < 8 || k % 8 != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(out) & 1)) {
+    return false;
+  }
+  return encode_fn() != nullptr;
+}
+
+cudaError_t fewrow_w16_matmul(const void *x, int is_bf16, int m, int n, int k, const void *w, const void *bias,
+                              const void *residual, int residual_rows, int64_t residual_ld, void *out, uint32_t *status,
+                              cudaStream_t stream, const char **why) {
+  return launch_q8(2, x, nullptr, m, n, k, w, nullptr, 0, bias, residual, residual_rows, residual_ld, 0, is_bf16, out, status,
+                   stream, why);
 }
 
 }  // namespace flsm100

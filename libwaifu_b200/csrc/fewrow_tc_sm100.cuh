@@ -32,4 +32,12 @@ cudaError_t fewrow_q8_linear(const uint8_t *codes, const float *row_scale, int m
                              int residual_rows, int64_t residual_ld, int act, int is_bf16, void *out, uint32_t *status,
                              cudaStream_t stream, const char **why);
 
+// The same kernel on 16-bit operands (fl_matmul's linear-layer case, kind::f16): x (m, k) and w (n, k)
+// half or bfloat16, out = round16(x . w^T + bias (n) + residual rows). At most 64 rows, k and n
+// multiples of 8, x and w 16-byte aligned.
+bool fewrow_w16_supported(int m, int n, int k, const void *x, const void *w, const void *out);
+cudaError_t fewrow_w16_matmul(const void *x, int is_bf16, int m, int n, int k, const void *w, const void *bias,
+                              const void *residual, int residual_rows, int64_t residual_ld, void *out, uint32_t *status,
+                              cudaStream_t stream, const char **why);
+
 }  // namespace flsm100

@@ -1256,16 +1256,40 @@ int32_t fl_matmul_add(fl_operators_t operators, fl_tensor_view_t a_h, fl_tensor_
       const int m = static_cast<int>(m64);
       // A handful of rows (the reference keeps a GEMV for this, flint/cuda/matvec.cu): one
       // bandwidth-shaped launch with the bias or residual in its epilogue, no scratch.
-      if (m <= 16) {
+      if (m <= 64) {
         static const bool no_skinny = []() {
           const char *v = std::getenv("FLINT_SM100_NO_SKINNY");
           return v && v[0] == '1';
+        }();
+        static const bool no_fewrow_tc = [] {
+          const char *e = std::getenv("FLINT_SM100_NO_FEWROW_TC");
+          return e && e[0] == '1';
         }();
         AddendPlan quick;
         std::vector<int32_t> bs;
         std::vector<int64_t> bt;
         if (addend) quick = plan_addend(*addend, out, &bs, &bt);
-        if (!no_skinny && !quick.needs_expand &&
+        // Against a wide weight: the weight on the M side of the tensor-core instruction
+        // (fewrow_tc_sm100.cu), whose time does not grow with the rows.
+        // Where it measured faster (1-64 rows, 3072-16384 channels, k = 3072 and 12288) than the
+        // kernel underneath (at most 16 rows, mma.sync) and the tile kernel: 16 x 16384 x 3072
+        // 19.3 us against 40.3, 32 x 8192 x 3072 15.0 against 21.9, 1 x 16384 x 12288 61.8 against
+        // 77.9 (6.5 TB/s of weight).
+        const bool fewrow_w16_wins = k < 2048 ? false
+                                     : m > 32 ? n >= 16384 || (n >= 3072 && k <= 6144)
+                                     : m >= 8 ? n >= 3072
+                                     : m >= 4 ? n >= 6144
+                                              : n >= 16384;
+        if (!no_skinny && !no_fewrow_tc && !quick.needs_expand && fewrow_w16_wins &&
+            fewrow_w16_supported(m, n, k, raw_ptr(a), raw_ptr(b), raw_ptr(out)) && (!quick.residual || quick.residual_rows > 0)) {
+          const char *why = "";
+          cudaError_t e = fewrow_w16_matmul(raw_ptr(a), is_bf16, m, n, k, raw_ptr(b), quick.bias, quick.residual,
+                                            quick.residual_rows, quick.residual_ld, raw_ptr(out), status_word(), 0, &why);
+          if (e != cudaSuccess) cuda_check(e, (std::string("few-row matmul: ") + why).c_str());
+          ++g_gemm_launches;
+          return clear_error();
+        }
+        if (m <= 16 && !no_skinny && !quick.needs_expand &&
             skinny_w16_supported(m, n, k, raw_ptr(a), raw_ptr(b), raw_ptr(out), quick.residual != nullptr)) {
           cuda_check(skinny_w16_matmul(raw_ptr(a), is_bf16, m, n, k, raw_ptr(b), quick.bias, quick.residual, quick.residual_rows,
                                        quick.residual_ld, raw_ptr(out), status_word(), 0),

@@ -30,6 +30,30 @@ def test_linear_16(flint, oracle, is_bf16, m, n, k):
     check_parity(oracle, got_b, oracle.epilogue(acc, bias=bias, out_is_bf16=is_bf16), is_bf16, what="matmul_add")
 
 
+@pytest.mark.parametrize("is_bf16", [False, True])
+@pytest.mark.parametrize("m,n,k", [(5, 6144, 2048), (16, 3080, 2056), (33, 3072, 2048), (64, 16384, 2048), (2, 16392, 2304),
+                                   (24, 19080, 2048)])
+def test_few_rows_wide_weight(flint, oracle, is_bf16, m, n, k):
+    """At most 64 rows against a wide 16-bit weight: the weight on the M side of the tensor-core
+    instruction. No addend, a bias, a residual; a ragged last block of channels, rows whose bytes
+    end inside a stage, more CTAs than SMs."""
+    F = flint
+    rng = np.random.default_rng(m * 11 + n + k)
+    dt = F.DType.BFLOAT16 if is_bf16 else F.DType.FLOAT16
+    a = oracle.narrow(randn(rng, (m, k)), is_bf16)
+    w = oracle.narrow(randn(rng, (n, k), 0.05), is_bf16)
+    bias = oracle.narrow(randn(rng, (n,), 0.1), is_bf16)
+    res = oracle.narrow(randn(rng, (m, n)), is_bf16)
+    dev = lambda x: F.Tensor.from_numpy(x, dt, F.Device.CUDA)
+    acc = oracle.gemm_f32_nt(oracle.widen(a, is_bf16), oracle.widen(w, is_bf16))
+    ad, wd = dev(a), dev(w)
+    check_parity(oracle, F.linear_16(ad, wd).numpy(), oracle.epilogue(acc, out_is_bf16=is_bf16), is_bf16, what="matmul")
+    check_parity(oracle, F.linear_16(ad, wd, dev(bias)).numpy(), oracle.epilogue(acc, bias=bias, out_is_bf16=is_bf16), is_bf16,
+                 what="matmul_add bias")
+    check_parity(oracle, F.linear_16(ad, wd, dev(res)).numpy(), oracle.epilogue(acc, residual=res, out_is_bf16=is_bf16), is_bf16,
+                 what="matmul_add residual")
+
+
 def matmul(F, a, b, out_dtype, addend=None):
     out = F.Tensor.empty(tuple(a.shape[:-1]) + (b.shape[-1],), out_dtype)
     if addend is None:
