@@ -1111,7 +1111,7 @@ int32_t fl_fp8_matmul_add(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tens
       // from 6144, eight or more from 3072; on shallower rows, where its fixed part weighs more,
       // only what was measured there. The instruction's time does not grow with its N, so 17 to 32
       // rows cost what 16 cost (32 x 16384 x 3072: 13.2 us against the tile kernel's 27.5) and 33
-      // to 64 a little more (18.6 us; with 12288-deep rows only the widest weights gain).
+      // to 64 a little more (64 x 16384 x 3072: 14.9 us against 27.2).
       static const bool no_fewrow_tc = [] {
         const char *e = std::getenv("FLINT_SM100_NO_FEWROW_TC");
         return e && e[0] == '1';
@@ -1119,8 +1119,7 @@ int32_t fl_fp8_matmul_add(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tens
       const bool fewrow_tc_wins =
           m <= 16 ? (k >= 2048 ? rows >= 8192 || (rows >= 6144 && m >= 2) || (rows >= 3072 && m >= 8)
                                : rows >= 16384 || (rows >= 12288 && m >= 4) || (rows >= 8192 && m >= 8))
-          : m <= 32 ? k >= 2048 && rows >= 3072
-                    : k >= 2048 && (rows >= 16384 || (rows >= 3072 && k <= 6144));
+                  : k >= 2048 && rows >= 3072;
       if (!no_skinny && !no_fewrow_tc && !quick.needs_expand && fewrow_tc_wins &&
           fewrow_tc_supported(m, rows, k, is_bf16, raw_ptr(a), raw_ptr(weight), raw_ptr(out)) &&
           (!quick.residual || quick.residual_rows > 0)) {
