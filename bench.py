@@ -995,7 +995,7 @@ def run_skinny(args):
     import torch
     from libwaifu_b200 import flint as F
     wl = dict(WORKLOADS["skinny_decode"])
-    if args.rows:  # (up to 16 rows; up to 32 through fl_fp8_linear)
+    if args.rows:  # (up to 64 rows; up to 32 through fl_fp8_linear)
         wl["m"] = args.rows
         wl["desc"] = wl["desc"] + f" [{args.rows} rows]"
     linear = args.decode_entry == "fp8_linear"
