@@ -27,6 +27,114 @@ __device__ __forceinline__ uint16_t narrow(float v, int is_bf16) {
 constexpr int kUnits = 2;
 constexpr int kMaxWarps = 16;
 
+// Two float32 values in one 64-bit register and instructions that work on both lanes at once, each
+// lane rounded as the scalar instruction rounds it: this kernel is bound by instruction issue.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float *lo, float *hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(*lo), "=f"(*hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t bf16x2_widen(uint32_t w) {
+  return f2_pack(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+__device__ __forceinline__ uint32_t bf16x2_narrow(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+// The kernel below for bfloat16 rows, a pair (one 32-bit word: the even and the odd element of a
+// rotation) at a time: the same operations per element in the same order, the head's sum of
+// squares kept in two lanes that are added before the shuffles.
+template <int LPH>
+__global__ void __launch_bounds__(kMaxWarps * 32) qk_norm_rope_bf16_kernel(uint16_t *__restrict__ qkv, int heads, int tokens,
+                                                                         const uint16_t *__restrict__ q_weight,
+                                                                         const uint16_t *__restrict__ k_weight,
+                                                                         const float *__restrict__ cos,
+                                                                         const float *__restrict__ sin, float eps) {
+  griddep_wait();
+  griddep_launch_dependents();
+  constexpr int HEAD_DIM = LPH * 8;
+  constexpr int HPW = 32 / LPH;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / LPH;
+  const int part = lane % LPH;
+  const int per_row = 2 * heads;
+  const int first = (blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5)) * kUnits * HPW;
+  const int64_t row = blockIdx.x;
+  const int pos = static_cast<int>(blockIdx.x % static_cast<unsigned>(tokens));
+
+  uint16_t *p[kUnits];
+  uint4 raw[kUnits];
+#pragma unroll
+  for (int u = 0; u < kUnits; ++u) {
+    const int slot = first + u * HPW + sub;
+    p[u] = nullptr;
+    if (slot < per_row) {
+      p[u] = qkv + row * (3LL * heads * HEAD_DIM) + static_cast<int64_t>(slot) * HEAD_DIM + part * 8;
+      raw[u] = *reinterpret_cast<const uint4 *>(p[u]);
+    } else {
+      raw[u] = make_uint4(0, 0, 0, 0);
+    }
+  }
+  const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cos + static_cast<int64_t>(pos) * (HEAD_DIM / 2)) + part);
+  const float4 s4 = __ldg(reinterpret_cast<const float4 *>(sin + static_cast<int64_t>(pos) * (HEAD_DIM / 2)) + part);
+  const uint64_t cc[4] = {f2_pack(c4.x, c4.x), f2_pack(c4.y, c4.y), f2_pack(c4.z, c4.z), f2_pack(c4.w, c4.w)};
+  const uint64_t sn[4] = {f2_pack(s4.x, s4.x), f2_pack(s4.y, s4.y), f2_pack(s4.z, s4.z), f2_pack(s4.w, s4.w)};
+
+#pragma unroll
+  for (int u = 0; u < kUnits; ++u) {
+    const int slot = first + u * HPW + sub;
+    const uint32_t w4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+    uint64_t f[4];
+    uint64_t ss2 = f2_pack(0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[i] = bf16x2_widen(w4[i]);
+      ss2 = f2_fma(f[i], f[i], ss2);
+    }
+    float ss, ss_hi;
+    f2_unpack(ss2, &ss, &ss_hi);
+    ss += ss_hi;
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (!p[u]) continue;
+    const uint16_t *weight = slot < heads ? q_weight : k_weight;
+    const float inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(HEAD_DIM)), eps)));
+    const uint64_t inv2 = f2_pack(inv, inv);
+    if (weight) {
+      const uint4 wq = __ldg(reinterpret_cast<const uint4 *>(weight) + part);
+      const uint32_t ww[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) f[i] = f2_mul(f[i], bf16x2_widen(ww[i]));
+    }
+    uint32_t out[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float a, b;
+      f2_unpack(f2_mul(f[j], inv2), &a, &b);
+      const uint64_t n = bf16x2_widen(bf16x2_narrow(a, b));  // the norm's 16-bit output: (even, odd)
+      float ec, oc, es, os;
+      f2_unpack(f2_mul(n, cc[j]), &ec, &oc);
+      f2_unpack(f2_mul(n, sn[j]), &es, &os);
+      out[j] = bf16x2_narrow(__fsub_rn(ec, os), __fadd_rn(es, oc));
+    }
+    *reinterpret_cast<uint4 *>(p[u]) = make_uint4(out[0], out[1], out[2], out[3]);
+  }
+}
+
 template <int LPH>
 __global__ void __launch_bounds__(kMaxWarps * 32) qk_norm_rope_kernel(uint16_t *__restrict__ qkv, int is_bf16,
                                                                     int heads, int tokens,
@@ -123,6 +231,10 @@ cudaError_t launch(void *qkv, int is_bf16, int64_t rows, int heads, int tokens, 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (is_bf16) {
+    return cudaLaunchKernelEx(&cfg, qk_norm_rope_bf16_kernel<LPH>, static_cast<uint16_t *>(qkv), heads, tokens,
+                              static_cast<const uint16_t *>(qw), static_cast<const uint16_t *>(kw), cos, sin, eps);
+  }
   return cudaLaunchKernelEx(&cfg, qk_norm_rope_kernel<LPH>, static_cast<uint16_t *>(qkv), is_bf16, heads, tokens,
                             static_cast<const uint16_t *>(qw), static_cast<const uint16_t *>(kw), cos, sin, eps);
 }

@@ -332,6 +332,133 @@ __global__ void __launch_bounds__(THREADS) ln_modulate_quantize_reg_kernel(const
   }
 }
 
+// Two float32 values in one 64-bit register and the instructions that work on both lanes at once
+// (each lane rounded to nearest even exactly as the scalar instruction rounds it): the row kernels
+// are bound by instruction issue, not by memory, and these halve the arithmetic's instructions.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float *lo, float *hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(*lo), "=f"(*hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+// The two bfloat16 of a 32-bit word, widened: the low one in the low lane.
+__device__ __forceinline__ uint64_t bf16x2_widen(uint32_t w) {
+  return f2_pack(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+
+// ln_modulate_quantize_reg_kernel for bfloat16 rows with the arithmetic two elements at a time:
+// the same operations in the same order per element (v - mean is v + (-mean) bit for bit), the
+// statistics summed in two lanes that are added at the end, the row's largest magnitude kept as
+// a bfloat16 pair.
+template <int VPT, int THREADS>
+__global__ void __launch_bounds__(THREADS) ln_modulate_quantize_bf16_kernel(const uint16_t *__restrict__ x, int k,
+                                                                      const uint16_t *__restrict__ scale,
+                                                                      const uint16_t *__restrict__ shift,
+                                                                      int rows_per_group, int64_t scale_pitch,
+                                                                      int64_t shift_pitch, float eps,
+                                                                      uint8_t *__restrict__ codes,
+                                                                      float *__restrict__ row_scales) {
+  griddep_wait();
+  __shared__ float red[8];
+  __shared__ float2 red2[8];
+  const int64_t row = blockIdx.x;
+  const uint4 *xv = reinterpret_cast<const uint4 *>(x + row * k);
+  uint2 *cv = reinterpret_cast<uint2 *>(codes + row * k);
+  const int64_t group = row / rows_per_group;
+  const uint16_t *s = scale ? scale + group * scale_pitch : nullptr;
+  const uint16_t *t = shift ? shift + group * shift_pitch : nullptr;
+  const int nvec = k / 8;
+  uint4 q[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    q[i] = (v < nvec) ? xv[v] : make_uint4(0, 0, 0, 0);
+  }
+  uint64_t sum2 = f2_pack(0.0f, 0.0f), sq2 = sum2;  // the zero padding of the last vectors adds nothing to either
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const uint32_t w[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint64_t p = bf16x2_widen(w[j]);
+      sum2 = f2_add(sum2, p);
+      sq2 = f2_fma(p, p, sq2);
+    }
+  }
+  float s0, s1, q0, q1;
+  f2_unpack(sum2, &s0, &s1);
+  f2_unpack(sq2, &q0, &q1);
+  const float2 stats = mean_rstd(block_sum2(s0 + s1, q0 + q1, red2), k, eps);
+  const uint64_t neg_mean2 = f2_pack(-stats.x, -stats.x), rstd2 = f2_pack(stats.y, stats.y);
+  __nv_bfloat162 amax2 = __floats2bfloat162_rn(0.0f, 0.0f);
+  const uint4 *sv = reinterpret_cast<const uint4 *>(s);
+  const uint4 *tv = reinterpret_cast<const uint4 *>(t);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    if (v < nvec) {
+      const uint32_t w[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+      const uint4 s4 = s ? __ldg(sv + v) : make_uint4(0, 0, 0, 0);
+      const uint4 t4 = t ? __ldg(tv + v) : make_uint4(0, 0, 0, 0);
+      const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
+      const uint32_t tw[4] = {t4.x, t4.y, t4.z, t4.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint64_t y = f2_mul(f2_add(bf16x2_widen(w[j]), neg_mean2), rstd2);
+        if (s) y = f2_add(f2_mul(y, bf16x2_widen(sw[j])), y);
+        if (t) y = f2_add(y, bf16x2_widen(tw[j]));
+        float y0, y1;
+        f2_unpack(y, &y0, &y1);
+        const __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
+        amax2 = __hmax2(amax2, __habs2(h));
+        o[j] = *reinterpret_cast<const uint32_t *>(&h);
+      }
+      q[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+  float amax = fmaxf(__low2float(amax2), __high2float(amax2));
+  amax = block_max(amax, red);
+  const float qscale = __fdiv_rn(amax, 448.0f);
+  const float inv = __frcp_rn(qscale > 0.0f ? qscale : 1.0f);
+  if (threadIdx.x == 0) row_scales[row] = qscale;
+  griddep_launch_dependents();
+  const uint64_t inv2 = f2_pack(inv, inv);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    if (v < nvec) {
+      const uint32_t w[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+      uint32_t out[2] = {0, 0};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a, b;
+        f2_unpack(f2_mul(bf16x2_widen(w[j]), inv2), &a, &b);
+        const uint32_t two = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3));
+        out[j >> 1] |= (two & 0xffff) << ((j & 1) * 16);
+      }
+      cv[v] = make_uint2(out[0], out[1]);
+    }
+  }
+}
+
 // The same arithmetic for rows of any length and any alignment: the row is read three times (an
 // L1/L2 hit after the first) and the modulated value is computed twice.
 __global__ void __launch_bounds__(256) ln_modulate_quantize_kernel(const uint16_t *__restrict__ x, int is_bf16, int k,
@@ -709,7 +836,14 @@ cudaError_t ln_modulate_quantize_fp8(const void *x, int is_bf16, int m, int k, c
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e;
-  if (vec && k <= 1024 * 3) {
+  if (vec && is_bf16 && k <= 1024 * 3) {
+    cfg.blockDim = dim3(128, 1, 1);
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_bf16_kernel<3, 128>, xs, k, sc, sh, rows_per_group, scale_pitch, shift_pitch, eps, codes, row_scales);
+  } else if (vec && is_bf16 && k <= 2048 * 2) {
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_bf16_kernel<2, 256>, xs, k, sc, sh, rows_per_group, scale_pitch, shift_pitch, eps, codes, row_scales);
+  } else if (vec && is_bf16 && k <= 2048 * 4) {
+    e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_bf16_kernel<4, 256>, xs, k, sc, sh, rows_per_group, scale_pitch, shift_pitch, eps, codes, row_scales);
+  } else if (vec && k <= 1024 * 3) {
     cfg.blockDim = dim3(128, 1, 1);
     e = cudaLaunchKernelEx(&cfg, ln_modulate_quantize_reg_kernel<3, 128>, xs, is_bf16, k, sc, sh, rows_per_group, scale_pitch, shift_pitch, eps, codes, row_scales);
   } else if (vec && k <= 2048 * 2) {
