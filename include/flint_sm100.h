@@ -391,6 +391,13 @@ FLAPI int32_t fl_qk_norm_rope(fl_tensor_view_t qkv, fl_tensor_view_t q_weight, f
 FLAPI int32_t fl_sm100_few_rows_plan(int32_t m, int32_t n, int32_t k, int32_t weight_bytes, int32_t activation_bytes,
                                      int32_t has_residual, int32_t *plan);
 
+/* Which kernel a product of few rows takes by its shape alone (operands aligned, the environment's
+ * switches unset); host arithmetic only, no GPU needed. entry 0: fl_fp8_matmul[_add] with half
+ * rows, 1: fl_fp8_linear (and _static, _quantized), 2: fl_matmul[_add] on 16-bit operands; n the
+ * weight's rows (output channels). Returns 2: a tensor-core few-row kernel (the weight on the M side
+ * of the instruction), 1: the mma.sync few-row kernel, 0: the tile kernel; -1 for a bad argument. */
+FLAPI int32_t fl_sm100_few_rows_route(int32_t entry, int32_t m, int32_t n, int32_t k);
+
 /* Which tile kernel a product of `kind` (0 half, 1 bfloat16, 2 e4m3, 3 nvfp4) and shape would run on
  * and how its tiles are dealt out over a device of `sms` SMs; host arithmetic only, no GPU needed, so
  * that the schedule can be checked anywhere. plan[8]: [0] CTAs per unit (2: a cluster pair sharing a

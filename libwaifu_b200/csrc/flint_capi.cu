@@ -567,6 +567,28 @@ struct Epilogue {
   float *row_amax = nullptr;
 };
 
+// Where the tensor-core few-row kernels (fewrow_tc_sm100.cu) measured faster than what a product
+// would run on otherwise; the thresholds are measurements on a B200 over 1-64 rows, 3072-24576
+// channels and 3072- and 12288-deep rows. Host arithmetic only: fl_sm100_few_rows_route reports
+// them, so that the CPU tests pin them.
+// fl_fp8_matmul[_add], half rows against an e4m3 weight (fewrow_tc_kernel):
+bool fewrow_tc_route(int m, int rows, int k) {
+  if (m > 64) return false;
+  if (m > 16) return k >= 2048 && rows >= 3072;
+  return k >= 2048 ? rows >= 8192 || (rows >= 6144 && m >= 2) || (rows >= 3072 && m >= 8)
+                   : rows >= 16384 || (rows >= 12288 && m >= 4) || (rows >= 8192 && m >= 8);
+}
+// fl_matmul[_add], 16-bit rows against a 16-bit weight (fewrow_q8_kernel, kind::f16):
+bool fewrow_w16_route(int m, int n, int k) {
+  if (m > 64 || k < 2048) return false;
+  return m > 32 ? n >= 16384 || (n >= 3072 && k <= 6144) : m >= 8 ? n >= 3072 : m >= 4 ? n >= 6144 : n >= 16384;
+}
+// fl_fp8_linear and its relatives, quantised rows against an e4m3 weight (fewrow_q8_kernel):
+bool fewrow_q8_route(int m, int rows, int k) {
+  if (m > 32 || k < 2048) return false;
+  return m >= 4 ? rows >= 3072 : rows >= 8192;
+}
+
 // The stream-K workspace, from the pool in stream 0's order the first time a GEMM runs (38 MB on a
 // 148-SM card), kept for the life of the process.
 void stream_k_workspace(GemmArgs *g) {
@@ -1116,10 +1138,7 @@ int32_t fl_fp8_matmul_add(fl_tensor_view_t a_h, fl_tensor_view_t data_h, fl_tens
         const char *e = std::getenv("FLINT_SM100_NO_FEWROW_TC");
         return e && e[0] == '1';
       }();
-      const bool fewrow_tc_wins =
-          m <= 16 ? (k >= 2048 ? rows >= 8192 || (rows >= 6144 && m >= 2) || (rows >= 3072 && m >= 8)
-                               : rows >= 16384 || (rows >= 12288 && m >= 4) || (rows >= 8192 && m >= 8))
-                  : k >= 2048 && rows >= 3072;
+      const bool fewrow_tc_wins = fewrow_tc_route(m, rows, k);
       if (!no_skinny && !no_fewrow_tc && !quick.needs_expand && fewrow_tc_wins &&
           fewrow_tc_supported(m, rows, k, is_bf16, raw_ptr(a), raw_ptr(weight), raw_ptr(out)) &&
           (!quick.residual || quick.residual_rows > 0)) {
@@ -1274,11 +1293,7 @@ int32_t fl_matmul_add(fl_operators_t operators, fl_tensor_view_t a_h, fl_tensor_
         // kernel underneath (at most 16 rows, mma.sync) and the tile kernel: 16 x 16384 x 3072
         // 19.3 us against 40.3, 32 x 8192 x 3072 15.0 against 21.9, 1 x 16384 x 12288 61.8 against
         // 77.9 (6.5 TB/s of weight).
-        const bool fewrow_w16_wins = k < 2048 ? false
-                                     : m > 32 ? n >= 16384 || (n >= 3072 && k <= 6144)
-                                     : m >= 8 ? n >= 3072
-                                     : m >= 4 ? n >= 6144
-                                              : n >= 16384;
+        const bool fewrow_w16_wins = fewrow_w16_route(m, n, k);
         if (!no_skinny && !no_fewrow_tc && !quick.needs_expand && fewrow_w16_wins &&
             fewrow_w16_supported(m, n, k, raw_ptr(a), raw_ptr(b), raw_ptr(out)) && (!quick.residual || quick.residual_rows > 0)) {
           const char *why = "";
@@ -1495,8 +1510,7 @@ bool fewrow_q8_wins(int m, int rows, int k) {
     const char *a = std::getenv("FLINT_SM100_NO_SKINNY"), *b = std::getenv("FLINT_SM100_NO_FEWROW_TC");
     return (a && a[0] == '1') || (b && b[0] == '1');
   }();
-  if (off || m > 32 || k < 2048) return false;
-  return m >= 4 ? rows >= 3072 : rows >= 8192;
+  return !off && fewrow_q8_route(m, rows, k);
 }
 
 // Runs it if it wins and can take the operands; false when the tile kernel should run.
@@ -2513,6 +2527,16 @@ int32_t fl_sm100_few_rows_plan(int32_t m, int32_t n, int32_t k, int32_t weight_b
     skinny_plan(m, n, k, weight_bytes, activation_bytes, has_residual, plan);
     return clear_error();
   });
+}
+
+int32_t fl_sm100_few_rows_route(int32_t entry, int32_t m, int32_t n, int32_t k) {
+  if (m < 1 || n < 1 || k < 1) return -1;
+  switch (entry) {
+    case 0: return fewrow_tc_route(m, n, k) ? 2 : m <= 16 ? 1 : 0;
+    case 1: return fewrow_q8_route(m, n, k) ? 2 : m <= 4 ? 1 : 0;
+    case 2: return fewrow_w16_route(m, n, k) ? 2 : m <= 16 ? 1 : 0;
+    default: return -1;
+  }
 }
 
 int32_t fl_sm100_gemm_plan(int32_t kind, int32_t m, int32_t n, int32_t k, int32_t sms, int32_t allow_stream_k, int32_t *plan) {

@@ -77,3 +77,34 @@ def test_refused_shapes_report_zero():
     assert not any(plan(17, 64, 64, 1, 1, False))   # more than 16 rows
     assert not any(plan(1, 60, 64, 1, 1, False))    # channels not a multiple of 8
     assert not any(plan(16, 64, 16384, 1, 2, False))  # 16 rows of 32 KB do not fit beside a ring
+
+
+def route(entry, m, n, k):
+    L = F.lib()
+    L.fl_sm100_few_rows_route.argtypes = [ctypes.c_int32] * 4
+    L.fl_sm100_few_rows_route.restype = ctypes.c_int32
+    return L.fl_sm100_few_rows_route(entry, m, n, k)
+
+
+def test_few_row_routes():
+    """Which kernel a few-row product takes, at the shapes the thresholds were measured on: the
+    reference's decode shape and its neighbours go to the tensor-core few-row kernels, narrow or
+    shallow weights stay with the mma.sync kernel, more rows than a kernel takes go to the tile
+    kernel."""
+    TILE, MMA_SYNC, TENSOR = 0, 1, 2
+    # fl_fp8_matmul, half rows (docs/fp8.md:225-244 is 1 x 16384 x 3072)
+    assert route(0, 1, 16384, 3072) == TENSOR and route(0, 16, 16384, 3072) == TENSOR
+    assert route(0, 1, 8192, 3072) == TENSOR and route(0, 1, 6144, 3072) == MMA_SYNC and route(0, 2, 6144, 3072) == TENSOR
+    assert route(0, 4, 3072, 3072) == MMA_SYNC and route(0, 8, 3072, 3072) == TENSOR
+    assert route(0, 1, 8192, 1024) == MMA_SYNC and route(0, 1, 16384, 1024) == TENSOR
+    assert route(0, 17, 3072, 2048) == TENSOR and route(0, 64, 16384, 12288) == TENSOR
+    assert route(0, 17, 2048, 3072) == TILE and route(0, 65, 16384, 3072) == TILE and route(0, 32, 8192, 1024) == TILE
+    # fl_fp8_linear: rows quantised per token
+    assert route(1, 1, 16384, 3072) == TENSOR and route(1, 2, 18432, 3072) == TENSOR and route(1, 32, 3072, 3072) == TENSOR
+    assert route(1, 1, 3072, 3072) == MMA_SYNC and route(1, 4, 3072, 3072) == TENSOR and route(1, 4, 3072, 1024) == MMA_SYNC
+    assert route(1, 33, 16384, 3072) == TILE and route(1, 5, 2048, 3072) == TILE
+    # fl_matmul on 16-bit operands
+    assert route(2, 1, 16384, 3072) == TENSOR and route(2, 1, 8192, 3072) == MMA_SYNC and route(2, 4, 6144, 3072) == TENSOR
+    assert route(2, 8, 3072, 3072) == TENSOR and route(2, 64, 3072, 3072) == TENSOR and route(2, 64, 3072, 12288) == TILE
+    assert route(2, 64, 16384, 12288) == TENSOR and route(2, 16, 3072, 1024) == MMA_SYNC and route(2, 17, 3072, 1024) == TILE
+    assert route(3, 1, 8, 8) == -1 and route(0, 0, 8, 8) == -1
