@@ -617,16 +617,11 @@ __device__ __forceinline__ uint8_t nvfp4_block(const float (&v)[16], float globa
   return sc;
 }
 
-// One thread per 16-element block of a 16-bit activation.
-__global__ void __launch_bounds__(256) quantize_nvfp4_act_kernel(const uint16_t *__restrict__ x, int is_bf16, int m,
-                                                               int k, uint8_t *__restrict__ codes,
-                                                               uint8_t *__restrict__ sf_tiled, int sf_k_tiles,
-                                                               int vec_ok) {
-  const int blocks_per_row = k / 16;
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= static_cast<int64_t>(m) * blocks_per_row) return;
-  const int r = static_cast<int>(idx / blocks_per_row);
-  const int b = static_cast<int>(idx % blocks_per_row);
+// Block b of row r of a 16-bit activation: 16 values -> 8 code bytes and the block's scale factor
+// in the tile layout.
+__device__ __forceinline__ void nvfp4_act_block(const uint16_t *__restrict__ x, int is_bf16, int k, int r, int b,
+                                                uint8_t *__restrict__ codes, uint8_t *__restrict__ sf_tiled,
+                                                int sf_k_tiles, int vec_ok) {
   const uint16_t *src = x + static_cast<int64_t>(r) * k + 16 * b;
   float v[16];
   if (vec_ok) {
@@ -655,6 +650,63 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_act_kernel(const uint16_t 
     for (int j = 0; j < 8; ++j) dst[j] = static_cast<uint8_t>(packed[j >> 2] >> ((j & 3) * 8));
   }
   sf_tiled[sf_tiled_offset(r, b, sf_k_tiles)] = sc;
+}
+
+// One thread per 16-element block of a 16-bit activation.
+__global__ void __launch_bounds__(256) quantize_nvfp4_act_kernel(const uint16_t *__restrict__ x, int is_bf16, int m,
+                                                               int k, uint8_t *__restrict__ codes,
+                                                               uint8_t *__restrict__ sf_tiled, int sf_k_tiles,
+                                                               int vec_ok) {
+  griddep_wait();
+  griddep_launch_dependents();
+  const int blocks_per_row = k / 16;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(m) * blocks_per_row) return;
+  nvfp4_act_block(x, is_bf16, k, static_cast<int>(idx / blocks_per_row), static_cast<int>(idx % blocks_per_row), codes,
+                  sf_tiled, sf_k_tiles, vec_ok);
+}
+
+// Everything fl_nvfp4_linear does ahead of its GEMM in one launch (two clears, the activation
+// quantiser and the re-tiling of the weight's block scales were four, with a launch gap each).
+// CTAs [0, a_ctas): one thread per 16-element block of the activation over the whole tiled domain
+// (row groups of 128, K tiles of 4 blocks, `sf_k_tiles` per group): a block of the activation is
+// quantised, one of the padding gets the scale factor 0. The other CTAs: one thread per 4 block
+// scales of the weight (a 32-bit word of the tile layout) over its tiled domain and one spare row
+// group, zeros outside the weight. Nothing has to be cleared beforehand.
+__global__ void __launch_bounds__(256) nvfp4_prepare_kernel(const uint16_t *__restrict__ x, int is_bf16, int m, int k,
+                                                          uint8_t *__restrict__ codes, uint8_t *__restrict__ sfa_tiled,
+                                                          int sf_k_tiles, int vec_ok, int a_ctas,
+                                                          const uint8_t *__restrict__ wsf_plain, int rows, int w_groups,
+                                                          uint8_t *__restrict__ sfb_tiled) {
+  griddep_wait();
+  griddep_launch_dependents();
+  const int kblocks = k / 16;
+  if (static_cast<int>(blockIdx.x) < a_ctas) {
+    const int kb_pad = sf_k_tiles * 4;
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t total = static_cast<int64_t>((m + 127) / 128) * 128 * kb_pad;
+    if (idx >= total) return;
+    const int r = static_cast<int>(idx / kb_pad), b = static_cast<int>(idx % kb_pad);
+    if (r < m && b < kblocks) {
+      nvfp4_act_block(x, is_bf16, k, r, b, codes, sfa_tiled, sf_k_tiles, vec_ok);
+    } else {
+      sfa_tiled[sf_tiled_offset(r, b, sf_k_tiles)] = 0;
+    }
+    return;
+  }
+  const int64_t idx = static_cast<int64_t>(static_cast<int>(blockIdx.x) - a_ctas) * blockDim.x + threadIdx.x;
+  const int64_t total = static_cast<int64_t>(w_groups) * 128 * sf_k_tiles;
+  if (idx >= total) return;
+  const int r = static_cast<int>(idx / sf_k_tiles), t4 = static_cast<int>(idx % sf_k_tiles) * 4;
+  uint32_t word = 0;
+  if (r < rows) {
+    const uint8_t *src = wsf_plain + static_cast<int64_t>(r) * kblocks + t4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (t4 + j < kblocks) word |= static_cast<uint32_t>(src[j]) << (8 * j);
+    }
+  }
+  *reinterpret_cast<uint32_t *>(sfb_tiled + sf_tiled_offset(r, t4, sf_k_tiles)) = word;
 }
 
 __global__ void __launch_bounds__(256) amax_f32_kernel(const float *__restrict__ w, int64_t numel, uint32_t *amax_word) {
@@ -898,10 +950,42 @@ cudaError_t quantize_nvfp4_act(const void *x, int is_bf16, int m, int k, uint8_t
   const int64_t blocks = static_cast<int64_t>(m) * (k / 16);
   const int grid = static_cast<int>((blocks + 255) / 256);
   const int vec = aligned16(x) && (reinterpret_cast<uintptr_t>(codes) & 7) == 0;
-  quantize_nvfp4_act_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t *>(x), is_bf16, m, k, codes,
-                                                     sf_tiled, sf_k_tiles_for(k), vec);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, quantize_nvfp4_act_kernel, static_cast<const uint16_t *>(x), is_bf16, m, k, codes,
+                                     sf_tiled, sf_k_tiles_for(k), vec);
   ++g_helper_launches;
-  return cudaGetLastError();
+  return e;
+}
+
+cudaError_t nvfp4_prepare(const void *x, int is_bf16, int m, int k, uint8_t *codes, uint8_t *sfa_tiled,
+                          const uint8_t *wsf_plain, int rows, int w_extra_groups, uint8_t *sfb_tiled, cudaStream_t stream) {
+  const int sf_k_tiles = sf_k_tiles_for(k);
+  const int64_t a_threads = static_cast<int64_t>((m + 127) / 128) * 128 * sf_k_tiles * 4;
+  const int w_groups = (rows + 127) / 128 + w_extra_groups;
+  const int64_t b_threads = static_cast<int64_t>(w_groups) * 128 * sf_k_tiles;
+  const int a_ctas = static_cast<int>((a_threads + 255) / 256), b_ctas = static_cast<int>((b_threads + 255) / 256);
+  const int vec = aligned16(x) && (reinterpret_cast<uintptr_t>(codes) & 7) == 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(a_ctas + b_ctas), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, nvfp4_prepare_kernel, static_cast<const uint16_t *>(x), is_bf16, m, k, codes,
+                                     sfa_tiled, sf_k_tiles, vec, a_ctas, wsf_plain, rows, w_groups, sfb_tiled);
+  ++g_helper_launches;
+  return e;
 }
 
 cudaError_t quantize_nvfp4_weight_f32(const float *w, int rows, int k, uint8_t *codes, uint8_t *sf_plain,

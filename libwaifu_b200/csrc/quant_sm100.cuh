@@ -49,6 +49,12 @@ inline int64_t sf_tiled_bytes(int rows, int k, int extra_groups) {
 // scale factors written straight into the tile layout (`sf_tiled` zeroed by the caller).
 cudaError_t quantize_nvfp4_act(const void *x, int is_bf16, int m, int k, uint8_t *codes, uint8_t *sf_tiled,
                                cudaStream_t stream);
+// What fl_nvfp4_linear needs ahead of its GEMM, in one launch: the activation's codes and tiled
+// scale factors (quantize_nvfp4_act) and the weight's plain (rows, k/16) block scales in the tile
+// layout with `w_extra_groups` spare row groups (pack_scale_factors), padding written as zeros, so
+// neither destination has to be cleared first.
+cudaError_t nvfp4_prepare(const void *x, int is_bf16, int m, int k, uint8_t *codes, uint8_t *sfa_tiled,
+                          const uint8_t *wsf_plain, int rows, int w_extra_groups, uint8_t *sfb_tiled, cudaStream_t stream);
 // NVFP4 weight from fp32: global = amax / (448 * 6); plain (rows, k/16) block scales.
 // `amax_word` is a device word used for the reduction.
 cudaError_t quantize_nvfp4_weight_f32(const float *w, int rows, int k, uint8_t *codes, uint8_t *sf_plain,
