@@ -799,7 +799,11 @@ attention2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     }
   } else if (warp == kMmaWarp2) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loop and one lane issues: what an instruction takes (descriptors,
+    // addresses) is then the same in every lane, which lets it live in uniform registers instead of
+    // being moved there instruction by instruction by a lone thread.
+    const bool issuer = lane == 0;
+    {
       const uint32_t fmt = p.is_bf16 ? 1u : 0u;
       const uint32_t idesc_s = umma_idesc(kBlockQ, kBlockKv, fmt, fmt);
       const uint32_t idesc_o = umma_idesc(kBlockQ, D, fmt, fmt);
@@ -816,7 +820,7 @@ attention2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 #pragma unroll
         for (int m = 0; m < kScoreMmas; ++m) {
           const int a = m / kMmasPerAtom, s = m % kMmasPerAtom;
-          umma_ss<kKindF16>(s_tmem, qd + (((a * kBlockQ * kAtomBytes) >> 4) + s * kMmaStep),
+          if (issuer) umma_ss<kKindF16>(s_tmem, qd + (((a * kBlockQ * kAtomBytes) >> 4) + s * kMmaStep),
                             kd + (((a * kBlockKv * kAtomBytes) >> 4) + s * kMmaStep), idesc_s, m != 0 ? 1u : 0u);
         }
       };
@@ -831,14 +835,14 @@ attention2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (p.v_direct) {
 #pragma unroll
           for (int m = 0; m < kOutMmas; ++m) {
-            umma_ts_f16(o_tmem, p_tmem + m * 8, (vd ^ mn_fields) + static_cast<uint64_t>(m * ((16 * kAtomBytes) >> 4)), idesc_o_mn,
+            if (issuer) umma_ts_f16(o_tmem, p_tmem + m * 8, (vd ^ mn_fields) + static_cast<uint64_t>(m * ((16 * kAtomBytes) >> 4)), idesc_o_mn,
                         m != 0 ? 1u : (first_block ^ 1u));
           }
         } else {
 #pragma unroll
           for (int m = 0; m < kOutMmas; ++m) {
             const int a = m / kMmasPerAtom, s = m % kMmasPerAtom;
-            umma_ts_f16(o_tmem, p_tmem + m * 8, vd + (((a * L::kVAtomBytes) >> 4) + s * kMmaStep), idesc_o,
+            if (issuer) umma_ts_f16(o_tmem, p_tmem + m * 8, vd + (((a * L::kVAtomBytes) >> 4) + s * kMmaStep), idesc_o,
                         m != 0 ? 1u : (first_block ^ 1u));
           }
         }
@@ -851,9 +855,9 @@ attention2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         tc_fence_after_sync();
         for (int i = 0; i < kTiles; ++i) {
           scores(i, desc_of(0));
-          umma_commit(&t.s_full_bar[i]);
+          if (issuer) umma_commit(&t.s_full_bar[i]);
         }
-        umma_commit(&t.slot_empty_bar[0]);
+        if (issuer) umma_commit(&t.slot_empty_bar[0]);
       }
       for (int j = 0; j < num_blocks && ok; ++j) {
         const bool more = j + 1 < num_blocks;
@@ -869,18 +873,18 @@ attention2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           // The product reads P from the columns the next scores overwrite: the instructions of one
           // thread run in the order they were issued.
           product(i, desc_of(nv), first_block);
-          if (!more) umma_commit(&t.pv_done_bar[i]);  // (a block's scores, which the softmax waits for, follow its product)
+          if (!more && issuer) umma_commit(&t.pv_done_bar[i]);  // (a block's scores, which the softmax waits for, follow its product)
           if (more) {
             scores(i, desc_of(nk));
-            umma_commit(&t.s_full_bar[i]);
+            if (issuer) umma_commit(&t.s_full_bar[i]);
           }
           if (i == kTiles - 1) {  // both tiles have read the two slots
-            umma_commit(&t.slot_empty_bar[nv % S]);
-            if (more) umma_commit(&t.slot_empty_bar[nk % S]);
+            if (issuer) umma_commit(&t.slot_empty_bar[nv % S]);
+            if (more && issuer) umma_commit(&t.slot_empty_bar[nk % S]);
           }
         }
       }
-      if (!ok) {
+      if (!ok && issuer) {
         abort_flag = 1;
         atomicCAS(p.status, 0u, kStatusAttentionTimeout);
       }
