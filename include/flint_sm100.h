@@ -366,6 +366,15 @@ FLAPI int32_t fl_fp8_linear_quantized(fl_tensor_view_t codes, fl_tensor_view_t r
                                       fl_tensor_view_t scales, fl_tensor_view_t bias, fl_tensor_view_t residual,
                                       int32_t act, fl_tensor_view_t out);
 
+/* fl_fp8_linear_quantized with row groups: rows [g * rows_per_group, (g + 1) * rows_per_group) of the
+ * left operand take their per-channel scales and bias from row g of `scales` <float>(groups, rows)
+ * and `bias` (groups, rows) -- a gate per image folded into the scales and the bias of one product
+ * (x + gate * linear(a): waifu/src/qwen_image/dit.rs:322-335) without one launch per image.
+ * rows_per_group is a multiple of 256 (no tile of the product holds rows of two groups). */
+FLAPI int32_t fl_fp8_linear_quantized_grouped(fl_tensor_view_t codes, fl_tensor_view_t row_scales, fl_tensor_view_t data,
+                                              fl_tensor_view_t scales, fl_tensor_view_t bias, fl_tensor_view_t residual,
+                                              int32_t act, int32_t rows_per_group, fl_tensor_view_t out);
+
 /* The step between the fused q/k/v projection and attention, in place on the projection's output
  * qkv <float16|bfloat16>(..., 3 * heads * head_dim) (q heads, k heads, v heads along the last
  * dimension; head_dim 64, 128 or 256; every operand 16-byte aligned): per row and q or k head,

@@ -564,6 +564,7 @@ struct Epilogue {
   int residual_rows = 0;
   int64_t residual_ld = 0;
   int act = 0;
+  int rows_per_group = 0;
   float *row_amax = nullptr;
 };
 
@@ -636,6 +637,7 @@ void run_gemm(GemmKind kind, int m, int n, int k, const void *a, const void *b, 
   g.residual_rows = ep.residual_rows;
   g.residual_ld = ep.residual_ld;
   g.act = ep.act;
+  g.rows_per_group = ep.rows_per_group;
   g.row_amax = ep.row_amax;
   g.out_bf16 = out_bf16;
   g.out = out;
@@ -2116,11 +2118,21 @@ namespace {
 int32_t fp8_linear_quantized_impl(fl_tensor_view_t codes_h, fl_tensor_view_t row_scales_h, fl_tensor_view_t data_h,
                                   fl_tensor_view_t scales_h, fl_tensor_view_t bias_h, fl_tensor_view_t residual_h,
                                   int32_t act, fl_tensor_view_t out_h, const fl_tensor_view_t *dests, int32_t n_dest,
-                                  int32_t col0) {
+                                  int32_t col0, int32_t rows_per_group = 0) {
   return guard([&]() -> int32_t {
     const fl_tensor_view_impl_t &weight = deref(data_h);
     const fl_tensor_view_impl_t &scales = deref(scales_h);
-    check_fp8_weight(weight, scales, /*per_channel_ok=*/true);
+    if (rows_per_group == 0) {
+      check_fp8_weight(weight, scales, /*per_channel_ok=*/true);
+    } else {
+      // Row groups: the scales (and the bias) are (groups, rows) matrices, row g for the rows of group g.
+      if (dtype_of(weight) != FL_DTYPE_FP8E4M3 || weight.shape.size() != 2 || !is_contiguous(weight) ||
+          numel_of(weight) >= INT32_MAX) {
+        invalid("fp8 operand: data is not a contiguous <fp8e4m3>(rows, k)");
+      }
+      if (rows_per_group < 0 || rows_per_group % 256 != 0) invalid("rows_per_group is not a positive multiple of 256");
+      if (!out_h) invalid("row groups and a scattered result do not combine");
+    }
     const fl_device_type_t device = device_of(weight);
     const int rows = weight.shape[0];
     const int k = weight.shape[1];
@@ -2156,10 +2168,16 @@ int32_t fp8_linear_quantized_impl(fl_tensor_view_t codes_h, fl_tensor_view_t row
     if (act != FL_ACT_NONE && act != FL_ACT_GELU_TANH) invalid("unknown activation");
     const fl_tensor_view_impl_t *bias = bias_h ? &deref(bias_h) : nullptr;
     const fl_tensor_view_impl_t *residual = residual_h ? &deref(residual_h) : nullptr;
+    const int64_t groups = rows_per_group > 0 ? (m64 + rows_per_group - 1) / rows_per_group : 1;
+    if (rows_per_group > 0 && (dtype_of(scales) != FL_DTYPE_FLOAT || numel_of(scales) != groups * rows || !is_contiguous(scales) ||
+                               device_of(scales) != device)) {
+      invalid("the scales are not a contiguous <float>(groups, rows) matrix on the weight's device");
+    }
     if (bias) {
-      if (device_of(*bias) != device || dtype_of(*bias) != out_dtype || numel_of(*bias) != rows ||
+      if (device_of(*bias) != device || dtype_of(*bias) != out_dtype || numel_of(*bias) != groups * rows ||
           !is_contiguous(*bias)) {
-        invalid("the bias is not a contiguous (rows) vector of out's type on the weight's device");
+        invalid(rows_per_group > 0 ? "the bias is not a contiguous (groups, rows) matrix of out's type on the weight's device"
+                                   : "the bias is not a contiguous (rows) vector of out's type on the weight's device");
       }
     }
     if (residual) {
@@ -2209,12 +2227,14 @@ int32_t fp8_linear_quantized_impl(fl_tensor_view_t codes_h, fl_tensor_view_t row
       ep.residual_ld = rows;
     }
     ep.act = act;
+    ep.rows_per_group = rows_per_group;
     if (!out_h) {
       ep.out_ld = sd.ld;
       ep.out_col0 = col0;
       for (int i = 0; i < sd.num_extra; ++i) ep.extra_out[ep.num_extra_out++] = sd.extra[i];
     }
-    if (out_h && try_fewrow_q8(reinterpret_cast<const uint8_t *>(a_ptr), ep.row_scale, m, rows, k, w_ptr, ep,
+    if (out_h && rows_per_group == 0 &&
+        try_fewrow_q8(reinterpret_cast<const uint8_t *>(a_ptr), ep.row_scale, m, rows, k, w_ptr, ep,
                                out_dtype == FL_DTYPE_BFLOAT16, sd.first, status_word())) {
       return clear_error();
     }
@@ -2230,6 +2250,15 @@ int32_t fl_fp8_linear_quantized(fl_tensor_view_t codes_h, fl_tensor_view_t row_s
                                 int32_t act, fl_tensor_view_t out_h) {
   if (!out_h) return guard([&]() -> int32_t { invalid("out is null"); });
   return fp8_linear_quantized_impl(codes_h, row_scales_h, data_h, scales_h, bias_h, residual_h, act, out_h, nullptr, 0, 0);
+}
+
+int32_t fl_fp8_linear_quantized_grouped(fl_tensor_view_t codes_h, fl_tensor_view_t row_scales_h, fl_tensor_view_t data_h,
+                                        fl_tensor_view_t scales_h, fl_tensor_view_t bias_h, fl_tensor_view_t residual_h,
+                                        int32_t act, int32_t rows_per_group, fl_tensor_view_t out_h) {
+  if (!out_h) return guard([&]() -> int32_t { invalid("out is null"); });
+  if (rows_per_group <= 0) return guard([&]() -> int32_t { invalid("rows_per_group is not a positive multiple of 256"); });
+  return fp8_linear_quantized_impl(codes_h, row_scales_h, data_h, scales_h, bias_h, residual_h, act, out_h, nullptr, 0, 0,
+                                   rows_per_group);
 }
 
 int32_t fl_fp8_linear_quantized_scatter(fl_tensor_view_t codes_h, fl_tensor_view_t row_scales_h, fl_tensor_view_t data_h,

@@ -106,6 +106,7 @@ struct KernelParams {
   const void *bias;
   const void *residual;
   int residual_rows;
+  int rows_per_group;
   long long residual_ld;
   int act;
   float *row_amax;  // (m) or null: per-row maximum of the rounded results' magnitudes, by atomicMax on the float's bits
@@ -780,10 +781,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // memory.
       if (has_cs_vec || has_bias) {
         __syncwarp();  // the previous tile's reads are done
+        // (with row groups, the tile's group picks the row of the (groups, n) scales and bias)
+        const long long goff = p.rows_per_group > 0 ? static_cast<long long>((tm * (kBlockM * CTAS)) / p.rows_per_group) * p.n : 0;
         for (int i = lane; i < HALF_N; i += 32) {
           const int n = n0 + i;
-          cs_t[i] = (has_cs_vec && n < p.n) ? __ldg(p.col_scale + n) : 1.0f;
-          bias_t[i] = (has_bias && n < p.n) ? load16(p.bias, n, is_bf16) : 0.0f;
+          cs_t[i] = (has_cs_vec && n < p.n) ? __ldg(p.col_scale + goff + n) : 1.0f;
+          bias_t[i] = (has_bias && n < p.n) ? load16(p.bias, goff + n, is_bf16) : 0.0f;
         }
         __syncwarp();
       }
@@ -1368,6 +1371,10 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
     *why = "operand base is not 16-byte aligned";
     return cudaErrorInvalidValue;
   }
+  if (a.rows_per_group != 0 && (a.rows_per_group < 0 || a.rows_per_group % 256 != 0 || a.col_scale_scalar)) {
+    *why = "row groups are multiples of 256 rows with one scale per channel";
+    return cudaErrorInvalidValue;
+  }
   KernelParams kp;
   kp.m = a.m;
   kp.n = a.n;
@@ -1383,6 +1390,7 @@ cudaError_t launch_gemm(const GemmArgs &a, const char **why) {
   kp.bias = a.bias;
   kp.residual = a.residual;
   kp.residual_rows = a.residual_rows > 0 ? a.residual_rows : a.m;
+  kp.rows_per_group = a.rows_per_group;
   kp.residual_ld = a.residual_ld;
   kp.act = a.act;
   kp.row_amax = a.row_amax;

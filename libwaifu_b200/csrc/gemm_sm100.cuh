@@ -52,6 +52,10 @@ struct GemmArgs {
   int residual_rows;           // period of the residual's rows over m (m itself for a full one)
   int64_t residual_ld;
   int act;
+  // Row groups (0: none): rows [g * rows_per_group, (g + 1) * rows_per_group) take col_scale and bias
+  // from row g of (groups, n) matrices instead of from one (n) vector. rows_per_group is a
+  // multiple of 256, so that no tile holds rows of two groups; col_scale is a vector then.
+  int rows_per_group;
   // (m) or NULL: the epilogue takes the maximum of |result| over each row, of the values as rounded to
   // the output type, into this array with atomicMax on the float's bits; the caller zeroes it.
   float *row_amax;

@@ -132,6 +132,8 @@ def lib() -> ctypes.CDLL:
     L.fl_fp8_layernorm_quantize.restype = c_int32
     L.fl_fp8_linear_quantized.argtypes = [V, V, V, V, V, V, c_int32, V]
     L.fl_fp8_linear_quantized.restype = c_int32
+    L.fl_fp8_linear_quantized_grouped.argtypes = [V, V, V, V, V, V, c_int32, c_int32, V]
+    L.fl_fp8_linear_quantized_grouped.restype = c_int32
     L.fl_fp8_swiglu_quantize.argtypes = [V, V, V]
     L.fl_fp8_swiglu_quantize.restype = c_int32
     L.fl_qk_norm_rope.argtypes = [V, V, V, V, V, ctypes.c_float, c_int32]
@@ -652,6 +654,16 @@ def fp8_swiglu_quantize(x: Tensor, codes: Optional[Tensor] = None, row_scales: O
         row_scales = Tensor.empty((rows,), DType.FLOAT)
     check(lib().fl_fp8_swiglu_quantize(x.raw(), codes.raw(), row_scales.raw()))
     return codes, row_scales
+
+
+def fp8_linear_quantized_grouped(codes: Tensor, row_scales: Tensor, weight: Tensor, scales: Tensor, bias: Optional[Tensor],
+                                 residual: Optional[Tensor], act: int, rows_per_group: int, out: Tensor) -> Tensor:
+    """fp8_linear_quantized whose rows come in groups of `rows_per_group` (a multiple of 256), each
+    with its own row of `scales` (groups, n) and `bias` (groups, n)."""
+    check(lib().fl_fp8_linear_quantized_grouped(codes.raw(), row_scales.raw(), weight.raw(), scales.raw(),
+                                                bias.raw() if bias else None, residual.raw() if residual else None,
+                                                int(act), int(rows_per_group), out.raw()))
+    return out
 
 
 def fp8_linear_quantized(codes: Tensor, row_scales: Tensor, weight: Tensor, scales: Tensor, bias: Optional[Tensor],

@@ -147,6 +147,41 @@ def test_few_rows_on_the_tensor_cores_match_the_tile_kernel(flint, oracle):
     assert np.array_equal(out2.numpy(), few)
 
 
+@pytest.mark.parametrize("m,rows_per_group,n,k", [(768, 256, 264, 320), (1152, 512, 520, 3072), (8704, 4352, 3072, 512)])
+def test_row_groups_equal_one_product_per_group(flint, oracle, m, rows_per_group, n, k):
+    """fl_fp8_linear_quantized_grouped: rows in groups, each with its own per-channel scales and bias
+    (a gate per image folded into them). Equal to the last bit to one product per group, and
+    within the path's tolerance of the oracle; a group size that is no multiple of 256 is refused."""
+    F = flint
+    rng = np.random.default_rng(71 + m + n)
+    groups = -(-m // rows_per_group)
+    x = oracle.narrow(randn(rng, (m, k)), True)
+    a_codes, a_scales = oracle.quantize_fp8_act(x, True)
+    w = randn(rng, (n, k), 0.02)
+    wc, ws = oracle.quantize_fp8_rows(w)
+    gate = (0.5 + rng.random((groups, n))).astype(np.float32)
+    scales = (gate * ws[None, :]).astype(np.float32)
+    bias = oracle.narrow(randn(rng, (groups, n), 0.1), True)
+    res = oracle.narrow(randn(rng, (m, n)), True)
+    bf = F.DType.BFLOAT16
+    cd, rsd, wd = dev(F, a_codes, F.DType.FP8E4M3), dev(F, a_scales, F.DType.FLOAT), dev(F, wc, F.DType.FP8E4M3)
+    out = F.Tensor.empty((m, n), bf)
+    F.fp8_linear_quantized_grouped(cd, rsd, wd, dev(F, scales, F.DType.FLOAT), dev(F, bias, bf), dev(F, res, bf), 1,
+                                   rows_per_group, out)
+    got = out.numpy()
+    for g in range(groups):
+        r0, r1 = g * rows_per_group, min(m, (g + 1) * rows_per_group)
+        part = F.Tensor.empty((r1 - r0, n), bf)
+        F.fp8_linear_quantized(dev(F, a_codes[r0:r1], F.DType.FP8E4M3), dev(F, a_scales[r0:r1], F.DType.FLOAT), wd,
+                               dev(F, scales[g], F.DType.FLOAT), dev(F, bias[g], bf), dev(F, res[r0:r1], bf), 1, part)
+        assert np.array_equal(part.numpy(), got[r0:r1]), f"group {g}"
+        want = oracle.fp8_linear_quantized(a_codes[r0:r1], a_scales[r0:r1], wc, scales[g], bias[g], res[r0:r1],
+                                           oracle.ACT_GELU_TANH)
+        check_parity(oracle, got[r0:r1], want, True, what=f"group {g}")
+    with pytest.raises(F.FlintError):
+        F.fp8_linear_quantized_grouped(cd, rsd, wd, dev(F, scales, F.DType.FLOAT), dev(F, bias, bf), dev(F, res, bf), 1, 100, out)
+
+
 def test_few_rows_match_the_tile_path_quantiser(flint, oracle):
     """The in-kernel quantiser of the few-row kernel is the activation quantiser's arithmetic: with
     a weight of exact small integers the two paths (m = 4 and the same rows inside m = 64) agree
