@@ -222,3 +222,30 @@ def test_asynchronous_copy_refuses_every_direction_but_its_own(flint):
     assert L.fl_add(None, src.raw(), src.raw(), src.raw()) == F.FL_ERROR_INVALID_ARG
     assert L.fl_cast(c_void_p(1), src.raw(), src.raw()) == F.FL_ERROR_INVALID_ARG
     assert b"not on the operators' device" in L.fl_get_last_error_message()
+
+
+def test_row_group_refusals(flint):
+    """fl_fp8_linear_quantized_grouped checks its groups before any device work: a group size that is
+    no multiple of 256, scales and bias that are not one row per group."""
+    F = flint
+    L = F.lib()
+    m, n, k, rpg = 512, 8, 32, 256
+    codes = cpu(F, np.zeros((m, k), np.uint8), F.DType.FP8E4M3)
+    rs = cpu(F, np.ones(m, np.float32), F.DType.FLOAT)
+    w = cpu(F, np.zeros((n, k), np.uint8), F.DType.FP8E4M3)
+    scales = cpu(F, np.ones((2, n), np.float32), F.DType.FLOAT)
+    bias = cpu(F, np.zeros((2, n), np.uint16), F.DType.BFLOAT16)
+    out = cpu(F, np.zeros((m, n), np.uint16), F.DType.BFLOAT16)
+
+    def call(scales_v, bias_v, group_rows):
+        return L.fl_fp8_linear_quantized_grouped(codes.raw(), rs.raw(), w.raw(), scales_v.raw(),
+                                                 bias_v.raw() if bias_v is not None else None, None, 0, group_rows, out.raw())
+
+    assert call(scales, bias, 100) == F.FL_ERROR_INVALID_ARG and b"multiple of 256" in L.fl_get_last_error_message()
+    assert call(scales, bias, 0) == F.FL_ERROR_INVALID_ARG and b"multiple of 256" in L.fl_get_last_error_message()
+    one_row = cpu(F, np.ones(n, np.float32), F.DType.FLOAT)
+    assert call(one_row, bias, rpg) == F.FL_ERROR_INVALID_ARG and b"(groups, rows)" in L.fl_get_last_error_message()
+    assert call(scales, cpu(F, np.zeros(n, np.uint16), F.DType.BFLOAT16), rpg) == F.FL_ERROR_INVALID_ARG
+    assert b"(groups, rows)" in L.fl_get_last_error_message()
+    # well-formed groups on CPU operands end where every FP8 entry point ends without a device
+    assert call(scales, bias, rpg) == F.FL_ERROR_INVALID_ARG and b"no FP8 kernels" in L.fl_get_last_error_message()
