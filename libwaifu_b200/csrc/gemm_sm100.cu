@@ -458,7 +458,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issue
-    if (lane == 0 && leader) {
+    // The whole warp of the leader walks the loop and one lane issues: what an instruction takes is
+    // then the same in every lane.
+    if (leader) {
+      const bool issuer = lane == 0;
       // e4m3 is format 0 of kind::f8f6f4; fp16 / bf16 are formats 0 / 1 of kind::f16.
       // (The mixed form exists for half only: both operands of a UMMA share one 16-bit format.)
       constexpr uint32_t kFmt = (KIND == kKindBF16) ? 1u : 0u;
@@ -466,6 +469,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           NVF4 ? umma_idesc_nvf4(kBlockM * CTAS, BLOCK_N) : umma_idesc(kBlockM * CTAS, BLOCK_N, kFmt, kFmt);
       // Hands a barrier (same offset in every CTA of the pair) the completion of the UMMAs so far.
       auto commit_to = [&](uint64_t *bar) {
+        if (!issuer) return;
         if constexpr (CTAS == 2) {
           umma_commit_pair_both(bar);
         } else {
@@ -530,10 +534,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
             for (int j = 0; j < kMmasPerStage; ++j) {
               if constexpr (CTAS == 2) {
-                umma_nvf4_ss_pair(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, ((kb - kb_first) | j) != 0 ? 1u : 0u,
+                if (issuer) umma_nvf4_ss_pair(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, ((kb - kb_first) | j) != 0 ? 1u : 0u,
                                   sfa_tmem + j * 4, sfb_tmem + j * Cfg::kSfbColsPerMma + sfb_skip);
               } else {
-                umma_nvf4_ss(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, ((kb - kb_first) | j) != 0 ? 1u : 0u,
+                if (issuer) umma_nvf4_ss(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, ((kb - kb_first) | j) != 0 ? 1u : 0u,
                              sfa_tmem + j * 4, sfb_tmem + j * Cfg::kSfbColsPerMma + sfb_skip);
               }
             }
@@ -541,9 +545,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
             for (int j = 0; j < kMmasPerStage; ++j) {
               if constexpr (CTAS == 2) {
-                umma_ss_pair<KIND>(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, ((kb - kb_first) | j) != 0 ? 1u : 0u);
+                if (issuer) umma_ss_pair<KIND>(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, ((kb - kb_first) | j) != 0 ? 1u : 0u);
               } else {
-                umma_ss<KIND>(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, ((kb - kb_first) | j) != 0 ? 1u : 0u);
+                if (issuer) umma_ss<KIND>(d_tmem, adesc + j * kMmaStep, bdesc + j * kMmaStep, idesc, ((kb - kb_first) | j) != 0 ? 1u : 0u);
               }
             }
           }
@@ -560,7 +564,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (!ok) break;
         commit_to(&acc_full_bar[acc]);
       }
-      if (!ok) {
+      if (!ok && issuer) {
         abort_flag = 1;
         atomicCAS(p.status, 0u, static_cast<uint32_t>(kStatusMmaTimeout));
       }
