@@ -1109,7 +1109,11 @@ def run_skinny(args):
     traffic = traffic_fields("skinny_decode")
     if linear:
         traffic = traffic_fields("skinny_decode_linear")
-    roofline = {"bound": "hbm", "kernel": "fewrow_q8_kernel" if linear else "fewrow_tc_kernel", "achieved": achieved,
+    if linear:  # (the routes of fl_sm100_few_rows_route: 33 rows and more go to the tile kernel)
+        kernel_name = "fewrow_q8_kernel" if m <= 32 else "gemm_tn_kernel"
+    else:
+        kernel_name = "fewrow_tc_kernel" if m <= 64 else "gemm_tn_kernel"
+    roofline = {"bound": "hbm", "kernel": kernel_name, "achieved": achieved,
                 "peak": hbm_peak, "unit": "GB/s",
                 "frac": achieved / hbm_peak, "peak_source": f"stream copy, of {peak_kind}", "launches": launches,
                 "avg_launch_ms": ms_step, **traffic,
