@@ -218,11 +218,13 @@ FLAPI int32_t fl_fp8_linear(fl_tensor_view_t a, fl_tensor_view_t data, fl_tensor
  * How: the quantised activation (m * k bytes), its m row scales and the kernels' status word live
  * in one fixed device array compiled into the library, about 16.3 MiB, which every GPU that loads
  * the library holds until the process ends. The call makes no cudaMalloc, cudaFree, cudaHostAlloc
- * or other allocating call. Arguments and checks are fl_fp8_linear()'s; the arithmetic is that of
- * fl_fp8_linear()'s tile path (quantiser kernel, then the tcgen05 GEMM) for every row count, so
- * from five rows on the results are bit-identical to fl_fp8_linear()'s, and for one to four rows,
- * where fl_fp8_linear() takes its few-row kernel with another summation order, they agree within
- * the path's tolerance. FLINT_SM100_SINGLE_CTA and fl_sm100_gemm_timing() do not apply here.
+ * or other allocating call. Arguments and checks are fl_fp8_linear()'s; the arithmetic is the
+ * quantiser kernel followed by the product kernel fl_fp8_linear() takes from five rows on (the
+ * tcgen05 tile GEMM, or for at most 32 rows against a wide weight the few-row tensor-core kernel)
+ * for every row count, so from five rows on the results are bit-identical to fl_fp8_linear()'s, and
+ * for one to four rows, where fl_fp8_linear() may take a one-launch few-row kernel with another
+ * summation order, they agree within the path's tolerance. FLINT_SM100_SINGLE_CTA and
+ * fl_sm100_gemm_timing() do not apply here.
  *
  * Limits, refused with FL_ERROR_INVALID_ARG before anything is launched: at most 65536 activation
  * rows (the product of a's leading dimensions), at most 16 Mi elements in m * k (4352 x 3072 fits),

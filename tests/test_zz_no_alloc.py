@@ -66,8 +66,9 @@ def test_static_entry_point_refuses_what_does_not_fit(flint, oracle):
 
 
 def test_static_entry_point_with_a_few_rows_matches_the_oracle(flint, oracle):
-    """For one to four rows fl_fp8_linear takes its few-row kernel, whose summation order differs;
-    the static entry point stays on the tile path, so here it is held to the oracle instead."""
+    """For one to four rows against a narrow weight fl_fp8_linear takes its one-launch few-row
+    kernel, whose summation order differs; the static entry point runs the quantiser and the tile
+    kernel, so here it is held to the oracle instead."""
     F = flint
     rng = np.random.default_rng(2025)
     bf = F.DType.BFLOAT16
